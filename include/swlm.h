@@ -1,0 +1,163 @@
+/*
+ * swlm.h — C ABI of libswlm_cuda.so, a CUDA (sm_100a) dispatch-plan backend for
+ * swift-lm's 4-bit decode/prefill hot path.
+ *
+ * The reference has no FFI of its own: its seams are Swift types. Each entry
+ * point below names the Swift interface it stands in for (paths relative to the
+ * reference project root).
+ *
+ * Conventions: every function returns 0 (SWLM_OK) or a negative status and never
+ * throws or aborts; the message for the last failure is read with
+ * swlm_last_error(). Weights belong to a `swlm_ctx` and are immutable and shared;
+ * runtime buffers belong to a `swlm_state`, one per generation context, and a
+ * state must not be used from two threads at once (the reference gives every
+ * LanguageModelContext its own clone of the runtime buffers —
+ * Sources/MetalCompiler/Execution/MetalCompiledModelRuntimeIsolation.swift:28-110).
+ * There is no CPU fallback: without a CUDA device every call that needs one fails.
+ */
+#ifndef SWLM_H
+#define SWLM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "swlm_plan.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SWLM_OK 0
+#define SWLM_ERR_INVALID (-1)     /* bad argument / shape */
+#define SWLM_ERR_CUDA (-2)        /* a CUDA runtime call failed */
+#define SWLM_ERR_NOT_FOUND (-3)   /* tensor name not in the weight store */
+#define SWLM_ERR_UNSUPPORTED (-4) /* step kind / format outside the hot path */
+#define SWLM_ERR_TIMEOUT (-5)     /* a bounded device-side wait expired */
+#define SWLM_ERR_STATE (-6)       /* call not valid in the current state */
+
+/* How a tensor is cut when ctx was created with tp_size > 1 (Megatron style). */
+#define SWLM_SHARD_REPLICATE 0
+#define SWLM_SHARD_COLUMN 1 /* split output rows N; result stays sharded */
+#define SWLM_SHARD_ROW 2    /* split input columns K on 64-element group boundaries; result needs an all-reduce */
+#define SWLM_SHARD_COLUMN3 3 /* N = three equal thirds (B|C|x of LFM2 in_proj), each split on its own */
+
+typedef struct swlm_ctx swlm_ctx;
+typedef struct swlm_plan swlm_plan;
+typedef struct swlm_state swlm_state;
+typedef struct swlm_snap swlm_snap;
+
+const char* swlm_version(void);
+int swlm_device_count(void);
+/* Message of the most recent failure on this thread. */
+const char* swlm_last_error(void);
+
+/* ---- context + weight store ------------------------------------------------
+ * Replaces STAFLoader.load(at:device:) -> STAFWeightStore
+ * (Sources/MetalCompiler/STAF/STAFLoader.swift:19-198, :213-299): a name ->
+ * device tensor map. Quantized tensors are re-tiled once, at upload, into the
+ * layout the GEMV kernels stream. */
+int swlm_ctx_create(int device_id, int tp_rank, int tp_size, swlm_ctx** out);
+void swlm_ctx_destroy(swlm_ctx* ctx);
+
+/* MLX affine source format: weight u32[n][k/8] (8 nibbles per word, LSB first
+ * along K), scales/biases bf16 [n][k/64]
+ * (Sources/MetalCompiler/STAF/STAFPayloadConverter.swift:209-282). */
+int swlm_weights_add_q4g64_mlx(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* weight,
+                               const uint16_t* scales_bf16, const uint16_t* biases_bf16, int shard_kind);
+/* STAF execution blocks, 36 bytes per 64 weights: fp16 scale | fp16 zero | 32 payload bytes
+ * (Sources/MetalCompiler/STAF/QuantizationFormat.swift:463-528). */
+int swlm_weights_add_q4g64_staf(swlm_ctx* ctx, const char* name, int n, int k, const void* blocks36,
+                                int shard_kind);
+/* Dense bf16 tensor (norm weights, embedding table, conv weights). `count` elements;
+ * rows/cols describe a 2-D view when shard_kind != replicate (cols = count / rows). */
+int swlm_weights_add_dense_bf16(swlm_ctx* ctx, const char* name, int64_t rows, int64_t cols,
+                                const uint16_t* data, int shard_kind);
+/* Total bytes of weights resident on the device for this context. */
+int64_t swlm_weights_bytes(const swlm_ctx* ctx);
+
+/* ---- plan --------------------------------------------------------------------
+ * Replaces MetalInferenceCompiler.compile(...) -> MetalCompiledModel.decodePlan
+ * (Sources/MetalCompiler/Compiler/MetalInferenceCompiler.swift:520-615) and
+ * MetalDispatchStepBuilder.buildDecodePlan (Compiler/MetalDispatchStepBuilder.swift:4-105):
+ * resolves tensor names, fuses adjacent steps into launches and sizes the buffer set. */
+int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const swlm_buffers_desc* desc,
+                    swlm_plan** out);
+void swlm_plan_destroy(swlm_plan* plan);
+/* Number of kernel launches one decode step issues after fusion. */
+int swlm_plan_launch_count(const swlm_plan* plan);
+/* Human-readable launch list, the counterpart of the reference's decode diagnostics
+ * (Execution/MetalDecodePlan.swift:122-133). Returns bytes needed, copies at most cap. */
+int swlm_plan_describe(const swlm_plan* plan, char* dst, int cap);
+
+/* ---- runtime state -------------------------------------------------------------
+ * Replaces MetalInferenceModel(plan:device:) and its buffer set
+ * (Sources/MetalCompiler/Execution/MetalInferenceModel.swift; MetalDecodePlan.swift MetalBufferSet). */
+int swlm_state_create(swlm_plan* plan, swlm_state** out);
+void swlm_state_destroy(swlm_state* state);
+/* Launch on this CUDA stream (a cudaStream_t) instead of the state's own. */
+int swlm_state_set_stream(swlm_state* state, void* cuda_stream);
+/* resetState() — MetalInferenceModel.swift:1911. */
+int swlm_state_reset(swlm_state* state);
+/* promptSnapshot / restore — Execution/MetalPromptStateStore.swift:5-137. */
+int swlm_state_snapshot(swlm_state* state, swlm_snap** out);
+int swlm_state_restore(swlm_state* state, const swlm_snap* snap);
+void swlm_snap_destroy(swlm_snap* snap);
+/* `position` — MetalInferenceModel.swift:9. */
+int swlm_position(const swlm_state* state);
+
+/* prefill(tokens:) -> first generated token — MetalInferenceModel.swift:464-526.
+ * tokens is [max_batch][n] int32 on the host; first_token receives max_batch values.
+ * Returns a negative status on failure and sets first_token[*] = -1 (the reference
+ * signals a failed submission with token -1, Execution/MetalDecodeExecutor.swift:33-42). */
+int swlm_prefill(swlm_state* state, const int32_t* tokens, int n, int32_t* first_token);
+/* decode(tokenID:) -> next token — MetalInferenceModel.swift:311-322,
+ * Execution/MetalDecodeExecutor.swift:7-43. One host round trip per token, as in the reference. */
+int swlm_decode(swlm_state* state, const int32_t* token_in, int32_t* token_out);
+/* n greedy steps without host round trips: token_out of step i feeds step i+1 on the
+ * device. tokens_out is [n][max_batch]. No counterpart in the reference, which
+ * synchronises every token (Execution/MetalSubmissionContext.swift:56-124). */
+int swlm_decode_n(swlm_state* state, const int32_t* token_in, int n, int32_t* tokens_out);
+/* Same loop, enqueue only: tokens stay in a device ring, read later with swlm_read_tokens. */
+int swlm_decode_n_async(swlm_state* state, const int32_t* token_in_or_null, int n);
+int swlm_read_tokens(swlm_state* state, int n, int32_t* tokens_out);
+int swlm_sync(swlm_state* state);
+/* decodePlan.buffers.logits for host-side sampling
+ * (Sources/SwiftLM/LanguageModelContext.swift:2197-2209): bf16 [max_batch][vocab]. */
+int swlm_read_logits(swlm_state* state, uint16_t* dst, size_t count);
+/* Copy a logical buffer (SWLM_BUF_*) to the host: [max_batch][count_per_row] bf16.
+ * Counterpart of the reference's binding probes (MetalInferenceModel.swift:59-62). */
+int swlm_read_buffer(swlm_state* state, int buf, uint16_t* dst, int count_per_row);
+int swlm_write_buffer(swlm_state* state, int buf, const uint16_t* src, int count_per_row);
+/* K (which=0) or V (which=1) rows [count][head_dim] bf16 of one KV slab / sequence / head. */
+int swlm_read_kv(swlm_state* state, int which, int layer, int b, int head, int count, uint16_t* dst);
+int swlm_write_kv(swlm_state* state, int which, int layer, int b, int head, int count, const uint16_t* src);
+int swlm_read_conv(swlm_state* state, int layer, int b, uint16_t* dst);
+int swlm_set_position(swlm_state* state, int position);
+/* Execute one plan step on the current buffers (kernel-level parity tests). */
+int swlm_run_step(swlm_state* state, const swlm_step* step, const int32_t* token_in, int32_t* token_out);
+/* Kernel launches issued by this state since creation. */
+int64_t swlm_launches(const swlm_state* state);
+
+/* ---- op-level entry points (host buffers; copies are part of the call) ----------
+ * Y[m][n] = bf16(X[m][k] . W^T): gemv_q4_g64 for m = 1
+ * (Generator/MetalSourceGenerator+Quantized.swift:496-575), gemm_q4_g64 for m > 1 (:88-156). */
+int swlm_op_qgemm(swlm_ctx* ctx, const char* weight, int m, const uint16_t* x_bf16, uint16_t* y_bf16);
+/* Device-pointer form: x [m][k] and y [m][n] bf16 already resident; enqueued on
+ * `cuda_stream` (NULL = the context's stream) without synchronising. */
+int swlm_op_qgemm_dev(swlm_ctx* ctx, const char* weight, int m, const void* x_dev, void* y_dev,
+                      void* cuda_stream);
+/* generateUnifiedDequantToBFloat (Generator/MetalSourceGenerator+Quantized.swift:361-416):
+ * the stored tensor unpacked to bf16 [n][k] on the host, from the device layout. */
+int swlm_op_dequant_bf16(swlm_ctx* ctx, const char* weight, uint16_t* out_bf16);
+/* Flash-decode over caller-provided device tensors: q [b][heads][hd] (RoPE already applied),
+ * k,v [b][kv_heads][ctx_stride][hd] bf16, attends over [0, ctx_len); out [b][heads][hd] bf16.
+ * scratch_dev needs swlm_op_flash_decode_scratch_bytes(). */
+size_t swlm_op_flash_decode_scratch_bytes(int b, int heads, int kv_heads, int hd, int ctx_len);
+int swlm_op_flash_decode_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int hd, int ctx_len,
+                             int ctx_stride, float scale, const void* q_dev, const void* k_dev,
+                             const void* v_dev, void* out_dev, void* scratch_dev, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SWLM_H */

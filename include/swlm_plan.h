@@ -1,0 +1,121 @@
+/*
+ * swlm_plan.h — the execution record shared by the host and the CUDA backend.
+ *
+ * A plan is a flat array of `swlm_step` records, one per reference dispatch.
+ * It replaces the reference's `MetalDispatchStep` / `MetalDispatchPlan`
+ * (Sources/MetalCompiler/Execution/MetalDecodePlan.swift:6-193): where the
+ * reference stores {pipeline, grid, buffer bindings, constants}, a step here
+ * stores {operation kind, logical buffer slots, tensor names, dimensions}.
+ * The backend is free to fuse adjacent steps into one launch as long as every
+ * value that the reference stores to a decode buffer is rounded to bf16 at the
+ * same point.
+ *
+ * Logical buffers follow the reference's decode buffer set
+ * (Sources/MetalCompiler/Buffer/MetalBufferAllocator.swift:4-132): `hidden`,
+ * `residual`, five scratch slots of `slot_dim` elements, `logits`, all bf16,
+ * one row per sequence of the batch.
+ */
+#ifndef SWLM_PLAN_H
+#define SWLM_PLAN_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SWLM_NAME_MAX 96
+
+/* Logical buffer ids used by swlm_step.in_buf / in2_buf / out_buf. */
+enum {
+    SWLM_BUF_NONE = -1,
+    SWLM_BUF_HIDDEN = 0,
+    SWLM_BUF_RESIDUAL = 1,
+    SWLM_BUF_SCRATCH0 = 2, /* block output: attention / conv / swiglu result, norm output */
+    SWLM_BUF_SCRATCH1 = 3, /* q, gate, packed B|C|x */
+    SWLM_BUF_SCRATCH2 = 4, /* k, up */
+    SWLM_BUF_SCRATCH3 = 5, /* v */
+    SWLM_BUF_SCRATCH4 = 6,
+    SWLM_BUF_LOGITS = 7,
+    SWLM_BUF_COUNT = 8
+};
+
+/* Step kinds. The comment names the reference kernel each one stands for. */
+enum {
+    /* embedding_lookup_bf16 — Generator/MetalSourceGenerator+Embedding.swift:3-48.
+       hidden[b] = table[token_in[b]]; weight = table [vocab, n] bf16. */
+    SWLM_STEP_EMBED = 1,
+    /* fused_copy_rms_norm — Primitives/Reduction.swift:74-115 + CopyFragment.
+       residual = in; out = bf16(in * rsqrt(mean(in^2)+eps) * (w + weight_bias)). */
+    SWLM_STEP_COPY_RMSNORM = 2,
+    /* fused_residual_add_copy_rms_norm — Compiler/MetalEntryCollector.swift:143-218.
+       h = float(in) + float(residual); residual = bf16(h);
+       out = bf16(h * rsqrt(mean(h^2)+eps) * (w + weight_bias)). */
+    SWLM_STEP_RESADD_COPY_RMSNORM = 3,
+    /* fused_residual_add_rms_norm (final norm): as above without the residual store. */
+    SWLM_STEP_RESADD_RMSNORM = 4,
+    /* gemv_q4_g64 — Generator/MetalSourceGenerator+Quantized.swift:496-575.
+       out[n] = bf16(sum_k (scale*q + zero) * in[k]), fp32 accumulation. */
+    SWLM_STEP_QGEMV = 5,
+    /* batched_qk_rms_norm_2 — Generator/MetalSourceGenerator+Batched.swift:681-760.
+       per-head RMSNorm of q (in_buf, `heads`) with `weight` and of k (in2_buf,
+       `kv_heads`) with `weight2`, in place. */
+    SWLM_STEP_QK_NORM = 6,
+    /* rope_flash_attn_decode — Generator/MetalSourceGenerator+Attention.swift:551-930.
+       q = in_buf, k = in2_buf, v = in3_buf, result = out_buf. Inline rotate-half
+       RoPE on q and the new k, append k,v at `position`, attend over [0, position]. */
+    SWLM_STEP_ATTN_DECODE = 7,
+    /* swiglu — Primitives/ElementwiseFragment.swift:49-54.
+       out = bf16(g/(1+exp(-g)) * up), g = in_buf, up = in2_buf. */
+    SWLM_STEP_SWIGLU = 8,
+    /* conv_state_update_bf16 — Generator/MetalSourceGenerator+ConvAndState.swift:27-70.
+       in_buf holds B|C|x (3*n); state [conv_kernel][n] bf16; weight [n][conv_kernel] bf16. */
+    SWLM_STEP_CONV_STATE_UPDATE = 9,
+    /* argmax — Generator/MetalSourceGenerator+Sampling.swift:62-107; lowest index
+       wins among equal maxima. token_out[b] = argmax(in_buf[b][0..n)). */
+    SWLM_STEP_ARGMAX = 10
+};
+
+typedef struct swlm_step {
+    int32_t kind;
+    int32_t layer;       /* index of the KV-cache / conv-state slab this step owns, else -1 */
+    int32_t in_buf;
+    int32_t in2_buf;
+    int32_t in3_buf;
+    int32_t out_buf;
+    int32_t n;           /* output width (rows of the weight) / vector dimension */
+    int32_t k;           /* input width (columns of the weight) */
+    int32_t heads;
+    int32_t kv_heads;
+    int32_t head_dim;
+    int32_t rope_dim;    /* 0 = no RoPE */
+    int32_t conv_kernel;
+    float   eps;
+    float   weight_bias;
+    float   scale;       /* attention scale */
+    float   rope_base;
+    char    weight[SWLM_NAME_MAX];
+    char    weight2[SWLM_NAME_MAX];
+} swlm_step;
+
+/* Sizes of the runtime buffer set; mirrors the inputs of
+   MetalBufferAllocator.makeDecodeBufferAllocation (Buffer/MetalBufferAllocator.swift:4-132)
+   and KVCacheSpecification (Buffer/MetalGraphAllocator.swift:15-223). */
+typedef struct swlm_buffers_desc {
+    int32_t hidden;       /* hidden size */
+    int32_t slot_dim;     /* elements per scratch slot */
+    int32_t vocab;
+    int32_t max_seq;      /* KV slots per sequence (maximumSequenceLength) */
+    int32_t max_batch;    /* sequences decoded together; the reference is 1 */
+    int32_t kv_layers;    /* number of attention layers (KV slabs) */
+    int32_t kv_heads;
+    int32_t head_dim;
+    int32_t conv_layers;  /* number of short-conv layers (state slabs) */
+    int32_t conv_dim;
+    int32_t conv_kernel;
+} swlm_buffers_desc;
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SWLM_PLAN_H */

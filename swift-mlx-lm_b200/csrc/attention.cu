@@ -1,0 +1,405 @@
+// Flash-decode GQA attention over a bf16 KV cache for sm_100a.
+//
+// Replaces `rope_flash_attn_decode` (Generator/MetalSourceGenerator+Attention.swift:551-930): the
+// reference runs one 32-thread group per query head that walks the context sequentially and re-reads
+// the K/V rows of a GQA group once per query head. Here
+//   * the KV range is split across CTAs (flash-decode); a second small kernel merges the partial
+//     (max, sum, output) triples;
+//   * one CTA serves all query heads of a KV head, so K/V are read once per group;
+//   * QK^T and PV run on the tensor cores (mma.m16n8k16, bf16 in, fp32 accumulate) with the head
+//     dimension permuted so that every lane fetches K and V with 128-bit loads and no shared memory:
+//     the contraction over d is order-independent, and for PV two tokens' values of one dimension are
+//     paired into a B-fragment register with one PRMT;
+//   * q is rotated (RoPE) in fp32 and fed to the tensor core as a bf16 hi + lo pair, so it keeps
+//     ~16 bits of mantissa (the reference keeps the rotated q in fp32);
+//   * the current token is not read back from the cache: the merge kernel adds its term in fp32 from
+//     the unrounded rotated k and v, exactly as the reference does (:866-868, :905-907), while the
+//     bf16-rounded copy is appended to the cache for later steps (:761-805).
+#include <cmath>
+
+#include "swlm_internal.h"
+
+namespace swlm {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kSplitWarps = 4;
+constexpr int kSplitThreads = kSplitWarps * 32;
+constexpr int kMaxGroup = 8;  // query heads per KV head served by one CTA
+
+struct AttnParams {
+    int heads, kv_heads, rope_dim, max_seq, splits;
+    float scale_log2;  // attention scale * log2(e)
+    const float* inv_freq;
+    const __nv_bfloat16* q; int q_stride;
+    const __nv_bfloat16* k; int k_stride;
+    const __nv_bfloat16* v; int v_stride;
+    __nv_bfloat16* kcache;
+    __nv_bfloat16* vcache;
+    size_t cache_seq_stride;   // elements between sequences
+    size_t cache_head_stride;  // elements between KV heads
+    const int32_t* position;   // decode: device scalar; plain: nullptr
+    int ctx_len;               // plain: number of cached tokens
+    __nv_bfloat16* out; int out_stride;
+    float* part_o;   // [m][heads][splits][HD]
+    float* part_ml;  // [m][heads][splits][2]
+};
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ uint4 ldg128(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// rotate-half RoPE of element d of a vector held in shared memory
+// (Generator/MetalSourceGenerator+Attention.swift:596-617): pairs (i, i + ropeDim/2).
+__device__ __forceinline__ float rope_elem(const float* v, int d, int rope_dim, const float* cs, const float* sn) {
+    const int pairs = rope_dim >> 1;
+    if (d < pairs) return v[d] * cs[d] - v[d + pairs] * sn[d];
+    if (d < rope_dim) return v[d - pairs] * sn[d - pairs] + v[d] * cs[d - pairs];
+    return v[d];
+}
+
+template <int HD, bool DECODE>
+__global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnParams p) {
+    constexpr int NCH = HD / 32;  // 16-byte K chunks per lane per token
+    constexpr int VH = HD / 64;   // 64-dimension halves of V
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int G = p.heads / p.kv_heads;
+    const int n_ctx = DECODE ? p.position[0] : p.ctx_len;  // cached tokens to attend (excludes the new one)
+
+    __shared__ float qrot[kMaxGroup][HD];
+    __shared__ float vec[HD];
+    __shared__ float cs[HD / 2], sn[HD / 2];
+    __shared__ float osm[kSplitWarps][kMaxGroup][HD + 4];
+    __shared__ float msm[kSplitWarps][kMaxGroup], lsm[kSplitWarps][kMaxGroup];
+
+    const __nv_bfloat16* kbase = p.kcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride;
+    const __nv_bfloat16* vbase = p.vcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride;
+
+    // ---- prologue: q (and, in split 0, the new k/v) ---------------------------------------------
+    if (DECODE) {
+        const int pairs = p.rope_dim >> 1;
+        for (int i = tid; i < pairs; i += kSplitThreads) {
+            float s, c;
+            sincosf((float)n_ctx * p.inv_freq[i], &s, &c);
+            cs[i] = c; sn[i] = s;
+        }
+        if (split == 0 && n_ctx < p.max_seq) {
+            for (int d = tid; d < HD; d += kSplitThreads) vec[d] = __bfloat162float(p.k[(size_t)b * p.k_stride + kvh * HD + d]);
+        }
+        __syncthreads();
+        if (split == 0 && n_ctx < p.max_seq) {
+            __nv_bfloat16* kw = p.kcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD;
+            __nv_bfloat16* vw = p.vcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD;
+            for (int d = tid; d < HD; d += kSplitThreads) {
+                kw[d] = __float2bfloat16_rn(rope_elem(vec, d, p.rope_dim, cs, sn));
+                vw[d] = p.v[(size_t)b * p.v_stride + kvh * HD + d];
+            }
+        }
+    }
+    // unrotated q into shared memory, then rotate in place through registers
+    for (int idx = tid; idx < G * HD; idx += kSplitThreads) {
+        const int r = idx / HD, d = idx - r * HD;
+        qrot[r][d] = __bfloat162float(p.q[(size_t)b * p.q_stride + (size_t)(kvh * G + r) * HD + d]);
+    }
+    __syncthreads();
+    if (DECODE && p.rope_dim > 0) {
+        float tmp[(kMaxGroup * HD + kSplitThreads - 1) / kSplitThreads];
+        int c = 0;
+        for (int idx = tid; idx < G * HD; idx += kSplitThreads, ++c) {
+            const int r = idx / HD, d = idx - r * HD;
+            tmp[c] = rope_elem(qrot[r], d, p.rope_dim, cs, sn);
+        }
+        __syncthreads();
+        c = 0;
+        for (int idx = tid; idx < G * HD; idx += kSplitThreads, ++c) {
+            const int r = idx / HD, d = idx - r * HD;
+            qrot[r][d] = tmp[c];
+        }
+        __syncthreads();
+    }
+
+    // A fragments of q: lane (g, t) holds q[g][32*i + 8*t + 0..7]; hi + lo bf16 split
+    unsigned qhi[NCH][4], qlo[NCH][4];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            float a = 0.f, c = 0.f;
+            if (g < G) { a = qrot[g][32 * i + 8 * t + 2 * w]; c = qrot[g][32 * i + 8 * t + 2 * w + 1]; }
+            const float ah = __bfloat162float(__float2bfloat16_rn(a)), ch = __bfloat162float(__float2bfloat16_rn(c));
+            qhi[i][w] = pack_bf16(ah, ch);
+            qlo[i][w] = pack_bf16(a - ah, c - ch);
+        }
+
+    // ---- token range of this split ----------------------------------------------------------------
+    int chunk = (n_ctx + p.splits - 1) / p.splits;
+    chunk = ((chunk + 63) / 64) * 64;
+    const int t_begin = split * chunk;
+    const int t_end = min(n_ctx, t_begin + chunk);
+
+    float m_run = -INFINITY, l_run = 0.f;
+    float oacc[VH][8][4];
+#pragma unroll
+    for (int hh = 0; hh < VH; ++hh)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) oacc[hh][u][0] = oacc[hh][u][1] = oacc[hh][u][2] = oacc[hh][u][3] = 0.f;
+
+    for (int tok0 = t_begin + warp * 16; tok0 < t_end; tok0 += kSplitWarps * 16) {
+        const int last = t_end - 1;
+        uint4 kreg[2][NCH];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int tok = min(tok0 + 8 * nt + g, last);
+            const __nv_bfloat16* rowp = kbase + (size_t)tok * HD;
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) kreg[nt][i] = ldg128(rowp + (4 * i + t) * 8);
+        }
+        uint4 va[VH], vb[VH], vc[VH], vd[VH];
+        {
+            const __nv_bfloat16* ra = vbase + (size_t)min(tok0 + 2 * t, last) * HD + 8 * g;
+            const __nv_bfloat16* rb = vbase + (size_t)min(tok0 + 2 * t + 1, last) * HD + 8 * g;
+            const __nv_bfloat16* rc = vbase + (size_t)min(tok0 + 2 * t + 8, last) * HD + 8 * g;
+            const __nv_bfloat16* rd = vbase + (size_t)min(tok0 + 2 * t + 9, last) * HD + 8 * g;
+#pragma unroll
+            for (int hh = 0; hh < VH; ++hh) {
+                va[hh] = ldg128(ra + 64 * hh); vb[hh] = ldg128(rb + 64 * hh);
+                vc[hh] = ldg128(rc + 64 * hh); vd[hh] = ldg128(rd + 64 * hh);
+            }
+        }
+        // S = q . K^T for 16 tokens
+        float sacc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const uint4 kk = kreg[nt][i];
+                mma_bf16(sacc[nt], qhi[i][0], 0u, qhi[i][1], 0u, kk.x, kk.y);
+                mma_bf16(sacc[nt], qhi[i][2], 0u, qhi[i][3], 0u, kk.z, kk.w);
+                if (DECODE) {
+                    mma_bf16(sacc[nt], qlo[i][0], 0u, qlo[i][1], 0u, kk.x, kk.y);
+                    mma_bf16(sacc[nt], qlo[i][2], 0u, qlo[i][3], 0u, kk.z, kk.w);
+                }
+            }
+        }
+        // online softmax in the log2 domain; row g lives in the four lanes t = 0..3
+        float sv[2][2];
+        float rmax = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = tok0 + 8 * nt + 2 * t + e;
+                sv[nt][e] = tok < t_end ? sacc[nt][e] * p.scale_log2 : -INFINITY;
+                rmax = fmaxf(rmax, sv[nt][e]);
+            }
+        rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+        rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+        const float m_new = fmaxf(m_run, rmax);
+        const float corr = exp2f(m_run - m_new);
+        float pv[2][2];
+        float psum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) { pv[nt][e] = exp2f(sv[nt][e] - m_new); psum += pv[nt][e]; }
+        l_run = l_run * corr + psum;
+        m_run = m_new;
+        if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+            for (int hh = 0; hh < VH; ++hh)
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { oacc[hh][u][0] *= corr; oacc[hh][u][1] *= corr; }
+        }
+        // O += P . V ; dimension 64*hh + 8*col + u sits in n-tile (hh, u), column col
+        const unsigned pa0 = pack_bf16(pv[0][0], pv[0][1]);
+        const unsigned pa2 = pack_bf16(pv[1][0], pv[1][1]);
+#pragma unroll
+        for (int hh = 0; hh < VH; ++hh) {
+            const unsigned aw[4] = {va[hh].x, va[hh].y, va[hh].z, va[hh].w};
+            const unsigned bw[4] = {vb[hh].x, vb[hh].y, vb[hh].z, vb[hh].w};
+            const unsigned cw[4] = {vc[hh].x, vc[hh].y, vc[hh].z, vc[hh].w};
+            const unsigned dw[4] = {vd[hh].x, vd[hh].y, vd[hh].z, vd[hh].w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                mma_bf16(oacc[hh][2 * w], pa0, 0u, pa2, 0u, __byte_perm(aw[w], bw[w], 0x5410), __byte_perm(cw[w], dw[w], 0x5410));
+                mma_bf16(oacc[hh][2 * w + 1], pa0, 0u, pa2, 0u, __byte_perm(aw[w], bw[w], 0x7632), __byte_perm(cw[w], dw[w], 0x7632));
+            }
+        }
+    }
+
+    // ---- merge the warps of this CTA ---------------------------------------------------------------
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (g < G) {
+#pragma unroll
+        for (int hh = 0; hh < VH; ++hh)
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                osm[warp][g][64 * hh + 8 * (2 * t) + u] = oacc[hh][u][0];
+                osm[warp][g][64 * hh + 8 * (2 * t + 1) + u] = oacc[hh][u][1];
+            }
+        if (t == 0) { msm[warp][g] = m_run; lsm[warp][g] = l_run; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += kSplitThreads) {
+        const int r = idx / HD, d = idx - r * HD;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kSplitWarps; ++w) mx = fmaxf(mx, msm[w][r]);
+        float o = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kSplitWarps; ++w) {
+            const float wgt = msm[w][r] == -INFINITY ? 0.f : exp2f(msm[w][r] - mx);
+            o = fmaf(wgt, osm[w][r][d], o);
+            l = fmaf(wgt, lsm[w][r], l);
+        }
+        const size_t slot = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits + split;
+        p.part_o[slot * HD + d] = o;
+        if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
+    }
+}
+
+// One CTA per (query head, sequence), one thread per output dimension.
+template <int HD, bool DECODE>
+__global__ void __launch_bounds__(HD) attn_combine_kernel(const AttnParams p) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const int kvh = h * p.kv_heads / p.heads;
+    __shared__ float qv[HD], kv[HD];
+    __shared__ float cs[HD / 2], sn[HD / 2];
+    __shared__ float red[HD / 32];
+
+    float m_self = -INFINITY, v_self = 0.f;
+    if (DECODE) {
+        const int pos = p.position[0];
+        if (d < (p.rope_dim >> 1)) {
+            float s, c;
+            sincosf((float)pos * p.inv_freq[d], &s, &c);
+            cs[d] = c; sn[d] = s;
+        }
+        qv[d] = __bfloat162float(p.q[(size_t)b * p.q_stride + (size_t)h * HD + d]);
+        kv[d] = __bfloat162float(p.k[(size_t)b * p.k_stride + (size_t)kvh * HD + d]);
+        __syncthreads();
+        float prod = rope_elem(qv, d, p.rope_dim, cs, sn) * rope_elem(kv, d, p.rope_dim, cs, sn);
+        for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
+        if ((d & 31) == 0) red[d >> 5] = prod;
+        __syncthreads();
+        float score = 0.f;
+#pragma unroll
+        for (int w = 0; w < HD / 32; ++w) score += red[w];
+        m_self = score * p.scale_log2;
+        v_self = __bfloat162float(p.v[(size_t)b * p.v_stride + (size_t)kvh * HD + d]);
+    }
+    const size_t base = ((size_t)b * p.heads + h) * p.splits;
+    float mx = m_self;
+    for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, p.part_ml[(base + s) * 2]);
+    float num = 0.f, den = 0.f;
+    if (DECODE) { const float w = exp2f(m_self - mx); num = w * v_self; den = w; }
+    for (int s = 0; s < p.splits; ++s) {
+        const float ms = p.part_ml[(base + s) * 2];
+        if (ms == -INFINITY) continue;
+        const float w = exp2f(ms - mx);
+        num = fmaf(w, p.part_o[(base + s) * HD + d], num);
+        den = fmaf(w, p.part_ml[(base + s) * 2 + 1], den);
+    }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    p.out[(size_t)b * p.out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(num * inv);
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    return SWLM_OK;
+}
+
+template <bool DECODE>
+int launch_both(const AttnParams& p, int m, int hd, cudaStream_t s) {
+    const dim3 grid(p.splits, p.kv_heads, m);
+    const dim3 cgrid(p.heads, m);
+    if (hd == 128) {
+        attn_split_kernel<128, DECODE><<<grid, kSplitThreads, 0, s>>>(p);
+        attn_combine_kernel<128, DECODE><<<cgrid, 128, 0, s>>>(p);
+    } else if (hd == 64) {
+        attn_split_kernel<64, DECODE><<<grid, kSplitThreads, 0, s>>>(p);
+        attn_combine_kernel<64, DECODE><<<cgrid, 64, 0, s>>>(p);
+    } else {
+        set_error("attention: head_dim %d not supported (64 or 128)", hd);
+        return SWLM_ERR_UNSUPPORTED;
+    }
+    return check_launch("attention launch");
+}
+
+}  // namespace
+
+int attn_init() { return SWLM_OK; }
+
+int attn_pick_splits(int m, int kv_heads, int max_ctx) {
+    int s = 300 / (m * kv_heads);
+    const int cap = max_ctx / 128;
+    if (s > 32) s = 32;
+    if (s > cap) s = cap;
+    if (s < 1) s = 1;
+    return s;
+}
+
+size_t attn_scratch_floats(int m, int heads, int head_dim, int splits) {
+    return (size_t)m * heads * splits * (head_dim + 2);
+}
+
+static int check_group(int heads, int kv_heads) {
+    if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > kMaxGroup) {
+        set_error("attention: %d query heads per KV head not supported (max %d)", kv_heads ? heads / kv_heads : 0, kMaxGroup);
+        return SWLM_ERR_UNSUPPORTED;
+    }
+    return SWLM_OK;
+}
+
+int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
+    int rc = check_group(a.heads, a.kv_heads);
+    if (rc) return rc;
+    if (a.rope_dim > a.head_dim || (a.rope_dim & 1)) { set_error("attention: bad rope_dim"); return SWLM_ERR_INVALID; }
+    AttnParams p{};
+    p.heads = a.heads; p.kv_heads = a.kv_heads; p.rope_dim = a.rope_dim; p.max_seq = a.max_seq; p.splits = a.splits;
+    p.scale_log2 = a.scale * kLog2e;
+    p.inv_freq = a.inv_freq;
+    p.q = a.q; p.q_stride = a.q_stride; p.k = a.k; p.k_stride = a.k_stride; p.v = a.v; p.v_stride = a.v_stride;
+    p.kcache = a.kcache; p.vcache = a.vcache;
+    p.cache_head_stride = (size_t)a.max_seq * a.head_dim;
+    p.cache_seq_stride = p.cache_head_stride * a.kv_heads;
+    p.position = a.position; p.ctx_len = 0;
+    p.out = a.out; p.out_stride = a.out_stride;
+    p.part_o = a.scratch;
+    p.part_ml = a.scratch + (size_t)a.m * a.heads * a.splits * a.head_dim;
+    return launch_both<true>(p, a.m, a.head_dim, s);
+}
+
+int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, float scale,
+                              const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                              __nv_bfloat16* out, float* scratch, int splits, cudaStream_t s) {
+    int rc = check_group(heads, kv_heads);
+    if (rc) return rc;
+    AttnParams p{};
+    p.heads = heads; p.kv_heads = kv_heads; p.rope_dim = 0; p.max_seq = ctx_stride; p.splits = splits;
+    p.scale_log2 = scale * kLog2e;
+    p.q = q; p.q_stride = heads * hd;
+    p.kcache = const_cast<__nv_bfloat16*>(k); p.vcache = const_cast<__nv_bfloat16*>(v);
+    p.cache_head_stride = (size_t)ctx_stride * hd;
+    p.cache_seq_stride = p.cache_head_stride * kv_heads;
+    p.position = nullptr; p.ctx_len = ctx_len;
+    p.out = out; p.out_stride = heads * hd;
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)m * heads * splits * hd;
+    return launch_both<false>(p, m, hd, s);
+}
+
+}  // namespace swlm

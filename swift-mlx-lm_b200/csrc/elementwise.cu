@@ -1,0 +1,287 @@
+// Latency-bound glue kernels of the decode step: fused residual/RMSNorm, per-head QK norm,
+// embedding gather, SwiGLU, gated short-conv state update, greedy argmax. Each is a few KB of
+// traffic; the design goal is one launch where the reference needs two or three, 128-bit accesses,
+// and bf16 rounding at exactly the points where the reference stores to a bf16 buffer.
+#include "swlm_internal.h"
+
+namespace swlm {
+namespace {
+
+__device__ __forceinline__ float bf_lo(unsigned w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(unsigned w) { return __uint_as_float(w & 0xFFFF0000u); }
+__device__ __forceinline__ unsigned pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int i = 0; i < nw; ++i) total += red[i];  // same order in every thread
+    __syncthreads();
+    return total;
+}
+
+// Replaces fused_copy_rms_norm / fused_residual_add_copy_rms_norm / fused_residual_add_rms_norm
+// (Primitives/Reduction.swift:74-115 synthesized with CopyFragment and ResidualAddFragment,
+// Compiler/MetalEntryCollector.swift:143-218). One CTA per sequence; h is kept in shared memory
+// in fp32 so the norm sees the unrounded sum, as the reference's fused kernel does.
+template <int MODE>  // 0 copy+norm, 1 add+copy+norm, 2 add+norm
+__global__ void __launch_bounds__(256) rmsnorm_kernel(int dim, const __nv_bfloat16* in, int in_stride,
+                                                     __nv_bfloat16* residual, int res_stride,
+                                                     const __nv_bfloat16* weight, float eps, float weight_bias,
+                                                     __nv_bfloat16* out, int out_stride) {
+    extern __shared__ __align__(16) float hbuf[];
+    __shared__ float red[8];
+    const int b = blockIdx.x;
+    const uint4* in4 = reinterpret_cast<const uint4*>(in + (size_t)b * in_stride);
+    uint4* res4 = reinterpret_cast<uint4*>(residual + (size_t)b * res_stride);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) {
+        const uint4 v = in4[i];
+        float h[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+        if (MODE != 0) {
+            const uint4 r = res4[i];
+            h[0] += bf_lo(r.x); h[1] += bf_hi(r.x); h[2] += bf_lo(r.y); h[3] += bf_hi(r.y);
+            h[4] += bf_lo(r.z); h[5] += bf_hi(r.z); h[6] += bf_lo(r.w); h[7] += bf_hi(r.w);
+        }
+        if (MODE != 2) res4[i] = make_uint4(pack_bf16(h[0], h[1]), pack_bf16(h[2], h[3]), pack_bf16(h[4], h[5]), pack_bf16(h[6], h[7]));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { hbuf[i * 8 + e] = h[e]; ss = fmaf(h[e], h[e], ss); }
+    }
+    const float total = block_sum(ss, red);
+    const float rs = rsqrtf(total / (float)dim + eps);
+    const uint4* w4 = reinterpret_cast<const uint4*>(weight);
+    uint4* out4 = reinterpret_cast<uint4*>(out + (size_t)b * out_stride);
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) {
+        const uint4 w = w4[i];
+        const float wf[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = hbuf[i * 8 + e] * rs * (wf[e] + weight_bias);
+        out4[i] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+    }
+}
+
+// batched_qk_rms_norm_2 (Generator/MetalSourceGenerator+Batched.swift:681-760): one warp per head.
+__global__ void qk_norm_kernel(int heads, int kv_heads, int head_dim, __nv_bfloat16* q, int q_stride,
+                               __nv_bfloat16* k, int k_stride, const __nv_bfloat16* wq, const __nv_bfloat16* wk,
+                               float eps, float weight_bias) {
+    const int b = blockIdx.y;
+    const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (head >= heads + kv_heads) return;
+    __nv_bfloat16* data = head < heads ? q + (size_t)b * q_stride + (size_t)head * head_dim
+                                       : k + (size_t)b * k_stride + (size_t)(head - heads) * head_dim;
+    const __nv_bfloat16* w = head < heads ? wq : wk;
+    float ss = 0.f;
+    for (int i = lane; i < head_dim; i += 32) { const float v = __bfloat162float(data[i]); ss = fmaf(v, v, ss); }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rs = rsqrtf(ss / (float)head_dim + eps);
+    for (int i = lane; i < head_dim; i += 32)
+        data[i] = __float2bfloat16_rn(__bfloat162float(data[i]) * rs * (__bfloat162float(w[i]) + weight_bias));
+}
+
+// embedding_lookup_bf16 (Generator/MetalSourceGenerator+Embedding.swift:3-48).
+__global__ void embed_kernel(int dim, const int32_t* tokens, int vocab, const __nv_bfloat16* table,
+                             __nv_bfloat16* out, int out_stride) {
+    const int b = blockIdx.y;
+    int tok = tokens[b];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)tok * dim);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)b * out_stride);
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < dim / 8) dst[i] = src[i];
+}
+
+// swiglu (Primitives/ElementwiseFragment.swift:49-54); used only when the plan cannot fold it
+// into the gate/up GEMV epilogue.
+__global__ void swiglu_kernel(int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
+                              __nv_bfloat16* out, int o_stride) {
+    const int b = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = __bfloat162float(gate[(size_t)b * g_stride + i]);
+    const float u = __bfloat162float(up[(size_t)b * u_stride + i]);
+    out[(size_t)b * o_stride + i] = __float2bfloat16_rn(g * (1.0f / (1.0f + expf(-g))) * u);
+}
+
+// conv_state_update_bf16 (Generator/MetalSourceGenerator+ConvAndState.swift:27-70): in = B|C|x,
+// state [kernel][dim] bf16 shifted by one, newest entry stored rounded but used unrounded.
+__global__ void conv_step_kernel(int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,
+                                 const __nv_bfloat16* in, int in_stride, const __nv_bfloat16* weight,
+                                 __nv_bfloat16* out, int out_stride) {
+    const int b = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= dim) return;
+    const __nv_bfloat16* x = in + (size_t)b * in_stride;
+    __nv_bfloat16* st = state + (size_t)b * state_seq_stride;
+    const float B = __bfloat162float(x[c]), C = __bfloat162float(x[dim + c]), xv = __bfloat162float(x[2 * dim + c]);
+    const float Bx = B * xv;
+    float acc = 0.f;
+    for (int k = 0; k + 1 < kernel; ++k) {
+        const __nv_bfloat16 s = st[(size_t)(k + 1) * dim + c];
+        st[(size_t)k * dim + c] = s;
+        acc += __bfloat162float(s) * __bfloat162float(weight[(size_t)c * kernel + k]);
+    }
+    st[(size_t)(kernel - 1) * dim + c] = __float2bfloat16_rn(Bx);
+    acc += Bx * __bfloat162float(weight[(size_t)c * kernel + (kernel - 1)]);
+    out[(size_t)b * out_stride + c] = __float2bfloat16_rn(C * acc);
+}
+
+// ---- argmax -----------------------------------------------------------------------------------------
+// Replaces the single-threadgroup `argmax` (Generator/MetalSourceGenerator+Sampling.swift:62-107) with a
+// two-level reduction. Lowest index wins among equal maxima.
+constexpr int kArgmaxBlocks = 128;
+
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(int n, const __nv_bfloat16* logits, int stride,
+                                                            float* pval, int32_t* pidx) {
+    const int b = blockIdx.y;
+    const __nv_bfloat16* row = logits + (size_t)b * stride;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = __bfloat162float(row[i]);
+        if (v > best) { best = v; bi = i; }   // i ascends within a thread: first maximum is kept
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        argmax_merge(best, bi, ov, oi);
+    }
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) argmax_merge(best, bi, sv[w], si[w]);
+        pval[b * kArgmaxBlocks + blockIdx.x] = best;
+        pidx[b * kArgmaxBlocks + blockIdx.x] = bi;
+    }
+}
+
+// one warp per sequence; finally thread 0 advances the device-side position and step counter
+__global__ void argmax_final_kernel(int m, const float* pval, const int32_t* pidx, int32_t* token_out,
+                                    int32_t* token_in_next, int32_t* ring, int32_t* step_counter, int ring_cap,
+                                    int32_t* position, int advance) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int b = warp; b < m; b += (blockDim.x >> 5)) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = lane; i < kArgmaxBlocks; i += 32) argmax_merge(best, bi, pval[b * kArgmaxBlocks + i], pidx[b * kArgmaxBlocks + i]);
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            argmax_merge(best, bi, ov, oi);
+        }
+        if (lane == 0) {
+            if (bi == 0x7fffffff) bi = 0;
+            token_out[b] = bi;
+            if (token_in_next) token_in_next[b] = bi;
+            if (ring) ring[(size_t)(step_counter[0] % ring_cap) * m + b] = bi;
+        }
+    }
+    __syncthreads();
+    if (advance && threadIdx.x == 0) {
+        position[0] += 1;
+        step_counter[0] += 1;
+    }
+}
+
+__global__ void fill_u32_kernel(uint32_t* p, size_t n, uint32_t v) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+__global__ void advance_kernel(int32_t* position, int32_t* step_counter) {
+    position[0] += 1;
+    if (step_counter) step_counter[0] += 1;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    return SWLM_OK;
+}
+
+}  // namespace
+
+int launch_rmsnorm(int mode, int m, int dim, const __nv_bfloat16* in, int in_stride, __nv_bfloat16* residual,
+                   int res_stride, const __nv_bfloat16* weight, float eps, float weight_bias, __nv_bfloat16* out,
+                   int out_stride, cudaStream_t s) {
+    if (dim % 8 || in_stride % 8 || res_stride % 8 || out_stride % 8 || dim > 12288) {
+        set_error("rmsnorm: dim=%d must be a multiple of 8 and <= 12288 with 16-byte aligned rows", dim);
+        return SWLM_ERR_INVALID;
+    }
+    const size_t smem = (size_t)dim * 4;
+    switch (mode) {
+    case SWLM_STEP_COPY_RMSNORM:
+        rmsnorm_kernel<0><<<m, 256, smem, s>>>(dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
+        break;
+    case SWLM_STEP_RESADD_COPY_RMSNORM:
+        rmsnorm_kernel<1><<<m, 256, smem, s>>>(dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
+        break;
+    case SWLM_STEP_RESADD_RMSNORM:
+        rmsnorm_kernel<2><<<m, 256, smem, s>>>(dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
+        break;
+    default:
+        set_error("rmsnorm: bad mode %d", mode);
+        return SWLM_ERR_INVALID;
+    }
+    return check_launch("rmsnorm launch");
+}
+
+int launch_qk_norm(int m, int heads, int kv_heads, int head_dim, __nv_bfloat16* q, int q_stride, __nv_bfloat16* k,
+                   int k_stride, const __nv_bfloat16* wq, const __nv_bfloat16* wk, float eps, float weight_bias,
+                   cudaStream_t s) {
+    const int total = heads + kv_heads;
+    qk_norm_kernel<<<dim3((total + 3) / 4, m), 128, 0, s>>>(heads, kv_heads, head_dim, q, q_stride, k, k_stride, wq, wk, eps, weight_bias);
+    return check_launch("qk_norm launch");
+}
+
+int launch_embed(int m, int dim, const int32_t* tokens, int vocab, const __nv_bfloat16* table, __nv_bfloat16* out,
+                 int out_stride, cudaStream_t s) {
+    if (dim % 8 || out_stride % 8) { set_error("embed: dim must be a multiple of 8"); return SWLM_ERR_INVALID; }
+    embed_kernel<<<dim3((dim / 8 + 127) / 128, m), 128, 0, s>>>(dim, tokens, vocab, table, out, out_stride);
+    return check_launch("embed launch");
+}
+
+int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
+                  __nv_bfloat16* out, int o_stride, cudaStream_t s) {
+    swiglu_kernel<<<dim3((n + 255) / 256, m), 256, 0, s>>>(n, gate, g_stride, up, u_stride, out, o_stride);
+    return check_launch("swiglu launch");
+}
+
+int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,
+                     const __nv_bfloat16* in, int in_stride, const __nv_bfloat16* weight, __nv_bfloat16* out,
+                     int out_stride, cudaStream_t s) {
+    conv_step_kernel<<<dim3((dim + 255) / 256, m), 256, 0, s>>>(dim, kernel, state, state_seq_stride, in, in_stride, weight, out, out_stride);
+    return check_launch("conv_step launch");
+}
+
+size_t argmax_scratch_elems(int m) { return (size_t)m * kArgmaxBlocks; }
+
+int launch_argmax(int m, int n, const __nv_bfloat16* logits, int stride, int32_t* token_out, int32_t* token_in_next,
+                  int32_t* ring, int32_t* step_counter, int ring_cap, int32_t* position, int advance,
+                  float* scratch_val, int32_t* scratch_idx, cudaStream_t s) {
+    argmax_partial_kernel<<<dim3(kArgmaxBlocks, m), 256, 0, s>>>(n, logits, stride, scratch_val, scratch_idx);
+    argmax_final_kernel<<<1, 256, 0, s>>>(m, scratch_val, scratch_idx, token_out, token_in_next, ring, step_counter,
+                                          ring_cap, position, advance);
+    return check_launch("argmax launch");
+}
+
+int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s) {
+    if (n == 0) return SWLM_OK;
+    fill_u32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p, n, v);
+    return check_launch("fill launch");
+}
+int launch_advance(int32_t* position, int32_t* step_counter, cudaStream_t s) {
+    advance_kernel<<<1, 1, 0, s>>>(position, step_counter);
+    return check_launch("advance launch");
+}
+
+}  // namespace swlm

@@ -1,0 +1,1101 @@
+// Host runtime of libswlm_cuda.so: weight store, plan compiler (step list -> fused launch list),
+// per-context runtime state, CUDA-graph decode executor, and the C ABI declared in include/swlm.h.
+//
+// Reference counterparts: STAFWeightStore (Sources/MetalCompiler/STAF/STAFLoader.swift:213-299),
+// MetalDispatchStepBuilder.buildDecodePlan (Compiler/MetalDispatchStepBuilder.swift:4-105),
+// MetalInferenceModel / MetalDecodeExecutor (Execution/MetalInferenceModel.swift,
+// Execution/MetalDecodeExecutor.swift:7-43), MetalPromptStateStore (Execution/MetalPromptStateStore.swift:5-137).
+// Where the reference encodes and commits a command buffer per token and blocks on it, this runtime
+// captures the whole step into one CUDA graph and keeps position, input token and output token on
+// the device, so consecutive greedy steps need no host round trip.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <algorithm>
+#include <cmath>
+
+#include "swlm_internal.h"
+
+namespace swlm {
+
+// ---- errors ---------------------------------------------------------------------------------------
+static thread_local char g_error[512] = "";
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return SWLM_ERR_CUDA;
+}
+
+}  // namespace swlm
+
+using namespace swlm;
+
+// =====================================================================================================
+// Context + weight store
+// =====================================================================================================
+struct swlm_ctx {
+    int device = 0, tp_rank = 0, tp_size = 1;
+    cudaStream_t stream = nullptr;
+    std::map<std::string, Q4Raw> raw;
+    std::map<std::string, Q4Tiled> tiled;  // plain and fused tensors, keyed by name ("a|b|c" for fused)
+    std::map<std::string, DenseTensor> dense;
+    int64_t bytes = 0;
+    float* op_partial = nullptr; size_t op_partial_floats = 0;
+    unsigned* op_counters = nullptr; size_t op_counter_count = 0;
+};
+
+namespace {
+
+int ensure_device(const swlm_ctx* ctx) {
+    SWLM_CUDA(cudaSetDevice(ctx->device));
+    return SWLM_OK;
+}
+
+template <typename T>
+int dev_alloc(T** p, size_t count, swlm_ctx* ctx = nullptr) {
+    *p = nullptr;
+    if (count == 0) return SWLM_OK;
+    SWLM_CUDA(cudaMalloc((void**)p, count * sizeof(T)));
+    if (ctx) ctx->bytes += (int64_t)(count * sizeof(T));
+    return SWLM_OK;
+}
+
+int alloc_tiled(swlm_ctx* ctx, int n, int k, bool sb_f16, Q4Tiled* t) {
+    t->n = n; t->k = k; t->sb_f16 = sb_f16;
+    t->row_tiles = (n + 15) / 16;
+    t->kt_pad = ((k / 64 + 3) / 4) * 4;
+    int rc = dev_alloc(&t->tiles, (size_t)t->row_tiles * t->kt_pad * 32, ctx);
+    if (rc) return rc;
+    return dev_alloc(&t->sb, (size_t)t->row_tiles * (t->kt_pad / 4) * 16, ctx);
+}
+
+// Rank-local slice of a [rows][cols] matrix given in `unit`-sized column units.
+struct Slice { int row0, rows, col0, cols; };
+int shard_slice(const swlm_ctx* ctx, int shard_kind, int n, int k, Slice* s) {
+    *s = Slice{0, n, 0, k};
+    if (ctx->tp_size == 1 || shard_kind == SWLM_SHARD_REPLICATE) return SWLM_OK;
+    if (shard_kind == SWLM_SHARD_COLUMN) {
+        if (n % ctx->tp_size) { set_error("column shard: n=%d not divisible by tp=%d", n, ctx->tp_size); return SWLM_ERR_INVALID; }
+        s->rows = n / ctx->tp_size; s->row0 = ctx->tp_rank * s->rows;
+        return SWLM_OK;
+    }
+    if (shard_kind == SWLM_SHARD_ROW) {
+        if (k % (64 * ctx->tp_size)) { set_error("row shard: k=%d not divisible by 64*tp", k); return SWLM_ERR_INVALID; }
+        s->cols = k / ctx->tp_size; s->col0 = ctx->tp_rank * s->cols;
+        return SWLM_OK;
+    }
+    set_error("unsupported shard kind %d", shard_kind);
+    return SWLM_ERR_UNSUPPORTED;
+}
+
+const Q4Tiled* find_tiled(swlm_ctx* ctx, const std::string& name) {
+    auto it = ctx->tiled.find(name);
+    return it == ctx->tiled.end() ? nullptr : &it->second;
+}
+
+// Build (or fetch) the streaming-layout tensor for one raw tensor or a fusion of several.
+int get_tiled(swlm_ctx* ctx, const std::vector<std::string>& names, int mode, const Q4Tiled** out) {
+    std::string key = names[0];
+    for (size_t i = 1; i < names.size(); ++i) key += (mode == 1 ? "^" : "|") + names[i];
+    if (const Q4Tiled* t = find_tiled(ctx, key)) { *out = t; return SWLM_OK; }
+    RepackSrc src[3];
+    int n_total = 0, k = 0;
+    bool f16 = false;
+    for (size_t i = 0; i < names.size(); ++i) {
+        auto it = ctx->raw.find(names[i]);
+        if (it == ctx->raw.end()) { set_error("tensor '%s' not in the weight store", names[i].c_str()); return SWLM_ERR_NOT_FOUND; }
+        const Q4Raw& r = it->second;
+        if (i == 0) { k = r.k; f16 = r.sb_f16; }
+        else if (r.k != k || r.sb_f16 != f16) { set_error("fused tensors must share K and header type"); return SWLM_ERR_INVALID; }
+        src[i] = RepackSrc{r.w, r.scales, r.biases, r.n};
+        n_total += r.n;
+    }
+    if (mode == 1) {
+        if (names.size() != 2 || src[0].n != src[1].n) { set_error("interleave needs two tensors with equal N"); return SWLM_ERR_INVALID; }
+        n_total = ((src[0].n + 7) / 8) * 16;
+    }
+    Q4Tiled t;
+    int rc = alloc_tiled(ctx, n_total, k, f16, &t);
+    if (rc) return rc;
+    t.interleaved = mode == 1;
+    rc = launch_repack(src, (int)names.size(), mode, k, t, ctx->stream);
+    if (rc) return rc;
+    SWLM_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->tiled[key] = t;
+    *out = &ctx->tiled[key];
+    return SWLM_OK;
+}
+
+int add_q4_raw(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* w, const uint16_t* s,
+               const uint16_t* b, bool f16, int shard_kind) {
+    if (!ctx || !name || !w || !s || !b) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    if (n <= 0 || k <= 0 || k % 64) { set_error("q4g64 tensor '%s': k=%d must be a positive multiple of 64", name, k); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    Slice sl;
+    rc = shard_slice(ctx, shard_kind, n, k, &sl);
+    if (rc) return rc;
+    Q4Raw r;
+    r.n = sl.rows; r.k = sl.cols; r.sb_f16 = f16; r.shard_kind = shard_kind;
+    const int wpr = k / 8, gpr = k / 64, lw = sl.cols / 8, lg = sl.cols / 64;
+    if ((rc = dev_alloc(&r.w, (size_t)r.n * lw, ctx))) return rc;
+    if ((rc = dev_alloc(&r.scales, (size_t)r.n * lg, ctx))) return rc;
+    if ((rc = dev_alloc(&r.biases, (size_t)r.n * lg, ctx))) return rc;
+    SWLM_CUDA(cudaMemcpy2D(r.w, (size_t)lw * 4, w + (size_t)sl.row0 * wpr + sl.col0 / 8, (size_t)wpr * 4, (size_t)lw * 4, r.n, cudaMemcpyHostToDevice));
+    SWLM_CUDA(cudaMemcpy2D(r.scales, (size_t)lg * 2, s + (size_t)sl.row0 * gpr + sl.col0 / 64, (size_t)gpr * 2, (size_t)lg * 2, r.n, cudaMemcpyHostToDevice));
+    SWLM_CUDA(cudaMemcpy2D(r.biases, (size_t)lg * 2, b + (size_t)sl.row0 * gpr + sl.col0 / 64, (size_t)gpr * 2, (size_t)lg * 2, r.n, cudaMemcpyHostToDevice));
+    ctx->raw[name] = r;
+    return SWLM_OK;
+}
+
+}  // namespace
+
+// =====================================================================================================
+// Plan
+// =====================================================================================================
+namespace {
+
+enum LaunchKind { L_EMBED, L_RMSNORM, L_QGEMV, L_QK_NORM, L_ATTN, L_SWIGLU, L_CONV, L_ARGMAX };
+
+struct Launch {
+    int kind = 0;
+    swlm_step st{};            // the (first) step this launch came from
+    const Q4Tiled* w = nullptr;
+    int epilogue = QGEMV_EPI_STORE;
+    int n_seg = 1;
+    int seg_buf[3] = {-1, -1, -1};
+    int seg_end[3] = {0, 0, 0};
+    const DenseTensor* d1 = nullptr;
+    const DenseTensor* d2 = nullptr;
+    int rope_table = -1;       // index into plan->rope_tables
+    std::string label;
+    int steps_covered = 1;
+};
+
+struct RopeTable { int rope_dim; float base; float* inv_freq; };
+
+}  // namespace
+
+struct swlm_plan {
+    swlm_ctx* ctx = nullptr;
+    swlm_buffers_desc desc{};
+    std::vector<swlm_step> steps;
+    std::vector<Launch> launches;
+    std::vector<RopeTable> rope_tables;
+    int attn_splits = 1;
+    size_t attn_scratch = 0, qgemv_partial = 0, qgemv_counters = 0;
+};
+
+namespace {
+
+int buf_width(const swlm_buffers_desc& d, int buf) {
+    if (buf == SWLM_BUF_HIDDEN || buf == SWLM_BUF_RESIDUAL) return d.hidden;
+    if (buf == SWLM_BUF_LOGITS) return d.vocab;
+    return d.slot_dim;
+}
+
+const DenseTensor* find_dense(swlm_ctx* ctx, const char* name) {
+    auto it = ctx->dense.find(name);
+    return it == ctx->dense.end() ? nullptr : &it->second;
+}
+
+int rope_table_for(swlm_plan* plan, int rope_dim, float base, int* index) {
+    for (size_t i = 0; i < plan->rope_tables.size(); ++i)
+        if (plan->rope_tables[i].rope_dim == rope_dim && plan->rope_tables[i].base == base) { *index = (int)i; return SWLM_OK; }
+    // theta_i = base^(-2i/ropeDim) evaluated in fp32 on the host
+    // (Generator/MetalSourceGenerator+Attention.swift:606-609 evaluates the same expression per call).
+    std::vector<float> f(rope_dim / 2);
+    for (int i = 0; i < rope_dim / 2; ++i) f[i] = powf(base, -2.0f * (float)i / (float)rope_dim);
+    RopeTable t{rope_dim, base, nullptr};
+    int rc = dev_alloc(&t.inv_freq, f.size());
+    if (rc) return rc;
+    SWLM_CUDA(cudaMemcpy(t.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice));
+    plan->rope_tables.push_back(t);
+    *index = (int)plan->rope_tables.size() - 1;
+    return SWLM_OK;
+}
+
+bool buf_ok(int b) { return b >= 0 && b < SWLM_BUF_COUNT; }
+
+int compile_plan(swlm_plan* plan) {
+    swlm_ctx* ctx = plan->ctx;
+    const swlm_buffers_desc& d = plan->desc;
+    const std::vector<swlm_step>& st = plan->steps;
+    const int m = d.max_batch;
+    int rc;
+    for (size_t i = 0; i < st.size();) {
+        const swlm_step& s = st[i];
+        Launch L;
+        L.st = s;
+        switch (s.kind) {
+        case SWLM_STEP_EMBED:
+            L.kind = L_EMBED;
+            L.d1 = find_dense(ctx, s.weight);
+            if (!L.d1) { set_error("embedding table '%s' missing", s.weight); return SWLM_ERR_NOT_FOUND; }
+            if (!buf_ok(s.out_buf) || s.n > buf_width(d, s.out_buf)) { set_error("embed: bad output buffer"); return SWLM_ERR_INVALID; }
+            L.label = std::string("embed ") + s.weight;
+            break;
+        case SWLM_STEP_COPY_RMSNORM:
+        case SWLM_STEP_RESADD_COPY_RMSNORM:
+        case SWLM_STEP_RESADD_RMSNORM:
+            L.kind = L_RMSNORM;
+            L.d1 = find_dense(ctx, s.weight);
+            if (!L.d1) { set_error("norm weight '%s' missing", s.weight); return SWLM_ERR_NOT_FOUND; }
+            if (!buf_ok(s.in_buf) || !buf_ok(s.out_buf) || L.d1->rows * L.d1->cols < s.n) { set_error("rmsnorm: bad buffers"); return SWLM_ERR_INVALID; }
+            L.label = std::string("rmsnorm ") + s.weight;
+            break;
+        case SWLM_STEP_QGEMV: {
+            L.kind = L_QGEMV;
+            if (!buf_ok(s.in_buf) || !buf_ok(s.out_buf)) { set_error("qgemv: bad buffers"); return SWLM_ERR_INVALID; }
+            // gate, up, swiglu -> one launch over row-interleaved weights with a SwiGLU epilogue
+            if (i + 2 < st.size() && st[i + 1].kind == SWLM_STEP_QGEMV && st[i + 2].kind == SWLM_STEP_SWIGLU &&
+                st[i + 1].in_buf == s.in_buf && st[i + 1].k == s.k && st[i + 1].n == s.n &&
+                st[i + 2].in_buf == s.out_buf && st[i + 2].in2_buf == st[i + 1].out_buf && (s.n % 8) == 0) {
+                rc = get_tiled(ctx, {s.weight, st[i + 1].weight}, 1, &L.w);
+                if (rc) return rc;
+                L.epilogue = QGEMV_EPI_SWIGLU;
+                L.seg_buf[0] = st[i + 2].out_buf;
+                L.seg_end[0] = ctx->raw[s.weight].n;
+                L.steps_covered = 3;
+                L.label = std::string("qgemv+swiglu ") + s.weight + " ^ " + st[i + 1].weight;
+                break;
+            }
+            // consecutive projections of one input -> one launch over concatenated rows
+            std::vector<std::string> names{s.weight};
+            size_t jn = i + 1;
+            while (jn < st.size() && names.size() < 3 && st[jn].kind == SWLM_STEP_QGEMV && st[jn].in_buf == s.in_buf &&
+                   st[jn].k == s.k && st[jn].out_buf != s.in_buf) {
+                bool clash = false;
+                for (size_t q = i; q < jn; ++q) clash |= st[q].out_buf == st[jn].out_buf;
+                if (clash) break;
+                names.push_back(st[jn].weight);
+                ++jn;
+            }
+            if (s.out_buf == s.in_buf && names.size() > 1) names.resize(1);
+            rc = get_tiled(ctx, names, 0, &L.w);
+            if (rc) return rc;
+            L.n_seg = (int)names.size();
+            int end = 0;
+            L.label = "qgemv";
+            for (int q = 0; q < L.n_seg; ++q) {
+                const Q4Raw& r = ctx->raw[names[q]];
+                end += r.n;
+                L.seg_buf[q] = st[i + q].out_buf;
+                L.seg_end[q] = end;
+                if (r.n > buf_width(d, st[i + q].out_buf)) { set_error("qgemv '%s': n=%d exceeds the output buffer", names[q].c_str(), r.n); return SWLM_ERR_INVALID; }
+                L.label += " " + names[q];
+            }
+            if (L.w->k > buf_width(d, s.in_buf)) { set_error("qgemv '%s': k=%d exceeds the input buffer", s.weight, L.w->k); return SWLM_ERR_INVALID; }
+            L.steps_covered = L.n_seg;
+            break;
+        }
+        case SWLM_STEP_QK_NORM:
+            L.kind = L_QK_NORM;
+            L.d1 = find_dense(ctx, s.weight);
+            L.d2 = find_dense(ctx, s.weight2);
+            if (!L.d1 || !L.d2) { set_error("qk norm weights missing"); return SWLM_ERR_NOT_FOUND; }
+            L.label = "qk_norm";
+            break;
+        case SWLM_STEP_ATTN_DECODE:
+            L.kind = L_ATTN;
+            if (s.layer < 0 || s.layer >= d.kv_layers) { set_error("attention: layer %d outside the KV cache", s.layer); return SWLM_ERR_INVALID; }
+            if (s.head_dim != d.head_dim) { set_error("attention: head_dim differs from the KV cache"); return SWLM_ERR_INVALID; }
+            if (s.rope_dim > 0) { rc = rope_table_for(plan, s.rope_dim, s.rope_base, &L.rope_table); if (rc) return rc; }
+            L.label = "attn_decode";
+            break;
+        case SWLM_STEP_SWIGLU:
+            L.kind = L_SWIGLU;
+            L.label = "swiglu";
+            break;
+        case SWLM_STEP_CONV_STATE_UPDATE:
+            L.kind = L_CONV;
+            L.d1 = find_dense(ctx, s.weight);
+            if (!L.d1) { set_error("conv weight '%s' missing", s.weight); return SWLM_ERR_NOT_FOUND; }
+            if (s.layer < 0 || s.layer >= d.conv_layers) { set_error("conv: layer %d outside the conv state", s.layer); return SWLM_ERR_INVALID; }
+            L.label = std::string("conv_state_update ") + s.weight;
+            break;
+        case SWLM_STEP_ARGMAX:
+            L.kind = L_ARGMAX;
+            L.label = "argmax";
+            break;
+        default:
+            set_error("step %zu: kind %d is outside the hot path", i, s.kind);
+            return SWLM_ERR_UNSUPPORTED;
+        }
+        i += L.steps_covered;
+        if (L.kind == L_QGEMV) {
+            plan->qgemv_partial = std::max(plan->qgemv_partial, qgemv_scratch_floats(*L.w, m));
+            plan->qgemv_counters = std::max(plan->qgemv_counters, (size_t)qgemv_counter_count(*L.w));
+        }
+        plan->launches.push_back(L);
+    }
+    plan->attn_splits = attn_pick_splits(m, std::max(1, d.kv_heads / std::max(1, ctx->tp_size)), d.max_seq);
+    return SWLM_OK;
+}
+
+}  // namespace
+
+// =====================================================================================================
+// State
+// =====================================================================================================
+struct swlm_state {
+    swlm_plan* plan = nullptr;
+    cudaStream_t own_stream = nullptr, stream = nullptr;
+    __nv_bfloat16* buf[SWLM_BUF_COUNT] = {};
+    int width[SWLM_BUF_COUNT] = {};
+    __nv_bfloat16* kcache = nullptr; __nv_bfloat16* vcache = nullptr; size_t kv_layer_elems = 0;
+    __nv_bfloat16* conv = nullptr; size_t conv_layer_elems = 0;
+    int32_t* position = nullptr; int32_t* step_counter = nullptr;
+    int32_t* token_in = nullptr; int32_t* token_out = nullptr; int32_t* ring = nullptr;
+    int32_t* prompt = nullptr; size_t prompt_cap = 0;
+    int ring_cap = 4096;
+    float* attn_scratch = nullptr; float* qgemv_partial = nullptr; unsigned* qgemv_counters = nullptr;
+    float* argmax_val = nullptr; int32_t* argmax_idx = nullptr;
+    int32_t* h_tok = nullptr;  // pinned host staging, 2 * max_batch
+    int pos_host = 0;
+    long long steps_host = 0;
+    cudaGraphExec_t graph_full = nullptr, graph_body = nullptr;
+    int64_t launches = 0;
+};
+
+struct swlm_snap {
+    std::vector<void*> dev;
+    std::vector<size_t> bytes;
+    int pos_host = 0;
+};
+
+namespace {
+
+int kv_heads_local(const swlm_plan* p) { return std::max(1, p->desc.kv_heads / std::max(1, p->ctx->tp_size)); }
+
+// Enqueue the launches of one decode step. body_only skips the output head (lm_head + argmax) and
+// advances the position with a one-thread kernel instead.
+int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream) {
+    const swlm_plan* plan = s->plan;
+    const swlm_buffers_desc& d = plan->desc;
+    const int m = d.max_batch;
+    int rc = SWLM_OK;
+    const size_t n_launch = plan->launches.size();
+    // the output head is the trailing [norm, lm_head, argmax] group
+    size_t head_begin = n_launch;
+    if (body_only) {
+        head_begin = n_launch;
+        while (head_begin > 0 && (plan->launches[head_begin - 1].kind == L_ARGMAX ||
+                                  (plan->launches[head_begin - 1].kind == L_QGEMV && plan->launches[head_begin - 1].seg_buf[0] == SWLM_BUF_LOGITS) ||
+                                  (plan->launches[head_begin - 1].kind == L_RMSNORM && plan->launches[head_begin - 1].st.kind == SWLM_STEP_RESADD_RMSNORM)))
+            --head_begin;
+    }
+    bool advanced = false;
+    for (size_t li = 0; li < head_begin; ++li) {
+        const Launch& L = plan->launches[li];
+        const swlm_step& st = L.st;
+        switch (L.kind) {
+        case L_EMBED:
+            rc = launch_embed(m, st.n, s->token_in, d.vocab, L.d1->data, s->buf[st.out_buf], s->width[st.out_buf], stream);
+            s->launches += 1;
+            break;
+        case L_RMSNORM:
+            rc = launch_rmsnorm(st.kind, m, st.n, s->buf[st.in_buf], s->width[st.in_buf], s->buf[SWLM_BUF_RESIDUAL],
+                                s->width[SWLM_BUF_RESIDUAL], L.d1->data, st.eps, st.weight_bias, s->buf[st.out_buf],
+                                s->width[st.out_buf], stream);
+            s->launches += 1;
+            break;
+        case L_QGEMV: {
+            QGemvLaunch a;
+            a.w = L.w; a.x = s->buf[st.in_buf]; a.x_stride = s->width[st.in_buf]; a.m = m; a.epilogue = L.epilogue;
+            for (int q = 0; q < L.n_seg; ++q) { a.y[q] = s->buf[L.seg_buf[q]]; a.y_stride[q] = s->width[L.seg_buf[q]]; a.seg_end[q] = L.seg_end[q]; }
+            a.partial = s->qgemv_partial; a.counters = s->qgemv_counters;
+            rc = launch_qgemv(a, stream);
+            s->launches += 1;
+            break;
+        }
+        case L_QK_NORM:
+            rc = launch_qk_norm(m, st.heads / plan->ctx->tp_size, kv_heads_local(plan), st.head_dim, s->buf[st.in_buf], s->width[st.in_buf],
+                                s->buf[st.in2_buf], s->width[st.in2_buf], L.d1->data, L.d2->data, st.eps, st.weight_bias, stream);
+            s->launches += 1;
+            break;
+        case L_ATTN: {
+            AttnLaunch a;
+            a.m = m; a.heads = st.heads / plan->ctx->tp_size; a.kv_heads = kv_heads_local(plan); a.head_dim = st.head_dim;
+            a.rope_dim = st.rope_dim; a.inv_freq = L.rope_table >= 0 ? plan->rope_tables[L.rope_table].inv_freq : nullptr;
+            a.scale = st.scale;
+            a.q = s->buf[st.in_buf]; a.q_stride = s->width[st.in_buf];
+            a.k = s->buf[st.in2_buf]; a.k_stride = s->width[st.in2_buf];
+            a.v = s->buf[st.in3_buf]; a.v_stride = s->width[st.in3_buf];
+            a.kcache = s->kcache + (size_t)st.layer * s->kv_layer_elems;
+            a.vcache = s->vcache + (size_t)st.layer * s->kv_layer_elems;
+            a.max_seq = d.max_seq; a.position = s->position;
+            a.out = s->buf[st.out_buf]; a.out_stride = s->width[st.out_buf];
+            a.scratch = s->attn_scratch; a.splits = plan->attn_splits;
+            rc = launch_attn_decode(a, stream);
+            s->launches += 2;
+            break;
+        }
+        case L_SWIGLU:
+            rc = launch_swiglu(m, st.n, s->buf[st.in_buf], s->width[st.in_buf], s->buf[st.in2_buf], s->width[st.in2_buf],
+                               s->buf[st.out_buf], s->width[st.out_buf], stream);
+            s->launches += 1;
+            break;
+        case L_CONV:
+            rc = launch_conv_step(m, st.n, st.conv_kernel, s->conv + (size_t)st.layer * s->conv_layer_elems,
+                                  (size_t)d.conv_kernel * d.conv_dim, s->buf[st.in_buf], s->width[st.in_buf], L.d1->data,
+                                  s->buf[st.out_buf], s->width[st.out_buf], stream);
+            s->launches += 1;
+            break;
+        case L_ARGMAX:
+            rc = launch_argmax(m, st.n, s->buf[st.in_buf], s->width[st.in_buf], s->token_out, s->token_in, s->ring,
+                               s->step_counter, s->ring_cap, s->position, 1, s->argmax_val, s->argmax_idx, stream);
+            s->launches += 2;
+            advanced = true;
+            break;
+        }
+        if (rc) return rc;
+    }
+    if (!advanced) {
+        rc = launch_advance(s->position, nullptr, stream);
+        s->launches += 1;
+    }
+    return rc;
+}
+
+int capture_graph(swlm_state* s, bool body_only, cudaGraphExec_t* out) {
+    cudaGraph_t graph = nullptr;
+    const int64_t before = s->launches;
+    SWLM_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_step(s, body_only, s->stream);
+    cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
+    s->launches = before;  // capture does not execute
+    if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
+    e = cudaGraphInstantiate(out, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+    return SWLM_OK;
+}
+
+int launches_per_step(const swlm_plan* plan, bool body_only) {
+    int n = 0;
+    bool has_argmax = false;
+    for (const Launch& L : plan->launches) {
+        if (body_only && (L.kind == L_ARGMAX || (L.kind == L_QGEMV && L.seg_buf[0] == SWLM_BUF_LOGITS) ||
+                          (L.kind == L_RMSNORM && L.st.kind == SWLM_STEP_RESADD_RMSNORM))) continue;
+        n += (L.kind == L_ATTN || L.kind == L_ARGMAX) ? 2 : 1;
+        has_argmax |= L.kind == L_ARGMAX;
+    }
+    if (body_only || !has_argmax) n += 1;
+    return n;
+}
+
+int run_graph(swlm_state* s, bool body_only) {
+    cudaGraphExec_t* g = body_only ? &s->graph_body : &s->graph_full;
+    if (!*g) {
+        int rc = capture_graph(s, body_only, g);
+        if (rc) return rc;
+    }
+    SWLM_CUDA(cudaGraphLaunch(*g, s->stream));
+    s->launches += launches_per_step(s->plan, body_only);
+    s->pos_host += 1;
+    s->steps_host += body_only ? 0 : 1;
+    return SWLM_OK;
+}
+
+void drop_graphs(swlm_state* s) {
+    if (s->graph_full) { cudaGraphExecDestroy(s->graph_full); s->graph_full = nullptr; }
+    if (s->graph_body) { cudaGraphExecDestroy(s->graph_body); s->graph_body = nullptr; }
+}
+
+struct Region { void* p; size_t bytes; };
+std::vector<Region> state_regions(swlm_state* s) {
+    const swlm_buffers_desc& d = s->plan->desc;
+    std::vector<Region> r;
+    for (int i = 0; i < SWLM_BUF_COUNT; ++i) r.push_back({s->buf[i], (size_t)d.max_batch * s->width[i] * 2});
+    r.push_back({s->kcache, (size_t)d.kv_layers * s->kv_layer_elems * 2});
+    r.push_back({s->vcache, (size_t)d.kv_layers * s->kv_layer_elems * 2});
+    r.push_back({s->conv, (size_t)d.conv_layers * s->conv_layer_elems * 2});
+    r.push_back({s->position, 4});
+    r.push_back({s->token_in, (size_t)d.max_batch * 4});
+    r.push_back({s->token_out, (size_t)d.max_batch * 4});
+    return r;
+}
+
+int check_position_room(swlm_state* s, int steps) {
+    if (s->pos_host + steps > s->plan->desc.max_seq) {
+        set_error("position %d + %d steps exceeds max_seq %d", s->pos_host, steps, s->plan->desc.max_seq);
+        return SWLM_ERR_STATE;
+    }
+    return SWLM_OK;
+}
+
+}  // namespace
+
+// =====================================================================================================
+// C ABI
+// =====================================================================================================
+extern "C" {
+
+const char* swlm_version(void) { return "swlm-cuda 0.1 (sm_100a)"; }
+const char* swlm_last_error(void) { return g_error; }
+
+int swlm_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+int swlm_ctx_create(int device_id, int tp_rank, int tp_size, swlm_ctx** out) {
+    if (!out) { set_error("null out"); return SWLM_ERR_INVALID; }
+    *out = nullptr;
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) { set_error("bad tp rank/size %d/%d", tp_rank, tp_size); return SWLM_ERR_INVALID; }
+    int n = swlm_device_count();
+    if (n <= 0) { set_error("no CUDA device: this library has no CPU path"); return SWLM_ERR_CUDA; }
+    if (device_id < 0 || device_id >= n) { set_error("device %d of %d", device_id, n); return SWLM_ERR_INVALID; }
+    SWLM_CUDA(cudaSetDevice(device_id));
+    cudaDeviceProp prop;
+    SWLM_CUDA(cudaGetDeviceProperties(&prop, device_id));
+    if (prop.major != 10) { set_error("device %d is sm_%d%d; this library is built for sm_100a only", device_id, prop.major, prop.minor); return SWLM_ERR_UNSUPPORTED; }
+    swlm_ctx* ctx = new swlm_ctx();
+    ctx->device = device_id; ctx->tp_rank = tp_rank; ctx->tp_size = tp_size;
+    cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete ctx; return cuda_fail(e, "cudaStreamCreate"); }
+    int rc = qgemv_init();
+    if (!rc) rc = attn_init();
+    if (rc) { cudaStreamDestroy(ctx->stream); delete ctx; return rc; }
+    *out = ctx;
+    return SWLM_OK;
+}
+
+void swlm_ctx_destroy(swlm_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    for (auto& kv : ctx->raw) { cudaFree(kv.second.w); cudaFree(kv.second.scales); cudaFree(kv.second.biases); }
+    for (auto& kv : ctx->tiled) { cudaFree(kv.second.tiles); cudaFree(kv.second.sb); }
+    for (auto& kv : ctx->dense) cudaFree(kv.second.data);
+    cudaFree(ctx->op_partial);
+    cudaFree(ctx->op_counters);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+int swlm_weights_add_q4g64_mlx(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* weight,
+                               const uint16_t* scales_bf16, const uint16_t* biases_bf16, int shard_kind) {
+    return add_q4_raw(ctx, name, n, k, weight, scales_bf16, biases_bf16, false, shard_kind);
+}
+
+int swlm_weights_add_q4g64_staf(swlm_ctx* ctx, const char* name, int n, int k, const void* blocks36, int shard_kind) {
+    if (!blocks36 || k <= 0 || k % 64) { set_error("bad STAF tensor"); return SWLM_ERR_INVALID; }
+    // De-interleave the 36-byte blocks into the three planes of the source layout; the payload bytes are
+    // the same LSB-first stream (Sources/MetalCompiler/STAF/STAFPayloadConverter.swift:268-274), and the
+    // fp16 scale/zero bits are kept as they are.
+    const int groups = k / 64;
+    std::vector<uint32_t> w((size_t)n * (k / 8));
+    std::vector<uint16_t> s((size_t)n * groups), z((size_t)n * groups);
+    const uint8_t* src = static_cast<const uint8_t*>(blocks36);
+    for (size_t g = 0; g < (size_t)n * groups; ++g) {
+        const uint8_t* blk = src + g * 36;
+        memcpy(&s[g], blk, 2);
+        memcpy(&z[g], blk + 2, 2);
+        memcpy(reinterpret_cast<uint8_t*>(w.data()) + g * 32, blk + 4, 32);
+    }
+    return add_q4_raw(ctx, name, n, k, w.data(), s.data(), z.data(), true, shard_kind);
+}
+
+int swlm_weights_add_dense_bf16(swlm_ctx* ctx, const char* name, int64_t rows, int64_t cols, const uint16_t* data,
+                                int shard_kind) {
+    if (!ctx || !name || !data || rows <= 0 || cols <= 0) { set_error("bad dense tensor"); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    Slice sl;
+    rc = shard_slice(ctx, shard_kind == SWLM_SHARD_ROW ? SWLM_SHARD_REPLICATE : shard_kind, (int)rows, (int)cols, &sl);
+    if (rc) return rc;
+    DenseTensor t;
+    t.rows = sl.rows; t.cols = cols; t.shard_kind = shard_kind;
+    if ((rc = dev_alloc(&t.data, (size_t)t.rows * cols, ctx))) return rc;
+    SWLM_CUDA(cudaMemcpy(t.data, data + (size_t)sl.row0 * cols, (size_t)t.rows * cols * 2, cudaMemcpyHostToDevice));
+    ctx->dense[name] = t;
+    return SWLM_OK;
+}
+
+int64_t swlm_weights_bytes(const swlm_ctx* ctx) { return ctx ? ctx->bytes : 0; }
+
+int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const swlm_buffers_desc* desc, swlm_plan** out) {
+    if (!ctx || !steps || n_steps <= 0 || !desc || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    *out = nullptr;
+    if (desc->max_batch < 1 || desc->max_batch > 16) { set_error("max_batch %d outside 1..16", desc->max_batch); return SWLM_ERR_INVALID; }
+    if (desc->hidden % 8 || desc->slot_dim % 8 || desc->vocab % 8) { set_error("hidden, slot_dim and vocab must be multiples of 8"); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    swlm_plan* plan = new swlm_plan();
+    plan->ctx = ctx;
+    plan->desc = *desc;
+    plan->steps.assign(steps, steps + n_steps);
+    rc = compile_plan(plan);
+    if (rc) { swlm_plan_destroy(plan); return rc; }
+    plan->attn_scratch = 0;
+    for (const Launch& L : plan->launches)
+        if (L.kind == L_ATTN)
+            plan->attn_scratch = std::max(plan->attn_scratch, attn_scratch_floats(desc->max_batch, L.st.heads / ctx->tp_size, L.st.head_dim, plan->attn_splits));
+    *out = plan;
+    return SWLM_OK;
+}
+
+void swlm_plan_destroy(swlm_plan* plan) {
+    if (!plan) return;
+    for (RopeTable& t : plan->rope_tables) cudaFree(t.inv_freq);
+    delete plan;
+}
+
+int swlm_plan_launch_count(const swlm_plan* plan) { return plan ? launches_per_step(plan, false) : 0; }
+
+int swlm_plan_describe(const swlm_plan* plan, char* dst, int cap) {
+    if (!plan) return 0;
+    std::string s;
+    char line[256];
+    for (size_t i = 0; i < plan->launches.size(); ++i) {
+        const Launch& L = plan->launches[i];
+        snprintf(line, sizeof(line), "%3zu %-60s steps=%d\n", i, L.label.c_str(), L.steps_covered);
+        s += line;
+    }
+    if (dst && cap > 0) {
+        const size_t c = std::min((size_t)cap - 1, s.size());
+        memcpy(dst, s.data(), c);
+        dst[c] = 0;
+    }
+    return (int)s.size() + 1;
+}
+
+int swlm_state_create(swlm_plan* plan, swlm_state** out) {
+    if (!plan || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    *out = nullptr;
+    int rc = ensure_device(plan->ctx);
+    if (rc) return rc;
+    const swlm_buffers_desc& d = plan->desc;
+    swlm_state* s = new swlm_state();
+    s->plan = plan;
+    auto fail = [&](int code) { swlm_state_destroy(s); return code; };
+    cudaError_t e = cudaStreamCreateWithFlags(&s->own_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return fail(cuda_fail(e, "cudaStreamCreate"));
+    s->stream = s->own_stream;
+    for (int i = 0; i < SWLM_BUF_COUNT; ++i) {
+        s->width[i] = buf_width(d, i);
+        if ((rc = dev_alloc(&s->buf[i], (size_t)d.max_batch * s->width[i]))) return fail(rc);
+    }
+    s->kv_layer_elems = (size_t)d.max_batch * kv_heads_local(plan) * d.max_seq * d.head_dim;
+    if ((rc = dev_alloc(&s->kcache, (size_t)d.kv_layers * s->kv_layer_elems))) return fail(rc);
+    if ((rc = dev_alloc(&s->vcache, (size_t)d.kv_layers * s->kv_layer_elems))) return fail(rc);
+    s->conv_layer_elems = (size_t)d.max_batch * d.conv_kernel * d.conv_dim;
+    if ((rc = dev_alloc(&s->conv, (size_t)d.conv_layers * s->conv_layer_elems))) return fail(rc);
+    if ((rc = dev_alloc(&s->position, 1))) return fail(rc);
+    if ((rc = dev_alloc(&s->step_counter, 1))) return fail(rc);
+    if ((rc = dev_alloc(&s->token_in, d.max_batch))) return fail(rc);
+    if ((rc = dev_alloc(&s->token_out, d.max_batch))) return fail(rc);
+    if ((rc = dev_alloc(&s->ring, (size_t)s->ring_cap * d.max_batch))) return fail(rc);
+    if ((rc = dev_alloc(&s->attn_scratch, plan->attn_scratch))) return fail(rc);
+    if ((rc = dev_alloc(&s->qgemv_partial, plan->qgemv_partial))) return fail(rc);
+    if ((rc = dev_alloc(&s->qgemv_counters, plan->qgemv_counters))) return fail(rc);
+    if ((rc = dev_alloc(&s->argmax_val, argmax_scratch_elems(d.max_batch)))) return fail(rc);
+    if ((rc = dev_alloc(&s->argmax_idx, argmax_scratch_elems(d.max_batch)))) return fail(rc);
+    e = cudaMallocHost((void**)&s->h_tok, sizeof(int32_t) * 2 * d.max_batch);
+    if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMallocHost"));
+    if (s->qgemv_counters) {
+        e = cudaMemset(s->qgemv_counters, 0, plan->qgemv_counters * sizeof(unsigned));
+        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemset"));
+    }
+    *out = s;
+    rc = swlm_state_reset(s);
+    if (rc) { *out = nullptr; return fail(rc); }
+    return SWLM_OK;
+}
+
+void swlm_state_destroy(swlm_state* s) {
+    if (!s) return;
+    cudaSetDevice(s->plan->ctx->device);
+    if (s->stream) cudaStreamSynchronize(s->stream);
+    drop_graphs(s);
+    for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->buf[i]);
+    cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->conv);
+    cudaFree(s->position); cudaFree(s->step_counter); cudaFree(s->token_in); cudaFree(s->token_out); cudaFree(s->ring);
+    cudaFree(s->prompt);
+    cudaFree(s->attn_scratch); cudaFree(s->qgemv_partial); cudaFree(s->qgemv_counters);
+    cudaFree(s->argmax_val); cudaFree(s->argmax_idx);
+    if (s->h_tok) cudaFreeHost(s->h_tok);
+    if (s->own_stream) cudaStreamDestroy(s->own_stream);
+    delete s;
+}
+
+int swlm_state_set_stream(swlm_state* s, void* cuda_stream) {
+    if (!s) { set_error("null state"); return SWLM_ERR_INVALID; }
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    s->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : s->own_stream;
+    return SWLM_OK;
+}
+
+int swlm_state_reset(swlm_state* s) {
+    if (!s) { set_error("null state"); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(s->plan->ctx);
+    if (rc) return rc;
+    for (const Region& r : state_regions(s))
+        if (r.bytes) SWLM_CUDA(cudaMemsetAsync(r.p, 0, r.bytes, s->stream));
+    SWLM_CUDA(cudaMemsetAsync(s->step_counter, 0, 4, s->stream));
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    s->pos_host = 0;
+    s->steps_host = 0;
+    return SWLM_OK;
+}
+
+int swlm_state_snapshot(swlm_state* s, swlm_snap** out) {
+    if (!s || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    *out = nullptr;
+    int rc = ensure_device(s->plan->ctx);
+    if (rc) return rc;
+    swlm_snap* snap = new swlm_snap();
+    for (const Region& r : state_regions(s)) {
+        void* p = nullptr;
+        if (r.bytes) {
+            cudaError_t e = cudaMalloc(&p, r.bytes);
+            if (e != cudaSuccess) { swlm_snap_destroy(snap); return cuda_fail(e, "cudaMalloc(snapshot)"); }
+            e = cudaMemcpyAsync(p, r.p, r.bytes, cudaMemcpyDeviceToDevice, s->stream);
+            if (e != cudaSuccess) { cudaFree(p); swlm_snap_destroy(snap); return cuda_fail(e, "cudaMemcpyAsync(snapshot)"); }
+        }
+        snap->dev.push_back(p);
+        snap->bytes.push_back(r.bytes);
+    }
+    snap->pos_host = s->pos_host;
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    *out = snap;
+    return SWLM_OK;
+}
+
+int swlm_state_restore(swlm_state* s, const swlm_snap* snap) {
+    if (!s || !snap) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    std::vector<Region> regions = state_regions(s);
+    if (regions.size() != snap->dev.size()) { set_error("snapshot belongs to another plan"); return SWLM_ERR_STATE; }
+    for (size_t i = 0; i < regions.size(); ++i) {
+        if (regions[i].bytes != snap->bytes[i]) { set_error("snapshot belongs to another plan"); return SWLM_ERR_STATE; }
+        if (regions[i].bytes) SWLM_CUDA(cudaMemcpyAsync(regions[i].p, snap->dev[i], regions[i].bytes, cudaMemcpyDeviceToDevice, s->stream));
+    }
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    s->pos_host = snap->pos_host;
+    return SWLM_OK;
+}
+
+void swlm_snap_destroy(swlm_snap* snap) {
+    if (!snap) return;
+    for (void* p : snap->dev) cudaFree(p);
+    delete snap;
+}
+
+int swlm_position(const swlm_state* s) { return s ? s->pos_host : -1; }
+
+int swlm_set_position(swlm_state* s, int position) {
+    if (!s || position < 0 || position > s->plan->desc.max_seq) { set_error("bad position"); return SWLM_ERR_INVALID; }
+    SWLM_CUDA(cudaMemcpyAsync(s->position, &position, 4, cudaMemcpyHostToDevice, s->stream));
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    s->pos_host = position;
+    return SWLM_OK;
+}
+
+int swlm_sync(swlm_state* s) {
+    if (!s) { set_error("null state"); return SWLM_ERR_INVALID; }
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    return SWLM_OK;
+}
+
+int swlm_decode(swlm_state* s, const int32_t* token_in, int32_t* token_out) {
+    if (!s || !token_in || !token_out) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    const int m = s->plan->desc.max_batch;
+    for (int b = 0; b < m; ++b) token_out[b] = -1;
+    int rc = ensure_device(s->plan->ctx);
+    if (!rc) rc = check_position_room(s, 1);
+    if (rc) return rc;
+    memcpy(s->h_tok, token_in, sizeof(int32_t) * m);
+    SWLM_CUDA(cudaMemcpyAsync(s->token_in, s->h_tok, sizeof(int32_t) * m, cudaMemcpyHostToDevice, s->stream));
+    rc = run_graph(s, false);
+    if (rc) return rc;
+    SWLM_CUDA(cudaMemcpyAsync(s->h_tok + m, s->token_out, sizeof(int32_t) * m, cudaMemcpyDeviceToHost, s->stream));
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    memcpy(token_out, s->h_tok + m, sizeof(int32_t) * m);
+    return SWLM_OK;
+}
+
+int swlm_decode_n_async(swlm_state* s, const int32_t* token_in, int n) {
+    if (!s || n < 0) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    const int m = s->plan->desc.max_batch;
+    int rc = ensure_device(s->plan->ctx);
+    if (!rc) rc = check_position_room(s, n);
+    if (rc) return rc;
+    if (n > s->ring_cap) { set_error("decode_n: n=%d exceeds the token ring (%d)", n, s->ring_cap); return SWLM_ERR_INVALID; }
+    if (token_in) {
+        memcpy(s->h_tok, token_in, sizeof(int32_t) * m);
+        SWLM_CUDA(cudaMemcpyAsync(s->token_in, s->h_tok, sizeof(int32_t) * m, cudaMemcpyHostToDevice, s->stream));
+    }
+    for (int i = 0; i < n; ++i) {
+        rc = run_graph(s, false);
+        if (rc) return rc;
+    }
+    return SWLM_OK;
+}
+
+int swlm_read_tokens(swlm_state* s, int n, int32_t* tokens_out) {
+    if (!s || !tokens_out || n < 0 || n > s->ring_cap) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    const int m = s->plan->desc.max_batch;
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    // the last n steps occupy ring slots (steps-n .. steps-1) mod ring_cap
+    for (int i = 0; i < n; ++i) {
+        const long long step = s->steps_host - n + i;
+        if (step < 0) { set_error("fewer than %d steps decoded", n); return SWLM_ERR_STATE; }
+        SWLM_CUDA(cudaMemcpy(tokens_out + (size_t)i * m, s->ring + (size_t)(step % s->ring_cap) * m, sizeof(int32_t) * m, cudaMemcpyDeviceToHost));
+    }
+    return SWLM_OK;
+}
+
+int swlm_decode_n(swlm_state* s, const int32_t* token_in, int n, int32_t* tokens_out) {
+    if (!tokens_out) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    int rc = swlm_decode_n_async(s, token_in, n);
+    if (rc) return rc;
+    return swlm_read_tokens(s, n, tokens_out);
+}
+
+int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_token) {
+    if (!s || !tokens || !first_token || n <= 0) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    const int m = s->plan->desc.max_batch;
+    for (int b = 0; b < m; ++b) first_token[b] = -1;
+    int rc = ensure_device(s->plan->ctx);
+    if (!rc) rc = check_position_room(s, n);
+    if (rc) return rc;
+    // token-major copy of the prompt so that step t reads m consecutive ids
+    std::vector<int32_t> tm((size_t)n * m);
+    for (int b = 0; b < m; ++b)
+        for (int t = 0; t < n; ++t) tm[(size_t)t * m + b] = tokens[(size_t)b * n + t];
+    if (s->prompt_cap < tm.size()) {
+        cudaFree(s->prompt);
+        s->prompt = nullptr; s->prompt_cap = 0;
+        if ((rc = dev_alloc(&s->prompt, tm.size()))) return rc;
+        s->prompt_cap = tm.size();
+    }
+    SWLM_CUDA(cudaMemcpyAsync(s->prompt, tm.data(), tm.size() * 4, cudaMemcpyHostToDevice, s->stream));
+    // Every prompt token runs the layer stack; only the last one runs the output head, as the reference's
+    // prefill replays the decode plan's lm_head + argmax for the final position
+    // (Execution/MetalPrefillExecutor.swift:1320-1359).
+    for (int t = 0; t < n; ++t) {
+        SWLM_CUDA(cudaMemcpyAsync(s->token_in, s->prompt + (size_t)t * m, sizeof(int32_t) * m, cudaMemcpyDeviceToDevice, s->stream));
+        rc = run_graph(s, t + 1 < n);
+        if (rc) return rc;
+    }
+    SWLM_CUDA(cudaMemcpyAsync(s->h_tok + m, s->token_out, sizeof(int32_t) * m, cudaMemcpyDeviceToHost, s->stream));
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    memcpy(first_token, s->h_tok + m, sizeof(int32_t) * m);
+    return SWLM_OK;
+}
+
+int swlm_read_buffer(swlm_state* s, int buf, uint16_t* dst, int count_per_row) {
+    if (!s || !dst || !buf_ok(buf) || count_per_row > s->width[buf]) { set_error("bad buffer read"); return SWLM_ERR_INVALID; }
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    SWLM_CUDA(cudaMemcpy2D(dst, (size_t)count_per_row * 2, s->buf[buf], (size_t)s->width[buf] * 2, (size_t)count_per_row * 2,
+                           s->plan->desc.max_batch, cudaMemcpyDeviceToHost));
+    return SWLM_OK;
+}
+
+int swlm_write_buffer(swlm_state* s, int buf, const uint16_t* src, int count_per_row) {
+    if (!s || !src || !buf_ok(buf) || count_per_row > s->width[buf]) { set_error("bad buffer write"); return SWLM_ERR_INVALID; }
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    SWLM_CUDA(cudaMemcpy2D(s->buf[buf], (size_t)s->width[buf] * 2, src, (size_t)count_per_row * 2, (size_t)count_per_row * 2,
+                           s->plan->desc.max_batch, cudaMemcpyHostToDevice));
+    return SWLM_OK;
+}
+
+int swlm_read_logits(swlm_state* s, uint16_t* dst, size_t count) {
+    if (!s || !dst) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (count != (size_t)d.max_batch * d.vocab) { set_error("logits are [%d][%d]", d.max_batch, d.vocab); return SWLM_ERR_INVALID; }
+    return swlm_read_buffer(s, SWLM_BUF_LOGITS, dst, d.vocab);
+}
+
+static int kv_ptr(swlm_state* s, int which, int layer, int b, int head, int count, __nv_bfloat16** p) {
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (layer < 0 || layer >= d.kv_layers || b < 0 || b >= d.max_batch || head < 0 || head >= kv_heads_local(s->plan) ||
+        count < 0 || count > d.max_seq) { set_error("bad KV address"); return SWLM_ERR_INVALID; }
+    __nv_bfloat16* base = which ? s->vcache : s->kcache;
+    *p = base + (size_t)layer * s->kv_layer_elems + ((size_t)b * kv_heads_local(s->plan) + head) * d.max_seq * d.head_dim;
+    return SWLM_OK;
+}
+
+int swlm_read_kv(swlm_state* s, int which, int layer, int b, int head, int count, uint16_t* dst) {
+    if (!s || !dst) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    __nv_bfloat16* p;
+    int rc = kv_ptr(s, which, layer, b, head, count, &p);
+    if (rc) return rc;
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    SWLM_CUDA(cudaMemcpy(dst, p, (size_t)count * s->plan->desc.head_dim * 2, cudaMemcpyDeviceToHost));
+    return SWLM_OK;
+}
+
+int swlm_write_kv(swlm_state* s, int which, int layer, int b, int head, int count, const uint16_t* src) {
+    if (!s || !src) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    __nv_bfloat16* p;
+    int rc = kv_ptr(s, which, layer, b, head, count, &p);
+    if (rc) return rc;
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    SWLM_CUDA(cudaMemcpy(p, src, (size_t)count * s->plan->desc.head_dim * 2, cudaMemcpyHostToDevice));
+    return SWLM_OK;
+}
+
+int swlm_read_conv(swlm_state* s, int layer, int b, uint16_t* dst) {
+    if (!s || !dst) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (layer < 0 || layer >= d.conv_layers || b < 0 || b >= d.max_batch) { set_error("bad conv address"); return SWLM_ERR_INVALID; }
+    const size_t n = (size_t)d.conv_kernel * d.conv_dim;
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    SWLM_CUDA(cudaMemcpy(dst, s->conv + (size_t)layer * s->conv_layer_elems + (size_t)b * n, n * 2, cudaMemcpyDeviceToHost));
+    return SWLM_OK;
+}
+
+int swlm_run_step(swlm_state* s, const swlm_step* step, const int32_t* token_in, int32_t* token_out) {
+    if (!s || !step) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    const int m = s->plan->desc.max_batch;
+    int rc = ensure_device(s->plan->ctx);
+    if (rc) return rc;
+    // compile a one-step plan against the same weight store and buffer set, run it eagerly
+    swlm_plan tmp;
+    tmp.ctx = s->plan->ctx;
+    tmp.desc = s->plan->desc;
+    tmp.steps.assign(step, step + 1);
+    rc = compile_plan(&tmp);
+    if (rc) return rc;
+    tmp.attn_splits = s->plan->attn_splits;
+    if (token_in) SWLM_CUDA(cudaMemcpyAsync(s->token_in, token_in, sizeof(int32_t) * m, cudaMemcpyHostToDevice, s->stream));
+    swlm_plan* saved = s->plan;
+    int saved_pos = s->pos_host;
+    // an argmax step advances the device position; keep single-step runs position-neutral
+    s->plan = &tmp;
+    rc = enqueue_step(s, false, s->stream);
+    s->plan = saved;
+    cudaError_t e = cudaStreamSynchronize(s->stream);
+    for (RopeTable& t : tmp.rope_tables) cudaFree(t.inv_freq);
+    if (rc) return rc;
+    if (e != cudaSuccess) return cuda_fail(e, "run_step sync");
+    SWLM_CUDA(cudaMemcpy(s->position, &saved_pos, 4, cudaMemcpyHostToDevice));
+    const int32_t saved_steps = (int32_t)s->steps_host;
+    SWLM_CUDA(cudaMemcpy(s->step_counter, &saved_steps, 4, cudaMemcpyHostToDevice));
+    if (token_out) SWLM_CUDA(cudaMemcpy(token_out, s->token_out, sizeof(int32_t) * m, cudaMemcpyDeviceToHost));
+    return SWLM_OK;
+}
+
+int64_t swlm_launches(const swlm_state* s) { return s ? s->launches : 0; }
+
+// ---- op-level ------------------------------------------------------------------------------------------
+
+static int op_scratch(swlm_ctx* ctx, const Q4Tiled& w, int m) {
+    const size_t pf = qgemv_scratch_floats(w, m), cc = (size_t)qgemv_counter_count(w);
+    if (pf > ctx->op_partial_floats) {
+        cudaFree(ctx->op_partial);
+        ctx->op_partial = nullptr; ctx->op_partial_floats = 0;
+        int rc = dev_alloc(&ctx->op_partial, pf);
+        if (rc) return rc;
+        ctx->op_partial_floats = pf;
+    }
+    if (cc > ctx->op_counter_count) {
+        cudaFree(ctx->op_counters);
+        ctx->op_counters = nullptr; ctx->op_counter_count = 0;
+        int rc = dev_alloc(&ctx->op_counters, cc);
+        if (rc) return rc;
+        SWLM_CUDA(cudaMemset(ctx->op_counters, 0, cc * sizeof(unsigned)));
+        ctx->op_counter_count = cc;
+    }
+    return SWLM_OK;
+}
+
+int swlm_op_qgemm_dev(swlm_ctx* ctx, const char* weight, int m, const void* x_dev, void* y_dev, void* cuda_stream) {
+    if (!ctx || !weight || !x_dev || !y_dev) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    const Q4Tiled* w;
+    rc = get_tiled(ctx, {weight}, 0, &w);
+    if (rc) return rc;
+    cudaStream_t stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->stream;
+    // m > 16 runs as passes of 16 rows: each pass re-streams the weights
+    for (int m0 = 0; m0 < m; m0 += 16) {
+        const int mc = std::min(16, m - m0);
+        rc = op_scratch(ctx, *w, mc);
+        if (rc) return rc;
+        QGemvLaunch a;
+        a.w = w; a.m = mc;
+        a.x = static_cast<const __nv_bfloat16*>(x_dev) + (size_t)m0 * w->k; a.x_stride = w->k;
+        a.y[0] = static_cast<__nv_bfloat16*>(y_dev) + (size_t)m0 * w->n; a.y_stride[0] = w->n; a.seg_end[0] = w->n;
+        a.partial = ctx->op_partial; a.counters = ctx->op_counters;
+        rc = launch_qgemv(a, stream);
+        if (rc) return rc;
+    }
+    return SWLM_OK;
+}
+
+int swlm_op_qgemm(swlm_ctx* ctx, const char* weight, int m, const uint16_t* x_bf16, uint16_t* y_bf16) {
+    if (!ctx || !weight || !x_bf16 || !y_bf16 || m <= 0) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    const Q4Tiled* w;
+    rc = get_tiled(ctx, {weight}, 0, &w);
+    if (rc) return rc;
+    __nv_bfloat16 *x = nullptr, *y = nullptr;
+    if ((rc = dev_alloc(&x, (size_t)m * w->k))) return rc;
+    if ((rc = dev_alloc(&y, (size_t)m * w->n))) { cudaFree(x); return rc; }
+    cudaError_t e = cudaMemcpyAsync(x, x_bf16, (size_t)m * w->k * 2, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) {
+        rc = swlm_op_qgemm_dev(ctx, weight, m, x, y, ctx->stream);
+        if (!rc) e = cudaMemcpyAsync(y_bf16, y, (size_t)m * w->n * 2, cudaMemcpyDeviceToHost, ctx->stream);
+    }
+    cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
+    cudaFree(x); cudaFree(y);
+    if (rc) return rc;
+    if (e != cudaSuccess) return cuda_fail(e, "qgemm copies");
+    if (e2 != cudaSuccess) return cuda_fail(e2, "qgemm sync");
+    return SWLM_OK;
+}
+
+int swlm_op_dequant_bf16(swlm_ctx* ctx, const char* weight, uint16_t* out_bf16) {
+    if (!ctx || !weight || !out_bf16) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    const Q4Tiled* w;
+    rc = get_tiled(ctx, {weight}, 0, &w);
+    if (rc) return rc;
+    __nv_bfloat16* d = nullptr;
+    if ((rc = dev_alloc(&d, (size_t)w->n * w->k))) return rc;
+    rc = launch_untile_bf16(*w, d, ctx->stream);
+    cudaError_t e = cudaSuccess;
+    if (!rc) e = cudaMemcpyAsync(out_bf16, d, (size_t)w->n * w->k * 2, cudaMemcpyDeviceToHost, ctx->stream);
+    cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
+    cudaFree(d);
+    if (rc) return rc;
+    if (e != cudaSuccess) return cuda_fail(e, "dequant copy");
+    if (e2 != cudaSuccess) return cuda_fail(e2, "dequant sync");
+    return SWLM_OK;
+}
+
+static int flash_splits(int b, int kv_heads, int ctx_len) { return attn_pick_splits(b, kv_heads, ctx_len); }
+
+size_t swlm_op_flash_decode_scratch_bytes(int b, int heads, int kv_heads, int hd, int ctx_len) {
+    return attn_scratch_floats(b, heads, hd, flash_splits(b, kv_heads, ctx_len)) * sizeof(float);
+}
+
+int swlm_op_flash_decode_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride,
+                             float scale, const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev,
+                             void* scratch_dev, void* cuda_stream) {
+    if (!ctx || !q_dev || !k_dev || !v_dev || !out_dev || !scratch_dev || b <= 0 || ctx_len <= 0 || ctx_len > ctx_stride) {
+        set_error("bad argument");
+        return SWLM_ERR_INVALID;
+    }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    cudaStream_t stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->stream;
+    return launch_flash_decode_plain(b, heads, kv_heads, hd, ctx_len, ctx_stride, scale, static_cast<const __nv_bfloat16*>(q_dev),
+                                     static_cast<const __nv_bfloat16*>(k_dev), static_cast<const __nv_bfloat16*>(v_dev),
+                                     static_cast<__nv_bfloat16*>(out_dev), static_cast<float*>(scratch_dev),
+                                     flash_splits(b, kv_heads, ctx_len), stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,149 @@
+// Internal declarations shared by the translation units of libswlm_cuda.so.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/swlm.h"
+
+namespace swlm {
+
+// ---- errors ------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);  // records the message, returns SWLM_ERR_CUDA
+#define SWLM_CUDA(call)                                          \
+    do {                                                         \
+        cudaError_t e__ = (call);                                \
+        if (e__ != cudaSuccess) return ::swlm::cuda_fail(e__, #call); \
+    } while (0)
+
+// ---- device tensors -----------------------------------------------------------
+//
+// Q4 group-64 tensor in the streaming layout of the GEMV/GEMM kernels.
+//   tiles : uint4[row_tiles][kt_pad][32]   one 512-byte tile = 16 rows x 64 columns,
+//           lane (g = lane>>2, t = lane&3) owns 16 bytes = 4 words; word j, nibble e holds
+//           W[16*rt + g + 8*(e&1)][64*kt + 16*j + 2*t + (e>>2) + 8*((e>>1)&1)],
+//           which is the A-fragment order of mma.m16n8k16 for k-step j.
+//   sb    : uint4[row_tiles][kt_pad/4][16]  per row, four consecutive groups' (scale, zero)
+//           pairs, each pair two 16-bit floats (bf16, or fp16 when the source was STAF).
+// kt_pad = K/64 rounded up to a multiple of 4; padding tiles hold q = 0, scale = zero = 0.
+struct Q4Tiled {
+    int n = 0, k = 0;           // logical (per-rank) shape
+    int row_tiles = 0;          // ceil(n / 16)
+    int kt_pad = 0;             // k-tiles including padding
+    bool sb_f16 = false;        // scale/zero stored as fp16 instead of bf16
+    bool interleaved = false;   // rows 0-7 of each tile from source A, rows 8-15 from source B
+    uint4* tiles = nullptr;
+    uint4* sb = nullptr;
+    size_t bytes() const { return (size_t)row_tiles * kt_pad * 512 + (size_t)row_tiles * (kt_pad / 4) * 256; }
+};
+
+// Raw source copy kept on the device so that fused tensors can be assembled at plan time.
+struct Q4Raw {
+    int n = 0, k = 0;
+    bool sb_f16 = false;
+    int shard_kind = 0;
+    uint32_t* w = nullptr;      // [n][k/8]
+    uint16_t* scales = nullptr; // [n][k/64]
+    uint16_t* biases = nullptr;
+};
+
+struct DenseTensor {
+    int64_t rows = 0, cols = 0;
+    int shard_kind = 0;
+    __nv_bfloat16* data = nullptr;
+};
+
+// ---- kernels: launch wrappers (each returns a status; no synchronisation) -------
+
+struct RepackSrc {
+    const uint32_t* w;
+    const uint16_t* scales;
+    const uint16_t* biases;
+    int n;
+};
+// Build a tiled tensor from up to three raw sources that share K.
+// mode 0: rows concatenated; mode 1: two sources interleaved 8 rows each per tile.
+int launch_repack(const RepackSrc* src, int n_src, int mode, int k, const Q4Tiled& dst, cudaStream_t s);
+int launch_untile_bf16(const Q4Tiled& t, __nv_bfloat16* out, cudaStream_t s);
+
+enum { QGEMV_EPI_STORE = 0, QGEMV_EPI_SWIGLU = 1 };
+
+struct QGemvLaunch {
+    const Q4Tiled* w = nullptr;
+    const __nv_bfloat16* x = nullptr;  // [m][x_stride]
+    int x_stride = 0;
+    // result rows [0, seg_end[0]) go to y[0], [seg_end[0], seg_end[1]) to y[1], ... each [m][y_stride[i]]
+    __nv_bfloat16* y[3] = {nullptr, nullptr, nullptr};
+    int y_stride[3] = {0, 0, 0};
+    int seg_end[3] = {0, 0, 0};
+    int m = 1;
+    int epilogue = QGEMV_EPI_STORE;
+    float* partial = nullptr;     // split-K scratch, see qgemv_scratch_floats()
+    unsigned* counters = nullptr; // one per CTA row group, zero between launches
+};
+size_t qgemv_scratch_floats(const Q4Tiled& w, int m);
+int qgemv_counter_count(const Q4Tiled& w);
+int launch_qgemv(const QGemvLaunch& a, cudaStream_t s);
+int qgemv_init();  // sets shared-memory attributes once per process
+
+// rmsnorm family: mode = SWLM_STEP_COPY_RMSNORM / RESADD_COPY_RMSNORM / RESADD_RMSNORM
+int launch_rmsnorm(int mode, int m, int dim, const __nv_bfloat16* in, int in_stride, __nv_bfloat16* residual,
+                   int res_stride, const __nv_bfloat16* weight, float eps, float weight_bias,
+                   __nv_bfloat16* out, int out_stride, cudaStream_t s);
+int launch_qk_norm(int m, int heads, int kv_heads, int head_dim, __nv_bfloat16* q, int q_stride,
+                   __nv_bfloat16* k, int k_stride, const __nv_bfloat16* wq, const __nv_bfloat16* wk,
+                   float eps, float weight_bias, cudaStream_t s);
+int launch_embed(int m, int dim, const int32_t* tokens, int vocab, const __nv_bfloat16* table,
+                 __nv_bfloat16* out, int out_stride, cudaStream_t s);
+int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
+                  __nv_bfloat16* out, int o_stride, cudaStream_t s);
+int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,
+                     const __nv_bfloat16* in, int in_stride, const __nv_bfloat16* weight,
+                     __nv_bfloat16* out, int out_stride, cudaStream_t s);
+// argmax over [m][n] bf16, lowest index wins. Writes token_out[m], token_in_next[m] (may be null) and
+// ring[(step_counter % ring_cap) * m + b] (ring may be null); when advance != 0 the last thread also
+// increments the device-side position and step counter. Two launches.
+int launch_argmax(int m, int n, const __nv_bfloat16* logits, int stride, int32_t* token_out,
+                  int32_t* token_in_next, int32_t* ring, int32_t* step_counter, int ring_cap,
+                  int32_t* position, int advance, float* scratch_val, int32_t* scratch_idx, cudaStream_t s);
+size_t argmax_scratch_elems(int m);
+
+struct AttnLaunch {
+    int m = 1;            // sequences
+    int heads = 0, kv_heads = 0, head_dim = 0;
+    int rope_dim = 0;
+    const float* inv_freq = nullptr;  // [rope_dim/2] device
+    float scale = 1.f;
+    const __nv_bfloat16* q = nullptr; int q_stride = 0;   // [m][heads*hd]
+    const __nv_bfloat16* k = nullptr; int k_stride = 0;   // new token's k [m][kv_heads*hd]
+    const __nv_bfloat16* v = nullptr; int v_stride = 0;
+    __nv_bfloat16* kcache = nullptr;  // [m][kv_heads][max_seq][hd]
+    __nv_bfloat16* vcache = nullptr;
+    int max_seq = 0;
+    const int32_t* position = nullptr;  // device scalar: index of the new token
+    __nv_bfloat16* out = nullptr; int out_stride = 0;
+    float* scratch = nullptr;   // attn_scratch_floats()
+    int splits = 1;             // KV splits per (sequence, kv head)
+};
+int attn_pick_splits(int m, int kv_heads, int max_ctx);
+size_t attn_scratch_floats(int m, int heads, int head_dim, int splits);
+// decode: q rows are unrotated; RoPE, KV append and the current token's unrounded term are handled inside.
+int launch_attn_decode(const AttnLaunch& a, cudaStream_t s);
+// generic flash-decode over an existing cache (q already rotated), ctx_len fixed on the host.
+int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, float scale,
+                              const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                              __nv_bfloat16* out, float* scratch, int splits, cudaStream_t s);
+int attn_init();
+
+int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s);
+int launch_advance(int32_t* position, int32_t* step_counter, cudaStream_t s);
+
+}  // namespace swlm

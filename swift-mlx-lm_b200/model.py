@@ -1,0 +1,224 @@
+"""Host-side mirror of the reference's weight store and inference model over the C ABI.
+
+`WeightStore` stands for `STAFWeightStore` (Sources/MetalCompiler/STAF/STAFLoader.swift:213-299) and
+`InferenceModel` for `MetalInferenceModel` (Sources/MetalCompiler/Execution/MetalInferenceModel.swift:
+prefill :464, decode :311, resetState :1911, promptSnapshot/restore :1897-1906, position :9).
+Method names keep the reference's meaning; errors raise `SwlmError` where the reference throws, and a
+failed decode returns token -1 as `MetalDecodeExecutor` does (Execution/MetalDecodeExecutor.swift:33-42).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from .lib import BuffersDesc, Library, Step, SwlmError, load_library
+
+
+def _ptr(a: np.ndarray) -> C.c_void_p:
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class WeightStore:
+    def __init__(self, device: int = 0, tp_rank: int = 0, tp_size: int = 1, lib: Optional[Library] = None):
+        self.lib = lib or load_library()
+        self.handle = C.c_void_p()
+        self.lib.check(self.lib.swlm_ctx_create(device, tp_rank, tp_size, C.byref(self.handle)))
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.swlm_ctx_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def add_q4_mlx(self, name: str, weight: np.ndarray, scales_bf16: np.ndarray, biases_bf16: np.ndarray, shard: int = 0) -> None:
+        w = np.ascontiguousarray(weight, dtype=np.uint32)
+        s = np.ascontiguousarray(scales_bf16, dtype=np.uint16)
+        b = np.ascontiguousarray(biases_bf16, dtype=np.uint16)
+        n, words = w.shape
+        self.lib.check(self.lib.swlm_weights_add_q4g64_mlx(self.handle, name.encode(), n, words * 8, _ptr(w), _ptr(s), _ptr(b), shard))
+
+    def add_q4_staf(self, name: str, blocks: np.ndarray, n: int, k: int, shard: int = 0) -> None:
+        blk = np.ascontiguousarray(blocks, dtype=np.uint8)
+        self.lib.check(self.lib.swlm_weights_add_q4g64_staf(self.handle, name.encode(), n, k, _ptr(blk), shard))
+
+    def add_dense(self, name: str, data_bf16: np.ndarray, shard: int = 0) -> None:
+        d = np.ascontiguousarray(data_bf16, dtype=np.uint16)
+        rows = d.shape[0] if d.ndim == 2 else 1
+        cols = d.size // rows
+        self.lib.check(self.lib.swlm_weights_add_dense_bf16(self.handle, name.encode(), rows, cols, _ptr(d), shard))
+
+    @property
+    def resident_bytes(self) -> int:
+        return int(self.lib.swlm_weights_bytes(self.handle))
+
+    # op-level entry points -----------------------------------------------------------------------
+    def qgemm(self, name: str, x_bf16: np.ndarray, n: int) -> np.ndarray:
+        x = np.ascontiguousarray(x_bf16, dtype=np.uint16)
+        m = x.shape[0]
+        y = np.empty((m, n), dtype=np.uint16)
+        self.lib.check(self.lib.swlm_op_qgemm(self.handle, name.encode(), m, _ptr(x), _ptr(y)))
+        return y
+
+    def dequant_bf16(self, name: str, n: int, k: int) -> np.ndarray:
+        out = np.empty((n, k), dtype=np.uint16)
+        self.lib.check(self.lib.swlm_op_dequant_bf16(self.handle, name.encode(), _ptr(out)))
+        return out
+
+
+class InferenceModel:
+    """Compiled plan + one isolated runtime state."""
+
+    def __init__(self, store: WeightStore, steps: Sequence[Step], desc: BuffersDesc):
+        self.store = store
+        self.lib = store.lib
+        self.desc = desc
+        self.batch = int(desc.max_batch)
+        arr = (Step * len(steps))(*steps)
+        self.plan = C.c_void_p()
+        self.lib.check(self.lib.swlm_plan_build(store.handle, arr, len(steps), C.byref(desc), C.byref(self.plan)))
+        self.state = C.c_void_p()
+        self.lib.check(self.lib.swlm_state_create(self.plan, C.byref(self.state)))
+
+    def close(self) -> None:
+        if getattr(self, "state", None):
+            self.lib.swlm_state_destroy(self.state)
+            self.state = C.c_void_p()
+        if getattr(self, "plan", None):
+            self.lib.swlm_plan_destroy(self.plan)
+            self.plan = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- reference surface ---------------------------------------------------------------------------
+    @property
+    def position(self) -> int:
+        return int(self.lib.swlm_position(self.state))
+
+    def reset_state(self) -> None:
+        self.lib.check(self.lib.swlm_state_reset(self.state))
+
+    def prefill(self, tokens) -> np.ndarray:
+        t = np.ascontiguousarray(np.atleast_2d(np.asarray(tokens, dtype=np.int32)))
+        assert t.shape[0] == self.batch
+        first = np.empty(self.batch, dtype=np.int32)
+        self.lib.check(self.lib.swlm_prefill(self.state, _ptr(t), t.shape[1], _ptr(first)))
+        return first
+
+    def decode(self, token_in) -> np.ndarray:
+        t = np.ascontiguousarray(np.asarray(token_in, dtype=np.int32).reshape(self.batch))
+        out = np.empty(self.batch, dtype=np.int32)
+        self.lib.check(self.lib.swlm_decode(self.state, _ptr(t), _ptr(out)))
+        return out
+
+    def decode_n(self, token_in, n: int) -> np.ndarray:
+        t = np.ascontiguousarray(np.asarray(token_in, dtype=np.int32).reshape(self.batch))
+        out = np.empty((n, self.batch), dtype=np.int32)
+        self.lib.check(self.lib.swlm_decode_n(self.state, _ptr(t), n, _ptr(out)))
+        return out
+
+    def decode_n_async(self, token_in, n: int) -> None:
+        p = None
+        if token_in is not None:
+            t = np.ascontiguousarray(np.asarray(token_in, dtype=np.int32).reshape(self.batch))
+            p = _ptr(t)
+        self.lib.check(self.lib.swlm_decode_n_async(self.state, p, n))
+
+    def read_tokens(self, n: int) -> np.ndarray:
+        out = np.empty((n, self.batch), dtype=np.int32)
+        self.lib.check(self.lib.swlm_read_tokens(self.state, n, _ptr(out)))
+        return out
+
+    def sync(self) -> None:
+        self.lib.check(self.lib.swlm_sync(self.state))
+
+    def set_stream(self, cuda_stream: int) -> None:
+        self.lib.check(self.lib.swlm_state_set_stream(self.state, C.c_void_p(cuda_stream)))
+
+    def prompt_snapshot(self) -> C.c_void_p:
+        snap = C.c_void_p()
+        self.lib.check(self.lib.swlm_state_snapshot(self.state, C.byref(snap)))
+        return snap
+
+    def restore(self, snap: C.c_void_p) -> None:
+        self.lib.check(self.lib.swlm_state_restore(self.state, snap))
+
+    def free_snapshot(self, snap: C.c_void_p) -> None:
+        self.lib.swlm_snap_destroy(snap)
+
+    def logits(self) -> np.ndarray:
+        out = np.empty((self.batch, int(self.desc.vocab)), dtype=np.uint16)
+        self.lib.check(self.lib.swlm_read_logits(self.state, _ptr(out), out.size))
+        return out
+
+    # -- probes -----------------------------------------------------------------------------------------
+    def read_buffer(self, buf: int, count: int) -> np.ndarray:
+        out = np.empty((self.batch, count), dtype=np.uint16)
+        self.lib.check(self.lib.swlm_read_buffer(self.state, buf, _ptr(out), count))
+        return out
+
+    def write_buffer(self, buf: int, data_bf16: np.ndarray) -> None:
+        d = np.ascontiguousarray(data_bf16, dtype=np.uint16).reshape(self.batch, -1)
+        self.lib.check(self.lib.swlm_write_buffer(self.state, buf, _ptr(d), d.shape[1]))
+
+    def read_kv(self, which: int, layer: int, b: int, head: int, count: int) -> np.ndarray:
+        out = np.empty((count, int(self.desc.head_dim)), dtype=np.uint16)
+        self.lib.check(self.lib.swlm_read_kv(self.state, which, layer, b, head, count, _ptr(out)))
+        return out
+
+    def write_kv(self, which: int, layer: int, b: int, head: int, rows_bf16: np.ndarray) -> None:
+        d = np.ascontiguousarray(rows_bf16, dtype=np.uint16)
+        self.lib.check(self.lib.swlm_write_kv(self.state, which, layer, b, head, d.shape[0], _ptr(d)))
+
+    def read_conv(self, layer: int, b: int) -> np.ndarray:
+        out = np.empty((int(self.desc.conv_kernel), int(self.desc.conv_dim)), dtype=np.uint16)
+        self.lib.check(self.lib.swlm_read_conv(self.state, layer, b, _ptr(out)))
+        return out
+
+    def set_position(self, position: int) -> None:
+        self.lib.check(self.lib.swlm_set_position(self.state, position))
+
+    def run_step(self, step: Step, token_in=None) -> np.ndarray:
+        tin = None
+        if token_in is not None:
+            t = np.ascontiguousarray(np.asarray(token_in, dtype=np.int32).reshape(self.batch))
+            tin = _ptr(t)
+        out = np.zeros(self.batch, dtype=np.int32)
+        self.lib.check(self.lib.swlm_run_step(self.state, C.byref(step), tin, _ptr(out)))
+        return out
+
+    @property
+    def launches_per_step(self) -> int:
+        return int(self.lib.swlm_plan_launch_count(self.plan))
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.swlm_launches(self.state))
+
+    def describe(self) -> str:
+        need = self.lib.swlm_plan_describe(self.plan, None, 0)
+        buf = C.create_string_buffer(need)
+        self.lib.swlm_plan_describe(self.plan, buf, need)
+        return buf.value.decode()
+
+
+def load_model(store: WeightStore, builder, weights) -> InferenceModel:
+    """Upload `weights` (name -> arrays, see synth.synth_model_weights) and compile the decode plan."""
+    for name, kind, _shape, shard in builder.tensors():
+        entry = weights[name]
+        if kind == "q4":
+            store.add_q4_mlx(name, entry[0], entry[1], entry[2], shard)
+        else:
+            store.add_dense(name, entry, shard if kind == "conv" else 0)
+    return InferenceModel(store, builder.decode_steps(), builder.config.buffers_desc())

@@ -1,0 +1,41 @@
+"""Seeded synthetic tensors with the shapes and value distributions of the benchmark configurations.
+
+Linear weights: nibbles uniform 0..15 packed 8 per uint32 along K, per-group bf16 scale ~ U(0.005, 0.02)
+and bf16 bias ~ N(0, 0.01). Embeddings bf16 ~ N(0, 0.02); norm weights bf16 ~ 1 + N(0, 0.02);
+conv weights bf16 ~ N(0, 0.02). There are no checkpoints involved: weights are random-init.
+"""
+from __future__ import annotations
+
+import zlib
+from typing import Dict
+
+import numpy as np
+
+from .formats import f32_to_bf16
+
+
+def synth_q4(n: int, k: int, seed: int):
+    """(weight u32 [n, k/8], scales bf16 [n, k/64], biases bf16 [n, k/64]) as uint arrays."""
+    rng = np.random.default_rng(seed)
+    w = rng.integers(0, 1 << 32, size=(n, k // 8), dtype=np.uint32)  # every nibble uniform on 0..15
+    scales = f32_to_bf16(rng.uniform(0.005, 0.02, size=(n, k // 64)).astype(np.float32))
+    biases = f32_to_bf16(rng.normal(0.0, 0.01, size=(n, k // 64)).astype(np.float32))
+    return w, scales, biases
+
+
+def _seed(base: int, name: str) -> int:
+    return (base * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFF
+
+
+def synth_model_weights(builder, seed: int = 3) -> Dict[str, object]:
+    """name -> (w, scales, biases) for quantized tensors, bf16 uint16 array for dense ones."""
+    out: Dict[str, object] = {}
+    for name, kind, shape, _shard in builder.tensors():
+        rng = np.random.default_rng(_seed(seed, name))
+        if kind == "q4":
+            out[name] = synth_q4(shape[0], shape[1], _seed(seed, name))
+        elif kind == "norm":
+            out[name] = f32_to_bf16((1.0 + rng.normal(0.0, 0.02, size=shape)).astype(np.float32))
+        else:  # embedding table, conv weights
+            out[name] = f32_to_bf16(rng.normal(0.0, 0.02, size=shape).astype(np.float32))
+    return out

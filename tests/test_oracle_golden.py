@@ -1,0 +1,138 @@
+"""Pins the CPU oracle on the known-answer vectors of the reference's own kernel tests (tests/golden)."""
+import base64
+
+import numpy as np
+import pytest
+
+from swlm_helpers import pattern_bf16
+
+
+def _pack(pkg, q_rows):
+    return pkg.pack_mlx_q4(np.array(q_rows, dtype=np.uint8))
+
+
+def _bf(pkg, a):
+    return pkg.f32_to_bf16(np.array(a, dtype=np.float32))
+
+
+def test_gemv_single_block(pkg, oracle, golden):
+    g = golden["gemv_single_block"]
+    w = _pack(pkg, [g["q"]])
+    s, z = _bf(pkg, [[g["scale"]]]), _bf(pkg, [[g["zero"]]])
+    # the reference test feeds fp16 activations; these values are exact in bf16 as well
+    x = np.array(g["x"], dtype=np.float32)
+    assert np.array_equal(pkg.bf16_to_f32(pkg.f32_to_bf16(x)), x)
+    blocks = oracle.staf_repack(w, s, z)
+    y = oracle.staf_gemv_f32(blocks, 1, 64, x)
+    tol = max(g["abs_tol"], g["rel_tol"] * abs(g["expected"]))
+    assert abs(float(y[0]) - g["expected"]) < tol
+    assert float(y[0]) == pytest.approx(g["expected"], abs=1e-6)  # same fp32 loop, same order
+    y_bf16, y64 = oracle.qgemm(pkg.f32_to_bf16(x)[None, :], w, s, z, want_f64=True)
+    assert abs(float(pkg.bf16_to_f32(y_bf16)[0, 0]) - g["expected"]) < tol
+    assert abs(y64[0, 0] - g["expected"]) < 1e-5
+
+
+def test_gemv_multi_row_and_staf_end_to_end(pkg, oracle, golden):
+    g = golden["gemv_multi_row"]
+    w = _pack(pkg, g["q"])
+    s, z = _bf(pkg, g["scales"]), _bf(pkg, g["zeros"])
+    # scale/zero patterns are exact in bf16 and fp16, so MLX -> STAF narrowing loses nothing here
+    assert np.array_equal(pkg.bf16_to_f32(s), np.array(g["scales"], dtype=np.float32))
+    x = np.array(g["x"], dtype=np.float32)
+    k = 64 * g["blocks"]
+    blocks = oracle.staf_repack(w, s, z)
+    y = oracle.staf_gemv_f32(blocks, g["rows"], k, x)
+    for r in range(g["rows"]):
+        tol = max(g["abs_tol"], g["rel_tol"] * abs(g["expected"][r]))
+        assert abs(float(y[r]) - g["expected"][r]) < tol
+        assert float(y[r]) == pytest.approx(g["expected"][r], abs=2e-6)
+    # the MLX-format path and the STAF-block path dequantise to the same weights
+    assert np.array_equal(oracle.dequant_mlx(w, s, z), oracle.dequant_staf(blocks, g["rows"], k))
+
+
+def test_dequant_block_bits(pkg, oracle, golden):
+    g = golden["dequant_block"]
+    w = _pack(pkg, [g["q"]])
+    out = oracle.dequant_bf16(w, _bf(pkg, [[g["scale"]]]), _bf(pkg, [[g["zero"]]]))
+    assert out[0].tolist() == g["expected_bf16_bits"]
+
+
+@pytest.mark.parametrize("case", ["staf_roundtrip_single", "staf_roundtrip_multi"])
+def test_staf_repack_is_byte_exact(pkg, oracle, golden, case):
+    g = golden[case]
+    w = _pack(pkg, g["q"])
+    s, z = _bf(pkg, g["scales"]), _bf(pkg, g["zeros"])
+    expected = np.array(g["expected_blocks"], dtype=np.uint8).reshape(g["rows"], g["blocks"], 36)
+    assert np.array_equal(oracle.staf_repack(w, s, z), expected)
+    assert np.array_equal(pkg.formats.repack_mlx_to_staf(w, s, z), expected)  # host-side NumPy converter
+
+
+@pytest.mark.parametrize("case", ["attention_pattern", "attention_pattern_hd128"])
+def test_attention_decode_trace(pkg, oracle, golden, case):
+    """Repeated decode over the reference's equivalence-test inputs against an fp64 softmax attention,
+    and the K/V cache bytes against the inputs themselves."""
+    g = golden[case]
+    H, KV, D, T = g["heads"], g["kv_heads"], g["head_dim"], g["seq_len"]
+    q = pattern_bf16(T * H * D, *g["q_pattern"]).reshape(T, H * D)
+    k = pattern_bf16(T * KV * D, *g["k_pattern"]).reshape(T, KV * D)
+    v = pattern_bf16(T * KV * D, *g["v_pattern"]).reshape(T, KV * D)
+    expected = np.frombuffer(base64.b64decode(g["expected_f32_b64"]), dtype="<f4").reshape(T, H * D)
+    desc = pkg.BuffersDesc(hidden=H * D, slot_dim=H * D, vocab=8, max_seq=g["max_seq"], max_batch=1, kv_layers=1,
+                           kv_heads=KV, head_dim=D, conv_layers=0, conv_dim=0, conv_kernel=0)
+    m = oracle.model(desc)
+    step = pkg.plan._step(pkg.plan.STEP_ATTN_DECODE, layer=0, in_buf=3, in2_buf=4, in3_buf=5, out_buf=2, heads=H,
+                          kv_heads=KV, head_dim=D, rope_dim=0, rope_base=0.0, scale=1.0 / np.sqrt(D))
+    for t in range(T):
+        m.set_position(t)
+        m.write_buffer(3, pkg.f32_to_bf16(q[t]))
+        m.write_buffer(4, pkg.f32_to_bf16(k[t]))
+        m.write_buffer(5, pkg.f32_to_bf16(v[t]))
+        m.run_step(step)
+        out = pkg.bf16_to_f32(m.read_buffer(2, H * D))[0]
+        assert np.max(np.abs(out - expected[t])) < g["tol"] * max(1.0, np.max(np.abs(expected[t])))
+    for h in range(KV):
+        kc = pkg.bf16_to_f32(m.read_kv(0, 0, 0, h, T))
+        vc = pkg.bf16_to_f32(m.read_kv(1, 0, 0, h, T))
+        assert np.array_equal(kc, k.reshape(T, KV, D)[:, h])
+        assert np.array_equal(vc, v.reshape(T, KV, D)[:, h])
+
+
+def test_conv_decode_trace_matches_sequence_formula_bit_for_bit(pkg, oracle, golden):
+    g = golden["conv_pattern"]
+    D, K, T = g["dim"], g["kernel"], g["seq_len"]
+    x = np.array(g["x"], dtype=np.float32).reshape(T, 3 * D)
+    assert np.array_equal(pkg.bf16_to_f32(pkg.f32_to_bf16(x)), x)  # exact in bf16
+    desc = pkg.BuffersDesc(hidden=D, slot_dim=3 * D, vocab=8, max_seq=8, max_batch=1, kv_layers=0, kv_heads=0,
+                           head_dim=0, conv_layers=1, conv_dim=D, conv_kernel=K)
+    m = oracle.model(desc)
+    m.add_dense("conv.weight", np.array(g["w_bf16_bits"], dtype=np.uint16))
+    step = pkg.plan._step(pkg.plan.STEP_CONV_STATE_UPDATE, layer=0, in_buf=3, out_buf=2, n=D, conv_kernel=K, weight="conv.weight")
+    out_bits = []
+    for t in range(T):
+        m.write_buffer(3, pkg.f32_to_bf16(x[t]))
+        m.run_step(step)
+        out_bits += m.read_buffer(2, D)[0].tolist()
+    assert out_bits == g["expected_out_bf16_bits"]
+    assert m.read_conv(0, 0).tolist() == g["expected_state_bf16_bits"]
+
+
+def test_bf16_rounding_rule(pkg, oracle):
+    rng = np.random.default_rng(0)
+    x = rng.normal(size=4096).astype(np.float32)
+    x[:4] = [1.00390625, 1.01171875, -1.00390625, 3.0e-40]  # ties to even, and a subnormal
+    ours = pkg.f32_to_bf16(x)
+    for v, b in zip(x[:64], ours[:64]):
+        assert oracle.dll.orc_f32_to_bf16(__import__("ctypes").c_float(float(v))) == int(b)
+    assert pkg.bf16_to_f32(ours[:2]).tolist() == [1.0, 1.015625]
+
+
+def test_rope_matches_closed_form(pkg, oracle):
+    hd, pos, base = 128, 777, 500000.0
+    rng = np.random.default_rng(1)
+    v = pkg.bf16_to_f32(pkg.f32_to_bf16(rng.normal(size=hd).astype(np.float32)))
+    got = pkg.bf16_to_f32(oracle.rope_bf16(pkg.f32_to_bf16(v), 1, hd, hd, base, pos))
+    i = np.arange(hd // 2)
+    theta = pos * base ** (-2.0 * i / hd)
+    want = np.concatenate([v[: hd // 2] * np.cos(theta) - v[hd // 2:] * np.sin(theta),
+                           v[: hd // 2] * np.sin(theta) + v[hd // 2:] * np.cos(theta)])
+    assert np.max(np.abs(got - want)) < 2e-2
