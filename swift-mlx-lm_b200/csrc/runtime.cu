@@ -140,6 +140,28 @@ int add_q4_raw(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* w,
     Slice sl;
     rc = shard_slice(ctx, shard_kind, n, k, &sl);
     if (rc) return rc;
+    // Re-adding a name replaces the tensor and every fused layout built from it; plans compiled against
+    // the old tensor must be rebuilt.
+    auto old = ctx->raw.find(name);
+    if (old != ctx->raw.end()) {
+        SWLM_CUDA(cudaDeviceSynchronize());
+        cudaFree(old->second.w); cudaFree(old->second.scales); cudaFree(old->second.biases);
+        ctx->raw.erase(old);
+        const std::string needle = name;
+        for (auto it = ctx->tiled.begin(); it != ctx->tiled.end();) {
+            bool uses = false;
+            size_t start = 0;
+            const std::string& key = it->first;
+            while (start <= key.size()) {
+                size_t end = key.find_first_of("|^", start);
+                if (end == std::string::npos) end = key.size();
+                uses |= key.compare(start, end - start, needle) == 0;
+                start = end + 1;
+            }
+            if (uses) { cudaFree(it->second.tiles); cudaFree(it->second.sb); it = ctx->tiled.erase(it); }
+            else ++it;
+        }
+    }
     Q4Raw r;
     r.n = sl.rows; r.k = sl.cols; r.sb_f16 = f16; r.shard_kind = shard_kind;
     const int wpr = k / 8, gpr = k / 64, lw = sl.cols / 8, lg = sl.cols / 64;
@@ -612,6 +634,12 @@ int swlm_weights_add_dense_bf16(swlm_ctx* ctx, const char* name, int64_t rows, i
     Slice sl;
     rc = shard_slice(ctx, shard_kind == SWLM_SHARD_ROW ? SWLM_SHARD_REPLICATE : shard_kind, (int)rows, (int)cols, &sl);
     if (rc) return rc;
+    auto old = ctx->dense.find(name);
+    if (old != ctx->dense.end()) {
+        SWLM_CUDA(cudaDeviceSynchronize());
+        cudaFree(old->second.data);
+        ctx->dense.erase(old);
+    }
     DenseTensor t;
     t.rows = sl.rows; t.cols = cols; t.shard_kind = shard_kind;
     if ((rc = dev_alloc(&t.data, (size_t)t.rows * cols, ctx))) return rc;

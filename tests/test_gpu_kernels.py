@@ -1,0 +1,324 @@
+"""Kernel-level parity on a B200: every CUDA kernel of the path against the CPU oracle, through the C ABI.
+
+Tolerance for floating-point results: relative error <= 1e-2 per bf16 output (helper `rel_err`, denominator
+floored at 2 % of the vector's largest magnitude). Integer / byte results (re-tiling, cache bytes, conv state,
+argmax indices) are compared exactly.
+"""
+import base64
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from swlm_helpers import pattern_bf16, rel_err
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def store(pkg):
+    s = pkg.WeightStore(0)
+    yield s
+    s.close()
+
+
+def _bf(pkg, a):
+    return pkg.f32_to_bf16(np.asarray(a, dtype=np.float32))
+
+
+# ---- qGEMV / small-M qGEMM --------------------------------------------------------------------------------
+
+def test_qgemv_reference_known_answers(pkg, store, golden):
+    g = golden["gemv_single_block"]
+    w = pkg.pack_mlx_q4(np.array([g["q"]], dtype=np.uint8))
+    store.add_q4_mlx("kat.single", w, _bf(pkg, [[g["scale"]]]), _bf(pkg, [[g["zero"]]]))
+    y = pkg.bf16_to_f32(store.qgemm("kat.single", _bf(pkg, [g["x"]]), 1))
+    assert abs(float(y[0, 0]) - g["expected"]) < max(g["abs_tol"], g["rel_tol"] * abs(g["expected"]))
+
+    g = golden["gemv_multi_row"]
+    w = pkg.pack_mlx_q4(np.array(g["q"], dtype=np.uint8))
+    s, z = _bf(pkg, g["scales"]), _bf(pkg, g["zeros"])
+    store.add_q4_mlx("kat.multi", w, s, z)
+    # same tensor through the STAF execution-block format (fp16 headers), as the reference's end-to-end test does
+    store.add_q4_staf("kat.multi.staf", pkg.formats.repack_mlx_to_staf(w, s, z), g["rows"], 64 * g["blocks"])
+    for name in ("kat.multi", "kat.multi.staf"):
+        y = pkg.bf16_to_f32(store.qgemm(name, _bf(pkg, [g["x"]]), g["rows"]))[0]
+        for r in range(g["rows"]):
+            assert abs(float(y[r]) - g["expected"][r]) < max(g["abs_tol"], g["rel_tol"] * abs(g["expected"][r]))
+
+
+@pytest.mark.parametrize("n,k,m", [
+    (4096, 4096, 1),      # the op-level benchmark shape
+    (1, 64, 1), (17, 128, 1), (100, 320, 3), (33, 64 * 5, 2),   # ragged: padding rows and k-tiles
+    (1024, 4096, 8), (4096, 14336, 1), (256, 14336, 16),        # batch columns; split-K through scratch
+    (128, 512, 16), (6144, 4096, 4), (2048, 1792, 1),
+])
+def test_qgemm_matches_oracle(pkg, store, oracle, n, k, m):
+    w, s, b = pkg.synth_q4(n, k, seed=n * 31 + k)
+    rng = np.random.default_rng(m * 7 + 1)
+    x = _bf(pkg, rng.normal(size=(m, k)))
+    name = f"t.{n}x{k}"
+    store.add_q4_mlx(name, w, s, b)
+    got = pkg.bf16_to_f32(store.qgemm(name, x, n))
+    oracle.set_threads(0)
+    ref_bf16, ref64 = oracle.qgemm(x, w, s, b, want_f64=True)
+    ref = pkg.bf16_to_f32(ref_bf16)
+    for row in range(m):
+        assert rel_err(got[row], ref[row]).max() <= RTOL
+        # against the fp64 accumulation the kernel must be as close as bf16 rounding allows
+        assert rel_err(got[row], ref64[row]).max() <= RTOL
+
+
+def test_qgemm_more_than_16_rows_runs_in_passes(pkg, store, oracle):
+    n, k, m = 512, 1024, 40
+    w, s, b = pkg.synth_q4(n, k, seed=5)
+    x = _bf(pkg, np.random.default_rng(2).normal(size=(m, k)))
+    store.add_q4_mlx("t.passes", w, s, b)
+    got = pkg.bf16_to_f32(store.qgemm("t.passes", x, n))
+    ref = pkg.bf16_to_f32(oracle.qgemm(x, w, s, b))
+    assert rel_err(got, ref).max() <= RTOL
+
+
+def test_device_layout_dequantises_bit_exactly(pkg, store, oracle):
+    for n, k in [(48, 256), (37, 64 * 7), (512, 4096)]:
+        w, s, b = pkg.synth_q4(n, k, seed=n + k)
+        store.add_q4_mlx(f"dq.{n}", w, s, b)
+        assert np.array_equal(store.dequant_bf16(f"dq.{n}", n, k), oracle.dequant_bf16(w, s, b))
+
+
+def test_dequant_known_answer_bits(pkg, store, golden):
+    g = golden["dequant_block"]
+    w = pkg.pack_mlx_q4(np.array([g["q"]], dtype=np.uint8))
+    store.add_q4_mlx("kat.dq", w, _bf(pkg, [[g["scale"]]]), _bf(pkg, [[g["zero"]]]))
+    assert store.dequant_bf16("kat.dq", 1, 64)[0].tolist() == g["expected_bf16_bits"]
+
+
+def test_one_hot_probes_at_full_size(pkg, store, oracle):
+    """Size-independent property at the full 14336 x 4096 shape: a one-hot activation returns the
+    dequantised column, so every probed weight is checked without a CPU GEMV."""
+    n, k = 14336, 4096
+    w, s, b = pkg.synth_q4(n, k, seed=99)
+    store.add_q4_mlx("probe", w, s, b)
+    cols = [0, 63, 64, 1000, 4095]
+    x = np.zeros((len(cols), k), dtype=np.float32)
+    for i, c in enumerate(cols):
+        x[i, c] = 1.0
+    got = pkg.bf16_to_f32(store.qgemm("probe", _bf(pkg, x), n))
+    deq = oracle.dequant_mlx(w, s, b)
+    for i, c in enumerate(cols):
+        want = pkg.bf16_to_f32(pkg.f32_to_bf16(deq[:, c]))
+        assert np.max(np.abs(got[i] - want) / np.maximum(np.abs(want), 1e-3)) <= 2.0 ** -7  # one bf16 ulp
+
+
+# ---- glue kernels through single plan steps -----------------------------------------------------------------
+
+def _mini(pkg, store, oracle, *, batch=1, hidden=256, slot=1024, vocab=512, max_seq=64, kv_layers=1, kv_heads=2,
+          head_dim=128, conv_layers=0, conv_dim=0, conv_kernel=0):
+    desc = pkg.BuffersDesc(hidden=hidden, slot_dim=slot, vocab=vocab, max_seq=max_seq, max_batch=batch,
+                           kv_layers=kv_layers, kv_heads=kv_heads, head_dim=head_dim, conv_layers=conv_layers,
+                           conv_dim=conv_dim, conv_kernel=conv_kernel)
+    table = _bf(pkg, np.random.default_rng(0).normal(0, 0.02, size=(vocab, hidden)))
+    if not getattr(store, "_mini_table", None) == (vocab, hidden):
+        store.add_dense("mini.embed", table)
+        store._mini_table = (vocab, hidden)
+    step = pkg.plan._step(pkg.plan.STEP_EMBED, out_buf=0, n=hidden, weight="mini.embed")
+    gm = pkg.InferenceModel(store, [step], desc)
+    om = oracle.model(desc)
+    om.add_dense("mini.embed", table)
+    return gm, om
+
+
+@pytest.mark.parametrize("kind_name", ["STEP_COPY_RMSNORM", "STEP_RESADD_COPY_RMSNORM", "STEP_RESADD_RMSNORM"])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_rmsnorm_family(pkg, store, oracle, kind_name, batch):
+    P = pkg.plan
+    hidden = 4096
+    gm, om = _mini(pkg, store, oracle, batch=batch, hidden=hidden, slot=4096)
+    rng = np.random.default_rng(3)
+    wn = _bf(pkg, 1.0 + rng.normal(0, 0.02, size=hidden))
+    store.add_dense("n.w", wn)
+    om.add_dense("n.w", wn)
+    h = _bf(pkg, rng.normal(size=(batch, hidden)))
+    r = _bf(pkg, rng.normal(size=(batch, hidden)))
+    for mdl in (gm, om):
+        mdl.write_buffer(P.BUF_HIDDEN, h)
+        mdl.write_buffer(P.BUF_RESIDUAL, r)
+    step = P._step(getattr(P, kind_name), in_buf=P.BUF_HIDDEN, out_buf=P.BUF_S0, n=hidden, eps=1e-5, weight_bias=0.0, weight="n.w")
+    gm.run_step(step)
+    om.run_step(step)
+    got, ref = pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, hidden)), pkg.bf16_to_f32(om.read_buffer(P.BUF_S0, hidden))
+    assert rel_err(got, ref).max() <= RTOL
+    # the residual stream is a sum of two bf16 values rounded once: exact
+    assert np.array_equal(gm.read_buffer(P.BUF_RESIDUAL, hidden), om.read_buffer(P.BUF_RESIDUAL, hidden))
+    gm.close()
+
+
+def test_qk_norm_swiglu_embed_argmax(pkg, store, oracle):
+    P = pkg.plan
+    batch, heads, kvh, hd = 2, 8, 2, 64
+    gm, om = _mini(pkg, store, oracle, batch=batch, hidden=256, slot=1024, vocab=512, head_dim=hd)
+    rng = np.random.default_rng(4)
+    wq, wk = _bf(pkg, 1 + rng.normal(0, 0.1, size=hd)), _bf(pkg, 1 + rng.normal(0, 0.1, size=hd))
+    for mdl in (store, om):
+        mdl.add_dense("qn", wq)
+        mdl.add_dense("kn", wk)
+    q, k = _bf(pkg, rng.normal(size=(batch, heads * hd))), _bf(pkg, rng.normal(size=(batch, kvh * hd)))
+    step = P._step(P.STEP_QK_NORM, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, heads=heads, kv_heads=kvh, head_dim=hd, eps=1e-5,
+                   weight_bias=0.0, weight="qn", weight2="kn")
+    for mdl in (gm, om):
+        mdl.write_buffer(P.BUF_S1, q)
+        mdl.write_buffer(P.BUF_S2, k)
+        mdl.run_step(step)
+    for buf, cnt in ((P.BUF_S1, heads * hd), (P.BUF_S2, kvh * hd)):
+        assert rel_err(pkg.bf16_to_f32(gm.read_buffer(buf, cnt)), pkg.bf16_to_f32(om.read_buffer(buf, cnt))).max() <= RTOL
+
+    g, u = _bf(pkg, rng.normal(size=(batch, 1000)) * 3), _bf(pkg, rng.normal(size=(batch, 1000)))
+    step = P._step(P.STEP_SWIGLU, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, out_buf=P.BUF_S0, n=1000)
+    for mdl in (gm, om):
+        mdl.write_buffer(P.BUF_S1, g)
+        mdl.write_buffer(P.BUF_S2, u)
+        mdl.run_step(step)
+    assert rel_err(pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, 1000)), pkg.bf16_to_f32(om.read_buffer(P.BUF_S0, 1000))).max() <= RTOL
+
+    step = P._step(P.STEP_EMBED, out_buf=P.BUF_HIDDEN, n=256, weight="mini.embed")
+    toks = np.array([511, 7], dtype=np.int32)
+    gm.run_step(step, toks)
+    om.run_step(step, toks)
+    assert np.array_equal(gm.read_buffer(P.BUF_HIDDEN, 256), om.read_buffer(P.BUF_HIDDEN, 256))
+
+    # argmax: ties resolve to the lowest index; -inf rows and a maximum in the last element
+    logits = rng.normal(size=(batch, 512)).astype(np.float32)
+    logits[0, [100, 37, 400]] = 9.0
+    logits[1, 511] = 50.0
+    step = P._step(P.STEP_ARGMAX, in_buf=P.BUF_LOGITS, n=512)
+    for mdl in (gm, om):
+        mdl.write_buffer(P.BUF_LOGITS, _bf(pkg, logits))
+    assert gm.run_step(step).tolist() == om.run_step(step).tolist() == [37, 511]
+    assert gm.position == 0  # single-step runs leave the position alone
+    gm.close()
+
+
+def test_argmax_full_vocab(pkg, store, oracle):
+    P = pkg.plan
+    vocab = 128256
+    gm, om = _mini(pkg, store, oracle, batch=2, hidden=256, slot=1024, vocab=vocab)
+    rng = np.random.default_rng(5)
+    logits = _bf(pkg, rng.normal(size=(2, vocab)))  # bf16 rounding creates plenty of exact ties
+    step = P._step(P.STEP_ARGMAX, in_buf=P.BUF_LOGITS, n=vocab)
+    for mdl in (gm, om):
+        mdl.write_buffer(P.BUF_LOGITS, logits)
+    assert gm.run_step(step).tolist() == om.run_step(step).tolist()
+    gm.close()
+
+
+def test_conv_state_update_known_answer_bits(pkg, store, oracle, golden):
+    g = golden["conv_pattern"]
+    D, K, T = g["dim"], g["kernel"], g["seq_len"]
+    P = pkg.plan
+    gm, _ = _mini(pkg, store, oracle, hidden=256, slot=1024, conv_layers=1, conv_dim=D, conv_kernel=K)
+    store.add_dense("kat.conv", np.array(g["w_bf16_bits"], dtype=np.uint16).reshape(D, K))
+    step = P._step(P.STEP_CONV_STATE_UPDATE, layer=0, in_buf=P.BUF_S1, out_buf=P.BUF_S0, n=D, conv_kernel=K, weight="kat.conv")
+    x = np.array(g["x"], dtype=np.float32).reshape(T, 3 * D)
+    out_bits = []
+    for t in range(T):
+        row = np.zeros((1, 1024), dtype=np.float32)
+        row[0, : 3 * D] = x[t]
+        gm.write_buffer(P.BUF_S1, _bf(pkg, row))
+        gm.run_step(step)
+        out_bits += gm.read_buffer(P.BUF_S0, D)[0].tolist()
+    assert out_bits == g["expected_out_bf16_bits"]
+    assert gm.read_conv(0, 0).tolist() == g["expected_state_bf16_bits"]
+    gm.close()
+
+
+# ---- attention --------------------------------------------------------------------------------------------
+
+def test_attention_reference_pattern(pkg, store, oracle, golden):
+    g = golden["attention_pattern_hd128"]
+    H, KV, D, T = g["heads"], g["kv_heads"], g["head_dim"], g["seq_len"]
+    P = pkg.plan
+    q = pattern_bf16(T * H * D, *g["q_pattern"]).reshape(T, H * D)
+    k = pattern_bf16(T * KV * D, *g["k_pattern"]).reshape(T, KV * D)
+    v = pattern_bf16(T * KV * D, *g["v_pattern"]).reshape(T, KV * D)
+    expected = np.frombuffer(base64.b64decode(g["expected_f32_b64"]), dtype="<f4").reshape(T, H * D)
+    gm, _ = _mini(pkg, store, oracle, hidden=256, slot=H * D, max_seq=g["max_seq"], kv_heads=KV, head_dim=D)
+    step = P._step(P.STEP_ATTN_DECODE, layer=0, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, in3_buf=P.BUF_S3, out_buf=P.BUF_S0,
+                   heads=H, kv_heads=KV, head_dim=D, rope_dim=0, rope_base=0.0, scale=1.0 / np.sqrt(D))
+    pad = lambda a: np.pad(a, (0, H * D - a.size))[None, :]
+    for t in range(T):
+        gm.set_position(t)
+        gm.write_buffer(P.BUF_S1, _bf(pkg, pad(q[t])))
+        gm.write_buffer(P.BUF_S2, _bf(pkg, pad(k[t])))
+        gm.write_buffer(P.BUF_S3, _bf(pkg, pad(v[t])))
+        gm.run_step(step)
+        out = pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, H * D))[0]
+        assert np.max(np.abs(out - expected[t])) < g["tol"] * max(1.0, np.max(np.abs(expected[t])))
+    # cache bytes equal the (bf16-exact) inputs, as the reference asserts between its two fill paths
+    for h in range(KV):
+        assert np.array_equal(pkg.bf16_to_f32(gm.read_kv(0, 0, 0, h, T)), k.reshape(T, KV, D)[:, h])
+        assert np.array_equal(pkg.bf16_to_f32(gm.read_kv(1, 0, 0, h, T)), v.reshape(T, KV, D)[:, h])
+    gm.close()
+
+
+@pytest.mark.parametrize("hd,heads,kvh", [(128, 32, 8), (64, 32, 8), (128, 8, 8)])
+@pytest.mark.parametrize("batch,ctx", [(1, 0), (1, 1), (1, 63), (1, 64), (1, 65), (1, 1000), (1, 4095), (3, 300)])
+def test_attention_decode_matches_oracle(pkg, store, oracle, hd, heads, kvh, batch, ctx):
+    """RoPE(q, k_new), KV append, attention over [0, ctx] with the cache pre-filled with random bf16 rows."""
+    P = pkg.plan
+    max_seq = 4096
+    gm, om = _mini(pkg, store, oracle, batch=batch, hidden=256, slot=heads * hd, max_seq=max_seq, kv_heads=kvh, head_dim=hd)
+    rng = np.random.default_rng(ctx * 13 + hd + batch)
+    if ctx:
+        for b in range(batch):
+            for h in range(kvh):
+                kr, vr = _bf(pkg, rng.normal(size=(ctx, hd))), _bf(pkg, rng.normal(size=(ctx, hd)))
+                for mdl in (gm, om):
+                    mdl.write_kv(0, 0, b, h, kr)
+                    mdl.write_kv(1, 0, b, h, vr)
+    q = _bf(pkg, rng.normal(size=(batch, heads * hd)))
+    k = _bf(pkg, np.pad(rng.normal(size=(batch, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+    v = _bf(pkg, np.pad(rng.normal(size=(batch, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+    step = P._step(P.STEP_ATTN_DECODE, layer=0, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, in3_buf=P.BUF_S3, out_buf=P.BUF_S0,
+                   heads=heads, kv_heads=kvh, head_dim=hd, rope_dim=hd, rope_base=500000.0, scale=1.0 / np.sqrt(hd))
+    for mdl in (gm, om):
+        mdl.set_position(ctx)
+        mdl.write_buffer(P.BUF_S1, q)
+        mdl.write_buffer(P.BUF_S2, k)
+        mdl.write_buffer(P.BUF_S3, v)
+        mdl.run_step(step)
+    got = pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, heads * hd))
+    ref = pkg.bf16_to_f32(om.read_buffer(P.BUF_S0, heads * hd))
+    assert rel_err(got, ref).max() <= RTOL
+    # the appended K row (RoPE in fp32, rounded once) and V row
+    for b in range(batch):
+        for h in range(kvh):
+            gk, ok = gm.read_kv(0, 0, b, h, ctx + 1)[ctx], om.read_kv(0, 0, b, h, ctx + 1)[ctx]
+            assert rel_err(pkg.bf16_to_f32(gk), pkg.bf16_to_f32(ok)).max() <= RTOL
+            assert np.array_equal(gm.read_kv(1, 0, b, h, ctx + 1)[ctx], om.read_kv(1, 0, b, h, ctx + 1)[ctx])
+    gm.close()
+
+
+def test_flash_decode_op_long_context(pkg, store):
+    """Config-2 shape through the device-pointer entry point, against a PyTorch fp32 reference of the same op."""
+    import torch
+
+    lib = store.lib
+    B, H, KV, D, ctx = 4, 32, 8, 128, 8192
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.randn(B, H, D, device="cuda", generator=gen).bfloat16()
+    k = torch.randn(B, KV, ctx, D, device="cuda", generator=gen).bfloat16()
+    v = torch.randn(B, KV, ctx, D, device="cuda", generator=gen).bfloat16()
+    out = torch.empty(B, H, D, device="cuda", dtype=torch.bfloat16)
+    scratch = torch.empty(lib.swlm_op_flash_decode_scratch_bytes(B, H, KV, D, ctx), device="cuda", dtype=torch.uint8)
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream().cuda_stream
+    lib.check(lib.swlm_op_flash_decode_dev(store.handle, B, H, KV, D, ctx, ctx, 1.0 / np.sqrt(D), q.data_ptr(), k.data_ptr(),
+                                           v.data_ptr(), out.data_ptr(), scratch.data_ptr(), C.c_void_p(stream)))
+    torch.cuda.synchronize()
+    qf = q.float().view(B, KV, H // KV, D)
+    s = torch.einsum("bgrd,bgtd->bgrt", qf, k.float()) / np.sqrt(D)
+    ref = torch.einsum("bgrt,bgtd->bgrd", torch.softmax(s, dim=-1), v.float()).reshape(B, H, D)
+    err = rel_err(out.float().cpu().numpy().reshape(B * H, D), ref.cpu().numpy().reshape(B * H, D))
+    assert err.max() <= RTOL

@@ -1,0 +1,124 @@
+"""CPU-only checks: format helpers, sizing contracts, plan builder shape, and that the C-ABI library loads
+and exports every symbol include/swlm.h declares (no compute calls without a GPU)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_pack_unpack_roundtrip(pkg):
+    rng = np.random.default_rng(0)
+    q = rng.integers(0, 16, size=(5, 192), dtype=np.uint8)
+    w = pkg.pack_mlx_q4(q)
+    assert w.shape == (5, 24) and w.dtype == np.uint32
+    assert np.array_equal(pkg.formats.unpack_mlx_q4(w, 192), q)
+    # element j of a row is nibble j%8 of word j/8, i.e. byte j/2, low nibble for even j
+    raw = w.view(np.uint8).reshape(5, 96)
+    assert np.array_equal(raw & 0xF, q[:, 0::2]) and np.array_equal(raw >> 4, q[:, 1::2])
+
+
+def test_staf_block_geometry(pkg):
+    fmt = pkg.AffineQ4Group64Format
+    # Tests/MetalCompilerTests/Core/SupportedQuantizationsContractTests.swift:95-113 (block geometry)
+    assert (fmt.bits, fmt.group_size, fmt.weights_per_block, fmt.bytes_per_block) == (4, 64, 64, 36)
+    assert fmt.bytes_per_block == 4 + fmt.weights_per_block * fmt.bits // 8
+    assert fmt.bytes_per_weight() == 0.5625
+
+
+def test_kv_cache_sizing_contract(pkg):
+    # Tests/MetalCompilerTests/Core/KVCacheSizingContractTests.swift:32-53, 129-185
+    spec = pkg.KVCacheSpecification(layer_count=32, kv_head_count=8, head_dimension=128, maximum_sequence_length=4224)
+    assert spec.bytes_per_head_slot() == 256
+    assert spec.bytes_per_token_slot() == 8 * 256
+    assert spec.bytes_per_layer() % spec.bytes_per_head_slot() == 0
+    assert spec.total_bytes() == 553_648_128
+    small = pkg.KVCacheSpecification(layer_count=6, kv_head_count=8, head_dimension=64, maximum_sequence_length=16)
+    assert small.bytes_per_head_slot() == 256  # 128 bytes of data aligned up to the 256-byte dense slot
+    assert small.sequence_major_offset(1, 2, 3) == 1 * 8 * 16 * 256 + 2 * 16 * 256 + 3 * 256
+
+
+def test_llama_plan_shape(pkg):
+    cfg = pkg.llama3_8b_config()
+    b = pkg.DispatchPlanBuilder(cfg)
+    steps = b.decode_steps()
+    kinds = [s.kind for s in steps]
+    P = pkg.plan
+    # embed + 32 x (norm, q, k, v, attn, o, norm, gate, up, swiglu, down) + final norm + lm_head + argmax
+    assert len(steps) == 1 + 32 * 11 + 3
+    assert kinds[0] == P.STEP_EMBED and kinds[1] == P.STEP_COPY_RMSNORM
+    assert kinds.count(P.STEP_QGEMV) == 32 * 7 + 1
+    assert kinds.count(P.STEP_RESADD_COPY_RMSNORM) == 63 and kinds[-3:] == [P.STEP_RESADD_RMSNORM, P.STEP_QGEMV, P.STEP_ARGMAX]
+    assert cfg.slot_dim == 16384
+    assert cfg.q4_weight_elems() == 7_504_658_432
+    assert int(cfg.q4_weight_elems() * 0.5625) == 4_221_370_368
+    # the step count does not depend on the token count (Tests/MetalCompilerTests/Core/PrefillTests.swift:49-71)
+    assert len(pkg.DispatchPlanBuilder(pkg.llama3_8b_config(max_seq=128)).decode_steps()) == len(steps)
+    names = {t[0] for t in b.tensors()}
+    for s in steps:
+        if s.weight:
+            assert s.weight.decode() in names
+
+
+def test_lfm2_plan_shape(pkg):
+    cfg = pkg.lfm2_like_config()
+    b = pkg.DispatchPlanBuilder(cfg)
+    steps = b.decode_steps()
+    P = pkg.plan
+    kinds = [s.kind for s in steps]
+    assert cfg.kv_layer_count == 6 and cfg.conv_layer_count == 10
+    assert kinds.count(P.STEP_CONV_STATE_UPDATE) == 10 and kinds.count(P.STEP_ATTN_DECODE) == 6
+    assert kinds.count(P.STEP_QK_NORM) == 6
+    conv_layers = [s.layer for s in steps if s.kind == P.STEP_CONV_STATE_UPDATE]
+    assert conv_layers == list(range(10))
+    assert cfg.q4_weight_elems() == 16 * 50_331_648 + 10 * 16_777_216 + 6 * 10_485_760 + 134_217_728
+
+
+def test_synth_distributions(pkg):
+    w, s, b = pkg.synth_q4(64, 4096, seed=0)
+    q = pkg.formats.unpack_mlx_q4(w, 4096)
+    assert q.min() == 0 and q.max() == 15 and abs(q.mean() - 7.5) < 0.05
+    sf, bf = pkg.bf16_to_f32(s), pkg.bf16_to_f32(b)
+    assert 0.00498 <= sf.min() and sf.max() <= 0.0201
+    assert abs(bf.std() - 0.01) < 0.001
+    w2, _, _ = pkg.synth_q4(64, 4096, seed=0)
+    assert np.array_equal(w, w2)
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "swlm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(swlm_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    syms = _declared_symbols()
+    assert len(syms) >= 35
+    lib = pkg.load_library()  # raises if the .so is missing: there is no fallback
+    for s in syms:
+        assert hasattr(lib.dll, s), f"{s} declared in include/swlm.h but not exported"
+        assert s in pkg.lib.SIGNATURES, f"{s} has no ctypes signature"
+    assert lib.swlm_version().startswith(b"swlm-cuda")
+
+
+def test_no_device_means_error_not_fallback(pkg):
+    lib = pkg.load_library()
+    if lib.swlm_device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    h = ctypes.c_void_p()
+    rc = lib.swlm_ctx_create(0, 0, 1, ctypes.byref(h))
+    assert rc != 0 and not h.value
+    assert b"no CUDA device" in lib.swlm_last_error()
+    with pytest.raises(pkg.SwlmError):
+        pkg.WeightStore(0)
+
+
+def test_bad_arguments_are_rejected(pkg):
+    lib = pkg.load_library()
+    h = ctypes.c_void_p()
+    assert lib.swlm_ctx_create(0, 3, 2, ctypes.byref(h)) == -1  # rank outside the group
+    assert lib.swlm_position(None) == -1
+    assert lib.swlm_plan_launch_count(None) == 0
