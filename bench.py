@@ -1,0 +1,306 @@
+"""Benchmark of the 4-bit decode hot path: Llama-3-8B-shape greedy decode, batch 1, on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--ctx C] [--small]
+
+A step is one greedy decode token (the whole layer stack, output head and argmax) at a context of `--ctx`
+tokens already in the KV cache. `value` is tokens/s with everything resident on the device (CUDA-graph
+replays, device-side token feedback), timed with CUDA events on the launching stream; `e2e` is the same metric
+through the per-token C-ABI call the reference's host would make (swlm_decode: token id in from pinned host
+memory, token id out, one synchronisation per token). Random-init weights of the named shape, seeded.
+
+With --impl reference the CPU oracle (a scalar restatement of the reference's arithmetic; the reference's
+Metal kernels cannot run here) decodes a bounded sample of the same workload on the host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from __graft_entry__ import load_package  # noqa: E402
+
+METRIC = "4-bit decode tok/s, Llama-3-8B shape bs1"
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_config(pkg, args, max_seq):
+    if args.small:  # debugging aid; never the reported workload
+        return pkg.ModelConfig("llama", hidden=1024, intermediate=2816, layers=4, heads=8, kv_heads=2, head_dim=128,
+                               vocab=8192, max_seq=max_seq, max_batch=1)
+    return pkg.llama3_8b_config(max_seq=max_seq, max_batch=1)
+
+
+def workload_name(args):
+    return ("small-debug" if args.small else "Llama-3-8B shape") + f", 4-bit g64 weights, batch 1, greedy decode at context {args.ctx}"
+
+
+def cpu_baseline(pkg, builder, weights, cfg, sample_steps, ctx):
+    """Oracle decode on the host cores over a bounded sample: `sample_steps` tokens at a short context."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_binding
+
+    so = os.path.join(ROOT, "oracle", "liboracle.so")
+    if not os.path.exists(so):
+        subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], check=True)
+    orc = oracle_binding.Oracle(so)
+    orc.set_threads(0)
+    cores = orc.threads()
+    small_cfg = pkg.ModelConfig(cfg.family, cfg.hidden, cfg.intermediate, cfg.layers, cfg.heads, cfg.kv_heads, cfg.head_dim,
+                                cfg.vocab, cfg.norm_eps, cfg.rope_theta, max_seq=sample_steps + 2, max_batch=1)
+    om = orc.model(small_cfg.buffers_desc())
+    om.load(builder, weights)
+    tok = np.array([1], dtype=np.int32)
+    tok = om.decode(tok)  # warm the caches / page in the weights
+    t0 = time.perf_counter()
+    for _ in range(sample_steps):
+        tok = om.decode(tok)
+    dt = time.perf_counter() - t0
+    return {"value": sample_steps / dt, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"{sample_steps} greedy decode steps of the full model at context <= {sample_steps + 1} "
+                      f"(the context-{ctx} KV read is 11% of a step's bytes and is not part of the CPU sample)"}
+
+
+def run_reference(args, pkg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = model_config(pkg, args, 64)
+    builder = pkg.DispatchPlanBuilder(cfg)
+    weights = pkg.synth_model_weights(builder, seed=3)
+    steps = max(1, min(args.steps, 8))
+    base = cpu_baseline(pkg, builder, weights, cfg, steps, args.ctx)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": 1, "ms_per_step": 1000.0 / base["value"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 activations, fp32 accumulate, 4-bit weights",
+            "data": "synthetic (seeded random-init weights of the named shape)",
+            "config": {"workload": workload_name(args), "note": "CPU oracle on host cores; the reference's Metal kernels are unavailable on this box"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="swlm")
+    ap.add_argument("--ctx", type=int, default=4096, help="tokens in the KV cache when the timed region starts")
+    ap.add_argument("--prefill", choices=["real", "synthetic"], default="real",
+                    help="how the KV cache gets its `ctx` tokens: by running the prompt, or random bf16 rows")
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--cpu-sample-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    pkg = load_package()
+
+    if args.impl == "reference":
+        run_reference(args, pkg)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    warm = max(3, args.warmup)
+    max_seq = args.ctx + 2 * (warm + args.steps) + 64
+    cfg = model_config(pkg, args, max_seq)
+    builder = pkg.DispatchPlanBuilder(cfg)
+    weights = pkg.synth_model_weights(builder, seed=3)
+    store = pkg.WeightStore(local_rank, tp_rank=rank, tp_size=world)
+    if world > 1:
+        from swlm_b200 import tp as tp_mod
+        tp_mod.attach(store, dist)
+    model = pkg.load_model(store, builder, weights)
+    stream = torch.cuda.current_stream()
+    model.set_stream(stream.cuda_stream)
+
+    # ---- context: `ctx` tokens in the KV cache ---------------------------------------------------------------
+    rng = np.random.default_rng(7)
+    if args.prefill == "real":
+        prompt = rng.integers(0, cfg.vocab, size=(1, args.ctx), dtype=np.int32)
+        tok = model.prefill(prompt)
+    else:
+        rows = pkg.f32_to_bf16(rng.normal(size=(args.ctx, cfg.head_dim)).astype(np.float32))
+        kv_local = cfg.kv_heads // world
+        for layer in range(cfg.kv_layer_count):
+            for h in range(kv_local):
+                model.write_kv(0, layer, 0, h, rows)
+                model.write_kv(1, layer, 0, h, rows)
+        model.set_position(args.ctx)
+        tok = np.array([1], dtype=np.int32)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput ---------------------------------------------------------------------------
+    model.decode_n_async(tok, warm)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = model.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    model.decode_n_async(None, args.steps)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = model.launches - launches0
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    tokens = model.read_tokens(args.steps)
+
+    # ---- end to end through the per-token call ----------------------------------------------------------------
+    tok = tokens[-1]
+    for _ in range(3):
+        tok = model.decode(tok)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok = model.decode(tok)   # H2D token id from pinned memory, graph replay, D2H token id, synchronise
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    # ---- roofline of the dominant kernel: every qGEMV launch of a step, back to back ------------------------
+    P = pkg.plan
+    reps = 20
+    model.profile_kind(P.STEP_QGEMV, 3)
+    barrier()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    model.profile_kind(P.STEP_QGEMV, reps)
+    g1.record(stream)
+    barrier()
+    gemv_ms = g0.elapsed_time(g1) / reps
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    model.profile_kind(P.STEP_ATTN_DECODE, 3)
+    barrier()
+    a0.record(stream)
+    model.profile_kind(P.STEP_ATTN_DECODE, reps)
+    a1.record(stream)
+    barrier()
+    attn_ms = a0.elapsed_time(a1) / reps
+
+    weight_bytes = cfg.q4_weight_elems() * 0.5625 / world            # per GPU, per step
+    kv_bytes = cfg.kv_layer_count * (cfg.kv_heads // world) * cfg.head_dim * 2 * 2 * model.position
+    n_gemv = sum(1 for l in model.describe().splitlines() if " qgemv" in l)
+    peak, peak_src = measured_peaks()
+    achieved = weight_bytes / (gemv_ms * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "qgemv_kernel (all %d launches of one decode step, timed back to back)" % n_gemv,
+        "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+        "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+        "bytes_per_launch_avg": weight_bytes / n_gemv, "avg_launch_us": gemv_ms * 1e3 / n_gemv,
+        "traffic": None,
+        "attention": {"kernel": "attn_split_kernel + attn_combine_kernel", "bytes_per_step": kv_bytes,
+                      "achieved": kv_bytes / (attn_ms * 1e-3) / 1e9, "unit": "GB/s"},
+        "whole_step": {"weight_bytes": weight_bytes, "weight_GBs": weight_bytes / (ms / args.steps * 1e-3) / 1e9,
+                       "weight_plus_kv_GBs": (weight_bytes + kv_bytes) / (ms / args.steps * 1e-3) / 1e9,
+                       "frac_of_measured_peak_weights_only": weight_bytes / (ms / args.steps * 1e-3) / 1e9 / peak,
+                       "frac_of_nominal_8TBs_weights_only": weight_bytes / (ms / args.steps * 1e-3) / 1e9 / NOMINAL_HBM_GBS},
+    }
+
+    base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        base = cpu_baseline(pkg, builder, weights, cfg, args.cpu_sample_steps, args.ctx)
+
+    if rank == 0:
+        value = args.steps / (ms * 1e-3)
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 activations, fp32 accumulate, 4-bit weights",
+            "data": "synthetic (seeded random-init weights of the named shape; KV context: %s)" % args.prefill,
+            "config": {"workload": workload_name(args), "parallelism": "tp%d" % world if world > 1 else "single GPU",
+                       "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (weight_bytes / 1e9),
+                       "launches_per_step": model.launches_per_step, "context_at_end": model.position},
+            "e2e": {"value": args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": roofline,
+            "cpu_baseline": base,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -137,6 +137,11 @@ int swlm_set_position(swlm_state* state, int position);
 int swlm_run_step(swlm_state* state, const swlm_step* step, const int32_t* token_in, int32_t* token_out);
 /* Kernel launches issued by this state since creation. */
 int64_t swlm_launches(const swlm_state* state);
+/* Enqueue, `repeats` times, only the launches that one step kind compiled to (SWLM_STEP_QGEMV,
+ * SWLM_STEP_ATTN_DECODE or SWLM_STEP_RESADD_COPY_RMSNORM), in plan order, without advancing the position.
+ * The per-kernel timing hook of the benchmark; counterpart of decodeSyncTimed
+ * (Sources/MetalCompiler/Execution/MetalDecodeExecutor.swift). */
+int swlm_profile_kind(swlm_state* state, int step_kind, int repeats);
 
 /* ---- op-level entry points (host buffers; copies are part of the call) ----------
  * Y[m][n] = bf16(X[m][k] . W^T): gemv_q4_g64 for m = 1

@@ -221,9 +221,17 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
 #pragma unroll
                 for (int u = 0; u < 8; ++u) { oacc[hh][u][0] *= corr; oacc[hh][u][1] *= corr; }
         }
-        // O += P . V ; dimension 64*hh + 8*col + u sits in n-tile (hh, u), column col
-        const unsigned pa0 = pack_bf16(pv[0][0], pv[0][1]);
-        const unsigned pa2 = pack_bf16(pv[1][0], pv[1][1]);
+        // O += P . V ; dimension 64*hh + 8*col + u sits in n-tile (hh, u), column col. P is fed as a bf16
+        // hi + lo pair: a single bf16 P (8 mantissa bits) costs ~2 bf16 ulps of the output at short contexts.
+        float ph[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) ph[nt][e] = __bfloat162float(__float2bfloat16_rn(pv[nt][e]));
+        const unsigned pa0 = pack_bf16(ph[0][0], ph[0][1]);
+        const unsigned pa2 = pack_bf16(ph[1][0], ph[1][1]);
+        const unsigned pl0 = pack_bf16(pv[0][0] - ph[0][0], pv[0][1] - ph[0][1]);
+        const unsigned pl2 = pack_bf16(pv[1][0] - ph[1][0], pv[1][1] - ph[1][1]);
 #pragma unroll
         for (int hh = 0; hh < VH; ++hh) {
             const unsigned aw[4] = {va[hh].x, va[hh].y, va[hh].z, va[hh].w};
@@ -232,8 +240,12 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
             const unsigned dw[4] = {vd[hh].x, vd[hh].y, vd[hh].z, vd[hh].w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                mma_bf16(oacc[hh][2 * w], pa0, 0u, pa2, 0u, __byte_perm(aw[w], bw[w], 0x5410), __byte_perm(cw[w], dw[w], 0x5410));
-                mma_bf16(oacc[hh][2 * w + 1], pa0, 0u, pa2, 0u, __byte_perm(aw[w], bw[w], 0x7632), __byte_perm(cw[w], dw[w], 0x7632));
+                const unsigned b0e = __byte_perm(aw[w], bw[w], 0x5410), b1e = __byte_perm(cw[w], dw[w], 0x5410);
+                const unsigned b0o = __byte_perm(aw[w], bw[w], 0x7632), b1o = __byte_perm(cw[w], dw[w], 0x7632);
+                mma_bf16(oacc[hh][2 * w], pa0, 0u, pa2, 0u, b0e, b1e);
+                mma_bf16(oacc[hh][2 * w], pl0, 0u, pl2, 0u, b0e, b1e);
+                mma_bf16(oacc[hh][2 * w + 1], pa0, 0u, pa2, 0u, b0o, b1o);
+                mma_bf16(oacc[hh][2 * w + 1], pl0, 0u, pl2, 0u, b0o, b1o);
             }
         }
     }

@@ -335,12 +335,27 @@ int launch_t(const QGemvParams& p, const QGemvConfig& c, cudaStream_t s) {
 
 }  // namespace
 
+static int g_max_dyn_smem = 0;
+
+template <typename K>
+static int opt_in_smem(K kernel) {
+    int dev = 0, optin = 0;
+    SWLM_CUDA(cudaGetDevice(&dev));
+    SWLM_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaFuncAttributes fa;
+    SWLM_CUDA(cudaFuncGetAttributes(&fa, kernel));
+    const int dyn = optin - (int)fa.sharedSizeBytes;  // static shared memory counts against the same limit
+    SWLM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    if (g_max_dyn_smem == 0 || dyn < g_max_dyn_smem) g_max_dyn_smem = dyn;
+    return SWLM_OK;
+}
+
 int qgemv_init() {
-    const int max_smem = 227 * 1024;
-    SWLM_CUDA(cudaFuncSetAttribute(qgemv_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    SWLM_CUDA(cudaFuncSetAttribute(qgemv_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    SWLM_CUDA(cudaFuncSetAttribute(qgemv_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    SWLM_CUDA(cudaFuncSetAttribute(qgemv_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    int rc;
+    if ((rc = opt_in_smem(qgemv_kernel<1, 0>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<1, 1>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<2, 0>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<2, 1>))) return rc;
     return SWLM_OK;
 }
 
@@ -359,7 +374,7 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
         return SWLM_ERR_INVALID;
     }
     QGemvConfig c = pick_config(w, a.m);
-    if (c.smem > 227 * 1024) { set_error("qgemv: shared memory %zu exceeds the SM", c.smem); return SWLM_ERR_INVALID; }
+    if (g_max_dyn_smem == 0 || c.smem > (size_t)g_max_dyn_smem) { set_error("qgemv: shared memory %zu exceeds the limit %d", c.smem, g_max_dyn_smem); return SWLM_ERR_INVALID; }
     if (c.sk > 1 && (!a.partial || !a.counters)) { set_error("qgemv: split-K launch without scratch"); return SWLM_ERR_INVALID; }
     QGemvParams p{};
     p.tiles = w.tiles; p.sb = w.sb; p.row_tiles = w.row_tiles; p.kt4_total = w.kt_pad / 4; p.sb_f16 = w.sb_f16 ? 1 : 0;

@@ -377,6 +377,7 @@ struct swlm_state {
     int32_t* prompt = nullptr; size_t prompt_cap = 0;
     int ring_cap = 4096;
     float* attn_scratch = nullptr; float* qgemv_partial = nullptr; unsigned* qgemv_counters = nullptr;
+    size_t attn_scratch_cap = 0, qgemv_partial_cap = 0, qgemv_counters_cap = 0;
     float* argmax_val = nullptr; int32_t* argmax_idx = nullptr;
     int32_t* h_tok = nullptr;  // pinned host staging, 2 * max_batch
     int pos_host = 0;
@@ -397,7 +398,7 @@ int kv_heads_local(const swlm_plan* p) { return std::max(1, p->desc.kv_heads / s
 
 // Enqueue the launches of one decode step. body_only skips the output head (lm_head + argmax) and
 // advances the position with a one-thread kernel instead.
-int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream) {
+int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_kind = -1) {
     const swlm_plan* plan = s->plan;
     const swlm_buffers_desc& d = plan->desc;
     const int m = d.max_batch;
@@ -416,6 +417,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream) {
     for (size_t li = 0; li < head_begin; ++li) {
         const Launch& L = plan->launches[li];
         const swlm_step& st = L.st;
+        if (only_kind >= 0 && L.kind != only_kind) continue;
         switch (L.kind) {
         case L_EMBED:
             rc = launch_embed(m, st.n, s->token_in, d.vocab, L.d1->data, s->buf[st.out_buf], s->width[st.out_buf], stream);
@@ -478,7 +480,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream) {
         }
         if (rc) return rc;
     }
-    if (!advanced) {
+    if (!advanced && only_kind < 0) {
         rc = launch_advance(s->position, nullptr, stream);
         s->launches += 1;
     }
@@ -543,6 +545,40 @@ std::vector<Region> state_regions(swlm_state* s) {
     r.push_back({s->token_in, (size_t)d.max_batch * 4});
     r.push_back({s->token_out, (size_t)d.max_batch * 4});
     return r;
+}
+
+// Scratch of the split kernels: attention partials, split-K partial sums and their arrival counters.
+// Grown (never shrunk) to what a plan needs; the counters must be zero between launches.
+int grow_scratch(swlm_state* s, size_t attn_floats, size_t partial_floats, size_t counters) {
+    int rc;
+    if (attn_floats > s->attn_scratch_cap) {
+        SWLM_CUDA(cudaStreamSynchronize(s->stream));
+        cudaFree(s->attn_scratch); s->attn_scratch = nullptr; s->attn_scratch_cap = 0;
+        if ((rc = dev_alloc(&s->attn_scratch, attn_floats))) return rc;
+        s->attn_scratch_cap = attn_floats;
+    }
+    if (partial_floats > s->qgemv_partial_cap) {
+        SWLM_CUDA(cudaStreamSynchronize(s->stream));
+        cudaFree(s->qgemv_partial); s->qgemv_partial = nullptr; s->qgemv_partial_cap = 0;
+        if ((rc = dev_alloc(&s->qgemv_partial, partial_floats))) return rc;
+        s->qgemv_partial_cap = partial_floats;
+    }
+    if (counters > s->qgemv_counters_cap) {
+        SWLM_CUDA(cudaStreamSynchronize(s->stream));
+        cudaFree(s->qgemv_counters); s->qgemv_counters = nullptr; s->qgemv_counters_cap = 0;
+        if ((rc = dev_alloc(&s->qgemv_counters, counters))) return rc;
+        SWLM_CUDA(cudaMemset(s->qgemv_counters, 0, counters * sizeof(unsigned)));
+        s->qgemv_counters_cap = counters;
+    }
+    return SWLM_OK;
+}
+
+size_t plan_attn_scratch(const swlm_plan* plan) {
+    size_t need = 0;
+    for (const Launch& L : plan->launches)
+        if (L.kind == L_ATTN)
+            need = std::max(need, attn_scratch_floats(plan->desc.max_batch, L.st.heads / plan->ctx->tp_size, L.st.head_dim, plan->attn_splits));
+    return need;
 }
 
 int check_position_room(swlm_state* s, int steps) {
@@ -663,10 +699,7 @@ int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const sw
     plan->steps.assign(steps, steps + n_steps);
     rc = compile_plan(plan);
     if (rc) { swlm_plan_destroy(plan); return rc; }
-    plan->attn_scratch = 0;
-    for (const Launch& L : plan->launches)
-        if (L.kind == L_ATTN)
-            plan->attn_scratch = std::max(plan->attn_scratch, attn_scratch_floats(desc->max_batch, L.st.heads / ctx->tp_size, L.st.head_dim, plan->attn_splits));
+    plan->attn_scratch = plan_attn_scratch(plan);
     *out = plan;
     return SWLM_OK;
 }
@@ -722,17 +755,11 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     if ((rc = dev_alloc(&s->token_in, d.max_batch))) return fail(rc);
     if ((rc = dev_alloc(&s->token_out, d.max_batch))) return fail(rc);
     if ((rc = dev_alloc(&s->ring, (size_t)s->ring_cap * d.max_batch))) return fail(rc);
-    if ((rc = dev_alloc(&s->attn_scratch, plan->attn_scratch))) return fail(rc);
-    if ((rc = dev_alloc(&s->qgemv_partial, plan->qgemv_partial))) return fail(rc);
-    if ((rc = dev_alloc(&s->qgemv_counters, plan->qgemv_counters))) return fail(rc);
+    if ((rc = grow_scratch(s, plan->attn_scratch, plan->qgemv_partial, plan->qgemv_counters))) return fail(rc);
     if ((rc = dev_alloc(&s->argmax_val, argmax_scratch_elems(d.max_batch)))) return fail(rc);
     if ((rc = dev_alloc(&s->argmax_idx, argmax_scratch_elems(d.max_batch)))) return fail(rc);
     e = cudaMallocHost((void**)&s->h_tok, sizeof(int32_t) * 2 * d.max_batch);
     if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMallocHost"));
-    if (s->qgemv_counters) {
-        e = cudaMemset(s->qgemv_counters, 0, plan->qgemv_counters * sizeof(unsigned));
-        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemset"));
-    }
     *out = s;
     rc = swlm_state_reset(s);
     if (rc) { *out = nullptr; return fail(rc); }
@@ -994,7 +1021,9 @@ int swlm_run_step(swlm_state* s, const swlm_step* step, const int32_t* token_in,
     tmp.steps.assign(step, step + 1);
     rc = compile_plan(&tmp);
     if (rc) return rc;
-    tmp.attn_splits = s->plan->attn_splits;
+    // a step the state's own plan does not contain may need more scratch than the state holds
+    rc = grow_scratch(s, plan_attn_scratch(&tmp), tmp.qgemv_partial, tmp.qgemv_counters);
+    if (rc) { for (RopeTable& t : tmp.rope_tables) cudaFree(t.inv_freq); return rc; }
     if (token_in) SWLM_CUDA(cudaMemcpyAsync(s->token_in, token_in, sizeof(int32_t) * m, cudaMemcpyHostToDevice, s->stream));
     swlm_plan* saved = s->plan;
     int saved_pos = s->pos_host;
@@ -1014,6 +1043,20 @@ int swlm_run_step(swlm_state* s, const swlm_step* step, const int32_t* token_in,
 }
 
 int64_t swlm_launches(const swlm_state* s) { return s ? s->launches : 0; }
+
+int swlm_profile_kind(swlm_state* s, int step_kind, int repeats) {
+    if (!s || repeats < 0) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    int kind;
+    switch (step_kind) {
+    case SWLM_STEP_QGEMV: kind = L_QGEMV; break;
+    case SWLM_STEP_ATTN_DECODE: kind = L_ATTN; break;
+    case SWLM_STEP_RESADD_COPY_RMSNORM: kind = L_RMSNORM; break;
+    default: set_error("profile: step kind %d has no per-kind loop", step_kind); return SWLM_ERR_UNSUPPORTED;
+    }
+    int rc = ensure_device(s->plan->ctx);
+    for (int i = 0; i < repeats && !rc; ++i) rc = enqueue_step(s, false, s->stream, kind);
+    return rc;
+}
 
 // ---- op-level ------------------------------------------------------------------------------------------
 

@@ -198,6 +198,9 @@ class InferenceModel:
         self.lib.check(self.lib.swlm_run_step(self.state, C.byref(step), tin, _ptr(out)))
         return out
 
+    def profile_kind(self, step_kind: int, repeats: int) -> None:
+        self.lib.check(self.lib.swlm_profile_kind(self.state, step_kind, repeats))
+
     @property
     def launches_per_step(self) -> int:
         return int(self.lib.swlm_plan_launch_count(self.plan))
