@@ -138,8 +138,96 @@ def run_reference(args, pkg):
     print(json.dumps(line))
 
 
+def run_op(args, pkg):
+    """Op-level lines: `--op qgemv` (one quantized GEMV/GEMM shape, rotating through enough distinct weight sets
+    to exceed L2) and `--op flash` (flash-decode over a synthetic KV cache). One JSON line each."""
+    import ctypes as C
+
+    import torch
+
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    store = pkg.WeightStore(0)
+    lib = store.lib
+    peak, peak_src = measured_peaks()
+    sptr = C.c_void_p(stream.cuda_stream)
+    if args.op == "qgemv":
+        n, k, m = args.n, args.k, args.m
+        per_set = n * k * 0.5625
+        sets = max(2, int(np.ceil(max(args.min_mb, 1) * 1e6 / per_set)))
+        for i in range(sets):
+            store.add_q4_mlx(f"w{i}", *pkg.synth_q4(n, k, seed=i))
+        x = torch.randn(m, k, device="cuda").bfloat16()
+        y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+
+        def one_round():
+            for i in range(sets):
+                lib.check(lib.swlm_op_qgemm_dev(store.handle, f"w{i}".encode(), m, x.data_ptr(), y.data_ptr(), sptr))
+
+        for _ in range(max(3, args.warmup)):
+            one_round()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            one_round()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (args.steps * sets)
+        bytes_per_launch = per_set + 2 * m * k + 2 * m * n
+        gbs = bytes_per_launch / (us * 1e-6) / 1e9
+        print(json.dumps({"metric": "qGEMV HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                          "config": {"workload": f"q4g64 GEMV N={n} K={k} M={m}, {sets} distinct weight sets in rotation ({sets * per_set / 1e6:.0f} MB > L2)"},
+                          "us_per_launch": us, "bytes_per_launch": bytes_per_launch,
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                       "peak_source": peak_src, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS, "traffic": None}}))
+    elif args.op == "flash":
+        B, H, KV, D, ctx = args.m, 32, 8, 128, args.ctx
+        q = torch.randn(B, H, D, device="cuda").bfloat16()
+        kc = torch.randn(B, KV, ctx, D, device="cuda").bfloat16()
+        vc = torch.randn(B, KV, ctx, D, device="cuda").bfloat16()
+        out = torch.empty(B, H, D, device="cuda", dtype=torch.bfloat16)
+        scratch = torch.empty(lib.swlm_op_flash_decode_scratch_bytes(B, H, KV, D, ctx), device="cuda", dtype=torch.uint8)
+        flush = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+        kv_bytes = 2 * B * KV * ctx * D * 2
+        small = kv_bytes < (160 << 20)
+
+        def call():
+            lib.check(lib.swlm_op_flash_decode_dev(store.handle, B, H, KV, D, ctx, ctx, 1.0 / np.sqrt(D), q.data_ptr(), kc.data_ptr(),
+                                                   vc.data_ptr(), out.data_ptr(), scratch.data_ptr(), sptr))
+
+        for _ in range(max(3, args.warmup)):
+            call()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(args.steps):
+            if small:
+                flush.fill_(1)  # the cache fits in L2: evict it between timed calls
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            call()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        us = total * 1e3 / args.steps
+        gbs = kv_bytes / (us * 1e-6) / 1e9
+        print(json.dumps({"metric": "flash-decode HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                          "config": {"workload": f"flash-decode GQA 32q/8kv x128, batch {B}, context {ctx}",
+                                     "l2": "L2 flushed between calls" if small else "KV cache larger than L2"},
+                          "us_per_call": us, "bytes_per_call": kv_bytes,
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                       "peak_source": peak_src, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS, "traffic": None}}))
+    store.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--op", choices=["qgemv", "flash"], default=None, help="op-level line instead of the decode benchmark")
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--min-mb", type=float, default=400.0, help="rotate through at least this many MB of distinct weights")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
@@ -155,6 +243,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, pkg)
+        return
+    if args.op:
+        run_op(args, pkg)
         return
 
     import torch
@@ -179,7 +270,9 @@ def main():
         from swlm_b200 import tp as tp_mod
         tp_mod.attach(store, dist)
     model = pkg.load_model(store, builder, weights)
-    stream = torch.cuda.current_stream()
+    # a stream of our own: torch's default stream has handle 0, which the C ABI reads as "use your own"
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     model.set_stream(stream.cuda_stream)
 
     # ---- context: `ctx` tokens in the KV cache ---------------------------------------------------------------
