@@ -3,8 +3,8 @@
 // Replaces `rope_flash_attn_decode` (Generator/MetalSourceGenerator+Attention.swift:551-930): the
 // reference runs one 32-thread group per query head that walks the context sequentially and re-reads
 // the K/V rows of a GQA group once per query head. Here
-//   * the KV range is split across CTAs (flash-decode); a second small kernel merges the partial
-//     (max, sum, output) triples;
+//   * the KV range is split across CTAs (flash-decode); the last CTA of a (sequence, KV head) to finish
+//     merges the partial (max, sum, output) triples, so the whole step is one launch;
 //   * one CTA serves all query heads of a KV head, so K/V are read once per group;
 //   * QK^T and PV run on the tensor cores (mma.m16n8k16, bf16 in, fp32 accumulate) with the head
 //     dimension permuted so that every lane fetches K and V with 128-bit loads and no shared memory:
@@ -12,7 +12,7 @@
 //     paired into a B-fragment register with one PRMT;
 //   * q is rotated (RoPE) in fp32 and fed to the tensor core as a bf16 hi + lo pair, so it keeps
 //     ~16 bits of mantissa (the reference keeps the rotated q in fp32);
-//   * the current token is not read back from the cache: the merge kernel adds its term in fp32 from
+//   * the current token is not read back from the cache: the merging CTA adds its term in fp32 from
 //     the unrounded rotated k and v, exactly as the reference does (:866-868, :905-907), while the
 //     bf16-rounded copy is appended to the cache for later steps (:761-805).
 #include <cmath>
@@ -43,6 +43,7 @@ struct AttnParams {
     __nv_bfloat16* out; int out_stride;
     float* part_o;   // [m][heads][splits][HD]
     float* part_ml;  // [m][heads][splits][2]
+    unsigned* counters;  // [m][kv_heads], zero between launches
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -69,6 +70,8 @@ __device__ __forceinline__ float rope_elem(const float* v, int d, int rope_dim, 
 
 template <int HD, bool DECODE>
 __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int NCH = HD / 32;  // 16-byte K chunks per lane per token
     constexpr int VH = HD / 64;   // 64-dimension halves of V
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -277,55 +280,64 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
             l = fmaf(wgt, lsm[w][r], l);
         }
         const size_t slot = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits + split;
-        p.part_o[slot * HD + d] = o;
-        if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
+        __stcg(p.part_o + slot * HD + d, o);
+        if (d == 0) { __stcg(p.part_ml + slot * 2, mx); __stcg(p.part_ml + slot * 2 + 1, l); }
     }
-}
 
-// One CTA per (query head, sequence), one thread per output dimension.
-template <int HD, bool DECODE>
-__global__ void __launch_bounds__(HD) attn_combine_kernel(const AttnParams p) {
-    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-    const int kvh = h * p.kv_heads / p.heads;
-    __shared__ float qv[HD], kv[HD];
-    __shared__ float cs[HD / 2], sn[HD / 2];
-    __shared__ float red[HD / 32];
+    // ---- the last CTA of this (sequence, KV head) to arrive merges the splits and writes the output ----
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned* ctr = p.counters + (size_t)b * p.kv_heads + kvh;
+        const unsigned prev = atomicAdd(ctr, 1u);
+        is_last = prev == (unsigned)p.splits - 1u;
+        if (is_last) *ctr = 0u;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
 
-    float m_self = -INFINITY, v_self = 0.f;
+    // current token: its score and value enter in fp32, from the unrounded rotated k and v
+    // (Generator/MetalSourceGenerator+Attention.swift:866-868, :905-907)
+    float* self_score = lsm[0];  // reuse: G floats
+    float* vnew = osm[0][0];     // reuse: HD floats
     if (DECODE) {
-        const int pos = p.position[0];
-        if (d < (p.rope_dim >> 1)) {
-            float s, c;
-            sincosf((float)pos * p.inv_freq[d], &s, &c);
-            cs[d] = c; sn[d] = s;
+        for (int d = tid; d < HD; d += kSplitThreads) {
+            vec[d] = __bfloat162float(p.k[(size_t)b * p.k_stride + kvh * HD + d]);
+            vnew[d] = __bfloat162float(p.v[(size_t)b * p.v_stride + kvh * HD + d]);
         }
-        qv[d] = __bfloat162float(p.q[(size_t)b * p.q_stride + (size_t)h * HD + d]);
-        kv[d] = __bfloat162float(p.k[(size_t)b * p.k_stride + (size_t)kvh * HD + d]);
         __syncthreads();
-        float prod = rope_elem(qv, d, p.rope_dim, cs, sn) * rope_elem(kv, d, p.rope_dim, cs, sn);
-        for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
-        if ((d & 31) == 0) red[d >> 5] = prod;
-        __syncthreads();
-        float score = 0.f;
+        float krot[(HD + 31) / 32];
 #pragma unroll
-        for (int w = 0; w < HD / 32; ++w) score += red[w];
-        m_self = score * p.scale_log2;
-        v_self = __bfloat162float(p.v[(size_t)b * p.v_stride + (size_t)kvh * HD + d]);
+        for (int i = 0; i < HD / 32; ++i) krot[i] = rope_elem(vec, lane + 32 * i, p.rope_dim, cs, sn);
+        for (int r = warp; r < G; r += kSplitWarps) {
+            float prod = 0.f;
+#pragma unroll
+            for (int i = 0; i < HD / 32; ++i) prod = fmaf(qrot[r][lane + 32 * i], krot[i], prod);
+            for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
+            if (lane == 0) self_score[r] = prod * p.scale_log2;
+        }
+        __syncthreads();
     }
-    const size_t base = ((size_t)b * p.heads + h) * p.splits;
-    float mx = m_self;
-    for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, p.part_ml[(base + s) * 2]);
-    float num = 0.f, den = 0.f;
-    if (DECODE) { const float w = exp2f(m_self - mx); num = w * v_self; den = w; }
-    for (int s = 0; s < p.splits; ++s) {
-        const float ms = p.part_ml[(base + s) * 2];
-        if (ms == -INFINITY) continue;
-        const float w = exp2f(ms - mx);
-        num = fmaf(w, p.part_o[(base + s) * HD + d], num);
-        den = fmaf(w, p.part_ml[(base + s) * 2 + 1], den);
+    for (int idx = tid; idx < G * HD; idx += kSplitThreads) {
+        const int r = idx / HD, d = idx - r * HD;
+        const size_t base = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits;
+        const float m_self = DECODE ? self_score[r] : -INFINITY;
+        float mx = m_self;
+        for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(p.part_ml + (base + s) * 2));
+        float num = 0.f, den = 0.f;
+        if (DECODE) { const float w = exp2f(m_self - mx); num = w * vnew[d]; den = w; }
+        for (int s = 0; s < p.splits; ++s) {
+            const float ms = __ldcg(p.part_ml + (base + s) * 2);
+            if (ms == -INFINITY) continue;
+            const float w = exp2f(ms - mx);
+            num = fmaf(w, __ldcg(p.part_o + (base + s) * HD + d), num);
+            den = fmaf(w, __ldcg(p.part_ml + (base + s) * 2 + 1), den);
+        }
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
+        p.out[(size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(num * inv);
     }
-    const float inv = den > 0.f ? 1.0f / den : 0.f;
-    p.out[(size_t)b * p.out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(num * inv);
 }
 
 int check_launch(const char* what) {
@@ -337,13 +349,10 @@ int check_launch(const char* what) {
 template <bool DECODE>
 int launch_both(const AttnParams& p, int m, int hd, cudaStream_t s) {
     const dim3 grid(p.splits, p.kv_heads, m);
-    const dim3 cgrid(p.heads, m);
     if (hd == 128) {
-        attn_split_kernel<128, DECODE><<<grid, kSplitThreads, 0, s>>>(p);
-        attn_combine_kernel<128, DECODE><<<cgrid, 128, 0, s>>>(p);
+        launch_k(attn_split_kernel<128, DECODE>, dim3(grid), dim3(kSplitThreads), 0, s, p);
     } else if (hd == 64) {
-        attn_split_kernel<64, DECODE><<<grid, kSplitThreads, 0, s>>>(p);
-        attn_combine_kernel<64, DECODE><<<cgrid, 64, 0, s>>>(p);
+        launch_k(attn_split_kernel<64, DECODE>, dim3(grid), dim3(kSplitThreads), 0, s, p);
     } else {
         set_error("attention: head_dim %d not supported (64 or 128)", hd);
         return SWLM_ERR_UNSUPPORTED;
@@ -392,12 +401,13 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     p.out = a.out; p.out_stride = a.out_stride;
     p.part_o = a.scratch;
     p.part_ml = a.scratch + (size_t)a.m * a.heads * a.splits * a.head_dim;
+    p.counters = a.counters;
     return launch_both<true>(p, a.m, a.head_dim, s);
 }
 
 int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, float scale,
                               const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
-                              __nv_bfloat16* out, float* scratch, int splits, cudaStream_t s) {
+                              __nv_bfloat16* out, float* scratch, unsigned* counters, int splits, cudaStream_t s) {
     int rc = check_group(heads, kv_heads);
     if (rc) return rc;
     AttnParams p{};
@@ -411,6 +421,7 @@ int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_le
     p.out = out; p.out_stride = heads * hd;
     p.part_o = scratch;
     p.part_ml = scratch + (size_t)m * heads * splits * hd;
+    p.counters = counters;
     return launch_both<false>(p, m, hd, s);
 }
 

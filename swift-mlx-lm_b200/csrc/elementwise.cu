@@ -34,6 +34,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(int dim, const __nv_bfloat
                                                      __nv_bfloat16* residual, int res_stride,
                                                      const __nv_bfloat16* weight, float eps, float weight_bias,
                                                      __nv_bfloat16* out, int out_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) float hbuf[];
     __shared__ float red[8];
     const int b = blockIdx.x;
@@ -70,6 +72,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(int dim, const __nv_bfloat
 __global__ void qk_norm_kernel(int heads, int kv_heads, int head_dim, __nv_bfloat16* q, int q_stride,
                                __nv_bfloat16* k, int k_stride, const __nv_bfloat16* wq, const __nv_bfloat16* wk,
                                float eps, float weight_bias) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.y;
     const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -88,6 +92,8 @@ __global__ void qk_norm_kernel(int heads, int kv_heads, int head_dim, __nv_bfloa
 // embedding_lookup_bf16 (Generator/MetalSourceGenerator+Embedding.swift:3-48).
 __global__ void embed_kernel(int dim, const int32_t* tokens, int vocab, const __nv_bfloat16* table,
                              __nv_bfloat16* out, int out_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.y;
     int tok = tokens[b];
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
@@ -101,6 +107,8 @@ __global__ void embed_kernel(int dim, const int32_t* tokens, int vocab, const __
 // into the gate/up GEMV epilogue.
 __global__ void swiglu_kernel(int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
                               __nv_bfloat16* out, int o_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float g = __bfloat162float(gate[(size_t)b * g_stride + i]);
@@ -113,6 +121,8 @@ __global__ void swiglu_kernel(int n, const __nv_bfloat16* gate, int g_stride, co
 __global__ void conv_step_kernel(int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,
                                  const __nv_bfloat16* in, int in_stride, const __nv_bfloat16* weight,
                                  __nv_bfloat16* out, int out_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= dim) return;
     const __nv_bfloat16* x = in + (size_t)b * in_stride;
@@ -141,6 +151,8 @@ __device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi)
 
 __global__ void __launch_bounds__(256) argmax_partial_kernel(int n, const __nv_bfloat16* logits, int stride,
                                                             float* pval, int32_t* pidx) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.y;
     const __nv_bfloat16* row = logits + (size_t)b * stride;
     float best = -INFINITY;
@@ -169,6 +181,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(int n, const __nv_b
 __global__ void argmax_final_kernel(int m, const float* pval, const int32_t* pidx, int32_t* token_out,
                                     int32_t* token_in_next, int32_t* ring, int32_t* step_counter, int ring_cap,
                                     int32_t* position, int advance) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int b = warp; b < m; b += (blockDim.x >> 5)) {
         float best = -INFINITY;
@@ -194,10 +208,14 @@ __global__ void argmax_final_kernel(int m, const float* pval, const int32_t* pid
 }
 
 __global__ void fill_u32_kernel(uint32_t* p, size_t n, uint32_t v) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;
 }
 __global__ void advance_kernel(int32_t* position, int32_t* step_counter) {
+    pdl_launch_dependents();
+    pdl_wait();
     position[0] += 1;
     if (step_counter) step_counter[0] += 1;
 }
@@ -220,13 +238,13 @@ int launch_rmsnorm(int mode, int m, int dim, const __nv_bfloat16* in, int in_str
     const size_t smem = (size_t)dim * 4;
     switch (mode) {
     case SWLM_STEP_COPY_RMSNORM:
-        rmsnorm_kernel<0><<<m, 256, smem, s>>>(dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
+        launch_k(rmsnorm_kernel<0>, m, 256, smem, s, dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
         break;
     case SWLM_STEP_RESADD_COPY_RMSNORM:
-        rmsnorm_kernel<1><<<m, 256, smem, s>>>(dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
+        launch_k(rmsnorm_kernel<1>, m, 256, smem, s, dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
         break;
     case SWLM_STEP_RESADD_RMSNORM:
-        rmsnorm_kernel<2><<<m, 256, smem, s>>>(dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
+        launch_k(rmsnorm_kernel<2>, m, 256, smem, s, dim, in, in_stride, residual, res_stride, weight, eps, weight_bias, out, out_stride);
         break;
     default:
         set_error("rmsnorm: bad mode %d", mode);
@@ -239,27 +257,27 @@ int launch_qk_norm(int m, int heads, int kv_heads, int head_dim, __nv_bfloat16* 
                    int k_stride, const __nv_bfloat16* wq, const __nv_bfloat16* wk, float eps, float weight_bias,
                    cudaStream_t s) {
     const int total = heads + kv_heads;
-    qk_norm_kernel<<<dim3((total + 3) / 4, m), 128, 0, s>>>(heads, kv_heads, head_dim, q, q_stride, k, k_stride, wq, wk, eps, weight_bias);
+    launch_k(qk_norm_kernel, dim3((total + 3) / 4, m), 128, 0, s, heads, kv_heads, head_dim, q, q_stride, k, k_stride, wq, wk, eps, weight_bias);
     return check_launch("qk_norm launch");
 }
 
 int launch_embed(int m, int dim, const int32_t* tokens, int vocab, const __nv_bfloat16* table, __nv_bfloat16* out,
                  int out_stride, cudaStream_t s) {
     if (dim % 8 || out_stride % 8) { set_error("embed: dim must be a multiple of 8"); return SWLM_ERR_INVALID; }
-    embed_kernel<<<dim3((dim / 8 + 127) / 128, m), 128, 0, s>>>(dim, tokens, vocab, table, out, out_stride);
+    launch_k(embed_kernel, dim3((dim / 8 + 127) / 128, m), 128, 0, s, dim, tokens, vocab, table, out, out_stride);
     return check_launch("embed launch");
 }
 
 int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
                   __nv_bfloat16* out, int o_stride, cudaStream_t s) {
-    swiglu_kernel<<<dim3((n + 255) / 256, m), 256, 0, s>>>(n, gate, g_stride, up, u_stride, out, o_stride);
+    launch_k(swiglu_kernel, dim3((n + 255) / 256, m), 256, 0, s, n, gate, g_stride, up, u_stride, out, o_stride);
     return check_launch("swiglu launch");
 }
 
 int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,
                      const __nv_bfloat16* in, int in_stride, const __nv_bfloat16* weight, __nv_bfloat16* out,
                      int out_stride, cudaStream_t s) {
-    conv_step_kernel<<<dim3((dim + 255) / 256, m), 256, 0, s>>>(dim, kernel, state, state_seq_stride, in, in_stride, weight, out, out_stride);
+    launch_k(conv_step_kernel, dim3((dim + 255) / 256, m), 256, 0, s, dim, kernel, state, state_seq_stride, in, in_stride, weight, out, out_stride);
     return check_launch("conv_step launch");
 }
 
@@ -268,19 +286,19 @@ size_t argmax_scratch_elems(int m) { return (size_t)m * kArgmaxBlocks; }
 int launch_argmax(int m, int n, const __nv_bfloat16* logits, int stride, int32_t* token_out, int32_t* token_in_next,
                   int32_t* ring, int32_t* step_counter, int ring_cap, int32_t* position, int advance,
                   float* scratch_val, int32_t* scratch_idx, cudaStream_t s) {
-    argmax_partial_kernel<<<dim3(kArgmaxBlocks, m), 256, 0, s>>>(n, logits, stride, scratch_val, scratch_idx);
-    argmax_final_kernel<<<1, 256, 0, s>>>(m, scratch_val, scratch_idx, token_out, token_in_next, ring, step_counter,
+    launch_k(argmax_partial_kernel, dim3(kArgmaxBlocks, m), 256, 0, s, n, logits, stride, scratch_val, scratch_idx);
+    launch_k(argmax_final_kernel, 1, 256, 0, s, m, scratch_val, scratch_idx, token_out, token_in_next, ring, step_counter,
                                           ring_cap, position, advance);
     return check_launch("argmax launch");
 }
 
 int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s) {
     if (n == 0) return SWLM_OK;
-    fill_u32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p, n, v);
+    launch_k(fill_u32_kernel, (unsigned)((n + 255) / 256), 256, 0, s, p, n, v);
     return check_launch("fill launch");
 }
 int launch_advance(int32_t* position, int32_t* step_counter, cudaStream_t s) {
-    advance_kernel<<<1, 1, 0, s>>>(position, step_counter);
+    launch_k(advance_kernel, 1, 1, 0, s, position, step_counter);
     return check_launch("advance launch");
 }
 

@@ -7,13 +7,21 @@
 // Design: the kernel is HBM-bound on the 0.5625 bytes/weight stream, and on B200 the
 // per-weight instruction budget is the second limit, so
 //   * weights are re-tiled at upload into 512-byte tiles (16 rows x 64 columns) laid out in
-//     mma.m16n8k16 A-fragment order: one 16-byte load per lane per tile, no shuffles;
-//   * every warp streams its tiles through a private cp.async ring in shared memory
-//     (kStages deep), so loads stay in flight independent of register pressure;
-//   * a nibble pair becomes two bf16 values 128+q with one LOP3 ((w>>s) & 0x000F000F | 0x43004300);
-//     the tensor core forms sum((128+q)*x) per group in fp32, and the group epilogue applies
-//     scale*(acc - 128*sum(x)) + zero*sum(x) in fp32 — algebraically the reference's
-//     sum((scale*q+zero)*x), with q and x exact in bf16 and products exact in fp32;
+//     mma.m16n8k16 A-fragment order: one 16-byte load per lane per tile, no shuffles. The contraction
+//     order inside a group is free, so k-step j of lane t is defined to cover columns 16t+4j..16t+4j+3:
+//     the matching B fragments are then 16 consecutive activations, read as they lie in memory;
+//   * the grid is persistent (at most three CTAs per SM, all resident) and the matrix is cut into
+//     (row tile, k-slice) units of a few KB that are dealt out evenly, so every SM streams the same
+//     number of bytes and nothing is left for a second wave; activations are staged once per CTA;
+//     partial sums of a row tile meet in global scratch and the last warp to arrive adds them in
+//     slice order, which keeps the result independent of scheduling;
+//   * every warp streams its units through a private cp.async ring in shared memory (kStages deep)
+//     that runs ahead across unit boundaries, so loads stay in flight independent of register pressure;
+//   * a nibble pair becomes two fp16 values 1024+q (low nibbles) or 1024+16q (high nibbles) with one
+//     LOP3 ((w & mask) | 0x64006400), one shift per four pairs; activations are converted bf16 -> fp16
+//     times a per-column power of two, which is exact; the tensor core forms sum((1024+q)*x) per group
+//     in fp32, and the group epilogue applies scale*(acc - 1024*sum(x)) + zero*sum(x) in fp32 —
+//     algebraically the reference's sum((scale*q+zero)*x), with q and x exact and products exact in fp32;
 //   * the B operand holds up to 16 sequences (columns), so batch <= 16 costs the same weight traffic.
 #include <algorithm>
 
@@ -24,11 +32,10 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 4;                 // ring depth per warp; one stage = 4 k-tiles + their scales
+constexpr int kStages = 3;                 // ring depth per warp; one stage = 4 k-tiles + their scales
 constexpr int kStageBytes = 4 * 512 + 256;
 constexpr int kRingBytes = kWarps * kStages * kStageBytes;
 constexpr int kXPad = 8;                   // bf16 elements of padding per x row (bank skew)
-constexpr int kMaxXBytes = 96 * 1024;
 
 struct QGemvParams {
     const uint4* tiles;
@@ -39,7 +46,7 @@ struct QGemvParams {
     __nv_bfloat16* y[3];
     int y_stride[3], seg_end[3];
     int m;
-    int rw, sw, sk;
+    int si, sk;   // k-slices per CTA group, CTA groups along K
     float* partial;
     unsigned* counters;
 };
@@ -60,275 +67,576 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_f16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                        unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ float half_bits_to_float(unsigned bits16, int is_f16) {
     return is_f16 ? __half2float(__ushort_as_half((unsigned short)bits16)) : __uint_as_float(bits16 << 16);
 }
+// (scale, zero) pair of one row and group: scale in the low half-word, zero in the high one
+template <bool F16SB>
+__device__ __forceinline__ float sb_scale(unsigned pair) {
+    return F16SB ? __half2float(__ushort_as_half((unsigned short)(pair & 0xFFFFu))) : __uint_as_float(pair << 16);
+}
+template <bool F16SB>
+__device__ __forceinline__ float sb_zero(unsigned pair) {
+    return F16SB ? __half2float(__ushort_as_half((unsigned short)(pair >> 16))) : __uint_as_float(pair & 0xFFFF0000u);
+}
 
-template <int NT, int EPI>
-__global__ void __launch_bounds__(kThreads, 2) qgemv_kernel(const QGemvParams p) {
+// One unit of work = (row tile rt, k-slice s): 16 output rows x a contiguous run of stages.
+struct UnitCursor {
+    int u, u_end;     // current unit and end of this warp's sequence (stride kWarps)
+    int st, st_end;   // current stage (in units of 4 k-tiles) and end of the current unit's run
+    int rt;
+};
+
+template <int NT, int EPI, bool F16SB>
+__global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const QGemvParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int COLS = 8 * NT;
+    __shared__ unsigned colmax[COLS];
+    __shared__ float colscale[COLS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
-    // k-range of this CTA and of this warp, in units of 4 k-tiles (256 columns)
-    const int c0 = (int)(((long long)blockIdx.y * p.kt4_total) / p.sk);
-    const int c1 = (int)(((long long)(blockIdx.y + 1) * p.kt4_total) / p.sk);
-    const int nk_cta = (c1 - c0) * 256;
+    // k-range of this CTA group (blockIdx.y), in stages of 4 k-tiles (256 columns)
+    const int g0 = (int)(((long long)blockIdx.y * p.kt4_total) / p.sk);
+    const int g1 = (int)(((long long)(blockIdx.y + 1) * p.kt4_total) / p.sk);
+    const int glen = g1 - g0;
+    const int nk_cta = glen * 256;
     const int xs_stride = nk_cta + kXPad;
     const int rows_x = p.m < COLS ? p.m : COLS;
 
-    unsigned char* ring = smem;
-    __nv_bfloat16* xperm = reinterpret_cast<__nv_bfloat16*>(smem + kRingBytes);
+    unsigned char* my_ring = smem + warp * (kStages * kStageBytes);
+    __nv_bfloat16* xsm = reinterpret_cast<__nv_bfloat16*>(smem + kRingBytes);
     float* xsum = reinterpret_cast<float*>(smem + kRingBytes + (size_t)rows_x * xs_stride * 2);
 
-    const int rt = blockIdx.x * p.rw + warp / p.sw;
-    const int ks = warp % p.sw;
-    const bool active = rt < p.row_tiles;
-    const int w0 = c0 + (ks * (c1 - c0)) / p.sw;
-    const int w1 = c0 + ((ks + 1) * (c1 - c0)) / p.sw;
-    const int nst = active ? (w1 - w0) : 0;
-
-    unsigned char* my_ring = ring + warp * (kStages * kStageBytes);
-    const uint4* tile_src = p.tiles + ((size_t)rt * p.kt4_total * 4) * 32;
-    const uint4* sb_src = p.sb + (size_t)rt * p.kt4_total * 16;
-
-    auto issue = [&](int i) {
-        if (i < nst) {
-            const int kt4 = w0 + i;
-            unsigned char* dst = my_ring + (i % kStages) * kStageBytes;
-            const uint4* src = tile_src + (size_t)kt4 * 128;
+    // units of this group: u = rt * si + s, s-th slice of the group's k-range; this CTA owns a contiguous
+    // share, its warps take them round-robin
+    const int units = p.row_tiles * p.si;
+    const int u_lo = (int)(((long long)blockIdx.x * units) / gridDim.x);
+    const int u_hi = (int)(((long long)(blockIdx.x + 1) * units) / gridDim.x);
+    auto open_unit = [&](UnitCursor& c) {
+        if (c.u < c.u_end) {
+            c.rt = c.u / p.si;
+            const int s = c.u - c.rt * p.si;
+            c.st = g0 + (s * glen) / p.si;
+            c.st_end = g0 + ((s + 1) * glen) / p.si;
+        }
+    };
+    UnitCursor ic{u_lo + warp, u_hi, 0, 0, 0};  // issue side, runs kStages-1 stages ahead
+    open_unit(ic);
+    auto issue = [&](int slot) {
+        while (ic.u < ic.u_end && ic.st >= ic.st_end) { ic.u += kWarps; open_unit(ic); }
+        if (ic.u < ic.u_end) {
+            unsigned char* dst = my_ring + slot * kStageBytes;
+            const uint4* src = p.tiles + ((size_t)ic.rt * p.kt4_total + ic.st) * 128;
 #pragma unroll
             for (int q = 0; q < 4; ++q) cp_async16(dst + (q * 32 + lane) * 16, src + q * 32 + lane);
-            if (lane < 16) cp_async16(dst + 2048 + lane * 16, sb_src + (size_t)kt4 * 16 + lane);
+            if (lane < 16) cp_async16(dst + 2048 + lane * 16, p.sb + ((size_t)ic.rt * p.kt4_total + ic.st) * 16 + lane);
+            ic.st += 1;
         }
         cp_async_commit();
     };
 
-    // Weights do not depend on the activations: start streaming before x is staged.
+    // Weights do not depend on the activations or on the preceding kernel: the ring starts filling at once.
+    pdl_launch_dependents();
+    int issued = 0, consumed = 0;
 #pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) issue(i);
-
-    // ---- stage x: permute each 64-element group into B-fragment order and sum it -------------
+    for (int i = 0; i < kStages - 1; ++i) { issue(issued % kStages); ++issued; }
+    pdl_wait();
+    // ---- x: asynchronous copy in its natural order (the tile layout was chosen so that lane t's B
+    // fragments of a group are the 16 consecutive elements 16t..16t+15)-------------------------------
     {
         const int chunks_per_row = nk_cta / 8;
         const int total = rows_x * chunks_per_row;
         for (int idx = tid; idx < total; idx += kThreads) {
             const int b = idx / chunks_per_row, cc = idx - b * chunks_per_row;
-            const int kglob = c0 * 256 + cc * 8;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (kglob < p.k) v = *reinterpret_cast<const uint4*>(p.x + (size_t)b * p.x_stride + kglob);
-            const int ktl = cc >> 3, c = cc & 7, j = c >> 1, half = c & 1;
-            unsigned* dst = reinterpret_cast<unsigned*>(xperm + (size_t)b * xs_stride + ktl * 64 + j * 4 + half * 2);
-            dst[0] = v.x;   // t = 0 : elements 2t, 2t+1 of this half
-            dst[8] = v.y;   // t = 1 (16 bf16 = 8 words apart)
-            dst[16] = v.z;
-            dst[24] = v.w;
-            float s = __uint_as_float(v.x << 16) + __uint_as_float(v.x & 0xFFFF0000u) +
-                      __uint_as_float(v.y << 16) + __uint_as_float(v.y & 0xFFFF0000u) +
-                      __uint_as_float(v.z << 16) + __uint_as_float(v.z & 0xFFFF0000u) +
-                      __uint_as_float(v.w << 16) + __uint_as_float(v.w & 0xFFFF0000u);
+            const int kglob = g0 * 256 + cc * 8;
+            __nv_bfloat16* dst = xsm + (size_t)b * xs_stride + cc * 8;
+            if (kglob < p.k) cp_async16(dst, p.x + (size_t)b * p.x_stride + kglob);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        cp_async_commit();
+    }
+
+    // ---- x: bf16 -> fp16 times a power of two (exact unless an element is 2^-24 below the column's
+    // largest), in place, and the per-group sums of the converted values (the zero-point term) -----------
+    cp_async_wait<0>();
+    if (tid < COLS) colmax[tid] = 0;
+    __syncthreads();
+    {
+        const int words_per_row = nk_cta / 2;
+        for (int b = 0; b < rows_x; ++b) {
+            const unsigned* xw = reinterpret_cast<const unsigned*>(xsm + (size_t)b * xs_stride);
+            unsigned mx = 0;
+            for (int i = tid; i < words_per_row; i += kThreads) {
+                const unsigned w = xw[i];
+                mx = max(mx, max(w & 0x7FFFu, (w >> 16) & 0x7FFFu));
+            }
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            if (lane == 0) atomicMax(&colmax[b], mx);
+        }
+    }
+    __syncthreads();
+    {
+        const int tasks_per_row = nk_cta / 16;
+        const int total = rows_x * tasks_per_row;
+        for (int base = 0; base < total; base += kThreads) {
+            const int idx = base + tid;
+            const bool valid = idx < total;
+            float s = 0.f;
+            int b = 0, c = 0;
+            if (valid) {
+                b = idx / tasks_per_row; c = idx - b * tasks_per_row;
+                // shift the column's largest exponent to 2^13: fp16 keeps every bf16 mantissa bit
+                const int e = (int)(colmax[b] >> 7);
+                const int sh = (e == 0 || e == 255) ? 0 : 140 - e;
+                const float mul = __uint_as_float((unsigned)(127 + max(-120, min(120, sh))) << 23);
+                unsigned* xp = reinterpret_cast<unsigned*>(xsm + (size_t)b * xs_stride + c * 16);
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    const unsigned v = xp[w];
+                    const __half2 h = __floats2half2_rn(__uint_as_float(v << 16) * mul, __uint_as_float(v & 0xFFFF0000u) * mul);
+                    xp[w] = *reinterpret_cast<const unsigned*>(&h);
+                    const float2 f = __half22float2(h);
+                    s += f.x + f.y;
+                }
+                if (c == 0) colscale[b] = 1.0f / mul;
+            }
             s += __shfl_xor_sync(0xffffffffu, s, 1);
             s += __shfl_xor_sync(0xffffffffu, s, 2);
-            s += __shfl_xor_sync(0xffffffffu, s, 4);
-            if (c == 0) xsum[ktl * COLS + b] = s;
+            if (valid && (c & 3) == 0) xsum[(c >> 2) * COLS + b] = s;
         }
     }
     __syncthreads();
 
-    float tot[NT][4];
+    const int s_total = p.sk * p.si;  // partial results per row tile
+    UnitCursor cc{u_lo + warp, u_hi, 0, 0, 0};
+    for (; cc.u < cc.u_end; cc.u += kWarps) {
+        open_unit(cc);
+        const int rt = cc.rt;
+        float tot[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.f;
+        for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.f;
 
-    for (int i = 0; i < nst; ++i) {
-        issue(i + kStages - 1);
-        cp_async_wait<kStages - 1>();
-        __syncwarp();
-        const unsigned char* st = my_ring + (i % kStages) * kStageBytes;
-        const uint4* wsm = reinterpret_cast<const uint4*>(st);
-        const uint4 sA = reinterpret_cast<const uint4*>(st + 2048)[g];
-        const uint4 sB = reinterpret_cast<const uint4*>(st + 2048)[g + 8];
-        const unsigned sAw[4] = {sA.x, sA.y, sA.z, sA.w};
-        const unsigned sBw[4] = {sB.x, sB.y, sB.z, sB.w};
-        const int ktl0 = (w0 + i - c0) * 4;
+        for (int stg = cc.st; stg < cc.st_end; ++stg) {
+            issue(issued % kStages); ++issued;
+            cp_async_wait<kStages - 1>();
+            __syncwarp();
+            const unsigned char* st = my_ring + (consumed % kStages) * kStageBytes;
+            ++consumed;
+            const uint4* wsm = reinterpret_cast<const uint4*>(st) + lane;
+            const uint4 sA = reinterpret_cast<const uint4*>(st + 2048)[g];
+            const uint4 sB = reinterpret_cast<const uint4*>(st + 2048)[g + 8];
+            const unsigned sAw[4] = {sA.x, sA.y, sA.z, sA.w};
+            const unsigned sBw[4] = {sB.x, sB.y, sB.z, sB.w};
+            const int ktl0 = (stg - g0) * 4;
+            const __nv_bfloat16* xrow = xsm + ktl0 * 64 + t * 16;
+            const float* xsrow = xsum + ktl0 * COLS + 2 * t;
 #pragma unroll
-        for (int ti = 0; ti < 4; ++ti) {
-            const uint4 wv = wsm[ti * 32 + lane];
-            const unsigned wr[4] = {wv.x, wv.y, wv.z, wv.w};
-            const int ktl = ktl0 + ti;
-            uint4 X0[NT], X1[NT];
-            float acc[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-                const int col = 8 * nt + g;
-                if (col < p.m) {
-                    const uint4* xp = reinterpret_cast<const uint4*>(xperm + (size_t)col * xs_stride + ktl * 64 + t * 16);
-                    X0[nt] = xp[0];
-                    X1[nt] = xp[1];
-                } else {
-                    X0[nt] = make_uint4(0, 0, 0, 0);
-                    X1[nt] = make_uint4(0, 0, 0, 0);
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const unsigned r = wr[j];
-                const unsigned a0 = (r & 0x000F000Fu) | 0x43004300u;
-                const unsigned a1 = ((r >> 4) & 0x000F000Fu) | 0x43004300u;
-                const unsigned a2 = ((r >> 8) & 0x000F000Fu) | 0x43004300u;
-                const unsigned a3 = ((r >> 12) & 0x000F000Fu) | 0x43004300u;
+            for (int ti = 0; ti < 4; ++ti) {
+                const uint4 wv = wsm[ti * 32];
+                const unsigned wr[4] = {wv.x, wv.y, wv.z, wv.w};
+                uint4 X0[NT], X1[NT];
+                float acc[NT][4];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    const unsigned b0 = j == 0 ? X0[nt].x : j == 1 ? X0[nt].z : j == 2 ? X1[nt].x : X1[nt].z;
-                    const unsigned b1 = j == 0 ? X0[nt].y : j == 1 ? X0[nt].w : j == 2 ? X1[nt].y : X1[nt].w;
-                    mma_bf16(acc[nt], a0, a1, a2, a3, b0, b1);
+                    acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+                    if (8 * nt + g < p.m) {
+                        const uint4* xp = reinterpret_cast<const uint4*>(xrow + (size_t)(8 * nt + g) * xs_stride + ti * 64);
+                        X0[nt] = xp[0];
+                        X1[nt] = xp[1];
+                    } else {
+                        X0[nt] = make_uint4(0, 0, 0, 0);
+                        X1[nt] = make_uint4(0, 0, 0, 0);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    // fp16 1024+q from the low nibble of each byte pair, 1024+16q from the high nibble:
+                    // rows g (a0, a2) carry q, rows g+8 (a1, a3) carry 16q, undone through their scale
+                    const unsigned r = wr[j], r8 = r >> 8;
+                    const unsigned a0 = (r & 0x000F000Fu) | 0x64006400u;
+                    const unsigned a1 = (r & 0x00F000F0u) | 0x64006400u;
+                    const unsigned a2 = (r8 & 0x000F000Fu) | 0x64006400u;
+                    const unsigned a3 = (r8 & 0x00F000F0u) | 0x64006400u;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const unsigned b0 = j == 0 ? X0[nt].x : j == 1 ? X0[nt].z : j == 2 ? X1[nt].x : X1[nt].z;
+                        const unsigned b1 = j == 0 ? X0[nt].y : j == 1 ? X0[nt].w : j == 2 ? X1[nt].y : X1[nt].w;
+                        mma_f16(acc[nt], a0, a1, a2, a3, b0, b1);
+                    }
+                }
+                // group epilogue: sum_k (s*q + z)*x = s*(acc - 1024*xsum) + z*xsum, with s/16 for rows g+8
+                const float s_lo = sb_scale<F16SB>(sAw[ti]), z_lo = sb_zero<F16SB>(sAw[ti]);
+                const float s_hi = sb_scale<F16SB>(sBw[ti]) * 0.0625f, z_hi = sb_zero<F16SB>(sBw[ti]);
+                const float zp_lo = fmaf(-1024.f, s_lo, z_lo);
+                const float zp_hi = fmaf(-1024.f, s_hi, z_hi);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const float2 xs2 = *reinterpret_cast<const float2*>(xsrow + ti * COLS + 8 * nt);
+                    tot[nt][0] = fmaf(s_lo, acc[nt][0], fmaf(zp_lo, xs2.x, tot[nt][0]));
+                    tot[nt][1] = fmaf(s_lo, acc[nt][1], fmaf(zp_lo, xs2.y, tot[nt][1]));
+                    tot[nt][2] = fmaf(s_hi, acc[nt][2], fmaf(zp_hi, xs2.x, tot[nt][2]));
+                    tot[nt][3] = fmaf(s_hi, acc[nt][3], fmaf(zp_hi, xs2.y, tot[nt][3]));
                 }
             }
-            // group epilogue: sum_k (s*q + z)*x = s*(acc - 128*xsum) + z*xsum
-            const float s_lo = half_bits_to_float(sAw[ti] & 0xFFFFu, p.sb_f16);
-            const float z_lo = half_bits_to_float(sAw[ti] >> 16, p.sb_f16);
-            const float s_hi = half_bits_to_float(sBw[ti] & 0xFFFFu, p.sb_f16);
-            const float z_hi = half_bits_to_float(sBw[ti] >> 16, p.sb_f16);
-            const float zp_lo = fmaf(-128.f, s_lo, z_lo);
-            const float zp_hi = fmaf(-128.f, s_hi, z_hi);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const float2 xs2 = *reinterpret_cast<const float2*>(xsum + ktl * COLS + 8 * nt + 2 * t);
-                tot[nt][0] = fmaf(s_lo, acc[nt][0], fmaf(zp_lo, xs2.x, tot[nt][0]));
-                tot[nt][1] = fmaf(s_lo, acc[nt][1], fmaf(zp_lo, xs2.y, tot[nt][1]));
-                tot[nt][2] = fmaf(s_hi, acc[nt][2], fmaf(zp_hi, xs2.x, tot[nt][2]));
-                tot[nt][3] = fmaf(s_hi, acc[nt][3], fmaf(zp_hi, xs2.y, tot[nt][3]));
-            }
+            __syncwarp();
         }
-        __syncwarp();
-    }
-    cp_async_wait<0>();
-
-    // ---- reduce the in-CTA k-splits through shared memory ---------------------------------------
-    if (p.sw > 1) {
-        __syncthreads();  // every warp is done with its ring
-        float* red = reinterpret_cast<float*>(smem);
-        float* mine = red + warp * (16 * COLS);
+        // undo the power-of-two scaling of x
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            *reinterpret_cast<float2*>(mine + g * COLS + 8 * nt + 2 * t) = make_float2(tot[nt][0], tot[nt][1]);
-            *reinterpret_cast<float2*>(mine + (g + 8) * COLS + 8 * nt + 2 * t) = make_float2(tot[nt][2], tot[nt][3]);
+            const float c0s = colscale[min(8 * nt + 2 * t, rows_x - 1)], c1s = colscale[min(8 * nt + 2 * t + 1, rows_x - 1)];
+            tot[nt][0] *= c0s; tot[nt][1] *= c1s; tot[nt][2] *= c0s; tot[nt][3] *= c1s;
         }
-        __syncthreads();
-        if (ks == 0) {
-            for (int o = 1; o < p.sw; ++o) {
-                const float* other = red + (warp + o) * (16 * COLS);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const float2 lo = *reinterpret_cast<const float2*>(other + g * COLS + 8 * nt + 2 * t);
-                    const float2 hi = *reinterpret_cast<const float2*>(other + (g + 8) * COLS + 8 * nt + 2 * t);
-                    tot[nt][0] += lo.x; tot[nt][1] += lo.y; tot[nt][2] += hi.x; tot[nt][3] += hi.y;
-                }
-            }
-        }
-    }
 
-    // ---- reduce the cross-CTA k-splits through global scratch; the last CTA to arrive finishes ----
-    if (p.sk > 1) {
-        __shared__ int is_last;
-        if (ks == 0 && active) {
-            float* dst = p.partial + (((size_t)rt * p.sk + blockIdx.y) * 16) * COLS;
+        // ---- partial results of a row tile meet in global scratch; the last warp to arrive sums them in
+        // slice order (so the result does not depend on arrival order) and runs the epilogue -----------
+        if (s_total > 1) {
+            const int s_glob = blockIdx.y * p.si + (cc.u - rt * p.si);
+            float* dst = p.partial + (((size_t)rt * s_total + s_glob) * 16) * COLS;
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                *reinterpret_cast<float2*>(dst + g * COLS + 8 * nt + 2 * t) = make_float2(tot[nt][0], tot[nt][1]);
-                *reinterpret_cast<float2*>(dst + (g + 8) * COLS + 8 * nt + 2 * t) = make_float2(tot[nt][2], tot[nt][3]);
-            }
-        }
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const unsigned prev = atomicAdd(p.counters + blockIdx.x, 1u);
-            is_last = (prev == (unsigned)p.sk - 1u);
-            if (is_last) p.counters[blockIdx.x] = 0u;  // ready for the next launch
-        }
-        __syncthreads();
-        if (!is_last) return;
-        __threadfence();
-        if (ks == 0 && active) {
+            for (int nt = 0; nt < NT; ++nt)
+                if (8 * nt + 2 * t < p.m) {
+                    __stcg(reinterpret_cast<float2*>(dst + g * COLS + 8 * nt + 2 * t), make_float2(tot[nt][0], tot[nt][1]));
+                    __stcg(reinterpret_cast<float2*>(dst + (g + 8) * COLS + 8 * nt + 2 * t), make_float2(tot[nt][2], tot[nt][3]));
+                }
+            __threadfence();
+            __syncwarp();
+            unsigned prev = 0;
+            if (lane == 0) prev = atomicAdd(p.counters + rt, 1u);
+            prev = __shfl_sync(0xffffffffu, prev, 0);
+            if (prev != (unsigned)s_total - 1u) continue;
+            __threadfence();
+            if (lane == 0) p.counters[rt] = 0u;  // ready for the next launch
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.f;
-            for (int s = 0; s < p.sk; ++s) {  // fixed order: results do not depend on arrival order
-                const float* src = p.partial + (((size_t)rt * p.sk + s) * 16) * COLS;
+            for (int s = 0; s < s_total; ++s) {
+                const float* src = p.partial + (((size_t)rt * s_total + s) * 16) * COLS;
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const float2 lo = __ldcg(reinterpret_cast<const float2*>(src + g * COLS + 8 * nt + 2 * t));
-                    const float2 hi = __ldcg(reinterpret_cast<const float2*>(src + (g + 8) * COLS + 8 * nt + 2 * t));
-                    tot[nt][0] += lo.x; tot[nt][1] += lo.y; tot[nt][2] += hi.x; tot[nt][3] += hi.y;
+                for (int nt = 0; nt < NT; ++nt)
+                    if (8 * nt + 2 * t < p.m) {
+                        const float2 lo = __ldcg(reinterpret_cast<const float2*>(src + g * COLS + 8 * nt + 2 * t));
+                        const float2 hi = __ldcg(reinterpret_cast<const float2*>(src + (g + 8) * COLS + 8 * nt + 2 * t));
+                        tot[nt][0] += lo.x; tot[nt][1] += lo.y; tot[nt][2] += hi.x; tot[nt][3] += hi.y;
+                    }
+            }
+        }
+
+        // ---- epilogue --------------------------------------------------------------------------------
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int col = 8 * nt + 2 * t + e;
+                if (col >= p.m) continue;
+                if (EPI == QGEMV_EPI_STORE) {
+#pragma unroll
+                    for (int hi = 0; hi < 2; ++hi) {
+                        const int r = rt * 16 + g + 8 * hi;
+                        const __nv_bfloat16 val = __float2bfloat16_rn(tot[nt][2 * hi + e]);
+                        if (r < p.seg_end[0]) p.y[0][(size_t)col * p.y_stride[0] + r] = val;
+                        else if (r < p.seg_end[1]) p.y[1][(size_t)col * p.y_stride[1] + (r - p.seg_end[0])] = val;
+                        else if (r < p.seg_end[2]) p.y[2][(size_t)col * p.y_stride[2] + (r - p.seg_end[1])] = val;
+                    }
+                } else {
+                    // rows 0-7 of the tile are gate rows, rows 8-15 the matching up rows; both are rounded to
+                    // bf16 first because the reference stores them to bf16 scratch before `swiglu` reads them
+                    // (Primitives/ElementwiseFragment.swift:49-54).
+                    const int r = rt * 8 + g;
+                    if (r < p.seg_end[0]) {
+                        const float gate = __bfloat162float(__float2bfloat16_rn(tot[nt][e]));
+                        const float up = __bfloat162float(__float2bfloat16_rn(tot[nt][2 + e]));
+                        const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
+                        p.y[0][(size_t)col * p.y_stride[0] + r] = __float2bfloat16_rn(act);
+                    }
                 }
             }
         }
     }
+    cp_async_wait<0>();
+}
 
-    if (ks != 0 || !active) return;
+// =================================================================================================
+// Single-sequence kernel (m == 1), the batch-1 decode path.
+//
+// With one activation column the tensor core multiplies seven columns of zeros, and on this part the
+// legacy mma.sync pipe saturates near 3.5 TB/s of weight stream, so batch 1 runs on the integer dot
+// product units instead. The activations are held in shared memory in block floating point: every run of
+// 16 consecutive elements (one lane's share of a group) carries a power-of-two exponent and 16-bit
+// integers split into a signed high and an unsigned low byte, exact for every element within 2^-8 of the
+// run's largest and within 2^-16 of it otherwise. A weight word yields four nibbles of row g with one AND
+// and four of row g+8 with a shift and an AND; two dp4a per digit accumulate exact integers, and the
+// group's scale and zero are applied once per lane in fp32. Same tiles, ring and unit scheduling as above.
+// =================================================================================================
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_uu(unsigned a, unsigned b, int c) {
+    int d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 
-    // ---- epilogue ----------------------------------------------------------------------------------
+template <int EPI, bool F16SB>
+__global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int kt_total = p.kt4_total * 4;
+
+    unsigned char* my_ring = smem + warp * (kStages * kStageBytes);
+    uint4* xq = reinterpret_cast<uint4*>(smem + kRingBytes);                       // [kt][t][hi, lo]
+    float2* xmeta = reinterpret_cast<float2*>(smem + kRingBytes + (size_t)kt_total * 128);  // [kt][t] {2^E, sum}
+
+    const int units = p.row_tiles * p.si;
+    const int u_lo = (int)(((long long)blockIdx.x * units) / gridDim.x);
+    const int u_hi = (int)(((long long)(blockIdx.x + 1) * units) / gridDim.x);
+    auto open_unit = [&](UnitCursor& c) {
+        if (c.u < c.u_end) {
+            c.rt = c.u / p.si;
+            const int s = c.u - c.rt * p.si;
+            c.st = (s * p.kt4_total) / p.si;
+            c.st_end = ((s + 1) * p.kt4_total) / p.si;
+        }
+    };
+    UnitCursor ic{u_lo + warp, u_hi, 0, 0, 0};
+    open_unit(ic);
+    auto issue = [&](int slot) {
+        while (ic.u < ic.u_end && ic.st >= ic.st_end) { ic.u += kWarps; open_unit(ic); }
+        if (ic.u < ic.u_end) {
+            unsigned char* dst = my_ring + slot * kStageBytes;
+            const uint4* src = p.tiles + ((size_t)ic.rt * p.kt4_total + ic.st) * 128;
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
+            for (int q = 0; q < 4; ++q) cp_async16(dst + (q * 32 + lane) * 16, src + q * 32 + lane);
+            if (lane < 16) cp_async16(dst + 2048 + lane * 16, p.sb + ((size_t)ic.rt * p.kt4_total + ic.st) * 16 + lane);
+            ic.st += 1;
+        }
+        cp_async_commit();
+    };
+    // Weights do not depend on the preceding kernel: the ring starts filling before its results are awaited.
+    pdl_launch_dependents();
+    int issued = 0, consumed = 0;
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const int col = 8 * nt + 2 * t + e;
-            if (col >= p.m) continue;
-            if (EPI == QGEMV_EPI_STORE) {
+    for (int i = 0; i < kStages - 1; ++i) { issue(issued % kStages); ++issued; }
+    pdl_wait();
+
+    // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
+    for (int run = tid; run < kt_total * 4; run += kThreads) {
+        const int k0 = run * 16;
+        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+        if (k0 < p.k) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + k0);
+            v0 = __ldg(src);
+            v1 = __ldg(src + 1);
+        }
+        const unsigned w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        unsigned mx = 0;
 #pragma unroll
-                for (int hi = 0; hi < 2; ++hi) {
-                    const int r = rt * 16 + g + 8 * hi;
-                    const __nv_bfloat16 val = __float2bfloat16_rn(tot[nt][2 * hi + e]);
-                    if (r < p.seg_end[0]) p.y[0][(size_t)col * p.y_stride[0] + r] = val;
-                    else if (r < p.seg_end[1]) p.y[1][(size_t)col * p.y_stride[1] + (r - p.seg_end[0])] = val;
-                    else if (r < p.seg_end[2]) p.y[2][(size_t)col * p.y_stride[2] + (r - p.seg_end[1])] = val;
+        for (int i = 0; i < 8; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+        const int e = (int)(mx >> 7);  // biased exponent of the largest magnitude
+        const bool live = e >= 16 && e < 255;
+        // largest magnitude -> [2^14, 2^15): multiply by 2^(141 - e)
+        const float mul = live ? __uint_as_float((unsigned)(268 - e) << 23) : 0.f;
+        int q[16];
+        int sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            q[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * mul);
+            q[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * mul);
+            sum += q[2 * i] + q[2 * i + 1];
+        }
+        // byte order inside a 4-element step matches the nibble order of a weight word: 0, 2, 1, 3
+        unsigned hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int a = q[4 * j], b = q[4 * j + 2], c = q[4 * j + 1], d = q[4 * j + 3];
+            hi[j] = ((unsigned)(a >> 8) & 0xFFu) | (((unsigned)(b >> 8) & 0xFFu) << 8) | (((unsigned)(c >> 8) & 0xFFu) << 16) | (((unsigned)(d >> 8) & 0xFFu) << 24);
+            lo[j] = ((unsigned)a & 0xFFu) | (((unsigned)b & 0xFFu) << 8) | (((unsigned)c & 0xFFu) << 16) | (((unsigned)d & 0xFFu) << 24);
+        }
+        xq[run * 2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        xq[run * 2 + 1] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        const float scale = live ? __uint_as_float((unsigned)(e - 14) << 23) : 0.f;  // 2^(e - 141) = 1 / mul
+        xmeta[run] = make_float2(scale, (float)sum * scale);
+    }
+    __syncthreads();
+
+    const int s_total = p.si;
+    UnitCursor cc{u_lo + warp, u_hi, 0, 0, 0};
+    for (; cc.u < cc.u_end; cc.u += kWarps) {
+        open_unit(cc);
+        const int rt = cc.rt;
+        float tot_lo = 0.f, tot_hi = 0.f;
+        for (int stg = cc.st; stg < cc.st_end; ++stg) {
+            issue(issued % kStages); ++issued;
+            cp_async_wait<kStages - 1>();
+            __syncwarp();
+            const unsigned char* st = my_ring + (consumed % kStages) * kStageBytes;
+            ++consumed;
+            const uint4* wsm = reinterpret_cast<const uint4*>(st) + lane;
+            const uint4 sA = reinterpret_cast<const uint4*>(st + 2048)[g];
+            const uint4 sB = reinterpret_cast<const uint4*>(st + 2048)[g + 8];
+            const unsigned sAw[4] = {sA.x, sA.y, sA.z, sA.w};
+            const unsigned sBw[4] = {sB.x, sB.y, sB.z, sB.w};
+            const uint4* xrun = xq + ((size_t)stg * 16 + t) * 2;
+            const float2* mrun = xmeta + (size_t)stg * 16 + t;
+#pragma unroll
+            for (int ti = 0; ti < 4; ++ti) {
+                const uint4 wv = wsm[ti * 32];
+                const uint4 xh = xrun[ti * 8], xl = xrun[ti * 8 + 1];
+                const float2 meta = mrun[ti * 4];
+                const unsigned wr[4] = {wv.x, wv.y, wv.z, wv.w};
+                const unsigned xhw[4] = {xh.x, xh.y, xh.z, xh.w};
+                const unsigned xlw[4] = {xl.x, xl.y, xl.z, xl.w};
+                int ah = 0, al = 0, bh = 0, bl = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned a = wr[j] & 0x0F0F0F0Fu;          // four weights of row g
+                    const unsigned b = (wr[j] >> 4) & 0x0F0F0F0Fu;   // four weights of row g + 8
+                    ah = dp4a_us(a, xhw[j], ah);
+                    al = dp4a_uu(a, xlw[j], al);
+                    bh = dp4a_us(b, xhw[j], bh);
+                    bl = dp4a_uu(b, xlw[j], bl);
                 }
-            } else {
-                // rows 0-7 of the tile are gate rows, rows 8-15 the matching up rows; both are rounded to
-                // bf16 first because the reference stores them to bf16 scratch before `swiglu` reads them
-                // (Primitives/ElementwiseFragment.swift:49-54).
-                const int r = rt * 8 + g;
-                if (r < p.seg_end[0]) {
-                    const float gate = __bfloat162float(__float2bfloat16_rn(tot[nt][e]));
-                    const float up = __bfloat162float(__float2bfloat16_rn(tot[nt][2 + e]));
-                    const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
-                    p.y[0][(size_t)col * p.y_stride[0] + r] = __float2bfloat16_rn(act);
-                }
+                const float fa = (float)(ah * 256 + al), fb = (float)(bh * 256 + bl);
+                const float s_lo = sb_scale<F16SB>(sAw[ti]) * meta.x, z_lo = sb_zero<F16SB>(sAw[ti]);
+                const float s_hi = sb_scale<F16SB>(sBw[ti]) * meta.x, z_hi = sb_zero<F16SB>(sBw[ti]);
+                tot_lo = fmaf(s_lo, fa, fmaf(z_lo, meta.y, tot_lo));
+                tot_hi = fmaf(s_hi, fb, fmaf(z_hi, meta.y, tot_hi));
+            }
+            __syncwarp();
+        }
+        // the four lanes of a row hold the four quarters of every group
+        tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 1);
+        tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 2);
+        tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 1);
+        tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 2);
+
+        if (s_total > 1) {
+            const int s_glob = cc.u - rt * p.si;
+            float* dst = p.partial + ((size_t)rt * s_total + s_glob) * 16;
+            if (t == 0) { __stcg(dst + g, tot_lo); __stcg(dst + g + 8, tot_hi); }
+            __threadfence();
+            __syncwarp();
+            unsigned prev = 0;
+            if (lane == 0) prev = atomicAdd(p.counters + rt, 1u);
+            prev = __shfl_sync(0xffffffffu, prev, 0);
+            if (prev != (unsigned)s_total - 1u) continue;
+            __threadfence();
+            if (lane == 0) p.counters[rt] = 0u;
+            tot_lo = tot_hi = 0.f;
+            for (int s = 0; s < s_total; ++s) {  // slice order: independent of arrival order
+                const float* src = p.partial + ((size_t)rt * s_total + s) * 16;
+                tot_lo += __ldcg(src + g);
+                tot_hi += __ldcg(src + g + 8);
+            }
+        }
+        if (t != 0) continue;
+        if (EPI == QGEMV_EPI_STORE) {
+#pragma unroll
+            for (int hi = 0; hi < 2; ++hi) {
+                const int r = rt * 16 + g + 8 * hi;
+                const __nv_bfloat16 val = __float2bfloat16_rn(hi ? tot_hi : tot_lo);
+                if (r < p.seg_end[0]) p.y[0][r] = val;
+                else if (r < p.seg_end[1]) p.y[1][r - p.seg_end[0]] = val;
+                else if (r < p.seg_end[2]) p.y[2][r - p.seg_end[1]] = val;
+            }
+        } else {
+            // gate rows 0-7, matching up rows 8-15; both rounded to bf16 first, as the reference stores them
+            // to bf16 scratch before `swiglu` reads them (Primitives/ElementwiseFragment.swift:49-54)
+            const int r = rt * 8 + g;
+            if (r < p.seg_end[0]) {
+                const float gate = __bfloat162float(__float2bfloat16_rn(tot_lo));
+                const float up = __bfloat162float(__float2bfloat16_rn(tot_hi));
+                p.y[0][r] = __float2bfloat16_rn(gate * (1.0f / (1.0f + expf(-gate))) * up);
             }
         }
     }
+    cp_async_wait<0>();
 }
 
 struct QGemvConfig {
-    int nt, rw, sw, sk;
+    int nt, si, sk, occ;
     dim3 grid;
     size_t smem;
 };
 
+constexpr int kSMs = 148;
+
+size_t x_smem_bytes(int rows_x, int cols, int kt4, int sk) {
+    const int nk = 256 * ((kt4 + sk - 1) / sk);
+    return (size_t)rows_x * (nk + kXPad) * 2 + (size_t)(nk / 64) * cols * 4;
+}
+
+// Persistent grid: at most occ CTAs per SM, all resident at once; work is cut into (row tile, k-slice)
+// units small enough that every SM streams the same number of bytes to within a few percent.
 QGemvConfig pick_config(const Q4Tiled& w, int m) {
     QGemvConfig c{};
+    if (m == 1) {
+        // integer dot-product kernel: the whole activation vector in block floating point (2 bytes + 1/8 byte
+        // of metadata per element), one CTA group
+        const int kt4 = w.kt_pad / 4;
+        c.nt = 0; c.sk = 1;
+        c.smem = (size_t)kRingBytes + (size_t)w.kt_pad * 160;
+        c.occ = std::max(1, std::min(3, (int)((227 * 1024) / (c.smem + 1024))));
+        c.si = 1;
+        while (c.si < 16 && c.si * 4 <= kt4 && (long long)w.row_tiles * c.si < 16LL * kSMs) c.si *= 2;
+        const int units = w.row_tiles * c.si;
+        c.grid = dim3((unsigned)std::min(kSMs * c.occ, (units + kWarps - 1) / kWarps), 1, 1);
+        return c;
+    }
     c.nt = m <= 8 ? 1 : 2;
     const int cols = 8 * c.nt;
     const int rows_x = std::min(m, cols);
     const int kt4 = w.kt_pad / 4;
-    // cross-CTA split until the x slice fits in shared memory
-    c.sk = 1;
-    while ((size_t)rows_x * ((size_t)256 * ((kt4 + c.sk - 1) / c.sk) + kXPad) * 2 > (size_t)kMaxXBytes && c.sk < kt4) ++c.sk;
-    const int kt4_cta = std::max(1, kt4 / c.sk);
-    // in-CTA split: enough warps to cover two resident CTAs on each of the 148 SMs
-    c.sw = 1;
-    while (c.sw < kWarps && (long long)w.row_tiles * c.sw * c.sk < 8LL * 296 && kt4_cta / (c.sw * 2) >= 1) c.sw *= 2;
-    c.rw = kWarps / c.sw;
-    c.grid = dim3((unsigned)((w.row_tiles + c.rw - 1) / c.rw), (unsigned)c.sk, 1);
-    const int nk_cta_max = 256 * ((kt4 + c.sk - 1) / c.sk);
-    c.smem = (size_t)kRingBytes + (size_t)rows_x * (nk_cta_max + kXPad) * 2 + (size_t)(nk_cta_max / 64) * cols * 4;
+    const int max_occ = c.nt == 1 ? 3 : 2;
+    const size_t sm_budget = 227 * 1024;
+    // highest occupancy whose shared-memory share holds the ring plus this group's slice of x;
+    // a second (or further) CTA group along K only when x does not fit otherwise
+    c.occ = 1; c.sk = kt4;
+    bool found = false;
+    for (int sk = 1; sk <= kt4 && !found; sk *= 2)
+        for (int occ = max_occ; occ >= 1 && !found; --occ) {
+            const size_t per_cta = sm_budget / occ - 1024;
+            if ((size_t)kRingBytes + x_smem_bytes(rows_x, cols, kt4, sk) <= per_cta) { c.occ = occ; c.sk = sk; found = true; }
+        }
+    c.sk = std::min(c.sk, kt4);
+    const int glen = std::max(1, kt4 / c.sk);
+    // k-slices per group: aim at >= 16 units per SM, never shorter than two stages (4.6 KB)
+    c.si = 1;
+    while (c.si < 16 && c.si * 4 <= glen && (long long)w.row_tiles * c.si * c.sk < 16LL * kSMs) c.si *= 2;
+    const int units = w.row_tiles * c.si;
+    int gx = std::max(1, (kSMs * c.occ) / c.sk);
+    gx = std::min(gx, (units + kWarps - 1) / kWarps);
+    c.grid = dim3((unsigned)gx, (unsigned)c.sk, 1);
+    c.smem = (size_t)kRingBytes + x_smem_bytes(rows_x, cols, kt4, c.sk);
     return c;
+}
+
+template <int EPI>
+int launch_1(const QGemvParams& p, const QGemvConfig& c, cudaStream_t s) {
+    cudaError_t e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true>, c.grid, dim3(kThreads), c.smem, s, p)
+                             : launch_k(qgemv1_kernel<EPI, false>, c.grid, dim3(kThreads), c.smem, s, p);
+    if (e != cudaSuccess) return cuda_fail(e, "qgemv1 launch");
+    return SWLM_OK;
 }
 
 template <int NT, int EPI>
 int launch_t(const QGemvParams& p, const QGemvConfig& c, cudaStream_t s) {
-    qgemv_kernel<NT, EPI><<<c.grid, kThreads, c.smem, s>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = p.sb_f16 ? launch_k(qgemv_kernel<NT, EPI, true>, c.grid, dim3(kThreads), c.smem, s, p)
+                             : launch_k(qgemv_kernel<NT, EPI, false>, c.grid, dim3(kThreads), c.smem, s, p);
     if (e != cudaSuccess) return cuda_fail(e, "qgemv launch");
     return SWLM_OK;
 }
@@ -352,17 +660,25 @@ static int opt_in_smem(K kernel) {
 
 int qgemv_init() {
     int rc;
-    if ((rc = opt_in_smem(qgemv_kernel<1, 0>))) return rc;
-    if ((rc = opt_in_smem(qgemv_kernel<1, 1>))) return rc;
-    if ((rc = opt_in_smem(qgemv_kernel<2, 0>))) return rc;
-    if ((rc = opt_in_smem(qgemv_kernel<2, 1>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<1, 0, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<1, 1, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<2, 0, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<2, 1, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<1, 0, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<1, 1, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<2, 0, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv_kernel<2, 1, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<0, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<1, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<0, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<1, true>))) return rc;
     return SWLM_OK;
 }
 
 size_t qgemv_scratch_floats(const Q4Tiled& w, int m) {
     QGemvConfig c = pick_config(w, m);
-    if (c.sk <= 1) return 0;
-    return (size_t)w.row_tiles * c.sk * 16 * (8 * c.nt);
+    if (c.sk * c.si <= 1) return 0;
+    return (size_t)w.row_tiles * c.sk * c.si * 16 * (c.nt ? 8 * c.nt : 1);
 }
 int qgemv_counter_count(const Q4Tiled& w) { return w.row_tiles; }
 
@@ -375,7 +691,7 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
     }
     QGemvConfig c = pick_config(w, a.m);
     if (g_max_dyn_smem == 0 || c.smem > (size_t)g_max_dyn_smem) { set_error("qgemv: shared memory %zu exceeds the limit %d", c.smem, g_max_dyn_smem); return SWLM_ERR_INVALID; }
-    if (c.sk > 1 && (!a.partial || !a.counters)) { set_error("qgemv: split-K launch without scratch"); return SWLM_ERR_INVALID; }
+    if (c.sk * c.si > 1 && (!a.partial || !a.counters)) { set_error("qgemv: split launch without scratch"); return SWLM_ERR_INVALID; }
     QGemvParams p{};
     p.tiles = w.tiles; p.sb = w.sb; p.row_tiles = w.row_tiles; p.kt4_total = w.kt_pad / 4; p.sb_f16 = w.sb_f16 ? 1 : 0;
     p.x = a.x; p.x_stride = a.x_stride; p.k = w.k;
@@ -384,7 +700,8 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
         p.seg_end[i] = a.seg_end[i] > 0 ? a.seg_end[i] : (i ? p.seg_end[i - 1] : 0);
     }
     p.m = a.m;
-    p.rw = c.rw; p.sw = c.sw; p.sk = c.sk; p.partial = a.partial; p.counters = a.counters;
+    p.si = c.si; p.sk = c.sk; p.partial = a.partial; p.counters = a.counters;
+    if (c.nt == 0) return a.epilogue == QGEMV_EPI_SWIGLU ? launch_1<1>(p, c, s) : launch_1<0>(p, c, s);
     if (a.epilogue == QGEMV_EPI_SWIGLU) return c.nt == 1 ? launch_t<1, 1>(p, c, s) : launch_t<2, 1>(p, c, s);
     return c.nt == 1 ? launch_t<1, 0>(p, c, s) : launch_t<2, 0>(p, c, s);
 }
@@ -430,7 +747,7 @@ __global__ void repack_tiles_kernel(const RepackParams p) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int dest_row = rt * 16 + g + 8 * (e & 1);
-            const int col = kt * 64 + 16 * j + 2 * t + (e >> 2) + 8 * ((e >> 1) & 1);
+            const int col = kt * 64 + 16 * t + 4 * j + (e >> 2) + 2 * ((e >> 1) & 1);
             int which, row;
             if (repack_source_row(p, dest_row, which, row)) {
                 const unsigned word = p.src[which].w[(size_t)row * (p.k / 8) + (col >> 3)];
@@ -466,8 +783,8 @@ __global__ void untile_bf16_kernel(const uint4* tiles, const uint4* sb, int n, i
     const int row = (int)(idx / k), col = (int)(idx % k);
     (void)interleaved;
     const int rt = row >> 4, r = row & 15, kt = col >> 6, kk = col & 63;
-    const int j = kk >> 4, w16 = kk & 15;
-    const int t = (w16 & 7) >> 1, e = ((w16 & 1) << 2) | ((w16 >> 3) << 1) | (r >> 3), g = r & 7;
+    const int t = kk >> 4, j = (kk & 15) >> 2, sl = kk & 3;
+    const int e = ((sl & 1) << 2) | ((sl >> 1) << 1) | (r >> 3), g = r & 7;
     const unsigned word = reinterpret_cast<const unsigned*>(tiles)[(((size_t)rt * kt_pad + kt) * 32 + (g * 4 + t)) * 4 + j];
     const unsigned q = (word >> (4 * e)) & 0xFu;
     const unsigned pair = reinterpret_cast<const unsigned*>(sb)[(((size_t)rt * (kt_pad / 4) + (kt >> 2)) * 16 + r) * 4 + (kt & 3)];
@@ -479,6 +796,10 @@ __global__ void untile_bf16_kernel(const uint4* tiles, const uint4* sb, int n, i
 
 int launch_repack(const RepackSrc* src, int n_src, int mode, int k, const Q4Tiled& dst, cudaStream_t s) {
     if (n_src < 1 || n_src > 3 || (mode == 1 && n_src != 2)) { set_error("repack: bad source count"); return SWLM_ERR_INVALID; }
+    {   // an error left behind by an earlier, unrelated runtime call must not be blamed on this launch
+        cudaError_t stale = cudaGetLastError();
+        if (stale != cudaSuccess) { set_error("stale CUDA error %d (%s) found before the repack launch", (int)stale, cudaGetErrorString(stale)); return SWLM_ERR_CUDA; }
+    }
     RepackParams p{};
     for (int i = 0; i < n_src; ++i) p.src[i] = src[i];
     p.n_src = n_src; p.mode = mode; p.k = k; p.row_tiles = dst.row_tiles; p.kt_pad = dst.kt_pad;

@@ -10,6 +10,7 @@
 // the device, so consecutive greedy steps need no host round trip.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <algorithm>
 #include <cmath>
@@ -25,6 +26,10 @@ void set_error(const char* fmt, ...) {
     va_start(ap, fmt);
     vsnprintf(g_error, sizeof(g_error), fmt, ap);
     va_end(ap);
+}
+bool pdl_enabled() {
+    static const bool on = [] { const char* v = getenv("SWLM_NO_PDL"); return !(v && v[0] == '1'); }();
+    return on;
 }
 int cuda_fail(cudaError_t e, const char* what) {
     set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
@@ -46,6 +51,7 @@ struct swlm_ctx {
     std::map<std::string, DenseTensor> dense;
     int64_t bytes = 0;
     float* op_partial = nullptr; size_t op_partial_floats = 0;
+    unsigned* op_attn_counters = nullptr; size_t op_attn_counter_count = 0;
     unsigned* op_counters = nullptr; size_t op_counter_count = 0;
 };
 
@@ -378,6 +384,7 @@ struct swlm_state {
     int ring_cap = 4096;
     float* attn_scratch = nullptr; float* qgemv_partial = nullptr; unsigned* qgemv_counters = nullptr;
     size_t attn_scratch_cap = 0, qgemv_partial_cap = 0, qgemv_counters_cap = 0;
+    unsigned* attn_counters = nullptr;
     float* argmax_val = nullptr; int32_t* argmax_idx = nullptr;
     int32_t* h_tok = nullptr;  // pinned host staging, 2 * max_batch
     int pos_host = 0;
@@ -455,9 +462,9 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             a.vcache = s->vcache + (size_t)st.layer * s->kv_layer_elems;
             a.max_seq = d.max_seq; a.position = s->position;
             a.out = s->buf[st.out_buf]; a.out_stride = s->width[st.out_buf];
-            a.scratch = s->attn_scratch; a.splits = plan->attn_splits;
+            a.scratch = s->attn_scratch; a.counters = s->attn_counters; a.splits = plan->attn_splits;
             rc = launch_attn_decode(a, stream);
-            s->launches += 2;
+            s->launches += 1;
             break;
         }
         case L_SWIGLU:
@@ -508,7 +515,7 @@ int launches_per_step(const swlm_plan* plan, bool body_only) {
     for (const Launch& L : plan->launches) {
         if (body_only && (L.kind == L_ARGMAX || (L.kind == L_QGEMV && L.seg_buf[0] == SWLM_BUF_LOGITS) ||
                           (L.kind == L_RMSNORM && L.st.kind == SWLM_STEP_RESADD_RMSNORM))) continue;
-        n += (L.kind == L_ATTN || L.kind == L_ARGMAX) ? 2 : 1;
+        n += L.kind == L_ARGMAX ? 2 : 1;
         has_argmax |= L.kind == L_ARGMAX;
     }
     if (body_only || !has_argmax) n += 1;
@@ -635,6 +642,7 @@ void swlm_ctx_destroy(swlm_ctx* ctx) {
     for (auto& kv : ctx->dense) cudaFree(kv.second.data);
     cudaFree(ctx->op_partial);
     cudaFree(ctx->op_counters);
+    cudaFree(ctx->op_attn_counters);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -756,6 +764,11 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     if ((rc = dev_alloc(&s->token_out, d.max_batch))) return fail(rc);
     if ((rc = dev_alloc(&s->ring, (size_t)s->ring_cap * d.max_batch))) return fail(rc);
     if ((rc = grow_scratch(s, plan->attn_scratch, plan->qgemv_partial, plan->qgemv_counters))) return fail(rc);
+    if ((rc = dev_alloc(&s->attn_counters, (size_t)d.max_batch * std::max(1, d.kv_heads)))) return fail(rc);
+    {
+        cudaError_t ce = cudaMemset(s->attn_counters, 0, (size_t)d.max_batch * std::max(1, d.kv_heads) * sizeof(unsigned));
+        if (ce != cudaSuccess) return fail(cuda_fail(ce, "cudaMemset"));
+    }
     if ((rc = dev_alloc(&s->argmax_val, argmax_scratch_elems(d.max_batch)))) return fail(rc);
     if ((rc = dev_alloc(&s->argmax_idx, argmax_scratch_elems(d.max_batch)))) return fail(rc);
     e = cudaMallocHost((void**)&s->h_tok, sizeof(int32_t) * 2 * d.max_batch);
@@ -775,7 +788,7 @@ void swlm_state_destroy(swlm_state* s) {
     cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->conv);
     cudaFree(s->position); cudaFree(s->step_counter); cudaFree(s->token_in); cudaFree(s->token_out); cudaFree(s->ring);
     cudaFree(s->prompt);
-    cudaFree(s->attn_scratch); cudaFree(s->qgemv_partial); cudaFree(s->qgemv_counters);
+    cudaFree(s->attn_scratch); cudaFree(s->qgemv_partial); cudaFree(s->qgemv_counters); cudaFree(s->attn_counters);
     cudaFree(s->argmax_val); cudaFree(s->argmax_idx);
     if (s->h_tok) cudaFreeHost(s->h_tok);
     if (s->own_stream) cudaStreamDestroy(s->own_stream);
@@ -1163,9 +1176,18 @@ int swlm_op_flash_decode_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int 
     int rc = ensure_device(ctx);
     if (rc) return rc;
     cudaStream_t stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->stream;
+    const size_t need = (size_t)b * kv_heads;
+    if (need > ctx->op_attn_counter_count) {
+        SWLM_CUDA(cudaDeviceSynchronize());
+        cudaFree(ctx->op_attn_counters);
+        ctx->op_attn_counters = nullptr; ctx->op_attn_counter_count = 0;
+        if ((rc = dev_alloc(&ctx->op_attn_counters, need))) return rc;
+        SWLM_CUDA(cudaMemset(ctx->op_attn_counters, 0, need * sizeof(unsigned)));
+        ctx->op_attn_counter_count = need;
+    }
     return launch_flash_decode_plain(b, heads, kv_heads, hd, ctx_len, ctx_stride, scale, static_cast<const __nv_bfloat16*>(q_dev),
                                      static_cast<const __nv_bfloat16*>(k_dev), static_cast<const __nv_bfloat16*>(v_dev),
-                                     static_cast<__nv_bfloat16*>(out_dev), static_cast<float*>(scratch_dev),
+                                     static_cast<__nv_bfloat16*>(out_dev), static_cast<float*>(scratch_dev), ctx->op_attn_counters,
                                      flash_splits(b, kv_heads, ctx_len), stream);
 }
 

@@ -24,13 +24,38 @@ int cuda_fail(cudaError_t e, const char* what);  // records the message, returns
         if (e__ != cudaSuccess) return ::swlm::cuda_fail(e__, #call); \
     } while (0)
 
+// ---- launches ------------------------------------------------------------------
+// Every kernel of the decode step is launched with programmatic stream serialization (programmatic
+// dependent launch): a kernel may start while its predecessor drains, does what does not depend on it
+// (the GEMV kernels start streaming weights), and executes `griddepcontrol.wait` before it touches
+// anything the predecessor wrote. SWLM_NO_PDL=1 in the environment turns the attribute off.
+bool pdl_enabled();
+template <typename... P, typename... A>
+inline cudaError_t launch_k(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, A... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+#ifdef __CUDACC__
+// Wait until the preceding kernel in the stream has completed and its writes are visible.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Allow the next kernel in the stream to begin launching.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 // ---- device tensors -----------------------------------------------------------
 //
 // Q4 group-64 tensor in the streaming layout of the GEMV/GEMM kernels.
 //   tiles : uint4[row_tiles][kt_pad][32]   one 512-byte tile = 16 rows x 64 columns,
 //           lane (g = lane>>2, t = lane&3) owns 16 bytes = 4 words; word j, nibble e holds
-//           W[16*rt + g + 8*(e&1)][64*kt + 16*j + 2*t + (e>>2) + 8*((e>>1)&1)],
-//           which is the A-fragment order of mma.m16n8k16 for k-step j.
+//           W[16*rt + g + 8*(e&1)][64*kt + 16*t + 4*j + (e>>2) + 2*((e>>1)&1)]:
+//           the A-fragment order of mma.m16n8k16 for k-step j, with the group's columns assigned to
+//           k-steps so that lane t's B fragments are the 16 consecutive activations 16t..16t+15.
 //   sb    : uint4[row_tiles][kt_pad/4][16]  per row, four consecutive groups' (scale, zero)
 //           pairs, each pair two 16-bit floats (bf16, or fp16 when the source was STAF).
 // kt_pad = K/64 rounded up to a multiple of 4; padding tiles hold q = 0, scale = zero = 0.
@@ -131,6 +156,7 @@ struct AttnLaunch {
     const int32_t* position = nullptr;  // device scalar: index of the new token
     __nv_bfloat16* out = nullptr; int out_stride = 0;
     float* scratch = nullptr;   // attn_scratch_floats()
+    unsigned* counters = nullptr;  // m * kv_heads arrival counters, zero between launches
     int splits = 1;             // KV splits per (sequence, kv head)
 };
 int attn_pick_splits(int m, int kv_heads, int max_ctx);
@@ -140,7 +166,7 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s);
 // generic flash-decode over an existing cache (q already rotated), ctx_len fixed on the host.
 int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, float scale,
                               const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
-                              __nv_bfloat16* out, float* scratch, int splits, cudaStream_t s);
+                              __nv_bfloat16* out, float* scratch, unsigned* counters, int splits, cudaStream_t s);
 int attn_init();
 
 int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s);
