@@ -353,7 +353,7 @@ def main():
 
     weight_bytes = cfg.q4_weight_elems() * 0.5625 / world            # per GPU, per step
     kv_bytes = cfg.kv_layer_count * (cfg.kv_heads // world) * cfg.head_dim * 2 * 2 * model.position
-    n_gemv = sum(1 for l in model.describe().splitlines() if " qgemv" in l)
+    n_gemv = sum(1 for l in model.describe().splitlines() if "qgemv" in l)
     peak, peak_src = measured_peaks()
     achieved = weight_bytes / (gemv_ms * 1e-3) / 1e9
     roofline = {

@@ -320,23 +320,46 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         }
         __syncthreads();
     }
-    for (int idx = tid; idx < G * HD; idx += kSplitThreads) {
-        const int r = idx / HD, d = idx - r * HD;
-        const size_t base = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits;
+    // weights of the splits, all (head, split) pairs in parallel: w = 2^(m_s - max), normalised by the
+    // total mass; kept in shared memory so that the output loop below issues independent loads only
+    float* wsm = &osm[1][0][0];            // [G][splits] weights (splits <= 64: fits the reused buffer)
+    float* msm2 = &osm[2][0][0];           // [G][splits] split maxima
+    float* lsm2 = &osm[3][0][0];           // [G][splits] split sums
+    for (int idx = tid; idx < G * p.splits; idx += kSplitThreads) {
+        const int r = idx / p.splits, sidx = idx - r * p.splits;
+        const size_t slot = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits + sidx;
+        msm2[idx] = __ldcg(p.part_ml + slot * 2);
+        lsm2[idx] = __ldcg(p.part_ml + slot * 2 + 1);
+    }
+    __syncthreads();
+    float* inv_den = msm[0];  // reuse: G floats
+    float* w_self = msm[1];
+    for (int r = warp; r < G; r += kSplitWarps) {
         const float m_self = DECODE ? self_score[r] : -INFINITY;
         float mx = m_self;
-        for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(p.part_ml + (base + s) * 2));
-        float num = 0.f, den = 0.f;
-        if (DECODE) { const float w = exp2f(m_self - mx); num = w * vnew[d]; den = w; }
-        for (int s = 0; s < p.splits; ++s) {
-            const float ms = __ldcg(p.part_ml + (base + s) * 2);
-            if (ms == -INFINITY) continue;
-            const float w = exp2f(ms - mx);
-            num = fmaf(w, __ldcg(p.part_o + (base + s) * HD + d), num);
-            den = fmaf(w, __ldcg(p.part_ml + (base + s) * 2 + 1), den);
+        for (int sidx = lane; sidx < p.splits; sidx += 32) mx = fmaxf(mx, msm2[r * p.splits + sidx]);
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float den = 0.f;
+        for (int sidx = lane; sidx < p.splits; sidx += 32) {
+            const float ms = msm2[r * p.splits + sidx];
+            const float w = ms == -INFINITY ? 0.f : exp2f(ms - mx);
+            wsm[r * p.splits + sidx] = w;
+            den = fmaf(w, lsm2[r * p.splits + sidx], den);
         }
-        const float inv = den > 0.f ? 1.0f / den : 0.f;
-        p.out[(size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(num * inv);
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        const float ws = DECODE ? exp2f(m_self - mx) : 0.f;
+        den += ws;
+        if (lane == 0) { inv_den[r] = den > 0.f ? 1.0f / den : 0.f; w_self[r] = ws; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += kSplitThreads) {
+        const int r = idx / HD, d = idx - r * HD;
+        const float* po = p.part_o + (((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits) * HD + d;
+        const float* wr = wsm + r * p.splits;
+        float num = DECODE ? w_self[r] * vnew[d] : 0.f;
+#pragma unroll 8
+        for (int sidx = 0; sidx < p.splits; ++sidx) num = fmaf(wr[sidx], __ldcg(po + (size_t)sidx * HD), num);
+        p.out[(size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(num * inv_den[r]);
     }
 }
 

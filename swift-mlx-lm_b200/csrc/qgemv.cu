@@ -49,6 +49,13 @@ struct QGemvParams {
     int si, sk;   // k-slices per CTA group, CTA groups along K
     float* partial;
     unsigned* counters;
+    // optional fused residual-add / copy / RMSNorm in front of the product (norm_mode = step kind, 0 = none)
+    int norm_mode;
+    const __nv_bfloat16* res_in;
+    __nv_bfloat16* res_out;
+    int res_stride;
+    const __nv_bfloat16* norm_w;
+    float eps, weight_bias;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -86,6 +93,70 @@ __device__ __forceinline__ float sb_scale(unsigned pair) {
 template <bool F16SB>
 __device__ __forceinline__ float sb_zero(unsigned pair) {
     return F16SB ? __half2float(__ushort_as_half((unsigned short)(pair >> 16))) : __uint_as_float(pair & 0xFFFF0000u);
+}
+
+
+// Fused fused_copy_rms_norm / fused_residual_add_copy_rms_norm / fused_residual_add_rms_norm
+// (Primitives/Reduction.swift:74-115 with CopyFragment / ResidualAddFragment,
+// Compiler/MetalEntryCollector.swift:143-218) as the prologue of the product that consumes it.
+// Every thread owns the run of 16 elements k0..k0+15 of row `b` (dimension <= 4096): h = in (+ residual)
+// in fp32, residual_out = bf16(h) (written by one CTA only), then bf16(h * rsqrt(mean(h^2)+eps) * (w+bias))
+// returned as eight packed bf16 pairs. The norm sees the unrounded sum, as the reference's fused kernel does.
+// res_in and res_out are different buffers: other CTAs read res_in while one writes res_out.
+__device__ __forceinline__ void fused_norm_run(const QGemvParams& p, int b, int k0, bool in_range, bool writer,
+                                               float* red, unsigned (&w)[8]) {
+    float h[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) h[i] = 0.f;
+    if (in_range) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)b * p.x_stride + k0);
+        const uint4 v0 = __ldcg(src), v1 = __ldcg(src + 1);
+        const unsigned vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { h[2 * i] = __uint_as_float(vw[i] << 16); h[2 * i + 1] = __uint_as_float(vw[i] & 0xFFFF0000u); }
+        if (p.norm_mode != SWLM_STEP_COPY_RMSNORM) {
+            const uint4* rs = reinterpret_cast<const uint4*>(p.res_in + (size_t)b * p.res_stride + k0);
+            const uint4 r0 = __ldcg(rs), r1 = __ldcg(rs + 1);
+            const unsigned rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { h[2 * i] += __uint_as_float(rw[i] << 16); h[2 * i + 1] += __uint_as_float(rw[i] & 0xFFFF0000u); }
+        }
+        if (writer && p.norm_mode != SWLM_STEP_RESADD_RMSNORM) {
+            unsigned o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __nv_bfloat162 v = __floats2bfloat162_rn(h[2 * i], h[2 * i + 1]);
+                o[i] = *reinterpret_cast<const unsigned*>(&v);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(p.res_out + (size_t)b * p.res_stride + k0);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) ss = fmaf(h[i], h[i], ss);
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __syncthreads();  // red may still be read from the previous row
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) total += red[i];
+    const float rs = rsqrtf(total / (float)p.k + p.eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = 0u;
+    if (in_range) {
+        const uint4* ws = reinterpret_cast<const uint4*>(p.norm_w + k0);
+        const uint4 n0 = __ldg(ws), n1 = __ldg(ws + 1);
+        const unsigned nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const __nv_bfloat162 v = __floats2bfloat162_rn(h[2 * i] * rs * (__uint_as_float(nw[i] << 16) + p.weight_bias),
+                                                           h[2 * i + 1] * rs * (__uint_as_float(nw[i] & 0xFFFF0000u) + p.weight_bias));
+            w[i] = *reinterpret_cast<const unsigned*>(&v);
+        }
+    }
 }
 
 // One unit of work = (row tile rt, k-slice s): 16 output rows x a contiguous run of stages.
@@ -152,7 +223,21 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
     pdl_wait();
     // ---- x: asynchronous copy in its natural order (the tile layout was chosen so that lane t's B
     // fragments of a group are the 16 consecutive elements 16t..16t+15)-------------------------------
-    {
+    __shared__ float red[kWarps];
+    if (p.norm_mode) {
+        // fused norm (dimension <= 4096, one CTA group): thread tid owns run tid of every row
+        for (int b = 0; b < rows_x; ++b) {
+            unsigned w[8];
+            const int k0 = tid * 16;
+            fused_norm_run(p, b, k0, k0 < p.k, blockIdx.x == 0, red, w);
+            if (k0 < nk_cta) {
+                uint4* dst = reinterpret_cast<uint4*>(xsm + (size_t)b * xs_stride + k0);
+                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+        }
+        cp_async_commit();
+    } else {
         const int chunks_per_row = nk_cta / 8;
         const int total = rows_x * chunks_per_row;
         for (int idx = tid; idx < total; idx += kThreads) {
@@ -434,15 +519,23 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
     pdl_wait();
 
     // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
-    for (int run = tid; run < kt_total * 4; run += kThreads) {
+    __shared__ float red[kWarps];
+    for (int run = tid; run < kt_total * 4 || (p.norm_mode && run < kThreads); run += kThreads) {
         const int k0 = run * 16;
-        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
-        if (k0 < p.k) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.x + k0);
-            v0 = __ldg(src);
-            v1 = __ldg(src + 1);
+        unsigned w[8];
+        if (p.norm_mode) {
+            // dimension <= 4096: exactly one pass, every thread takes part in the block-wide sum
+            fused_norm_run(p, 0, k0, k0 < p.k, blockIdx.x == 0, red, w);
+            if (run >= kt_total * 4) continue;
+        } else {
+            uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+            if (k0 < p.k) {
+                const uint4* src = reinterpret_cast<const uint4*>(p.x + k0);
+                v0 = __ldg(src);
+                v1 = __ldg(src + 1);
+            }
+            w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w; w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
         }
-        const unsigned w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
         unsigned mx = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
@@ -701,6 +794,15 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
     }
     p.m = a.m;
     p.si = c.si; p.sk = c.sk; p.partial = a.partial; p.counters = a.counters;
+    p.norm_mode = a.norm.mode;
+    if (a.norm.mode) {
+        if (w.k > 4096 || (w.k & 15) || c.sk != 1 || !a.norm.weight || a.norm.res_in == a.norm.res_out) {
+            set_error("qgemv: fused norm needs k <= 4096, k %% 16 == 0 and distinct residual buffers");
+            return SWLM_ERR_INVALID;
+        }
+        p.res_in = a.norm.res_in; p.res_out = a.norm.res_out; p.res_stride = a.norm.res_stride;
+        p.norm_w = a.norm.weight; p.eps = a.norm.eps; p.weight_bias = a.norm.weight_bias;
+    }
     if (c.nt == 0) return a.epilogue == QGEMV_EPI_SWIGLU ? launch_1<1>(p, c, s) : launch_1<0>(p, c, s);
     if (a.epilogue == QGEMV_EPI_SWIGLU) return c.nt == 1 ? launch_t<1, 1>(p, c, s) : launch_t<2, 1>(p, c, s);
     return c.nt == 1 ? launch_t<1, 0>(p, c, s) : launch_t<2, 0>(p, c, s);

@@ -203,6 +203,11 @@ struct Launch {
     int rope_table = -1;       // index into plan->rope_tables
     std::string label;
     int steps_covered = 1;
+    // residual add / copy / RMSNorm folded into this product's prologue (norm.kind == 0: none)
+    swlm_step norm{};
+    const DenseTensor* norm_w = nullptr;
+    int x_buf = -1;            // buffer the product reads (the norm's input when fused)
+    int res_in = 0, res_out = 0;  // physical residual buffers (0 or 1) this launch reads / writes
 };
 
 struct RopeTable { int rope_dim; float base; float* inv_freq; };
@@ -217,6 +222,7 @@ struct swlm_plan {
     std::vector<RopeTable> rope_tables;
     int attn_splits = 1;
     size_t attn_scratch = 0, qgemv_partial = 0, qgemv_counters = 0;
+    int final_res = 0;  // physical residual buffer that holds the residual stream after a step
 };
 
 namespace {
@@ -363,6 +369,61 @@ int compile_plan(swlm_plan* plan) {
         plan->launches.push_back(L);
     }
     plan->attn_splits = attn_pick_splits(m, std::max(1, d.kv_heads / std::max(1, ctx->tp_size)), d.max_seq);
+
+    // A gate/up launch with the SwiGLU epilogue writes while other CTAs may still be reading its input:
+    // when both are the same buffer, send the result to scratch slot 4 and point the readers there.
+    {
+        int from = -1, to = -1;
+        for (Launch& L : plan->launches) {
+            auto redirect = [&](int& b) { if (from >= 0 && b == from) b = to; };
+            redirect(L.st.in_buf); redirect(L.st.in2_buf); redirect(L.st.in3_buf);
+            bool writes = L.st.out_buf == from;
+            for (int q = 0; q < L.n_seg; ++q) writes |= L.seg_buf[q] == from;
+            if (L.kind == L_QGEMV && L.epilogue == QGEMV_EPI_SWIGLU && L.seg_buf[0] == L.st.in_buf) {
+                from = L.seg_buf[0]; to = SWLM_BUF_SCRATCH4;
+                L.seg_buf[0] = to;
+            } else if (writes && L.kind != L_QK_NORM) {
+                from = to = -1;  // the original buffer holds fresh data again
+            }
+        }
+    }
+
+    // Fold each norm into the product that consumes it: the product's CTAs recompute the (tiny) norm in
+    // their prologue instead of waiting for a separate launch. Conditions: dimension <= 4096, the product is
+    // the very next launch and the only reader of the norm's output.
+    const char* no_fuse = getenv("SWLM_NO_NORM_FUSION");
+    for (size_t i = 0; i + 1 < plan->launches.size() && !(no_fuse && no_fuse[0] == '1'); ++i) {
+        Launch& A = plan->launches[i];
+        Launch& B = plan->launches[i + 1];
+        if (A.kind != L_RMSNORM || B.kind != L_QGEMV) continue;
+        if (B.st.in_buf != A.st.out_buf || B.w->k != A.st.n || A.st.n > 4096 || (A.st.n & 15)) continue;
+        bool ok = true;
+        for (int q = 0; q < B.n_seg; ++q) ok &= B.seg_buf[q] != A.st.in_buf && B.seg_buf[q] != SWLM_BUF_RESIDUAL;
+        for (size_t j = i + 2; j < plan->launches.size() && ok; ++j) {
+            const Launch& C = plan->launches[j];
+            if (C.st.in_buf == A.st.out_buf || C.st.in2_buf == A.st.out_buf || C.st.in3_buf == A.st.out_buf) ok = false;
+            bool writes = C.st.out_buf == A.st.out_buf;
+            for (int q = 0; q < C.n_seg; ++q) writes |= C.seg_buf[q] == A.st.out_buf;
+            if (writes) break;
+        }
+        if (!ok) continue;
+        B.norm = A.st;
+        B.norm_w = A.d1;
+        B.x_buf = A.st.in_buf;
+        B.label = "rmsnorm+" + B.label;
+        B.steps_covered += 1;
+        plan->launches.erase(plan->launches.begin() + i);
+    }
+    // residual ping-pong: a fused norm reads one physical residual buffer and writes the other
+    int cur = 0;
+    for (Launch& L : plan->launches) {
+        L.res_in = L.res_out = cur;
+        if (L.kind == L_QGEMV && L.norm.kind) {
+            L.res_out = 1 - cur;
+            if (L.norm.kind != SWLM_STEP_RESADD_RMSNORM) cur = 1 - cur;
+        }
+    }
+    plan->final_res = cur;
     return SWLM_OK;
 }
 
@@ -386,6 +447,7 @@ struct swlm_state {
     size_t attn_scratch_cap = 0, qgemv_partial_cap = 0, qgemv_counters_cap = 0;
     unsigned* attn_counters = nullptr;
     float* argmax_val = nullptr; int32_t* argmax_idx = nullptr;
+    __nv_bfloat16* res2 = nullptr;  // second physical residual buffer (ping-pong partner of buf[RESIDUAL])
     int32_t* h_tok = nullptr;  // pinned host staging, 2 * max_batch
     int pos_host = 0;
     long long steps_host = 0;
@@ -400,6 +462,8 @@ struct swlm_snap {
 };
 
 namespace {
+
+__nv_bfloat16* res_buf(swlm_state* s, int phys) { return phys ? s->res2 : s->buf[SWLM_BUF_RESIDUAL]; }
 
 int kv_heads_local(const swlm_plan* p) { return std::max(1, p->desc.kv_heads / std::max(1, p->ctx->tp_size)); }
 
@@ -431,14 +495,21 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             s->launches += 1;
             break;
         case L_RMSNORM:
-            rc = launch_rmsnorm(st.kind, m, st.n, s->buf[st.in_buf], s->width[st.in_buf], s->buf[SWLM_BUF_RESIDUAL],
+            rc = launch_rmsnorm(st.kind, m, st.n, s->buf[st.in_buf], s->width[st.in_buf], res_buf(s, L.res_in),
                                 s->width[SWLM_BUF_RESIDUAL], L.d1->data, st.eps, st.weight_bias, s->buf[st.out_buf],
                                 s->width[st.out_buf], stream);
             s->launches += 1;
             break;
         case L_QGEMV: {
             QGemvLaunch a;
-            a.w = L.w; a.x = s->buf[st.in_buf]; a.x_stride = s->width[st.in_buf]; a.m = m; a.epilogue = L.epilogue;
+            const int xb = L.norm.kind ? L.x_buf : st.in_buf;
+            a.w = L.w; a.x = s->buf[xb]; a.x_stride = s->width[xb]; a.m = m; a.epilogue = L.epilogue;
+            if (L.norm.kind) {
+                a.norm.mode = L.norm.kind;
+                a.norm.res_in = res_buf(s, L.res_in); a.norm.res_out = res_buf(s, L.res_out);
+                a.norm.res_stride = s->width[SWLM_BUF_RESIDUAL];
+                a.norm.weight = L.norm_w->data; a.norm.eps = L.norm.eps; a.norm.weight_bias = L.norm.weight_bias;
+            }
             for (int q = 0; q < L.n_seg; ++q) { a.y[q] = s->buf[L.seg_buf[q]]; a.y_stride[q] = s->width[L.seg_buf[q]]; a.seg_end[q] = L.seg_end[q]; }
             a.partial = s->qgemv_partial; a.counters = s->qgemv_counters;
             rc = launch_qgemv(a, stream);
@@ -548,6 +619,7 @@ std::vector<Region> state_regions(swlm_state* s) {
     r.push_back({s->kcache, (size_t)d.kv_layers * s->kv_layer_elems * 2});
     r.push_back({s->vcache, (size_t)d.kv_layers * s->kv_layer_elems * 2});
     r.push_back({s->conv, (size_t)d.conv_layers * s->conv_layer_elems * 2});
+    r.push_back({s->res2, (size_t)d.max_batch * s->width[SWLM_BUF_RESIDUAL] * 2});
     r.push_back({s->position, 4});
     r.push_back({s->token_in, (size_t)d.max_batch * 4});
     r.push_back({s->token_out, (size_t)d.max_batch * 4});
@@ -758,6 +830,7 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     if ((rc = dev_alloc(&s->vcache, (size_t)d.kv_layers * s->kv_layer_elems))) return fail(rc);
     s->conv_layer_elems = (size_t)d.max_batch * d.conv_kernel * d.conv_dim;
     if ((rc = dev_alloc(&s->conv, (size_t)d.conv_layers * s->conv_layer_elems))) return fail(rc);
+    if ((rc = dev_alloc(&s->res2, (size_t)d.max_batch * s->width[SWLM_BUF_RESIDUAL]))) return fail(rc);
     if ((rc = dev_alloc(&s->position, 1))) return fail(rc);
     if ((rc = dev_alloc(&s->step_counter, 1))) return fail(rc);
     if ((rc = dev_alloc(&s->token_in, d.max_batch))) return fail(rc);
@@ -785,7 +858,7 @@ void swlm_state_destroy(swlm_state* s) {
     if (s->stream) cudaStreamSynchronize(s->stream);
     drop_graphs(s);
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->buf[i]);
-    cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->conv);
+    cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->conv); cudaFree(s->res2);
     cudaFree(s->position); cudaFree(s->step_counter); cudaFree(s->token_in); cudaFree(s->token_out); cudaFree(s->ring);
     cudaFree(s->prompt);
     cudaFree(s->attn_scratch); cudaFree(s->qgemv_partial); cudaFree(s->qgemv_counters); cudaFree(s->attn_counters);
@@ -963,7 +1036,9 @@ int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_tok
 int swlm_read_buffer(swlm_state* s, int buf, uint16_t* dst, int count_per_row) {
     if (!s || !dst || !buf_ok(buf) || count_per_row > s->width[buf]) { set_error("bad buffer read"); return SWLM_ERR_INVALID; }
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
-    SWLM_CUDA(cudaMemcpy2D(dst, (size_t)count_per_row * 2, s->buf[buf], (size_t)s->width[buf] * 2, (size_t)count_per_row * 2,
+    // the residual stream ends a step in whichever of its two physical buffers the plan wrote last
+    const __nv_bfloat16* src = buf == SWLM_BUF_RESIDUAL ? res_buf(s, s->plan->final_res) : s->buf[buf];
+    SWLM_CUDA(cudaMemcpy2D(dst, (size_t)count_per_row * 2, src, (size_t)s->width[buf] * 2, (size_t)count_per_row * 2,
                            s->plan->desc.max_batch, cudaMemcpyDeviceToHost));
     return SWLM_OK;
 }
@@ -973,6 +1048,9 @@ int swlm_write_buffer(swlm_state* s, int buf, const uint16_t* src, int count_per
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     SWLM_CUDA(cudaMemcpy2D(s->buf[buf], (size_t)s->width[buf] * 2, src, (size_t)count_per_row * 2, (size_t)count_per_row * 2,
                            s->plan->desc.max_batch, cudaMemcpyHostToDevice));
+    if (buf == SWLM_BUF_RESIDUAL)
+        SWLM_CUDA(cudaMemcpy2D(s->res2, (size_t)s->width[buf] * 2, src, (size_t)count_per_row * 2, (size_t)count_per_row * 2,
+                               s->plan->desc.max_batch, cudaMemcpyHostToDevice));
     return SWLM_OK;
 }
 

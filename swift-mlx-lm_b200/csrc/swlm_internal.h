@@ -101,8 +101,20 @@ int launch_untile_bf16(const Q4Tiled& t, __nv_bfloat16* out, cudaStream_t s);
 
 enum { QGEMV_EPI_STORE = 0, QGEMV_EPI_SWIGLU = 1 };
 
+// Residual add / copy / RMSNorm fused in front of a product (mode = the step kind it replaces, 0 = none).
+// x of the launch is then the un-normalised input; res_in and res_out must be different buffers.
+struct XNorm {
+    int mode = 0;
+    const __nv_bfloat16* res_in = nullptr;
+    __nv_bfloat16* res_out = nullptr;
+    int res_stride = 0;
+    const __nv_bfloat16* weight = nullptr;
+    float eps = 0.f, weight_bias = 0.f;
+};
+
 struct QGemvLaunch {
     const Q4Tiled* w = nullptr;
+    XNorm norm;
     const __nv_bfloat16* x = nullptr;  // [m][x_stride]
     int x_stride = 0;
     // result rows [0, seg_end[0]) go to y[0], [seg_end[0], seg_end[1]) to y[1], ... each [m][y_stride[i]]

@@ -92,10 +92,11 @@ def test_plan_fuses_launches(pkg, oracle):
     cfg = small_llama(pkg)
     store, gm, om = build_pair(pkg, oracle, cfg)
     text = gm.describe()
-    # per layer: norm, fused qkv, attention (2 kernels), o, norm, fused gate/up + swiglu, down
+    # per layer: norm + fused qkv, attention, o, norm + fused gate/up + swiglu, down; then norm + lm_head, argmax x2
     assert text.count("qgemv+swiglu") == cfg.layers
+    assert text.count("rmsnorm+") == 2 * cfg.layers + 1
     assert sum("self_attn.q_proj" in l and "self_attn.v_proj" in l for l in text.splitlines()) == cfg.layers
-    assert gm.launches_per_step == 1 + cfg.layers * 8 + 1 + 1 + 2
+    assert gm.launches_per_step == 1 + cfg.layers * 5 + 1 + 2
     before = gm.launches
     gm.decode([1])
     assert gm.launches - before == gm.launches_per_step
