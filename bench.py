@@ -266,10 +266,9 @@ def main():
     builder = pkg.DispatchPlanBuilder(cfg)
     weights = pkg.synth_model_weights(builder, seed=3)
     store = pkg.WeightStore(local_rank, tp_rank=rank, tp_size=world)
-    if world > 1:
-        from swlm_b200 import tp as tp_mod
-        tp_mod.attach(store, dist)
     model = pkg.load_model(store, builder, weights)
+    if world > 1:
+        pkg.tp.attach(model, dist)
     # a stream of our own: torch's default stream has handle 0, which the C ABI reads as "use your own"
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)

@@ -143,6 +143,21 @@ int64_t swlm_launches(const swlm_state* state);
  * (Sources/MetalCompiler/Execution/MetalDecodeExecutor.swift). */
 int swlm_profile_kind(swlm_state* state, int step_kind, int repeats);
 
+/* ---- tensor parallel: one process per GPU, tp_size of them ----------------------------------------------
+ * No counterpart in the reference (single device). Each rank creates its context with (tp_rank, tp_size),
+ * uploads the full tensors with a shard kind (the library keeps its slice), builds the same plan and state,
+ * then: swlm_tp_export -> exchange the 64-byte handles between the processes (any transport; the harness
+ * uses torch.distributed) -> swlm_tp_attach with all handles in rank order -> a barrier -> decode as usual.
+ * Row-parallel products push their partial sums into every rank's exchange buffer over NVLink and the next
+ * product adds them up in its prologue; the vocabulary-sharded argmax is exchanged the same way. Every device
+ * wait is bounded: if a rank does not arrive, swlm_tp_status returns SWLM_ERR_TIMEOUT instead of hanging. */
+#define SWLM_TP_HANDLE_BYTES 64
+int swlm_tp_export(swlm_state* state, void* handle_out);
+int swlm_tp_attach(swlm_state* state, const void* handles);
+int swlm_tp_status(swlm_state* state);
+/* Rank-local slice {row0, rows, col0, cols} of an n x k tensor under a SWLM_SHARD_* kind (host only). */
+int swlm_shard_range(int shard_kind, int n, int k, int tp_rank, int tp_size, int* out4);
+
 /* ---- op-level entry points (host buffers; copies are part of the call) ----------
  * Y[m][n] = bf16(X[m][k] . W^T): gemv_q4_g64 for m = 1
  * (Generator/MetalSourceGenerator+Quantized.swift:496-575), gemm_q4_g64 for m > 1 (:88-156). */

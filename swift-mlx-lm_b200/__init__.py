@@ -24,5 +24,5 @@ from .plan import (  # noqa: F401
     lfm2_like_config,
 )
 from .model import InferenceModel, WeightStore, load_model  # noqa: F401
-from . import formats, plan  # noqa: F401
+from . import formats, plan, tp  # noqa: F401
 from .synth import synth_model_weights, synth_q4  # noqa: F401

@@ -177,13 +177,18 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(int n, const __nv_b
     }
 }
 
-// one warp per sequence; finally thread 0 advances the device-side position and step counter
+// one warp per sequence; finally thread 0 advances the device-side position and step counter.
+// Tensor parallel (vocabulary sharded): every rank pushes its local (max, global index) per sequence into
+// every rank's exchange buffer, waits (bounded) for the others and takes the best pair, lowest index first
+// among equal maxima, so all ranks continue with the same token.
 __global__ void argmax_final_kernel(int m, const float* pval, const int32_t* pidx, int32_t* token_out,
                                     int32_t* token_in_next, int32_t* ring, int32_t* step_counter, int ring_cap,
-                                    int32_t* position, int advance) {
+                                    int32_t* position, int advance, TpParams tp, int32_t* am_epoch, int shard_offset) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float best_v[16];
+    __shared__ int best_i[16];
     for (int b = warp; b < m; b += (blockDim.x >> 5)) {
         float best = -INFINITY;
         int bi = 0x7fffffff;
@@ -195,10 +200,41 @@ __global__ void argmax_final_kernel(int m, const float* pval, const int32_t* pid
         }
         if (lane == 0) {
             if (bi == 0x7fffffff) bi = 0;
-            token_out[b] = bi;
-            if (token_in_next) token_in_next[b] = bi;
-            if (ring) ring[(size_t)(step_counter[0] % ring_cap) * m + b] = bi;
+            best_v[b] = best; best_i[b] = bi + shard_offset;
         }
+    }
+    __syncthreads();
+    if (tp.tp > 1) {
+        const int epoch = *am_epoch + 1, par = epoch & 1;
+        for (int idx = threadIdx.x; idx < m * tp.tp; idx += blockDim.x) {
+            const int b = idx / tp.tp, r = idx - b * tp.tp;
+            float2* dst = reinterpret_cast<float2*>(tp.peer[r] + tp.lay.recv_am(par, tp.rank, b));
+            *dst = make_float2(best_v[b], __int_as_float(best_i[b]));
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < tp.tp)
+            st_release_sys(reinterpret_cast<unsigned*>(tp.peer[threadIdx.x] + tp.lay.flags_am(par, tp.rank)), (unsigned)epoch);
+        tp_wait_flags(tp, tp.peer[tp.rank], tp.lay.flags_am(par, 0), epoch, threadIdx.x);
+        __syncthreads();
+        if (threadIdx.x < m) {
+            const int b = threadIdx.x;
+            float best = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int src = 0; src < tp.tp; ++src) {
+                const float2 v = __ldcg(reinterpret_cast<const float2*>(tp.peer[tp.rank] + tp.lay.recv_am(par, src, b)));
+                argmax_merge(best, bi, v.x, __float_as_int(v.y));
+            }
+            best_v[b] = best; best_i[b] = bi == 0x7fffffff ? 0 : bi;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) *am_epoch = epoch;
+    }
+    if (threadIdx.x < m) {
+        const int b = threadIdx.x, bi = best_i[b];
+        token_out[b] = bi;
+        if (token_in_next) token_in_next[b] = bi;
+        if (ring) ring[(size_t)(step_counter[0] % ring_cap) * m + b] = bi;
     }
     __syncthreads();
     if (advance && threadIdx.x == 0) {
@@ -285,10 +321,11 @@ size_t argmax_scratch_elems(int m) { return (size_t)m * kArgmaxBlocks; }
 
 int launch_argmax(int m, int n, const __nv_bfloat16* logits, int stride, int32_t* token_out, int32_t* token_in_next,
                   int32_t* ring, int32_t* step_counter, int ring_cap, int32_t* position, int advance,
-                  float* scratch_val, int32_t* scratch_idx, cudaStream_t s) {
+                  float* scratch_val, int32_t* scratch_idx, const TpParams& tp, int32_t* am_epoch, int shard_offset,
+                  cudaStream_t s) {
     launch_k(argmax_partial_kernel, dim3(kArgmaxBlocks, m), 256, 0, s, n, logits, stride, scratch_val, scratch_idx);
     launch_k(argmax_final_kernel, 1, 256, 0, s, m, scratch_val, scratch_idx, token_out, token_in_next, ring, step_counter,
-                                          ring_cap, position, advance);
+                                          ring_cap, position, advance, tp, am_epoch, shard_offset);
     return check_launch("argmax launch");
 }
 

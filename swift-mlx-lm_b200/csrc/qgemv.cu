@@ -26,6 +26,7 @@
 #include <algorithm>
 
 #include "swlm_internal.h"
+#include "tp_device.cuh"
 
 namespace swlm {
 namespace {
@@ -36,6 +37,7 @@ constexpr int kStages = 3;                 // ring depth per warp; one stage = 4
 constexpr int kStageBytes = 4 * 512 + 256;
 constexpr int kRingBytes = kWarps * kStages * kStageBytes;
 constexpr int kXPad = 8;                   // bf16 elements of padding per x row (bank skew)
+constexpr int kL2Ahead = 10;               // stages (2.3 KB each) a warp prefetches into L2 ahead of its ring
 
 struct QGemvParams {
     const uint4* tiles;
@@ -47,6 +49,7 @@ struct QGemvParams {
     int y_stride[3], seg_end[3];
     int m;
     int si, sk;   // k-slices per CTA group, CTA groups along K
+    int cta_mode; // batch-1 kernel: slices of a row tile live in one CTA and meet in shared memory
     float* partial;
     unsigned* counters;
     // optional fused residual-add / copy / RMSNorm in front of the product (norm_mode = step kind, 0 = none)
@@ -56,12 +59,17 @@ struct QGemvParams {
     int res_stride;
     const __nv_bfloat16* norm_w;
     float eps, weight_bias;
+    // tensor parallel: push = this product's rows are partial sums that go to every rank's exchange buffer;
+    // in_tp = the fused norm's input is the sum of the partials the preceding product pushed
+    int push, in_tp;
+    TpParams tp;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -104,16 +112,33 @@ __device__ __forceinline__ float sb_zero(unsigned pair) {
 // returned as eight packed bf16 pairs. The norm sees the unrounded sum, as the reference's fused kernel does.
 // res_in and res_out are different buffers: other CTAs read res_in while one writes res_out.
 __device__ __forceinline__ void fused_norm_run(const QGemvParams& p, int b, int k0, bool in_range, bool writer,
-                                               float* red, unsigned (&w)[8]) {
+                                               float* red, unsigned (&w)[8], int tp_epoch) {
     float h[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) h[i] = 0.f;
     if (in_range) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)b * p.x_stride + k0);
-        const uint4 v0 = __ldcg(src), v1 = __ldcg(src + 1);
-        const unsigned vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        if (p.in_tp) {
+            // all-reduce, consuming side: partial sums of every rank, added in rank order, rounded once to
+            // bf16 (the value a single GPU would have stored to the hidden buffer)
+            const int par = tp_epoch & 1;
+#pragma unroll 1
+            for (int src = 0; src < p.tp.tp; ++src) {
+                const float4* r = reinterpret_cast<const float4*>(p.tp.peer[p.tp.rank] + p.tp.lay.recv_ar(par, src, b)) + k0 / 4;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { h[2 * i] = __uint_as_float(vw[i] << 16); h[2 * i + 1] = __uint_as_float(vw[i] & 0xFFFF0000u); }
+                for (int q = 0; q < 4; ++q) {
+                    const float4 v = __ldcg(r + q);
+                    h[4 * q] += v.x; h[4 * q + 1] += v.y; h[4 * q + 2] += v.z; h[4 * q + 3] += v.w;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) h[i] = __bfloat162float(__float2bfloat16_rn(h[i]));
+        } else {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)b * p.x_stride + k0);
+            const uint4 v0 = __ldcg(src), v1 = __ldcg(src + 1);
+            const unsigned vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { h[2 * i] = __uint_as_float(vw[i] << 16); h[2 * i + 1] = __uint_as_float(vw[i] & 0xFFFF0000u); }
+        }
         if (p.norm_mode != SWLM_STEP_COPY_RMSNORM) {
             const uint4* rs = reinterpret_cast<const uint4*>(p.res_in + (size_t)b * p.res_stride + k0);
             const uint4 r0 = __ldcg(rs), r1 = __ldcg(rs + 1);
@@ -155,6 +180,29 @@ __device__ __forceinline__ void fused_norm_run(const QGemvParams& p, int b, int 
             const __nv_bfloat162 v = __floats2bfloat162_rn(h[2 * i] * rs * (__uint_as_float(nw[i] << 16) + p.weight_bias),
                                                            h[2 * i + 1] * rs * (__uint_as_float(nw[i] & 0xFFFF0000u) + p.weight_bias));
             w[i] = *reinterpret_cast<const unsigned*>(&v);
+        }
+    }
+}
+
+// All-reduce, producing side: one fp32 value of row `row`, sequence `col`, into every rank's buffer.
+__device__ __forceinline__ void tp_push_value(const QGemvParams& p, int epoch, int row, int col, float v) {
+    const size_t off = p.tp.lay.recv_ar(epoch & 1, p.tp.rank, col) + (size_t)row * 4;
+#pragma unroll 1
+    for (int r = 0; r < p.tp.tp; ++r) *reinterpret_cast<float*>(p.tp.peer[r] + off) = v;
+}
+// Called by one whole warp after it pushed a row tile: the warp that completes the count raises this
+// rank's flag on every rank and advances the local epoch.
+__device__ __forceinline__ void tp_row_tile_done(const QGemvParams& p, int epoch, int lane) {
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) {
+        const unsigned prev = atomicAdd(p.tp.done, 1u);
+        if (prev == (unsigned)p.row_tiles - 1u) {
+            *p.tp.done = 0u;
+            __threadfence_system();
+            for (int r = 0; r < p.tp.tp; ++r)
+                st_release_sys(reinterpret_cast<unsigned*>(p.tp.peer[r] + p.tp.lay.flags_ar(epoch & 1, p.tp.rank)), (unsigned)epoch);
+            *p.tp.epoch = epoch;
         }
     }
 }
@@ -224,12 +272,17 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
     // ---- x: asynchronous copy in its natural order (the tile layout was chosen so that lane t's B
     // fragments of a group are the 16 consecutive elements 16t..16t+15)-------------------------------
     __shared__ float red[kWarps];
+    const int tp_epoch = (p.push || p.in_tp) ? *p.tp.epoch + (p.push ? 1 : 0) : 0;
+    if (p.in_tp) {
+        tp_wait_flags(p.tp, p.tp.peer[p.tp.rank], p.tp.lay.flags_ar(tp_epoch & 1, 0), tp_epoch, tid);
+        __syncthreads();
+    }
     if (p.norm_mode) {
         // fused norm (dimension <= 4096, one CTA group): thread tid owns run tid of every row
         for (int b = 0; b < rows_x; ++b) {
             unsigned w[8];
             const int k0 = tid * 16;
-            fused_norm_run(p, b, k0, k0 < p.k, blockIdx.x == 0, red, w);
+            fused_norm_run(p, b, k0, k0 < p.k, blockIdx.x == 0, red, w, tp_epoch);
             if (k0 < nk_cta) {
                 uint4* dst = reinterpret_cast<uint4*>(xsm + (size_t)b * xs_stride + k0);
                 dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -425,7 +478,13 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
             for (int e = 0; e < 2; ++e) {
                 const int col = 8 * nt + 2 * t + e;
                 if (col >= p.m) continue;
-                if (EPI == QGEMV_EPI_STORE) {
+                if (EPI == QGEMV_EPI_STORE && p.push) {
+#pragma unroll
+                    for (int hi = 0; hi < 2; ++hi) {
+                        const int r = rt * 16 + g + 8 * hi;
+                        if (r < p.seg_end[0]) tp_push_value(p, tp_epoch, r, col, tot[nt][2 * hi + e]);
+                    }
+                } else if (EPI == QGEMV_EPI_STORE) {
 #pragma unroll
                     for (int hi = 0; hi < 2; ++hi) {
                         const int r = rt * 16 + g + 8 * hi;
@@ -448,6 +507,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
                 }
             }
         }
+        if (EPI == QGEMV_EPI_STORE && p.push) tp_row_tile_done(p, tp_epoch, lane);
     }
     cp_async_wait<0>();
 }
@@ -455,24 +515,22 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
 // =================================================================================================
 // Single-sequence kernel (m == 1), the batch-1 decode path.
 //
-// With one activation column the tensor core multiplies seven columns of zeros, and on this part the
-// legacy mma.sync pipe saturates near 3.5 TB/s of weight stream, so batch 1 runs on the integer dot
-// product units instead. The activations are held in shared memory in block floating point: every run of
-// 16 consecutive elements (one lane's share of a group) carries a power-of-two exponent and 16-bit
-// integers split into a signed high and an unsigned low byte, exact for every element within 2^-8 of the
-// run's largest and within 2^-16 of it otherwise. A weight word yields four nibbles of row g with one AND
-// and four of row g+8 with a shift and an AND; two dp4a per digit accumulate exact integers, and the
-// group's scale and zero are applied once per lane in fp32. Same tiles, ring and unit scheduling as above.
+// The fp16 tensor-core path above spends one mma.m16n8k16 per 256 weights and, on this part, saturates the
+// legacy mma.sync pipe near 3.5 TB/s of weight stream; the integer dot-product instruction (dp4a) turned
+// out to issue on the quarter-rate conversion pipe. Batch 1 therefore uses the 8-bit integer tensor-core
+// shape m16n8k32, twice the weights per instruction and almost no unpacking: a weight word gives four
+// exact 8-bit weights of row g with one AND and four of row g+8 with a shift and an AND. The activations
+// are held in shared memory in block floating point: every group of 64 carries a power-of-two exponent and
+// 15-bit integers split into two signed bytes, exact for every element within 2^-7 of the group's largest
+// and within 2^-14 of it otherwise. High and low digits ride in columns 0 and 1 of the B operand, so one
+// instruction serves both; the integer sums are exact, and the group's scale and zero are applied once in
+// fp32. Same tiles, ring and unit scheduling as above.
 // =================================================================================================
-__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp4a_uu(unsigned a, unsigned b, int c) {
-    int d;
-    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
+__device__ __forceinline__ void imma_u8s8(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 template <int EPI, bool F16SB>
@@ -486,9 +544,17 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
     uint4* xq = reinterpret_cast<uint4*>(smem + kRingBytes);                       // [kt][t][hi, lo]
     float2* xmeta = reinterpret_cast<float2*>(smem + kRingBytes + (size_t)kt_total * 128);  // [kt][t] {2^E, sum}
 
+    // Two ways of dealing out the (row tile, k-slice) units. cta_mode (matrices with no more row tiles than
+    // resident CTAs): a CTA takes eight consecutive units at a time, i.e. all slices of 8/si row tiles, and
+    // adds the slices through shared memory. Otherwise every CTA owns an equal contiguous share, its warps
+    // take units round-robin and the slices of a row tile meet in global scratch.
     const int units = p.row_tiles * p.si;
     const int u_lo = (int)(((long long)blockIdx.x * units) / gridDim.x);
     const int u_hi = (int)(((long long)(blockIdx.x + 1) * units) / gridDim.x);
+    const int u_first = p.cta_mode ? blockIdx.x * kWarps : u_lo;
+    const int u_end = p.cta_mode ? units : u_hi;
+    const int u_limit = p.cta_mode ? ((units + kWarps - 1) / kWarps) * kWarps : u_hi;  // uniform across the CTA
+    const int u_stride = p.cta_mode ? gridDim.x * kWarps : kWarps;
     auto open_unit = [&](UnitCursor& c) {
         if (c.u < c.u_end) {
             c.rt = c.u / p.si;
@@ -497,10 +563,21 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
             c.st_end = ((s + 1) * p.kt4_total) / p.si;
         }
     };
-    UnitCursor ic{u_lo + warp, u_hi, 0, 0, 0};
+    UnitCursor ic{u_first + warp, u_end, 0, 0, 0};   // cp.async side, kStages-1 stages ahead of the math
+    UnitCursor pc{u_first + warp, u_end, 0, 0, 0};   // L2 prefetch side, kL2Ahead stages further ahead
     open_unit(ic);
+    open_unit(pc);
+    auto prefetch_next = [&]() {
+        while (pc.u < pc.u_end && pc.st >= pc.st_end) { pc.u += u_stride; open_unit(pc); }
+        if (pc.u < pc.u_end) {
+            const size_t stage = (size_t)pc.rt * p.kt4_total + pc.st;
+            if (lane < 16) prefetch_l2(reinterpret_cast<const unsigned char*>(p.tiles + stage * 128) + lane * 128);
+            else if (lane < 18) prefetch_l2(reinterpret_cast<const unsigned char*>(p.sb + stage * 16) + (lane - 16) * 128);
+            pc.st += 1;
+        }
+    };
     auto issue = [&](int slot) {
-        while (ic.u < ic.u_end && ic.st >= ic.st_end) { ic.u += kWarps; open_unit(ic); }
+        while (ic.u < ic.u_end && ic.st >= ic.st_end) { ic.u += u_stride; open_unit(ic); }
         if (ic.u < ic.u_end) {
             unsigned char* dst = my_ring + slot * kStageBytes;
             const uint4* src = p.tiles + ((size_t)ic.rt * p.kt4_total + ic.st) * 128;
@@ -510,22 +587,31 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
             ic.st += 1;
         }
         cp_async_commit();
+        prefetch_next();
     };
     // Weights do not depend on the preceding kernel: the ring starts filling before its results are awaited.
+    // HBM keeps streaming into L2 while the activations are prepared: the ring alone holds 4.6 KB per warp.
     pdl_launch_dependents();
     int issued = 0, consumed = 0;
+#pragma unroll
+    for (int i = 0; i < kL2Ahead; ++i) prefetch_next();
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) { issue(issued % kStages); ++issued; }
     pdl_wait();
 
     // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
     __shared__ float red[kWarps];
+    const int tp_epoch = (p.push || p.in_tp) ? *p.tp.epoch + (p.push ? 1 : 0) : 0;
+    if (p.in_tp) {
+        tp_wait_flags(p.tp, p.tp.peer[p.tp.rank], p.tp.lay.flags_ar(tp_epoch & 1, 0), tp_epoch, tid);
+        __syncthreads();
+    }
     for (int run = tid; run < kt_total * 4 || (p.norm_mode && run < kThreads); run += kThreads) {
         const int k0 = run * 16;
         unsigned w[8];
         if (p.norm_mode) {
             // dimension <= 4096: exactly one pass, every thread takes part in the block-wide sum
-            fused_norm_run(p, 0, k0, k0 < p.k, blockIdx.x == 0, red, w);
+            fused_norm_run(p, 0, k0, k0 < p.k, blockIdx.x == 0, red, w, tp_epoch);
             if (run >= kt_total * 4) continue;
         } else {
             uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
@@ -536,13 +622,17 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
             }
             w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w; w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
         }
+        // one exponent per group of 64: the four runs of a group sit in four neighbouring threads
+        const unsigned act = __activemask();
         unsigned mx = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
-        const int e = (int)(mx >> 7);  // biased exponent of the largest magnitude
+        mx = max(mx, __shfl_xor_sync(act, mx, 1));
+        mx = max(mx, __shfl_xor_sync(act, mx, 2));
+        const int e = (int)(mx >> 7);  // biased exponent of the group's largest magnitude
         const bool live = e >= 16 && e < 255;
-        // largest magnitude -> [2^14, 2^15): multiply by 2^(141 - e)
-        const float mul = live ? __uint_as_float((unsigned)(268 - e) << 23) : 0.f;
+        // largest magnitude -> [2^13, 2^14): multiply by 2^(140 - e); 15-bit integers, two signed bytes each
+        const float mul = live ? __uint_as_float((unsigned)(267 - e) << 23) : 0.f;
         int q[16];
         int sum = 0;
 #pragma unroll
@@ -551,28 +641,41 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
             q[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * mul);
             sum += q[2 * i] + q[2 * i + 1];
         }
-        // byte order inside a 4-element step matches the nibble order of a weight word: 0, 2, 1, 3
+        sum += __shfl_xor_sync(act, sum, 1);
+        sum += __shfl_xor_sync(act, sum, 2);
+        // v = 256 * hi + lo with both digits signed bytes; byte order inside a 4-element step matches the
+        // nibble order of a weight word: 0, 2, 1, 3
         unsigned hi[4], lo[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int a = q[4 * j], b = q[4 * j + 2], c = q[4 * j + 1], d = q[4 * j + 3];
-            hi[j] = ((unsigned)(a >> 8) & 0xFFu) | (((unsigned)(b >> 8) & 0xFFu) << 8) | (((unsigned)(c >> 8) & 0xFFu) << 16) | (((unsigned)(d >> 8) & 0xFFu) << 24);
-            lo[j] = ((unsigned)a & 0xFFu) | (((unsigned)b & 0xFFu) << 8) | (((unsigned)c & 0xFFu) << 16) | (((unsigned)d & 0xFFu) << 24);
+            const int v[4] = {q[4 * j], q[4 * j + 2], q[4 * j + 1], q[4 * j + 3]};
+            unsigned hw = 0, lw = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int h = (v[i] + 128) >> 8, l = v[i] - (h << 8);
+                hw |= ((unsigned)h & 0xFFu) << (8 * i);
+                lw |= ((unsigned)l & 0xFFu) << (8 * i);
+            }
+            hi[j] = hw; lo[j] = lw;
         }
         xq[run * 2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         xq[run * 2 + 1] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        const float scale = live ? __uint_as_float((unsigned)(e - 14) << 23) : 0.f;  // 2^(e - 141) = 1 / mul
-        xmeta[run] = make_float2(scale, (float)sum * scale);
+        const float scale = live ? __uint_as_float((unsigned)(e - 13) << 23) : 0.f;  // 2^(e - 140) = 1 / mul
+        if ((run & 3) == 0) xmeta[run >> 2] = make_float2(scale, (float)sum * scale);
     }
     __syncthreads();
 
     const int s_total = p.si;
-    UnitCursor cc{u_lo + warp, u_hi, 0, 0, 0};
-    for (; cc.u < cc.u_end; cc.u += kWarps) {
+    __shared__ float cta_red[2][kWarps][16];
+    int round = 0;
+    for (int base = u_first; base < u_limit; base += u_stride, ++round) {
+        UnitCursor cc{base + warp, u_end, 0, 0, 0};
+        const bool valid = cc.u < cc.u_end;
         open_unit(cc);
         const int rt = cc.rt;
+        const int slice = cc.u - rt * p.si;
         float tot_lo = 0.f, tot_hi = 0.f;
-        for (int stg = cc.st; stg < cc.st_end; ++stg) {
+        for (int stg = cc.st; valid && stg < cc.st_end; ++stg) {
             issue(issued % kStages); ++issued;
             cp_async_wait<kStages - 1>();
             __syncwarp();
@@ -583,27 +686,21 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
             const uint4 sB = reinterpret_cast<const uint4*>(st + 2048)[g + 8];
             const unsigned sAw[4] = {sA.x, sA.y, sA.z, sA.w};
             const unsigned sBw[4] = {sB.x, sB.y, sB.z, sB.w};
-            const uint4* xrun = xq + ((size_t)stg * 16 + t) * 2;
-            const float2* mrun = xmeta + (size_t)stg * 16 + t;
+            const uint4* xrun = xq + ((size_t)stg * 16 + t) * 2 + (g & 1);
+            const float2* mrun = xmeta + (size_t)stg * 4;
 #pragma unroll
             for (int ti = 0; ti < 4; ++ti) {
                 const uint4 wv = wsm[ti * 32];
-                const uint4 xh = xrun[ti * 8], xl = xrun[ti * 8 + 1];
-                const float2 meta = mrun[ti * 4];
-                const unsigned wr[4] = {wv.x, wv.y, wv.z, wv.w};
-                const unsigned xhw[4] = {xh.x, xh.y, xh.z, xh.w};
-                const unsigned xlw[4] = {xl.x, xl.y, xl.z, xl.w};
-                int ah = 0, al = 0, bh = 0, bl = 0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const unsigned a = wr[j] & 0x0F0F0F0Fu;          // four weights of row g
-                    const unsigned b = (wr[j] >> 4) & 0x0F0F0F0Fu;   // four weights of row g + 8
-                    ah = dp4a_us(a, xhw[j], ah);
-                    al = dp4a_uu(a, xlw[j], al);
-                    bh = dp4a_us(b, xhw[j], bh);
-                    bl = dp4a_uu(b, xlw[j], bl);
-                }
-                const float fa = (float)(ah * 256 + al), fb = (float)(bh * 256 + bl);
+                // B operand: column 0 = high digits, column 1 = low digits of the activations, the rest zero
+                uint4 xd = make_uint4(0, 0, 0, 0);
+                if (g < 2) xd = xrun[ti * 8];
+                const float2 meta = mrun[ti];
+                int c[4] = {0, 0, 0, 0};
+                // rows g take the low nibble of every byte, rows g + 8 the high nibble: exact 8-bit integers
+                imma_u8s8(c, wv.x & 0x0F0F0F0Fu, (wv.x >> 4) & 0x0F0F0F0Fu, wv.y & 0x0F0F0F0Fu, (wv.y >> 4) & 0x0F0F0F0Fu, xd.x, xd.y);
+                imma_u8s8(c, wv.z & 0x0F0F0F0Fu, (wv.z >> 4) & 0x0F0F0F0Fu, wv.w & 0x0F0F0F0Fu, (wv.w >> 4) & 0x0F0F0F0Fu, xd.z, xd.w);
+                // lanes t == 0 hold columns 0 and 1 of rows g and g + 8: sum(q * x) = 256 * hi + lo, exactly
+                const float fa = (float)(c[0] * 256 + c[1]), fb = (float)(c[2] * 256 + c[3]);
                 const float s_lo = sb_scale<F16SB>(sAw[ti]) * meta.x, z_lo = sb_zero<F16SB>(sAw[ti]);
                 const float s_hi = sb_scale<F16SB>(sBw[ti]) * meta.x, z_hi = sb_zero<F16SB>(sBw[ti]);
                 tot_lo = fmaf(s_lo, fa, fmaf(z_lo, meta.y, tot_lo));
@@ -611,14 +708,25 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
             }
             __syncwarp();
         }
-        // the four lanes of a row hold the four quarters of every group
-        tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 1);
-        tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 2);
-        tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 1);
-        tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 2);
+        // lanes t == 0 hold the sums of rows g and g + 8; the other lanes carried zero columns
 
-        if (s_total > 1) {
-            const int s_glob = cc.u - rt * p.si;
+        bool finisher = valid;
+        if (p.cta_mode) {
+            if (s_total > 1) {
+                // slices of a row tile sit in neighbouring warps: add them in slice order through shared memory
+                if (valid && t == 0) { cta_red[round & 1][warp][g] = tot_lo; cta_red[round & 1][warp][g + 8] = tot_hi; }
+                __syncthreads();
+                finisher = valid && slice == 0;
+                if (finisher) {
+                    tot_lo = tot_hi = 0.f;
+                    for (int s = 0; s < s_total; ++s) {
+                        tot_lo += cta_red[round & 1][warp + s][g];
+                        tot_hi += cta_red[round & 1][warp + s][g + 8];
+                    }
+                }
+            }
+        } else if (s_total > 1 && valid) {
+            const int s_glob = slice;
             float* dst = p.partial + ((size_t)rt * s_total + s_glob) * 16;
             if (t == 0) { __stcg(dst + g, tot_lo); __stcg(dst + g + 8, tot_hi); }
             __threadfence();
@@ -626,15 +734,26 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
             unsigned prev = 0;
             if (lane == 0) prev = atomicAdd(p.counters + rt, 1u);
             prev = __shfl_sync(0xffffffffu, prev, 0);
-            if (prev != (unsigned)s_total - 1u) continue;
-            __threadfence();
-            if (lane == 0) p.counters[rt] = 0u;
-            tot_lo = tot_hi = 0.f;
-            for (int s = 0; s < s_total; ++s) {  // slice order: independent of arrival order
-                const float* src = p.partial + ((size_t)rt * s_total + s) * 16;
-                tot_lo += __ldcg(src + g);
-                tot_hi += __ldcg(src + g + 8);
+            finisher = prev == (unsigned)s_total - 1u;
+            if (finisher) {
+                __threadfence();
+                if (lane == 0) p.counters[rt] = 0u;
+                tot_lo = tot_hi = 0.f;
+                for (int s = 0; s < s_total; ++s) {  // slice order: independent of arrival order
+                    const float* src = p.partial + ((size_t)rt * s_total + s) * 16;
+                    tot_lo += __ldcg(src + g);
+                    tot_hi += __ldcg(src + g + 8);
+                }
             }
+        }
+        if (!finisher) continue;
+        if (EPI == QGEMV_EPI_STORE && p.push) {
+            if (t == 0) {
+                if (rt * 16 + g < p.seg_end[0]) tp_push_value(p, tp_epoch, rt * 16 + g, 0, tot_lo);
+                if (rt * 16 + g + 8 < p.seg_end[0]) tp_push_value(p, tp_epoch, rt * 16 + g + 8, 0, tot_hi);
+            }
+            tp_row_tile_done(p, tp_epoch, lane);
+            continue;
         }
         if (t != 0) continue;
         if (EPI == QGEMV_EPI_STORE) {
@@ -661,7 +780,7 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
 }
 
 struct QGemvConfig {
-    int nt, si, sk, occ;
+    int nt, si, sk, occ, cta_mode;
     dim3 grid;
     size_t smem;
 };
@@ -684,10 +803,20 @@ QGemvConfig pick_config(const Q4Tiled& w, int m) {
         c.nt = 0; c.sk = 1;
         c.smem = (size_t)kRingBytes + (size_t)w.kt_pad * 160;
         c.occ = std::max(1, std::min(3, (int)((227 * 1024) / (c.smem + 1024))));
+        const int slots = kSMs * c.occ;
+        if (w.row_tiles <= slots) {
+            // few row tiles: one row tile per CTA, its warps split K (no global scratch, no atomics)
+            c.cta_mode = 1;
+            c.si = 1;
+            while (c.si < kWarps && c.si * 2 <= kt4) c.si *= 2;
+            const int chunks = (w.row_tiles * c.si + kWarps - 1) / kWarps;
+            c.grid = dim3((unsigned)std::min(slots, chunks), 1, 1);
+            return c;
+        }
         c.si = 1;
         while (c.si < 16 && c.si * 4 <= kt4 && (long long)w.row_tiles * c.si < 16LL * kSMs) c.si *= 2;
         const int units = w.row_tiles * c.si;
-        c.grid = dim3((unsigned)std::min(kSMs * c.occ, (units + kWarps - 1) / kWarps), 1, 1);
+        c.grid = dim3((unsigned)std::min(slots, (units + kWarps - 1) / kWarps), 1, 1);
         return c;
     }
     c.nt = m <= 8 ? 1 : 2;
@@ -770,7 +899,7 @@ int qgemv_init() {
 
 size_t qgemv_scratch_floats(const Q4Tiled& w, int m) {
     QGemvConfig c = pick_config(w, m);
-    if (c.sk * c.si <= 1) return 0;
+    if (c.sk * c.si <= 1 || c.cta_mode) return 0;
     return (size_t)w.row_tiles * c.sk * c.si * 16 * (c.nt ? 8 * c.nt : 1);
 }
 int qgemv_counter_count(const Q4Tiled& w) { return w.row_tiles; }
@@ -784,7 +913,7 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
     }
     QGemvConfig c = pick_config(w, a.m);
     if (g_max_dyn_smem == 0 || c.smem > (size_t)g_max_dyn_smem) { set_error("qgemv: shared memory %zu exceeds the limit %d", c.smem, g_max_dyn_smem); return SWLM_ERR_INVALID; }
-    if (c.sk * c.si > 1 && (!a.partial || !a.counters)) { set_error("qgemv: split launch without scratch"); return SWLM_ERR_INVALID; }
+    if (c.sk * c.si > 1 && !c.cta_mode && (!a.partial || !a.counters)) { set_error("qgemv: split launch without scratch"); return SWLM_ERR_INVALID; }
     QGemvParams p{};
     p.tiles = w.tiles; p.sb = w.sb; p.row_tiles = w.row_tiles; p.kt4_total = w.kt_pad / 4; p.sb_f16 = w.sb_f16 ? 1 : 0;
     p.x = a.x; p.x_stride = a.x_stride; p.k = w.k;
@@ -793,7 +922,10 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
         p.seg_end[i] = a.seg_end[i] > 0 ? a.seg_end[i] : (i ? p.seg_end[i - 1] : 0);
     }
     p.m = a.m;
-    p.si = c.si; p.sk = c.sk; p.partial = a.partial; p.counters = a.counters;
+    p.si = c.si; p.sk = c.sk; p.cta_mode = c.cta_mode; p.partial = a.partial; p.counters = a.counters;
+    p.push = a.push; p.in_tp = a.in_tp; p.tp = a.tp;
+    if ((a.push || a.in_tp) && (a.tp.tp < 2 || !a.tp.epoch || !a.tp.done || !a.tp.status)) { set_error("qgemv: tensor-parallel exchange not attached"); return SWLM_ERR_STATE; }
+    if (a.in_tp && !a.norm.mode) { set_error("qgemv: a pushed partial sum must be consumed by a fused norm"); return SWLM_ERR_INVALID; }
     p.norm_mode = a.norm.mode;
     if (a.norm.mode) {
         if (w.k > 4096 || (w.k & 15) || c.sk != 1 || !a.norm.weight || a.norm.res_in == a.norm.res_out) {

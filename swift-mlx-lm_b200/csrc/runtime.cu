@@ -207,6 +207,7 @@ struct Launch {
     swlm_step norm{};
     const DenseTensor* norm_w = nullptr;
     int x_buf = -1;            // buffer the product reads (the norm's input when fused)
+    int push = 0, in_tp = 0;   // tensor parallel: partial rows pushed to all ranks / pushed partials consumed
     int res_in = 0, res_out = 0;  // physical residual buffers (0 or 1) this launch reads / writes
 };
 
@@ -424,6 +425,31 @@ int compile_plan(swlm_plan* plan) {
         }
     }
     plan->final_res = cur;
+
+    // Tensor parallel: a product over a K-sharded (row-parallel) weight yields partial sums. It pushes them
+    // to every rank, and the product that follows must be one with a fused norm, which adds them up.
+    if (ctx->tp_size > 1) {
+        for (size_t i = 0; i < plan->launches.size(); ++i) {
+            Launch& L = plan->launches[i];
+            if (L.kind == L_CONV) { set_error("short-conv layers are not supported under tensor parallelism"); return SWLM_ERR_UNSUPPORTED; }
+            if (L.kind != L_QGEMV) continue;
+            auto it = ctx->raw.find(L.st.weight);
+            if (it == ctx->raw.end() || it->second.shard_kind != SWLM_SHARD_ROW) continue;
+            if (L.n_seg != 1 || L.epilogue != QGEMV_EPI_STORE || L.seg_buf[0] != SWLM_BUF_HIDDEN || L.seg_end[0] != d.hidden) {
+                set_error("row-parallel product '%s' must write the hidden buffer", L.st.weight);
+                return SWLM_ERR_UNSUPPORTED;
+            }
+            if (i + 1 >= plan->launches.size() || plan->launches[i + 1].kind != L_QGEMV || !plan->launches[i + 1].norm.kind ||
+                plan->launches[i + 1].x_buf != SWLM_BUF_HIDDEN) {
+                set_error("row-parallel product '%s' is not followed by a product with a fused norm", L.st.weight);
+                return SWLM_ERR_UNSUPPORTED;
+            }
+            L.push = 1;
+            plan->launches[i + 1].in_tp = 1;
+            L.label = "push " + L.label;
+            plan->launches[i + 1].label = "allreduce+" + plan->launches[i + 1].label;
+        }
+    }
     return SWLM_OK;
 }
 
@@ -448,6 +474,10 @@ struct swlm_state {
     unsigned* attn_counters = nullptr;
     float* argmax_val = nullptr; int32_t* argmax_idx = nullptr;
     __nv_bfloat16* res2 = nullptr;  // second physical residual buffer (ping-pong partner of buf[RESIDUAL])
+    // tensor-parallel exchange (tp_size > 1): this rank's buffer, the peers' mappings, local counters
+    TpParams tp{};
+    bool tp_attached = false;
+    int32_t* tp_words = nullptr;  // [0] all-reduce epoch, [1] rows-done counter, [2] status, [3] argmax epoch
     int32_t* h_tok = nullptr;  // pinned host staging, 2 * max_batch
     int pos_host = 0;
     long long steps_host = 0;
@@ -512,6 +542,10 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             }
             for (int q = 0; q < L.n_seg; ++q) { a.y[q] = s->buf[L.seg_buf[q]]; a.y_stride[q] = s->width[L.seg_buf[q]]; a.seg_end[q] = L.seg_end[q]; }
             a.partial = s->qgemv_partial; a.counters = s->qgemv_counters;
+            if (L.push || L.in_tp) {
+                if (!s->tp_attached) { set_error("tensor-parallel plan: call swlm_tp_export / swlm_tp_attach on the state first"); return SWLM_ERR_STATE; }
+                a.push = L.push; a.in_tp = L.in_tp; a.tp = s->tp;
+            }
             rc = launch_qgemv(a, stream);
             s->launches += 1;
             break;
@@ -550,8 +584,14 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             s->launches += 1;
             break;
         case L_ARGMAX:
-            rc = launch_argmax(m, st.n, s->buf[st.in_buf], s->width[st.in_buf], s->token_out, s->token_in, s->ring,
-                               s->step_counter, s->ring_cap, s->position, 1, s->argmax_val, s->argmax_idx, stream);
+            if (plan->ctx->tp_size > 1 && !s->tp_attached) { set_error("tensor-parallel plan: call swlm_tp_export / swlm_tp_attach on the state first"); return SWLM_ERR_STATE; }
+            {
+                // a vocabulary-sharded output head gives local indices; shift them to global ones
+                const int local_n = plan->ctx->tp_size > 1 ? st.n / plan->ctx->tp_size : st.n;
+                rc = launch_argmax(m, local_n, s->buf[st.in_buf], s->width[st.in_buf], s->token_out, s->token_in, s->ring,
+                                   s->step_counter, s->ring_cap, s->position, 1, s->argmax_val, s->argmax_idx, s->tp,
+                                   s->tp_words ? s->tp_words + 3 : nullptr, plan->ctx->tp_rank * local_n, stream);
+            }
             s->launches += 2;
             advanced = true;
             break;
@@ -859,6 +899,12 @@ void swlm_state_destroy(swlm_state* s) {
     drop_graphs(s);
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->buf[i]);
     cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->conv); cudaFree(s->res2);
+    if (s->tp.tp > 1) {
+        for (int r = 0; r < s->tp.tp; ++r)
+            if (r != s->tp.rank && s->tp_attached && s->tp.peer[r]) cudaIpcCloseMemHandle(s->tp.peer[r]);
+        cudaFree(s->tp.peer[s->tp.rank]);
+    }
+    cudaFree(s->tp_words);
     cudaFree(s->position); cudaFree(s->step_counter); cudaFree(s->token_in); cudaFree(s->token_out); cudaFree(s->ring);
     cudaFree(s->prompt);
     cudaFree(s->attn_scratch); cudaFree(s->qgemv_partial); cudaFree(s->qgemv_counters); cudaFree(s->attn_counters);
@@ -1134,6 +1180,75 @@ int swlm_run_step(swlm_state* s, const swlm_step* step, const int32_t* token_in,
 }
 
 int64_t swlm_launches(const swlm_state* s) { return s ? s->launches : 0; }
+
+int swlm_tp_export(swlm_state* s, void* handle_out) {
+    if (!s || !handle_out) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    swlm_ctx* ctx = s->plan->ctx;
+    if (ctx->tp_size < 2) { set_error("context was created with tp_size 1"); return SWLM_ERR_STATE; }
+    if (ctx->tp_size > kTpMax) { set_error("tp_size %d exceeds %d", ctx->tp_size, kTpMax); return SWLM_ERR_UNSUPPORTED; }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    if (!s->tp.peer[ctx->tp_rank]) {
+        s->tp.tp = ctx->tp_size; s->tp.rank = ctx->tp_rank;
+        s->tp.lay = TpLayout{ctx->tp_size, s->plan->desc.max_batch, s->plan->desc.hidden};
+        unsigned char* buf = nullptr;
+        if ((rc = dev_alloc(&buf, s->tp.lay.total()))) return rc;
+        SWLM_CUDA(cudaMemset(buf, 0, s->tp.lay.total()));
+        s->tp.peer[ctx->tp_rank] = buf;
+        if ((rc = dev_alloc(&s->tp_words, 4))) return rc;
+        SWLM_CUDA(cudaMemset(s->tp_words, 0, 16));
+        s->tp.epoch = s->tp_words; s->tp.done = reinterpret_cast<unsigned*>(s->tp_words + 1); s->tp.status = s->tp_words + 2;
+        SWLM_CUDA(cudaDeviceSynchronize());
+    }
+    cudaIpcMemHandle_t h;
+    SWLM_CUDA(cudaIpcGetMemHandle(&h, s->tp.peer[ctx->tp_rank]));
+    static_assert(sizeof(h) == SWLM_TP_HANDLE_BYTES, "IPC handle size");
+    memcpy(handle_out, &h, sizeof(h));
+    return SWLM_OK;
+}
+
+int swlm_tp_attach(swlm_state* s, const void* handles) {
+    if (!s || !handles) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    swlm_ctx* ctx = s->plan->ctx;
+    if (ctx->tp_size < 2 || !s->tp.peer[ctx->tp_rank]) { set_error("call swlm_tp_export first"); return SWLM_ERR_STATE; }
+    if (s->tp_attached) return SWLM_OK;
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    const unsigned char* hb = static_cast<const unsigned char*>(handles);
+    for (int r = 0; r < ctx->tp_size; ++r) {
+        if (r == ctx->tp_rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, hb + (size_t)r * SWLM_TP_HANDLE_BYTES, sizeof(h));
+        void* p = nullptr;
+        SWLM_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        s->tp.peer[r] = static_cast<unsigned char*>(p);
+    }
+    s->tp_attached = true;
+    drop_graphs(s);
+    return SWLM_OK;
+}
+
+int swlm_tp_status(swlm_state* s) {
+    if (!s) { set_error("null state"); return SWLM_ERR_INVALID; }
+    if (!s->tp_words) return SWLM_OK;
+    int32_t w[4];
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    SWLM_CUDA(cudaMemcpy(w, s->tp_words, sizeof(w), cudaMemcpyDeviceToHost));
+    if (w[2]) { set_error("a bounded wait on another rank expired (all-reduce epoch %d, argmax epoch %d)", w[0], w[3]); return SWLM_ERR_TIMEOUT; }
+    return SWLM_OK;
+}
+
+/* Rank-local slice of an n x k tensor under a shard kind: out = {row0, rows, col0, cols}. Host-only. */
+int swlm_shard_range(int shard_kind, int n, int k, int tp_rank, int tp_size, int* out4) {
+    if (!out4 || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    swlm_ctx fake;
+    fake.tp_rank = tp_rank; fake.tp_size = tp_size;
+    Slice sl;
+    int rc = shard_slice(&fake, shard_kind, n, k, &sl);
+    if (rc) return rc;
+    out4[0] = sl.row0; out4[1] = sl.rows; out4[2] = sl.col0; out4[3] = sl.cols;
+    return SWLM_OK;
+}
 
 int swlm_profile_kind(swlm_state* s, int step_kind, int repeats) {
     if (!s || repeats < 0) { set_error("bad argument"); return SWLM_ERR_INVALID; }

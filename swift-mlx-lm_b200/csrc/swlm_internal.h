@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "../../include/swlm.h"
+#include "tp_device.cuh"
 
 namespace swlm {
 
@@ -115,6 +116,8 @@ struct XNorm {
 struct QGemvLaunch {
     const Q4Tiled* w = nullptr;
     XNorm norm;
+    int push = 0, in_tp = 0;   // tensor parallel: push partial rows to every rank / consume pushed partials
+    TpParams tp{};
     const __nv_bfloat16* x = nullptr;  // [m][x_stride]
     int x_stride = 0;
     // result rows [0, seg_end[0]) go to y[0], [seg_end[0], seg_end[1]) to y[1], ... each [m][y_stride[i]]
@@ -150,7 +153,8 @@ int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t st
 // increments the device-side position and step counter. Two launches.
 int launch_argmax(int m, int n, const __nv_bfloat16* logits, int stride, int32_t* token_out,
                   int32_t* token_in_next, int32_t* ring, int32_t* step_counter, int ring_cap,
-                  int32_t* position, int advance, float* scratch_val, int32_t* scratch_idx, cudaStream_t s);
+                  int32_t* position, int advance, float* scratch_val, int32_t* scratch_idx, const TpParams& tp,
+                  int32_t* am_epoch, int shard_offset, cudaStream_t s);
 size_t argmax_scratch_elems(int m);
 
 struct AttnLaunch {

@@ -1,0 +1,66 @@
+// Device side of the tensor-parallel exchange: a one-shot push all-reduce fused into the row-parallel
+// product that produces the partial sums and the product that consumes them.
+//
+// The reference has no multi-device code; this is the sm_100a design for "one all-reduce per attention
+// and MLP block". Every rank owns one exchange buffer, mapped into every other rank's address space
+// (cudaIpc handles). The producing kernel stores its fp32 partial row straight into every rank's
+// buffer over NVLink (plain peer stores: the data lands in the consumer's own memory), then raises a
+// per-source flag with the epoch number. The consuming kernel polls its own flags, adds the partials in
+// rank order (the same order on every rank, so all ranks continue with bit-identical activations) and
+// goes on with the residual add and the norm. Two parities of buffers suffice: a rank can only be one
+// exchange ahead of the slowest rank. Every wait is bounded; on expiry an error word is set and the
+// kernel carries on with whatever it has, so a missing rank surfaces as a status, not as a hung GPU.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+namespace swlm {
+
+constexpr int kTpMax = 8;
+
+struct TpLayout {
+    int tp, batch, hidden;
+    __host__ __device__ size_t flags_ar(int par, int src) const { return ((size_t)par * kTpMax + src) * 4; }
+    __host__ __device__ size_t flags_am(int par, int src) const { return 64 + ((size_t)par * kTpMax + src) * 4; }
+    __host__ __device__ size_t recv_ar(int par, int src, int b) const { return 256 + ((((size_t)par * tp + src) * batch + b) * hidden) * 4; }
+    __host__ __device__ size_t recv_am(int par, int src, int b) const { return 256 + (size_t)2 * tp * batch * hidden * 4 + (((size_t)par * tp + src) * batch + b) * 8; }
+    __host__ __device__ size_t total() const { return 256 + (size_t)2 * tp * batch * hidden * 4 + (size_t)2 * tp * batch * 8; }
+};
+
+// What a kernel needs to take part in an exchange. tp == 1: unused.
+struct TpParams {
+    int tp, rank;
+    TpLayout lay;
+    unsigned char* peer[kTpMax];  // exchange buffers of all ranks; peer[rank] is this rank's own
+    int* epoch;                   // local: number of all-reduces completed so far
+    unsigned* done;               // local: row tiles of the current product already pushed
+    int* status;                  // local: set to non-zero when a bounded wait expired
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+constexpr int kTpSpinLimit = 1 << 21;  // polls of ~128 ns each: about a quarter of a second
+
+// Wait (bounded) until every source has raised flag `epoch` on this rank. One lane per source.
+__device__ __forceinline__ void tp_wait_flags(const TpParams& tp, const unsigned char* own, size_t flag_off0, int epoch, int lane_src) {
+    if (lane_src < tp.tp) {
+        const unsigned* f = reinterpret_cast<const unsigned*>(own + flag_off0 + (size_t)lane_src * 4);
+        int spins = 0;
+        while ((int)ld_acquire_sys(f) < epoch) {
+            if (++spins > kTpSpinLimit) { atomicExch(tp.status, 1); break; }
+            __nanosleep(128);
+        }
+    }
+}
+#endif
+
+}  // namespace swlm

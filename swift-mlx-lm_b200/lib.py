@@ -101,6 +101,10 @@ SIGNATURES = {
     "swlm_run_step": (_I, [_P, C.POINTER(Step), _P, _P]),
     "swlm_launches": (C.c_int64, [_P]),
     "swlm_profile_kind": (_I, [_P, _I, _I]),
+    "swlm_tp_export": (_I, [_P, _P]),
+    "swlm_tp_attach": (_I, [_P, _P]),
+    "swlm_tp_status": (_I, [_P]),
+    "swlm_shard_range": (_I, [_I, _I, _I, _I, _I, C.POINTER(_I)]),
     "swlm_op_qgemm": (_I, [_P, C.c_char_p, _I, _P, _P]),
     "swlm_op_qgemm_dev": (_I, [_P, C.c_char_p, _I, _P, _P, _P]),
     "swlm_op_dequant_bf16": (_I, [_P, C.c_char_p, _P]),
