@@ -177,6 +177,23 @@ int swlm_op_flash_decode_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int 
                              int ctx_stride, float scale, const void* q_dev, const void* k_dev,
                              const void* v_dev, void* out_dev, void* scratch_dev, void* cuda_stream);
 
+/* Flash-decode that allocates nothing. No counterpart in the reference.
+ * For callers that are not allowed to allocate device memory while running: a serving process that
+ * reserved its whole budget at start-up and forbids later cudaMalloc (it synchronises the device and may
+ * fail under pressure), or an embedder whose runtime owns the allocator. Same arguments and result as
+ * swlm_op_flash_decode_dev, but the split kernel's partials and arrival counters live in an 8 MiB array
+ * built into the library (held by every GPU that loads it, until the process exits) instead of in scratch
+ * the caller or the library allocates; the call issues no cudaMalloc/cudaFree.
+ * Limits and rules: a request whose scratch need exceeds swlm_op_flash_decode_noalloc_capacity() bytes
+ * (roughly batch x heads x splits x (head_dim + 2) x 4) is rejected with SWLM_ERR_INVALID. The first call on
+ * a device resolves the array's device address; make that first call before any stream capture. All calls
+ * share the array: it keeps the last call's contents (the counters are cleared on the call's stream before
+ * each launch), and two calls that overlap on the GPU race on it — keep them ordered. */
+size_t swlm_op_flash_decode_noalloc_capacity(void);
+int swlm_op_flash_decode_noalloc_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int hd, int ctx_len,
+                                     int ctx_stride, float scale, const void* q_dev, const void* k_dev,
+                                     const void* v_dev, void* out_dev, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -448,4 +448,47 @@ int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_le
     return launch_both<false>(p, m, hd, s);
 }
 
+// ---- allocation-free flash-decode ---------------------------------------------------------------------
+// Some embedders may not allocate device memory once they are running: a serving loop that reserved its
+// whole memory budget at start-up and treats any later cudaMalloc as a bug (it synchronises the device and
+// can fail under memory pressure), or a host runtime that owns the allocator and hands this library no
+// pool of its own. For them the partial results and arrival counters of the split kernel live in a fixed
+// array that is part of the loaded module instead of in caller- or library-allocated scratch.
+//
+// The array is 8 MiB on every GPU that loads the library, for the life of the process. All calls share it
+// and it keeps the previous call's contents: the counters are cleared (asynchronously, on the call's
+// stream) before every launch, the partials are overwritten before they are read. Two calls that overlap
+// on the GPU (different streams, no ordering between them) would race on it; serialise them.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_flash_static_scratch[kStaticScratchBytes];
+static void* g_flash_static_addr[64] = {};  // device address of the array, per device ordinal
+
+size_t flash_decode_static_capacity() { return kStaticScratchBytes; }
+
+int launch_flash_decode_static(int device, int m, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, float scale,
+                               const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, __nv_bfloat16* out,
+                               cudaStream_t s) {
+    if (device < 0 || device >= 64) { set_error("flash-decode (static scratch): device ordinal %d out of range", device); return SWLM_ERR_INVALID; }
+    if (!g_flash_static_addr[device]) {
+        // In host code the array's name is only a handle; the kernel needs the device address, which the
+        // runtime resolves for the device that is current now. Done once per device, on the first call.
+        void* addr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&addr, g_flash_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(flash-decode static scratch)");
+        g_flash_static_addr[device] = addr;
+    }
+    const int splits = attn_pick_splits(m, kv_heads, ctx_len);
+    const size_t counter_bytes = (((size_t)m * kv_heads * sizeof(unsigned)) + 255) / 256 * 256;
+    const size_t need = counter_bytes + attn_scratch_floats(m, heads, hd, splits) * sizeof(float);
+    if (need > kStaticScratchBytes) {
+        set_error("flash-decode (static scratch): batch %d x %d heads x %d splits needs %zu bytes, the built-in scratch holds %zu",
+                  m, heads, splits, need, kStaticScratchBytes);
+        return SWLM_ERR_INVALID;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_flash_static_addr[device]);
+    SWLM_CUDA(cudaMemsetAsync(base, 0, counter_bytes, s));  // arrival counters must start at zero
+    return launch_flash_decode_plain(m, heads, kv_heads, hd, ctx_len, ctx_stride, scale, q, k, v, out,
+                                     reinterpret_cast<float*>(base + counter_bytes), reinterpret_cast<unsigned*>(base), splits, s);
+}
+
 }  // namespace swlm

@@ -1384,4 +1384,21 @@ int swlm_op_flash_decode_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int 
                                      flash_splits(b, kv_heads, ctx_len), stream);
 }
 
+int swlm_op_flash_decode_noalloc_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride,
+                                     float scale, const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev,
+                                     void* cuda_stream) {
+    if (!ctx || !q_dev || !k_dev || !v_dev || !out_dev || b <= 0 || ctx_len <= 0 || ctx_len > ctx_stride) {
+        set_error("bad argument");
+        return SWLM_ERR_INVALID;
+    }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    cudaStream_t stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->stream;
+    return launch_flash_decode_static(ctx->device, b, heads, kv_heads, hd, ctx_len, ctx_stride, scale,
+                                      static_cast<const __nv_bfloat16*>(q_dev), static_cast<const __nv_bfloat16*>(k_dev),
+                                      static_cast<const __nv_bfloat16*>(v_dev), static_cast<__nv_bfloat16*>(out_dev), stream);
+}
+
+size_t swlm_op_flash_decode_noalloc_capacity(void) { return flash_decode_static_capacity(); }
+
 }  // extern "C"

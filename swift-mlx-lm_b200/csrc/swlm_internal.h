@@ -184,6 +184,10 @@ int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_le
                               const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                               __nv_bfloat16* out, float* scratch, unsigned* counters, int splits, cudaStream_t s);
 int attn_init();
+size_t flash_decode_static_capacity();
+int launch_flash_decode_static(int device, int m, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, float scale,
+                               const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, __nv_bfloat16* out,
+                               cudaStream_t s);
 
 int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s);
 int launch_advance(int32_t* position, int32_t* step_counter, cudaStream_t s);

@@ -110,6 +110,8 @@ SIGNATURES = {
     "swlm_op_dequant_bf16": (_I, [_P, C.c_char_p, _P]),
     "swlm_op_flash_decode_scratch_bytes": (C.c_size_t, [_I, _I, _I, _I, _I]),
     "swlm_op_flash_decode_dev": (_I, [_P, _I, _I, _I, _I, _I, _I, C.c_float, _P, _P, _P, _P, _P, _P]),
+    "swlm_op_flash_decode_noalloc_capacity": (C.c_size_t, []),
+    "swlm_op_flash_decode_noalloc_dev": (_I, [_P, _I, _I, _I, _I, _I, _I, C.c_float, _P, _P, _P, _P, _P]),
 }
 
 
