@@ -187,12 +187,10 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {
                 const uint4 kk = kreg[nt][i];
-                mma_bf16(sacc[nt], qhi[i][0], 0u, qhi[i][1], 0u, kk.x, kk.y);
-                mma_bf16(sacc[nt], qhi[i][2], 0u, qhi[i][3], 0u, kk.z, kk.w);
-                if (DECODE) {
-                    mma_bf16(sacc[nt], qlo[i][0], 0u, qlo[i][1], 0u, kk.x, kk.y);
-                    mma_bf16(sacc[nt], qlo[i][2], 0u, qlo[i][3], 0u, kk.z, kk.w);
-                }
+                // rows g carry the high parts of q, rows g + 8 the low parts: one instruction forms both
+                // products, and their sum is taken in-lane below
+                mma_bf16(sacc[nt], qhi[i][0], qlo[i][0], qhi[i][1], qlo[i][1], kk.x, kk.y);
+                mma_bf16(sacc[nt], qhi[i][2], qlo[i][2], qhi[i][3], qlo[i][3], kk.z, kk.w);
             }
         }
         // online softmax in the log2 domain; row g lives in the four lanes t = 0..3
@@ -203,7 +201,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int tok = tok0 + 8 * nt + 2 * t + e;
-                sv[nt][e] = tok < t_end ? sacc[nt][e] * p.scale_log2 : -INFINITY;
+                sv[nt][e] = tok < t_end ? (sacc[nt][e] + sacc[nt][2 + e]) * p.scale_log2 : -INFINITY;
                 rmax = fmaxf(rmax, sv[nt][e]);
             }
         rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
@@ -222,7 +220,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
 #pragma unroll
             for (int hh = 0; hh < VH; ++hh)
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { oacc[hh][u][0] *= corr; oacc[hh][u][1] *= corr; }
+                for (int u = 0; u < 8; ++u) { oacc[hh][u][0] *= corr; oacc[hh][u][1] *= corr; oacc[hh][u][2] *= corr; oacc[hh][u][3] *= corr; }
         }
         // O += P . V ; dimension 64*hh + 8*col + u sits in n-tile (hh, u), column col. P is fed as a bf16
         // hi + lo pair: a single bf16 P (8 mantissa bits) costs ~2 bf16 ulps of the output at short contexts.
@@ -245,10 +243,9 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
             for (int w = 0; w < 4; ++w) {
                 const unsigned b0e = __byte_perm(aw[w], bw[w], 0x5410), b1e = __byte_perm(cw[w], dw[w], 0x5410);
                 const unsigned b0o = __byte_perm(aw[w], bw[w], 0x7632), b1o = __byte_perm(cw[w], dw[w], 0x7632);
-                mma_bf16(oacc[hh][2 * w], pa0, 0u, pa2, 0u, b0e, b1e);
-                mma_bf16(oacc[hh][2 * w], pl0, 0u, pl2, 0u, b0e, b1e);
-                mma_bf16(oacc[hh][2 * w + 1], pa0, 0u, pa2, 0u, b0o, b1o);
-                mma_bf16(oacc[hh][2 * w + 1], pl0, 0u, pl2, 0u, b0o, b1o);
+                // rows g: high part of P, rows g + 8: low part; added when the accumulators are read out
+                mma_bf16(oacc[hh][2 * w], pa0, pl0, pa2, pl2, b0e, b1e);
+                mma_bf16(oacc[hh][2 * w + 1], pa0, pl0, pa2, pl2, b0o, b1o);
             }
         }
     }
@@ -261,8 +258,8 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         for (int hh = 0; hh < VH; ++hh)
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                osm[warp][g][64 * hh + 8 * (2 * t) + u] = oacc[hh][u][0];
-                osm[warp][g][64 * hh + 8 * (2 * t + 1) + u] = oacc[hh][u][1];
+                osm[warp][g][64 * hh + 8 * (2 * t) + u] = oacc[hh][u][0] + oacc[hh][u][2];
+                osm[warp][g][64 * hh + 8 * (2 * t + 1) + u] = oacc[hh][u][1] + oacc[hh][u][3];
             }
         if (t == 0) { msm[warp][g] = m_run; lsm[warp][g] = l_run; }
     }

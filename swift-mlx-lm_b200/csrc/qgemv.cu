@@ -49,6 +49,7 @@ struct QGemvParams {
     int y_stride[3], seg_end[3];
     int m;
     int si, sk;   // k-slices per CTA group, CTA groups along K
+    int si_shift; // log2(si) for the batch-1 kernel
     int cta_mode; // batch-1 kernel: slices of a row tile live in one CTA and meet in shared memory
     float* partial;
     unsigned* counters;
@@ -526,6 +527,13 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
 // instruction serves both; the integer sums are exact, and the group's scale and zero are applied once in
 // fp32. Same tiles, ring and unit scheduling as above.
 // =================================================================================================
+__device__ __forceinline__ void imma_u8s8_zero(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    const int z = 0;
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
 __device__ __forceinline__ void imma_u8s8(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -547,56 +555,56 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
     // Two ways of dealing out the (row tile, k-slice) units. cta_mode (matrices with no more row tiles than
     // resident CTAs): a CTA takes eight consecutive units at a time, i.e. all slices of 8/si row tiles, and
     // adds the slices through shared memory. Otherwise every CTA owns an equal contiguous share, its warps
-    // take units round-robin and the slices of a row tile meet in global scratch.
-    const int units = p.row_tiles * p.si;
+    // take units round-robin and the slices of a row tile meet in global scratch. si is a power of two.
+    const int units = p.row_tiles << p.si_shift;
     const int u_lo = (int)(((long long)blockIdx.x * units) / gridDim.x);
     const int u_hi = (int)(((long long)(blockIdx.x + 1) * units) / gridDim.x);
     const int u_first = p.cta_mode ? blockIdx.x * kWarps : u_lo;
     const int u_end = p.cta_mode ? units : u_hi;
     const int u_limit = p.cta_mode ? ((units + kWarps - 1) / kWarps) * kWarps : u_hi;  // uniform across the CTA
     const int u_stride = p.cta_mode ? gridDim.x * kWarps : kWarps;
-    auto open_unit = [&](UnitCursor& c) {
-        if (c.u < c.u_end) {
-            c.rt = c.u / p.si;
-            const int s = c.u - c.rt * p.si;
-            c.st = (s * p.kt4_total) / p.si;
-            c.st_end = ((s + 1) * p.kt4_total) / p.si;
-        }
+    const int si_mask = (1 << p.si_shift) - 1;
+    // stages are addressed by one absolute index a = rt * kt4_total + st: tiles at a * 128, pairs at a * 16
+    auto unit_range = [&](int u, int& a0, int& a1) {
+        const int rt = u >> p.si_shift, sl = u & si_mask;
+        a0 = rt * p.kt4_total + ((sl * p.kt4_total) >> p.si_shift);
+        a1 = rt * p.kt4_total + (((sl + 1) * p.kt4_total) >> p.si_shift);
     };
-    UnitCursor ic{u_first + warp, u_end, 0, 0, 0};   // cp.async side, kStages-1 stages ahead of the math
-    UnitCursor pc{u_first + warp, u_end, 0, 0, 0};   // L2 prefetch side, kL2Ahead stages further ahead
-    open_unit(ic);
-    open_unit(pc);
-    auto prefetch_next = [&]() {
-        while (pc.u < pc.u_end && pc.st >= pc.st_end) { pc.u += u_stride; open_unit(pc); }
-        if (pc.u < pc.u_end) {
-            const size_t stage = (size_t)pc.rt * p.kt4_total + pc.st;
-            if (lane < 16) prefetch_l2(reinterpret_cast<const unsigned char*>(p.tiles + stage * 128) + lane * 128);
-            else if (lane < 18) prefetch_l2(reinterpret_cast<const unsigned char*>(p.sb + stage * 16) + (lane - 16) * 128);
-            pc.st += 1;
-        }
-    };
+    // cp.async side: runs kStages-1 stages ahead of the math, across unit boundaries
+    int iu = u_first + warp, ia = 0, ia_end = 0;
+    if (iu < u_end) unit_range(iu, ia, ia_end);
+    const unsigned ring_sa = (unsigned)__cvta_generic_to_shared(my_ring) + lane * 16;
+    const bool sb_lane = lane < 16;
     auto issue = [&](int slot) {
-        while (ic.u < ic.u_end && ic.st >= ic.st_end) { ic.u += u_stride; open_unit(ic); }
-        if (ic.u < ic.u_end) {
-            unsigned char* dst = my_ring + slot * kStageBytes;
-            const uint4* src = p.tiles + ((size_t)ic.rt * p.kt4_total + ic.st) * 128;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) cp_async16(dst + (q * 32 + lane) * 16, src + q * 32 + lane);
-            if (lane < 16) cp_async16(dst + 2048 + lane * 16, p.sb + ((size_t)ic.rt * p.kt4_total + ic.st) * 16 + lane);
-            ic.st += 1;
+        if (ia == ia_end && iu < u_end) {
+            iu += u_stride;
+            if (iu < u_end) unit_range(iu, ia, ia_end);
+        }
+        if (iu < u_end) {
+            const unsigned dst = ring_sa + slot * kStageBytes;
+            const uint4* src = p.tiles + (size_t)ia * 128 + lane;
+            asm volatile(
+                "cp.async.cg.shared.global [%0], [%1], 16;\n"
+                "cp.async.cg.shared.global [%0+512], [%1+512], 16;\n"
+                "cp.async.cg.shared.global [%0+1024], [%1+1024], 16;\n"
+                "cp.async.cg.shared.global [%0+1536], [%1+1536], 16;\n" ::"r"(dst), "l"(src) : "memory");
+            if (sb_lane) {
+                const uint4* ssrc = p.sb + (size_t)ia * 16 + lane;
+                asm volatile("cp.async.cg.shared.global [%0+2048], [%1], 16;\n" ::"r"(dst), "l"(ssrc) : "memory");
+            }
+            // HBM -> L2 a few stages further ahead inside the same unit (one 128-byte line per lane)
+            if (sb_lane && ia + kL2Ahead < ia_end)
+                prefetch_l2(reinterpret_cast<const unsigned char*>(p.tiles + (size_t)(ia + kL2Ahead) * 128) + lane * 128);
+            ++ia;
         }
         cp_async_commit();
-        prefetch_next();
     };
     // Weights do not depend on the preceding kernel: the ring starts filling before its results are awaited.
     // HBM keeps streaming into L2 while the activations are prepared: the ring alone holds 4.6 KB per warp.
     pdl_launch_dependents();
-    int issued = 0, consumed = 0;
+    int islot = 0, cslot = 0;  // ring slots of the next stage to issue / to consume
 #pragma unroll
-    for (int i = 0; i < kL2Ahead; ++i) prefetch_next();
-#pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) { issue(issued % kStages); ++issued; }
+    for (int i = 0; i < kStages - 1; ++i) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
     pdl_wait();
 
     // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
@@ -665,46 +673,60 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
     }
     __syncthreads();
 
-    const int s_total = p.si;
+    const int s_total = 1 << p.si_shift;
     __shared__ float cta_red[2][kWarps][16];
+    __shared__ __align__(16) unsigned zero16[4];
+    if (tid < 4) zero16[tid] = 0u;
+    __syncthreads();
+    // B operand source: lanes g = 0 / 1 read the high / low digits of their quarter of the group, all other
+    // lanes (columns 2..7) read zeros; expressed as a base pointer and a per-tile stride so that the tile
+    // loop is branch-free
+    const unsigned char* xq_bytes = reinterpret_cast<const unsigned char*>(xq);
+    const unsigned char* zero_bytes = reinterpret_cast<const unsigned char*>(zero16);
+    const bool xlane = g < 2;
+    const int xlane_off = t * 32 + g * 16;
+    const int xtile_stride = xlane ? 128 : 0;
     int round = 0;
     for (int base = u_first; base < u_limit; base += u_stride, ++round) {
-        UnitCursor cc{base + warp, u_end, 0, 0, 0};
-        const bool valid = cc.u < cc.u_end;
-        open_unit(cc);
-        const int rt = cc.rt;
-        const int slice = cc.u - rt * p.si;
+        const int u = base + warp;
+        const bool valid = u < u_end;
+        const int rt = u >> p.si_shift;
+        const int slice = u & si_mask;
         float tot_lo = 0.f, tot_hi = 0.f;
-        for (int stg = cc.st; valid && stg < cc.st_end; ++stg) {
-            issue(issued % kStages); ++issued;
+        int a0 = 0, a1 = 0;
+        if (valid) unit_range(u, a0, a1);
+        for (int a = a0; a < a1; ++a) {
+            issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1;
             cp_async_wait<kStages - 1>();
             __syncwarp();
-            const unsigned char* st = my_ring + (consumed % kStages) * kStageBytes;
-            ++consumed;
+            const unsigned char* st = my_ring + cslot * kStageBytes;
+            cslot = cslot + 1 == kStages ? 0 : cslot + 1;
             const uint4* wsm = reinterpret_cast<const uint4*>(st) + lane;
             const uint4 sA = reinterpret_cast<const uint4*>(st + 2048)[g];
             const uint4 sB = reinterpret_cast<const uint4*>(st + 2048)[g + 8];
             const unsigned sAw[4] = {sA.x, sA.y, sA.z, sA.w};
             const unsigned sBw[4] = {sB.x, sB.y, sB.z, sB.w};
-            const uint4* xrun = xq + ((size_t)stg * 16 + t) * 2 + (g & 1);
-            const float2* mrun = xmeta + (size_t)stg * 4;
+            const int stg = a - rt * p.kt4_total;
+            const unsigned char* xbase = xlane ? xq_bytes + (size_t)stg * 512 + xlane_off : zero_bytes;
+            const float4* mrun = reinterpret_cast<const float4*>(xmeta + (size_t)stg * 4);
+            const float4 m01 = mrun[0], m23 = mrun[1];
+            const float mscale[4] = {m01.x, m01.z, m23.x, m23.z};
+            const float msum[4] = {m01.y, m01.w, m23.y, m23.w};
 #pragma unroll
             for (int ti = 0; ti < 4; ++ti) {
                 const uint4 wv = wsm[ti * 32];
                 // B operand: column 0 = high digits, column 1 = low digits of the activations, the rest zero
-                uint4 xd = make_uint4(0, 0, 0, 0);
-                if (g < 2) xd = xrun[ti * 8];
-                const float2 meta = mrun[ti];
-                int c[4] = {0, 0, 0, 0};
+                const uint4 xd = *reinterpret_cast<const uint4*>(xbase + ti * xtile_stride);
+                int c[4];
                 // rows g take the low nibble of every byte, rows g + 8 the high nibble: exact 8-bit integers
-                imma_u8s8(c, wv.x & 0x0F0F0F0Fu, (wv.x >> 4) & 0x0F0F0F0Fu, wv.y & 0x0F0F0F0Fu, (wv.y >> 4) & 0x0F0F0F0Fu, xd.x, xd.y);
+                imma_u8s8_zero(c, wv.x & 0x0F0F0F0Fu, (wv.x >> 4) & 0x0F0F0F0Fu, wv.y & 0x0F0F0F0Fu, (wv.y >> 4) & 0x0F0F0F0Fu, xd.x, xd.y);
                 imma_u8s8(c, wv.z & 0x0F0F0F0Fu, (wv.z >> 4) & 0x0F0F0F0Fu, wv.w & 0x0F0F0F0Fu, (wv.w >> 4) & 0x0F0F0F0Fu, xd.z, xd.w);
                 // lanes t == 0 hold columns 0 and 1 of rows g and g + 8: sum(q * x) = 256 * hi + lo, exactly
                 const float fa = (float)(c[0] * 256 + c[1]), fb = (float)(c[2] * 256 + c[3]);
-                const float s_lo = sb_scale<F16SB>(sAw[ti]) * meta.x, z_lo = sb_zero<F16SB>(sAw[ti]);
-                const float s_hi = sb_scale<F16SB>(sBw[ti]) * meta.x, z_hi = sb_zero<F16SB>(sBw[ti]);
-                tot_lo = fmaf(s_lo, fa, fmaf(z_lo, meta.y, tot_lo));
-                tot_hi = fmaf(s_hi, fb, fmaf(z_hi, meta.y, tot_hi));
+                const float s_lo = sb_scale<F16SB>(sAw[ti]) * mscale[ti], z_lo = sb_zero<F16SB>(sAw[ti]);
+                const float s_hi = sb_scale<F16SB>(sBw[ti]) * mscale[ti], z_hi = sb_zero<F16SB>(sBw[ti]);
+                tot_lo = fmaf(s_lo, fa, fmaf(z_lo, msum[ti], tot_lo));
+                tot_hi = fmaf(s_hi, fb, fmaf(z_hi, msum[ti], tot_hi));
             }
             __syncwarp();
         }
@@ -726,8 +748,7 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
                 }
             }
         } else if (s_total > 1 && valid) {
-            const int s_glob = slice;
-            float* dst = p.partial + ((size_t)rt * s_total + s_glob) * 16;
+            float* dst = p.partial + ((size_t)rt * s_total + slice) * 16;
             if (t == 0) { __stcg(dst + g, tot_lo); __stcg(dst + g + 8, tot_hi); }
             __threadfence();
             __syncwarp();
@@ -922,7 +943,9 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
         p.seg_end[i] = a.seg_end[i] > 0 ? a.seg_end[i] : (i ? p.seg_end[i - 1] : 0);
     }
     p.m = a.m;
-    p.si = c.si; p.sk = c.sk; p.cta_mode = c.cta_mode; p.partial = a.partial; p.counters = a.counters;
+    p.si = c.si; p.sk = c.sk; p.cta_mode = c.cta_mode;
+    p.si_shift = 0;
+    while ((1 << p.si_shift) < c.si) ++p.si_shift; p.partial = a.partial; p.counters = a.counters;
     p.push = a.push; p.in_tp = a.in_tp; p.tp = a.tp;
     if ((a.push || a.in_tp) && (a.tp.tp < 2 || !a.tp.epoch || !a.tp.done || !a.tp.status)) { set_error("qgemv: tensor-parallel exchange not attached"); return SWLM_ERR_STATE; }
     if (a.in_tp && !a.norm.mode) { set_error("qgemv: a pushed partial sum must be consumed by a fused norm"); return SWLM_ERR_INVALID; }
