@@ -37,6 +37,14 @@ def measured_peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def measured_tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
 
@@ -177,6 +185,16 @@ def run_op(args, pkg):
         us = e0.elapsed_time(e1) * 1e3 / (args.steps * sets)
         bytes_per_launch = per_set + 2 * m * k + 2 * m * n
         gbs = bytes_per_launch / (us * 1e-6) / 1e9
+        if m >= 64:  # tensor-core (tcgen05) prefill product: the bound is the tensor pipe, not HBM
+            tfs = 2.0 * m * n * k / (us * 1e-6) / 1e12
+            tpeak, tsrc = measured_tensor_peak()
+            print(json.dumps({"metric": "q4 prefill GEMM TFLOP/s", "value": tfs, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+                              "config": {"workload": f"q4g64 GEMM N={n} K={k} M={m} (tcgen05), {sets} distinct weight sets in rotation"},
+                              "us_per_launch": us, "flops_per_launch": 2.0 * m * n * k, "weight_stream_gbs": gbs,
+                              "roofline": {"bound": "tensor", "achieved": tfs, "peak": tpeak, "unit": "TFLOP/s", "frac": tfs / tpeak,
+                                           "peak_source": tsrc, "traffic": None}}))
+            store.close()
+            return
         print(json.dumps({"metric": "qGEMV HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
                           "config": {"workload": f"q4g64 GEMV N={n} K={k} M={m}, {sets} distinct weight sets in rotation ({sets * per_set / 1e6:.0f} MB > L2)"},
                           "us_per_launch": us, "bytes_per_launch": bytes_per_launch,
@@ -390,6 +408,8 @@ def main():
             "cpu_baseline": base,
         }
         print(json.dumps(line))
+    model.close()
+    store.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -57,6 +57,8 @@ const char* swlm_last_error(void);
  * device tensor map. Quantized tensors are re-tiled once, at upload, into the
  * layout the GEMV kernels stream. */
 int swlm_ctx_create(int device_id, int tp_rank, int tp_size, swlm_ctx** out);
+/* Plans keep their context alive and states their plan: destroying an object that still has users is deferred
+ * until the last of them is destroyed, so wrappers may release context, plan and state in any order. */
 void swlm_ctx_destroy(swlm_ctx* ctx);
 
 /* MLX affine source format: weight u32[n][k/8] (8 nibbles per word, LSB first
@@ -96,6 +98,12 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out);
 void swlm_state_destroy(swlm_state* state);
 /* Launch on this CUDA stream (a cudaStream_t) instead of the state's own. */
 int swlm_state_set_stream(swlm_state* state, void* cuda_stream);
+/* Prompt ingestion (swlm_prefill) runs the prompt in chunks of up to `tokens` tokens with one activation row per
+ * token and the products on the tensor cores, as the reference's sequence prefill does
+ * (Execution/MetalPrefillExecutor.swift); the last prompt token always takes the decode path. 0 = one token at a
+ * time through the decode graph. Default 512. Chunking applies to single-sequence, single-GPU states; others
+ * ingest token by token. */
+int swlm_state_set_prefill_chunk(swlm_state* state, int tokens);
 /* resetState() — MetalInferenceModel.swift:1911. */
 int swlm_state_reset(swlm_state* state);
 /* promptSnapshot / restore — Execution/MetalPromptStateStore.swift:5-137. */

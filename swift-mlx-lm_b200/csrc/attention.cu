@@ -40,6 +40,7 @@ struct AttnParams {
     size_t cache_head_stride;  // elements between KV heads
     const int32_t* position;   // decode: device scalar; plain: nullptr
     int ctx_len;               // plain: number of cached tokens
+    int pos_base;              // prompt ingestion: position of the chunk's first token
     __nv_bfloat16* out; int out_stride;
     float* part_o;   // [m][heads][splits][HD]
     float* part_ml;  // [m][heads][splits][2]
@@ -68,8 +69,15 @@ __device__ __forceinline__ float rope_elem(const float* v, int d, int rope_dim, 
     return v[d];
 }
 
-template <int HD, bool DECODE>
+// MODE 0: plain flash-decode over an existing cache (q already rotated, context length from the host).
+// MODE 1: decode step: sequence b at the device-resident position; rotates q and the new k, appends k/v to the
+//         cache and adds the new token's own term from the unrounded values.
+// MODE 2: prompt ingestion: "sequence" b is prompt token b of ONE sequence at position pos_base + b; all of the
+//         chunk's k/v rows are already in the cache (rope_append_kernel), token b attends rows 0..pos_base+b.
+template <int HD, int MODE>
 __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnParams p) {
+    constexpr bool DECODE = MODE == 1;
+    constexpr bool PREFILL = MODE == 2;
     pdl_launch_dependents();
     pdl_wait();
     constexpr int NCH = HD / 32;  // 16-byte K chunks per lane per token
@@ -77,78 +85,122 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int G = p.heads / p.kv_heads;
-    const int n_ctx = DECODE ? p.position[0] : p.ctx_len;  // cached tokens to attend (excludes the new one)
+    // cached tokens to attend (in a decode step the new token is not among them)
+    const int n_ctx = DECODE ? p.position[0] : PREFILL ? p.pos_base + b + 1 : p.ctx_len;
+    const int rope_pos = PREFILL ? p.pos_base + b : n_ctx;
 
-    __shared__ float qrot[kMaxGroup][HD];
-    __shared__ float vec[HD];
+    __shared__ float qrot[kMaxGroup][HD];   // unrotated q of the group
+    __shared__ float vec[HD];               // unrotated new k
+    __shared__ float vraw[HD];              // new v
     __shared__ float cs[HD / 2], sn[HD / 2];
+    __shared__ float self_score[kMaxGroup]; // q . k of the new token, log2 domain
     __shared__ float osm[kSplitWarps][kMaxGroup][HD + 4];
     __shared__ float msm[kSplitWarps][kMaxGroup], lsm[kSplitWarps][kMaxGroup];
 
-    const __nv_bfloat16* kbase = p.kcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride;
-    const __nv_bfloat16* vbase = p.vcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride;
-
-    // ---- prologue: q (and, in split 0, the new k/v) ---------------------------------------------
-    if (DECODE) {
-        const int pairs = p.rope_dim >> 1;
-        for (int i = tid; i < pairs; i += kSplitThreads) {
-            float s, c;
-            sincosf((float)n_ctx * p.inv_freq[i], &s, &c);
-            cs[i] = c; sn[i] = s;
-        }
-        if (split == 0 && n_ctx < p.max_seq) {
-            for (int d = tid; d < HD; d += kSplitThreads) vec[d] = __bfloat162float(p.k[(size_t)b * p.k_stride + kvh * HD + d]);
-        }
-        __syncthreads();
-        if (split == 0 && n_ctx < p.max_seq) {
-            __nv_bfloat16* kw = p.kcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD;
-            __nv_bfloat16* vw = p.vcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD;
-            for (int d = tid; d < HD; d += kSplitThreads) {
-                kw[d] = __float2bfloat16_rn(rope_elem(vec, d, p.rope_dim, cs, sn));
-                vw[d] = p.v[(size_t)b * p.v_stride + kvh * HD + d];
-            }
-        }
-    }
-    // unrotated q into shared memory, then rotate in place through registers
-    for (int idx = tid; idx < G * HD; idx += kSplitThreads) {
-        const int r = idx / HD, d = idx - r * HD;
-        qrot[r][d] = __bfloat162float(p.q[(size_t)b * p.q_stride + (size_t)(kvh * G + r) * HD + d]);
-    }
-    __syncthreads();
-    if (DECODE && p.rope_dim > 0) {
-        float tmp[(kMaxGroup * HD + kSplitThreads - 1) / kSplitThreads];
-        int c = 0;
-        for (int idx = tid; idx < G * HD; idx += kSplitThreads, ++c) {
-            const int r = idx / HD, d = idx - r * HD;
-            tmp[c] = rope_elem(qrot[r], d, p.rope_dim, cs, sn);
-        }
-        __syncthreads();
-        c = 0;
-        for (int idx = tid; idx < G * HD; idx += kSplitThreads, ++c) {
-            const int r = idx / HD, d = idx - r * HD;
-            qrot[r][d] = tmp[c];
-        }
-        __syncthreads();
-    }
-
-    // A fragments of q: lane (g, t) holds q[g][32*i + 8*t + 0..7]; hi + lo bf16 split
-    unsigned qhi[NCH][4], qlo[NCH][4];
-#pragma unroll
-    for (int i = 0; i < NCH; ++i)
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            float a = 0.f, c = 0.f;
-            if (g < G) { a = qrot[g][32 * i + 8 * t + 2 * w]; c = qrot[g][32 * i + 8 * t + 2 * w + 1]; }
-            const float ah = __bfloat162float(__float2bfloat16_rn(a)), ch = __bfloat162float(__float2bfloat16_rn(c));
-            qhi[i][w] = pack_bf16(ah, ch);
-            qlo[i][w] = pack_bf16(a - ah, c - ch);
-        }
+    const __nv_bfloat16* kbase = p.kcache + (PREFILL ? 0 : (size_t)b * p.cache_seq_stride) + (size_t)kvh * p.cache_head_stride;
+    const __nv_bfloat16* vbase = p.vcache + (PREFILL ? 0 : (size_t)b * p.cache_seq_stride) + (size_t)kvh * p.cache_head_stride;
 
     // ---- token range of this split ----------------------------------------------------------------
     int chunk = (n_ctx + p.splits - 1) / p.splits;
     chunk = ((chunk + 63) / 64) * 64;
     const int t_begin = split * chunk;
     const int t_end = min(n_ctx, t_begin + chunk);
+    const int last = t_end - 1;
+
+    // K and V of 16 tokens per warp live in registers; the first batch is requested before anything else so
+    // that its trip to HBM overlaps the whole prologue
+    uint4 kreg[2][NCH];
+    uint4 va[VH], vb[VH], vc[VH], vd[VH];
+    auto load_k = [&](int tok0) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const __nv_bfloat16* rowp = kbase + (size_t)min(tok0 + 8 * nt + g, last) * HD;
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) kreg[nt][i] = ldg128(rowp + (4 * i + t) * 8);
+        }
+    };
+    auto load_v = [&](int tok0) {
+        const __nv_bfloat16* ra = vbase + (size_t)min(tok0 + 2 * t, last) * HD + 8 * g;
+        const __nv_bfloat16* rb = vbase + (size_t)min(tok0 + 2 * t + 1, last) * HD + 8 * g;
+        const __nv_bfloat16* rc = vbase + (size_t)min(tok0 + 2 * t + 8, last) * HD + 8 * g;
+        const __nv_bfloat16* rd = vbase + (size_t)min(tok0 + 2 * t + 9, last) * HD + 8 * g;
+#pragma unroll
+        for (int hh = 0; hh < VH; ++hh) {
+            va[hh] = ldg128(ra + 64 * hh); vb[hh] = ldg128(rb + 64 * hh);
+            vc[hh] = ldg128(rc + 64 * hh); vd[hh] = ldg128(rd + 64 * hh);
+        }
+    };
+    int tok0 = t_begin + warp * 16;
+    if (tok0 < t_end) { load_k(tok0); load_v(tok0); }
+
+    // ---- prologue: q, the new k and v, the rotation table: all global loads first, one barrier ------
+    {
+        constexpr int VPR = HD / 8;  // 16-byte vectors per head row
+        uint4 qv = make_uint4(0, 0, 0, 0), kv = qv, vv = qv;
+        const bool has_q = tid < G * VPR;
+        const bool has_k = DECODE && tid < VPR;
+        const bool has_v = DECODE && tid >= 32 && tid < 32 + VPR;
+        if (has_q) qv = *reinterpret_cast<const uint4*>(p.q + (size_t)b * p.q_stride + (size_t)kvh * G * HD + (size_t)tid * 8);
+        if (has_k) kv = *reinterpret_cast<const uint4*>(p.k + (size_t)b * p.k_stride + (size_t)kvh * HD + (size_t)tid * 8);
+        if (has_v) vv = *reinterpret_cast<const uint4*>(p.v + (size_t)b * p.v_stride + (size_t)kvh * HD + (size_t)(tid - 32) * 8);
+        if (DECODE || PREFILL) {
+            const int pairs = p.rope_dim >> 1;
+            for (int i = tid; i < pairs; i += kSplitThreads) {
+                float sv_, cv_;
+                sincosf((float)rope_pos * p.inv_freq[i], &sv_, &cv_);
+                cs[i] = cv_; sn[i] = sv_;
+            }
+        }
+        auto spill8 = [](float* dst, const uint4& w) {
+            const unsigned u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { dst[2 * j] = __uint_as_float(u[j] << 16); dst[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
+        };
+        if (has_q) spill8(&qrot[0][0] + tid * 8, qv);
+        if (has_k) spill8(vec + tid * 8, kv);
+        if (has_v) {
+            spill8(vraw + (tid - 32) * 8, vv);
+            if (split == 0 && n_ctx < p.max_seq)  // the new v row goes to the cache as it is
+                *reinterpret_cast<uint4*>(p.vcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD + (size_t)(tid - 32) * 8) = vv;
+        }
+    }
+    __syncthreads();
+    const bool rotate = (DECODE || PREFILL) && p.rope_dim > 0;
+    if (DECODE) {
+        if (split == 0 && n_ctx < p.max_seq) {  // the rotated new k row, rounded, for later steps
+            __nv_bfloat16* kw = p.kcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD;
+            for (int d = tid; d < HD; d += kSplitThreads) kw[d] = __float2bfloat16_rn(rope_elem(vec, d, p.rope_dim, cs, sn));
+        }
+        // score of the new token against itself, in fp32 from the unrounded rotated q and k
+        // (Generator/MetalSourceGenerator+Attention.swift:866-868)
+        for (int r = warp; r < G; r += kSplitWarps) {
+            float prod = 0.f;
+#pragma unroll
+            for (int i = 0; i < HD / 32; ++i) {
+                const int d = lane + 32 * i;
+                prod = fmaf(rope_elem(qrot[r], d, p.rope_dim, cs, sn), rope_elem(vec, d, p.rope_dim, cs, sn), prod);
+            }
+            for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
+            if (lane == 0) self_score[r] = prod * p.scale_log2;
+        }
+    }
+
+    // A fragments of the rotated q: lane (g, t) holds q[g][32*i + 8*t + 0..7]; hi + lo bf16 split
+    unsigned qhi[NCH][4], qlo[NCH][4];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            float a = 0.f, c = 0.f;
+            if (g < G) {
+                const int d = 32 * i + 8 * t + 2 * w;
+                a = rotate ? rope_elem(qrot[g], d, p.rope_dim, cs, sn) : qrot[g][d];
+                c = rotate ? rope_elem(qrot[g], d + 1, p.rope_dim, cs, sn) : qrot[g][d + 1];
+            }
+            const float ah = __bfloat162float(__float2bfloat16_rn(a)), ch = __bfloat162float(__float2bfloat16_rn(c));
+            qhi[i][w] = pack_bf16(ah, ch);
+            qlo[i][w] = pack_bf16(a - ah, c - ch);
+        }
 
     float m_run = -INFINITY, l_run = 0.f;
     float oacc[VH][8][4];
@@ -157,28 +209,8 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
 #pragma unroll
         for (int u = 0; u < 8; ++u) oacc[hh][u][0] = oacc[hh][u][1] = oacc[hh][u][2] = oacc[hh][u][3] = 0.f;
 
-    for (int tok0 = t_begin + warp * 16; tok0 < t_end; tok0 += kSplitWarps * 16) {
-        const int last = t_end - 1;
-        uint4 kreg[2][NCH];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            const int tok = min(tok0 + 8 * nt + g, last);
-            const __nv_bfloat16* rowp = kbase + (size_t)tok * HD;
-#pragma unroll
-            for (int i = 0; i < NCH; ++i) kreg[nt][i] = ldg128(rowp + (4 * i + t) * 8);
-        }
-        uint4 va[VH], vb[VH], vc[VH], vd[VH];
-        {
-            const __nv_bfloat16* ra = vbase + (size_t)min(tok0 + 2 * t, last) * HD + 8 * g;
-            const __nv_bfloat16* rb = vbase + (size_t)min(tok0 + 2 * t + 1, last) * HD + 8 * g;
-            const __nv_bfloat16* rc = vbase + (size_t)min(tok0 + 2 * t + 8, last) * HD + 8 * g;
-            const __nv_bfloat16* rd = vbase + (size_t)min(tok0 + 2 * t + 9, last) * HD + 8 * g;
-#pragma unroll
-            for (int hh = 0; hh < VH; ++hh) {
-                va[hh] = ldg128(ra + 64 * hh); vb[hh] = ldg128(rb + 64 * hh);
-                vc[hh] = ldg128(rc + 64 * hh); vd[hh] = ldg128(rd + 64 * hh);
-            }
-        }
+    for (; tok0 < t_end; tok0 += kSplitWarps * 16) {
+        const int nxt = tok0 + kSplitWarps * 16;
         // S = q . K^T for 16 tokens
         float sacc[2][4];
 #pragma unroll
@@ -193,6 +225,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
                 mma_bf16(sacc[nt], qhi[i][2], qlo[i][2], qhi[i][3], qlo[i][3], kk.z, kk.w);
             }
         }
+        if (nxt < t_end) load_k(nxt);  // the K registers are free again
         // online softmax in the log2 domain; row g lives in the four lanes t = 0..3
         float sv[2][2];
         float rmax = -INFINITY;
@@ -248,6 +281,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
                 mma_bf16(oacc[hh][2 * w + 1], pa0, pl0, pa2, pl2, b0o, b1o);
             }
         }
+        if (nxt < t_end) load_v(nxt);
     }
 
     // ---- merge the warps of this CTA ---------------------------------------------------------------
@@ -283,52 +317,58 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
 
     // ---- the last CTA of this (sequence, KV head) to arrive merges the splits and writes the output ----
     __shared__ int is_last;
-    __threadfence();
     __syncthreads();
     if (tid == 0) {
+        // release: cumulative over the partials every thread of this CTA wrote before the barrier; acquire: the
+        // last arriver sees the partials of all the others
         unsigned* ctr = p.counters + (size_t)b * p.kv_heads + kvh;
-        const unsigned prev = atomicAdd(ctr, 1u);
+        unsigned prev;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(ctr) : "memory");
         is_last = prev == (unsigned)p.splits - 1u;
         if (is_last) *ctr = 0u;  // ready for the next launch
     }
     __syncthreads();
     if (!is_last) return;
-    __threadfence();
 
-    // current token: its score and value enter in fp32, from the unrounded rotated k and v
-    // (Generator/MetalSourceGenerator+Attention.swift:866-868, :905-907)
-    float* self_score = lsm[0];  // reuse: G floats
-    float* vnew = osm[0][0];     // reuse: HD floats
-    if (DECODE) {
-        for (int d = tid; d < HD; d += kSplitThreads) {
-            vec[d] = __bfloat162float(p.k[(size_t)b * p.k_stride + kvh * HD + d]);
-            vnew[d] = __bfloat162float(p.v[(size_t)b * p.v_stride + kvh * HD + d]);
-        }
-        __syncthreads();
-        float krot[(HD + 31) / 32];
+    // Everything that does not depend on the split weights is requested first: the (max, sum) pairs and the
+    // first 16 partial outputs of this thread's four dimensions travel together.
+    constexpr int kPre = 32;
+    const int n_out4 = G * HD / 4;  // float4 outputs of the group
+    float* wsm = &osm[1][0][0];     // [G][splits] weights (splits <= 64: fits the reused buffer)
+    float* msm2 = &osm[2][0][0];    // [G][splits] split maxima
+    float* lsm2 = &osm[3][0][0];    // [G][splits] split sums
+    float2 ml[2];
 #pragma unroll
-        for (int i = 0; i < HD / 32; ++i) krot[i] = rope_elem(vec, lane + 32 * i, p.rope_dim, cs, sn);
-        for (int r = warp; r < G; r += kSplitWarps) {
-            float prod = 0.f;
-#pragma unroll
-            for (int i = 0; i < HD / 32; ++i) prod = fmaf(qrot[r][lane + 32 * i], krot[i], prod);
-            for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
-            if (lane == 0) self_score[r] = prod * p.scale_log2;
+    for (int j = 0; j < 2; ++j) {
+        const int idx = tid + j * kSplitThreads;
+        if (idx < G * p.splits) {
+            const int r = idx / p.splits, sidx = idx - r * p.splits;
+            const size_t slot = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits + sidx;
+            ml[j] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + slot * 2));
         }
-        __syncthreads();
     }
-    // weights of the splits, all (head, split) pairs in parallel: w = 2^(m_s - max), normalised by the
-    // total mass; kept in shared memory so that the output loop below issues independent loads only
-    float* wsm = &osm[1][0][0];            // [G][splits] weights (splits <= 64: fits the reused buffer)
-    float* msm2 = &osm[2][0][0];           // [G][splits] split maxima
-    float* lsm2 = &osm[3][0][0];           // [G][splits] split sums
-    for (int idx = tid; idx < G * p.splits; idx += kSplitThreads) {
+    float4 pre[kPre];
+    const float* po0 = nullptr;
+    if (tid < n_out4) {
+        const int r = tid / (HD / 4), d4 = tid - r * (HD / 4);
+        po0 = p.part_o + (((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits) * HD + d4 * 4;
+#pragma unroll
+        for (int sidx = 0; sidx < kPre; ++sidx)
+            if (sidx < p.splits) pre[sidx] = __ldcg(reinterpret_cast<const float4*>(po0 + (size_t)sidx * HD));
+    }
+    for (int j = 0; j < 2; ++j) {
+        const int idx = tid + j * kSplitThreads;
+        if (idx < G * p.splits) { msm2[idx] = ml[j].x; lsm2[idx] = ml[j].y; }
+    }
+    for (int idx = tid + 2 * kSplitThreads; idx < G * p.splits; idx += kSplitThreads) {
         const int r = idx / p.splits, sidx = idx - r * p.splits;
         const size_t slot = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits + sidx;
         msm2[idx] = __ldcg(p.part_ml + slot * 2);
         lsm2[idx] = __ldcg(p.part_ml + slot * 2 + 1);
     }
     __syncthreads();
+    // weights of the splits: w = 2^(m_s - max), normalised by the total mass; the new token enters with its
+    // own score and its unrounded v (Generator/MetalSourceGenerator+Attention.swift:905-907)
     float* inv_den = msm[0];  // reuse: G floats
     float* w_self = msm[1];
     for (int r = warp; r < G; r += kSplitWarps) {
@@ -349,14 +389,63 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         if (lane == 0) { inv_den[r] = den > 0.f ? 1.0f / den : 0.f; w_self[r] = ws; }
     }
     __syncthreads();
-    for (int idx = tid; idx < G * HD; idx += kSplitThreads) {
-        const int r = idx / HD, d = idx - r * HD;
-        const float* po = p.part_o + (((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits) * HD + d;
+    for (int idx = tid; idx < n_out4; idx += kSplitThreads) {
+        const int r = idx / (HD / 4), d4 = idx - r * (HD / 4);
+        const float* po = p.part_o + (((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits) * HD + d4 * 4;
         const float* wr = wsm + r * p.splits;
-        float num = DECODE ? w_self[r] * vnew[d] : 0.f;
-#pragma unroll 8
-        for (int sidx = 0; sidx < p.splits; ++sidx) num = fmaf(wr[sidx], __ldcg(po + (size_t)sidx * HD), num);
-        p.out[(size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(num * inv_den[r]);
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (DECODE) {
+            const float ws = w_self[r];
+            num = make_float4(ws * vraw[d4 * 4], ws * vraw[d4 * 4 + 1], ws * vraw[d4 * 4 + 2], ws * vraw[d4 * 4 + 3]);
+        }
+        int s0 = 0;
+        if (idx == tid) {  // this thread's first output: its first partials are already in registers
+#pragma unroll
+            for (int sidx = 0; sidx < kPre; ++sidx)
+                if (sidx < p.splits) {
+                    const float w = wr[sidx];
+                    num.x = fmaf(w, pre[sidx].x, num.x); num.y = fmaf(w, pre[sidx].y, num.y);
+                    num.z = fmaf(w, pre[sidx].z, num.z); num.w = fmaf(w, pre[sidx].w, num.w);
+                }
+            s0 = min(kPre, p.splits);
+        }
+#pragma unroll 16
+        for (int sidx = s0; sidx < p.splits; ++sidx) {
+            const float4 v4 = __ldcg(reinterpret_cast<const float4*>(po + (size_t)sidx * HD));
+            const float w = wr[sidx];
+            num.x = fmaf(w, v4.x, num.x); num.y = fmaf(w, v4.y, num.y);
+            num.z = fmaf(w, v4.z, num.z); num.w = fmaf(w, v4.w, num.w);
+        }
+        const float inv = inv_den[r];
+        uint2 packed;
+        packed.x = pack_bf16(num.x * inv, num.y * inv);
+        packed.y = pack_bf16(num.z * inv, num.w * inv);
+        *reinterpret_cast<uint2*>(p.out + (size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d4 * 4) = packed;
+    }
+}
+
+// Prompt ingestion: rotate the chunk's k rows (token b at position pos_base + b) and append them and the v rows to
+// the cache of sequence 0, rounded to bf16 (Generator/MetalSourceGenerator+Attention.swift:761-805 does the same
+// per decode step). One CTA per (token, KV head).
+__global__ void __launch_bounds__(128) rope_append_kernel(const AttnParams p, int hd) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float vec[128];
+    __shared__ float cs[64], sn[64];
+    const int b = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
+    const int pos = p.pos_base + b;
+    if (pos >= p.max_seq) return;
+    for (int i = tid; i < (p.rope_dim >> 1); i += 128) {
+        float sv_, cv_;
+        sincosf((float)pos * p.inv_freq[i], &sv_, &cv_);
+        cs[i] = cv_; sn[i] = sv_;
+    }
+    for (int d = tid; d < hd; d += 128) vec[d] = __bfloat162float(p.k[(size_t)b * p.k_stride + kvh * hd + d]);
+    __syncthreads();
+    const size_t row = (size_t)kvh * p.cache_head_stride + (size_t)pos * hd;
+    for (int d = tid; d < hd; d += 128) {
+        p.kcache[row + d] = __float2bfloat16_rn(rope_elem(vec, d, p.rope_dim, cs, sn));
+        p.vcache[row + d] = p.v[(size_t)b * p.v_stride + kvh * hd + d];
     }
 }
 
@@ -366,13 +455,13 @@ int check_launch(const char* what) {
     return SWLM_OK;
 }
 
-template <bool DECODE>
+template <int MODE>
 int launch_both(const AttnParams& p, int m, int hd, cudaStream_t s) {
     const dim3 grid(p.splits, p.kv_heads, m);
     if (hd == 128) {
-        launch_k(attn_split_kernel<128, DECODE>, dim3(grid), dim3(kSplitThreads), 0, s, p);
+        launch_k(attn_split_kernel<128, MODE>, dim3(grid), dim3(kSplitThreads), 0, s, p);
     } else if (hd == 64) {
-        launch_k(attn_split_kernel<64, DECODE>, dim3(grid), dim3(kSplitThreads), 0, s, p);
+        launch_k(attn_split_kernel<64, MODE>, dim3(grid), dim3(kSplitThreads), 0, s, p);
     } else {
         set_error("attention: head_dim %d not supported (64 or 128)", hd);
         return SWLM_ERR_UNSUPPORTED;
@@ -409,6 +498,11 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     int rc = check_group(a.heads, a.kv_heads);
     if (rc) return rc;
     if (a.rope_dim > a.head_dim || (a.rope_dim & 1)) { set_error("attention: bad rope_dim"); return SWLM_ERR_INVALID; }
+    if (((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.out)) & 15) ||
+        ((a.q_stride | a.k_stride | a.v_stride | a.out_stride) & 7)) {
+        set_error("attention: q, k, v and out rows must be 16-byte aligned");
+        return SWLM_ERR_INVALID;
+    }
     AttnParams p{};
     p.heads = a.heads; p.kv_heads = a.kv_heads; p.rope_dim = a.rope_dim; p.max_seq = a.max_seq; p.splits = a.splits;
     p.scale_log2 = a.scale * kLog2e;
@@ -422,7 +516,15 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     p.part_o = a.scratch;
     p.part_ml = a.scratch + (size_t)a.m * a.heads * a.splits * a.head_dim;
     p.counters = a.counters;
-    return launch_both<true>(p, a.m, a.head_dim, s);
+    if (a.pos_base >= 0) {
+        // prompt ingestion: rows of q/k/v are consecutive tokens of sequence 0
+        if (a.head_dim > 128) { set_error("attention: head_dim %d not supported", a.head_dim); return SWLM_ERR_UNSUPPORTED; }
+        p.pos_base = a.pos_base;
+        cudaError_t e = launch_k(rope_append_kernel, dim3(a.m, a.kv_heads, 1), dim3(128), 0, s, p, a.head_dim);
+        if (e != cudaSuccess) return cuda_fail(e, "rope_append launch");
+        return launch_both<2>(p, a.m, a.head_dim, s);
+    }
+    return launch_both<1>(p, a.m, a.head_dim, s);
 }
 
 int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, float scale,
@@ -430,6 +532,7 @@ int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_le
                               __nv_bfloat16* out, float* scratch, unsigned* counters, int splits, cudaStream_t s) {
     int rc = check_group(heads, kv_heads);
     if (rc) return rc;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15) { set_error("flash-decode: q and out must be 16-byte aligned"); return SWLM_ERR_INVALID; }
     AttnParams p{};
     p.heads = heads; p.kv_heads = kv_heads; p.rope_dim = 0; p.max_seq = ctx_stride; p.splits = splits;
     p.scale_log2 = scale * kLog2e;
@@ -442,7 +545,7 @@ int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_le
     p.part_o = scratch;
     p.part_ml = scratch + (size_t)m * heads * splits * hd;
     p.counters = counters;
-    return launch_both<false>(p, m, hd, s);
+    return launch_both<0>(p, m, hd, s);
 }
 
 // ---- allocation-free flash-decode ---------------------------------------------------------------------

@@ -140,6 +140,40 @@ __global__ void conv_step_kernel(int dim, int kernel, __nv_bfloat16* state, size
     out[(size_t)b * out_stride + c] = __float2bfloat16_rn(C * acc);
 }
 
+// The same update over `tokens` consecutive prompt tokens of one sequence: a thread keeps its channel's window in
+// registers and walks the tokens in order, so every intermediate value (and the state left behind) is bit for bit
+// what `tokens` single steps produce.
+constexpr int kConvMaxKernel = 8;
+__global__ void conv_prefill_kernel(int dim, int kernel, int tokens, __nv_bfloat16* state, const __nv_bfloat16* in,
+                                    int in_stride, const __nv_bfloat16* weight, __nv_bfloat16* out, int out_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= dim) return;
+    float win[kConvMaxKernel], w[kConvMaxKernel];
+#pragma unroll
+    for (int k = 0; k < kConvMaxKernel; ++k) {
+        win[k] = k < kernel ? __bfloat162float(state[(size_t)k * dim + c]) : 0.f;
+        w[k] = k < kernel ? __bfloat162float(weight[(size_t)c * kernel + k]) : 0.f;
+    }
+    for (int tkn = 0; tkn < tokens; ++tkn) {
+        const __nv_bfloat16* x = in + (size_t)tkn * in_stride;
+        const float B = __bfloat162float(x[c]), C = __bfloat162float(x[dim + c]), xv = __bfloat162float(x[2 * dim + c]);
+        const float Bx = B * xv;
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k + 1 < kConvMaxKernel; ++k)
+            if (k + 1 < kernel) { win[k] = win[k + 1]; acc += win[k] * w[k]; }
+#pragma unroll
+        for (int k = 0; k < kConvMaxKernel; ++k)
+            if (k == kernel - 1) { win[k] = __bfloat162float(__float2bfloat16_rn(Bx)); acc += Bx * w[k]; }
+        out[(size_t)tkn * out_stride + c] = __float2bfloat16_rn(C * acc);
+    }
+#pragma unroll
+    for (int k = 0; k < kConvMaxKernel; ++k)
+        if (k < kernel) state[(size_t)k * dim + c] = __float2bfloat16_rn(win[k]);
+}
+
 // ---- argmax -----------------------------------------------------------------------------------------
 // Replaces the single-threadgroup `argmax` (Generator/MetalSourceGenerator+Sampling.swift:62-107) with a
 // two-level reduction. Lowest index wins among equal maxima.
@@ -315,6 +349,13 @@ int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t st
                      int out_stride, cudaStream_t s) {
     launch_k(conv_step_kernel, dim3((dim + 255) / 256, m), 256, 0, s, dim, kernel, state, state_seq_stride, in, in_stride, weight, out, out_stride);
     return check_launch("conv_step launch");
+}
+
+int launch_conv_prefill(int tokens, int dim, int kernel, __nv_bfloat16* state, const __nv_bfloat16* in, int in_stride,
+                        const __nv_bfloat16* weight, __nv_bfloat16* out, int out_stride, cudaStream_t s) {
+    if (kernel > kConvMaxKernel) { set_error("conv: kernel size %d not supported for prompt ingestion (max %d)", kernel, kConvMaxKernel); return SWLM_ERR_UNSUPPORTED; }
+    launch_k(conv_prefill_kernel, dim3((dim + 127) / 128), 128, 0, s, dim, kernel, tokens, state, in, in_stride, weight, out, out_stride);
+    return check_launch("conv_prefill launch");
 }
 
 size_t argmax_scratch_elems(int m) { return (size_t)m * kArgmaxBlocks; }

@@ -1,0 +1,310 @@
+// Q4 group-64 prefill GEMM for sm_100a on the 5th-generation tensor cores (tcgen05 / TMEM).
+//
+// Replaces the reference's `gemm_q4_g64` for M >= 64 (Generator/MetalSourceGenerator+Quantized.swift:88-156,
+// which repeats the per-row dot product for every sequence position and so re-reads the weights M times)
+// with a real contraction. Arithmetic follows the reference's other prefill route, dequantise-then-matmul
+// (`dequant_q4_g64_bf16`, +Quantized.swift:361-416: W_bf16 = bf16(scale*q + zero), then a dense product with
+// fp32 accumulation), except that the bf16 weights never exist in global memory.
+//
+// One CTA computes a 128 (weight rows) x BN (tokens) tile of Y^T:
+//   * every thread owns one weight row: per 64-column group it loads the row's 32 packed bytes and its
+//     (scale, zero), turns nibble pairs into bf16 with LOP3 (128+q), subtracts 128 and applies scale and zero
+//     with one bf16x2 FMA each — exactly bf16(scale*q + zero) — and stores the 128-byte row into shared
+//     memory in the K-major, 128-byte-swizzled layout tcgen05.mma reads;
+//   * the activation tile (BN tokens x 64 columns, bf16) is copied into the same layout with cp.async;
+//   * one thread issues four tcgen05.mma (M=128, N=BN, K=16, kind::f16, bf16 x bf16 -> fp32) per group into
+//     a TMEM accumulator; tcgen05.commit signals an mbarrier when the stage may be overwritten;
+//   * the epilogue reads the accumulator with tcgen05.ld, rounds to bf16 and stores Y[token][row].
+// Every mbarrier wait is bounded: on expiry an error word is set, the CTA stops issuing, frees its TMEM
+// and returns.
+#include "swlm_internal.h"
+
+namespace swlm {
+namespace {
+
+constexpr int kTcThreads = 256;
+constexpr int kTcRows = 128;            // weight rows per CTA = UMMA M
+constexpr int kTcBK = 64;               // one quantisation group per pipeline stage
+constexpr int kTcSpinLimit = 1 << 22;
+
+struct QGemmTcParams {
+    const uint32_t* w;        // [n][k/8] MLX words
+    const uint16_t* scales;   // [n][k/64] bf16
+    const uint16_t* biases;
+    int n, k;
+    const __nv_bfloat16* x;   // [m][x_stride]
+    int x_stride, m;
+    __nv_bfloat16* y;         // [m][y_stride]
+    int y_stride;
+    int* status;              // set non-zero when a bounded wait expired
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+// Bounded wait on phase parity; returns false when the limit was reached.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (int spin = 0; spin < kTcSpinLimit; ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024
+// bytes apart (stride byte offset); leading byte offset unused for this layout; descriptor version 1.
+__device__ __forceinline__ unsigned long long umma_desc(unsigned smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)(1024u >> 4) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: D = fp32, A = B = bf16, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr unsigned umma_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(kTcRows >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// byte offset of 16-byte chunk c (0..7) of row r inside a K-major tile with 128-byte rows and 128B swizzle
+__device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
+
+// F16SB: scale and zero are fp16 (tensors uploaded as STAF blocks) instead of bf16 (MLX tensors).
+//
+// 256 threads: thread (r = tid & 127, h = tid >> 7) dequantises columns 32h..32h+31 of weight row r in every
+// group, so a group costs a thread one 16-byte load and about 90 instructions. Packed weights and (scale, zero)
+// are fetched two groups ahead into registers, the activation tile one group ahead with cp.async, so that
+// neither latency sits between two MMAs. STAGES shared-memory stages; tcgen05.commit frees a stage.
+template <int BN, int STAGES, bool F16SB>
+__global__ void __launch_bounds__(kTcThreads) qgemm_tc_kernel(const QGemmTcParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // 1024-byte alignment for the swizzle atoms
+    unsigned char* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+    constexpr int A_BYTES = kTcRows * 128;
+    constexpr int B_BYTES = BN * 128;
+    __shared__ __align__(8) unsigned long long empty_bar[STAGES];
+    __shared__ __align__(8) unsigned long long done_bar;
+    __shared__ unsigned tmem_base_smem;
+    __shared__ int failed;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = tid & 127, half = tid >> 7;
+    const int row0 = blockIdx.x * kTcRows, tok0 = blockIdx.y * BN;
+    const int kt_total = p.k / kTcBK;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(&empty_bar[s], 1);
+        mbar_init(&done_bar, 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();  // the allocation is a warp-wide instruction: re-converge after the single-thread block
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_smem)), "r"((unsigned)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_d = tmem_base_smem;
+
+    const int row = row0 + r;
+    const bool row_ok = row < p.n;
+    // this thread's 16 bytes of group kt: words 4h..4h+3 of the row's eight
+    const uint4* wrow = reinterpret_cast<const uint4*>(p.w + (size_t)(row_ok ? row : 0) * (p.k / 8)) + half;
+    const uint16_t* srow = p.scales + (size_t)(row_ok ? row : 0) * kt_total;
+    const uint16_t* zrow = p.biases + (size_t)(row_ok ? row : 0) * kt_total;
+    constexpr unsigned idesc = umma_idesc(BN);
+
+    struct WReg { uint4 w; unsigned s, z; };
+    auto load_w = [&](int kt) {
+        WReg v; v.w = make_uint4(0, 0, 0, 0); v.s = 0; v.z = 0;
+        if (row_ok && kt < kt_total) { v.w = __ldg(wrow + kt * 2); v.s = __ldg(srow + kt); v.z = __ldg(zrow + kt); }
+        return v;
+    };
+    auto issue_x = [&](int kt) {
+        unsigned char* const b_tile = smem + (kt % STAGES) * (A_BYTES + B_BYTES) + A_BYTES;
+#pragma unroll
+        for (int i = 0; i < BN * 8 / kTcThreads; ++i) {
+            const int idx = tid + i * kTcThreads;
+            const int tkn = idx >> 3, c = idx & 7;
+            unsigned char* dst = b_tile + swz(tkn, c);
+            if (tok0 + tkn < p.m) {
+                const __nv_bfloat16* src = p.x + (size_t)(tok0 + tkn) * p.x_stride + kt * kTcBK + c * 8;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    WReg w_cur = load_w(0), w_nxt = load_w(1);  // weights do not depend on the preceding kernel
+    pdl_wait();                                 // the activations may come from the kernel just before this one
+    issue_x(0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    for (int kt = 0; kt < kt_total; ++kt) {
+        const int s = kt % STAGES;
+        unsigned char* const a_tile = smem + s * (A_BYTES + B_BYTES);
+        unsigned char* const b_tile = a_tile + A_BYTES;
+        // ---- activations of the next group into the next stage, once its previous MMAs have read it ------
+        if (kt + 1 < kt_total) {
+            const int use1 = (kt + 1) / STAGES;
+            if (use1 > 0 && !mbar_wait(&empty_bar[(kt + 1) % STAGES], (unsigned)((use1 - 1) & 1))) { atomicExch(p.status, 1); failed = 1; }
+            issue_x(kt + 1);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // ---- weights: 32 nibbles of this thread's row -> 32 bf16 = bf16(scale * q + zero) -----------------
+        {
+            const WReg v = w_cur;
+            w_cur = w_nxt;
+            w_nxt = load_w(kt + 2);
+            const unsigned s2 = v.s | (v.s << 16), z2 = v.z | (v.z << 16);
+            const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(&s2);
+            const __nv_bfloat162 zr = *reinterpret_cast<const __nv_bfloat162*>(&z2);
+            const float sf = F16SB ? __half2float(__ushort_as_half((unsigned short)v.s)) : 0.f;
+            const float zf = F16SB ? __half2float(__ushort_as_half((unsigned short)v.z)) : 0.f;
+            const unsigned c128 = 0x43004300u;
+            const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162*>(&c128);
+            const unsigned words[4] = {v.w.x, v.w.y, v.w.z, v.w.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                // a word holds 8 consecutive columns, nibble j = column j; pairs (j, j+4) come out of one LOP3
+                const unsigned wv = words[c];
+                unsigned o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned pr = ((wv >> (4 * j)) & 0x000F000Fu) | 0x43004300u;         // (128+q_j, 128+q_{j+4})
+                    __nv_bfloat162 q2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pr), off);
+                    if (F16SB) {
+                        // fp16 scale and zero widened to fp32, one fused multiply-add, one rounding to bf16
+                        const unsigned qb = *reinterpret_cast<const unsigned*>(&q2);
+                        q2 = __floats2bfloat162_rn(fmaf(sf, __uint_as_float(qb << 16), zf), fmaf(sf, __uint_as_float(qb & 0xFFFF0000u), zf));
+                    } else {
+                        q2 = __hfma2(q2, sc, zr);                                              // bf16(s*q + z), one rounding
+                    }
+                    o[j] = *reinterpret_cast<const unsigned*>(&q2);                            // lo = column j, hi = column j+4
+                }
+                // reorder the pairs (j, j+4) into consecutive columns 0..7
+                const uint4 out = make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),
+                                             __byte_perm(o[0], o[1], 0x7632), __byte_perm(o[2], o[3], 0x7632));
+                *reinterpret_cast<uint4*>(a_tile + swz(r, half * 4 + c)) = out;
+            }
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // this group's activations have landed
+        // generic-proxy writes to shared memory -> visible to the tensor core (async proxy)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (failed) break;
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned a_addr = smem_u32(a_tile), b_addr = smem_u32(b_tile);
+#pragma unroll
+            for (int j = 0; j < kTcBK / 16; ++j)  // 16 bf16 = 32 bytes along K inside the 128-byte row
+                umma_f16(tmem_d, umma_desc(a_addr + 32 * j), umma_desc(b_addr + 32 * j), idesc, (kt > 0 || j > 0) ? 1u : 0u);
+            umma_commit(&empty_bar[s]);
+            if (kt == kt_total - 1) umma_commit(&done_bar);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    // ---- epilogue: TMEM -> registers -> bf16 -> Y[token][row] --------------------------------------------
+    // a warp reads the 32 accumulator lanes of its quarter (warp & 3); warps 0-3 take the first half of the
+    // token columns, warps 4-7 the second
+    bool ok = !failed;
+    if (ok && !mbar_wait(&done_bar, 0u)) { atomicExch(p.status, 1); ok = false; }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+        const int erow = row0 + (warp & 3) * 32 + lane;
+        const int cbase = (warp >> 2) * (BN / 2);
+#pragma unroll 1
+        for (int c0 = cbase; c0 < cbase + BN / 2; c0 += 16) {
+            if (tok0 + c0 >= p.m) break;  // uniform across the warp
+            unsigned v[16];
+            const unsigned taddr = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)c0;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                : "r"(taddr) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (erow < p.n) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int tkn = tok0 + c0 + i;
+                    if (tkn < p.m) p.y[(size_t)tkn * p.y_stride + erow] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((unsigned)BN) : "memory");
+}
+
+template <int BN, int STAGES>
+constexpr size_t tc_smem_bytes() { return (size_t)STAGES * (kTcRows * 128 + BN * 128) + 1024; }
+
+template <int BN, int STAGES>
+int tc_init_one() {
+    SWLM_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<BN, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes<BN, STAGES>()));
+    SWLM_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<BN, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes<BN, STAGES>()));
+    return SWLM_OK;
+}
+template <int BN, int STAGES>
+cudaError_t tc_launch_one(const QGemmTcParams& p, bool f16, cudaStream_t s) {
+    const dim3 grid((unsigned)((p.n + kTcRows - 1) / kTcRows), (unsigned)((p.m + BN - 1) / BN), 1);
+    return f16 ? launch_k(qgemm_tc_kernel<BN, STAGES, true>, grid, dim3(kTcThreads), tc_smem_bytes<BN, STAGES>(), s, p)
+               : launch_k(qgemm_tc_kernel<BN, STAGES, false>, grid, dim3(kTcThreads), tc_smem_bytes<BN, STAGES>(), s, p);
+}
+
+}  // namespace
+
+int qgemm_tc_init() {
+    int rc;
+    if ((rc = tc_init_one<64, 3>())) return rc;
+    if ((rc = tc_init_one<128, 3>())) return rc;
+    if ((rc = tc_init_one<256, 4>())) return rc;
+    return SWLM_OK;
+}
+
+// Y[m][n] = bf16(X[m][k] . bf16(W)^T) on the tcgen05 path. `status` is a device word the kernel sets when a
+// bounded wait expires. Token tile: 256 when there are that many tokens (each dequantised weight then feeds
+// 256 columns of the MMA), else 128 or 64.
+int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
+                    int* status, cudaStream_t s) {
+    if (w.k % kTcBK || (x_stride & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) { set_error("qgemm (tcgen05): bad shape or alignment"); return SWLM_ERR_INVALID; }
+    QGemmTcParams p{};
+    p.w = w.w; p.scales = w.scales; p.biases = w.biases; p.n = w.n; p.k = w.k;
+    p.x = x; p.x_stride = x_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;
+    cudaError_t e;
+    if (m > 128) e = tc_launch_one<256, 4>(p, w.sb_f16, s);
+    else if (m > 64) e = tc_launch_one<128, 3>(p, w.sb_f16, s);
+    else e = tc_launch_one<64, 3>(p, w.sb_f16, s);
+    if (e != cudaSuccess) return cuda_fail(e, "qgemm_tc launch");
+    return SWLM_OK;
+}
+
+}  // namespace swlm

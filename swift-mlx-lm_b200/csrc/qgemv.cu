@@ -24,6 +24,8 @@
 //     algebraically the reference's sum((scale*q+zero)*x), with q and x exact and products exact in fp32;
 //   * the B operand holds up to 16 sequences (columns), so batch <= 16 costs the same weight traffic.
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 
 #include "swlm_internal.h"
 #include "tp_device.cuh"
@@ -36,6 +38,10 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;                 // ring depth per warp; one stage = 4 k-tiles + their scales
 constexpr int kStageBytes = 4 * 512 + 256;
 constexpr int kRingBytes = kWarps * kStages * kStageBytes;
+// Batch-1 kernel: a CTA is up to three groups of eight warps. The groups share one copy of the quantised
+// activations (prepared once per SM instead of once per group) and otherwise behave like separate CTAs.
+constexpr int kMaxGroups = 3;
+constexpr int kMaxWarps1 = kMaxGroups * kWarps;
 constexpr int kXPad = 8;                   // bf16 elements of padding per x row (bank skew)
 constexpr int kL2Ahead = 10;               // stages (2.3 KB each) a warp prefetches into L2 ahead of its ring
 
@@ -64,13 +70,27 @@ struct QGemvParams {
     // in_tp = the fused norm's input is the sum of the partials the preceding product pushed
     int push, in_tp;
     TpParams tp;
+    // phase timestamps (SWLM_TRACE=1): [cta][4] = kernel entry, predecessor complete, activations ready, done
+    unsigned long long* trace;
 };
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// one instruction asks for `bytes` (a multiple of 16, 16-byte aligned) to be brought from HBM into L2
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, unsigned bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+constexpr int kBulkPiece = 8;        // stages per bulk prefetch instruction (16 KB of tiles + 2 KB of pairs)
+constexpr int kBulkMaxStages = 16;   // at most 36 KB per CTA requested up front (the rolling prefetch does the rest)
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -113,7 +133,7 @@ __device__ __forceinline__ float sb_zero(unsigned pair) {
 // returned as eight packed bf16 pairs. The norm sees the unrounded sum, as the reference's fused kernel does.
 // res_in and res_out are different buffers: other CTAs read res_in while one writes res_out.
 __device__ __forceinline__ void fused_norm_run(const QGemvParams& p, int b, int k0, bool in_range, bool writer,
-                                               float* red, unsigned (&w)[8], int tp_epoch) {
+                                               float* red, unsigned (&w)[8], int tp_epoch, int nwarps = kWarps) {
     float h[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) h[i] = 0.f;
@@ -159,6 +179,12 @@ __device__ __forceinline__ void fused_norm_run(const QGemvParams& p, int b, int 
             dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
     }
+    // the norm weights do not depend on the sum below: requested now, used after the barriers
+    uint4 n0 = make_uint4(0, 0, 0, 0), n1 = n0;
+    if (in_range) {
+        const uint4* ws = reinterpret_cast<const uint4*>(p.norm_w + k0);
+        n0 = __ldg(ws); n1 = __ldg(ws + 1);
+    }
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) ss = fmaf(h[i], h[i], ss);
@@ -167,14 +193,11 @@ __device__ __forceinline__ void fused_norm_run(const QGemvParams& p, int b, int 
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     float total = 0.f;
-#pragma unroll
-    for (int i = 0; i < kWarps; ++i) total += red[i];
+    for (int i = 0; i < nwarps; ++i) total += red[i];
     const float rs = rsqrtf(total / (float)p.k + p.eps);
 #pragma unroll
     for (int i = 0; i < 8; ++i) w[i] = 0u;
     if (in_range) {
-        const uint4* ws = reinterpret_cast<const uint4*>(p.norm_w + k0);
-        const uint4 n0 = __ldg(ws), n1 = __ldg(ws + 1);
         const unsigned nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -542,27 +565,33 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], unsigned a0, unsigned a1,
 }
 
 template <int EPI, bool F16SB>
-__global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p) {
+__global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const QGemvParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, cta_warp = tid >> 5;
+    const int groups = blockDim.x / kThreads, grp = cta_warp / kWarps;
+    const int warp = cta_warp % kWarps;   // warp within its group
+    const int gtid = tid % kThreads;      // thread within its group
+    const int vb = grp * gridDim.x + blockIdx.x, vgrid = gridDim.x * groups;  // the group as a virtual CTA
     const int g = lane >> 2, t = lane & 3;
     const int kt_total = p.kt4_total * 4;
+    if (p.trace && tid == 0) p.trace[blockIdx.x * 4] = global_timer_ns();
 
-    unsigned char* my_ring = smem + warp * (kStages * kStageBytes);
-    uint4* xq = reinterpret_cast<uint4*>(smem + kRingBytes);                       // [kt][t][hi, lo]
-    float2* xmeta = reinterpret_cast<float2*>(smem + kRingBytes + (size_t)kt_total * 128);  // [kt][t] {2^E, sum}
+    const int ring_bytes = groups * kRingBytes;
+    unsigned char* my_ring = smem + cta_warp * (kStages * kStageBytes);
+    uint4* xq = reinterpret_cast<uint4*>(smem + ring_bytes);                       // [kt][t][hi, lo]
+    float2* xmeta = reinterpret_cast<float2*>(smem + ring_bytes + (size_t)kt_total * 128);  // [kt][t] {2^E, sum}
 
     // Two ways of dealing out the (row tile, k-slice) units. cta_mode (matrices with no more row tiles than
     // resident CTAs): a CTA takes eight consecutive units at a time, i.e. all slices of 8/si row tiles, and
     // adds the slices through shared memory. Otherwise every CTA owns an equal contiguous share, its warps
     // take units round-robin and the slices of a row tile meet in global scratch. si is a power of two.
     const int units = p.row_tiles << p.si_shift;
-    const int u_lo = (int)(((long long)blockIdx.x * units) / gridDim.x);
-    const int u_hi = (int)(((long long)(blockIdx.x + 1) * units) / gridDim.x);
-    const int u_first = p.cta_mode ? blockIdx.x * kWarps : u_lo;
+    const int u_lo = (int)(((long long)vb * units) / vgrid);
+    const int u_hi = (int)(((long long)(vb + 1) * units) / vgrid);
+    const int u_first = p.cta_mode ? vb * kWarps : u_lo;
     const int u_end = p.cta_mode ? units : u_hi;
-    const int u_limit = p.cta_mode ? ((units + kWarps - 1) / kWarps) * kWarps : u_hi;  // uniform across the CTA
-    const int u_stride = p.cta_mode ? gridDim.x * kWarps : kWarps;
+    const int u_limit = p.cta_mode ? ((units + kWarps - 1) / kWarps) * kWarps : u_hi;  // uniform across the group
+    const int u_stride = p.cta_mode ? vgrid * kWarps : kWarps;
     const int si_mask = (1 << p.si_shift) - 1;
     // stages are addressed by one absolute index a = rt * kt4_total + st: tiles at a * 128, pairs at a * 16
     auto unit_range = [&](int u, int& a0, int& a1) {
@@ -599,27 +628,47 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
         }
         cp_async_commit();
     };
-    // Weights do not depend on the preceding kernel: the ring starts filling before its results are awaited.
-    // HBM keeps streaming into L2 while the activations are prepared: the ring alone holds 4.6 KB per warp.
+    // Weights do not depend on the preceding kernel: before anything else the CTA asks for its whole share (up
+    // to a cap) to be moved from HBM into L2, a few instructions in total, so that HBM streams at full rate
+    // while the preceding kernel drains and the activations are prepared; the ring then fills from L2.
     pdl_launch_dependents();
+    {
+        const int pu0 = p.cta_mode ? u_first : u_lo;
+        const int pu1 = p.cta_mode ? min(u_first + kWarps, units) : u_hi;
+        if (pu0 < pu1) {
+            int pa0, pa1, unused;
+            unit_range(pu0, pa0, unused);
+            unit_range(pu1 - 1, unused, pa1);
+            pa1 = min(pa1, pa0 + kBulkMaxStages);
+            const int piece = gtid >> 1;  // even threads: tiles, odd threads: scale/zero pairs
+            const int s0 = pa0 + piece * kBulkPiece;
+            if (s0 < pa1) {
+                const int ns = min(kBulkPiece, pa1 - s0);
+                if (gtid & 1) prefetch_l2_bulk(p.sb + (size_t)s0 * 16, (unsigned)ns * 256u);
+                else prefetch_l2_bulk(p.tiles + (size_t)s0 * 128, (unsigned)ns * 2048u);
+            }
+        }
+    }
     int islot = 0, cslot = 0;  // ring slots of the next stage to issue / to consume
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
     pdl_wait();
+    if (p.trace && tid == 0) p.trace[blockIdx.x * 4 + 1] = global_timer_ns();
 
     // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
-    __shared__ float red[kWarps];
+    __shared__ float red[kMaxWarps1];
     const int tp_epoch = (p.push || p.in_tp) ? *p.tp.epoch + (p.push ? 1 : 0) : 0;
     if (p.in_tp) {
         tp_wait_flags(p.tp, p.tp.peer[p.tp.rank], p.tp.lay.flags_ar(tp_epoch & 1, 0), tp_epoch, tid);
         __syncthreads();
     }
-    for (int run = tid; run < kt_total * 4 || (p.norm_mode && run < kThreads); run += kThreads) {
+    const int nthreads = blockDim.x;
+    for (int run = tid; run < kt_total * 4 || (p.norm_mode && run < nthreads); run += nthreads) {
         const int k0 = run * 16;
         unsigned w[8];
         if (p.norm_mode) {
             // dimension <= 4096: exactly one pass, every thread takes part in the block-wide sum
-            fused_norm_run(p, 0, k0, k0 < p.k, blockIdx.x == 0, red, w, tp_epoch);
+            fused_norm_run(p, 0, k0, k0 < p.k, blockIdx.x == 0, red, w, tp_epoch, nthreads >> 5);
             if (run >= kt_total * 4) continue;
         } else {
             uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
@@ -673,8 +722,10 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
     }
     __syncthreads();
 
+    if (p.trace && tid == 0) p.trace[blockIdx.x * 4 + 2] = global_timer_ns();
     const int s_total = 1 << p.si_shift;
-    __shared__ float cta_red[2][kWarps][16];
+    __shared__ float cta_red_all[kMaxGroups][2][kWarps][16];
+    float (*cta_red)[kWarps][16] = cta_red_all[grp];
     __shared__ __align__(16) unsigned zero16[4];
     if (tid < 4) zero16[tid] = 0u;
     __syncthreads();
@@ -737,7 +788,7 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
             if (s_total > 1) {
                 // slices of a row tile sit in neighbouring warps: add them in slice order through shared memory
                 if (valid && t == 0) { cta_red[round & 1][warp][g] = tot_lo; cta_red[round & 1][warp][g + 8] = tot_hi; }
-                __syncthreads();
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(kThreads) : "memory");  // the group's own barrier
                 finisher = valid && slice == 0;
                 if (finisher) {
                     tot_lo = tot_hi = 0.f;
@@ -798,6 +849,10 @@ __global__ void __launch_bounds__(kThreads, 3) qgemv1_kernel(const QGemvParams p
         }
     }
     cp_async_wait<0>();
+    if (p.trace) {
+        __syncthreads();
+        if (tid == 0) p.trace[blockIdx.x * 4 + 3] = global_timer_ns();
+    }
 }
 
 struct QGemvConfig {
@@ -822,22 +877,28 @@ QGemvConfig pick_config(const Q4Tiled& w, int m) {
         // of metadata per element), one CTA group
         const int kt4 = w.kt_pad / 4;
         c.nt = 0; c.sk = 1;
-        c.smem = (size_t)kRingBytes + (size_t)w.kt_pad * 160;
-        c.occ = std::max(1, std::min(3, (int)((227 * 1024) / (c.smem + 1024))));
-        const int slots = kSMs * c.occ;
+        // one CTA per SM made of up to three eight-warp groups (c.occ = groups) that share the activations
+        c.occ = kMaxGroups;
+        const size_t x_bytes = (size_t)w.kt_pad * 160, budget = 227 * 1024 - 8192;
+        while (c.occ > 1 && (size_t)c.occ * kRingBytes + x_bytes > budget) --c.occ;
+        c.smem = (size_t)c.occ * kRingBytes + x_bytes;
+        const int slots = kSMs * c.occ;  // groups resident on the GPU
+        int vgrid;
         if (w.row_tiles <= slots) {
-            // few row tiles: one row tile per CTA, its warps split K (no global scratch, no atomics)
+            // few row tiles: one row tile per group, its warps split K (no global scratch, no atomics)
             c.cta_mode = 1;
             c.si = 1;
             while (c.si < kWarps && c.si * 2 <= kt4) c.si *= 2;
             const int chunks = (w.row_tiles * c.si + kWarps - 1) / kWarps;
-            c.grid = dim3((unsigned)std::min(slots, chunks), 1, 1);
-            return c;
+            vgrid = std::min(slots, chunks);
+        } else {
+            c.si = 1;
+            while (c.si < 16 && c.si * 4 <= kt4 && (long long)w.row_tiles * c.si < 16LL * kSMs) c.si *= 2;
+            const int units = w.row_tiles * c.si;
+            vgrid = std::min(slots, (units + kWarps - 1) / kWarps);
         }
-        c.si = 1;
-        while (c.si < 16 && c.si * 4 <= kt4 && (long long)w.row_tiles * c.si < 16LL * kSMs) c.si *= 2;
-        const int units = w.row_tiles * c.si;
-        c.grid = dim3((unsigned)std::min(slots, (units + kWarps - 1) / kWarps), 1, 1);
+        // groups are numbered group-major (group * CTAs + CTA): work spreads over the SMs before it stacks up
+        c.grid = dim3((unsigned)std::min(kSMs, vgrid), 1, 1);
         return c;
     }
     c.nt = m <= 8 ? 1 : 2;
@@ -868,10 +929,26 @@ QGemvConfig pick_config(const Q4Tiled& w, int m) {
     return c;
 }
 
+// ---- phase tracing of the batch-1 kernel (diagnostic, SWLM_TRACE=1) ---------------------------------------
+// The first kTraceSlots launches get a slot each; a CUDA graph keeps the slots it was captured with, so after
+// replays the buffer holds the timeline of the last replayed decode step. The report goes to stderr when a context is
+// destroyed.
+constexpr int kTraceSlots = 256, kTraceCtas = 512;
+unsigned long long* g_trace_buf = nullptr;
+int g_trace_next = 0;
+struct TraceSlot { int ctas, row_tiles, kt4, epi, norm; };
+TraceSlot g_trace_slot[kTraceSlots];
+
 template <int EPI>
-int launch_1(const QGemvParams& p, const QGemvConfig& c, cudaStream_t s) {
-    cudaError_t e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true>, c.grid, dim3(kThreads), c.smem, s, p)
-                             : launch_k(qgemv1_kernel<EPI, false>, c.grid, dim3(kThreads), c.smem, s, p);
+int launch_1(const QGemvParams& p_in, const QGemvConfig& c, cudaStream_t s) {
+    QGemvParams p = p_in;
+    if (g_trace_buf && (int)c.grid.x <= kTraceCtas && g_trace_next < kTraceSlots) {
+        const int slot = g_trace_next++;
+        g_trace_slot[slot] = {(int)c.grid.x, p.row_tiles, p.kt4_total, EPI, p.norm_mode};
+        p.trace = g_trace_buf + (size_t)slot * kTraceCtas * 4;
+    }
+    cudaError_t e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true>, c.grid, dim3(c.occ * kThreads), c.smem, s, p)
+                             : launch_k(qgemv1_kernel<EPI, false>, c.grid, dim3(c.occ * kThreads), c.smem, s, p);
     if (e != cudaSuccess) return cuda_fail(e, "qgemv1 launch");
     return SWLM_OK;
 }
@@ -901,8 +978,45 @@ static int opt_in_smem(K kernel) {
     return SWLM_OK;
 }
 
+void qgemv_trace_report() {
+    if (!g_trace_buf) return;
+    cudaDeviceSynchronize();
+    std::vector<unsigned long long> h((size_t)kTraceSlots * kTraceCtas * 4);
+    if (cudaMemcpy(h.data(), g_trace_buf, h.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return;
+    const int used = std::min(g_trace_next, kTraceSlots);
+    unsigned long long origin = 0;
+    fprintf(stderr, "times in us from the first traced kernel's first CTA entry; dur = means over CTAs\n");
+    fprintf(stderr, "slot ctas rowtiles kt4 epi norm | first-entry first-deps last-deps last-xready first-done last-done | dur: wait prologue stream\n");
+    for (int sl = 0; sl < used; ++sl) {
+        const TraceSlot& t = g_trace_slot[sl];
+        const unsigned long long* r = h.data() + (size_t)sl * kTraceCtas * 4;
+        unsigned long long e0 = ~0ull, d0 = ~0ull, d1 = 0, x1 = 0, f0 = ~0ull, f1 = 0;
+        double a = 0, b = 0, c = 0;
+        int n = 0;
+        for (int i = 0; i < t.ctas; ++i) {
+            if (!r[i * 4] || !r[i * 4 + 3]) continue;
+            e0 = std::min(e0, r[i * 4]);
+            d0 = std::min(d0, r[i * 4 + 1]); d1 = std::max(d1, r[i * 4 + 1]);
+            x1 = std::max(x1, r[i * 4 + 2]);
+            f0 = std::min(f0, r[i * 4 + 3]); f1 = std::max(f1, r[i * 4 + 3]);
+            a += (double)(r[i * 4 + 1] - r[i * 4]); b += (double)(r[i * 4 + 2] - r[i * 4 + 1]); c += (double)(r[i * 4 + 3] - r[i * 4 + 2]);
+            ++n;
+        }
+        if (!n) continue;
+        if (!origin || e0 < origin) origin = e0;
+        auto rel = [&](unsigned long long v) { return ((double)v - (double)origin) / 1e3; };
+        fprintf(stderr, "%3d %4d %6d %4d %d %d | %9.2f %9.2f %9.2f %9.2f %9.2f %9.2f | %6.2f %6.2f %6.2f\n", sl, t.ctas, t.row_tiles, t.kt4, t.epi,
+                t.norm, rel(e0), rel(d0), rel(d1), rel(x1), rel(f0), rel(f1), a / n / 1e3, b / n / 1e3, c / n / 1e3);
+    }
+}
+
 int qgemv_init() {
     int rc;
+    const char* tr = getenv("SWLM_TRACE");
+    if (tr && tr[0] == '1' && !g_trace_buf) {
+        SWLM_CUDA(cudaMalloc((void**)&g_trace_buf, (size_t)kTraceSlots * kTraceCtas * 4 * 8));
+        SWLM_CUDA(cudaMemset(g_trace_buf, 0, (size_t)kTraceSlots * kTraceCtas * 4 * 8));
+    }
     if ((rc = opt_in_smem(qgemv_kernel<1, 0, false>))) return rc;
     if ((rc = opt_in_smem(qgemv_kernel<1, 1, false>))) return rc;
     if ((rc = opt_in_smem(qgemv_kernel<2, 0, false>))) return rc;

@@ -53,6 +53,12 @@ struct swlm_ctx {
     float* op_partial = nullptr; size_t op_partial_floats = 0;
     unsigned* op_attn_counters = nullptr; size_t op_attn_counter_count = 0;
     unsigned* op_counters = nullptr; size_t op_counter_count = 0;
+    int* tc_status = nullptr;  // device word the tcgen05 GEMM sets when one of its bounded waits expired
+    // Lifetime: plans keep their context alive, states their plan. A destroy call on an object that still has
+    // users only marks it; the memory goes when the last user is destroyed (hosts with garbage-collected
+    // wrappers release objects in no particular order).
+    int users = 0;
+    bool destroy_requested = false;
 };
 
 namespace {
@@ -224,6 +230,8 @@ struct swlm_plan {
     int attn_splits = 1;
     size_t attn_scratch = 0, qgemv_partial = 0, qgemv_counters = 0;
     int final_res = 0;  // physical residual buffer that holds the residual stream after a step
+    int users = 0;
+    bool destroy_requested = false;
 };
 
 namespace {
@@ -483,6 +491,12 @@ struct swlm_state {
     long long steps_host = 0;
     cudaGraphExec_t graph_full = nullptr, graph_body = nullptr;
     int64_t launches = 0;
+    // prompt ingestion in chunks: activation rows for `pf_rows` tokens per logical buffer, attention scratch
+    __nv_bfloat16* pf_buf[SWLM_BUF_COUNT] = {};
+    int pf_rows = 0;
+    unsigned* pf_attn_counters = nullptr;
+    int* pf_status = nullptr;      // device word: a bounded wait of the tensor-core product expired
+    int prefill_chunk = 512;       // tokens per chunk; 0 = one token at a time through the decode graph
 };
 
 struct swlm_snap {
@@ -708,6 +722,129 @@ int check_position_room(swlm_state* s, int steps) {
     return SWLM_OK;
 }
 
+// ---- prompt ingestion in chunks ---------------------------------------------------------------------
+// The reference's prefill runs sequence kernels over the whole prompt (Execution/MetalPrefillExecutor.swift,
+// gemm_q4_g64 or dequantise-then-matmul for the products) and replays the decode head for the last position.
+// Here all prompt tokens but the last go through the plan's steps, unfused, in chunks of up to
+// `prefill_chunk` tokens with one activation row per token: products on the tensor cores (tcgen05), norms and
+// SwiGLU row-wise, rope + KV append for the whole chunk, causal attention over the cache, the short-conv
+// recurrence walked in order inside one kernel. The last token (and a tail shorter than kPrefillMinChunk)
+// takes the decode graph, so the state a decode step sees afterwards is the one it would have produced itself.
+constexpr int kPrefillMinChunk = 32;
+
+bool prefill_batchable(const swlm_plan* plan) {
+    if (plan->desc.max_batch != 1 || plan->ctx->tp_size != 1 || plan->desc.head_dim > 128) return false;
+    for (const swlm_step& st : plan->steps) {
+        if (st.kind == SWLM_STEP_QGEMV && st.in_buf == st.out_buf) return false;
+        if (st.kind == SWLM_STEP_QGEMV && (st.k & 63)) return false;
+        if (st.kind == SWLM_STEP_CONV_STATE_UPDATE && st.conv_kernel > 8) return false;
+    }
+    return true;
+}
+
+int prefill_workspace(swlm_state* s, int rows) {
+    int rc;
+    if (!s->pf_status) {
+        if ((rc = dev_alloc(&s->pf_status, 1))) return rc;
+        SWLM_CUDA(cudaMemset(s->pf_status, 0, sizeof(int)));
+    }
+    if (rows <= s->pf_rows) return SWLM_OK;
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    for (int i = 0; i < SWLM_BUF_COUNT; ++i) { cudaFree(s->pf_buf[i]); s->pf_buf[i] = nullptr; }
+    cudaFree(s->pf_attn_counters); s->pf_attn_counters = nullptr;
+    s->pf_rows = 0;
+    for (int i = 0; i < SWLM_BUF_COUNT; ++i) {
+        if (i == SWLM_BUF_LOGITS) continue;  // the output head never runs on a chunk
+        if ((rc = dev_alloc(&s->pf_buf[i], (size_t)rows * s->width[i]))) return rc;
+    }
+    const size_t n_ctr = (size_t)rows * std::max(1, s->plan->desc.kv_heads);
+    if ((rc = dev_alloc(&s->pf_attn_counters, n_ctr))) return rc;
+    SWLM_CUDA(cudaMemset(s->pf_attn_counters, 0, n_ctr * sizeof(unsigned)));
+    size_t attn_floats = 0;
+    for (const swlm_step& st : s->plan->steps)
+        if (st.kind == SWLM_STEP_ATTN_DECODE) attn_floats = std::max(attn_floats, attn_scratch_floats(rows, st.heads, st.head_dim, 1));
+    if ((rc = grow_scratch(s, attn_floats, 0, 0))) return rc;
+    s->pf_rows = rows;
+    return SWLM_OK;
+}
+
+// `c` consecutive prompt tokens of sequence 0 (ids on the device at `tokens`), the first at position pos0.
+int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0, cudaStream_t stream) {
+    swlm_plan* plan = s->plan;
+    swlm_ctx* ctx = plan->ctx;
+    const swlm_buffers_desc& d = plan->desc;
+    __nv_bfloat16** pf = s->pf_buf;
+    const int* wd = s->width;
+    int rc = SWLM_OK;
+    for (const swlm_step& st : plan->steps) {
+        switch (st.kind) {
+        case SWLM_STEP_EMBED:
+            rc = launch_embed(c, st.n, tokens, d.vocab, find_dense(ctx, st.weight)->data, pf[st.out_buf], wd[st.out_buf], stream);
+            s->launches += 1;
+            break;
+        case SWLM_STEP_COPY_RMSNORM:
+        case SWLM_STEP_RESADD_COPY_RMSNORM:
+            rc = launch_rmsnorm(st.kind, c, st.n, pf[st.in_buf], wd[st.in_buf], pf[SWLM_BUF_RESIDUAL], wd[SWLM_BUF_RESIDUAL],
+                                find_dense(ctx, st.weight)->data, st.eps, st.weight_bias, pf[st.out_buf], wd[st.out_buf], stream);
+            s->launches += 1;
+            break;
+        case SWLM_STEP_RESADD_RMSNORM:  // final norm: part of the output head, which only the last token runs
+        case SWLM_STEP_ARGMAX:
+            break;
+        case SWLM_STEP_QGEMV: {
+            if (st.out_buf == SWLM_BUF_LOGITS) break;
+            const Q4Raw& raw = ctx->raw[st.weight];
+            rc = launch_qgemm_tc(raw, c, pf[st.in_buf], wd[st.in_buf], pf[st.out_buf], wd[st.out_buf], s->pf_status, stream);
+            s->launches += 1;
+            break;
+        }
+        case SWLM_STEP_QK_NORM:
+            rc = launch_qk_norm(c, st.heads, kv_heads_local(plan), st.head_dim, pf[st.in_buf], wd[st.in_buf], pf[st.in2_buf], wd[st.in2_buf],
+                                find_dense(ctx, st.weight)->data, find_dense(ctx, st.weight2)->data, st.eps, st.weight_bias, stream);
+            s->launches += 1;
+            break;
+        case SWLM_STEP_ATTN_DECODE: {
+            AttnLaunch a;
+            a.m = c; a.heads = st.heads; a.kv_heads = kv_heads_local(plan); a.head_dim = st.head_dim;
+            a.rope_dim = st.rope_dim;
+            if (st.rope_dim > 0) {
+                int ti = -1;
+                if ((rc = rope_table_for(plan, st.rope_dim, st.rope_base, &ti))) return rc;
+                a.inv_freq = plan->rope_tables[ti].inv_freq;
+            }
+            a.scale = st.scale;
+            a.q = pf[st.in_buf]; a.q_stride = wd[st.in_buf];
+            a.k = pf[st.in2_buf]; a.k_stride = wd[st.in2_buf];
+            a.v = pf[st.in3_buf]; a.v_stride = wd[st.in3_buf];
+            a.kcache = s->kcache + (size_t)st.layer * s->kv_layer_elems;
+            a.vcache = s->vcache + (size_t)st.layer * s->kv_layer_elems;
+            a.max_seq = d.max_seq; a.position = s->position; a.pos_base = pos0;
+            a.out = pf[st.out_buf]; a.out_stride = wd[st.out_buf];
+            a.scratch = s->attn_scratch; a.counters = s->pf_attn_counters; a.splits = 1;
+            rc = launch_attn_decode(a, stream);
+            s->launches += 2;
+            break;
+        }
+        case SWLM_STEP_SWIGLU:
+            rc = launch_swiglu(c, st.n, pf[st.in_buf], wd[st.in_buf], pf[st.in2_buf], wd[st.in2_buf], pf[st.out_buf], wd[st.out_buf], stream);
+            s->launches += 1;
+            break;
+        case SWLM_STEP_CONV_STATE_UPDATE:
+            rc = launch_conv_prefill(c, st.n, st.conv_kernel, s->conv + (size_t)st.layer * s->conv_layer_elems, pf[st.in_buf], wd[st.in_buf],
+                                     find_dense(ctx, st.weight)->data, pf[st.out_buf], wd[st.out_buf], stream);
+            s->launches += 1;
+            break;
+        default:
+            set_error("prompt ingestion: step kind %d", st.kind);
+            return SWLM_ERR_UNSUPPORTED;
+        }
+        if (rc) return rc;
+    }
+    rc = launch_fill_u32(reinterpret_cast<uint32_t*>(s->position), 1, (uint32_t)(pos0 + c), stream);
+    s->launches += 1;
+    return rc;
+}
+
 }  // namespace
 
 // =====================================================================================================
@@ -741,6 +878,7 @@ int swlm_ctx_create(int device_id, int tp_rank, int tp_size, swlm_ctx** out) {
     if (e != cudaSuccess) { delete ctx; return cuda_fail(e, "cudaStreamCreate"); }
     int rc = qgemv_init();
     if (!rc) rc = attn_init();
+    if (!rc) rc = qgemm_tc_init();
     if (rc) { cudaStreamDestroy(ctx->stream); delete ctx; return rc; }
     *out = ctx;
     return SWLM_OK;
@@ -748,11 +886,14 @@ int swlm_ctx_create(int device_id, int tp_rank, int tp_size, swlm_ctx** out) {
 
 void swlm_ctx_destroy(swlm_ctx* ctx) {
     if (!ctx) return;
+    if (ctx->users > 0) { ctx->destroy_requested = true; return; }
+    qgemv_trace_report();
     cudaSetDevice(ctx->device);
     for (auto& kv : ctx->raw) { cudaFree(kv.second.w); cudaFree(kv.second.scales); cudaFree(kv.second.biases); }
     for (auto& kv : ctx->tiled) { cudaFree(kv.second.tiles); cudaFree(kv.second.sb); }
     for (auto& kv : ctx->dense) cudaFree(kv.second.data);
     cudaFree(ctx->op_partial);
+    cudaFree(ctx->tc_status);
     cudaFree(ctx->op_counters);
     cudaFree(ctx->op_attn_counters);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -815,6 +956,7 @@ int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const sw
     if (rc) return rc;
     swlm_plan* plan = new swlm_plan();
     plan->ctx = ctx;
+    ctx->users += 1;
     plan->desc = *desc;
     plan->steps.assign(steps, steps + n_steps);
     rc = compile_plan(plan);
@@ -826,8 +968,13 @@ int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const sw
 
 void swlm_plan_destroy(swlm_plan* plan) {
     if (!plan) return;
+    if (plan->users > 0) { plan->destroy_requested = true; return; }
+    swlm_ctx* ctx = plan->ctx;
+    cudaSetDevice(ctx->device);
     for (RopeTable& t : plan->rope_tables) cudaFree(t.inv_freq);
     delete plan;
+    ctx->users -= 1;
+    if (ctx->users == 0 && ctx->destroy_requested) swlm_ctx_destroy(ctx);
 }
 
 int swlm_plan_launch_count(const swlm_plan* plan) { return plan ? launches_per_step(plan, false) : 0; }
@@ -857,6 +1004,7 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     const swlm_buffers_desc& d = plan->desc;
     swlm_state* s = new swlm_state();
     s->plan = plan;
+    plan->users += 1;
     auto fail = [&](int code) { swlm_state_destroy(s); return code; };
     cudaError_t e = cudaStreamCreateWithFlags(&s->own_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) return fail(cuda_fail(e, "cudaStreamCreate"));
@@ -909,9 +1057,14 @@ void swlm_state_destroy(swlm_state* s) {
     cudaFree(s->prompt);
     cudaFree(s->attn_scratch); cudaFree(s->qgemv_partial); cudaFree(s->qgemv_counters); cudaFree(s->attn_counters);
     cudaFree(s->argmax_val); cudaFree(s->argmax_idx);
+    for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->pf_buf[i]);
+    cudaFree(s->pf_attn_counters); cudaFree(s->pf_status);
     if (s->h_tok) cudaFreeHost(s->h_tok);
     if (s->own_stream) cudaStreamDestroy(s->own_stream);
+    swlm_plan* plan = s->plan;
     delete s;
+    plan->users -= 1;
+    if (plan->users == 0 && plan->destroy_requested) swlm_plan_destroy(plan);
 }
 
 int swlm_state_set_stream(swlm_state* s, void* cuda_stream) {
@@ -1068,7 +1221,17 @@ int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_tok
     // Every prompt token runs the layer stack; only the last one runs the output head, as the reference's
     // prefill replays the decode plan's lm_head + argmax for the final position
     // (Execution/MetalPrefillExecutor.swift:1320-1359).
-    for (int t = 0; t < n; ++t) {
+    int t = 0;
+    if (s->prefill_chunk >= kPrefillMinChunk && prefill_batchable(s->plan)) {
+        while (n - 1 - t >= kPrefillMinChunk) {
+            const int c = std::min(s->prefill_chunk, n - 1 - t);
+            if ((rc = prefill_workspace(s, std::min(s->prefill_chunk, n - 1)))) return rc;
+            if ((rc = enqueue_prefill_chunk(s, s->prompt + t, c, s->pos_host, s->stream))) return rc;
+            s->pos_host += c;
+            t += c;
+        }
+    }
+    for (; t < n; ++t) {
         SWLM_CUDA(cudaMemcpyAsync(s->token_in, s->prompt + (size_t)t * m, sizeof(int32_t) * m, cudaMemcpyDeviceToDevice, s->stream));
         rc = run_graph(s, t + 1 < n);
         if (rc) return rc;
@@ -1076,6 +1239,17 @@ int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_tok
     SWLM_CUDA(cudaMemcpyAsync(s->h_tok + m, s->token_out, sizeof(int32_t) * m, cudaMemcpyDeviceToHost, s->stream));
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     memcpy(first_token, s->h_tok + m, sizeof(int32_t) * m);
+    if (s->pf_status) {
+        int st = 0;
+        SWLM_CUDA(cudaMemcpy(&st, s->pf_status, sizeof(int), cudaMemcpyDeviceToHost));
+        if (st) { set_error("prefill: a bounded wait in the tensor-core product expired"); return SWLM_ERR_TIMEOUT; }
+    }
+    return SWLM_OK;
+}
+
+int swlm_state_set_prefill_chunk(swlm_state* s, int tokens) {
+    if (!s || tokens < 0) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    s->prefill_chunk = tokens;
     return SWLM_OK;
 }
 
@@ -1294,7 +1468,18 @@ int swlm_op_qgemm_dev(swlm_ctx* ctx, const char* weight, int m, const void* x_de
     rc = get_tiled(ctx, {weight}, 0, &w);
     if (rc) return rc;
     cudaStream_t stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->stream;
-    // m > 16 runs as passes of 16 rows: each pass re-streams the weights
+    // m >= 64: tensor-core contraction straight from the packed source copy
+    auto raw = ctx->raw.find(weight);
+    if (m >= kQGemmTcMinRows && raw != ctx->raw.end() && !raw->second.sb_f16 && raw->second.k % 64 == 0) {
+        if (!ctx->tc_status) {
+            if ((rc = dev_alloc(&ctx->tc_status, 1))) return rc;
+            SWLM_CUDA(cudaMemsetAsync(ctx->tc_status, 0, sizeof(int), ctx->stream));
+            SWLM_CUDA(cudaStreamSynchronize(ctx->stream));
+        }
+        return launch_qgemm_tc(raw->second, m, static_cast<const __nv_bfloat16*>(x_dev), raw->second.k,
+                               static_cast<__nv_bfloat16*>(y_dev), raw->second.n, ctx->tc_status, stream);
+    }
+    // 16 < m < 64 runs as passes of 16 rows: each pass re-streams the weights
     for (int m0 = 0; m0 < m; m0 += 16) {
         const int mc = std::min(16, m - m0);
         rc = op_scratch(ctx, *w, mc);
@@ -1330,6 +1515,11 @@ int swlm_op_qgemm(swlm_ctx* ctx, const char* weight, int m, const uint16_t* x_bf
     if (rc) return rc;
     if (e != cudaSuccess) return cuda_fail(e, "qgemm copies");
     if (e2 != cudaSuccess) return cuda_fail(e2, "qgemm sync");
+    if (ctx->tc_status) {
+        int st = 0;
+        SWLM_CUDA(cudaMemcpy(&st, ctx->tc_status, sizeof(int), cudaMemcpyDeviceToHost));
+        if (st) { set_error("qgemm: a bounded wait in the tensor-core kernel expired"); return SWLM_ERR_TIMEOUT; }
+    }
     return SWLM_OK;
 }
 

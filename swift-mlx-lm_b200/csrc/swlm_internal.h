@@ -133,6 +133,7 @@ size_t qgemv_scratch_floats(const Q4Tiled& w, int m);
 int qgemv_counter_count(const Q4Tiled& w);
 int launch_qgemv(const QGemvLaunch& a, cudaStream_t s);
 int qgemv_init();  // sets shared-memory attributes once per process
+void qgemv_trace_report();  // SWLM_TRACE=1: phase timeline of the batch-1 launches, to stderr
 
 // rmsnorm family: mode = SWLM_STEP_COPY_RMSNORM / RESADD_COPY_RMSNORM / RESADD_RMSNORM
 int launch_rmsnorm(int mode, int m, int dim, const __nv_bfloat16* in, int in_stride, __nv_bfloat16* residual,
@@ -148,6 +149,10 @@ int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const _
 int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,
                      const __nv_bfloat16* in, int in_stride, const __nv_bfloat16* weight,
                      __nv_bfloat16* out, int out_stride, cudaStream_t s);
+// conv_state_update over `tokens` consecutive tokens of one sequence (state of that sequence), bit-identical to
+// `tokens` single steps.
+int launch_conv_prefill(int tokens, int dim, int kernel, __nv_bfloat16* state, const __nv_bfloat16* in, int in_stride,
+                        const __nv_bfloat16* weight, __nv_bfloat16* out, int out_stride, cudaStream_t s);
 // argmax over [m][n] bf16, lowest index wins. Writes token_out[m], token_in_next[m] (may be null) and
 // ring[(step_counter % ring_cap) * m + b] (ring may be null); when advance != 0 the last thread also
 // increments the device-side position and step counter. Two launches.
@@ -174,6 +179,9 @@ struct AttnLaunch {
     float* scratch = nullptr;   // attn_scratch_floats()
     unsigned* counters = nullptr;  // m * kv_heads arrival counters, zero between launches
     int splits = 1;             // KV splits per (sequence, kv head)
+    // >= 0: prompt ingestion. The m rows are consecutive tokens of sequence 0 starting at this position; their
+    // k/v rows are appended first, then token b attends cache rows 0..pos_base+b. `position` is not read.
+    int pos_base = -1;
 };
 int attn_pick_splits(int m, int kv_heads, int max_ctx);
 size_t attn_scratch_floats(int m, int heads, int head_dim, int splits);
@@ -188,6 +196,12 @@ size_t flash_decode_static_capacity();
 int launch_flash_decode_static(int device, int m, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, float scale,
                                const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, __nv_bfloat16* out,
                                cudaStream_t s);
+
+// Tensor-core (tcgen05) form of the quantised product for m >= kQGemmTcMinRows, fed from the packed source copy.
+constexpr int kQGemmTcMinRows = 64;
+int qgemm_tc_init();
+int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
+                    int* status, cudaStream_t s);
 
 int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s);
 int launch_advance(int32_t* position, int32_t* step_counter, cudaStream_t s);

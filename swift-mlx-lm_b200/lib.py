@@ -80,6 +80,7 @@ SIGNATURES = {
     "swlm_state_create": (_I, [_P, C.POINTER(_P)]),
     "swlm_state_destroy": (None, [_P]),
     "swlm_state_set_stream": (_I, [_P, _P]),
+    "swlm_state_set_prefill_chunk": (_I, [_P, _I]),
     "swlm_state_reset": (_I, [_P]),
     "swlm_state_snapshot": (_I, [_P, C.POINTER(_P)]),
     "swlm_state_restore": (_I, [_P, _P]),

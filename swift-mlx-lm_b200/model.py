@@ -146,6 +146,10 @@ class InferenceModel:
     def set_stream(self, cuda_stream: int) -> None:
         self.lib.check(self.lib.swlm_state_set_stream(self.state, C.c_void_p(cuda_stream)))
 
+    def set_prefill_chunk(self, tokens: int) -> None:
+        """Tokens per prompt-ingestion chunk (0: one token at a time through the decode graph)."""
+        self.lib.check(self.lib.swlm_state_set_prefill_chunk(self.state, tokens))
+
     def prompt_snapshot(self) -> C.c_void_p:
         snap = C.c_void_p()
         self.lib.check(self.lib.swlm_state_snapshot(self.state, C.byref(snap)))

@@ -81,6 +81,47 @@ def test_qgemm_more_than_16_rows_runs_in_passes(pkg, store, oracle):
     assert rel_err(got, ref).max() <= RTOL
 
 
+@pytest.mark.parametrize("n,k,m", [
+    (128, 64, 64),        # one tile, one group
+    (256, 256, 64),
+    (192, 512, 100),      # ragged in both the weight rows and the tokens
+    (512, 4096, 128),     # 128-token tile
+    (1000, 1024, 300),    # several token tiles, last one partial
+])
+def test_qgemm_tensor_core_matches_oracle(pkg, store, oracle, n, k, m):
+    """m >= 64 runs on the tcgen05 kernel. It follows the reference's dequantise-then-matmul prefill route
+    (dequant_q4_g64_bf16, then a bf16 x bf16 product accumulated in fp32): the oracle is the pinned bf16
+    dequantisation followed by an fp64 product, tolerance 1e-2 per bf16 output. Against the route that keeps
+    the dequantised weights in fp32 (gemm_q4_g64) the bf16 rounding of the weights shows as noise of about
+    2^-9 of the output's scale, checked in the L2 norm."""
+    w, s, b = pkg.synth_q4(n, k, seed=n * 17 + k + m)
+    x = _bf(pkg, np.random.default_rng(m).normal(size=(m, k)))
+    name = f"tc.{n}x{k}x{m}"
+    store.add_q4_mlx(name, w, s, b)
+    got = pkg.bf16_to_f32(store.qgemm(name, x, n))
+    wq = pkg.bf16_to_f32(oracle.dequant_bf16(w, s, b)).astype(np.float64)
+    ref = pkg.bf16_to_f32(pkg.f32_to_bf16((pkg.bf16_to_f32(x).astype(np.float64) @ wq.T).astype(np.float32)))
+    assert rel_err(got, ref).max() <= RTOL
+    oracle.set_threads(0)
+    ref32 = pkg.bf16_to_f32(oracle.qgemm(x, w, s, b))
+    assert np.linalg.norm(got - ref32) <= 4e-3 * np.linalg.norm(ref32)
+
+
+@pytest.mark.parametrize("n,k,m", [(384, 1024, 64), (130, 128, 128)])
+def test_qgemm_tensor_core_one_hot_is_bit_exact(pkg, store, oracle, n, k, m):
+    """One-hot tokens pick single columns of the dequantised matrix: the tensor-core path must return
+    bf16(scale * q + zero) bit for bit, which pins the nibble order, the shared-memory swizzle and the
+    accumulator read-out at once."""
+    w, s, b = pkg.synth_q4(n, k, seed=n + k)
+    cols = (np.arange(m) * 37 + 5) % k
+    x = np.zeros((m, k), dtype=np.float32)
+    x[np.arange(m), cols] = 1.0
+    store.add_q4_mlx(f"tc1h.{n}", w, s, b)
+    got = store.qgemm(f"tc1h.{n}", _bf(pkg, x), n)
+    want = oracle.dequant_bf16(w, s, b)
+    assert np.array_equal(got, want[:, cols].T)
+
+
 def test_device_layout_dequantises_bit_exactly(pkg, store, oracle):
     for n, k in [(48, 256), (37, 64 * 7), (512, 4096)]:
         w, s, b = pkg.synth_q4(n, k, seed=n + k)
