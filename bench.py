@@ -163,7 +163,8 @@ def run_op(args, pkg):
     if args.op == "qgemv":
         n, k, m = args.n, args.k, args.m
         per_set = n * k * 0.5625
-        sets = max(2, int(np.ceil(max(args.min_mb, 1) * 1e6 / per_set)))
+        # --min-mb 0: one weight set, i.e. L2-resident weights when they fit (shows the compute-side ceiling)
+        sets = 1 if args.min_mb <= 0 else max(2, int(np.ceil(args.min_mb * 1e6 / per_set)))
         for i in range(sets):
             store.add_q4_mlx(f"w{i}", *pkg.synth_q4(n, k, seed=i))
         x = torch.randn(m, k, device="cuda").bfloat16()

@@ -45,6 +45,7 @@ struct AttnParams {
     float* part_o;   // [m][heads][splits][HD]
     float* part_ml;  // [m][heads][splits][2]
     unsigned* counters;  // [m][kv_heads], zero between launches
+    PrefetchTarget prefetch;  // weights of a later product, requested into L2 while this kernel runs
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -79,6 +80,9 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
     constexpr bool DECODE = MODE == 1;
     constexpr bool PREFILL = MODE == 2;
     pdl_launch_dependents();
+    if (DECODE)
+        prefetch_target_slice(p.prefetch, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                              gridDim.x * gridDim.y * gridDim.z, threadIdx.x, kSplitThreads);
     pdl_wait();
     constexpr int NCH = HD / 32;  // 16-byte K chunks per lane per token
     constexpr int VH = HD / 64;   // 64-dimension halves of V
@@ -516,6 +520,7 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     p.part_o = a.scratch;
     p.part_ml = a.scratch + (size_t)a.m * a.heads * a.splits * a.head_dim;
     p.counters = a.counters;
+    p.prefetch = a.prefetch;
     if (a.pos_base >= 0) {
         // prompt ingestion: rows of q/k/v are consecutive tokens of sequence 0
         if (a.head_dim > 128) { set_error("attention: head_dim %d not supported", a.head_dim); return SWLM_ERR_UNSUPPORTED; }

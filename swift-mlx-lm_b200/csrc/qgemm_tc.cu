@@ -227,6 +227,7 @@ __global__ void __launch_bounds__(kTcThreads) qgemm_tc_kernel(const QGemmTcParam
             umma_commit(&empty_bar[s]);
             if (kt == kt_total - 1) umma_commit(&done_bar);
         }
+        __syncwarp();  // warp 0 arrives at the block-wide barriers as one
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 

@@ -29,6 +29,7 @@
 
 #include "swlm_internal.h"
 #include "tp_device.cuh"
+#include "qgemv_common.cuh"
 
 namespace swlm {
 namespace {
@@ -44,41 +45,6 @@ constexpr int kMaxGroups = 3;
 constexpr int kMaxWarps1 = kMaxGroups * kWarps;
 constexpr int kXPad = 8;                   // bf16 elements of padding per x row (bank skew)
 constexpr int kL2Ahead = 10;               // stages (2.3 KB each) a warp prefetches into L2 ahead of its ring
-
-struct QGemvParams {
-    const uint4* tiles;
-    const uint4* sb;
-    int row_tiles, kt4_total, sb_f16;
-    const __nv_bfloat16* x;
-    int x_stride, k;
-    __nv_bfloat16* y[3];
-    int y_stride[3], seg_end[3];
-    int m;
-    int si, sk;   // k-slices per CTA group, CTA groups along K
-    int si_shift; // log2(si) for the batch-1 kernel
-    int cta_mode; // batch-1 kernel: slices of a row tile live in one CTA and meet in shared memory
-    float* partial;
-    unsigned* counters;
-    // optional fused residual-add / copy / RMSNorm in front of the product (norm_mode = step kind, 0 = none)
-    int norm_mode;
-    const __nv_bfloat16* res_in;
-    __nv_bfloat16* res_out;
-    int res_stride;
-    const __nv_bfloat16* norm_w;
-    float eps, weight_bias;
-    // tensor parallel: push = this product's rows are partial sums that go to every rank's exchange buffer;
-    // in_tp = the fused norm's input is the sum of the partials the preceding product pushed
-    int push, in_tp;
-    TpParams tp;
-    // phase timestamps (SWLM_TRACE=1): [cta][4] = kernel entry, predecessor complete, activations ready, done
-    unsigned long long* trace;
-};
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
@@ -632,6 +598,7 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
     // to a cap) to be moved from HBM into L2, a few instructions in total, so that HBM streams at full rate
     // while the preceding kernel drains and the activations are prepared; the ring then fills from L2.
     pdl_launch_dependents();
+    prefetch_target_slice(p.prefetch, blockIdx.x, gridDim.x, tid, blockDim.x);  // a later launch's weights
     {
         const int pu0 = p.cta_mode ? u_first : u_lo;
         const int pu1 = p.cta_mode ? min(u_first + kWarps, units) : u_hi;
@@ -663,62 +630,58 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
         __syncthreads();
     }
     const int nthreads = blockDim.x;
-    for (int run = tid; run < kt_total * 4 || (p.norm_mode && run < nthreads); run += nthreads) {
-        const int k0 = run * 16;
-        unsigned w[8];
+    const int nruns = kt_total * 8;  // runs of 8 elements: eight neighbouring threads share a group of 64
+    for (int run = tid; run < nruns || (p.norm_mode && run < nthreads); run += nthreads) {
+        const int k0 = run * 8;
+        float xf[8];
         if (p.norm_mode) {
             // dimension <= 4096: exactly one pass, every thread takes part in the block-wide sum
-            fused_norm_run(p, 0, k0, k0 < p.k, blockIdx.x == 0, red, w, tp_epoch, nthreads >> 5);
-            if (run >= kt_total * 4) continue;
+            fused_norm_run8(p, k0, k0 < p.k, blockIdx.x == 0, red, xf, tp_epoch, nthreads >> 5);
+            if (run >= nruns) continue;
         } else {
-            uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
-            if (k0 < p.k) {
-                const uint4* src = reinterpret_cast<const uint4*>(p.x + k0);
-                v0 = __ldg(src);
-                v1 = __ldg(src + 1);
-            }
-            w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w; w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
-        }
-        // one exponent per group of 64: the four runs of a group sit in four neighbouring threads
-        const unsigned act = __activemask();
-        unsigned mx = 0;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (k0 < p.k) v = __ldg(reinterpret_cast<const uint4*>(p.x + k0));
+            const unsigned vw[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
-        mx = max(mx, __shfl_xor_sync(act, mx, 1));
-        mx = max(mx, __shfl_xor_sync(act, mx, 2));
-        const int e = (int)(mx >> 7);  // biased exponent of the group's largest magnitude
-        const bool live = e >= 16 && e < 255;
-        // largest magnitude -> [2^13, 2^14): multiply by 2^(140 - e); 15-bit integers, two signed bytes each
-        const float mul = live ? __uint_as_float((unsigned)(267 - e) << 23) : 0.f;
-        int q[16];
+            for (int i = 0; i < 4; ++i) { xf[2 * i] = __uint_as_float(vw[i] << 16); xf[2 * i + 1] = __uint_as_float(vw[i] & 0xFFFF0000u); }
+        }
+        // one exponent per group of 64
+        const unsigned act = __activemask();
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(xf[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(act, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(act, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(act, amax, 4));
+        const int e = (int)(__float_as_uint(amax) >> 23);  // biased exponent of the group's largest magnitude
+        const bool live = e >= 16 && e < 255;               // not all-zero / denormal, not inf / nan
+        // largest magnitude -> [2^13, 2^14): multiply by 2^(140 - e). Adding 1.5 * 2^23 leaves the rounded
+        // (nearest-even) integer in the low mantissa bits in two's complement: its low byte is the low digit
+        // as a signed byte, and (v + 128) >> 8 is the high digit, v = 256 * hi + lo.
+        const float mul = __uint_as_float((unsigned)(267 - e) << 23);
+        unsigned rb[8], rh[8];
         int sum = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            q[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * mul);
-            q[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * mul);
-            sum += q[2 * i] + q[2 * i + 1];
+            rb[i] = live ? __float_as_uint(fmaf(xf[i], mul, 12582912.0f)) : 0x4B400000u;
+            rh[i] = rb[i] + 128u;
+            sum += (int)(rb[i] - 0x4B400000u);
         }
         sum += __shfl_xor_sync(act, sum, 1);
         sum += __shfl_xor_sync(act, sum, 2);
-        // v = 256 * hi + lo with both digits signed bytes; byte order inside a 4-element step matches the
-        // nibble order of a weight word: 0, 2, 1, 3
-        unsigned hi[4], lo[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int v[4] = {q[4 * j], q[4 * j + 2], q[4 * j + 1], q[4 * j + 3]};
-            unsigned hw = 0, lw = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int h = (v[i] + 128) >> 8, l = v[i] - (h << 8);
-                hw |= ((unsigned)h & 0xFFu) << (8 * i);
-                lw |= ((unsigned)l & 0xFFu) << (8 * i);
-            }
-            hi[j] = hw; lo[j] = lw;
-        }
-        xq[run * 2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        xq[run * 2 + 1] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        sum += __shfl_xor_sync(act, sum, 4);
+        // byte order inside a 4-element step matches the nibble order of a weight word: 0, 2, 1, 3
+        uint2 hi, lo;
+        lo.x = __byte_perm(__byte_perm(rb[0], rb[2], 0x0040), __byte_perm(rb[1], rb[3], 0x0040), 0x5410);
+        lo.y = __byte_perm(__byte_perm(rb[4], rb[6], 0x0040), __byte_perm(rb[5], rb[7], 0x0040), 0x5410);
+        hi.x = __byte_perm(__byte_perm(rh[0], rh[2], 0x0051), __byte_perm(rh[1], rh[3], 0x0051), 0x5410);
+        hi.y = __byte_perm(__byte_perm(rh[4], rh[6], 0x0051), __byte_perm(rh[5], rh[7], 0x0051), 0x5410);
+        // a quarter of a group (16 elements) is 16 high-digit bytes followed by 16 low-digit bytes
+        unsigned char* qd = reinterpret_cast<unsigned char*>(xq) + (size_t)(run >> 1) * 32 + (run & 1) * 8;
+        *reinterpret_cast<uint2*>(qd) = hi;
+        *reinterpret_cast<uint2*>(qd + 16) = lo;
         const float scale = live ? __uint_as_float((unsigned)(e - 13) << 23) : 0.f;  // 2^(e - 140) = 1 / mul
-        if ((run & 3) == 0) xmeta[run >> 2] = make_float2(scale, (float)sum * scale);
+        if ((run & 7) == 0) xmeta[run >> 3] = make_float2(scale, (float)sum * scale);
     }
     __syncthreads();
 
@@ -743,7 +706,7 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
         const bool valid = u < u_end;
         const int rt = u >> p.si_shift;
         const int slice = u & si_mask;
-        float tot_lo = 0.f, tot_hi = 0.f;
+        float tot_lo = 0.f, tot_hi = 0.f, tot_hi16 = 0.f, tot_hiz = 0.f;
         int a0 = 0, a1 = 0;
         if (valid) unit_range(u, a0, a1);
         for (int a = a0; a < a1; ++a) {
@@ -769,18 +732,22 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
                 // B operand: column 0 = high digits, column 1 = low digits of the activations, the rest zero
                 const uint4 xd = *reinterpret_cast<const uint4*>(xbase + ti * xtile_stride);
                 int c[4];
-                // rows g take the low nibble of every byte, rows g + 8 the high nibble: exact 8-bit integers
-                imma_u8s8_zero(c, wv.x & 0x0F0F0F0Fu, (wv.x >> 4) & 0x0F0F0F0Fu, wv.y & 0x0F0F0F0Fu, (wv.y >> 4) & 0x0F0F0F0Fu, xd.x, xd.y);
-                imma_u8s8(c, wv.z & 0x0F0F0F0Fu, (wv.z >> 4) & 0x0F0F0F0Fu, wv.w & 0x0F0F0F0Fu, (wv.w >> 4) & 0x0F0F0F0Fu, xd.z, xd.w);
-                // lanes t == 0 hold columns 0 and 1 of rows g and g + 8: sum(q * x) = 256 * hi + lo, exactly
-                const float fa = (float)(c[0] * 256 + c[1]), fb = (float)(c[2] * 256 + c[3]);
-                const float s_lo = sb_scale<F16SB>(sAw[ti]) * mscale[ti], z_lo = sb_zero<F16SB>(sAw[ti]);
-                const float s_hi = sb_scale<F16SB>(sBw[ti]) * mscale[ti], z_hi = sb_zero<F16SB>(sBw[ti]);
-                tot_lo = fmaf(s_lo, fa, fmaf(z_lo, msum[ti], tot_lo));
-                tot_hi = fmaf(s_hi, fb, fmaf(z_hi, msum[ti], tot_hi));
+                // A byte holds the nibble of row g (low) and of row g + 8 (high) for the same column. Rows g take
+                // the masked low nibbles; rows g + 8 take the bytes as they are, lo + 16 * hi, against the same
+                // activations: their sum is (row g's sum) + 16 * (row g + 8's sum), all exact integers, so the
+                // high rows cost no unpacking at all and are recovered by one subtraction
+                imma_u8s8_zero(c, wv.x & 0x0F0F0F0Fu, wv.x, wv.y & 0x0F0F0F0Fu, wv.y, xd.x, xd.y);
+                imma_u8s8(c, wv.z & 0x0F0F0F0Fu, wv.z, wv.w & 0x0F0F0F0Fu, wv.w, xd.z, xd.w);
+                // lanes t == 0 hold columns 0 and 1 (high and low activation digits): sum = 256 * hi + lo
+                const float fa = (float)(c[0] * 256 + c[1]);
+                const float fb16 = (float)((c[2] - c[0]) * 256 + (c[3] - c[1]));  // 16 x the sum of row g + 8
+                tot_lo = fmaf(sb_scale<F16SB>(sAw[ti]) * mscale[ti], fa, fmaf(sb_zero<F16SB>(sAw[ti]), msum[ti], tot_lo));
+                tot_hi16 = fmaf(sb_scale<F16SB>(sBw[ti]) * mscale[ti], fb16, tot_hi16);
+                tot_hiz = fmaf(sb_zero<F16SB>(sBw[ti]), msum[ti], tot_hiz);
             }
             __syncwarp();
         }
+        tot_hi = fmaf(tot_hi16, 0.0625f, tot_hiz);
         // lanes t == 0 hold the sums of rows g and g + 8; the other lanes carried zero columns
 
         bool finisher = valid;
@@ -942,11 +909,7 @@ TraceSlot g_trace_slot[kTraceSlots];
 template <int EPI>
 int launch_1(const QGemvParams& p_in, const QGemvConfig& c, cudaStream_t s) {
     QGemvParams p = p_in;
-    if (g_trace_buf && (int)c.grid.x <= kTraceCtas && g_trace_next < kTraceSlots) {
-        const int slot = g_trace_next++;
-        g_trace_slot[slot] = {(int)c.grid.x, p.row_tiles, p.kt4_total, EPI, p.norm_mode};
-        p.trace = g_trace_buf + (size_t)slot * kTraceCtas * 4;
-    }
+    p.trace = qgemv_trace_slot((int)c.grid.x, p.row_tiles, p.kt4_total, EPI, p.norm_mode);
     cudaError_t e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true>, c.grid, dim3(c.occ * kThreads), c.smem, s, p)
                              : launch_k(qgemv1_kernel<EPI, false>, c.grid, dim3(c.occ * kThreads), c.smem, s, p);
     if (e != cudaSuccess) return cuda_fail(e, "qgemv1 launch");
@@ -978,6 +941,13 @@ static int opt_in_smem(K kernel) {
     return SWLM_OK;
 }
 
+unsigned long long* qgemv_trace_slot(int ctas, int row_tiles, int kt4, int epi, int norm) {
+    if (!g_trace_buf || ctas > kTraceCtas || g_trace_next >= kTraceSlots) return nullptr;
+    const int slot = g_trace_next++;
+    g_trace_slot[slot] = {ctas, row_tiles, kt4, epi, norm};
+    return g_trace_buf + (size_t)slot * kTraceCtas * 4;
+}
+
 void qgemv_trace_report() {
     if (!g_trace_buf) return;
     cudaDeviceSynchronize();
@@ -1005,8 +975,34 @@ void qgemv_trace_report() {
         if (!n) continue;
         if (!origin || e0 < origin) origin = e0;
         auto rel = [&](unsigned long long v) { return ((double)v - (double)origin) / 1e3; };
-        fprintf(stderr, "%3d %4d %6d %4d %d %d | %9.2f %9.2f %9.2f %9.2f %9.2f %9.2f | %6.2f %6.2f %6.2f\n", sl, t.ctas, t.row_tiles, t.kt4, t.epi,
+        fprintf(stderr, "%3d %4d %6d %4d %d %d | %9.2f %9.2f %9.2f %9.2f %9.2f %9.2f | %6.2f %6.2f %6.2f", sl, t.ctas, t.row_tiles, t.kt4, t.epi,
                 t.norm, rel(e0), rel(d0), rel(d1), rel(x1), rel(f0), rel(f1), a / n / 1e3, b / n / 1e3, c / n / 1e3);
+        // the tensor-core kernel also stamps the end of its set-up and the release of its TMEM, in the rows after
+        // its CTAs'
+        if (2 * t.ctas <= kTraceCtas && r[t.ctas * 4]) {
+            unsigned long long s1 = 0, r1 = 0;
+            double dd = 0, tw = 0, tl = 0, gap = 0, gapmax = 0, setup = 0;
+            for (int i = 0; i < t.ctas; ++i) {
+                const unsigned long long* q = r + (size_t)(t.ctas + i) * 4;
+                s1 = std::max(s1, q[0]); r1 = std::max(r1, q[1]);
+                dd += (double)(q[1] - q[2]); tw += (double)(q[3] >> 32); tl += (double)(q[3] & 0xFFFFFFFFull);
+                gap += (double)q[2] - (double)r[i * 4 + 3]; gapmax = std::max(gapmax, (double)q[2] - (double)r[i * 4 + 3]);
+                setup += (double)q[0] - (double)r[i * 4];
+            }
+            if (3 * t.ctas <= kTraceCtas) {
+                double m0 = 0, m1 = 0, m2 = 0, m3 = 0;
+                for (int i = 0; i < t.ctas; ++i) {
+                    const unsigned long long* q2 = r + (size_t)(2 * t.ctas + i) * 4;
+                    const double done = (double)r[i * 4 + 3];
+                    m0 += (double)q2[0] - done; m1 += (double)q2[1] - done; m2 += (double)q2[2] - done; m3 += (double)q2[3] - done;
+                }
+                fprintf(stderr, " | rel. to done (us): mma loop exit %.2f, warp1 after last barrier %.2f, epilogue exit %.2f, mask exit %.2f",
+                        m0 / t.ctas / 1e3, m1 / t.ctas / 1e3, m2 / t.ctas / 1e3, m3 / t.ctas / 1e3);
+            }
+            fprintf(stderr, " | set-up mean %.2f us, last done %9.2f; done -> release mean %.2f max %.2f us, release %.2f us; epilogue clocks per CTA: waiting for MMAs %.0f, reading TMEM %.0f",
+                    setup / t.ctas / 1e3, rel(s1), gap / t.ctas / 1e3, gapmax / 1e3, dd / t.ctas / 1e3, tw / t.ctas, tl / t.ctas);
+        }
+        fprintf(stderr, "\n");
     }
 }
 
@@ -1061,6 +1057,7 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
     p.si_shift = 0;
     while ((1 << p.si_shift) < c.si) ++p.si_shift; p.partial = a.partial; p.counters = a.counters;
     p.push = a.push; p.in_tp = a.in_tp; p.tp = a.tp;
+    p.prefetch = a.prefetch;
     if ((a.push || a.in_tp) && (a.tp.tp < 2 || !a.tp.epoch || !a.tp.done || !a.tp.status)) { set_error("qgemv: tensor-parallel exchange not attached"); return SWLM_ERR_STATE; }
     if (a.in_tp && !a.norm.mode) { set_error("qgemv: a pushed partial sum must be consumed by a fused norm"); return SWLM_ERR_INVALID; }
     p.norm_mode = a.norm.mode;

@@ -48,6 +48,7 @@ struct swlm_ctx {
     cudaStream_t stream = nullptr;
     std::map<std::string, Q4Raw> raw;
     std::map<std::string, Q4Tiled> tiled;  // plain and fused tensors, keyed by name ("a|b|c" for fused)
+    std::map<std::string, Q4Umma> umma;    // the same tensors as shared-memory images for the tensor-core GEMV
     std::map<std::string, DenseTensor> dense;
     int64_t bytes = 0;
     float* op_partial = nullptr; size_t op_partial_floats = 0;
@@ -143,6 +144,45 @@ int get_tiled(swlm_ctx* ctx, const std::vector<std::string>& names, int mode, co
     return SWLM_OK;
 }
 
+// Build (or fetch) the tensor-core GEMV layout for one raw tensor or a fusion of several (same keys as above).
+int get_umma(swlm_ctx* ctx, const std::vector<std::string>& names, int mode, const Q4Umma** out) {
+    std::string key = names[0];
+    for (size_t i = 1; i < names.size(); ++i) key += (mode == 1 ? "^" : "|") + names[i];
+    auto found = ctx->umma.find(key);
+    if (found != ctx->umma.end()) { *out = &found->second; return SWLM_OK; }
+    RepackSrc src[3];
+    int n_total = 0, k = 0;
+    bool f16 = false;
+    for (size_t i = 0; i < names.size(); ++i) {
+        auto it = ctx->raw.find(names[i]);
+        if (it == ctx->raw.end()) { set_error("tensor '%s' not in the weight store", names[i].c_str()); return SWLM_ERR_NOT_FOUND; }
+        const Q4Raw& r = it->second;
+        if (i == 0) { k = r.k; f16 = r.sb_f16; }
+        else if (r.k != k || r.sb_f16 != f16) { set_error("fused tensors must share K and header type"); return SWLM_ERR_INVALID; }
+        src[i] = RepackSrc{r.w, r.scales, r.biases, r.n};
+        n_total += r.n;
+    }
+    Q4Umma t;
+    t.k = k; t.sb_f16 = f16; t.interleaved = mode == 1;
+    t.chunks = (k + 127) / 128;
+    if (mode == 1) {
+        if (names.size() != 2 || src[0].n != src[1].n) { set_error("interleave needs two tensors with equal N"); return SWLM_ERR_INVALID; }
+        t.n = src[0].n;
+        t.row_blocks = (src[0].n + 127) / 128;
+    } else {
+        t.n = n_total;
+        t.row_blocks = (n_total + 255) / 256;
+    }
+    int rc = dev_alloc(&t.tiles, t.bytes(), ctx);
+    if (rc) return rc;
+    rc = launch_umma_repack(src, (int)names.size(), mode, k, t, ctx->stream);
+    if (rc) return rc;
+    SWLM_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->umma[key] = t;
+    *out = &ctx->umma[key];
+    return SWLM_OK;
+}
+
 int add_q4_raw(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* w, const uint16_t* s,
                const uint16_t* b, bool f16, int shard_kind) {
     if (!ctx || !name || !w || !s || !b) { set_error("null argument"); return SWLM_ERR_INVALID; }
@@ -200,6 +240,9 @@ struct Launch {
     int kind = 0;
     swlm_step st{};            // the (first) step this launch came from
     const Q4Tiled* w = nullptr;
+    const Q4Umma* wu = nullptr;  // tensor-core layout of the same weights (single-sequence plans)
+    std::vector<std::string> w_names;
+    int w_mode = 0;
     int epilogue = QGEMV_EPI_STORE;
     int n_seg = 1;
     int seg_buf[3] = {-1, -1, -1};
@@ -215,6 +258,7 @@ struct Launch {
     int x_buf = -1;            // buffer the product reads (the norm's input when fused)
     int push = 0, in_tp = 0;   // tensor parallel: partial rows pushed to all ranks / pushed partials consumed
     int res_in = 0, res_out = 0;  // physical residual buffers (0 or 1) this launch reads / writes
+    int prefetch_launch = -1;     // index of the later product whose weights this launch pulls into L2
 };
 
 struct RopeTable { int rope_dim; float base; float* inv_freq; };
@@ -301,6 +345,7 @@ int compile_plan(swlm_plan* plan) {
                 st[i + 2].in_buf == s.out_buf && st[i + 2].in2_buf == st[i + 1].out_buf && (s.n % 8) == 0) {
                 rc = get_tiled(ctx, {s.weight, st[i + 1].weight}, 1, &L.w);
                 if (rc) return rc;
+                L.w_names = {s.weight, st[i + 1].weight}; L.w_mode = 1;
                 L.epilogue = QGEMV_EPI_SWIGLU;
                 L.seg_buf[0] = st[i + 2].out_buf;
                 L.seg_end[0] = ctx->raw[s.weight].n;
@@ -322,6 +367,7 @@ int compile_plan(swlm_plan* plan) {
             if (s.out_buf == s.in_buf && names.size() > 1) names.resize(1);
             rc = get_tiled(ctx, names, 0, &L.w);
             if (rc) return rc;
+            L.w_names = names; L.w_mode = 0;
             L.n_seg = (int)names.size();
             int end = 0;
             L.label = "qgemv";
@@ -434,6 +480,32 @@ int compile_plan(swlm_plan* plan) {
     }
     plan->final_res = cur;
 
+    // Cross-launch L2 prefetch (single sequence), off unless SWLM_L2_PREFETCH_MB sets a budget: a product's
+    // weights are requested one or two launches early, by attention or by another product, as long as
+    // everything requested but not yet consumed stays below the budget (L2 is 126 MB). Measured on a B200 with
+    // the Llama-3-8B shape it does not pay: the products are bound by instruction issue, not by HBM, and
+    // attention slows down under the extra traffic (527 tok/s without, 501 with a 110 MB budget).
+    if (m == 1) {
+        double budget = 0;
+        if (const char* e = getenv("SWLM_L2_PREFETCH_MB")) budget = atof(e) * 1e6;
+        auto wbytes = [&](const Launch& L) { return L.kind == L_QGEMV ? (double)L.w->bytes() : 0.0; };
+        for (int j = 0; j < (int)plan->launches.size() && budget > 0; ++j) {
+            const Launch& T = plan->launches[j];
+            if (T.kind != L_QGEMV || wbytes(T) > 80e6) continue;
+            for (int dist = 2; dist >= 1; --dist) {
+                const int i = j - dist;
+                if (i < 0) continue;
+                Launch& P = plan->launches[i];
+                if ((P.kind != L_QGEMV && P.kind != L_ATTN) || P.prefetch_launch >= 0) continue;
+                double live = wbytes(T);
+                for (int l = i; l < j; ++l) live += wbytes(plan->launches[l]);
+                if (live > budget) continue;
+                P.prefetch_launch = j;
+                break;
+            }
+        }
+    }
+
     // Tensor parallel: a product over a K-sharded (row-parallel) weight yields partial sums. It pushes them
     // to every rank, and the product that follows must be one with a fused norm, which adds them up.
     if (ctx->tp_size > 1) {
@@ -456,6 +528,22 @@ int compile_plan(swlm_plan* plan) {
             plan->launches[i + 1].in_tp = 1;
             L.label = "push " + L.label;
             plan->launches[i + 1].label = "allreduce+" + plan->launches[i + 1].label;
+        }
+    }
+
+    // SWLM_TC_GEMV=1: single-sequence plans run their products on the tensor-core (tcgen05) GEMV instead of the
+    // mma.sync kernel. Off by default: measured on a B200 with the Llama-3-8B shape the mma.sync kernel is the
+    // faster one at batch 1 (its stream already runs at HBM speed and its latency per launch is lower).
+    const char* use_tc = getenv("SWLM_TC_GEMV");
+    if (m == 1 && use_tc && use_tc[0] == '1') {
+        for (Launch& L : plan->launches) {
+            if (L.kind != L_QGEMV || L.push || L.in_tp) continue;
+            if (L.norm.kind && (L.w->k > 4096 || (L.w->k & 15))) continue;
+            rc = get_umma(ctx, L.w_names, L.w_mode, &L.wu);
+            if (rc) return rc;
+            plan->qgemv_partial = std::max(plan->qgemv_partial, qgemv_tc_scratch_floats());
+            plan->qgemv_counters = std::max(plan->qgemv_counters, (size_t)qgemv_tc_counter_count(*L.wu));
+            L.label = "tc " + L.label;
         }
     }
     return SWLM_OK;
@@ -497,6 +585,7 @@ struct swlm_state {
     unsigned* pf_attn_counters = nullptr;
     int* pf_status = nullptr;      // device word: a bounded wait of the tensor-core product expired
     int prefill_chunk = 512;       // tokens per chunk; 0 = one token at a time through the decode graph
+    int* tc_status = nullptr;      // pinned host word (mapped): a bounded wait of the tensor-core GEMV expired
 };
 
 struct swlm_snap {
@@ -506,6 +595,13 @@ struct swlm_snap {
 };
 
 namespace {
+
+PrefetchTarget prefetch_of(const Launch& L) {
+    PrefetchTarget t;
+    t.p[0] = L.w->tiles; t.bytes[0] = (unsigned long long)L.w->row_tiles * L.w->kt_pad * 512;
+    t.p[1] = L.w->sb; t.bytes[1] = (unsigned long long)L.w->row_tiles * (L.w->kt_pad / 4) * 256;
+    return t;
+}
 
 __nv_bfloat16* res_buf(swlm_state* s, int phys) { return phys ? s->res2 : s->buf[SWLM_BUF_RESIDUAL]; }
 
@@ -556,11 +652,13 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             }
             for (int q = 0; q < L.n_seg; ++q) { a.y[q] = s->buf[L.seg_buf[q]]; a.y_stride[q] = s->width[L.seg_buf[q]]; a.seg_end[q] = L.seg_end[q]; }
             a.partial = s->qgemv_partial; a.counters = s->qgemv_counters;
+            if (L.prefetch_launch >= 0) a.prefetch = prefetch_of(plan->launches[L.prefetch_launch]);
             if (L.push || L.in_tp) {
                 if (!s->tp_attached) { set_error("tensor-parallel plan: call swlm_tp_export / swlm_tp_attach on the state first"); return SWLM_ERR_STATE; }
                 a.push = L.push; a.in_tp = L.in_tp; a.tp = s->tp;
             }
-            rc = launch_qgemv(a, stream);
+            if (L.wu && qgemv_tc_supports(*L.wu, a)) rc = launch_qgemv_tc(*L.wu, a, s->tc_status, stream);
+            else rc = launch_qgemv(a, stream);
             s->launches += 1;
             break;
         }
@@ -582,6 +680,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             a.max_seq = d.max_seq; a.position = s->position;
             a.out = s->buf[st.out_buf]; a.out_stride = s->width[st.out_buf];
             a.scratch = s->attn_scratch; a.counters = s->attn_counters; a.splits = plan->attn_splits;
+            if (L.prefetch_launch >= 0) a.prefetch = prefetch_of(plan->launches[L.prefetch_launch]);
             rc = launch_attn_decode(a, stream);
             s->launches += 1;
             break;
@@ -712,6 +811,16 @@ size_t plan_attn_scratch(const swlm_plan* plan) {
         if (L.kind == L_ATTN)
             need = std::max(need, attn_scratch_floats(plan->desc.max_batch, L.st.heads / plan->ctx->tp_size, L.st.head_dim, plan->attn_splits));
     return need;
+}
+
+// After a synchronisation: did a bounded wait of the tensor-core GEMV give up since the last check?
+int check_tc_status(swlm_state* s) {
+    if (s->tc_status && *s->tc_status) {
+        set_error("a bounded wait in the tensor-core GEMV expired (code %d)", *s->tc_status);
+        *s->tc_status = 0;
+        return SWLM_ERR_TIMEOUT;
+    }
+    return SWLM_OK;
 }
 
 int check_position_room(swlm_state* s, int steps) {
@@ -879,6 +988,7 @@ int swlm_ctx_create(int device_id, int tp_rank, int tp_size, swlm_ctx** out) {
     int rc = qgemv_init();
     if (!rc) rc = attn_init();
     if (!rc) rc = qgemm_tc_init();
+    if (!rc) rc = qgemv_tc_init();
     if (rc) { cudaStreamDestroy(ctx->stream); delete ctx; return rc; }
     *out = ctx;
     return SWLM_OK;
@@ -891,6 +1001,7 @@ void swlm_ctx_destroy(swlm_ctx* ctx) {
     cudaSetDevice(ctx->device);
     for (auto& kv : ctx->raw) { cudaFree(kv.second.w); cudaFree(kv.second.scales); cudaFree(kv.second.biases); }
     for (auto& kv : ctx->tiled) { cudaFree(kv.second.tiles); cudaFree(kv.second.sb); }
+    for (auto& kv : ctx->umma) cudaFree(kv.second.tiles);
     for (auto& kv : ctx->dense) cudaFree(kv.second.data);
     cudaFree(ctx->op_partial);
     cudaFree(ctx->tc_status);
@@ -1034,6 +1145,10 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     if ((rc = dev_alloc(&s->argmax_idx, argmax_scratch_elems(d.max_batch)))) return fail(rc);
     e = cudaMallocHost((void**)&s->h_tok, sizeof(int32_t) * 2 * d.max_batch);
     if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMallocHost"));
+    // pinned and mapped: the kernels write it only when a wait expires, the host reads it after every sync for free
+    e = cudaHostAlloc((void**)&s->tc_status, sizeof(int), cudaHostAllocMapped);
+    if (e != cudaSuccess) return fail(cuda_fail(e, "cudaHostAlloc"));
+    *s->tc_status = 0;
     *out = s;
     rc = swlm_state_reset(s);
     if (rc) { *out = nullptr; return fail(rc); }
@@ -1060,6 +1175,7 @@ void swlm_state_destroy(swlm_state* s) {
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->pf_buf[i]);
     cudaFree(s->pf_attn_counters); cudaFree(s->pf_status);
     if (s->h_tok) cudaFreeHost(s->h_tok);
+    if (s->tc_status) cudaFreeHost(s->tc_status);
     if (s->own_stream) cudaStreamDestroy(s->own_stream);
     swlm_plan* plan = s->plan;
     delete s;
@@ -1142,7 +1258,7 @@ int swlm_set_position(swlm_state* s, int position) {
 int swlm_sync(swlm_state* s) {
     if (!s) { set_error("null state"); return SWLM_ERR_INVALID; }
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
-    return SWLM_OK;
+    return check_tc_status(s);
 }
 
 int swlm_decode(swlm_state* s, const int32_t* token_in, int32_t* token_out) {
@@ -1159,7 +1275,7 @@ int swlm_decode(swlm_state* s, const int32_t* token_in, int32_t* token_out) {
     SWLM_CUDA(cudaMemcpyAsync(s->h_tok + m, s->token_out, sizeof(int32_t) * m, cudaMemcpyDeviceToHost, s->stream));
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     memcpy(token_out, s->h_tok + m, sizeof(int32_t) * m);
-    return SWLM_OK;
+    return check_tc_status(s);
 }
 
 int swlm_decode_n_async(swlm_state* s, const int32_t* token_in, int n) {
@@ -1190,7 +1306,7 @@ int swlm_read_tokens(swlm_state* s, int n, int32_t* tokens_out) {
         if (step < 0) { set_error("fewer than %d steps decoded", n); return SWLM_ERR_STATE; }
         SWLM_CUDA(cudaMemcpy(tokens_out + (size_t)i * m, s->ring + (size_t)(step % s->ring_cap) * m, sizeof(int32_t) * m, cudaMemcpyDeviceToHost));
     }
-    return SWLM_OK;
+    return check_tc_status(s);
 }
 
 int swlm_decode_n(swlm_state* s, const int32_t* token_in, int n, int32_t* tokens_out) {
@@ -1440,8 +1556,11 @@ int swlm_profile_kind(swlm_state* s, int step_kind, int repeats) {
 
 // ---- op-level ------------------------------------------------------------------------------------------
 
+static int op_scratch_sized(swlm_ctx* ctx, size_t pf, size_t cc);
 static int op_scratch(swlm_ctx* ctx, const Q4Tiled& w, int m) {
-    const size_t pf = qgemv_scratch_floats(w, m), cc = (size_t)qgemv_counter_count(w);
+    return op_scratch_sized(ctx, qgemv_scratch_floats(w, m), (size_t)qgemv_counter_count(w));
+}
+static int op_scratch_sized(swlm_ctx* ctx, size_t pf, size_t cc) {
     if (pf > ctx->op_partial_floats) {
         cudaFree(ctx->op_partial);
         ctx->op_partial = nullptr; ctx->op_partial_floats = 0;
@@ -1468,14 +1587,29 @@ int swlm_op_qgemm_dev(swlm_ctx* ctx, const char* weight, int m, const void* x_de
     rc = get_tiled(ctx, {weight}, 0, &w);
     if (rc) return rc;
     cudaStream_t stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->stream;
+    if (!ctx->tc_status) {
+        if ((rc = dev_alloc(&ctx->tc_status, 1))) return rc;
+        SWLM_CUDA(cudaMemsetAsync(ctx->tc_status, 0, sizeof(int), ctx->stream));
+        SWLM_CUDA(cudaStreamSynchronize(ctx->stream));
+    }
+    // SWLM_TC_GEMV=1, m == 1: the tensor-core GEMV over shared-memory images of the weights
+    const char* use_tc = getenv("SWLM_TC_GEMV");
+    if (m == 1 && use_tc && use_tc[0] == '1' && ctx->raw.count(weight)) {
+        const Q4Umma* wu;
+        if ((rc = get_umma(ctx, {weight}, 0, &wu))) return rc;
+        QGemvLaunch a;
+        a.m = 1;
+        a.x = static_cast<const __nv_bfloat16*>(x_dev); a.x_stride = wu->k;
+        a.y[0] = static_cast<__nv_bfloat16*>(y_dev); a.y_stride[0] = wu->n; a.seg_end[0] = wu->n;
+        if (qgemv_tc_supports(*wu, a)) {
+            if ((rc = op_scratch_sized(ctx, qgemv_tc_scratch_floats(), (size_t)qgemv_tc_counter_count(*wu)))) return rc;
+            a.partial = ctx->op_partial; a.counters = ctx->op_counters;
+            return launch_qgemv_tc(*wu, a, ctx->tc_status, stream);
+        }
+    }
     // m >= 64: tensor-core contraction straight from the packed source copy
     auto raw = ctx->raw.find(weight);
-    if (m >= kQGemmTcMinRows && raw != ctx->raw.end() && !raw->second.sb_f16 && raw->second.k % 64 == 0) {
-        if (!ctx->tc_status) {
-            if ((rc = dev_alloc(&ctx->tc_status, 1))) return rc;
-            SWLM_CUDA(cudaMemsetAsync(ctx->tc_status, 0, sizeof(int), ctx->stream));
-            SWLM_CUDA(cudaStreamSynchronize(ctx->stream));
-        }
+    if (m >= kQGemmTcMinRows && raw != ctx->raw.end() && raw->second.k % 64 == 0) {
         return launch_qgemm_tc(raw->second, m, static_cast<const __nv_bfloat16*>(x_dev), raw->second.k,
                                static_cast<__nv_bfloat16*>(y_dev), raw->second.n, ctx->tc_status, stream);
     }
@@ -1518,7 +1652,11 @@ int swlm_op_qgemm(swlm_ctx* ctx, const char* weight, int m, const uint16_t* x_bf
     if (ctx->tc_status) {
         int st = 0;
         SWLM_CUDA(cudaMemcpy(&st, ctx->tc_status, sizeof(int), cudaMemcpyDeviceToHost));
-        if (st) { set_error("qgemm: a bounded wait in the tensor-core kernel expired"); return SWLM_ERR_TIMEOUT; }
+        if (st) {
+            set_error("qgemm: a bounded wait in a tensor-core kernel expired (code %d)", st);
+            cudaMemset(ctx->tc_status, 0, sizeof(int));
+            return SWLM_ERR_TIMEOUT;
+        }
     }
     return SWLM_OK;
 }

@@ -71,6 +71,24 @@ struct Q4Tiled {
     size_t bytes() const { return (size_t)row_tiles * kt_pad * 512 + (size_t)row_tiles * (kt_pad / 4) * 256; }
 };
 
+// Q4 group-64 tensor as shared-memory images for the tensor-core (tcgen05) single-sequence GEMV.
+//   tiles : [row_blocks][chunks] records of 18432 bytes. A record covers 256 rows x 128 columns:
+//           16384 bytes = 128 byte-rows x 128 bytes, byte (i, k) = nibble of row 256*rb + i (low) | nibble of row
+//           256*rb + 128 + i (high) << 4 for column 128*c + k, stored K-major with the 128-byte swizzle (16-byte
+//           chunk j of byte-row i sits at chunk position j ^ (i & 7)); then uint2[2 groups][128 byte-rows] =
+//           (scale, zero) pairs of the low row and of the high row (two 16-bit floats each, scale in the low half).
+//   interleaved: low nibbles are rows of source A (gate), high nibbles the same rows of source B (up);
+//           a row block then covers 128 rows of each.
+// Rows and columns beyond n / k hold q = 0, scale = zero = 0.
+struct Q4Umma {
+    int n = 0, k = 0;
+    int row_blocks = 0, chunks = 0;
+    bool sb_f16 = false;
+    bool interleaved = false;
+    unsigned char* tiles = nullptr;
+    size_t bytes() const;
+};
+
 // Raw source copy kept on the device so that fused tensors can be assembled at plan time.
 struct Q4Raw {
     int n = 0, k = 0;
@@ -102,6 +120,29 @@ int launch_untile_bf16(const Q4Tiled& t, __nv_bfloat16* out, cudaStream_t s);
 
 enum { QGEMV_EPI_STORE = 0, QGEMV_EPI_SWIGLU = 1 };
 
+// Weights of a later launch that this launch asks the memory system to bring from HBM into L2 while it runs
+// (its own data comes from L2 or is small, so HBM would otherwise idle). Two arrays, sizes multiples of 256.
+struct PrefetchTarget {
+    const void* p[2] = {nullptr, nullptr};
+    unsigned long long bytes[2] = {0, 0};
+};
+#ifdef __CUDACC__
+// CTA `part` of `nparts` requests its share, 16 KB per instruction, one instruction per thread and round.
+__device__ __forceinline__ void prefetch_target_slice(const PrefetchTarget& t, int part, int nparts, int tid, int nthreads) {
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+        if (!t.p[a]) continue;
+        const unsigned long long gran = t.bytes[a] >> 8;
+        const unsigned long long g0 = gran * (unsigned long long)part / (unsigned long long)nparts;
+        const unsigned long long g1 = gran * (unsigned long long)(part + 1) / (unsigned long long)nparts;
+        for (unsigned long long g = g0 + 64ull * tid; g < g1; g += 64ull * nthreads) {
+            const unsigned n = (unsigned)((g1 - g < 64ull ? g1 - g : 64ull) << 8);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const unsigned char*>(t.p[a]) + (g << 8)), "r"(n) : "memory");
+        }
+    }
+}
+#endif
+
 // Residual add / copy / RMSNorm fused in front of a product (mode = the step kind it replaces, 0 = none).
 // x of the launch is then the un-normalised input; res_in and res_out must be different buffers.
 struct XNorm {
@@ -128,10 +169,21 @@ struct QGemvLaunch {
     int epilogue = QGEMV_EPI_STORE;
     float* partial = nullptr;     // split-K scratch, see qgemv_scratch_floats()
     unsigned* counters = nullptr; // one per CTA row group, zero between launches
+    PrefetchTarget prefetch;      // batch-1 kernel only
 };
 size_t qgemv_scratch_floats(const Q4Tiled& w, int m);
 int qgemv_counter_count(const Q4Tiled& w);
 int launch_qgemv(const QGemvLaunch& a, cudaStream_t s);
+// Tensor-core (tcgen05) single-sequence GEMV over a Q4Umma tensor: same launch description as launch_qgemv
+// (a.w is ignored). `status` is a word the kernel sets when a bounded wait expired.
+int launch_umma_repack(const RepackSrc* src, int n_src, int mode, int k, const Q4Umma& dst, cudaStream_t s);
+int qgemv_tc_init();
+bool qgemv_tc_supports(const Q4Umma& w, const QGemvLaunch& a);
+int launch_qgemv_tc(const Q4Umma& w, const QGemvLaunch& a, int* status, cudaStream_t s);
+size_t qgemv_tc_scratch_floats();
+int qgemv_tc_counter_count(const Q4Umma& w);
+// SWLM_TRACE=1: slot for the phase timestamps of one launch (nullptr when tracing is off or the slots are used up)
+unsigned long long* qgemv_trace_slot(int ctas, int row_tiles, int kt4, int epi, int norm);
 int qgemv_init();  // sets shared-memory attributes once per process
 void qgemv_trace_report();  // SWLM_TRACE=1: phase timeline of the batch-1 launches, to stderr
 
@@ -182,6 +234,7 @@ struct AttnLaunch {
     // >= 0: prompt ingestion. The m rows are consecutive tokens of sequence 0 starting at this position; their
     // k/v rows are appended first, then token b attends cache rows 0..pos_base+b. `position` is not read.
     int pos_base = -1;
+    PrefetchTarget prefetch;
 };
 int attn_pick_splits(int m, int kv_heads, int max_ctx);
 size_t attn_scratch_floats(int m, int heads, int head_dim, int splits);
