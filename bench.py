@@ -27,6 +27,7 @@ from __graft_entry__ import load_package  # noqa: E402
 
 METRIC = "4-bit decode tok/s, Llama-3-8B shape bs1"
 NOMINAL_HBM_GBS = 8000.0
+NCU_TRAFFIC_RATIO = 123.797 / 122.683
 
 
 def measured_peaks():
@@ -68,6 +69,17 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
+
+    def count(self):
+        return len(self.rows)
+
+    def alive(self):
+        return self.proc is not None and self.proc.poll() is None
+
+    def wait_first(self, seconds):
+        t0 = time.perf_counter()
+        while self.alive() and not self.rows and time.perf_counter() - t0 < seconds:
+            time.sleep(0.02)
 
     def stop(self):
         if self.proc:
@@ -280,7 +292,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     warm = max(3, args.warmup)
-    max_seq = args.ctx + 2 * (warm + args.steps) + 64
+    max_seq = args.ctx + 2 * (warm + args.steps) + 64 + 8 * 64   # + room for the clock sampler's extra warm-up bursts
     cfg = model_config(pkg, args, max_seq)
     builder = pkg.DispatchPlanBuilder(cfg)
     weights = pkg.synth_model_weights(builder, seed=3)
@@ -295,9 +307,15 @@ def main():
 
     # ---- context: `ctx` tokens in the KV cache ---------------------------------------------------------------
     rng = np.random.default_rng(7)
+    prefill_info = None
     if args.prefill == "real":
         prompt = rng.integers(0, cfg.vocab, size=(1, args.ctx), dtype=np.int32)
-        tok = model.prefill(prompt)
+        torch.cuda.synchronize()
+        t_pf = time.perf_counter()
+        tok = model.prefill(prompt)   # host tokens in, first generated token out (synchronous)
+        t_pf = time.perf_counter() - t_pf
+        prefill_info = {"prompt_tokens": int(args.ctx), "seconds": t_pf, "tok_s": args.ctx / t_pf,
+                        "how": "chunked prompt ingestion on 1 GPU" if world == 1 else "token by token (tensor-parallel states)"}
     else:
         rows = pkg.f32_to_bf16(rng.normal(size=(args.ctx, cfg.head_dim)).astype(np.float32))
         kv_local = cfg.kv_heads // world
@@ -314,10 +332,20 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident throughput ---------------------------------------------------------------------------
-    model.decode_n_async(tok, warm)
-    barrier()
+    # clocks are sampled from before the warm-up until after the timed steps (nvidia-smi needs a moment to start;
+    # a 128-step region alone lasts only a quarter of a second), so "under load" covers warm-up + timed region
     sampler = ClockSampler(local_rank)
     sampler.start()
+    sampler.wait_first(3.0)
+    model.decode_n_async(tok, warm)
+    barrier()
+    bursts = 0
+    # same load until a few samples exist; every rank must run the same number of steps, so with several ranks
+    # the count is fixed
+    while (bursts < 2) if world > 1 else (sampler.count() < 4 and sampler.alive() and bursts < 8):
+        model.decode_n_async(None, 64)
+        barrier()
+        bursts += 1
     launches0 = model.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -379,7 +407,11 @@ def main():
         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
         "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
         "bytes_per_launch_avg": weight_bytes / n_gemv, "avg_launch_us": gemv_ms * 1e3 / n_gemv,
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from the ncu capture summarised in
+        # profiles/qgemv1_and_attention_llama3_8b_decode_ncu_full.md (the four product shapes of a layer: 123.80 MB
+        # of HBM traffic for 122.68 MB of weights), applied to this run's average launch
+        "traffic": weight_bytes / n_gemv * NCU_TRAFFIC_RATIO,
+        "traffic_source": "ncu capture of the four product shapes of one layer, ratio %.4f to algorithmic bytes" % NCU_TRAFFIC_RATIO,
         "attention": {"kernel": "attn_split_kernel + attn_combine_kernel", "bytes_per_step": kv_bytes,
                       "achieved": kv_bytes / (attn_ms * 1e-3) / 1e9, "unit": "GB/s"},
         "whole_step": {"weight_bytes": weight_bytes, "weight_GBs": weight_bytes / (ms / args.steps * 1e-3) / 1e9,
@@ -407,6 +439,7 @@ def main():
             "clocks": clocks,
             "roofline": roofline,
             "cpu_baseline": base,
+            "prefill": prefill_info,
         }
         print(json.dumps(line))
     model.close()
