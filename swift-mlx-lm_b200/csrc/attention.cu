@@ -46,7 +46,14 @@ struct AttnParams {
     float* part_ml;  // [m][heads][splits][2]
     unsigned* counters;  // [m][kv_heads], zero between launches
     PrefetchTarget prefetch;  // weights of a later product, requested into L2 while this kernel runs
+    unsigned long long* trace;  // SWLM_TRACE=1: [cta][4] = entry, predecessor complete, loop done, partials published
 };
+
+__device__ __forceinline__ unsigned long long attn_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -79,11 +86,14 @@ template <int HD, int MODE>
 __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnParams p) {
     constexpr bool DECODE = MODE == 1;
     constexpr bool PREFILL = MODE == 2;
+    const int cta_linear = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (p.trace && threadIdx.x == 0) p.trace[cta_linear * 4] = attn_timer_ns();
     pdl_launch_dependents();
     if (DECODE)
         prefetch_target_slice(p.prefetch, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                               gridDim.x * gridDim.y * gridDim.z, threadIdx.x, kSplitThreads);
     pdl_wait();
+    if (p.trace && threadIdx.x == 0) p.trace[cta_linear * 4 + 1] = attn_timer_ns();
     constexpr int NCH = HD / 32;  // 16-byte K chunks per lane per token
     constexpr int VH = HD / 64;   // 64-dimension halves of V
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -288,6 +298,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         if (nxt < t_end) load_v(nxt);
     }
 
+    if (p.trace && threadIdx.x == 0) p.trace[cta_linear * 4 + 2] = attn_timer_ns();
     // ---- merge the warps of this CTA ---------------------------------------------------------------
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
@@ -332,6 +343,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         if (is_last) *ctr = 0u;  // ready for the next launch
     }
     __syncthreads();
+    if (p.trace && threadIdx.x == 0) p.trace[cta_linear * 4 + 3] = attn_timer_ns();
     if (!is_last) return;
 
     // Everything that does not depend on the split weights is requested first: the (max, sum) pairs and the
@@ -425,6 +437,10 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         packed.x = pack_bf16(num.x * inv, num.y * inv);
         packed.y = pack_bf16(num.z * inv, num.w * inv);
         *reinterpret_cast<uint2*>(p.out + (size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d4 * 4) = packed;
+    }
+    if (p.trace) {
+        __syncthreads();
+        if (threadIdx.x == 0) p.trace[(gridDim.x * gridDim.y * gridDim.z + (blockIdx.z * gridDim.y + blockIdx.y)) * 4] = attn_timer_ns();  // merged
     }
 }
 
@@ -521,6 +537,8 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     p.part_ml = a.scratch + (size_t)a.m * a.heads * a.splits * a.head_dim;
     p.counters = a.counters;
     p.prefetch = a.prefetch;
+    if (a.pos_base < 0 && a.m * a.kv_heads * a.splits + a.m * a.kv_heads <= 512)
+        p.trace = qgemv_trace_slot(a.m * a.kv_heads * a.splits, -a.kv_heads * a.m, a.splits, 9, 0);
     if (a.pos_base >= 0) {
         // prompt ingestion: rows of q/k/v are consecutive tokens of sequence 0
         if (a.head_dim > 128) { set_error("attention: head_dim %d not supported", a.head_dim); return SWLM_ERR_UNSUPPORTED; }

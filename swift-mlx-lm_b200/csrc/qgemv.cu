@@ -530,9 +530,11 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], unsigned a0, unsigned a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int EPI, bool F16SB>
-__global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const QGemvParams p) {
-    extern __shared__ __align__(16) unsigned char smem[];
+// The single-sequence product. (Running o_proj, gate/up, down and the next q/k/v as one launch with a software
+// grid barrier between them was tried: on this part the barrier costs about 4.5 us, more than the 0.8 us a
+// dependent launch needs to see its predecessor complete, so every product is its own launch.)
+template <int EPI, bool F16SB, bool RANGE>
+__device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char* smem) {
     const int tid = threadIdx.x, lane = tid & 31, cta_warp = tid >> 5;
     const int groups = blockDim.x / kThreads, grp = cta_warp / kWarps;
     const int warp = cta_warp % kWarps;   // warp within its group
@@ -565,17 +567,33 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
         a0 = rt * p.kt4_total + ((sl * p.kt4_total) >> p.si_shift);
         a1 = rt * p.kt4_total + (((sl + 1) * p.kt4_total) >> p.si_shift);
     };
+    // Third way (range mode, large matrices): the stages of the whole matrix, in [row tile][k] order, are cut into
+    // one contiguous range per warp of the GPU, equal to within one stage, whatever the number of row tiles. A
+    // warp's range may cross row-tile boundaries; the parts of a row tile (two to fifteen warps) meet in global
+    // scratch like the slices above, in warp order.
+    constexpr bool range_mode = RANGE;
+    const long long S_all = (long long)p.row_tiles * p.kt4_total;
+    const int W_all = vgrid * kWarps, gwarp = vb * kWarps + warp;
+    const int A0 = range_mode ? (int)(S_all * gwarp / W_all) : 0, A1 = range_mode ? (int)(S_all * (gwarp + 1) / W_all) : 0;
+    auto stage_owner = [&](long long a) {  // warp whose range holds stage a
+        int c = (int)(((a + 1) * W_all - 1) / S_all);
+        while (c > 0 && S_all * c / W_all > a) --c;
+        while (c + 1 < W_all && S_all * (c + 1) / W_all <= a) ++c;
+        return c;
+    };
     // cp.async side: runs kStages-1 stages ahead of the math, across unit boundaries
     int iu = u_first + warp, ia = 0, ia_end = 0;
-    if (iu < u_end) unit_range(iu, ia, ia_end);
+    int iu_end = u_end;
+    if (range_mode) { iu = A0 < A1 ? 0 : 1; iu_end = 1; ia = A0; ia_end = A1; }
+    else if (iu < u_end) unit_range(iu, ia, ia_end);
     const unsigned ring_sa = (unsigned)__cvta_generic_to_shared(my_ring) + lane * 16;
     const bool sb_lane = lane < 16;
     auto issue = [&](int slot) {
-        if (ia == ia_end && iu < u_end) {
+        if (ia == ia_end && iu < iu_end) {
             iu += u_stride;
-            if (iu < u_end) unit_range(iu, ia, ia_end);
+            if (iu < iu_end) unit_range(iu, ia, ia_end);
         }
-        if (iu < u_end) {
+        if (iu < iu_end) {
             const unsigned dst = ring_sa + slot * kStageBytes;
             const uint4* src = p.tiles + (size_t)ia * 128 + lane;
             asm volatile(
@@ -602,10 +620,15 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
     {
         const int pu0 = p.cta_mode ? u_first : u_lo;
         const int pu1 = p.cta_mode ? min(u_first + kWarps, units) : u_hi;
-        if (pu0 < pu1) {
+        if (pu0 < pu1 || range_mode) {
             int pa0, pa1, unused;
-            unit_range(pu0, pa0, unused);
-            unit_range(pu1 - 1, unused, pa1);
+            if (range_mode) {
+                pa0 = (int)(S_all * (vb * kWarps) / W_all);
+                pa1 = (int)(S_all * (vb * kWarps + kWarps) / W_all);
+            } else {
+                unit_range(pu0, pa0, unused);
+                unit_range(pu1 - 1, unused, pa1);
+            }
             pa1 = min(pa1, pa0 + kBulkMaxStages);
             const int piece = gtid >> 1;  // even threads: tiles, odd threads: scale/zero pairs
             const int s0 = pa0 + piece * kBulkPiece;
@@ -701,14 +724,25 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
     const int xlane_off = t * 32 + g * 16;
     const int xtile_stride = xlane ? 128 : 0;
     int round = 0;
-    for (int base = u_first; base < u_limit; base += u_stride, ++round) {
+    int seg_rt = range_mode ? A0 / p.kt4_total : 0;  // range mode: next row tile of this warp's range
+    for (int base = u_first; range_mode ? (A0 < A1 && seg_rt * p.kt4_total < A1) : (base < u_limit); base += u_stride, ++round) {
         const int u = base + warp;
-        const bool valid = u < u_end;
-        const int rt = u >> p.si_shift;
-        const int slice = u & si_mask;
+        bool valid = u < u_end;
+        int rt = u >> p.si_shift;
+        int slice = u & si_mask;
+        int n_slices = s_total, pstride = s_total;
         float tot_lo = 0.f, tot_hi = 0.f, tot_hi16 = 0.f, tot_hiz = 0.f;
         int a0 = 0, a1 = 0;
-        if (valid) unit_range(u, a0, a1);
+        if (range_mode) {
+            rt = seg_rt++;
+            valid = true;
+            a0 = max(A0, rt * p.kt4_total);
+            a1 = min(A1, (rt + 1) * p.kt4_total);
+            const int first = stage_owner((long long)rt * p.kt4_total), last = stage_owner((long long)(rt + 1) * p.kt4_total - 1);
+            slice = gwarp - first;
+            n_slices = last - first + 1;
+            pstride = p.range_slots;
+        } else if (valid) unit_range(u, a0, a1);
         for (int a = a0; a < a1; ++a) {
             issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1;
             cp_async_wait<kStages - 1>();
@@ -765,21 +799,21 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
                     }
                 }
             }
-        } else if (s_total > 1 && valid) {
-            float* dst = p.partial + ((size_t)rt * s_total + slice) * 16;
+        } else if (n_slices > 1 && valid) {
+            float* dst = p.partial + ((size_t)rt * pstride + slice) * 16;
             if (t == 0) { __stcg(dst + g, tot_lo); __stcg(dst + g + 8, tot_hi); }
             __threadfence();
             __syncwarp();
             unsigned prev = 0;
             if (lane == 0) prev = atomicAdd(p.counters + rt, 1u);
             prev = __shfl_sync(0xffffffffu, prev, 0);
-            finisher = prev == (unsigned)s_total - 1u;
+            finisher = prev == (unsigned)n_slices - 1u;
             if (finisher) {
                 __threadfence();
                 if (lane == 0) p.counters[rt] = 0u;
                 tot_lo = tot_hi = 0.f;
-                for (int s = 0; s < s_total; ++s) {  // slice order: independent of arrival order
-                    const float* src = p.partial + ((size_t)rt * s_total + s) * 16;
+                for (int s = 0; s < n_slices; ++s) {  // slice order: independent of arrival order
+                    const float* src = p.partial + ((size_t)rt * pstride + s) * 16;
                     tot_lo += __ldcg(src + g);
                     tot_hi += __ldcg(src + g + 8);
                 }
@@ -822,8 +856,15 @@ __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const 
     }
 }
 
+template <int EPI, bool F16SB, bool RANGE>
+__global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const QGemvParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    qgemv1_body<EPI, F16SB, RANGE>(p, smem);
+}
+
 struct QGemvConfig {
     int nt, si, sk, occ, cta_mode;
+    int range_mode, range_slots;
     dim3 grid;
     size_t smem;
 };
@@ -846,12 +887,22 @@ QGemvConfig pick_config(const Q4Tiled& w, int m) {
         c.nt = 0; c.sk = 1;
         // one CTA per SM made of up to three eight-warp groups (c.occ = groups) that share the activations
         c.occ = kMaxGroups;
-        const size_t x_bytes = (size_t)w.kt_pad * 160, budget = 227 * 1024 - 8192;
+        const size_t x_bytes = (size_t)w.kt_pad * 160, budget = 214 * 1024;  // below every kernel's limit (opt-in maximum minus its static shared memory)
         while (c.occ > 1 && (size_t)c.occ * kRingBytes + x_bytes > budget) --c.occ;
         c.smem = (size_t)c.occ * kRingBytes + x_bytes;
         const int slots = kSMs * c.occ;  // groups resident on the GPU
         int vgrid;
-        if (w.row_tiles <= slots) {
+        const long long stages = (long long)w.row_tiles * kt4, warps = (long long)slots * kWarps;
+        const char* no_range = getenv("SWLM_NO_RANGE_MODE");
+        const int per = (int)(stages / warps);
+        if (per >= 3 && 2 * per >= kt4 && per < 2 * kt4 && !(no_range && no_range[0] == '1')) {
+            // large matrix, at most three warps per row tile: every warp of the GPU gets one contiguous range of
+            // stages, equal to within one stage
+            c.range_mode = 1;
+            c.si = 1;
+            c.range_slots = std::min(kt4, (kt4 + per - 1) / per + 1);
+            vgrid = slots;
+        } else if (w.row_tiles <= slots) {
             // few row tiles: one row tile per group, its warps split K (no global scratch, no atomics)
             c.cta_mode = 1;
             c.si = 1;
@@ -910,8 +961,13 @@ template <int EPI>
 int launch_1(const QGemvParams& p_in, const QGemvConfig& c, cudaStream_t s) {
     QGemvParams p = p_in;
     p.trace = qgemv_trace_slot((int)c.grid.x, p.row_tiles, p.kt4_total, EPI, p.norm_mode);
-    cudaError_t e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true>, c.grid, dim3(c.occ * kThreads), c.smem, s, p)
-                             : launch_k(qgemv1_kernel<EPI, false>, c.grid, dim3(c.occ * kThreads), c.smem, s, p);
+    cudaError_t e;
+    if (c.range_mode)
+        e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true, true>, c.grid, dim3(c.occ * kThreads), c.smem, s, p)
+                     : launch_k(qgemv1_kernel<EPI, false, true>, c.grid, dim3(c.occ * kThreads), c.smem, s, p);
+    else
+        e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true, false>, c.grid, dim3(c.occ * kThreads), c.smem, s, p)
+                     : launch_k(qgemv1_kernel<EPI, false, false>, c.grid, dim3(c.occ * kThreads), c.smem, s, p);
     if (e != cudaSuccess) return cuda_fail(e, "qgemv1 launch");
     return SWLM_OK;
 }
@@ -974,6 +1030,16 @@ void qgemv_trace_report() {
         }
         if (!n) continue;
         if (!origin || e0 < origin) origin = e0;
+        if (t.epi == 9) {
+            // attention: [1] predecessor complete, [2] main loop done, [3] partials published; merged stamps follow
+            auto rel9 = [&](unsigned long long v) { return ((double)v - (double)origin) / 1e3; };
+            unsigned long long m0 = ~0ull, m1 = 0;
+            const int nm = -t.row_tiles;
+            for (int i = 0; i < nm; ++i) { const unsigned long long v = r[(t.ctas + i) * 4]; if (v) { m0 = std::min(m0, v); m1 = std::max(m1, v); } }
+            fprintf(stderr, "%3d attention %d CTAs | first-entry %9.2f deps %9.2f..%9.2f loop-done(last) %9.2f published %9.2f..%9.2f merged %9.2f..%9.2f | dur: wait %.2f prologue+loop %.2f publish %.2f\n",
+                    sl, t.ctas, rel9(e0), rel9(d0), rel9(d1), rel9(x1), rel9(f0), rel9(f1), rel9(m0), rel9(m1), a / n / 1e3, b / n / 1e3, c / n / 1e3);
+            continue;
+        }
         auto rel = [&](unsigned long long v) { return ((double)v - (double)origin) / 1e3; };
         fprintf(stderr, "%3d %4d %6d %4d %d %d | %9.2f %9.2f %9.2f %9.2f %9.2f %9.2f | %6.2f %6.2f %6.2f", sl, t.ctas, t.row_tiles, t.kt4, t.epi,
                 t.norm, rel(e0), rel(d0), rel(d1), rel(x1), rel(f0), rel(f1), a / n / 1e3, b / n / 1e3, c / n / 1e3);
@@ -1021,31 +1087,48 @@ int qgemv_init() {
     if ((rc = opt_in_smem(qgemv_kernel<1, 1, true>))) return rc;
     if ((rc = opt_in_smem(qgemv_kernel<2, 0, true>))) return rc;
     if ((rc = opt_in_smem(qgemv_kernel<2, 1, true>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<0, false>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<1, false>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<0, true>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<1, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<0, false, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<1, false, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<0, true, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<1, true, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<0, false, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<1, false, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<0, true, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<1, true, true>))) return rc;
     return SWLM_OK;
 }
 
 size_t qgemv_scratch_floats(const Q4Tiled& w, int m) {
     QGemvConfig c = pick_config(w, m);
+    if (c.range_mode) return (size_t)w.row_tiles * c.range_slots * 16;
     if (c.sk * c.si <= 1 || c.cta_mode) return 0;
     return (size_t)w.row_tiles * c.sk * c.si * 16 * (c.nt ? 8 * c.nt : 1);
 }
 int qgemv_counter_count(const Q4Tiled& w) { return w.row_tiles; }
 
+static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c);
+
 int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
+    QGemvParams p{};
+    QGemvConfig c{};
+    int rc = build_params(a, p, c);
+    if (rc) return rc;
+    if (c.nt == 0) return a.epilogue == QGEMV_EPI_SWIGLU ? launch_1<1>(p, c, s) : launch_1<0>(p, c, s);
+    if (a.epilogue == QGEMV_EPI_SWIGLU) return c.nt == 1 ? launch_t<1, 1>(p, c, s) : launch_t<2, 1>(p, c, s);
+    return c.nt == 1 ? launch_t<1, 0>(p, c, s) : launch_t<2, 0>(p, c, s);
+}
+
+static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c) {
     const Q4Tiled& w = *a.w;
     if (a.m < 1 || a.m > 16) { set_error("qgemv: m=%d outside 1..16", a.m); return SWLM_ERR_INVALID; }
     if ((a.x_stride & 7) || (reinterpret_cast<uintptr_t>(a.x) & 15)) {
         set_error("qgemv: x must be 16-byte aligned with a stride that is a multiple of 8 elements");
         return SWLM_ERR_INVALID;
     }
-    QGemvConfig c = pick_config(w, a.m);
+    c = pick_config(w, a.m);
     if (g_max_dyn_smem == 0 || c.smem > (size_t)g_max_dyn_smem) { set_error("qgemv: shared memory %zu exceeds the limit %d", c.smem, g_max_dyn_smem); return SWLM_ERR_INVALID; }
-    if (c.sk * c.si > 1 && !c.cta_mode && (!a.partial || !a.counters)) { set_error("qgemv: split launch without scratch"); return SWLM_ERR_INVALID; }
-    QGemvParams p{};
+    if ((c.range_mode || (c.sk * c.si > 1 && !c.cta_mode)) && (!a.partial || !a.counters)) { set_error("qgemv: split launch without scratch"); return SWLM_ERR_INVALID; }
+    p = QGemvParams{};
     p.tiles = w.tiles; p.sb = w.sb; p.row_tiles = w.row_tiles; p.kt4_total = w.kt_pad / 4; p.sb_f16 = w.sb_f16 ? 1 : 0;
     p.x = a.x; p.x_stride = a.x_stride; p.k = w.k;
     for (int i = 0; i < 3; ++i) {
@@ -1054,6 +1137,7 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
     }
     p.m = a.m;
     p.si = c.si; p.sk = c.sk; p.cta_mode = c.cta_mode;
+    p.range_mode = c.range_mode; p.range_slots = c.range_slots;
     p.si_shift = 0;
     while ((1 << p.si_shift) < c.si) ++p.si_shift; p.partial = a.partial; p.counters = a.counters;
     p.push = a.push; p.in_tp = a.in_tp; p.tp = a.tp;
@@ -1069,9 +1153,7 @@ int launch_qgemv(const QGemvLaunch& a, cudaStream_t s) {
         p.res_in = a.norm.res_in; p.res_out = a.norm.res_out; p.res_stride = a.norm.res_stride;
         p.norm_w = a.norm.weight; p.eps = a.norm.eps; p.weight_bias = a.norm.weight_bias;
     }
-    if (c.nt == 0) return a.epilogue == QGEMV_EPI_SWIGLU ? launch_1<1>(p, c, s) : launch_1<0>(p, c, s);
-    if (a.epilogue == QGEMV_EPI_SWIGLU) return c.nt == 1 ? launch_t<1, 1>(p, c, s) : launch_t<2, 1>(p, c, s);
-    return c.nt == 1 ? launch_t<1, 0>(p, c, s) : launch_t<2, 0>(p, c, s);
+    return SWLM_OK;
 }
 
 // =================================================================================================

@@ -20,6 +20,7 @@ struct QGemvParams {
     int si, sk;   // k-slices per CTA group, CTA groups along K
     int si_shift; // log2(si) for the batch-1 kernel
     int cta_mode; // batch-1 kernel: slices of a row tile live in one CTA and meet in shared memory
+    int range_mode, range_slots;  // batch-1 kernel: one contiguous range of stages per warp; partial slots per row tile
     float* partial;
     unsigned* counters;
     // optional fused residual-add / copy / RMSNorm in front of the product (norm_mode = step kind, 0 = none)

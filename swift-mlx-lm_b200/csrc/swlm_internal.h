@@ -125,10 +125,33 @@ enum { QGEMV_EPI_STORE = 0, QGEMV_EPI_SWIGLU = 1 };
 struct PrefetchTarget {
     const void* p[2] = {nullptr, nullptr};
     unsigned long long bytes[2] = {0, 0};
+    // heads > 0: the two arrays are the K and V caches of one layer and sequence; what is requested is the first
+    // position[0] rows (row_bytes each) of every head, heads being head_stride bytes apart. The position is only a
+    // hint here: a stale value requests a row too few.
+    int heads = 0, row_bytes = 0;
+    unsigned long long head_stride = 0;
+    const int* position = nullptr;
 };
 #ifdef __CUDACC__
 // CTA `part` of `nparts` requests its share, 16 KB per instruction, one instruction per thread and round.
 __device__ __forceinline__ void prefetch_target_slice(const PrefetchTarget& t, int part, int nparts, int tid, int nthreads) {
+    if (t.heads > 0) {
+        // KV rows: 256-byte granules, numbered head-major over both caches
+        const unsigned long long per_head = ((unsigned long long)t.position[0] * (unsigned)t.row_bytes) >> 8;
+        if (per_head == 0) return;
+        const unsigned long long gran = per_head * (unsigned)t.heads * 2ull;
+        const unsigned long long g0 = gran * (unsigned long long)part / (unsigned long long)nparts;
+        const unsigned long long g1 = gran * (unsigned long long)(part + 1) / (unsigned long long)nparts;
+        for (unsigned long long g = g0 + 16ull * tid; g < g1; g += 16ull * nthreads) {  // 4 KB per instruction
+            const unsigned long long hd = g / per_head, off = g - hd * per_head;        // head index over both caches
+            const unsigned long long run = per_head - off < 16ull ? per_head - off : 16ull;
+            const unsigned n = (unsigned)((g1 - g < run ? g1 - g : run) << 8);
+            const unsigned char* base = static_cast<const unsigned char*>(t.p[hd >= (unsigned)t.heads ? 1 : 0]) +
+                                        (hd % (unsigned)t.heads) * t.head_stride + (off << 8);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(n) : "memory");
+        }
+        return;
+    }
 #pragma unroll
     for (int a = 0; a < 2; ++a) {
         if (!t.p[a]) continue;
