@@ -17,12 +17,13 @@
 //   * the epilogue reads the accumulator with tcgen05.ld, rounds to bf16 and stores Y[token][row].
 // Every mbarrier wait is bounded: on expiry an error word is set, the CTA stops issuing, frees its TMEM
 // and returns.
+#include <cstdlib>
 #include "swlm_internal.h"
 
 namespace swlm {
 namespace {
 
-constexpr int kTcThreads = 256;
+constexpr int kTcThreads = 256;          // dequantising threads; one more warp issues the MMAs
 constexpr int kTcRows = 128;            // weight rows per CTA = UMMA M
 constexpr int kTcBK = 64;               // one quantisation group per pipeline stage
 constexpr int kTcSpinLimit = 1 << 22;
@@ -37,6 +38,7 @@ struct QGemmTcParams {
     __nv_bfloat16* y;         // [m][y_stride]
     int y_stride;
     int* status;              // set non-zero when a bounded wait expired
+    unsigned long long* trace; // SWLM_TRACE=1: clocks CTA 0 spent per phase, summed over its groups
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -93,16 +95,22 @@ __device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7
 //
 // 256 threads: thread (r = tid & 127, h = tid >> 7) dequantises columns 32h..32h+31 of weight row r in every
 // group, so a group costs a thread one 16-byte load and about 90 instructions. Packed weights and (scale, zero)
-// are fetched two groups ahead into registers, the activation tile one group ahead with cp.async, so that
-// neither latency sits between two MMAs. STAGES shared-memory stages; tcgen05.commit frees a stage.
+// are fetched four groups ahead into registers, the activation tiles two groups ahead with cp.async into a ring
+// of their own (SB stages; the dequantised weight tiles need only SA = 2), so that neither latency sits between
+// two MMAs. A ninth warp issues the MMAs: the 256 threads arrive on ready_bar[kt % 2] once their part of group kt
+// is in shared memory and go on with group kt + 1 while the tensor core works; tcgen05.commit signals, per
+// group, that its MMAs are done and its stages may be overwritten.
 template <int BN, int STAGES, bool F16SB>
-__global__ void __launch_bounds__(kTcThreads) qgemm_tc_kernel(const QGemmTcParams p) {
+__global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTcParams p) {
+    constexpr int SA = 2, SB = STAGES;
+    static_assert(SB >= 4, "activation tiles are requested two groups ahead of a stage that was used two groups ago");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment for the swizzle atoms
     unsigned char* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
     constexpr int A_BYTES = kTcRows * 128;
     constexpr int B_BYTES = BN * 128;
     __shared__ __align__(8) unsigned long long empty_bar[STAGES];
+    __shared__ __align__(8) unsigned long long ready_bar[2];   // a weight tile and its activation tile are in place
     __shared__ __align__(8) unsigned long long done_bar;
     __shared__ unsigned tmem_base_smem;
     __shared__ int failed;
@@ -111,10 +119,13 @@ __global__ void __launch_bounds__(kTcThreads) qgemm_tc_kernel(const QGemmTcParam
     const int r = tid & 127, half = tid >> 7;
     const int row0 = blockIdx.x * kTcRows, tok0 = blockIdx.y * BN;
     const int kt_total = p.k / kTcBK;
+    unsigned char* const b_ring = smem + SA * A_BYTES;
 
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) mbar_init(&empty_bar[s], 1);
+        mbar_init(&ready_bar[0], kTcThreads);
+        mbar_init(&ready_bar[1], kTcThreads);
         mbar_init(&done_bar, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -143,43 +154,68 @@ __global__ void __launch_bounds__(kTcThreads) qgemm_tc_kernel(const QGemmTcParam
         if (row_ok && kt < kt_total) { v.w = __ldg(wrow + kt * 2); v.s = __ldg(srow + kt); v.z = __ldg(zrow + kt); }
         return v;
     };
+    // activation tile: thread (token t = tid >> 3 (+ 32 i), 16-byte chunk c = tid & 7); the swizzled position of
+    // a chunk depends on t & 7 only, which is the same for all i, so source and destination advance by constants
+    const int x_tok = tid >> 3, x_c = tid & 7;
+    const __nv_bfloat16* const x_src0 = p.x + (size_t)(tok0 + x_tok) * p.x_stride + x_c * 8;
+    const size_t x_src_step = (size_t)32 * p.x_stride;
+    const unsigned x_dst0 = smem_u32(b_ring) + (unsigned)swz(x_tok, x_c);
     auto issue_x = [&](int kt) {
-        unsigned char* const b_tile = smem + (kt % STAGES) * (A_BYTES + B_BYTES) + A_BYTES;
+        if (kt >= kt_total) return;
+        const unsigned dst = x_dst0 + (unsigned)((kt % SB) * B_BYTES);
+        const __nv_bfloat16* src = x_src0 + (size_t)kt * kTcBK;
 #pragma unroll
         for (int i = 0; i < BN * 8 / kTcThreads; ++i) {
-            const int idx = tid + i * kTcThreads;
-            const int tkn = idx >> 3, c = idx & 7;
-            unsigned char* dst = b_tile + swz(tkn, c);
-            if (tok0 + tkn < p.m) {
-                const __nv_bfloat16* src = p.x + (size_t)(tok0 + tkn) * p.x_stride + kt * kTcBK + c * 8;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-            } else {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-            }
+            if (tok0 + x_tok + 32 * i < p.m)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (unsigned)i * 4096u), "l"(src + (size_t)i * x_src_step) : "memory");
+            else
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + (unsigned)i * 4096u), "r"(0u) : "memory");
         }
     };
 
-    WReg w_cur = load_w(0), w_nxt = load_w(1);  // weights do not depend on the preceding kernel
+    // packed weights and their scale/zero run four groups ahead in registers (L2 latency is several groups long);
+    // they do not depend on the preceding kernel
+    if (warp == kTcThreads / 32) {
+        // ---- MMA warp: one thread issues the four MMAs of a group as soon as its tiles are in place; the
+        // dequantising warps are already busy with the next group by then -----------------------------------
+        if (lane == 0) {
+            for (int kt = 0; kt < kt_total; ++kt) {
+                if (!mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1))) { atomicExch(p.status, 2); failed = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned a_addr = smem_u32(smem + (kt % SA) * A_BYTES), b_addr = smem_u32(b_ring + (kt % SB) * B_BYTES);
+#pragma unroll
+                for (int j = 0; j < kTcBK / 16; ++j)  // 16 bf16 = 32 bytes along K inside the 128-byte row
+                    umma_f16(tmem_d, umma_desc(a_addr + 32 * j), umma_desc(b_addr + 32 * j), idesc, (kt > 0 || j > 0) ? 1u : 0u);
+                umma_commit(&empty_bar[kt % SB]);
+                if (kt == kt_total - 1) umma_commit(&done_bar);
+            }
+        }
+        __syncwarp();
+    } else {
+    WReg w_q0 = load_w(0), w_q1 = load_w(1), w_q2 = load_w(2), w_q3 = load_w(3);
     pdl_wait();                                 // the activations may come from the kernel just before this one
     issue_x(0);
     asm volatile("cp.async.commit_group;" ::: "memory");
+    issue_x(1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
+    long long c_wait = 0, c_x = 0, c_deq = 0, c_land = 0, c_sync = 0, c_mma = 0;  // tracing only
+    const bool timing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
     for (int kt = 0; kt < kt_total; ++kt) {
-        const int s = kt % STAGES;
-        unsigned char* const a_tile = smem + s * (A_BYTES + B_BYTES);
-        unsigned char* const b_tile = a_tile + A_BYTES;
-        // ---- activations of the next group into the next stage, once its previous MMAs have read it ------
-        if (kt + 1 < kt_total) {
-            const int use1 = (kt + 1) / STAGES;
-            if (use1 > 0 && !mbar_wait(&empty_bar[(kt + 1) % STAGES], (unsigned)((use1 - 1) & 1))) { atomicExch(p.status, 1); failed = 1; }
-            issue_x(kt + 1);
-        }
+        const long long t_a = timing ? clock64() : 0;
+        unsigned char* const a_tile = smem + (kt % SA) * A_BYTES;
+        // ---- the MMAs of group kt - 2 are done: its weight tile (this group's) and its activation tile (that of
+        // group kt + 2, requested now) may be overwritten -----------------------------------------------------
+        if (kt >= 2 && !mbar_wait(&empty_bar[(kt - 2) % SB], (unsigned)(((kt - 2) / SB) & 1))) { atomicExch(p.status, 1); failed = 1; }
+        const long long t_b = timing ? clock64() : 0;
+        issue_x(kt + 2);
         asm volatile("cp.async.commit_group;" ::: "memory");
+        const long long t_c = timing ? clock64() : 0;
         // ---- weights: 32 nibbles of this thread's row -> 32 bf16 = bf16(scale * q + zero) -----------------
         {
-            const WReg v = w_cur;
-            w_cur = w_nxt;
-            w_nxt = load_w(kt + 2);
+            const WReg v = w_q0;
+            w_q0 = w_q1; w_q1 = w_q2; w_q2 = w_q3;
+            w_q3 = load_w(kt + 4);
             const unsigned s2 = v.s | (v.s << 16), z2 = v.z | (v.z << 16);
             const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(&s2);
             const __nv_bfloat162 zr = *reinterpret_cast<const __nv_bfloat162*>(&z2);
@@ -212,29 +248,30 @@ __global__ void __launch_bounds__(kTcThreads) qgemm_tc_kernel(const QGemmTcParam
                 *reinterpret_cast<uint4*>(a_tile + swz(r, half * 4 + c)) = out;
             }
         }
-        asm volatile("cp.async.wait_group 1;" ::: "memory");  // this group's activations have landed
-        // generic-proxy writes to shared memory -> visible to the tensor core (async proxy)
+        const long long t_d = timing ? clock64() : 0;
+        asm volatile("cp.async.wait_group 2;" ::: "memory");  // this group's activations have landed
+        const long long t_e = timing ? clock64() : 0;
+        // generic-proxy writes to shared memory -> visible to the tensor core (async proxy), then tell the MMA warp
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ready_bar[kt % SA])) : "memory");
+        const long long t_f = timing ? clock64() : 0;
         if (failed) break;
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned a_addr = smem_u32(a_tile), b_addr = smem_u32(b_tile);
-#pragma unroll
-            for (int j = 0; j < kTcBK / 16; ++j)  // 16 bf16 = 32 bytes along K inside the 128-byte row
-                umma_f16(tmem_d, umma_desc(a_addr + 32 * j), umma_desc(b_addr + 32 * j), idesc, (kt > 0 || j > 0) ? 1u : 0u);
-            umma_commit(&empty_bar[s]);
-            if (kt == kt_total - 1) umma_commit(&done_bar);
+        if (timing) {
+            c_wait += t_b - t_a; c_x += t_c - t_b; c_deq += t_d - t_c; c_land += t_e - t_d; c_sync += t_f - t_e; c_mma += clock64() - t_f;
         }
-        __syncwarp();  // warp 0 arrives at the block-wide barriers as one
+    }
+    if (timing) {
+        p.trace[0] = (unsigned long long)c_wait; p.trace[1] = (unsigned long long)c_x; p.trace[2] = (unsigned long long)c_deq;
+        p.trace[3] = (unsigned long long)c_land; p.trace[4] = (unsigned long long)c_sync; p.trace[5] = (unsigned long long)c_mma;
+        p.trace[6] = (unsigned long long)kt_total;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }  // dequantising warps
 
     // ---- epilogue: TMEM -> registers -> bf16 -> Y[token][row] --------------------------------------------
     // a warp reads the 32 accumulator lanes of its quarter (warp & 3); warps 0-3 take the first half of the
     // token columns, warps 4-7 the second
-    bool ok = !failed;
+    bool ok = !failed && warp < kTcThreads / 32;
     if (ok && !mbar_wait(&done_bar, 0u)) { atomicExch(p.status, 1); ok = false; }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
@@ -266,7 +303,7 @@ __global__ void __launch_bounds__(kTcThreads) qgemm_tc_kernel(const QGemmTcParam
 }
 
 template <int BN, int STAGES>
-constexpr size_t tc_smem_bytes() { return (size_t)STAGES * (kTcRows * 128 + BN * 128) + 1024; }
+constexpr size_t tc_smem_bytes() { return (size_t)2 * kTcRows * 128 + (size_t)STAGES * BN * 128 + 1024; }
 
 template <int BN, int STAGES>
 int tc_init_one() {
@@ -277,16 +314,16 @@ int tc_init_one() {
 template <int BN, int STAGES>
 cudaError_t tc_launch_one(const QGemmTcParams& p, bool f16, cudaStream_t s) {
     const dim3 grid((unsigned)((p.n + kTcRows - 1) / kTcRows), (unsigned)((p.m + BN - 1) / BN), 1);
-    return f16 ? launch_k(qgemm_tc_kernel<BN, STAGES, true>, grid, dim3(kTcThreads), tc_smem_bytes<BN, STAGES>(), s, p)
-               : launch_k(qgemm_tc_kernel<BN, STAGES, false>, grid, dim3(kTcThreads), tc_smem_bytes<BN, STAGES>(), s, p);
+    return f16 ? launch_k(qgemm_tc_kernel<BN, STAGES, true>, grid, dim3(kTcThreads + 32), tc_smem_bytes<BN, STAGES>(), s, p)
+               : launch_k(qgemm_tc_kernel<BN, STAGES, false>, grid, dim3(kTcThreads + 32), tc_smem_bytes<BN, STAGES>(), s, p);
 }
 
 }  // namespace
 
 int qgemm_tc_init() {
     int rc;
-    if ((rc = tc_init_one<64, 3>())) return rc;
-    if ((rc = tc_init_one<128, 3>())) return rc;
+    if ((rc = tc_init_one<64, 4>())) return rc;
+    if ((rc = tc_init_one<128, 4>())) return rc;
     if ((rc = tc_init_one<256, 4>())) return rc;
     return SWLM_OK;
 }
@@ -300,10 +337,14 @@ int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride,
     QGemmTcParams p{};
     p.w = w.w; p.scales = w.scales; p.biases = w.biases; p.n = w.n; p.k = w.k;
     p.x = x; p.x_stride = x_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;
+    p.trace = qgemv_trace_slot(2, w.n, m, 10, 0);
     cudaError_t e;
-    if (m > 128) e = tc_launch_one<256, 4>(p, w.sb_f16, s);
-    else if (m > 64) e = tc_launch_one<128, 3>(p, w.sb_f16, s);
-    else e = tc_launch_one<64, 3>(p, w.sb_f16, s);
+    int bn = m > 128 ? 256 : m > 64 ? 128 : 64;
+    static const int forced_bn = [] { const char* v = getenv("SWLM_TC_BN"); return v ? atoi(v) : 0; }();
+    if (forced_bn == 64 || forced_bn == 128 || forced_bn == 256) bn = forced_bn;
+    if (bn == 256) e = tc_launch_one<256, 4>(p, w.sb_f16, s);
+    else if (bn == 128) e = tc_launch_one<128, 4>(p, w.sb_f16, s);
+    else e = tc_launch_one<64, 4>(p, w.sb_f16, s);
     if (e != cudaSuccess) return cuda_fail(e, "qgemm_tc launch");
     return SWLM_OK;
 }

@@ -110,12 +110,9 @@ __device__ __forceinline__ void fused_norm_run(const QGemvParams& p, int b, int 
             const int par = tp_epoch & 1;
 #pragma unroll 1
             for (int src = 0; src < p.tp.tp; ++src) {
-                const float4* r = reinterpret_cast<const float4*>(p.tp.peer[p.tp.rank] + p.tp.lay.recv_ar(par, src, b)) + k0 / 4;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 v = __ldcg(r + q);
-                    h[4 * q] += v.x; h[4 * q + 1] += v.y; h[4 * q + 2] += v.z; h[4 * q + 3] += v.w;
-                }
+                const unsigned char* r = p.tp.peer[p.tp.rank] + p.tp.lay.recv_ar(par, src, b) + (size_t)k0 * 8;
+                tp_add_tagged<4>(p.tp, r, tp_epoch, h);
+                tp_add_tagged<4>(p.tp, r + 64, tp_epoch, h + 8);
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) h[i] = __bfloat162float(__float2bfloat16_rn(h[i]));
@@ -176,22 +173,17 @@ __device__ __forceinline__ void fused_norm_run(const QGemvParams& p, int b, int 
 
 // All-reduce, producing side: one fp32 value of row `row`, sequence `col`, into every rank's buffer.
 __device__ __forceinline__ void tp_push_value(const QGemvParams& p, int epoch, int row, int col, float v) {
-    const size_t off = p.tp.lay.recv_ar(epoch & 1, p.tp.rank, col) + (size_t)row * 4;
+    const size_t off = p.tp.lay.recv_ar(epoch & 1, p.tp.rank, col) + (size_t)row * 8;
 #pragma unroll 1
-    for (int r = 0; r < p.tp.tp; ++r) *reinterpret_cast<float*>(p.tp.peer[r] + off) = v;
+    for (int r = 0; r < p.tp.tp; ++r) tp_store_tagged(p.tp.peer[r] + off, v, epoch);
 }
-// Called by one whole warp after it pushed a row tile: the warp that completes the count raises this
-// rank's flag on every rank and advances the local epoch.
+// Called by one whole warp after it pushed a row tile: the warp that completes the count advances the local
+// epoch for the kernels that follow (the pushed elements carry the number themselves and need no fence).
 __device__ __forceinline__ void tp_row_tile_done(const QGemvParams& p, int epoch, int lane) {
-    __threadfence_system();
-    __syncwarp();
     if (lane == 0) {
         const unsigned prev = atomicAdd(p.tp.done, 1u);
         if (prev == (unsigned)p.row_tiles - 1u) {
             *p.tp.done = 0u;
-            __threadfence_system();
-            for (int r = 0; r < p.tp.tp; ++r)
-                st_release_sys(reinterpret_cast<unsigned*>(p.tp.peer[r] + p.tp.lay.flags_ar(epoch & 1, p.tp.rank)), (unsigned)epoch);
             *p.tp.epoch = epoch;
         }
     }
@@ -263,10 +255,6 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
     // fragments of a group are the 16 consecutive elements 16t..16t+15)-------------------------------
     __shared__ float red[kWarps];
     const int tp_epoch = (p.push || p.in_tp) ? *p.tp.epoch + (p.push ? 1 : 0) : 0;
-    if (p.in_tp) {
-        tp_wait_flags(p.tp, p.tp.peer[p.tp.rank], p.tp.lay.flags_ar(tp_epoch & 1, 0), tp_epoch, tid);
-        __syncthreads();
-    }
     if (p.norm_mode) {
         // fused norm (dimension <= 4096, one CTA group): thread tid owns run tid of every row
         for (int b = 0; b < rows_x; ++b) {
@@ -648,10 +636,6 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
     __shared__ float red[kMaxWarps1];
     const int tp_epoch = (p.push || p.in_tp) ? *p.tp.epoch + (p.push ? 1 : 0) : 0;
-    if (p.in_tp) {
-        tp_wait_flags(p.tp, p.tp.peer[p.tp.rank], p.tp.lay.flags_ar(tp_epoch & 1, 0), tp_epoch, tid);
-        __syncthreads();
-    }
     const int nthreads = blockDim.x;
     const int nruns = kt_total * 8;  // runs of 8 elements: eight neighbouring threads share a group of 64
     for (int run = tid; run < nruns || (p.norm_mode && run < nthreads); run += nthreads) {
@@ -1016,6 +1000,11 @@ void qgemv_trace_report() {
     for (int sl = 0; sl < used; ++sl) {
         const TraceSlot& t = g_trace_slot[sl];
         const unsigned long long* r = h.data() + (size_t)sl * kTraceCtas * 4;
+        if (t.epi == 10) {  // tensor-core prefill product: clocks of CTA 0's thread 0 per phase, per group
+            if (r[6]) fprintf(stderr, "%3d prefill product n=%d m=%d | clocks per group: wait for MMAs %.0f, request x %.0f, dequantise %.0f, x landed %.0f, barrier %.0f, issue MMAs %.0f\n",
+                              sl, t.row_tiles, t.kt4, (double)r[0] / r[6], (double)r[1] / r[6], (double)r[2] / r[6], (double)r[3] / r[6], (double)r[4] / r[6], (double)r[5] / r[6]);
+            continue;
+        }
         unsigned long long e0 = ~0ull, d0 = ~0ull, d1 = 0, x1 = 0, f0 = ~0ull, f1 = 0;
         double a = 0, b = 0, c = 0;
         int n = 0;

@@ -68,9 +68,7 @@ __device__ __forceinline__ void fused_norm_run8(const QGemvParams& p, int k0, bo
             const int par = tp_epoch & 1;
 #pragma unroll 1
             for (int src = 0; src < p.tp.tp; ++src) {
-                const float4* r = reinterpret_cast<const float4*>(p.tp.peer[p.tp.rank] + p.tp.lay.recv_ar(par, src, 0)) + k0 / 4;
-                const float4 v0 = __ldcg(r), v1 = __ldcg(r + 1);
-                h[0] += v0.x; h[1] += v0.y; h[2] += v0.z; h[3] += v0.w; h[4] += v1.x; h[5] += v1.y; h[6] += v1.z; h[7] += v1.w;
+                tp_add_tagged<4>(p.tp, p.tp.peer[p.tp.rank] + p.tp.lay.recv_ar(par, src, 0) + (size_t)k0 * 8, tp_epoch, h);
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) h[i] = __bfloat162float(__float2bfloat16_rn(h[i]));

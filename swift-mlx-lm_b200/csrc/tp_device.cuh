@@ -4,12 +4,15 @@
 // The reference has no multi-device code; this is the sm_100a design for "one all-reduce per attention
 // and MLP block". Every rank owns one exchange buffer, mapped into every other rank's address space
 // (cudaIpc handles). The producing kernel stores its fp32 partial row straight into every rank's
-// buffer over NVLink (plain peer stores: the data lands in the consumer's own memory), then raises a
-// per-source flag with the epoch number. The consuming kernel polls its own flags, adds the partials in
-// rank order (the same order on every rank, so all ranks continue with bit-identical activations) and
+// buffer over NVLink (plain peer stores: the data lands in the consumer's own memory). Every element
+// travels as one 8-byte store {value, number of the exchange}: a reader that sees the number sees the
+// value, so the exchange needs no fence, no completion count and no separate flag, and its latency is
+// one NVLink store. The consuming kernel polls the elements it needs in its own memory, adds the partials
+// in rank order (the same order on every rank, so all ranks continue with bit-identical activations) and
 // goes on with the residual add and the norm. Two parities of buffers suffice: a rank can only be one
 // exchange ahead of the slowest rank. Every wait is bounded; on expiry an error word is set and the
 // kernel carries on with whatever it has, so a missing rank surfaces as a status, not as a hung GPU.
+// (The arg-max exchange of a vocabulary-sharded head, once per token, still uses a flag per source.)
 #pragma once
 
 #include <cstddef>
@@ -23,9 +26,10 @@ struct TpLayout {
     int tp, batch, hidden;
     __host__ __device__ size_t flags_ar(int par, int src) const { return ((size_t)par * kTpMax + src) * 4; }
     __host__ __device__ size_t flags_am(int par, int src) const { return 64 + ((size_t)par * kTpMax + src) * 4; }
-    __host__ __device__ size_t recv_ar(int par, int src, int b) const { return 256 + ((((size_t)par * tp + src) * batch + b) * hidden) * 4; }
-    __host__ __device__ size_t recv_am(int par, int src, int b) const { return 256 + (size_t)2 * tp * batch * hidden * 4 + (((size_t)par * tp + src) * batch + b) * 8; }
-    __host__ __device__ size_t total() const { return 256 + (size_t)2 * tp * batch * hidden * 4 + (size_t)2 * tp * batch * 8; }
+    // partial sums: 8 bytes per element {fp32 bits, exchange number}
+    __host__ __device__ size_t recv_ar(int par, int src, int b) const { return 256 + ((((size_t)par * tp + src) * batch + b) * hidden) * 8; }
+    __host__ __device__ size_t recv_am(int par, int src, int b) const { return 256 + (size_t)2 * tp * batch * hidden * 8 + (((size_t)par * tp + src) * batch + b) * 8; }
+    __host__ __device__ size_t total() const { return 256 + (size_t)2 * tp * batch * hidden * 8 + (size_t)2 * tp * batch * 8; }
 };
 
 // What a kernel needs to take part in an exchange. tp == 1: unused.
@@ -34,7 +38,7 @@ struct TpParams {
     TpLayout lay;
     unsigned char* peer[kTpMax];  // exchange buffers of all ranks; peer[rank] is this rank's own
     int* epoch;                   // local: number of all-reduces completed so far
-    unsigned* done;               // local: row tiles of the current product already pushed
+    unsigned* done;               // local: row tiles of the current product already pushed (the last one advances epoch)
     int* status;                  // local: set to non-zero when a bounded wait expired
 };
 
@@ -60,6 +64,34 @@ __device__ __forceinline__ void tp_wait_flags(const TpParams& tp, const unsigned
             __nanosleep(128);
         }
     }
+}
+
+// One element of a partial-sum buffer, written with a single 8-byte store.
+__device__ __forceinline__ void tp_store_tagged(unsigned char* dst, float v, int epoch) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"((unsigned)epoch) : "memory");
+}
+
+// Read 2 * N2 consecutive elements of a partial-sum buffer in this rank's own memory and add them to acc,
+// polling (bounded) until all of them carry the number of this exchange. After a wait has expired once,
+// later exchanges do not wait again: the status word says so.
+template <int N2>
+__device__ __forceinline__ void tp_add_tagged(const TpParams& tp, const unsigned char* src, int epoch, float* acc) {
+    uint4 v[N2];
+    int spins = 0;
+    for (;;) {
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < N2; ++i)
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "l"(src + 16 * i) : "memory");
+#pragma unroll
+        for (int i = 0; i < N2; ++i) ok = ok && v[i].y == (unsigned)epoch && v[i].w == (unsigned)epoch;
+        if (ok) break;
+        if (spins == 0 && *reinterpret_cast<volatile int*>(tp.status) != 0) break;
+        if (++spins > kTpSpinLimit) { atomicExch(tp.status, 1); break; }
+        __nanosleep(64);
+    }
+#pragma unroll
+    for (int i = 0; i < N2; ++i) { acc[2 * i] += __uint_as_float(v[i].x); acc[2 * i + 1] += __uint_as_float(v[i].z); }
 }
 #endif
 
