@@ -92,24 +92,41 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
     if (DECODE)
         prefetch_target_slice(p.prefetch, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                               gridDim.x * gridDim.y * gridDim.z, threadIdx.x, kSplitThreads);
-    pdl_wait();
-    if (p.trace && threadIdx.x == 0) p.trace[cta_linear * 4 + 1] = attn_timer_ns();
     constexpr int NCH = HD / 32;  // 16-byte K chunks per lane per token
     constexpr int VH = HD / 64;   // 64-dimension halves of V
+    constexpr int VPR = HD / 8;   // 16-byte vectors per head row
+    constexpr int PITCH = HD + 2; // row pitch of q in shared memory: the 8-byte fragment reads below hit 16 different bank pairs
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int G = p.heads / p.kv_heads;
+    const bool rotate = (DECODE || PREFILL) && p.rope_dim > 0;
+    // rotation: this thread owns the pairs (i, i + rope_dim/2) of rows tid / (HD/2), + kSplitThreads / (HD/2), ...;
+    // its frequency is a constant of the model and is fetched before the predecessor has finished
+    const int pairs = p.rope_dim >> 1;
+    const int rot_i = tid & (HD / 2 - 1);
+    float inv_f = 0.f;
+    if (rotate && rot_i < pairs) inv_f = __ldg(p.inv_freq + rot_i);
+    pdl_wait();
+    if (p.trace && threadIdx.x == 0) p.trace[cta_linear * 4 + 1] = attn_timer_ns();
+
+    __shared__ __align__(16) float qk[kMaxGroup + 1][PITCH];  // rows 0..G-1: q of the group, row G: the new k
+    __shared__ float vraw[HD];                                // new v
+    __shared__ float self_score[kMaxGroup];                   // q . k of the new token, log2 domain
+    __shared__ float osm[kSplitWarps][kMaxGroup][HD + 4];
+    __shared__ float msm[kSplitWarps][kMaxGroup], lsm[kSplitWarps][kMaxGroup];
+
+    // ---- q and the new k and v are requested first: they do not depend on the position --------------------
+    uint4 qv = make_uint4(0, 0, 0, 0), kv = qv, vv = qv;
+    const bool has_q = tid < G * VPR;
+    const bool has_k = DECODE && tid >= 64 && tid < 64 + VPR;
+    const bool has_v = DECODE && tid >= 96 && tid < 96 + VPR;
+    if (has_q) qv = *reinterpret_cast<const uint4*>(p.q + (size_t)b * p.q_stride + (size_t)kvh * G * HD + (size_t)tid * 8);
+    if (has_k) kv = *reinterpret_cast<const uint4*>(p.k + (size_t)b * p.k_stride + (size_t)kvh * HD + (size_t)(tid - 64) * 8);
+    if (has_v) vv = *reinterpret_cast<const uint4*>(p.v + (size_t)b * p.v_stride + (size_t)kvh * HD + (size_t)(tid - 96) * 8);
+
     // cached tokens to attend (in a decode step the new token is not among them)
     const int n_ctx = DECODE ? p.position[0] : PREFILL ? p.pos_base + b + 1 : p.ctx_len;
     const int rope_pos = PREFILL ? p.pos_base + b : n_ctx;
-
-    __shared__ float qrot[kMaxGroup][HD];   // unrotated q of the group
-    __shared__ float vec[HD];               // unrotated new k
-    __shared__ float vraw[HD];              // new v
-    __shared__ float cs[HD / 2], sn[HD / 2];
-    __shared__ float self_score[kMaxGroup]; // q . k of the new token, log2 domain
-    __shared__ float osm[kSplitWarps][kMaxGroup][HD + 4];
-    __shared__ float msm[kSplitWarps][kMaxGroup], lsm[kSplitWarps][kMaxGroup];
 
     const __nv_bfloat16* kbase = p.kcache + (PREFILL ? 0 : (size_t)b * p.cache_seq_stride) + (size_t)kvh * p.cache_head_stride;
     const __nv_bfloat16* vbase = p.vcache + (PREFILL ? 0 : (size_t)b * p.cache_seq_stride) + (size_t)kvh * p.cache_head_stride;
@@ -121,8 +138,8 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
     const int t_end = min(n_ctx, t_begin + chunk);
     const int last = t_end - 1;
 
-    // K and V of 16 tokens per warp live in registers; the first batch is requested before anything else so
-    // that its trip to HBM overlaps the whole prologue
+    // K and V of 16 tokens per warp live in registers; the first batch is requested before the rest of the
+    // prologue so that its trip to HBM overlaps it
     uint4 kreg[2][NCH];
     uint4 va[VH], vb[VH], vc[VH], vd[VH];
     auto load_k = [&](int tok0) {
@@ -147,53 +164,51 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
     int tok0 = t_begin + warp * 16;
     if (tok0 < t_end) { load_k(tok0); load_v(tok0); }
 
-    // ---- prologue: q, the new k and v, the rotation table: all global loads first, one barrier ------
+    // ---- prologue: q, k, v to shared memory as floats; then every pair is rotated once, in place ----------
+    float rot_s = 0.f, rot_c = 1.f;
+    if (rotate && rot_i < pairs) sincosf((float)rope_pos * inv_f, &rot_s, &rot_c);
     {
-        constexpr int VPR = HD / 8;  // 16-byte vectors per head row
-        uint4 qv = make_uint4(0, 0, 0, 0), kv = qv, vv = qv;
-        const bool has_q = tid < G * VPR;
-        const bool has_k = DECODE && tid < VPR;
-        const bool has_v = DECODE && tid >= 32 && tid < 32 + VPR;
-        if (has_q) qv = *reinterpret_cast<const uint4*>(p.q + (size_t)b * p.q_stride + (size_t)kvh * G * HD + (size_t)tid * 8);
-        if (has_k) kv = *reinterpret_cast<const uint4*>(p.k + (size_t)b * p.k_stride + (size_t)kvh * HD + (size_t)tid * 8);
-        if (has_v) vv = *reinterpret_cast<const uint4*>(p.v + (size_t)b * p.v_stride + (size_t)kvh * HD + (size_t)(tid - 32) * 8);
-        if (DECODE || PREFILL) {
-            const int pairs = p.rope_dim >> 1;
-            for (int i = tid; i < pairs; i += kSplitThreads) {
-                float sv_, cv_;
-                sincosf((float)rope_pos * p.inv_freq[i], &sv_, &cv_);
-                cs[i] = cv_; sn[i] = sv_;
-            }
-        }
-        auto spill8 = [](float* dst, const uint4& w) {
+        auto spill8 = [](float* dst, const uint4& w) {  // dst is 8-byte aligned
             const unsigned u[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { dst[2 * j] = __uint_as_float(u[j] << 16); dst[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<float2*>(dst + 2 * j) = make_float2(__uint_as_float(u[j] << 16), __uint_as_float(u[j] & 0xffff0000u));
         };
-        if (has_q) spill8(&qrot[0][0] + tid * 8, qv);
-        if (has_k) spill8(vec + tid * 8, kv);
+        if (has_q) spill8(&qk[tid / VPR][(tid % VPR) * 8], qv);
+        if (has_k) spill8(&qk[G][(tid - 64) * 8], kv);
         if (has_v) {
-            spill8(vraw + (tid - 32) * 8, vv);
+            const unsigned u[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { vraw[(tid - 96) * 8 + 2 * j] = __uint_as_float(u[j] << 16); vraw[(tid - 96) * 8 + 2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
             if (split == 0 && n_ctx < p.max_seq)  // the new v row goes to the cache as it is
-                *reinterpret_cast<uint4*>(p.vcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD + (size_t)(tid - 32) * 8) = vv;
+                *reinterpret_cast<uint4*>(p.vcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD + (size_t)(tid - 96) * 8) = vv;
         }
     }
     __syncthreads();
-    const bool rotate = (DECODE || PREFILL) && p.rope_dim > 0;
+    const int n_ctas = gridDim.x * gridDim.y * gridDim.z;
+    const bool stamp0 = p.trace && cta_linear == 0 && threadIdx.x == 0;  // finer stamps of the first CTA only
+    if (stamp0) p.trace[n_ctas * 4 + 1] = attn_timer_ns();
+    if (rotate) {
+        // rotate-half RoPE (Generator/MetalSourceGenerator+Attention.swift:596-617): pairs (i, i + rope_dim/2)
+        if (rot_i < pairs)
+            for (int r = tid / (HD / 2); r < G + (DECODE ? 1 : 0); r += kSplitThreads / (HD / 2)) {
+                const float lo = qk[r][rot_i], hi = qk[r][rot_i + pairs];
+                qk[r][rot_i] = lo * rot_c - hi * rot_s;
+                qk[r][rot_i + pairs] = lo * rot_s + hi * rot_c;
+            }
+        __syncthreads();
+    }
     if (DECODE) {
         if (split == 0 && n_ctx < p.max_seq) {  // the rotated new k row, rounded, for later steps
             __nv_bfloat16* kw = p.kcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD;
-            for (int d = tid; d < HD; d += kSplitThreads) kw[d] = __float2bfloat16_rn(rope_elem(vec, d, p.rope_dim, cs, sn));
+            for (int d = tid; d < HD; d += kSplitThreads) kw[d] = __float2bfloat16_rn(qk[G][d]);
         }
         // score of the new token against itself, in fp32 from the unrounded rotated q and k
         // (Generator/MetalSourceGenerator+Attention.swift:866-868)
         for (int r = warp; r < G; r += kSplitWarps) {
             float prod = 0.f;
 #pragma unroll
-            for (int i = 0; i < HD / 32; ++i) {
-                const int d = lane + 32 * i;
-                prod = fmaf(rope_elem(qrot[r], d, p.rope_dim, cs, sn), rope_elem(vec, d, p.rope_dim, cs, sn), prod);
-            }
+            for (int i = 0; i < HD / 32; ++i) prod = fmaf(qk[r][lane + 32 * i], qk[G][lane + 32 * i], prod);
             for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
             if (lane == 0) self_score[r] = prod * p.scale_log2;
         }
@@ -205,17 +220,14 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
     for (int i = 0; i < NCH; ++i)
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            float a = 0.f, c = 0.f;
-            if (g < G) {
-                const int d = 32 * i + 8 * t + 2 * w;
-                a = rotate ? rope_elem(qrot[g], d, p.rope_dim, cs, sn) : qrot[g][d];
-                c = rotate ? rope_elem(qrot[g], d + 1, p.rope_dim, cs, sn) : qrot[g][d + 1];
-            }
-            const float ah = __bfloat162float(__float2bfloat16_rn(a)), ch = __bfloat162float(__float2bfloat16_rn(c));
+            float2 ac = make_float2(0.f, 0.f);
+            if (g < G) ac = *reinterpret_cast<const float2*>(&qk[g][32 * i + 8 * t + 2 * w]);
+            const float ah = __bfloat162float(__float2bfloat16_rn(ac.x)), ch = __bfloat162float(__float2bfloat16_rn(ac.y));
             qhi[i][w] = pack_bf16(ah, ch);
-            qlo[i][w] = pack_bf16(a - ah, c - ch);
+            qlo[i][w] = pack_bf16(ac.x - ah, ac.y - ch);
         }
 
+    if (stamp0) p.trace[n_ctas * 4 + 2] = attn_timer_ns();
     float m_run = -INFINITY, l_run = 0.f;
     float oacc[VH][8][4];
 #pragma unroll
@@ -296,6 +308,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
             }
         }
         if (nxt < t_end) load_v(nxt);
+        if (stamp0 && tok0 == t_begin) p.trace[n_ctas * 4 + 3] = attn_timer_ns();
     }
 
     if (p.trace && threadIdx.x == 0) p.trace[cta_linear * 4 + 2] = attn_timer_ns();

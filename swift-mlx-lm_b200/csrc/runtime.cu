@@ -599,7 +599,7 @@ struct swlm_state {
     int pf_rows = 0;
     unsigned* pf_attn_counters = nullptr;
     int* pf_status = nullptr;      // device word: a bounded wait of the tensor-core product expired
-    int prefill_chunk = 512;       // tokens per chunk; 0 = one token at a time through the decode graph
+    int prefill_chunk = 2048;      // tokens per chunk; 0 = one token at a time through the decode graph
     int* tc_status = nullptr;      // pinned host word (mapped): a bounded wait of a kernel expired
 };
 
