@@ -131,18 +131,19 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
     const __nv_bfloat16* kbase = p.kcache + (PREFILL ? 0 : (size_t)b * p.cache_seq_stride) + (size_t)kvh * p.cache_head_stride;
     const __nv_bfloat16* vbase = p.vcache + (PREFILL ? 0 : (size_t)b * p.cache_seq_stride) + (size_t)kvh * p.cache_head_stride;
 
-    // ---- token range of this split ----------------------------------------------------------------
-    int chunk = (n_ctx + p.splits - 1) / p.splits;
-    chunk = ((chunk + 63) / 64) * 64;
-    const int t_begin = split * chunk;
-    const int t_end = min(n_ctx, t_begin + chunk);
-    const int last = t_end - 1;
+    // ---- tokens of this split: blocks of 64 tokens, block j belongs to split j % splits. A split's first block
+    // does not depend on the context length, so in a decode step it is requested before the position has arrived
+    // (rows are clamped to the cache's last row there; what lies beyond the context is masked below).
+    constexpr int kBlock = kSplitWarps * 16;
+    const int t_begin = split * kBlock;
+    const int t_end = n_ctx;
+    const int t_stride = p.splits * kBlock;
 
     // K and V of 16 tokens per warp live in registers; the first batch is requested before the rest of the
     // prologue so that its trip to HBM overlaps it
     uint4 kreg[2][NCH];
     uint4 va[VH], vb[VH], vc[VH], vd[VH];
-    auto load_k = [&](int tok0) {
+    auto load_k = [&](int tok0, int last) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             const __nv_bfloat16* rowp = kbase + (size_t)min(tok0 + 8 * nt + g, last) * HD;
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
             for (int i = 0; i < NCH; ++i) kreg[nt][i] = ldg128(rowp + (4 * i + t) * 8);
         }
     };
-    auto load_v = [&](int tok0) {
+    auto load_v = [&](int tok0, int last) {
         const __nv_bfloat16* ra = vbase + (size_t)min(tok0 + 2 * t, last) * HD + 8 * g;
         const __nv_bfloat16* rb = vbase + (size_t)min(tok0 + 2 * t + 1, last) * HD + 8 * g;
         const __nv_bfloat16* rc = vbase + (size_t)min(tok0 + 2 * t + 8, last) * HD + 8 * g;
@@ -162,7 +163,18 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         }
     };
     int tok0 = t_begin + warp * 16;
-    if (tok0 < t_end) { load_k(tok0); load_v(tok0); }
+    if (DECODE) { load_k(tok0, p.max_seq - 1); load_v(tok0, p.max_seq - 1); }
+    else if (tok0 < t_end) { load_k(tok0, t_end - 1); load_v(tok0, t_end - 1); }
+    // the split's later blocks are asked into L2 (two ahead; the loop keeps that distance): the register loads
+    // of the loop then find them there
+    constexpr int kAhead = 2;
+    auto prefetch_block = [&](int blk_tok) {
+        if (blk_tok >= t_end) return;
+        const unsigned bytes = (unsigned)(min(kBlock, t_end - blk_tok) * HD * 2);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(kbase + (size_t)blk_tok * HD), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vbase + (size_t)blk_tok * HD), "r"(bytes) : "memory");
+    };
+    if (tid < kAhead) prefetch_block(t_begin + (tid + 1) * t_stride);
 
     // ---- prologue: q, k, v to shared memory as floats; then every pair is rotated once, in place ----------
     float rot_s = 0.f, rot_c = 1.f;
@@ -235,8 +247,21 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
 #pragma unroll
         for (int u = 0; u < 8; ++u) oacc[hh][u][0] = oacc[hh][u][1] = oacc[hh][u][2] = oacc[hh][u][3] = 0.f;
 
-    for (; tok0 < t_end; tok0 += kSplitWarps * 16) {
-        const int nxt = tok0 + kSplitWarps * 16;
+    if (DECODE && tok0 < t_end && tok0 + 16 > t_end) {
+        // first batch, requested before the context length was known: rows beyond the context may hold anything;
+        // their probabilities are zero, their values must be finite
+        const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int hh = 0; hh < VH; ++hh) {
+            if (tok0 + 2 * t >= t_end) va[hh] = z;
+            if (tok0 + 2 * t + 1 >= t_end) vb[hh] = z;
+            if (tok0 + 2 * t + 8 >= t_end) vc[hh] = z;
+            if (tok0 + 2 * t + 9 >= t_end) vd[hh] = z;
+        }
+    }
+    for (; tok0 < t_end; tok0 += t_stride) {
+        const int nxt = tok0 + t_stride;
+        if (tid == 0) prefetch_block(tok0 + (kAhead + 1) * t_stride);
         // S = q . K^T for 16 tokens
         float sacc[2][4];
 #pragma unroll
@@ -251,7 +276,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
                 mma_bf16(sacc[nt], qhi[i][2], qlo[i][2], qhi[i][3], qlo[i][3], kk.z, kk.w);
             }
         }
-        if (nxt < t_end) load_k(nxt);  // the K registers are free again
+        if (nxt < t_end) load_k(nxt, t_end - 1);  // the K registers are free again
         // online softmax in the log2 domain; row g lives in the four lanes t = 0..3
         float sv[2][2];
         float rmax = -INFINITY;
@@ -307,7 +332,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
                 mma_bf16(oacc[hh][2 * w + 1], pa0, pl0, pa2, pl2, b0o, b1o);
             }
         }
-        if (nxt < t_end) load_v(nxt);
+        if (nxt < t_end) load_v(nxt, t_end - 1);
         if (stamp0 && tok0 == t_begin) p.trace[n_ctas * 4 + 3] = attn_timer_ns();
     }
 

@@ -11,19 +11,23 @@
 //     (scale, zero), turns nibble pairs into bf16 with LOP3 (128+q), subtracts 128 and applies scale and zero
 //     with one bf16x2 FMA each — exactly bf16(scale*q + zero) — and stores the 128-byte row into shared
 //     memory in the K-major, 128-byte-swizzled layout tcgen05.mma reads;
-//   * the activation tile (BN tokens x 64 columns, bf16) is copied into the same layout with cp.async;
-//   * one thread issues four tcgen05.mma (M=128, N=BN, K=16, kind::f16, bf16 x bf16 -> fp32) per group into
+//   * the activation tile (BN tokens x 64 columns, bf16) arrives in the same layout by TMA: one thread of a
+//     producer warp issues one cp.async.bulk.tensor per group (128-byte swizzle, rows past the last token
+//     filled with zeros), several groups ahead, and an mbarrier counts the bytes;
+//   * one thread of another warp issues four tcgen05.mma (M=128, N=BN, K=16, kind::f16, bf16 x bf16 -> fp32) per group into
 //     a TMEM accumulator; tcgen05.commit signals an mbarrier when the stage may be overwritten;
 //   * the epilogue reads the accumulator with tcgen05.ld, rounds to bf16 and stores Y[token][row].
 // Every mbarrier wait is bounded: on expiry an error word is set, the CTA stops issuing, frees its TMEM
 // and returns.
 #include <cstdlib>
+#include <cuda.h>
 #include "swlm_internal.h"
 
 namespace swlm {
 namespace {
 
-constexpr int kTcThreads = 256;          // dequantising threads; one more warp issues the MMAs
+constexpr int kTcThreads = 256;          // dequantising threads
+constexpr int kTcAllThreads = kTcThreads + 64;  // + the MMA warp and the activation (TMA) warp
 constexpr int kTcRows = 128;            // weight rows per CTA = UMMA M
 constexpr int kTcBK = 64;               // one quantisation group per pipeline stage
 constexpr int kTcSpinLimit = 1 << 22;
@@ -95,21 +99,22 @@ __device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7
 //
 // 256 threads: thread (r = tid & 127, h = tid >> 7) dequantises columns 32h..32h+31 of weight row r in every
 // group, so a group costs a thread one 16-byte load and about 90 instructions. Packed weights and (scale, zero)
-// are fetched four groups ahead into registers, the activation tiles two groups ahead with cp.async into a ring
-// of their own (SB stages; the dequantised weight tiles need only SA = 2), so that neither latency sits between
-// two MMAs. A ninth warp issues the MMAs: the 256 threads arrive on ready_bar[kt % 2] once their part of group kt
-// is in shared memory and go on with group kt + 1 while the tensor core works; tcgen05.commit signals, per
-// group, that its MMAs are done and its stages may be overwritten.
+// are fetched four groups ahead into registers. The activation tiles have a ring of their own (SB stages; the
+// dequantised weight tiles need only SA = 2) that the tenth warp fills by TMA. The ninth warp issues the MMAs:
+// the 256 threads arrive on ready_bar[kt % 2] once their part of group kt is in shared memory and go on with
+// group kt + 1 while the tensor core works; full_bar[kt % SB] completes when the group's activations have landed;
+// tcgen05.commit signals, per group, that its MMAs are done and its stages may be overwritten.
 template <int BN, int STAGES, bool F16SB>
-__global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTcParams p) {
+__global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcParams p, const __grid_constant__ CUtensorMap xmap) {
     constexpr int SA = 2, SB = STAGES;
-    static_assert(SB >= 4, "activation tiles are requested two groups ahead of a stage that was used two groups ago");
+    static_assert(SB >= 3, "the activation ring must be deeper than the weight ring");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment for the swizzle atoms
     unsigned char* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
     constexpr int A_BYTES = kTcRows * 128;
     constexpr int B_BYTES = BN * 128;
     __shared__ __align__(8) unsigned long long empty_bar[STAGES];
+    __shared__ __align__(8) unsigned long long full_bar[STAGES];    // the activation tile of a stage has landed
     __shared__ __align__(8) unsigned long long ready_bar[2];   // a weight tile and its activation tile are in place
     __shared__ __align__(8) unsigned long long done_bar;
     __shared__ unsigned tmem_base_smem;
@@ -123,7 +128,7 @@ __global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTc
 
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < STAGES; ++s) mbar_init(&empty_bar[s], 1);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&empty_bar[s], 1); mbar_init(&full_bar[s], 1); }
         mbar_init(&ready_bar[0], kTcThreads);
         mbar_init(&ready_bar[1], kTcThreads);
         mbar_init(&done_bar, 1);
@@ -154,25 +159,6 @@ __global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTc
         if (row_ok && kt < kt_total) { v.w = __ldg(wrow + kt * 2); v.s = __ldg(srow + kt); v.z = __ldg(zrow + kt); }
         return v;
     };
-    // activation tile: thread (token t = tid >> 3 (+ 32 i), 16-byte chunk c = tid & 7); the swizzled position of
-    // a chunk depends on t & 7 only, which is the same for all i, so source and destination advance by constants
-    const int x_tok = tid >> 3, x_c = tid & 7;
-    const __nv_bfloat16* const x_src0 = p.x + (size_t)(tok0 + x_tok) * p.x_stride + x_c * 8;
-    const size_t x_src_step = (size_t)32 * p.x_stride;
-    const unsigned x_dst0 = smem_u32(b_ring) + (unsigned)swz(x_tok, x_c);
-    auto issue_x = [&](int kt) {
-        if (kt >= kt_total) return;
-        const unsigned dst = x_dst0 + (unsigned)((kt % SB) * B_BYTES);
-        const __nv_bfloat16* src = x_src0 + (size_t)kt * kTcBK;
-#pragma unroll
-        for (int i = 0; i < BN * 8 / kTcThreads; ++i) {
-            if (tok0 + x_tok + 32 * i < p.m)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (unsigned)i * 4096u), "l"(src + (size_t)i * x_src_step) : "memory");
-            else
-                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + (unsigned)i * 4096u), "r"(0u) : "memory");
-        }
-    };
-
     // packed weights and their scale/zero run four groups ahead in registers (L2 latency is several groups long);
     // they do not depend on the preceding kernel
     if (warp == kTcThreads / 32) {
@@ -180,7 +166,9 @@ __global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTc
         // dequantising warps are already busy with the next group by then -----------------------------------
         if (lane == 0) {
             for (int kt = 0; kt < kt_total; ++kt) {
-                if (!mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1))) { atomicExch(p.status, 2); failed = 1; break; }
+                if (!mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1)) || !mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1))) {
+                    atomicExch(p.status, 2); failed = 1; break;
+                }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned a_addr = smem_u32(smem + (kt % SA) * A_BYTES), b_addr = smem_u32(b_ring + (kt % SB) * B_BYTES);
 #pragma unroll
@@ -191,26 +179,40 @@ __global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTc
             }
         }
         __syncwarp();
+    } else if (warp == kTcThreads / 32 + 1) {
+        // ---- activation warp: one thread keeps the ring of activation tiles full ----------------------------
+        if (lane == 0) {
+            pdl_wait();                         // the activations may come from the kernel just before this one
+            int issued = 0;
+            for (int kt = 0; kt < kt_total; ++kt) {
+                const int s = kt % SB;
+                // the MMAs that read this stage SB groups ago are done
+                if (kt >= SB && !mbar_wait(&empty_bar[s], (unsigned)((kt / SB - 1) & 1))) { atomicExch(p.status, 3); failed = 1; break; }
+                if (failed) break;
+                const unsigned bar = smem_u32(&full_bar[s]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)B_BYTES) : "memory");
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(smem_u32(b_ring + s * B_BYTES)), "l"(reinterpret_cast<unsigned long long>(&xmap)), "r"(kt * kTcBK), "r"(tok0), "r"(bar) : "memory");
+                issued = kt + 1;
+            }
+            if (failed) {
+                // stopping early: the copies already requested still write shared memory; wait for them (bounded)
+                for (int kt = issued > SB ? issued - SB : 0; kt < issued; ++kt) mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1));
+            }
+        }
+        __syncwarp();
     } else {
     WReg w_q0 = load_w(0), w_q1 = load_w(1), w_q2 = load_w(2), w_q3 = load_w(3);
-    pdl_wait();                                 // the activations may come from the kernel just before this one
-    issue_x(0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    issue_x(1);
-    asm volatile("cp.async.commit_group;" ::: "memory");
 
     long long c_wait = 0, c_x = 0, c_deq = 0, c_land = 0, c_sync = 0, c_mma = 0;  // tracing only
     const bool timing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
     for (int kt = 0; kt < kt_total; ++kt) {
         const long long t_a = timing ? clock64() : 0;
         unsigned char* const a_tile = smem + (kt % SA) * A_BYTES;
-        // ---- the MMAs of group kt - 2 are done: its weight tile (this group's) and its activation tile (that of
-        // group kt + 2, requested now) may be overwritten -----------------------------------------------------
+        // ---- the MMAs of group kt - 2 are done: its weight tile (this group's) may be overwritten ------------
         if (kt >= 2 && !mbar_wait(&empty_bar[(kt - 2) % SB], (unsigned)(((kt - 2) / SB) & 1))) { atomicExch(p.status, 1); failed = 1; }
         const long long t_b = timing ? clock64() : 0;
-        issue_x(kt + 2);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        const long long t_c = timing ? clock64() : 0;
+        const long long t_c = t_b;
         // ---- weights: 32 nibbles of this thread's row -> 32 bf16 = bf16(scale * q + zero) -----------------
         {
             const WReg v = w_q0;
@@ -249,8 +251,7 @@ __global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTc
             }
         }
         const long long t_d = timing ? clock64() : 0;
-        asm volatile("cp.async.wait_group 2;" ::: "memory");  // this group's activations have landed
-        const long long t_e = timing ? clock64() : 0;
+        const long long t_e = t_d;
         // generic-proxy writes to shared memory -> visible to the tensor core (async proxy), then tell the MMA warp
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ready_bar[kt % SA])) : "memory");
@@ -265,7 +266,6 @@ __global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTc
         p.trace[3] = (unsigned long long)c_land; p.trace[4] = (unsigned long long)c_sync; p.trace[5] = (unsigned long long)c_mma;
         p.trace[6] = (unsigned long long)kt_total;
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
     }  // dequantising warps
 
     // ---- epilogue: TMEM -> registers -> bf16 -> Y[token][row] --------------------------------------------
@@ -305,6 +305,35 @@ __global__ void __launch_bounds__(kTcThreads + 32) qgemm_tc_kernel(const QGemmTc
 template <int BN, int STAGES>
 constexpr size_t tc_smem_bytes() { return (size_t)2 * kTcRows * 128 + (size_t)STAGES * BN * 128 + 1024; }
 
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link against the driver
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+TensorMapEncodeFn tensor_map_encode_fn() {
+    static TensorMapEncodeFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+        return reinterpret_cast<TensorMapEncodeFn>(f);
+    }();
+    return fn;
+}
+
+// bf16 activations X[m][x_stride] as a 2-D tensor (k innermost); box = 64 columns x bn tokens, 128-byte swizzle
+int make_x_map(const __nv_bfloat16* x, int x_stride, int m, int k, int bn, CUtensorMap* map) {
+    TensorMapEncodeFn fn = tensor_map_encode_fn();
+    if (!fn) { set_error("qgemm (tcgen05): cuTensorMapEncodeTiled is not available"); return SWLM_ERR_CUDA; }
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)x_stride * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)bn};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(x), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("qgemm (tcgen05): cuTensorMapEncodeTiled failed (%d)", (int)r); return SWLM_ERR_CUDA; }
+    return SWLM_OK;
+}
+
 template <int BN, int STAGES>
 int tc_init_one() {
     SWLM_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<BN, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes<BN, STAGES>()));
@@ -312,19 +341,24 @@ int tc_init_one() {
     return SWLM_OK;
 }
 template <int BN, int STAGES>
-cudaError_t tc_launch_one(const QGemmTcParams& p, bool f16, cudaStream_t s) {
+int tc_launch_one(const QGemmTcParams& p, bool f16, cudaStream_t s) {
+    CUtensorMap xmap;
+    int rc = make_x_map(p.x, p.x_stride, p.m, p.k, BN, &xmap);
+    if (rc) return rc;
     const dim3 grid((unsigned)((p.n + kTcRows - 1) / kTcRows), (unsigned)((p.m + BN - 1) / BN), 1);
-    return f16 ? launch_k(qgemm_tc_kernel<BN, STAGES, true>, grid, dim3(kTcThreads + 32), tc_smem_bytes<BN, STAGES>(), s, p)
-               : launch_k(qgemm_tc_kernel<BN, STAGES, false>, grid, dim3(kTcThreads + 32), tc_smem_bytes<BN, STAGES>(), s, p);
+    const cudaError_t e = f16 ? launch_k(qgemm_tc_kernel<BN, STAGES, true>, grid, dim3(kTcAllThreads), tc_smem_bytes<BN, STAGES>(), s, p, xmap)
+                              : launch_k(qgemm_tc_kernel<BN, STAGES, false>, grid, dim3(kTcAllThreads), tc_smem_bytes<BN, STAGES>(), s, p, xmap);
+    if (e != cudaSuccess) return cuda_fail(e, "qgemm_tc launch");
+    return SWLM_OK;
 }
 
 }  // namespace
 
 int qgemm_tc_init() {
     int rc;
-    if ((rc = tc_init_one<64, 4>())) return rc;
-    if ((rc = tc_init_one<128, 4>())) return rc;
-    if ((rc = tc_init_one<256, 4>())) return rc;
+    if ((rc = tc_init_one<64, 6>())) return rc;
+    if ((rc = tc_init_one<128, 6>())) return rc;
+    if ((rc = tc_init_one<256, 5>())) return rc;
     return SWLM_OK;
 }
 
@@ -338,15 +372,14 @@ int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride,
     p.w = w.w; p.scales = w.scales; p.biases = w.biases; p.n = w.n; p.k = w.k;
     p.x = x; p.x_stride = x_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;
     p.trace = qgemv_trace_slot(2, w.n, m, 10, 0);
-    cudaError_t e;
+    int rc;
     int bn = m > 128 ? 256 : m > 64 ? 128 : 64;
     static const int forced_bn = [] { const char* v = getenv("SWLM_TC_BN"); return v ? atoi(v) : 0; }();
     if (forced_bn == 64 || forced_bn == 128 || forced_bn == 256) bn = forced_bn;
-    if (bn == 256) e = tc_launch_one<256, 4>(p, w.sb_f16, s);
-    else if (bn == 128) e = tc_launch_one<128, 4>(p, w.sb_f16, s);
-    else e = tc_launch_one<64, 4>(p, w.sb_f16, s);
-    if (e != cudaSuccess) return cuda_fail(e, "qgemm_tc launch");
-    return SWLM_OK;
+    if (bn == 256) rc = tc_launch_one<256, 5>(p, w.sb_f16, s);
+    else if (bn == 128) rc = tc_launch_one<128, 6>(p, w.sb_f16, s);
+    else rc = tc_launch_one<64, 6>(p, w.sb_f16, s);
+    return rc;
 }
 
 }  // namespace swlm
