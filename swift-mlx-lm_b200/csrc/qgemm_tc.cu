@@ -7,8 +7,10 @@
 // fp32 accumulation), except that the bf16 weights never exist in global memory.
 //
 // One CTA computes a 128 (weight rows) x BN (tokens) tile of Y^T:
-//   * every thread owns one weight row: per 64-column group it loads the row's 32 packed bytes and its
-//     (scale, zero), turns nibble pairs into bf16 with LOP3 (128+q), subtracts 128 and applies scale and zero
+//   * the packed weights of a group (128 rows x 32 bytes) arrive in shared memory by TMA, together with the
+//     activation tile; two threads own one weight row: per 64-column group each reads 16 packed bytes from
+//     shared memory, takes the row's (scale, zero) from registers (fetched eight groups at a time), turns
+//     nibble pairs into bf16 with LOP3 (128+q), subtracts 128 and applies scale and zero
 //     with one bf16x2 FMA each — exactly bf16(scale*q + zero) — and stores the 128-byte row into shared
 //     memory in the K-major, 128-byte-swizzled layout tcgen05.mma reads;
 //   * the activation tile (BN tokens x 64 columns, bf16) arrives in the same layout by TMA: one thread of a
@@ -97,15 +99,15 @@ __device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7
 
 // F16SB: scale and zero are fp16 (tensors uploaded as STAF blocks) instead of bf16 (MLX tensors).
 //
-// 256 threads: thread (r = tid & 127, h = tid >> 7) dequantises columns 32h..32h+31 of weight row r in every
-// group, so a group costs a thread one 16-byte load and about 90 instructions. Packed weights and (scale, zero)
-// are fetched four groups ahead into registers. The activation tiles have a ring of their own (SB stages; the
-// dequantised weight tiles need only SA = 2) that the tenth warp fills by TMA. The ninth warp issues the MMAs:
+// 256 threads: thread (r = tid >> 1, h = tid & 1) dequantises columns 32h..32h+31 of weight row r in every
+// group: one 16-byte read from shared memory and about 90 instructions. The packed weights and the activation
+// tiles share a ring of SB stages that the tenth warp fills by TMA (the dequantised weight tiles need only
+// SA = 2); scales and zeros are read straight from global memory, eight groups per 16-byte load. The ninth warp issues the MMAs:
 // the 256 threads arrive on ready_bar[kt % 2] once their part of group kt is in shared memory and go on with
 // group kt + 1 while the tensor core works; full_bar[kt % SB] completes when the group's activations have landed;
 // tcgen05.commit signals, per group, that its MMAs are done and its stages may be overwritten.
 template <int BN, int STAGES, bool F16SB>
-__global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcParams p, const __grid_constant__ CUtensorMap xmap) {
+__global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
     constexpr int SA = 2, SB = STAGES;
     static_assert(SB >= 3, "the activation ring must be deeper than the weight ring");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -113,6 +115,8 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     unsigned char* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
     constexpr int A_BYTES = kTcRows * 128;
     constexpr int B_BYTES = BN * 128;
+    constexpr int W_BYTES = kTcRows * 32;        // packed weights of one group
+    constexpr int STAGE_BYTES = B_BYTES + W_BYTES;
     __shared__ __align__(8) unsigned long long empty_bar[STAGES];
     __shared__ __align__(8) unsigned long long full_bar[STAGES];    // the activation tile of a stage has landed
     __shared__ __align__(8) unsigned long long ready_bar[2];   // a weight tile and its activation tile are in place
@@ -121,7 +125,8 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     __shared__ int failed;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int r = tid & 127, half = tid >> 7;
+    const long long t_entry = clock64();
+    const int r = (tid >> 1) & 127, half = tid & 1;
     const int row0 = blockIdx.x * kTcRows, tok0 = blockIdx.y * BN;
     const int kt_total = p.k / kTcBK;
     unsigned char* const b_ring = smem + SA * A_BYTES;
@@ -147,20 +152,27 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
 
     const int row = row0 + r;
     const bool row_ok = row < p.n;
-    // this thread's 16 bytes of group kt: words 4h..4h+3 of the row's eight
-    const uint4* wrow = reinterpret_cast<const uint4*>(p.w + (size_t)(row_ok ? row : 0) * (p.k / 8)) + half;
     const uint16_t* srow = p.scales + (size_t)(row_ok ? row : 0) * kt_total;
     const uint16_t* zrow = p.biases + (size_t)(row_ok ? row : 0) * kt_total;
     constexpr unsigned idesc = umma_idesc(BN);
 
-    struct WReg { uint4 w; unsigned s, z; };
-    auto load_w = [&](int kt) {
-        WReg v; v.w = make_uint4(0, 0, 0, 0); v.s = 0; v.z = 0;
-        if (row_ok && kt < kt_total) { v.w = __ldg(wrow + kt * 2); v.s = __ldg(srow + kt); v.z = __ldg(zrow + kt); }
-        return v;
+    // scales and zeros of groups kt0..kt0+7 of this thread's row (16-bit each), one 16-byte load each when the
+    // rows are 16-byte aligned; they do not depend on the preceding kernel
+    const bool sz_vec = (kt_total & 7) == 0;
+    auto load8 = [&](const uint16_t* rowp, int kt0) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (!row_ok || kt0 >= kt_total) return v;
+        if (sz_vec) return __ldg(reinterpret_cast<const uint4*>(rowp + kt0));
+        unsigned h[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = kt0 + j < kt_total ? (unsigned)__ldg(rowp + kt0 + j) : 0u;
+        return make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
     };
-    // packed weights and their scale/zero run four groups ahead in registers (L2 latency is several groups long);
-    // they do not depend on the preceding kernel
+    auto pick16 = [](const uint4& v, int j) {  // 16-bit element j (0..7)
+        const unsigned lo = (j & 2) ? v.y : v.x, hi = (j & 2) ? v.w : v.z;
+        const unsigned w = (j & 4) ? hi : lo;
+        return (j & 1) ? w >> 16 : w & 0xFFFFu;
+    };
     if (warp == kTcThreads / 32) {
         // ---- MMA warp: one thread issues the four MMAs of a group as soon as its tiles are in place; the
         // dequantising warps are already busy with the next group by then -----------------------------------
@@ -170,7 +182,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
                     atomicExch(p.status, 2); failed = 1; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned a_addr = smem_u32(smem + (kt % SA) * A_BYTES), b_addr = smem_u32(b_ring + (kt % SB) * B_BYTES);
+                const unsigned a_addr = smem_u32(smem + (kt % SA) * A_BYTES), b_addr = smem_u32(b_ring + (kt % SB) * STAGE_BYTES);
 #pragma unroll
                 for (int j = 0; j < kTcBK / 16; ++j)  // 16 bf16 = 32 bytes along K inside the 128-byte row
                     umma_f16(tmem_d, umma_desc(a_addr + 32 * j), umma_desc(b_addr + 32 * j), idesc, (kt > 0 || j > 0) ? 1u : 0u);
@@ -190,9 +202,11 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
                 if (kt >= SB && !mbar_wait(&empty_bar[s], (unsigned)((kt / SB - 1) & 1))) { atomicExch(p.status, 3); failed = 1; break; }
                 if (failed) break;
                 const unsigned bar = smem_u32(&full_bar[s]);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)B_BYTES) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)STAGE_BYTES) : "memory");
                 asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(smem_u32(b_ring + s * B_BYTES)), "l"(reinterpret_cast<unsigned long long>(&xmap)), "r"(kt * kTcBK), "r"(tok0), "r"(bar) : "memory");
+                             ::"r"(smem_u32(b_ring + s * STAGE_BYTES + B_BYTES)), "l"(reinterpret_cast<unsigned long long>(&wmap)), "r"(kt * 32), "r"(row0), "r"(bar) : "memory");
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(smem_u32(b_ring + s * STAGE_BYTES)), "l"(reinterpret_cast<unsigned long long>(&xmap)), "r"(kt * kTcBK), "r"(tok0), "r"(bar) : "memory");
                 issued = kt + 1;
             }
             if (failed) {
@@ -202,22 +216,26 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         }
         __syncwarp();
     } else {
-    WReg w_q0 = load_w(0), w_q1 = load_w(1), w_q2 = load_w(2), w_q3 = load_w(3);
+    uint4 s_cur = load8(srow, 0), z_cur = load8(zrow, 0), s_nxt = load8(srow, 8), z_nxt = load8(zrow, 8);
 
     long long c_wait = 0, c_x = 0, c_deq = 0, c_land = 0, c_sync = 0, c_mma = 0;  // tracing only
     const bool timing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
+    if (timing) p.trace[7] = (unsigned long long)(clock64() - t_entry);  // set-up
     for (int kt = 0; kt < kt_total; ++kt) {
         const long long t_a = timing ? clock64() : 0;
         unsigned char* const a_tile = smem + (kt % SA) * A_BYTES;
         // ---- the MMAs of group kt - 2 are done: its weight tile (this group's) may be overwritten ------------
         if (kt >= 2 && !mbar_wait(&empty_bar[(kt - 2) % SB], (unsigned)(((kt - 2) / SB) & 1))) { atomicExch(p.status, 1); failed = 1; }
         const long long t_b = timing ? clock64() : 0;
-        const long long t_c = t_b;
+        // ---- this group's packed weights have landed (with its activations) ---------------------------------
+        if (!mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1))) { atomicExch(p.status, 1); failed = 1; }
+        const long long t_c = timing ? clock64() : 0;
         // ---- weights: 32 nibbles of this thread's row -> 32 bf16 = bf16(scale * q + zero) -----------------
         {
-            const WReg v = w_q0;
-            w_q0 = w_q1; w_q1 = w_q2; w_q2 = w_q3;
-            w_q3 = load_w(kt + 4);
+            struct { uint4 w; unsigned s, z; } v;
+            v.w = *reinterpret_cast<const uint4*>(b_ring + (kt % SB) * STAGE_BYTES + B_BYTES + r * 32 + half * 16);
+            if ((kt & 7) == 0 && kt > 0) { s_cur = s_nxt; z_cur = z_nxt; s_nxt = load8(srow, kt + 8); z_nxt = load8(zrow, kt + 8); }
+            v.s = pick16(s_cur, kt & 7); v.z = pick16(z_cur, kt & 7);
             const unsigned s2 = v.s | (v.s << 16), z2 = v.z | (v.z << 16);
             const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(&s2);
             const __nv_bfloat162 zr = *reinterpret_cast<const __nv_bfloat162*>(&z2);
@@ -265,6 +283,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         p.trace[0] = (unsigned long long)c_wait; p.trace[1] = (unsigned long long)c_x; p.trace[2] = (unsigned long long)c_deq;
         p.trace[3] = (unsigned long long)c_land; p.trace[4] = (unsigned long long)c_sync; p.trace[5] = (unsigned long long)c_mma;
         p.trace[6] = (unsigned long long)kt_total;
+        p.trace[8] = (unsigned long long)(clock64() - t_entry);  // end of this thread's loop
     }
     }  // dequantising warps
 
@@ -298,12 +317,14 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) p.trace[9] = (unsigned long long)(clock64() - t_entry);  // own epilogue done
     __syncthreads();
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) p.trace[10] = (unsigned long long)(clock64() - t_entry);
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((unsigned)BN) : "memory");
 }
 
 template <int BN, int STAGES>
-constexpr size_t tc_smem_bytes() { return (size_t)2 * kTcRows * 128 + (size_t)STAGES * BN * 128 + 1024; }
+constexpr size_t tc_smem_bytes() { return (size_t)2 * kTcRows * 128 + (size_t)STAGES * (BN * 128 + kTcRows * 32) + 1024; }
 
 // cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link against the driver
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -340,14 +361,30 @@ int tc_init_one() {
     SWLM_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<BN, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes<BN, STAGES>()));
     return SWLM_OK;
 }
+// packed weights W[n][k/2 bytes] as a 2-D byte tensor; box = 32 bytes (one group) x 128 rows, no swizzle
+int make_w_map(const uint32_t* w, int n, int k, CUtensorMap* map) {
+    TensorMapEncodeFn fn = tensor_map_encode_fn();
+    if (!fn) { set_error("qgemm (tcgen05): cuTensorMapEncodeTiled is not available"); return SWLM_ERR_CUDA; }
+    const cuuint64_t dims[2] = {(cuuint64_t)k / 2, (cuuint64_t)n};
+    const cuuint64_t strides[1] = {(cuuint64_t)k / 2};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kTcRows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(w), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("qgemm (tcgen05): cuTensorMapEncodeTiled failed for the weights (%d)", (int)r); return SWLM_ERR_CUDA; }
+    return SWLM_OK;
+}
+
 template <int BN, int STAGES>
 int tc_launch_one(const QGemmTcParams& p, bool f16, cudaStream_t s) {
-    CUtensorMap xmap;
+    CUtensorMap xmap, wmap;
     int rc = make_x_map(p.x, p.x_stride, p.m, p.k, BN, &xmap);
     if (rc) return rc;
+    if ((rc = make_w_map(p.w, p.n, p.k, &wmap))) return rc;
     const dim3 grid((unsigned)((p.n + kTcRows - 1) / kTcRows), (unsigned)((p.m + BN - 1) / BN), 1);
-    const cudaError_t e = f16 ? launch_k(qgemm_tc_kernel<BN, STAGES, true>, grid, dim3(kTcAllThreads), tc_smem_bytes<BN, STAGES>(), s, p, xmap)
-                              : launch_k(qgemm_tc_kernel<BN, STAGES, false>, grid, dim3(kTcAllThreads), tc_smem_bytes<BN, STAGES>(), s, p, xmap);
+    const cudaError_t e = f16 ? launch_k(qgemm_tc_kernel<BN, STAGES, true>, grid, dim3(kTcAllThreads), tc_smem_bytes<BN, STAGES>(), s, p, xmap, wmap)
+                              : launch_k(qgemm_tc_kernel<BN, STAGES, false>, grid, dim3(kTcAllThreads), tc_smem_bytes<BN, STAGES>(), s, p, xmap, wmap);
     if (e != cudaSuccess) return cuda_fail(e, "qgemm_tc launch");
     return SWLM_OK;
 }
