@@ -15,6 +15,7 @@
 //   * the current token is not read back from the cache: the merging CTA adds its term in fp32 from
 //     the unrounded rotated k and v, exactly as the reference does (:866-868, :905-907), while the
 //     bf16-rounded copy is appended to the cache for later steps (:761-805).
+#include <cstdlib>
 #include <cmath>
 
 #include "swlm_internal.h"
@@ -41,6 +42,7 @@ struct AttnParams {
     const int32_t* position;   // decode: device scalar; plain: nullptr
     int ctx_len;               // plain: number of cached tokens
     int pos_base;              // prompt ingestion: position of the chunk's first token
+    int chunk_tokens;          // prompt ingestion: tokens in the chunk
     __nv_bfloat16* out; int out_stride;
     float* part_o;   // [m][heads][splits][HD]
     float* part_ml;  // [m][heads][splits][2]
@@ -529,7 +531,210 @@ int launch_both(const AttnParams& p, int m, int hd, cudaStream_t s) {
 
 }  // namespace
 
-int attn_init() { return SWLM_OK; }
+// ---- prompt ingestion: tiled causal attention over the cache ----------------------------------------------
+// The chunk's k/v rows are already in the cache (rope_append_kernel); token b of the chunk attends rows
+// 0..pos_base+b. One CTA serves 64 query rows = (64 / G) consecutive tokens x the G query heads of one KV head, so
+// a K/V tile is read once per 64 rows instead of once per token (the reference's prefill attention walks the
+// context once per query head and position, Generator/MetalSourceGenerator+Attention.swift:551-930). K/V tiles of
+// 64 rows go through shared memory (cp.async, two stages, ldmatrix); arithmetic as in the decode kernel: q is
+// rotated in fp32 and fed as a bf16 hi + lo pair in rows g / g + 8 of the A fragment, as are the probabilities;
+// scores, softmax and the output accumulate in fp32.
+constexpr int kPfWarps = 8, kPfThreads = kPfWarps * 32, kPfRows = kPfWarps * 8, kPfTile = 64;
+
+template <int HD>
+constexpr size_t attn_prefill_smem() {
+    return (size_t)4 * kPfTile * (HD * 2 + 16) + (size_t)kPfRows * (HD + 2) * 4 + (size_t)kPfRows * HD * 4;
+}
+
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const AttnParams p) {
+    constexpr int PK = HD * 2 + 16;       // bytes per K/V row in shared memory: 8 rows of an ldmatrix hit 8 different 16-byte bank groups
+    constexpr int TILE_BYTES = kPfTile * PK;
+    constexpr int QP = HD + 2;            // floats per q row
+    constexpr int KS = HD / 16;           // k-steps of q . K^T
+    extern __shared__ __align__(16) unsigned char pf_smem[];
+    unsigned char* kv_sm = pf_smem;                                          // [2 stages][K tile | V tile]
+    float* q_sm = reinterpret_cast<float*>(pf_smem + 4 * TILE_BYTES);        // [64 rows][QP]
+    float* cs_sm = q_sm + kPfRows * QP;                                      // [tokens][HD / 2] cos, then the same for sin
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int G = p.heads / p.kv_heads;   // 1, 2, 4 or 8
+    const int TQ = kPfRows / G;           // tokens per CTA
+    const int qt = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;   // the longest rows first
+    const int tok0 = qt * TQ;
+    const int n_tok = min(TQ, p.chunk_tokens - tok0);
+    const int pairs = p.rope_dim >> 1;
+    float* sn_sm = cs_sm + TQ * (HD / 2);
+    pdl_wait();
+
+    const __nv_bfloat16* kbase = p.kcache + (size_t)kvh * p.cache_head_stride;
+    const __nv_bfloat16* vbase = p.vcache + (size_t)kvh * p.cache_head_stride;
+    const int last_row = p.pos_base + p.chunk_tokens - 1;              // last cache row that holds data
+    const int n_tiles = (p.pos_base + tok0 + n_tok - 1) / kPfTile + 1; // tiles the CTA's last token attends
+    auto load_tile = [&](int tile, int stage) {
+        unsigned char* kd = kv_sm + (size_t)stage * 2 * TILE_BYTES;
+        unsigned char* vd = kd + TILE_BYTES;
+        constexpr int CPR = HD / 8;  // 16-byte chunks per row
+        for (int idx = tid; idx < kPfTile * CPR; idx += kPfThreads) {
+            const int r = idx / CPR, c = idx - r * CPR;
+            const size_t src = (size_t)min(tile * kPfTile + r, last_row) * HD + c * 8;
+            const unsigned kdst = (unsigned)__cvta_generic_to_shared(kd + r * PK + c * 16);
+            const unsigned vdst = (unsigned)__cvta_generic_to_shared(vd + r * PK + c * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst), "l"(kbase + src) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst), "l"(vbase + src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile(0, 0);
+
+    // ---- prologue: q rows (row = token * G + head) to shared memory as floats, rotation table, rotation ----
+    for (int idx = tid; idx < kPfRows * (HD / 8); idx += kPfThreads) {
+        const int rr = idx / (HD / 8), c = idx - rr * (HD / 8);
+        const int tl = rr / G, head = rr - tl * G;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tl < n_tok) v = *reinterpret_cast<const uint4*>(p.q + (size_t)(tok0 + tl) * p.q_stride + (size_t)(kvh * G + head) * HD + c * 8);
+        const unsigned u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<float2*>(q_sm + rr * QP + c * 8 + 2 * j) = make_float2(__uint_as_float(u[j] << 16), __uint_as_float(u[j] & 0xffff0000u));
+    }
+    for (int idx = tid; idx < n_tok * pairs; idx += kPfThreads) {
+        const int tl = idx / pairs, i = idx - tl * pairs;
+        float sv_, cv_;
+        sincosf((float)(p.pos_base + tok0 + tl) * p.inv_freq[i], &sv_, &cv_);
+        cs_sm[tl * (HD / 2) + i] = cv_; sn_sm[tl * (HD / 2) + i] = sv_;
+    }
+    __syncthreads();
+    // rotate-half RoPE (Generator/MetalSourceGenerator+Attention.swift:596-617): pairs (i, i + rope_dim/2)
+    for (int idx = tid; idx < n_tok * G * pairs; idx += kPfThreads) {
+        const int rr = idx / pairs, i = idx - rr * pairs;
+        const int tl = rr / G;
+        const float c = cs_sm[tl * (HD / 2) + i], sn = sn_sm[tl * (HD / 2) + i];
+        const float lo = q_sm[rr * QP + i], hi = q_sm[rr * QP + i + pairs];
+        q_sm[rr * QP + i] = lo * c - hi * sn;
+        q_sm[rr * QP + i + pairs] = lo * sn + hi * c;
+    }
+    __syncthreads();
+    // A fragments of this warp's 8 rows: rows g carry the high bf16 parts, rows g + 8 the low parts
+    unsigned qa[KS][4];
+    {
+        const float* qrow = q_sm + (warp * 8 + g) * QP;
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk) {
+            const float2 x0 = *reinterpret_cast<const float2*>(qrow + 16 * kk + 2 * t);
+            const float2 x1 = *reinterpret_cast<const float2*>(qrow + 16 * kk + 8 + 2 * t);
+            const float h0 = __bfloat162float(__float2bfloat16_rn(x0.x)), h1 = __bfloat162float(__float2bfloat16_rn(x0.y));
+            const float h2 = __bfloat162float(__float2bfloat16_rn(x1.x)), h3 = __bfloat162float(__float2bfloat16_rn(x1.y));
+            qa[kk][0] = pack_bf16(h0, h1); qa[kk][1] = pack_bf16(x0.x - h0, x0.y - h1);
+            qa[kk][2] = pack_bf16(h2, h3); qa[kk][3] = pack_bf16(x1.x - h2, x1.y - h3);
+        }
+    }
+    // position of this lane's row; rows past the chunk's end repeat the last token (their output is dropped)
+    const int row_tl = min((warp * 8 + g) / G, n_tok - 1);
+    const int pos_row = p.pos_base + tok0 + row_tl;
+    const int warp_last_pos = p.pos_base + tok0 + min((warp * 8 + 7) / G, n_tok - 1);
+
+    float m_run = -INFINITY, l_run = 0.f;
+    float oacc[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
+
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        if (tile + 1 < n_tiles) load_tile(tile + 1, (tile + 1) & 1);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        if (tile * kPfTile <= warp_last_pos) {
+            const unsigned kb = (unsigned)__cvta_generic_to_shared(kv_sm + (size_t)(tile & 1) * 2 * TILE_BYTES);
+            const unsigned vb = kb + TILE_BYTES;
+            // S = q . K^T: 8 key tiles of 8
+            float sacc[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < KS / 2; ++k2) {
+                    unsigned b[4];
+                    ldsm_x4(b, kb + (unsigned)((8 * j + (lane & 7)) * PK + (32 * k2 + 8 * (lane >> 3)) * 2));
+                    mma_bf16(sacc[j], qa[2 * k2][0], qa[2 * k2][1], qa[2 * k2][2], qa[2 * k2][3], b[0], b[1]);
+                    mma_bf16(sacc[j], qa[2 * k2 + 1][0], qa[2 * k2 + 1][1], qa[2 * k2 + 1][2], qa[2 * k2 + 1][3], b[2], b[3]);
+                }
+            }
+            // causal mask, online softmax in the log2 domain; row g lives in the four lanes t = 0..3
+            float rmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = tile * kPfTile + 8 * j + 2 * t + e;
+                    const float v = key <= pos_row ? (sacc[j][e] + sacc[j][2 + e]) * p.scale_log2 : -INFINITY;
+                    sacc[j][e] = v;
+                    rmax = fmaxf(rmax, v);
+                }
+            rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+            rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+            const float m_new = fmaxf(m_run, rmax);   // finite: key 0 is never masked
+            const float corr = exp2f(m_run - m_new);
+            float psum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) { sacc[j][e] = exp2f(sacc[j][e] - m_new); psum += sacc[j][e]; }
+            l_run = l_run * corr + psum;
+            m_run = m_new;
+            if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+                for (int j = 0; j < HD / 8; ++j) { oacc[j][0] *= corr; oacc[j][1] *= corr; oacc[j][2] *= corr; oacc[j][3] *= corr; }
+            }
+            // O += P . V over 4 steps of 16 keys; P as hi + lo in rows g / g + 8
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                unsigned pa[4];
+                {
+                    const float a0 = sacc[2 * kk][0], a1 = sacc[2 * kk][1], c0 = sacc[2 * kk + 1][0], c1 = sacc[2 * kk + 1][1];
+                    const float ah0 = __bfloat162float(__float2bfloat16_rn(a0)), ah1 = __bfloat162float(__float2bfloat16_rn(a1));
+                    const float ch0 = __bfloat162float(__float2bfloat16_rn(c0)), ch1 = __bfloat162float(__float2bfloat16_rn(c1));
+                    pa[0] = pack_bf16(ah0, ah1); pa[1] = pack_bf16(a0 - ah0, a1 - ah1);
+                    pa[2] = pack_bf16(ch0, ch1); pa[3] = pack_bf16(c0 - ch0, c1 - ch1);
+                }
+#pragma unroll
+                for (int jj = 0; jj < HD / 16; ++jj) {
+                    unsigned b[4];
+                    ldsm_x4_trans(b, vb + (unsigned)((16 * kk + (lane & 7) + 8 * ((lane >> 3) & 1)) * PK + (16 * jj + 8 * (lane >> 4)) * 2));
+                    mma_bf16(oacc[2 * jj], pa[0], pa[1], pa[2], pa[3], b[0], b[1]);
+                    mma_bf16(oacc[2 * jj + 1], pa[0], pa[1], pa[2], pa[3], b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();  // the stage is rewritten by the next iteration's copies
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    const int rr = warp * 8 + g;
+    const int tl = rr / G, head = rr - tl * G;
+    if (tl < n_tok) {
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        __nv_bfloat16* orow = p.out + (size_t)(tok0 + tl) * p.out_stride + (size_t)(kvh * G + head) * HD;
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j)
+            *reinterpret_cast<unsigned*>(orow + 8 * j + 2 * t) = pack_bf16((oacc[j][0] + oacc[j][2]) * inv, (oacc[j][1] + oacc[j][3]) * inv);
+    }
+}
+
+int attn_init() {
+    SWLM_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_prefill_smem<128>()));
+    SWLM_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_prefill_smem<64>()));
+    return SWLM_OK;
+}
 
 int attn_pick_splits(int m, int kv_heads, int max_ctx) {
     int s = 300 / (m * kv_heads);
@@ -581,8 +786,20 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
         // prompt ingestion: rows of q/k/v are consecutive tokens of sequence 0
         if (a.head_dim > 128) { set_error("attention: head_dim %d not supported", a.head_dim); return SWLM_ERR_UNSUPPORTED; }
         p.pos_base = a.pos_base;
+        p.chunk_tokens = a.m;
         cudaError_t e = launch_k(rope_append_kernel, dim3(a.m, a.kv_heads, 1), dim3(128), 0, s, p, a.head_dim);
         if (e != cudaSuccess) return cuda_fail(e, "rope_append launch");
+        // tiled causal kernel when the GQA group fills the 8 rows of a warp evenly; SWLM_PREFILL_ATTN=0 keeps the
+        // per-token kernel (for comparisons)
+        static const bool tiled = [] { const char* v = getenv("SWLM_PREFILL_ATTN"); return !(v && v[0] == '0'); }();
+        const int G = a.heads / a.kv_heads;
+        if (tiled && (G == 1 || G == 2 || G == 4 || G == 8) && (a.head_dim == 64 || a.head_dim == 128) && a.rope_dim <= a.head_dim) {
+            const dim3 grid((unsigned)((a.m + kPfRows / G - 1) / (kPfRows / G)), (unsigned)a.kv_heads, 1);
+            e = a.head_dim == 128 ? launch_k(attn_prefill_kernel<128>, grid, dim3(kPfThreads), attn_prefill_smem<128>(), s, p)
+                                  : launch_k(attn_prefill_kernel<64>, grid, dim3(kPfThreads), attn_prefill_smem<64>(), s, p);
+            if (e != cudaSuccess) return cuda_fail(e, "attn_prefill launch");
+            return SWLM_OK;
+        }
         return launch_both<2>(p, a.m, a.head_dim, s);
     }
     return launch_both<1>(p, a.m, a.head_dim, s);

@@ -177,8 +177,15 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         // ---- MMA warp: one thread issues the four MMAs of a group as soon as its tiles are in place; the
         // dequantising warps are already busy with the next group by then -----------------------------------
         if (lane == 0) {
+            const bool mtiming = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+            long long m_ready = 0, m_full = 0;
             for (int kt = 0; kt < kt_total; ++kt) {
-                if (!mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1)) || !mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1))) {
+                const long long m_a = mtiming ? clock64() : 0;
+                const bool ok_r = mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1));
+                const long long m_b = mtiming ? clock64() : 0;
+                const bool ok_f = mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1));
+                if (mtiming) { m_ready += m_b - m_a; m_full += clock64() - m_b; }
+                if (!ok_r || !ok_f) {
                     atomicExch(p.status, 2); failed = 1; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -189,6 +196,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
                 umma_commit(&empty_bar[kt % SB]);
                 if (kt == kt_total - 1) umma_commit(&done_bar);
             }
+            if (mtiming) { p.trace[11] = (unsigned long long)m_ready; p.trace[12] = (unsigned long long)m_full; }
         }
         __syncwarp();
     } else if (warp == kTcThreads / 32 + 1) {

@@ -138,6 +138,29 @@ def test_chunked_prompt_ingestion_matches_oracle_and_token_by_token(pkg, oracle,
     gm.close(); store.close()
 
 
+def test_chunked_prompt_ingestion_head_dim_128_over_several_key_tiles(pkg, oracle):
+    """Head dimension 128, one KV head for four query heads, a 200-token prompt in chunks of 128 and 71: the tiled
+    causal attention walks up to four 64-row key tiles, the second chunk starts at a position that is not zero."""
+    cfg = pkg.ModelConfig("llama", hidden=512, intermediate=1536, layers=2, heads=4, kv_heads=1, head_dim=128,
+                          vocab=4096, norm_eps=1e-5, rope_theta=500000.0, max_seq=256, max_batch=1)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    gm.set_prefill_chunk(128)
+    before = gm.launches
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=200, steps=16)
+    assert len(mism) <= 2, mism
+    assert gm.launches - before < 60 * gm.launches_per_step
+    for which in (0, 1):
+        for layer in range(cfg.kv_layer_count):
+            ref = pkg.bf16_to_f32(om.read_kv(which, layer, 0, 0, 200))
+            got = pkg.bf16_to_f32(gm.read_kv(which, layer, 0, 0, 200))
+            row_err = np.linalg.norm(got - ref, axis=1) / np.maximum(np.linalg.norm(ref, axis=1), 1e-6)
+            what = f"cache {which} layer {layer}: worst row {int(row_err.argmax())} rel L2 {row_err.max():.4f}"
+            assert np.median(row_err) <= 1e-2, what
+            assert int((row_err > 5e-2).sum()) <= 4, what
+            assert np.linalg.norm(got - ref) <= 6e-2 * np.linalg.norm(ref), what
+    gm.close(); store.close()
+
+
 def test_objects_may_be_destroyed_in_any_order(pkg, oracle):
     """Wrappers with garbage collection release context, plan and state in no particular order; a context
     destroyed first must stay valid until its plan and state are gone, and leave no CUDA error behind."""
