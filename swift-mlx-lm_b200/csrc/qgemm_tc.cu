@@ -8,7 +8,7 @@
 //
 // One CTA computes a 128 (weight rows) x BN (tokens) tile of Y^T:
 //   * the packed weights of a group (128 rows x 32 bytes) arrive in shared memory by TMA, together with the
-//     activation tile; two threads own one weight row: per 64-column group each reads 16 packed bytes from
+//     activation tile; four threads own one weight row: per 64-column group each reads 8 packed bytes from
 //     shared memory, takes the row's (scale, zero) from registers (fetched eight groups at a time), turns
 //     nibble pairs into bf16 with LOP3 (128+q), subtracts 128 and applies scale and zero
 //     with one bf16x2 FMA each — exactly bf16(scale*q + zero) — and stores the 128-byte row into shared
@@ -28,7 +28,7 @@
 namespace swlm {
 namespace {
 
-constexpr int kTcThreads = 256;          // dequantising threads
+constexpr int kTcThreads = 512;          // dequantising threads
 constexpr int kTcAllThreads = kTcThreads + 64;  // + the MMA warp and the activation (TMA) warp
 constexpr int kTcRows = 128;            // weight rows per CTA = UMMA M
 constexpr int kTcBK = 64;               // one quantisation group per pipeline stage
@@ -99,8 +99,9 @@ __device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7
 
 // F16SB: scale and zero are fp16 (tensors uploaded as STAF blocks) instead of bf16 (MLX tensors).
 //
-// 256 threads: thread (r = tid >> 1, h = tid & 1) dequantises columns 32h..32h+31 of weight row r in every
-// group: one 16-byte read from shared memory and about 90 instructions. The packed weights and the activation
+// 512 threads: thread (r = tid >> 2, h = tid & 3) dequantises columns 16h..16h+15 of weight row r in every
+// group: one 8-byte read from shared memory and about 50 instructions (the tensor core needs ~500 clocks per group;
+// with 16 warps the dequantisation of the next group hides behind it, with 8 it did not: 580 clocks). The packed weights and the activation
 // tiles share a ring of SB stages that the tenth warp fills by TMA (the dequantised weight tiles need only
 // SA = 2); scales and zeros are read straight from global memory, eight groups per 16-byte load. The ninth warp issues the MMAs:
 // the 256 threads arrive on ready_bar[kt % 2] once their part of group kt is in shared memory and go on with
@@ -126,7 +127,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const long long t_entry = clock64();
-    const int r = (tid >> 1) & 127, half = tid & 1;
+    const int r = (tid >> 2) & 127, half = tid & 3;   // half: which 16 of the group's 64 columns
     const int row0 = blockIdx.x * kTcRows, tok0 = blockIdx.y * BN;
     const int kt_total = p.k / kTcBK;
     unsigned char* const b_ring = smem + SA * A_BYTES;
@@ -240,8 +241,8 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         const long long t_c = timing ? clock64() : 0;
         // ---- weights: 32 nibbles of this thread's row -> 32 bf16 = bf16(scale * q + zero) -----------------
         {
-            struct { uint4 w; unsigned s, z; } v;
-            v.w = *reinterpret_cast<const uint4*>(b_ring + (kt % SB) * STAGE_BYTES + B_BYTES + r * 32 + half * 16);
+            struct { uint2 w; unsigned s, z; } v;
+            v.w = *reinterpret_cast<const uint2*>(b_ring + (kt % SB) * STAGE_BYTES + B_BYTES + r * 32 + half * 8);
             if ((kt & 7) == 0 && kt > 0) { s_cur = s_nxt; z_cur = z_nxt; s_nxt = load8(srow, kt + 8); z_nxt = load8(zrow, kt + 8); }
             v.s = pick16(s_cur, kt & 7); v.z = pick16(z_cur, kt & 7);
             const unsigned s2 = v.s | (v.s << 16), z2 = v.z | (v.z << 16);
@@ -251,9 +252,9 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
             const float zf = F16SB ? __half2float(__ushort_as_half((unsigned short)v.z)) : 0.f;
             const unsigned c128 = 0x43004300u;
             const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162*>(&c128);
-            const unsigned words[4] = {v.w.x, v.w.y, v.w.z, v.w.w};
+            const unsigned words[2] = {v.w.x, v.w.y};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 // a word holds 8 consecutive columns, nibble j = column j; pairs (j, j+4) come out of one LOP3
                 const unsigned wv = words[c];
                 unsigned o[4];
@@ -273,7 +274,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
                 // reorder the pairs (j, j+4) into consecutive columns 0..7
                 const uint4 out = make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),
                                              __byte_perm(o[0], o[1], 0x7632), __byte_perm(o[2], o[3], 0x7632));
-                *reinterpret_cast<uint4*>(a_tile + swz(r, half * 4 + c)) = out;
+                *reinterpret_cast<uint4*>(a_tile + swz(r, half * 2 + c)) = out;
             }
         }
         const long long t_d = timing ? clock64() : 0;
@@ -296,16 +297,16 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     }  // dequantising warps
 
     // ---- epilogue: TMEM -> registers -> bf16 -> Y[token][row] --------------------------------------------
-    // a warp reads the 32 accumulator lanes of its quarter (warp & 3); warps 0-3 take the first half of the
-    // token columns, warps 4-7 the second
+    // a warp reads the 32 accumulator lanes of its quarter (warp & 3); warps 4i..4i+3 take the i-th quarter of
+    // the token columns
     bool ok = !failed && warp < kTcThreads / 32;
     if (ok && !mbar_wait(&done_bar, 0u)) { atomicExch(p.status, 1); ok = false; }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
         const int erow = row0 + (warp & 3) * 32 + lane;
-        const int cbase = (warp >> 2) * (BN / 2);
+        const int cbase = (warp >> 2) * (BN / 4);
 #pragma unroll 1
-        for (int c0 = cbase; c0 < cbase + BN / 2; c0 += 16) {
+        for (int c0 = cbase; c0 < cbase + BN / 4; c0 += 16) {
             if (tok0 + c0 >= p.m) break;  // uniform across the warp
             unsigned v[16];
             const unsigned taddr = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)c0;
