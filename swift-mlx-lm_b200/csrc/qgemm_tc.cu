@@ -6,21 +6,24 @@
 // (`dequant_q4_g64_bf16`, +Quantized.swift:361-416: W_bf16 = bf16(scale*q + zero), then a dense product with
 // fp32 accumulation), except that the bf16 weights never exist in global memory.
 //
-// One CTA computes a 128 (weight rows) x BN (tokens) tile of Y^T:
-//   * the packed weights of a group (128 rows x 32 bytes) arrive in shared memory by TMA, together with the
-//     activation tile; four threads own one weight row: per 64-column group each reads 8 packed bytes from
-//     shared memory, takes the row's (scale, zero) from registers (fetched eight groups at a time), turns
-//     nibble pairs into bf16 with LOP3 (128+q), subtracts 128 and applies scale and zero
-//     with one bf16x2 FMA each — exactly bf16(scale*q + zero) — and stores the 128-byte row into shared
-//     memory in the K-major, 128-byte-swizzled layout tcgen05.mma reads;
-//   * the activation tile (BN tokens x 64 columns, bf16) arrives in the same layout by TMA: one thread of a
-//     producer warp issues one cp.async.bulk.tensor per group (128-byte swizzle, rows past the last token
-//     filled with zeros), several groups ahead, and an mbarrier counts the bytes;
-//   * one thread of another warp issues four tcgen05.mma (M=128, N=BN, K=16, kind::f16, bf16 x bf16 -> fp32) per group into
-//     a TMEM accumulator; tcgen05.commit signals an mbarrier when the stage may be overwritten;
+// One CTA (18 warps) computes a 128 (weight rows) x BN (tokens) tile of Y^T:
+//   * a TMA warp (one thread) keeps a ring of stages full, two cp.async.bulk.tensor.2d per 64-column group
+//     (no multicast): the packed weights of the group (128 rows x 32 bytes) and the activation tile (BN tokens
+//     x 64 columns of bf16, 128-byte swizzle, rows past the last token filled with zeros); an mbarrier per
+//     stage counts the bytes;
+//   * 16 warps dequantise: four threads own one weight row, per group each reads 8 packed bytes from shared
+//     memory, takes the row's (scale, zero) from registers (fetched eight groups at a time), turns nibble
+//     pairs into bf16 with LOP3 (128+q), subtracts 128 and applies scale and zero with one bf16x2 FMA each
+//     — exactly bf16(scale*q + zero) — and stores its 16 values into the row's lane of tensor memory
+//     (tcgen05.st): the A operand of the MMA is read from TMEM, so the dequantised weights never cross shared
+//     memory and four such tiles (32 columns each) fit beside the accumulator;
+//   * an MMA warp (one thread) issues four tcgen05.mma (M=128, N=BN, K=16, kind::f16, A from TMEM, B through
+//     a shared-memory descriptor, fp32 accumulator in TMEM) per group as soon as the group's weights and
+//     activations are in place; tcgen05.commit signals an mbarrier when the stage and the weight tile may
+//     be overwritten;
 //   * the epilogue reads the accumulator with tcgen05.ld, rounds to bf16 and stores Y[token][row].
-// Every mbarrier wait is bounded: on expiry an error word is set, the CTA stops issuing, frees its TMEM
-// and returns.
+// Every mbarrier wait is bounded: on expiry an error word is set, the CTA stops issuing, waits (bounded) for
+// the copies it has in flight, frees its TMEM and returns.
 #include <cstdlib>
 #include <cuda.h>
 #include "swlm_internal.h"
@@ -44,7 +47,6 @@ struct QGemmTcParams {
     __nv_bfloat16* y;         // [m][y_stride]
     int y_stride;
     int* status;              // set non-zero when a bounded wait expired
-    unsigned long long* trace; // SWLM_TRACE=1: clocks CTA 0 spent per phase, summed over its groups
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -83,67 +85,61 @@ __host__ __device__ constexpr unsigned umma_idesc(int bn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(kTcRows >> 4) << 24);
 }
 
-__device__ __forceinline__ void umma_f16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc, unsigned accumulate) {
+// D[tmem] (+)= A[tmem] x B[shared memory]: the A operand (128 rows x 16 bf16 = 8 columns of 32 bits) is read from
+// tensor memory, where the dequantising threads put it, so it never crosses shared memory
+__device__ __forceinline__ void umma_f16_ta(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned idesc, unsigned accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// byte offset of 16-byte chunk c (0..7) of row r inside a K-major tile with 128-byte rows and 128B swizzle
-__device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
-
 // F16SB: scale and zero are fp16 (tensors uploaded as STAF blocks) instead of bf16 (MLX tensors).
 //
-// 512 threads: thread (r = tid >> 2, h = tid & 3) dequantises columns 16h..16h+15 of weight row r in every
-// group: one 8-byte read from shared memory and about 50 instructions (the tensor core needs ~500 clocks per group;
-// with 16 warps the dequantisation of the next group hides behind it, with 8 it did not: 580 clocks). The packed weights and the activation
-// tiles share a ring of SB stages that the tenth warp fills by TMA (the dequantised weight tiles need only
-// SA = 2); scales and zeros are read straight from global memory, eight groups per 16-byte load. The ninth warp issues the MMAs:
-// the 256 threads arrive on ready_bar[kt % 2] once their part of group kt is in shared memory and go on with
-// group kt + 1 while the tensor core works; full_bar[kt % SB] completes when the group's activations have landed;
-// tcgen05.commit signals, per group, that its MMAs are done and its stages may be overwritten.
+// Dequantising thread (warp w, lane l): weight row 32 (w & 3) + l (= its TMEM lane), columns 16 (w >> 2) ..
+// + 15 of every group. ready_bar[kt % SA] collects the 512 arrivals of group kt; full_bar[kt % SB] completes
+// when the group's stage has landed; empty_bar[kt % SB] when its MMAs are done. With SA = 2 the dequantisation
+// of group kt had to wait for the MMAs of group kt - 2 (measured: 200 clocks per group); SA = 4 removes that.
 template <int BN, int STAGES, bool F16SB>
 __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
-    constexpr int SA = 2, SB = STAGES;
+    constexpr int SA = BN == 64 ? 2 : 4, SB = STAGES;   // dequantised weight tiles in flight
+    constexpr unsigned kTmemCols = BN == 256 ? 512 : BN == 128 ? 256 : 128;   // accumulator (BN) + SA weight tiles of 32, power of two
+    constexpr unsigned kACol0 = BN;                                            // first column of the weight tiles
     static_assert(SB >= 3, "the activation ring must be deeper than the weight ring");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment for the swizzle atoms
     unsigned char* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
-    constexpr int A_BYTES = kTcRows * 128;
     constexpr int B_BYTES = BN * 128;
     constexpr int W_BYTES = kTcRows * 32;        // packed weights of one group
     constexpr int STAGE_BYTES = B_BYTES + W_BYTES;
     __shared__ __align__(8) unsigned long long empty_bar[STAGES];
     __shared__ __align__(8) unsigned long long full_bar[STAGES];    // the activation tile of a stage has landed
-    __shared__ __align__(8) unsigned long long ready_bar[2];   // a weight tile and its activation tile are in place
+    __shared__ __align__(8) unsigned long long ready_bar[4];   // a weight tile and its activation tile are in place
     __shared__ __align__(8) unsigned long long done_bar;
     __shared__ unsigned tmem_base_smem;
     __shared__ int failed;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const long long t_entry = clock64();
-    const int r = (tid >> 2) & 127, half = tid & 3;   // half: which 16 of the group's 64 columns
+    const int r = (warp & 3) * 32 + lane, half = (warp >> 2) & 3;   // TMEM lane = weight row; half: which 16 of the group's 64 columns
     const int row0 = blockIdx.x * kTcRows, tok0 = blockIdx.y * BN;
     const int kt_total = p.k / kTcBK;
-    unsigned char* const b_ring = smem + SA * A_BYTES;
+    unsigned char* const b_ring = smem;
 
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) { mbar_init(&empty_bar[s], 1); mbar_init(&full_bar[s], 1); }
-        mbar_init(&ready_bar[0], kTcThreads);
-        mbar_init(&ready_bar[1], kTcThreads);
+        for (int i = 0; i < 4; ++i) mbar_init(&ready_bar[i], kTcThreads);
         mbar_init(&done_bar, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         __syncwarp();  // the allocation is a warp-wide instruction: re-converge after the single-thread block
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_smem)), "r"((unsigned)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_smem)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -178,26 +174,18 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         // ---- MMA warp: one thread issues the four MMAs of a group as soon as its tiles are in place; the
         // dequantising warps are already busy with the next group by then -----------------------------------
         if (lane == 0) {
-            const bool mtiming = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
-            long long m_ready = 0, m_full = 0;
             for (int kt = 0; kt < kt_total; ++kt) {
-                const long long m_a = mtiming ? clock64() : 0;
-                const bool ok_r = mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1));
-                const long long m_b = mtiming ? clock64() : 0;
-                const bool ok_f = mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1));
-                if (mtiming) { m_ready += m_b - m_a; m_full += clock64() - m_b; }
-                if (!ok_r || !ok_f) {
+                if (!mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1)) || !mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1))) {
                     atomicExch(p.status, 2); failed = 1; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned a_addr = smem_u32(smem + (kt % SA) * A_BYTES), b_addr = smem_u32(b_ring + (kt % SB) * STAGE_BYTES);
+                const unsigned a_addr = tmem_d + kACol0 + (unsigned)(kt % SA) * 32u, b_addr = smem_u32(b_ring + (kt % SB) * STAGE_BYTES);
 #pragma unroll
-                for (int j = 0; j < kTcBK / 16; ++j)  // 16 bf16 = 32 bytes along K inside the 128-byte row
-                    umma_f16(tmem_d, umma_desc(a_addr + 32 * j), umma_desc(b_addr + 32 * j), idesc, (kt > 0 || j > 0) ? 1u : 0u);
+                for (int j = 0; j < kTcBK / 16; ++j)  // 16 bf16 = 8 columns of A, 32 bytes along K inside B's 128-byte row
+                    umma_f16_ta(tmem_d, a_addr + 8u * j, umma_desc(b_addr + 32 * j), idesc, (kt > 0 || j > 0) ? 1u : 0u);
                 umma_commit(&empty_bar[kt % SB]);
                 if (kt == kt_total - 1) umma_commit(&done_bar);
             }
-            if (mtiming) { p.trace[11] = (unsigned long long)m_ready; p.trace[12] = (unsigned long long)m_full; }
         }
         __syncwarp();
     } else if (warp == kTcThreads / 32 + 1) {
@@ -227,22 +215,25 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     } else {
     uint4 s_cur = load8(srow, 0), z_cur = load8(zrow, 0), s_nxt = load8(srow, 8), z_nxt = load8(zrow, 8);
 
-    long long c_wait = 0, c_x = 0, c_deq = 0, c_land = 0, c_sync = 0, c_mma = 0;  // tracing only
-    const bool timing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
-    if (timing) p.trace[7] = (unsigned long long)(clock64() - t_entry);  // set-up
+    // ring bookkeeping without divisions: stage and parity of this group's activations/packed weights, and of
+    // the group SA back whose MMAs free this group's weight tile
+    int fs = 0, es = 0, as = 0;
+    unsigned fpar = 0, epar = 0;
+    const unsigned char* const w_src = b_ring + B_BYTES + r * 32 + half * 8;
+    const unsigned a_dst = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + kACol0 + (unsigned)half * 8u;
     for (int kt = 0; kt < kt_total; ++kt) {
-        const long long t_a = timing ? clock64() : 0;
-        unsigned char* const a_tile = smem + (kt % SA) * A_BYTES;
-        // ---- the MMAs of group kt - 2 are done: its weight tile (this group's) may be overwritten ------------
-        if (kt >= 2 && !mbar_wait(&empty_bar[(kt - 2) % SB], (unsigned)(((kt - 2) / SB) & 1))) { atomicExch(p.status, 1); failed = 1; }
-        const long long t_b = timing ? clock64() : 0;
+        // ---- the MMAs of group kt - SA are done: its weight tile (this group's) may be overwritten -----------
+        if (kt >= SA) {
+            if (!mbar_wait(&empty_bar[es], epar)) { atomicExch(p.status, 1); failed = 1; }
+            if (++es == SB) { es = 0; epar ^= 1u; }
+        }
         // ---- this group's packed weights have landed (with its activations) ---------------------------------
-        if (!mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1))) { atomicExch(p.status, 1); failed = 1; }
-        const long long t_c = timing ? clock64() : 0;
+        if (!mbar_wait(&full_bar[fs], fpar)) { atomicExch(p.status, 1); failed = 1; }
         // ---- weights: 32 nibbles of this thread's row -> 32 bf16 = bf16(scale * q + zero) -----------------
         {
             struct { uint2 w; unsigned s, z; } v;
-            v.w = *reinterpret_cast<const uint2*>(b_ring + (kt % SB) * STAGE_BYTES + B_BYTES + r * 32 + half * 8);
+            v.w = *reinterpret_cast<const uint2*>(w_src + fs * STAGE_BYTES);
+            if (++fs == SB) { fs = 0; fpar ^= 1u; }
             if ((kt & 7) == 0 && kt > 0) { s_cur = s_nxt; z_cur = z_nxt; s_nxt = load8(srow, kt + 8); z_nxt = load8(zrow, kt + 8); }
             v.s = pick16(s_cur, kt & 7); v.z = pick16(z_cur, kt & 7);
             const unsigned s2 = v.s | (v.s << 16), z2 = v.z | (v.z << 16);
@@ -253,6 +244,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
             const unsigned c128 = 0x43004300u;
             const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162*>(&c128);
             const unsigned words[2] = {v.w.x, v.w.y};
+            unsigned a_regs[8];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 // a word holds 8 consecutive columns, nibble j = column j; pairs (j, j+4) come out of one LOP3
@@ -272,27 +264,20 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
                     o[j] = *reinterpret_cast<const unsigned*>(&q2);                            // lo = column j, hi = column j+4
                 }
                 // reorder the pairs (j, j+4) into consecutive columns 0..7
-                const uint4 out = make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),
-                                             __byte_perm(o[0], o[1], 0x7632), __byte_perm(o[2], o[3], 0x7632));
-                *reinterpret_cast<uint4*>(a_tile + swz(r, half * 2 + c)) = out;
+                a_regs[4 * c + 0] = __byte_perm(o[0], o[1], 0x5410); a_regs[4 * c + 1] = __byte_perm(o[2], o[3], 0x5410);
+                a_regs[4 * c + 2] = __byte_perm(o[0], o[1], 0x7632); a_regs[4 * c + 3] = __byte_perm(o[2], o[3], 0x7632);
             }
+            // 16 bf16 of this row -> 8 columns of the row's TMEM lane (a warp owns the 32 lanes of its quarter)
+            const unsigned taddr = a_dst + (unsigned)as * 32u;
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                         ::"r"(taddr), "r"(a_regs[0]), "r"(a_regs[1]), "r"(a_regs[2]), "r"(a_regs[3]), "r"(a_regs[4]), "r"(a_regs[5]), "r"(a_regs[6]), "r"(a_regs[7]) : "memory");
         }
-        const long long t_d = timing ? clock64() : 0;
-        const long long t_e = t_d;
-        // generic-proxy writes to shared memory -> visible to the tensor core (async proxy), then tell the MMA warp
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ready_bar[kt % SA])) : "memory");
-        const long long t_f = timing ? clock64() : 0;
+        // the stores to tensor memory are complete and ordered before the MMA warp's reads, then tell the MMA warp
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ready_bar[as])) : "memory");
+        if (++as == SA) as = 0;
         if (failed) break;
-        if (timing) {
-            c_wait += t_b - t_a; c_x += t_c - t_b; c_deq += t_d - t_c; c_land += t_e - t_d; c_sync += t_f - t_e; c_mma += clock64() - t_f;
-        }
-    }
-    if (timing) {
-        p.trace[0] = (unsigned long long)c_wait; p.trace[1] = (unsigned long long)c_x; p.trace[2] = (unsigned long long)c_deq;
-        p.trace[3] = (unsigned long long)c_land; p.trace[4] = (unsigned long long)c_sync; p.trace[5] = (unsigned long long)c_mma;
-        p.trace[6] = (unsigned long long)kt_total;
-        p.trace[8] = (unsigned long long)(clock64() - t_entry);  // end of this thread's loop
     }
     }  // dequantising warps
 
@@ -326,14 +311,12 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) p.trace[9] = (unsigned long long)(clock64() - t_entry);  // own epilogue done
     __syncthreads();
-    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) p.trace[10] = (unsigned long long)(clock64() - t_entry);
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((unsigned)BN) : "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTmemCols) : "memory");
 }
 
 template <int BN, int STAGES>
-constexpr size_t tc_smem_bytes() { return (size_t)2 * kTcRows * 128 + (size_t)STAGES * (BN * 128 + kTcRows * 32) + 1024; }
+constexpr size_t tc_smem_bytes() { return (size_t)STAGES * (BN * 128 + kTcRows * 32) + 1024; }
 
 // cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link against the driver
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -404,7 +387,7 @@ int qgemm_tc_init() {
     int rc;
     if ((rc = tc_init_one<64, 6>())) return rc;
     if ((rc = tc_init_one<128, 6>())) return rc;
-    if ((rc = tc_init_one<256, 5>())) return rc;
+    if ((rc = tc_init_one<256, 6>())) return rc;
     return SWLM_OK;
 }
 
@@ -417,12 +400,11 @@ int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride,
     QGemmTcParams p{};
     p.w = w.w; p.scales = w.scales; p.biases = w.biases; p.n = w.n; p.k = w.k;
     p.x = x; p.x_stride = x_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;
-    p.trace = qgemv_trace_slot(2, w.n, m, 10, 0);
     int rc;
     int bn = m > 128 ? 256 : m > 64 ? 128 : 64;
     static const int forced_bn = [] { const char* v = getenv("SWLM_TC_BN"); return v ? atoi(v) : 0; }();
     if (forced_bn == 64 || forced_bn == 128 || forced_bn == 256) bn = forced_bn;
-    if (bn == 256) rc = tc_launch_one<256, 5>(p, w.sb_f16, s);
+    if (bn == 256) rc = tc_launch_one<256, 6>(p, w.sb_f16, s);
     else if (bn == 128) rc = tc_launch_one<128, 6>(p, w.sb_f16, s);
     else rc = tc_launch_one<64, 6>(p, w.sb_f16, s);
     return rc;

@@ -1000,12 +1000,6 @@ void qgemv_trace_report() {
     for (int sl = 0; sl < used; ++sl) {
         const TraceSlot& t = g_trace_slot[sl];
         const unsigned long long* r = h.data() + (size_t)sl * kTraceCtas * 4;
-        if (t.epi == 10) {  // tensor-core prefill product: clocks of CTA 0's thread 0 per phase, per group
-            if (r[6]) fprintf(stderr, "%3d prefill product n=%d m=%d | clocks per group: wait for MMAs %.0f, wait for the stage %.0f, dequantise %.0f, fence + arrive %.0f, rest %.0f; MMA warp: wait for weights %.0f, for the stage %.0f | CTA 0 clocks: set-up %llu, loop end %llu, epilogue end %llu, all warps done %llu (%llu groups)\n",
-                              sl, t.row_tiles, t.kt4, (double)r[0] / r[6], (double)r[1] / r[6], (double)r[2] / r[6], (double)r[4] / r[6], (double)r[5] / r[6],
-                              (double)r[11] / r[6], (double)r[12] / r[6], r[7], r[8], r[9], r[10], r[6]);
-            continue;
-        }
         unsigned long long e0 = ~0ull, d0 = ~0ull, d1 = 0, x1 = 0, f0 = ~0ull, f1 = 0;
         double a = 0, b = 0, c = 0;
         int n = 0;
