@@ -737,6 +737,8 @@ int attn_init() {
 }
 
 int attn_pick_splits(int m, int kv_heads, int max_ctx) {
+    static const int forced = [] { const char* v = getenv("SWLM_ATTN_SPLITS"); return v ? atoi(v) : 0; }();
+    if (forced >= 1 && forced <= 64) return forced;
     int s = 300 / (m * kv_heads);
     const int cap = max_ctx / 128;
     if (s > 32) s = 32;
