@@ -116,6 +116,25 @@ __global__ void swiglu_kernel(int n, const __nv_bfloat16* gate, int g_stride, co
     out[(size_t)b * o_stride + i] = __float2bfloat16_rn(g * (1.0f / (1.0f + expf(-g))) * u);
 }
 
+// the same, eight elements per thread with 128-bit accesses (rows of many tokens in prompt ingestion)
+__global__ void swiglu8_kernel(int n8, const uint4* gate, int g_stride8, const uint4* up, int u_stride8, uint4* out, int o_stride8) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const uint4 gv = gate[(size_t)b * g_stride8 + i], uv = up[(size_t)b * u_stride8 + i];
+    const unsigned gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+    unsigned ow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
+        const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
+        const __nv_bfloat162 o = __floats2bfloat162_rn(g0 * (1.0f / (1.0f + expf(-g0))) * u0, g1 * (1.0f / (1.0f + expf(-g1))) * u1);
+        ow[j] = *reinterpret_cast<const unsigned*>(&o);
+    }
+    out[(size_t)b * o_stride8 + i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
 // conv_state_update_bf16 (Generator/MetalSourceGenerator+ConvAndState.swift:27-70): in = B|C|x,
 // state [kernel][dim] bf16 shifted by one, newest entry stored rounded but used unrounded.
 __global__ void conv_step_kernel(int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,
@@ -340,7 +359,13 @@ int launch_embed(int m, int dim, const int32_t* tokens, int vocab, const __nv_bf
 
 int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
                   __nv_bfloat16* out, int o_stride, cudaStream_t s) {
-    launch_k(swiglu_kernel, dim3((n + 255) / 256, m), 256, 0, s, n, gate, g_stride, up, u_stride, out, o_stride);
+    const bool vec = !((n | g_stride | u_stride | o_stride) & 7) &&
+                     !((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) & 15);
+    if (vec)
+        launch_k(swiglu8_kernel, dim3((n / 8 + 255) / 256, m), 256, 0, s, n / 8, reinterpret_cast<const uint4*>(gate), g_stride / 8,
+                 reinterpret_cast<const uint4*>(up), u_stride / 8, reinterpret_cast<uint4*>(out), o_stride / 8);
+    else
+        launch_k(swiglu_kernel, dim3((n + 255) / 256, m), 256, 0, s, n, gate, g_stride, up, u_stride, out, o_stride);
     return check_launch("swiglu launch");
 }
 
