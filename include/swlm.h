@@ -101,7 +101,7 @@ int swlm_state_set_stream(swlm_state* state, void* cuda_stream);
 /* Prompt ingestion (swlm_prefill) runs the prompt in chunks of up to `tokens` tokens with one activation row per
  * token and the products on the tensor cores, as the reference's sequence prefill does
  * (Execution/MetalPrefillExecutor.swift); the last prompt token always takes the decode path. 0 = one token at a
- * time through the decode graph. Default 512. Chunking applies to single-sequence, single-GPU states; others
+ * time through the decode graph. Default 2048. Chunking applies to single-sequence, single-GPU states; others
  * ingest token by token. */
 int swlm_state_set_prefill_chunk(swlm_state* state, int tokens);
 /* resetState() — MetalInferenceModel.swift:1911. */
