@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     __shared__ int failed;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int r = (warp & 3) * 32 + lane, half = (warp >> 2) & 3;   // TMEM lane = weight row; half: which 16 of the group's 64 columns
+    const int r = (warp & 3) * 32 + lane, part = (warp >> 2) & 3;   // TMEM lane = weight row; part: which 16 of the group's 64 columns
     const int row0 = blockIdx.x * kTcRows, tok0 = blockIdx.y * BN;
     const int kt_total = p.k / kTcBK;
     unsigned char* const b_ring = smem;
@@ -219,8 +219,8 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     // the group SA back whose MMAs free this group's weight tile
     int fs = 0, es = 0, as = 0;
     unsigned fpar = 0, epar = 0;
-    const unsigned char* const w_src = b_ring + B_BYTES + r * 32 + half * 8;
-    const unsigned a_dst = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + kACol0 + (unsigned)half * 8u;
+    const unsigned char* const w_src = b_ring + B_BYTES + r * 32 + part * 8;
+    const unsigned a_dst = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + kACol0 + (unsigned)part * 8u;
     for (int kt = 0; kt < kt_total; ++kt) {
         // ---- the MMAs of group kt - SA are done: its weight tile (this group's) may be overwritten -----------
         if (kt >= SA) {

@@ -24,7 +24,6 @@ constexpr int kTpMax = 8;
 
 struct TpLayout {
     int tp, batch, hidden;
-    __host__ __device__ size_t flags_ar(int par, int src) const { return ((size_t)par * kTpMax + src) * 4; }
     __host__ __device__ size_t flags_am(int par, int src) const { return 64 + ((size_t)par * kTpMax + src) * 4; }
     // partial sums: 8 bytes per element {fp32 bits, exchange number}
     __host__ __device__ size_t recv_ar(int par, int src, int b) const { return 256 + ((((size_t)par * tp + src) * batch + b) * hidden) * 8; }
