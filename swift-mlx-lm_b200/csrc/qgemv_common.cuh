@@ -66,10 +66,7 @@ __device__ __forceinline__ void fused_norm_run8(const QGemvParams& p, int k0, bo
         nw4 = __ldg(reinterpret_cast<const uint4*>(p.norm_w + k0));  // independent of everything below
         if (p.in_tp) {
             const int par = tp_epoch & 1;
-#pragma unroll 1
-            for (int src = 0; src < p.tp.tp; ++src) {
-                tp_add_tagged<4>(p.tp, p.tp.peer[p.tp.rank] + p.tp.lay.recv_ar(par, src, 0) + (size_t)k0 * 8, tp_epoch, h);
-            }
+            tp_add_tagged_all<4>(p.tp, p.tp.lay.recv_ar(par, 0, 0) + (size_t)k0 * 8, p.tp.lay.recv_ar(par, 1, 0) - p.tp.lay.recv_ar(par, 0, 0), tp_epoch, h);
 #pragma unroll
             for (int i = 0; i < 8; ++i) h[i] = __bfloat162float(__float2bfloat16_rn(h[i]));
         } else {

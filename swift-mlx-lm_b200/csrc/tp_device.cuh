@@ -70,27 +70,65 @@ __device__ __forceinline__ void tp_store_tagged(unsigned char* dst, float v, int
     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"((unsigned)epoch) : "memory");
 }
 
-// Read 2 * N2 consecutive elements of a partial-sum buffer in this rank's own memory and add them to acc,
-// polling (bounded) until all of them carry the number of this exchange. After a wait has expired once,
-// later exchanges do not wait again: the status word says so.
+// 2 * N2 consecutive elements of a partial-sum buffer in this rank's own memory: one attempt, ...
 template <int N2>
-__device__ __forceinline__ void tp_add_tagged(const TpParams& tp, const unsigned char* src, int epoch, float* acc) {
-    uint4 v[N2];
+__device__ __forceinline__ void tp_load_tagged(const unsigned char* src, uint4 (&v)[N2]) {
+#pragma unroll
+    for (int i = 0; i < N2; ++i)
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "l"(src + 16 * i) : "memory");
+}
+// ... the check that all of them carry the number of this exchange, ...
+template <int N2>
+__device__ __forceinline__ bool tp_all_tagged(const uint4 (&v)[N2], int epoch) {
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < N2; ++i) ok = ok && v[i].y == (unsigned)epoch && v[i].w == (unsigned)epoch;
+    return ok;
+}
+// ... and the bounded polling for those that did not on the first attempt. After a wait has expired once, later
+// exchanges do not wait again: the status word says so.
+template <int N2>
+__device__ __forceinline__ void tp_poll_tagged(const TpParams& tp, const unsigned char* src, int epoch, uint4 (&v)[N2]) {
     int spins = 0;
-    for (;;) {
-        bool ok = true;
-#pragma unroll
-        for (int i = 0; i < N2; ++i)
-            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "l"(src + 16 * i) : "memory");
-#pragma unroll
-        for (int i = 0; i < N2; ++i) ok = ok && v[i].y == (unsigned)epoch && v[i].w == (unsigned)epoch;
-        if (ok) break;
+    while (!tp_all_tagged(v, epoch)) {
         if (spins == 0 && *reinterpret_cast<volatile int*>(tp.status) != 0) break;
         if (++spins > kTpSpinLimit) { atomicExch(tp.status, 1); break; }
         __nanosleep(64);
+        tp_load_tagged(src, v);
     }
+}
+template <int N2>
+__device__ __forceinline__ void tp_accumulate(const uint4 (&v)[N2], float* acc) {
 #pragma unroll
     for (int i = 0; i < N2; ++i) { acc[2 * i] += __uint_as_float(v[i].x); acc[2 * i + 1] += __uint_as_float(v[i].z); }
+}
+// One source after the other.
+template <int N2>
+__device__ __forceinline__ void tp_add_tagged(const TpParams& tp, const unsigned char* src, int epoch, float* acc) {
+    uint4 v[N2];
+    tp_load_tagged(src, v);
+    tp_poll_tagged(tp, src, epoch, v);
+    tp_accumulate(v, acc);
+}
+// All sources of an exchange, two at a time: their loads travel together (one L2 round trip per two ranks
+// instead of one per rank; more at a time would spill the product kernels' registers); the sums are still
+// taken in rank order.
+template <int N2>
+__device__ __forceinline__ void tp_add_tagged_all(const TpParams& tp, size_t off0, size_t src_stride, int epoch, float* acc) {
+    const unsigned char* own = tp.peer[tp.rank];
+#pragma unroll 1
+    for (int s0 = 0; s0 < tp.tp; s0 += 2) {
+        uint4 v[2][N2];
+        const bool two = s0 + 1 < tp.tp;
+        tp_load_tagged(own + off0 + (size_t)s0 * src_stride, v[0]);
+        if (two) tp_load_tagged(own + off0 + (size_t)(s0 + 1) * src_stride, v[1]);
+        tp_poll_tagged(tp, own + off0 + (size_t)s0 * src_stride, epoch, v[0]);
+        tp_accumulate(v[0], acc);
+        if (two) {
+            tp_poll_tagged(tp, own + off0 + (size_t)(s0 + 1) * src_stride, epoch, v[1]);
+            tp_accumulate(v[1], acc);
+        }
+    }
 }
 #endif
 
