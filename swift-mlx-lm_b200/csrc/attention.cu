@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
             }
         __syncthreads();
     }
+    if (stamp0) p.trace[(n_ctas + 1) * 4 + 1] = attn_timer_ns();
     if (DECODE) {
         if (split == 0 && n_ctx < p.max_seq) {  // the rotated new k row, rounded, for later steps
             __nv_bfloat16* kw = p.kcache + (size_t)b * p.cache_seq_stride + (size_t)kvh * p.cache_head_stride + (size_t)n_ctx * HD;
@@ -228,6 +229,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         }
     }
 
+    if (stamp0) p.trace[(n_ctas + 1) * 4 + 2] = attn_timer_ns();
     // A fragments of the rotated q: lane (g, t) holds q[g][32*i + 8*t + 0..7]; hi + lo bf16 split
     unsigned qhi[NCH][4], qlo[NCH][4];
 #pragma unroll

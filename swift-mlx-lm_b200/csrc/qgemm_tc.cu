@@ -54,20 +54,29 @@ __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)_
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-// Bounded wait on phase parity; returns false when the limit was reached.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    for (int spin = 0; spin < kTcSpinLimit; ++spin) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
+// Bounded wait on phase parity; returns false when the limit was reached. The loop is two instructions per
+// attempt (try_wait suspends the warp for a while by itself): waiting warps share their scheduler with warps
+// that still dequantise.
+__device__ __forceinline__ bool mbar_wait_addr(unsigned addr, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "SWLM_TRY:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra SWLM_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %3;\n\t"
+        "@q bra SWLM_TRY;\n\t"
+        "SWLM_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done) : "r"(addr), "r"(parity), "r"((unsigned)kTcSpinLimit) : "memory");
+    return done != 0;
 }
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) { return mbar_wait_addr(smem_u32(bar), parity); }
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024
 // bytes apart (stride byte offset); leading byte offset unused for this layout; descriptor version 1.
@@ -221,63 +230,66 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     unsigned fpar = 0, epar = 0;
     const unsigned char* const w_src = b_ring + B_BYTES + r * 32 + part * 8;
     const unsigned a_dst = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + kACol0 + (unsigned)part * 8u;
-    for (int kt = 0; kt < kt_total; ++kt) {
+    const unsigned full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]), ready0 = smem_u32(&ready_bar[0]);
+    // one group; j = kt & 7 is a compile-time constant in the unrolled loop below, so picking the group's scale and
+    // zero out of the 16-byte vectors costs one instruction each
+    auto group = [&](int kt, int j) {
         // ---- the MMAs of group kt - SA are done: its weight tile (this group's) may be overwritten -----------
         if (kt >= SA) {
-            if (!mbar_wait(&empty_bar[es], epar)) { atomicExch(p.status, 1); failed = 1; }
+            if (!mbar_wait_addr(empty0 + 8u * es, epar)) { atomicExch(p.status, 1); failed = 1; }
             if (++es == SB) { es = 0; epar ^= 1u; }
         }
         // ---- this group's packed weights have landed (with its activations) ---------------------------------
-        if (!mbar_wait(&full_bar[fs], fpar)) { atomicExch(p.status, 1); failed = 1; }
-        // ---- weights: 32 nibbles of this thread's row -> 32 bf16 = bf16(scale * q + zero) -----------------
-        {
-            struct { uint2 w; unsigned s, z; } v;
-            v.w = *reinterpret_cast<const uint2*>(w_src + fs * STAGE_BYTES);
-            if (++fs == SB) { fs = 0; fpar ^= 1u; }
-            if ((kt & 7) == 0 && kt > 0) { s_cur = s_nxt; z_cur = z_nxt; s_nxt = load8(srow, kt + 8); z_nxt = load8(zrow, kt + 8); }
-            v.s = pick16(s_cur, kt & 7); v.z = pick16(z_cur, kt & 7);
-            const unsigned s2 = v.s | (v.s << 16), z2 = v.z | (v.z << 16);
-            const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(&s2);
-            const __nv_bfloat162 zr = *reinterpret_cast<const __nv_bfloat162*>(&z2);
-            const float sf = F16SB ? __half2float(__ushort_as_half((unsigned short)v.s)) : 0.f;
-            const float zf = F16SB ? __half2float(__ushort_as_half((unsigned short)v.z)) : 0.f;
-            const unsigned c128 = 0x43004300u;
-            const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162*>(&c128);
-            const unsigned words[2] = {v.w.x, v.w.y};
-            unsigned a_regs[8];
+        if (!mbar_wait_addr(full0 + 8u * fs, fpar)) { atomicExch(p.status, 1); failed = 1; }
+        // ---- weights: 16 nibbles of this thread's row -> 16 bf16 = bf16(scale * q + zero) -----------------
+        const uint2 wq = *reinterpret_cast<const uint2*>(w_src + fs * STAGE_BYTES);
+        if (++fs == SB) { fs = 0; fpar ^= 1u; }
+        const unsigned vs = pick16(s_cur, j), vz = pick16(z_cur, j);
+        const unsigned s2 = vs | (vs << 16), z2 = vz | (vz << 16);
+        const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(&s2);
+        const __nv_bfloat162 zr = *reinterpret_cast<const __nv_bfloat162*>(&z2);
+        const float sf = F16SB ? __half2float(__ushort_as_half((unsigned short)vs)) : 0.f;
+        const float zf = F16SB ? __half2float(__ushort_as_half((unsigned short)vz)) : 0.f;
+        const unsigned c128 = 0x43004300u;
+        const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162*>(&c128);
+        const unsigned words[2] = {wq.x, wq.y};
+        unsigned a_regs[8];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                // a word holds 8 consecutive columns, nibble j = column j; pairs (j, j+4) come out of one LOP3
-                const unsigned wv = words[c];
-                unsigned o[4];
+        for (int c = 0; c < 2; ++c) {
+            // a word holds 8 consecutive columns, nibble i = column i; pairs (i, i+4) come out of one LOP3
+            const unsigned wv = words[c];
+            unsigned o[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const unsigned pr = ((wv >> (4 * j)) & 0x000F000Fu) | 0x43004300u;         // (128+q_j, 128+q_{j+4})
-                    __nv_bfloat162 q2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pr), off);
-                    if (F16SB) {
-                        // fp16 scale and zero widened to fp32, one fused multiply-add, one rounding to bf16
-                        const unsigned qb = *reinterpret_cast<const unsigned*>(&q2);
-                        q2 = __floats2bfloat162_rn(fmaf(sf, __uint_as_float(qb << 16), zf), fmaf(sf, __uint_as_float(qb & 0xFFFF0000u), zf));
-                    } else {
-                        q2 = __hfma2(q2, sc, zr);                                              // bf16(s*q + z), one rounding
-                    }
-                    o[j] = *reinterpret_cast<const unsigned*>(&q2);                            // lo = column j, hi = column j+4
+            for (int i = 0; i < 4; ++i) {
+                const unsigned pr = ((wv >> (4 * i)) & 0x000F000Fu) | 0x43004300u;         // (128+q_i, 128+q_{i+4})
+                __nv_bfloat162 q2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pr), off);
+                if (F16SB) {
+                    // fp16 scale and zero widened to fp32, one fused multiply-add, one rounding to bf16
+                    const unsigned qb = *reinterpret_cast<const unsigned*>(&q2);
+                    q2 = __floats2bfloat162_rn(fmaf(sf, __uint_as_float(qb << 16), zf), fmaf(sf, __uint_as_float(qb & 0xFFFF0000u), zf));
+                } else {
+                    q2 = __hfma2(q2, sc, zr);                                              // bf16(s*q + z), one rounding
                 }
-                // reorder the pairs (j, j+4) into consecutive columns 0..7
-                a_regs[4 * c + 0] = __byte_perm(o[0], o[1], 0x5410); a_regs[4 * c + 1] = __byte_perm(o[2], o[3], 0x5410);
-                a_regs[4 * c + 2] = __byte_perm(o[0], o[1], 0x7632); a_regs[4 * c + 3] = __byte_perm(o[2], o[3], 0x7632);
+                o[i] = *reinterpret_cast<const unsigned*>(&q2);                            // lo = column i, hi = column i+4
             }
-            // 16 bf16 of this row -> 8 columns of the row's TMEM lane (a warp owns the 32 lanes of its quarter)
-            const unsigned taddr = a_dst + (unsigned)as * 32u;
-            asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                         ::"r"(taddr), "r"(a_regs[0]), "r"(a_regs[1]), "r"(a_regs[2]), "r"(a_regs[3]), "r"(a_regs[4]), "r"(a_regs[5]), "r"(a_regs[6]), "r"(a_regs[7]) : "memory");
+            // reorder the pairs (i, i+4) into consecutive columns 0..7
+            a_regs[4 * c + 0] = __byte_perm(o[0], o[1], 0x5410); a_regs[4 * c + 1] = __byte_perm(o[2], o[3], 0x5410);
+            a_regs[4 * c + 2] = __byte_perm(o[0], o[1], 0x7632); a_regs[4 * c + 3] = __byte_perm(o[2], o[3], 0x7632);
         }
+        // 16 bf16 of this row -> 8 columns of the row's TMEM lane (a warp owns the 32 lanes of its quarter)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"r"(a_dst + (unsigned)as * 32u), "r"(a_regs[0]), "r"(a_regs[1]), "r"(a_regs[2]), "r"(a_regs[3]), "r"(a_regs[4]), "r"(a_regs[5]), "r"(a_regs[6]), "r"(a_regs[7]) : "memory");
         // the stores to tensor memory are complete and ordered before the MMA warp's reads, then tell the MMA warp
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ready_bar[as])) : "memory");
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * as) : "memory");
         if (++as == SA) as = 0;
-        if (failed) break;
+    };
+    for (int kt0 = 0; kt0 < kt_total && !failed; kt0 += 8) {
+        if (kt0 > 0) { s_cur = s_nxt; z_cur = z_nxt; s_nxt = load8(srow, kt0 + 8); z_nxt = load8(zrow, kt0 + 8); }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (kt0 + j < kt_total) group(kt0 + j, j);
     }
     }  // dequantising warps
 

@@ -1023,8 +1023,9 @@ void qgemv_trace_report() {
             fprintf(stderr, "%3d attention %d CTAs | first-entry %9.2f deps %9.2f..%9.2f loop-done(last) %9.2f published %9.2f..%9.2f merged %9.2f..%9.2f | dur: wait %.2f prologue+loop %.2f publish %.2f\n",
                     sl, t.ctas, rel9(e0), rel9(d0), rel9(d1), rel9(x1), rel9(f0), rel9(f1), rel9(m0), rel9(m1), a / n / 1e3, b / n / 1e3, c / n / 1e3);
             if (r[t.ctas * 4 + 1])  // finer stamps of CTA 0, relative to the completion of its predecessor
-                fprintf(stderr, "    CTA 0 after deps (us): q/k/v in shared memory %.2f, q fragments %.2f, first 64 tokens %.2f, loop done %.2f, published %.2f\n",
-                        ((double)r[t.ctas * 4 + 1] - (double)r[1]) / 1e3, ((double)r[t.ctas * 4 + 2] - (double)r[1]) / 1e3,
+                fprintf(stderr, "    CTA 0 after deps (us): q/k/v in shared memory %.2f, rotated %.2f, self score %.2f, q fragments %.2f, first 64 tokens %.2f, loop done %.2f, published %.2f\n",
+                        ((double)r[t.ctas * 4 + 1] - (double)r[1]) / 1e3, ((double)r[(t.ctas + 1) * 4 + 1] - (double)r[1]) / 1e3,
+                        ((double)r[(t.ctas + 1) * 4 + 2] - (double)r[1]) / 1e3, ((double)r[t.ctas * 4 + 2] - (double)r[1]) / 1e3,
                         ((double)r[t.ctas * 4 + 3] - (double)r[1]) / 1e3, ((double)r[2] - (double)r[1]) / 1e3, ((double)r[3] - (double)r[1]) / 1e3);
             continue;
         }
