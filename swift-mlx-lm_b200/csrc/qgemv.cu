@@ -576,7 +576,28 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     else if (iu < u_end) unit_range(iu, ia, ia_end);
     const unsigned ring_sa = (unsigned)__cvta_generic_to_shared(my_ring) + lane * 16;
     const bool sb_lane = lane < 16;
+    // range mode: the warp's stages are contiguous in memory, so the sources are running pointers
+    const uint4* r_src = p.tiles + (size_t)ia * 128 + lane;
+    const uint4* r_ssrc = p.sb + (size_t)ia * 16 + lane;
     auto issue = [&](int slot) {
+        if (RANGE) {
+            if (ia < ia_end) {
+                const unsigned dst = ring_sa + slot * kStageBytes;
+                asm volatile(
+                    "cp.async.cg.shared.global [%0], [%1], 16;\n"
+                    "cp.async.cg.shared.global [%0+512], [%1+512], 16;\n"
+                    "cp.async.cg.shared.global [%0+1024], [%1+1024], 16;\n"
+                    "cp.async.cg.shared.global [%0+1536], [%1+1536], 16;\n" ::"r"(dst), "l"(r_src) : "memory");
+                if (sb_lane) {
+                    asm volatile("cp.async.cg.shared.global [%0+2048], [%1], 16;\n" ::"r"(dst), "l"(r_ssrc) : "memory");
+                    // HBM -> L2 a few stages further ahead (one 128-byte line per lane)
+                    if (ia + kL2Ahead < ia_end) prefetch_l2(reinterpret_cast<const unsigned char*>(r_src) + kL2Ahead * 2048 + lane * 112);
+                }
+                r_src += 128; r_ssrc += 16; ++ia;
+            }
+            cp_async_commit();
+            return;
+        }
         if (ia == ia_end && iu < iu_end) {
             iu += u_stride;
             if (iu < iu_end) unit_range(iu, ia, ia_end);
