@@ -56,7 +56,8 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void* p, unsigned bytes) 
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 constexpr int kBulkPiece = 8;        // stages per bulk prefetch instruction (16 KB of tiles + 2 KB of pairs)
-constexpr int kBulkMaxStages = 16;   // at most 36 KB per CTA requested up front (the rolling prefetch does the rest)
+constexpr int kBulkMaxStages = 8;    // at most 18 KB per CTA requested up front (the rolling prefetch does the rest); measured:
+                                     // 0 -> 582, 8 -> 585, 16 -> 575, 32 -> 563, 64 -> 541 tok/s on the Llama-3-8B shape
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -638,7 +639,7 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
                 unit_range(pu0, pa0, unused);
                 unit_range(pu1 - 1, unused, pa1);
             }
-            pa1 = min(pa1, pa0 + kBulkMaxStages);
+            pa1 = min(pa1, pa0 + p.bulk_stages);
             const int piece = gtid >> 1;  // even threads: tiles, odd threads: scale/zero pairs
             const int s0 = pa0 + piece * kBulkPiece;
             if (s0 < pa1) {
@@ -650,9 +651,20 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     }
     int islot = 0, cslot = 0;  // ring slots of the next stage to issue / to consume
 #pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
+    for (int i = 0; i < kStages - 1; ++i)
+        if (i < p.pre_stages) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
     pdl_wait();
     if (p.trace && tid == 0) p.trace[blockIdx.x * 4 + 1] = global_timer_ns();
+    // The activations of this thread's first run are requested now, ahead of the remaining ring stages: a load
+    // issued after them would wait in the SM's memory pipeline behind tens of kilobytes of weights, and the
+    // whole product waits for the activations.
+    NormRunLoads pre_loads;
+    pre_loads.x = pre_loads.res = pre_loads.nw = make_uint4(0, 0, 0, 0);
+    if (p.norm_mode) pre_loads = fused_norm_load8(p, tid * 8, tid * 8 < p.k);
+    else if (tid * 8 < p.k) pre_loads.x = __ldg(reinterpret_cast<const uint4*>(p.x + tid * 8));
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i)
+        if (i >= p.pre_stages) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
 
     // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
     __shared__ float red[kMaxWarps1];
@@ -664,11 +676,12 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
         float xf[8];
         if (p.norm_mode) {
             // dimension <= 4096: exactly one pass, every thread takes part in the block-wide sum
-            fused_norm_run8(p, k0, k0 < p.k, blockIdx.x == 0, red, xf, tp_epoch, nthreads >> 5);
+            fused_norm_run8(p, k0, k0 < p.k, blockIdx.x == 0, red, xf, tp_epoch, nthreads >> 5, pre_loads);
             if (run >= nruns) continue;
         } else {
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (k0 < p.k) v = __ldg(reinterpret_cast<const uint4*>(p.x + k0));
+            if (run == tid) v = pre_loads.x;
+            else if (k0 < p.k) v = __ldg(reinterpret_cast<const uint4*>(p.x + k0));
             const unsigned vw[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) { xf[2 * i] = __uint_as_float(vw[i] << 16); xf[2 * i + 1] = __uint_as_float(vw[i] & 0xFFFF0000u); }
@@ -1148,6 +1161,16 @@ static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c) {
     p.m = a.m;
     p.si = c.si; p.sk = c.sk; p.cta_mode = c.cta_mode;
     p.range_mode = c.range_mode; p.range_slots = c.range_slots;
+    {
+        // Ring stages requested before the wait for the preceding kernel, and stages asked into L2 up front. Both
+        // put weight traffic ahead of the activation loads in the SM's memory pipeline, and the product cannot
+        // start before its activations: measured best on the Llama-3-8B shape is no stage before the wait
+        // (563 / 570 / 575 tok/s for 2 / 1 / 0) and 8 stages into L2.
+        static const int pre = [] { const char* v = getenv("SWLM_PRE_STAGES"); return v ? atoi(v) : 0; }();
+        p.pre_stages = pre < 0 ? 0 : pre;
+        static const int bulk = [] { const char* v = getenv("SWLM_BULK_STAGES"); return v ? atoi(v) : kBulkMaxStages; }();
+        p.bulk_stages = bulk;
+    }
     p.si_shift = 0;
     while ((1 << p.si_shift) < c.si) ++p.si_shift; p.partial = a.partial; p.counters = a.counters;
     p.push = a.push; p.in_tp = a.in_tp; p.tp = a.tp;

@@ -21,6 +21,8 @@ struct QGemvParams {
     int si_shift; // log2(si) for the batch-1 kernel
     int cta_mode; // batch-1 kernel: slices of a row tile live in one CTA and meet in shared memory
     int range_mode, range_slots;  // batch-1 kernel: one contiguous range of stages per warp; partial slots per row tile
+    int pre_stages;               // batch-1 kernel: ring stages requested before the wait for the preceding kernel
+    int bulk_stages;              // batch-1 kernel: stages per CTA asked into L2 up front
     float* partial;
     unsigned* counters;
     // optional fused residual-add / copy / RMSNorm in front of the product (norm_mode = step kind, 0 = none)
@@ -56,27 +58,39 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // (written by one CTA only), then bf16(h * rsqrt(mean(h^2)+eps) * (w+bias)) returned as floats holding
 // bf16-rounded numbers. The norm sees the unrounded sum, as the reference's fused kernel does. res_in and
 // res_out are different buffers: other CTAs read res_in while one writes res_out.
+// The global loads of a run, issued ahead of their use (the caller puts other memory traffic between the two).
+struct NormRunLoads { uint4 x, res, nw; };
+__device__ __forceinline__ NormRunLoads fused_norm_load8(const QGemvParams& p, int k0, bool in_range) {
+    NormRunLoads l;
+    l.x = l.res = l.nw = make_uint4(0, 0, 0, 0);
+    if (in_range) {
+        l.nw = __ldg(reinterpret_cast<const uint4*>(p.norm_w + k0));
+        if (!p.in_tp) l.x = __ldcg(reinterpret_cast<const uint4*>(p.x + k0));
+        if (p.norm_mode != SWLM_STEP_COPY_RMSNORM) l.res = __ldcg(reinterpret_cast<const uint4*>(p.res_in + k0));
+    }
+    return l;
+}
 __device__ __forceinline__ void fused_norm_run8(const QGemvParams& p, int k0, bool in_range, bool writer,
-                                                float* red, float (&xf)[8], int tp_epoch, int nwarps) {
+                                                float* red, float (&xf)[8], int tp_epoch, int nwarps, const NormRunLoads& pre) {
     float h[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) h[i] = 0.f;
     uint4 nw4 = make_uint4(0, 0, 0, 0);
     if (in_range) {
-        nw4 = __ldg(reinterpret_cast<const uint4*>(p.norm_w + k0));  // independent of everything below
+        nw4 = pre.nw;
         if (p.in_tp) {
             const int par = tp_epoch & 1;
             tp_add_tagged_all<4>(p.tp, p.tp.lay.recv_ar(par, 0, 0) + (size_t)k0 * 8, p.tp.lay.recv_ar(par, 1, 0) - p.tp.lay.recv_ar(par, 0, 0), tp_epoch, h);
 #pragma unroll
             for (int i = 0; i < 8; ++i) h[i] = __bfloat162float(__float2bfloat16_rn(h[i]));
         } else {
-            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.x + k0));
+            const uint4 v = pre.x;
             const unsigned vw[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) { h[2 * i] = __uint_as_float(vw[i] << 16); h[2 * i + 1] = __uint_as_float(vw[i] & 0xFFFF0000u); }
         }
         if (p.norm_mode != SWLM_STEP_COPY_RMSNORM) {
-            const uint4 r = __ldcg(reinterpret_cast<const uint4*>(p.res_in + k0));
+            const uint4 r = pre.res;
             const unsigned rw[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) { h[2 * i] += __uint_as_float(rw[i] << 16); h[2 * i + 1] += __uint_as_float(rw[i] & 0xFFFF0000u); }

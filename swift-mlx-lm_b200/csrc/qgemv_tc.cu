@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kTcgThreads, 1) qgemv_tc_kernel(const QGemvPar
             const int k0 = run * 8;
             float xf[8];
             if (p.norm_mode) {
-                fused_norm_run8(p, k0, k0 < p.k, blockIdx.x == 0, red, xf, 0, kTcgThreads >> 5);
+                fused_norm_run8(p, k0, k0 < p.k, blockIdx.x == 0, red, xf, 0, kTcgThreads >> 5, fused_norm_load8(p, k0, k0 < p.k));
                 if (run >= nruns) continue;
             } else {
                 uint4 v = make_uint4(0, 0, 0, 0);
