@@ -668,6 +668,8 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
 
     // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
     __shared__ float red[kMaxWarps1];
+    __shared__ __align__(16) unsigned zero16[4];   // B operand of the lanes that carry no activations
+    if (tid < 4) zero16[tid] = 0u;                 // visible after the barrier that ends this section
     const int tp_epoch = (p.push || p.in_tp) ? *p.tp.epoch + (p.push ? 1 : 0) : 0;
     const int nthreads = blockDim.x;
     const int nruns = kt_total * 8;  // runs of 8 elements: eight neighbouring threads share a group of 64
@@ -730,9 +732,6 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     const int s_total = 1 << p.si_shift;
     __shared__ float cta_red_all[kMaxGroups][2][kWarps][16];
     float (*cta_red)[kWarps][16] = cta_red_all[grp];
-    __shared__ __align__(16) unsigned zero16[4];
-    if (tid < 4) zero16[tid] = 0u;
-    __syncthreads();
     // B operand source: lanes g = 0 / 1 read the high / low digits of their quarter of the group, all other
     // lanes (columns 2..7) read zeros; expressed as a base pointer and a per-tile stride so that the tile
     // loop is branch-free
