@@ -543,8 +543,13 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     // adds the slices through shared memory. Otherwise every CTA owns an equal contiguous share, its warps
     // take units round-robin and the slices of a row tile meet in global scratch. si is a power of two.
     const int units = p.row_tiles << p.si_shift;
-    const int u_lo = (int)(((long long)vb * units) / vgrid);
-    const int u_hi = (int)(((long long)(vb + 1) * units) / vgrid);
+    // floor(a * b / c): 32-bit when the host has checked that every such product fits (a 64-bit division costs
+    // over a hundred instructions, and this set-up sits between the predecessor's end and the first load)
+    auto muldiv = [&](long long a, int b, int c) {
+        return p.idx32 ? (int)(((unsigned)a * (unsigned)b) / (unsigned)c) : (int)(a * b / c);
+    };
+    const int u_lo = muldiv(units, vb, vgrid);
+    const int u_hi = muldiv(units, vb + 1, vgrid);
     const int u_first = p.cta_mode ? vb * kWarps : u_lo;
     const int u_end = p.cta_mode ? units : u_hi;
     const int u_limit = p.cta_mode ? ((units + kWarps - 1) / kWarps) * kWarps : u_hi;  // uniform across the group
@@ -563,11 +568,11 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     constexpr bool range_mode = RANGE;
     const long long S_all = (long long)p.row_tiles * p.kt4_total;
     const int W_all = vgrid * kWarps, gwarp = vb * kWarps + warp;
-    const int A0 = range_mode ? (int)(S_all * gwarp / W_all) : 0, A1 = range_mode ? (int)(S_all * (gwarp + 1) / W_all) : 0;
+    const int A0 = range_mode ? muldiv(S_all, gwarp, W_all) : 0, A1 = range_mode ? muldiv(S_all, gwarp + 1, W_all) : 0;
     auto stage_owner = [&](long long a) {  // warp whose range holds stage a
-        int c = (int)(((a + 1) * W_all - 1) / S_all);
-        while (c > 0 && S_all * c / W_all > a) --c;
-        while (c + 1 < W_all && S_all * (c + 1) / W_all <= a) ++c;
+        int c = p.idx32 ? (int)((((unsigned)a + 1u) * (unsigned)W_all - 1u) / (unsigned)S_all) : (int)(((a + 1) * W_all - 1) / S_all);
+        while (c > 0 && muldiv(S_all, c, W_all) > a) --c;
+        while (c + 1 < W_all && muldiv(S_all, c + 1, W_all) <= a) ++c;
         return c;
     };
     // cp.async side: runs kStages-1 stages ahead of the math, across unit boundaries
@@ -633,8 +638,8 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
         if (pu0 < pu1 || range_mode) {
             int pa0, pa1, unused;
             if (range_mode) {
-                pa0 = (int)(S_all * (vb * kWarps) / W_all);
-                pa1 = (int)(S_all * (vb * kWarps + kWarps) / W_all);
+                pa0 = muldiv(S_all, vb * kWarps, W_all);
+                pa1 = muldiv(S_all, vb * kWarps + kWarps, W_all);
             } else {
                 unit_range(pu0, pa0, unused);
                 unit_range(pu1 - 1, unused, pa1);
@@ -1172,6 +1177,12 @@ static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c) {
     }
     p.si_shift = 0;
     while ((1 << p.si_shift) < c.si) ++p.si_shift; p.partial = a.partial; p.counters = a.counters;
+    {
+        const unsigned long long vgrid = (unsigned long long)c.grid.x * (unsigned long long)std::max(1, c.occ);
+        const unsigned long long stages = (unsigned long long)p.row_tiles * (unsigned long long)p.kt4_total;
+        const unsigned long long units = (unsigned long long)p.row_tiles << p.si_shift;
+        p.idx32 = (stages + 1) * (vgrid * kWarps + 1) < (1ull << 32) && (units + 1) * (vgrid + 1) < (1ull << 32);
+    }
     p.push = a.push; p.in_tp = a.in_tp; p.tp = a.tp;
     p.prefetch = a.prefetch;
     if ((a.push || a.in_tp) && (a.tp.tp < 2 || !a.tp.epoch || !a.tp.done || !a.tp.status)) { set_error("qgemv: tensor-parallel exchange not attached"); return SWLM_ERR_STATE; }

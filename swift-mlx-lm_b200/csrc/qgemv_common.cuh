@@ -23,6 +23,7 @@ struct QGemvParams {
     int range_mode, range_slots;  // batch-1 kernel: one contiguous range of stages per warp; partial slots per row tile
     int pre_stages;               // batch-1 kernel: ring stages requested before the wait for the preceding kernel
     int bulk_stages;              // batch-1 kernel: stages per CTA asked into L2 up front
+    int idx32;                    // batch-1 kernel: the share arithmetic (stages x warps, units x CTAs) fits 32 bits
     float* partial;
     unsigned* counters;
     // optional fused residual-add / copy / RMSNorm in front of the product (norm_mode = step kind, 0 = none)
