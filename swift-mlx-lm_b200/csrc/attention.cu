@@ -15,6 +15,11 @@
 //   * the current token is not read back from the cache: the merging CTA adds its term in fp32 from
 //     the unrounded rotated k and v, exactly as the reference does (:866-868, :905-907), while the
 //     bf16-rounded copy is appended to the cache for later steps (:761-805).
+//   * blocks of 64 tokens are dealt to the splits round-robin, so a split's first block does not depend on the
+//     context length: in a decode step it is requested before the device-resident position has arrived, and
+//     the split's later blocks are asked into L2 as soon as it has; q, k and v of the new token are requested
+//     before any of that, and each RoPE pair is rotated once in shared memory.
+// Prompt chunks use a tiled causal kernel further down (attn_prefill_kernel).
 #include <cstdlib>
 #include <cmath>
 

@@ -23,6 +23,15 @@
 //     in fp32, and the group epilogue applies scale*(acc - 1024*sum(x)) + zero*sum(x) in fp32 —
 //     algebraically the reference's sum((scale*q+zero)*x), with q and x exact and products exact in fp32;
 //   * the B operand holds up to 16 sequences (columns), so batch <= 16 costs the same weight traffic.
+//
+// The single-sequence product (qgemv1_kernel, further down) keeps the tiles, the per-warp ring and the even
+// deal, but holds the activations as block floating point (one exponent per group of 64, two signed 8-bit
+// digits per element) and contracts them with the nibbles on the int8 tensor-core shape (mma.m16n8k32 u8 x s8):
+// rows g of a tile take the masked low nibbles, rows g + 8 the bytes as they are, and one subtraction
+// recovers the high nibbles. One CTA per SM of up to three 8-warp groups shares one copy of the activations.
+// Order in the SM's memory pipeline matters: the activation loads are issued first after the wait for the
+// preceding kernel and the ring stages only after them, because the product cannot start before its
+// activations and a load issued behind 100 KB of weights arrives late.
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
