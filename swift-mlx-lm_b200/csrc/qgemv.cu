@@ -528,10 +528,26 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], unsigned a0, unsigned a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ uint4 lds128(unsigned sa) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sa));
+    return v;
+}
+__device__ __forceinline__ unsigned lds32(unsigned sa) {
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(sa));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f(unsigned sa) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(sa));
+    return v;
+}
+
 // The single-sequence product. (Running o_proj, gate/up, down and the next q/k/v as one launch with a software
 // grid barrier between them was tried: on this part the barrier costs about 4.5 us, more than the 0.8 us a
 // dependent launch needs to see its predecessor complete, so every product is its own launch.)
-template <int EPI, bool F16SB, bool RANGE>
+template <int EPI, bool F16SB>
 __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char* smem) {
     const int tid = threadIdx.x, lane = tid & 31, cta_warp = tid >> 5;
     const int groups = blockDim.x / kThreads, grp = cta_warp / kWarps;
@@ -570,49 +586,13 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
         a0 = rt * p.kt4_total + ((sl * p.kt4_total) >> p.si_shift);
         a1 = rt * p.kt4_total + (((sl + 1) * p.kt4_total) >> p.si_shift);
     };
-    // Third way (range mode, large matrices): the stages of the whole matrix, in [row tile][k] order, are cut into
-    // one contiguous range per warp of the GPU, equal to within one stage, whatever the number of row tiles. A
-    // warp's range may cross row-tile boundaries; the parts of a row tile (two to fifteen warps) meet in global
-    // scratch like the slices above, in warp order.
-    constexpr bool range_mode = RANGE;
-    const long long S_all = (long long)p.row_tiles * p.kt4_total;
-    const int W_all = vgrid * kWarps, gwarp = vb * kWarps + warp;
-    const int A0 = range_mode ? muldiv(S_all, gwarp, W_all) : 0, A1 = range_mode ? muldiv(S_all, gwarp + 1, W_all) : 0;
-    auto stage_owner = [&](long long a) {  // warp whose range holds stage a
-        int c = p.idx32 ? (int)((((unsigned)a + 1u) * (unsigned)W_all - 1u) / (unsigned)S_all) : (int)(((a + 1) * W_all - 1) / S_all);
-        while (c > 0 && muldiv(S_all, c, W_all) > a) --c;
-        while (c + 1 < W_all && muldiv(S_all, c + 1, W_all) <= a) ++c;
-        return c;
-    };
     // cp.async side: runs kStages-1 stages ahead of the math, across unit boundaries
     int iu = u_first + warp, ia = 0, ia_end = 0;
-    int iu_end = u_end;
-    if (range_mode) { iu = A0 < A1 ? 0 : 1; iu_end = 1; ia = A0; ia_end = A1; }
-    else if (iu < u_end) unit_range(iu, ia, ia_end);
+    const int iu_end = u_end;
+    if (iu < u_end) unit_range(iu, ia, ia_end);
     const unsigned ring_sa = (unsigned)__cvta_generic_to_shared(my_ring) + lane * 16;
     const bool sb_lane = lane < 16;
-    // range mode: the warp's stages are contiguous in memory, so the sources are running pointers
-    const uint4* r_src = p.tiles + (size_t)ia * 128 + lane;
-    const uint4* r_ssrc = p.sb + (size_t)ia * 16 + lane;
     auto issue = [&](int slot) {
-        if (RANGE) {
-            if (ia < ia_end) {
-                const unsigned dst = ring_sa + slot * kStageBytes;
-                asm volatile(
-                    "cp.async.cg.shared.global [%0], [%1], 16;\n"
-                    "cp.async.cg.shared.global [%0+512], [%1+512], 16;\n"
-                    "cp.async.cg.shared.global [%0+1024], [%1+1024], 16;\n"
-                    "cp.async.cg.shared.global [%0+1536], [%1+1536], 16;\n" ::"r"(dst), "l"(r_src) : "memory");
-                if (sb_lane) {
-                    asm volatile("cp.async.cg.shared.global [%0+2048], [%1], 16;\n" ::"r"(dst), "l"(r_ssrc) : "memory");
-                    // HBM -> L2 a few stages further ahead (one 128-byte line per lane)
-                    if (ia + kL2Ahead < ia_end) prefetch_l2(reinterpret_cast<const unsigned char*>(r_src) + kL2Ahead * 2048 + lane * 112);
-                }
-                r_src += 128; r_ssrc += 16; ++ia;
-            }
-            cp_async_commit();
-            return;
-        }
         if (ia == ia_end && iu < iu_end) {
             iu += u_stride;
             if (iu < iu_end) unit_range(iu, ia, ia_end);
@@ -644,15 +624,10 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     {
         const int pu0 = p.cta_mode ? u_first : u_lo;
         const int pu1 = p.cta_mode ? min(u_first + kWarps, units) : u_hi;
-        if (pu0 < pu1 || range_mode) {
+        if (pu0 < pu1) {
             int pa0, pa1, unused;
-            if (range_mode) {
-                pa0 = muldiv(S_all, vb * kWarps, W_all);
-                pa1 = muldiv(S_all, vb * kWarps + kWarps, W_all);
-            } else {
-                unit_range(pu0, pa0, unused);
-                unit_range(pu1 - 1, unused, pa1);
-            }
+            unit_range(pu0, pa0, unused);
+            unit_range(pu1 - 1, unused, pa1);
             pa1 = min(pa1, pa0 + p.bulk_stages);
             const int piece = gtid >> 1;  // even threads: tiles, odd threads: scale/zero pairs
             const int s0 = pa0 + piece * kBulkPiece;
@@ -667,15 +642,27 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i)
         if (i < p.pre_stages) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
+    // the norm weights are constants of the model (and come from HBM): requested before the wait for the predecessor
+    uint4 nw_early = make_uint4(0, 0, 0, 0);
+    if (p.norm_mode && tid * 8 < p.k) nw_early = __ldg(reinterpret_cast<const uint4*>(p.norm_w + tid * 8));
     pdl_wait();
     if (p.trace && tid == 0) p.trace[blockIdx.x * 4 + 1] = global_timer_ns();
-    // The activations of this thread's first run are requested now, ahead of the remaining ring stages: a load
-    // issued after them would wait in the SM's memory pipeline behind tens of kilobytes of weights, and the
-    // whole product waits for the activations.
+    // The activations of this thread's runs are requested now, all of them together (one trip to L2, not one per
+    // run) and ahead of the remaining ring stages: a load issued after those would wait in the SM's memory pipeline
+    // behind tens of kilobytes of weights, and the whole product waits for the activations.
     NormRunLoads pre_loads;
     pre_loads.x = pre_loads.res = pre_loads.nw = make_uint4(0, 0, 0, 0);
-    if (p.norm_mode) pre_loads = fused_norm_load8(p, tid * 8, tid * 8 < p.k);
-    else if (tid * 8 < p.k) pre_loads.x = __ldg(reinterpret_cast<const uint4*>(p.x + tid * 8));
+    uint4 x_more[2];
+    x_more[0] = x_more[1] = make_uint4(0, 0, 0, 0);
+    if (p.norm_mode) { pre_loads = fused_norm_load8(p, tid * 8, tid * 8 < p.k); pre_loads.nw = nw_early; }
+    else {
+        if (tid * 8 < p.k) pre_loads.x = __ldcg(reinterpret_cast<const uint4*>(p.x + tid * 8));
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int k0 = (tid + (i + 1) * (int)blockDim.x) * 8;
+            if (k0 < p.k) x_more[i] = __ldcg(reinterpret_cast<const uint4*>(p.x + k0));
+        }
+    }
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i)
         if (i >= p.pre_stages) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
@@ -697,7 +684,9 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
         } else {
             uint4 v = make_uint4(0, 0, 0, 0);
             if (run == tid) v = pre_loads.x;
-            else if (k0 < p.k) v = __ldg(reinterpret_cast<const uint4*>(p.x + k0));
+            else if (run == tid + nthreads) v = x_more[0];
+            else if (run == tid + 2 * nthreads) v = x_more[1];
+            else if (k0 < p.k) v = __ldcg(reinterpret_cast<const uint4*>(p.x + k0));
             const unsigned vw[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) { xf[2 * i] = __uint_as_float(vw[i] << 16); xf[2 * i + 1] = __uint_as_float(vw[i] & 0xFFFF0000u); }
@@ -746,74 +735,64 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     const int s_total = 1 << p.si_shift;
     __shared__ float cta_red_all[kMaxGroups][2][kWarps][16];
     float (*cta_red)[kWarps][16] = cta_red_all[grp];
-    // B operand source: lanes g = 0 / 1 read the high / low digits of their quarter of the group, all other
-    // lanes (columns 2..7) read zeros; expressed as a base pointer and a per-tile stride so that the tile
-    // loop is branch-free
-    const unsigned char* xq_bytes = reinterpret_cast<const unsigned char*>(xq);
-    const unsigned char* zero_bytes = reinterpret_cast<const unsigned char*>(zero16);
-    const bool xlane = g < 2;
-    const int xlane_off = t * 32 + g * 16;
-    const int xtile_stride = xlane ? 128 : 0;
+    // B operand source. The four k-tiles of a stage (four groups of 64) share one set of accumulators: tile ti
+    // carries its activations in columns 2 ti (high digits) and 2 ti + 1 (low digits) of the B operand and zeros
+    // elsewhere, so after the stage's eight instructions lane (g, t) holds the integer sums of group t for rows g and
+    // g + 8, and the scale / zero epilogue runs once per stage with all 32 lanes busy (one group each) instead of
+    // once per tile with eight. Lane (g, t) therefore supplies data for tile g >> 1 only and reads zeros for the
+    // other three. All shared-memory addresses below are 32-bit.
+    const unsigned xq_sa = (unsigned)__cvta_generic_to_shared(xq);
+    const unsigned xmeta_sa = (unsigned)__cvta_generic_to_shared(xmeta) + t * 8;
+    const unsigned zero_sa = (unsigned)__cvta_generic_to_shared(zero16);
+    const int my_ti = g >> 1;
+    const unsigned my_xoff = xq_sa + my_ti * 128 + t * 32 + (g & 1) * 16;
+    const unsigned ring_warp_sa = (unsigned)__cvta_generic_to_shared(my_ring);
     int round = 0;
-    int seg_rt = range_mode ? A0 / p.kt4_total : 0;  // range mode: next row tile of this warp's range
-    for (int base = u_first; range_mode ? (A0 < A1 && seg_rt * p.kt4_total < A1) : (base < u_limit); base += u_stride, ++round) {
+    for (int base = u_first; base < u_limit; base += u_stride, ++round) {
         const int u = base + warp;
-        bool valid = u < u_end;
-        int rt = u >> p.si_shift;
-        int slice = u & si_mask;
-        int n_slices = s_total, pstride = s_total;
+        const bool valid = u < u_end;
+        const int rt = u >> p.si_shift;
+        const int slice = u & si_mask;
+        const int n_slices = s_total, pstride = s_total;
         float tot_lo = 0.f, tot_hi = 0.f, tot_hi16 = 0.f, tot_hiz = 0.f;
         int a0 = 0, a1 = 0;
-        if (range_mode) {
-            rt = seg_rt++;
-            valid = true;
-            a0 = max(A0, rt * p.kt4_total);
-            a1 = min(A1, (rt + 1) * p.kt4_total);
-            const int first = stage_owner((long long)rt * p.kt4_total), last = stage_owner((long long)(rt + 1) * p.kt4_total - 1);
-            slice = gwarp - first;
-            n_slices = last - first + 1;
-            pstride = p.range_slots;
-        } else if (valid) unit_range(u, a0, a1);
-        for (int a = a0; a < a1; ++a) {
+        if (valid) unit_range(u, a0, a1);
+        int stg = a0 - rt * p.kt4_total;
+        for (int a = a0; a < a1; ++a, ++stg) {
             issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1;
             cp_async_wait<kStages - 1>();
             __syncwarp();
-            const unsigned char* st = my_ring + cslot * kStageBytes;
+            const unsigned st = ring_warp_sa + cslot * kStageBytes;
             cslot = cslot + 1 == kStages ? 0 : cslot + 1;
-            const uint4* wsm = reinterpret_cast<const uint4*>(st) + lane;
-            const uint4 sA = reinterpret_cast<const uint4*>(st + 2048)[g];
-            const uint4 sB = reinterpret_cast<const uint4*>(st + 2048)[g + 8];
-            const unsigned sAw[4] = {sA.x, sA.y, sA.z, sA.w};
-            const unsigned sBw[4] = {sB.x, sB.y, sB.z, sB.w};
-            const int stg = a - rt * p.kt4_total;
-            const unsigned char* xbase = xlane ? xq_bytes + (size_t)stg * 512 + xlane_off : zero_bytes;
-            const float4* mrun = reinterpret_cast<const float4*>(xmeta + (size_t)stg * 4);
-            const float4 m01 = mrun[0], m23 = mrun[1];
-            const float mscale[4] = {m01.x, m01.z, m23.x, m23.z};
-            const float msum[4] = {m01.y, m01.w, m23.y, m23.w};
+            const unsigned wsa = st + lane * 16;
+            const unsigned xmine = my_xoff + stg * 512;
+            int c[4];
 #pragma unroll
             for (int ti = 0; ti < 4; ++ti) {
-                const uint4 wv = wsm[ti * 32];
-                // B operand: column 0 = high digits, column 1 = low digits of the activations, the rest zero
-                const uint4 xd = *reinterpret_cast<const uint4*>(xbase + ti * xtile_stride);
-                int c[4];
+                const uint4 wv = lds128(wsa + ti * 512);
+                const uint4 xd = lds128(ti == my_ti ? xmine : zero_sa);
                 // A byte holds the nibble of row g (low) and of row g + 8 (high) for the same column. Rows g take
                 // the masked low nibbles; rows g + 8 take the bytes as they are, lo + 16 * hi, against the same
                 // activations: their sum is (row g's sum) + 16 * (row g + 8's sum), all exact integers, so the
                 // high rows cost no unpacking at all and are recovered by one subtraction
-                imma_u8s8_zero(c, wv.x & 0x0F0F0F0Fu, wv.x, wv.y & 0x0F0F0F0Fu, wv.y, xd.x, xd.y);
+                if (ti == 0) imma_u8s8_zero(c, wv.x & 0x0F0F0F0Fu, wv.x, wv.y & 0x0F0F0F0Fu, wv.y, xd.x, xd.y);
+                else imma_u8s8(c, wv.x & 0x0F0F0F0Fu, wv.x, wv.y & 0x0F0F0F0Fu, wv.y, xd.x, xd.y);
                 imma_u8s8(c, wv.z & 0x0F0F0F0Fu, wv.z, wv.w & 0x0F0F0F0Fu, wv.w, xd.z, xd.w);
-                // lanes t == 0 hold columns 0 and 1 (high and low activation digits): sum = 256 * hi + lo
-                const float fa = (float)(c[0] * 256 + c[1]);
-                const float fb16 = (float)((c[2] - c[0]) * 256 + (c[3] - c[1]));  // 16 x the sum of row g + 8
-                tot_lo = fmaf(sb_scale<F16SB>(sAw[ti]) * mscale[ti], fa, fmaf(sb_zero<F16SB>(sAw[ti]), msum[ti], tot_lo));
-                tot_hi16 = fmaf(sb_scale<F16SB>(sBw[ti]) * mscale[ti], fb16, tot_hi16);
-                tot_hiz = fmaf(sb_zero<F16SB>(sBw[ti]), msum[ti], tot_hiz);
             }
+            // group t of the stage: (scale, zero) of rows g and g + 8, the group's 2^E and scaled activation sum
+            const unsigned pa = lds32(st + 2048 + lane * 4), pb = lds32(st + 2048 + 128 + lane * 4);
+            const float2 mt = lds64f(xmeta_sa + stg * 32);
+            const float fa = (float)(c[0] * 256 + c[1]);                         // sum = 256 * hi + lo
+            const float fb16 = (float)((c[2] - c[0]) * 256 + (c[3] - c[1]));     // 16 x the sum of row g + 8
+            tot_lo = fmaf(sb_scale<F16SB>(pa) * mt.x, fa, fmaf(sb_zero<F16SB>(pa), mt.y, tot_lo));
+            tot_hi16 = fmaf(sb_scale<F16SB>(pb) * mt.x, fb16, tot_hi16);
+            tot_hiz = fmaf(sb_zero<F16SB>(pb), mt.y, tot_hiz);
             __syncwarp();
         }
         tot_hi = fmaf(tot_hi16, 0.0625f, tot_hiz);
-        // lanes t == 0 hold the sums of rows g and g + 8; the other lanes carried zero columns
+        // lane (g, t) holds the part of groups t, t + 4, ... of rows g and g + 8: add the four lanes of a row
+        tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 1); tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 2);
+        tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 1); tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 2);
 
         bool finisher = valid;
         if (p.cta_mode) {
@@ -887,15 +866,14 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     }
 }
 
-template <int EPI, bool F16SB, bool RANGE>
+template <int EPI, bool F16SB>
 __global__ void __launch_bounds__(kMaxGroups * kThreads, 1) qgemv1_kernel(const QGemvParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
-    qgemv1_body<EPI, F16SB, RANGE>(p, smem);
+    qgemv1_body<EPI, F16SB>(p, smem);
 }
 
 struct QGemvConfig {
     int nt, si, sk, occ, cta_mode;
-    int range_mode, range_slots;
     dim3 grid;
     size_t smem;
 };
@@ -923,18 +901,12 @@ QGemvConfig pick_config(const Q4Tiled& w, int m) {
         c.smem = (size_t)c.occ * kRingBytes + x_bytes;
         const int slots = kSMs * c.occ;  // groups resident on the GPU
         int vgrid;
-        const long long stages = (long long)w.row_tiles * kt4, warps = (long long)slots * kWarps;
-        const char* no_range = getenv("SWLM_NO_RANGE_MODE");
-        const int per = (int)(stages / warps);
-        if (per >= 3 && 2 * per >= kt4 && per < 2 * kt4 && !(no_range && no_range[0] == '1')) {
-            // large matrix, at most three warps per row tile: every warp of the GPU gets one contiguous range of
-            // stages, equal to within one stage
-            c.range_mode = 1;
-            c.si = 1;
-            c.range_slots = std::min(kt4, (kt4 + per - 1) / per + 1);
-            vgrid = slots;
-        } else if (w.row_tiles <= slots) {
-            // few row tiles: one row tile per group, its warps split K (no global scratch, no atomics)
+        if (kt4 >= 2) {
+            // One row tile per group and round, its eight warps split K and add their parts through shared memory (no
+            // global scratch, no atomics); group v takes row tiles v, v + groups, ...: in every round the GPU reads one
+            // contiguous window of the matrix, which is what HBM likes (measured on the 28672 x 4096 gate/up product:
+            // 16.8 us when every warp streamed a private contiguous range of the matrix, 14.3 us this way; the
+            // 128256 x 4096 output head 60 -> 50 us).
             c.cta_mode = 1;
             c.si = 1;
             while (c.si < kWarps && c.si * 2 <= kt4) c.si *= 2;
@@ -942,7 +914,6 @@ QGemvConfig pick_config(const Q4Tiled& w, int m) {
             vgrid = std::min(slots, chunks);
         } else {
             c.si = 1;
-            while (c.si < 16 && c.si * 4 <= kt4 && (long long)w.row_tiles * c.si < 16LL * kSMs) c.si *= 2;
             const int units = w.row_tiles * c.si;
             vgrid = std::min(slots, (units + kWarps - 1) / kWarps);
         }
@@ -993,12 +964,8 @@ int launch_1(const QGemvParams& p_in, const QGemvConfig& c, cudaStream_t s) {
     QGemvParams p = p_in;
     p.trace = qgemv_trace_slot((int)c.grid.x, p.row_tiles, p.kt4_total, EPI, p.norm_mode);
     cudaError_t e;
-    if (c.range_mode)
-        e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true, true>, c.grid, dim3(c.occ * kThreads), c.smem, s, p)
-                     : launch_k(qgemv1_kernel<EPI, false, true>, c.grid, dim3(c.occ * kThreads), c.smem, s, p);
-    else
-        e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true, false>, c.grid, dim3(c.occ * kThreads), c.smem, s, p)
-                     : launch_k(qgemv1_kernel<EPI, false, false>, c.grid, dim3(c.occ * kThreads), c.smem, s, p);
+    e = p.sb_f16 ? launch_k(qgemv1_kernel<EPI, true>, c.grid, dim3(c.occ * kThreads), c.smem, s, p)
+                 : launch_k(qgemv1_kernel<EPI, false>, c.grid, dim3(c.occ * kThreads), c.smem, s, p);
     if (e != cudaSuccess) return cuda_fail(e, "qgemv1 launch");
     return SWLM_OK;
 }
@@ -1079,6 +1046,12 @@ void qgemv_trace_report() {
         auto rel = [&](unsigned long long v) { return ((double)v - (double)origin) / 1e3; };
         fprintf(stderr, "%3d %4d %6d %4d %d %d | %9.2f %9.2f %9.2f %9.2f %9.2f %9.2f | %6.2f %6.2f %6.2f", sl, t.ctas, t.row_tiles, t.kt4, t.epi,
                 t.norm, rel(e0), rel(d0), rel(d1), rel(x1), rel(f0), rel(f1), a / n / 1e3, b / n / 1e3, c / n / 1e3);
+        if ((t.ctas + 2) * 4 <= kTraceCtas * 4 && !r[t.ctas * 4] && r[(t.ctas + 1) * 4 + 3]) {
+            // bulk-copy ring kernel: finer stamps of CTA 0, relative to the completion of its predecessor
+            auto d0 = [&](unsigned long long v) { return v ? ((double)v - (double)r[1]) / 1e3 : 0.0; };
+            fprintf(stderr, " | CTA 0 after deps (us): norm inputs %.2f, norm barrier %.2f, x ready %.2f, warp 0 done %.2f, all warps %.2f, done %.2f",
+                    d0(r[(t.ctas + 1) * 4]), d0(r[(t.ctas + 1) * 4 + 1]), d0(r[2]), d0(r[(t.ctas + 1) * 4 + 2]), d0(r[(t.ctas + 1) * 4 + 3]), d0(r[3]));
+        }
         // the tensor-core kernel also stamps the end of its set-up and the release of its TMEM, in the rows after
         // its CTAs'
         if (2 * t.ctas <= kTraceCtas && r[t.ctas * 4]) {
@@ -1123,20 +1096,15 @@ int qgemv_init() {
     if ((rc = opt_in_smem(qgemv_kernel<1, 1, true>))) return rc;
     if ((rc = opt_in_smem(qgemv_kernel<2, 0, true>))) return rc;
     if ((rc = opt_in_smem(qgemv_kernel<2, 1, true>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<0, false, false>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<1, false, false>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<0, true, false>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<1, true, false>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<0, false, true>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<1, false, true>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<0, true, true>))) return rc;
-    if ((rc = opt_in_smem(qgemv1_kernel<1, true, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<0, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<1, false>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<0, true>))) return rc;
+    if ((rc = opt_in_smem(qgemv1_kernel<1, true>))) return rc;
     return SWLM_OK;
 }
 
 size_t qgemv_scratch_floats(const Q4Tiled& w, int m) {
     QGemvConfig c = pick_config(w, m);
-    if (c.range_mode) return (size_t)w.row_tiles * c.range_slots * 16;
     if (c.sk * c.si <= 1 || c.cta_mode) return 0;
     return (size_t)w.row_tiles * c.sk * c.si * 16 * (c.nt ? 8 * c.nt : 1);
 }
@@ -1163,7 +1131,7 @@ static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c) {
     }
     c = pick_config(w, a.m);
     if (g_max_dyn_smem == 0 || c.smem > (size_t)g_max_dyn_smem) { set_error("qgemv: shared memory %zu exceeds the limit %d", c.smem, g_max_dyn_smem); return SWLM_ERR_INVALID; }
-    if ((c.range_mode || (c.sk * c.si > 1 && !c.cta_mode)) && (!a.partial || !a.counters)) { set_error("qgemv: split launch without scratch"); return SWLM_ERR_INVALID; }
+    if (c.sk * c.si > 1 && !c.cta_mode && (!a.partial || !a.counters)) { set_error("qgemv: split launch without scratch"); return SWLM_ERR_INVALID; }
     p = QGemvParams{};
     p.tiles = w.tiles; p.sb = w.sb; p.row_tiles = w.row_tiles; p.kt4_total = w.kt_pad / 4; p.sb_f16 = w.sb_f16 ? 1 : 0;
     p.x = a.x; p.x_stride = a.x_stride; p.k = w.k;
@@ -1173,7 +1141,6 @@ static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c) {
     }
     p.m = a.m;
     p.si = c.si; p.sk = c.sk; p.cta_mode = c.cta_mode;
-    p.range_mode = c.range_mode; p.range_slots = c.range_slots;
     {
         // Ring stages requested before the wait for the preceding kernel, and stages asked into L2 up front. Both
         // put weight traffic ahead of the activation loads in the SM's memory pipeline, and the product cannot

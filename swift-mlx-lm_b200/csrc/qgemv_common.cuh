@@ -20,7 +20,6 @@ struct QGemvParams {
     int si, sk;   // k-slices per CTA group, CTA groups along K
     int si_shift; // log2(si) for the batch-1 kernel
     int cta_mode; // batch-1 kernel: slices of a row tile live in one CTA and meet in shared memory
-    int range_mode, range_slots;  // batch-1 kernel: one contiguous range of stages per warp; partial slots per row tile
     int pre_stages;               // batch-1 kernel: ring stages requested before the wait for the preceding kernel
     int bulk_stages;              // batch-1 kernel: stages per CTA asked into L2 up front
     int idx32;                    // batch-1 kernel: the share arithmetic (stages x warps, units x CTAs) fits 32 bits
@@ -40,10 +39,6 @@ struct QGemvParams {
     // phase timestamps (SWLM_TRACE=1): [cta][4] = kernel entry, predecessor complete, activations ready, done
     unsigned long long* trace;
     PrefetchTarget prefetch;
-    // tensor-core (tcgen05) kernel: weights as shared-memory images, see Q4Umma
-    const unsigned char* tc_tiles;
-    int row_blocks, chunks, tc_interleaved;
-    int* status;  // set non-zero when a bounded wait expired
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -64,8 +59,7 @@ struct NormRunLoads { uint4 x, res, nw; };
 __device__ __forceinline__ NormRunLoads fused_norm_load8(const QGemvParams& p, int k0, bool in_range) {
     NormRunLoads l;
     l.x = l.res = l.nw = make_uint4(0, 0, 0, 0);
-    if (in_range) {
-        l.nw = __ldg(reinterpret_cast<const uint4*>(p.norm_w + k0));
+    if (in_range) {   // (the caller fills in the norm weights, which it requested earlier)
         if (!p.in_tp) l.x = __ldcg(reinterpret_cast<const uint4*>(p.x + k0));
         if (p.norm_mode != SWLM_STEP_COPY_RMSNORM) l.res = __ldcg(reinterpret_cast<const uint4*>(p.res_in + k0));
     }

@@ -48,7 +48,6 @@ struct swlm_ctx {
     cudaStream_t stream = nullptr;
     std::map<std::string, Q4Raw> raw;
     std::map<std::string, Q4Tiled> tiled;  // plain and fused tensors, keyed by name ("a|b|c" for fused)
-    std::map<std::string, Q4Umma> umma;    // the same tensors as shared-memory images for the tensor-core GEMV
     std::map<std::string, DenseTensor> dense;
     int64_t bytes = 0;
     float* op_partial = nullptr; size_t op_partial_floats = 0;
@@ -144,45 +143,6 @@ int get_tiled(swlm_ctx* ctx, const std::vector<std::string>& names, int mode, co
     return SWLM_OK;
 }
 
-// Build (or fetch) the tensor-core GEMV layout for one raw tensor or a fusion of several (same keys as above).
-int get_umma(swlm_ctx* ctx, const std::vector<std::string>& names, int mode, const Q4Umma** out) {
-    std::string key = names[0];
-    for (size_t i = 1; i < names.size(); ++i) key += (mode == 1 ? "^" : "|") + names[i];
-    auto found = ctx->umma.find(key);
-    if (found != ctx->umma.end()) { *out = &found->second; return SWLM_OK; }
-    RepackSrc src[3];
-    int n_total = 0, k = 0;
-    bool f16 = false;
-    for (size_t i = 0; i < names.size(); ++i) {
-        auto it = ctx->raw.find(names[i]);
-        if (it == ctx->raw.end()) { set_error("tensor '%s' not in the weight store", names[i].c_str()); return SWLM_ERR_NOT_FOUND; }
-        const Q4Raw& r = it->second;
-        if (i == 0) { k = r.k; f16 = r.sb_f16; }
-        else if (r.k != k || r.sb_f16 != f16) { set_error("fused tensors must share K and header type"); return SWLM_ERR_INVALID; }
-        src[i] = RepackSrc{r.w, r.scales, r.biases, r.n};
-        n_total += r.n;
-    }
-    Q4Umma t;
-    t.k = k; t.sb_f16 = f16; t.interleaved = mode == 1;
-    t.chunks = (k + 127) / 128;
-    if (mode == 1) {
-        if (names.size() != 2 || src[0].n != src[1].n) { set_error("interleave needs two tensors with equal N"); return SWLM_ERR_INVALID; }
-        t.n = src[0].n;
-        t.row_blocks = (src[0].n + 127) / 128;
-    } else {
-        t.n = n_total;
-        t.row_blocks = (n_total + 255) / 256;
-    }
-    int rc = dev_alloc(&t.tiles, t.bytes(), ctx);
-    if (rc) return rc;
-    rc = launch_umma_repack(src, (int)names.size(), mode, k, t, ctx->stream);
-    if (rc) return rc;
-    SWLM_CUDA(cudaStreamSynchronize(ctx->stream));
-    ctx->umma[key] = t;
-    *out = &ctx->umma[key];
-    return SWLM_OK;
-}
-
 int add_q4_raw(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* w, const uint16_t* s,
                const uint16_t* b, bool f16, int shard_kind) {
     if (!ctx || !name || !w || !s || !b) { set_error("null argument"); return SWLM_ERR_INVALID; }
@@ -240,7 +200,6 @@ struct Launch {
     int kind = 0;
     swlm_step st{};            // the (first) step this launch came from
     const Q4Tiled* w = nullptr;
-    const Q4Umma* wu = nullptr;  // tensor-core layout of the same weights (single-sequence plans)
     std::vector<std::string> w_names;
     int w_mode = 0;
     int epilogue = QGEMV_EPI_STORE;
@@ -546,21 +505,6 @@ int compile_plan(swlm_plan* plan) {
         }
     }
 
-    // SWLM_TC_GEMV=1: single-sequence plans run their products on the tensor-core (tcgen05) GEMV instead of the
-    // mma.sync kernel. Off by default: measured on a B200 with the Llama-3-8B shape the mma.sync kernel is the
-    // faster one at batch 1 (its stream already runs at HBM speed and its latency per launch is lower).
-    const char* use_tc = getenv("SWLM_TC_GEMV");
-    if (m == 1 && use_tc && use_tc[0] == '1') {
-        for (Launch& L : plan->launches) {
-            if (L.kind != L_QGEMV || L.push || L.in_tp) continue;
-            if (L.norm.kind && (L.w->k > 4096 || (L.w->k & 15))) continue;
-            rc = get_umma(ctx, L.w_names, L.w_mode, &L.wu);
-            if (rc) return rc;
-            plan->qgemv_partial = std::max(plan->qgemv_partial, qgemv_tc_scratch_floats());
-            plan->qgemv_counters = std::max(plan->qgemv_counters, (size_t)qgemv_tc_counter_count(*L.wu));
-            L.label = "tc " + L.label;
-        }
-    }
     return SWLM_OK;
 }
 
@@ -690,8 +634,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
                 if (!s->tp_attached) { set_error("tensor-parallel plan: call swlm_tp_export / swlm_tp_attach on the state first"); return SWLM_ERR_STATE; }
                 a.push = L.push; a.in_tp = L.in_tp; a.tp = s->tp;
             }
-            if (L.wu && qgemv_tc_supports(*L.wu, a)) rc = launch_qgemv_tc(*L.wu, a, s->tc_status, stream);
-            else rc = launch_qgemv(a, stream);
+            rc = launch_qgemv(a, stream);
             s->launches += 1;
             break;
         }
@@ -849,7 +792,7 @@ size_t plan_attn_scratch(const swlm_plan* plan) {
 // After a synchronisation: did a bounded wait of the tensor-core GEMV give up since the last check?
 int check_tc_status(swlm_state* s) {
     if (s->tc_status && *s->tc_status) {
-        set_error("a bounded device-side wait expired (code %d, tensor-core GEMV)", *s->tc_status);
+        set_error("a bounded device-side wait expired (code %d)", *s->tc_status);
         *s->tc_status = 0;
         return SWLM_ERR_TIMEOUT;
     }
@@ -1021,7 +964,6 @@ int swlm_ctx_create(int device_id, int tp_rank, int tp_size, swlm_ctx** out) {
     int rc = qgemv_init();
     if (!rc) rc = attn_init();
     if (!rc) rc = qgemm_tc_init();
-    if (!rc) rc = qgemv_tc_init();
     if (rc) { cudaStreamDestroy(ctx->stream); delete ctx; return rc; }
     *out = ctx;
     return SWLM_OK;
@@ -1034,7 +976,6 @@ void swlm_ctx_destroy(swlm_ctx* ctx) {
     cudaSetDevice(ctx->device);
     for (auto& kv : ctx->raw) { cudaFree(kv.second.w); cudaFree(kv.second.scales); cudaFree(kv.second.biases); }
     for (auto& kv : ctx->tiled) { cudaFree(kv.second.tiles); cudaFree(kv.second.sb); }
-    for (auto& kv : ctx->umma) cudaFree(kv.second.tiles);
     for (auto& kv : ctx->dense) cudaFree(kv.second.data);
     cudaFree(ctx->op_partial);
     cudaFree(ctx->tc_status);
@@ -1624,21 +1565,6 @@ int swlm_op_qgemm_dev(swlm_ctx* ctx, const char* weight, int m, const void* x_de
         if ((rc = dev_alloc(&ctx->tc_status, 1))) return rc;
         SWLM_CUDA(cudaMemsetAsync(ctx->tc_status, 0, sizeof(int), ctx->stream));
         SWLM_CUDA(cudaStreamSynchronize(ctx->stream));
-    }
-    // SWLM_TC_GEMV=1, m == 1: the tensor-core GEMV over shared-memory images of the weights
-    const char* use_tc = getenv("SWLM_TC_GEMV");
-    if (m == 1 && use_tc && use_tc[0] == '1' && ctx->raw.count(weight)) {
-        const Q4Umma* wu;
-        if ((rc = get_umma(ctx, {weight}, 0, &wu))) return rc;
-        QGemvLaunch a;
-        a.m = 1;
-        a.x = static_cast<const __nv_bfloat16*>(x_dev); a.x_stride = wu->k;
-        a.y[0] = static_cast<__nv_bfloat16*>(y_dev); a.y_stride[0] = wu->n; a.seg_end[0] = wu->n;
-        if (qgemv_tc_supports(*wu, a)) {
-            if ((rc = op_scratch_sized(ctx, qgemv_tc_scratch_floats(), (size_t)qgemv_tc_counter_count(*wu)))) return rc;
-            a.partial = ctx->op_partial; a.counters = ctx->op_counters;
-            return launch_qgemv_tc(*wu, a, ctx->tc_status, stream);
-        }
     }
     // m >= 64: tensor-core contraction straight from the packed source copy
     auto raw = ctx->raw.find(weight);

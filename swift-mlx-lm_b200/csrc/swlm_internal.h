@@ -71,24 +71,6 @@ struct Q4Tiled {
     size_t bytes() const { return (size_t)row_tiles * kt_pad * 512 + (size_t)row_tiles * (kt_pad / 4) * 256; }
 };
 
-// Q4 group-64 tensor as shared-memory images for the tensor-core (tcgen05) single-sequence GEMV.
-//   tiles : [row_blocks][chunks] records of 18432 bytes. A record covers 256 rows x 128 columns:
-//           16384 bytes = 128 byte-rows x 128 bytes, byte (i, k) = nibble of row 256*rb + i (low) | nibble of row
-//           256*rb + 128 + i (high) << 4 for column 128*c + k, stored K-major with the 128-byte swizzle (16-byte
-//           chunk j of byte-row i sits at chunk position j ^ (i & 7)); then uint2[2 groups][128 byte-rows] =
-//           (scale, zero) pairs of the low row and of the high row (two 16-bit floats each, scale in the low half).
-//   interleaved: low nibbles are rows of source A (gate), high nibbles the same rows of source B (up);
-//           a row block then covers 128 rows of each.
-// Rows and columns beyond n / k hold q = 0, scale = zero = 0.
-struct Q4Umma {
-    int n = 0, k = 0;
-    int row_blocks = 0, chunks = 0;
-    bool sb_f16 = false;
-    bool interleaved = false;
-    unsigned char* tiles = nullptr;
-    size_t bytes() const;
-};
-
 // Raw source copy kept on the device so that fused tensors can be assembled at plan time.
 struct Q4Raw {
     int n = 0, k = 0;
@@ -197,14 +179,6 @@ struct QGemvLaunch {
 size_t qgemv_scratch_floats(const Q4Tiled& w, int m);
 int qgemv_counter_count(const Q4Tiled& w);
 int launch_qgemv(const QGemvLaunch& a, cudaStream_t s);
-// Tensor-core (tcgen05) single-sequence GEMV over a Q4Umma tensor: same launch description as launch_qgemv
-// (a.w is ignored). `status` is a word the kernel sets when a bounded wait expired.
-int launch_umma_repack(const RepackSrc* src, int n_src, int mode, int k, const Q4Umma& dst, cudaStream_t s);
-int qgemv_tc_init();
-bool qgemv_tc_supports(const Q4Umma& w, const QGemvLaunch& a);
-int launch_qgemv_tc(const Q4Umma& w, const QGemvLaunch& a, int* status, cudaStream_t s);
-size_t qgemv_tc_scratch_floats();
-int qgemv_tc_counter_count(const Q4Umma& w);
 // SWLM_TRACE=1: slot for the phase timestamps of one launch (nullptr when tracing is off or the slots are used up)
 unsigned long long* qgemv_trace_slot(int ctas, int row_tiles, int kt4, int epi, int norm);
 int qgemv_init();  // sets shared-memory attributes once per process

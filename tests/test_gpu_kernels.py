@@ -71,28 +71,6 @@ def test_qgemm_matches_oracle(pkg, store, oracle, n, k, m):
         assert rel_err(got[row], ref64[row]).max() <= RTOL
 
 
-@pytest.mark.parametrize("n,k", [(1, 64), (17, 128), (300, 320), (4096, 4096), (6144, 4096), (4096, 14336), (2048, 1792)])
-@pytest.mark.parametrize("staf", [False, True])
-def test_qgemv_tensor_core_variant_matches_oracle(pkg, store, oracle, monkeypatch, n, k, staf):
-    """SWLM_TC_GEMV=1 runs the single-sequence product on the tcgen05 kernel (weights as shared-memory images, raw
-    bytes and a low-nibble copy multiplied by two signed-byte digits of the activations, exact integer sums, group
-    scale and zero applied from TMEM): same contract and tolerance as the default kernel. Row counts that are not
-    multiples of 256, K that is not a multiple of 128 and row blocks split across CTAs are all in the list."""
-    monkeypatch.setenv("SWLM_TC_GEMV", "1")
-    w, s, b = pkg.synth_q4(n, k, seed=n * 13 + k)
-    x = _bf(pkg, np.random.default_rng(n + k).normal(size=(1, k)))
-    name = f"tcv.{n}x{k}.{int(staf)}"
-    if staf:
-        store.add_q4_staf(name, pkg.formats.repack_mlx_to_staf(w, s, b), n, k)
-    else:
-        store.add_q4_mlx(name, w, s, b)
-    got = pkg.bf16_to_f32(store.qgemm(name, x, n))
-    oracle.set_threads(0)
-    ref_bf16, ref64 = oracle.qgemm(x, w, s, b, staf_fp16=staf, want_f64=True)
-    assert rel_err(got[0], pkg.bf16_to_f32(ref_bf16)[0]).max() <= RTOL
-    assert rel_err(got[0], ref64[0]).max() <= RTOL
-
-
 def test_qgemm_more_than_16_rows_runs_in_passes(pkg, store, oracle):
     n, k, m = 512, 1024, 40
     w, s, b = pkg.synth_q4(n, k, seed=5)
