@@ -53,6 +53,7 @@ constexpr int kRingBytes = kWarps * kStages * kStageBytes;
 constexpr int kMaxGroups = 3;
 constexpr int kMaxWarps1 = kMaxGroups * kWarps;
 constexpr int kXPad = 8;                   // bf16 elements of padding per x row (bank skew)
+constexpr int kTraceRows = 512;            // rows of four stamps per traced launch
 constexpr int kL2Ahead = 10;               // stages (2.3 KB each) a warp prefetches into L2 ahead of its ring
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -609,9 +610,6 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
                 const uint4* ssrc = p.sb + (size_t)ia * 16 + lane;
                 asm volatile("cp.async.cg.shared.global [%0+2048], [%1], 16;\n" ::"r"(dst), "l"(ssrc) : "memory");
             }
-            // HBM -> L2 a few stages further ahead inside the same unit (one 128-byte line per lane)
-            if (sb_lane && ia + kL2Ahead < ia_end)
-                prefetch_l2(reinterpret_cast<const unsigned char*>(p.tiles + (size_t)(ia + kL2Ahead) * 128) + lane * 128);
             ++ia;
         }
         cp_async_commit();
@@ -663,9 +661,14 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
             if (k0 < p.k) x_more[i] = __ldcg(reinterpret_cast<const uint4*>(p.x + k0));
         }
     }
+    // ring_late of the remaining stages are held back until the activations are in shared memory
+    int held = 0;
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i)
-        if (i >= p.pre_stages) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
+        if (i >= p.pre_stages) {
+            if (kStages - 1 - i <= p.ring_late) { ++held; continue; }
+            issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1;
+        }
 
     // ---- activations -> block floating point, one run of 16 elements per thread ------------------------
     __shared__ float red[kMaxWarps1];
@@ -674,12 +677,15 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
     const int tp_epoch = (p.push || p.in_tp) ? *p.tp.epoch + (p.push ? 1 : 0) : 0;
     const int nthreads = blockDim.x;
     const int nruns = kt_total * 8;  // runs of 8 elements: eight neighbouring threads share a group of 64
+    const bool stamp0 = p.trace && blockIdx.x == 0 && tid == 0 && gridDim.x + 2 <= kTraceRows;  // finer stamps of the first CTA
+    if (stamp0) p.trace[(gridDim.x + 1) * 4] = global_timer_ns();   // loads and ring stages issued
     for (int run = tid; run < nruns || (p.norm_mode && run < nthreads); run += nthreads) {
         const int k0 = run * 8;
         float xf[8];
         if (p.norm_mode) {
             // dimension <= 4096: exactly one pass, every thread takes part in the block-wide sum
             fused_norm_run8(p, k0, k0 < p.k, blockIdx.x == 0, red, xf, tp_epoch, nthreads >> 5, pre_loads);
+            if (stamp0) p.trace[(gridDim.x + 1) * 4 + 1] = global_timer_ns();   // inputs arrived, norm formed
             if (run >= nruns) continue;
         } else {
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -728,7 +734,10 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
         *reinterpret_cast<uint2*>(qd + 16) = lo;
         const float scale = live ? __uint_as_float((unsigned)(e - 13) << 23) : 0.f;  // 2^(e - 140) = 1 / mul
         if ((run & 7) == 0) xmeta[run >> 3] = make_float2(scale, (float)sum * scale);
+        if (stamp0 && run == tid) p.trace[(gridDim.x + 1) * 4 + 2] = global_timer_ns();   // this thread's first run quantised
     }
+    if (stamp0) p.trace[(gridDim.x + 1) * 4 + 3] = global_timer_ns();   // all of this thread's runs
+    for (; held > 0; --held) { issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1; }
     __syncthreads();
 
     if (p.trace && tid == 0) p.trace[blockIdx.x * 4 + 2] = global_timer_ns();
@@ -1046,11 +1055,11 @@ void qgemv_trace_report() {
         auto rel = [&](unsigned long long v) { return ((double)v - (double)origin) / 1e3; };
         fprintf(stderr, "%3d %4d %6d %4d %d %d | %9.2f %9.2f %9.2f %9.2f %9.2f %9.2f | %6.2f %6.2f %6.2f", sl, t.ctas, t.row_tiles, t.kt4, t.epi,
                 t.norm, rel(e0), rel(d0), rel(d1), rel(x1), rel(f0), rel(f1), a / n / 1e3, b / n / 1e3, c / n / 1e3);
-        if ((t.ctas + 2) * 4 <= kTraceCtas * 4 && !r[t.ctas * 4] && r[(t.ctas + 1) * 4 + 3]) {
-            // bulk-copy ring kernel: finer stamps of CTA 0, relative to the completion of its predecessor
+        if (t.ctas + 2 <= kTraceCtas && !r[t.ctas * 4] && r[(t.ctas + 1) * 4 + 3]) {
+            // finer stamps of CTA 0, relative to the completion of its predecessor
             auto d0 = [&](unsigned long long v) { return v ? ((double)v - (double)r[1]) / 1e3 : 0.0; };
-            fprintf(stderr, " | CTA 0 after deps (us): norm inputs %.2f, norm barrier %.2f, x ready %.2f, warp 0 done %.2f, all warps %.2f, done %.2f",
-                    d0(r[(t.ctas + 1) * 4]), d0(r[(t.ctas + 1) * 4 + 1]), d0(r[2]), d0(r[(t.ctas + 1) * 4 + 2]), d0(r[(t.ctas + 1) * 4 + 3]), d0(r[3]));
+            fprintf(stderr, " | CTA 0 after deps (us): requests issued %.2f, norm formed %.2f, first run quantised %.2f, all runs %.2f, x ready %.2f, done %.2f",
+                    d0(r[(t.ctas + 1) * 4]), d0(r[(t.ctas + 1) * 4 + 1]), d0(r[(t.ctas + 1) * 4 + 2]), d0(r[(t.ctas + 1) * 4 + 3]), d0(r[2]), d0(r[3]));
         }
         // the tensor-core kernel also stamps the end of its set-up and the release of its TMEM, in the rows after
         // its CTAs'
@@ -1150,6 +1159,9 @@ static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c) {
         p.pre_stages = pre < 0 ? 0 : pre;
         static const int bulk = [] { const char* v = getenv("SWLM_BULK_STAGES"); return v ? atoi(v) : kBulkMaxStages; }();
         p.bulk_stages = bulk;
+        // measured on the Llama-3-8B shape: 630 / 634 / 616 tok/s for 0 / 1 / 2 stages held back
+        static const int late = [] { const char* v = getenv("SWLM_RING_LATE"); return v ? atoi(v) : 1; }();
+        p.ring_late = late;
     }
     p.si_shift = 0;
     while ((1 << p.si_shift) < c.si) ++p.si_shift; p.partial = a.partial; p.counters = a.counters;

@@ -22,6 +22,7 @@ struct QGemvParams {
     int cta_mode; // batch-1 kernel: slices of a row tile live in one CTA and meet in shared memory
     int pre_stages;               // batch-1 kernel: ring stages requested before the wait for the preceding kernel
     int bulk_stages;              // batch-1 kernel: stages per CTA asked into L2 up front
+    int ring_late;                // batch-1 kernel: ring stages held back until the activations are in shared memory
     int idx32;                    // batch-1 kernel: the share arithmetic (stages x warps, units x CTAs) fits 32 bits
     float* partial;
     unsigned* counters;
