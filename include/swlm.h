@@ -158,13 +158,20 @@ int swlm_profile_kind(swlm_state* state, int step_kind, int repeats);
  * uses torch.distributed) -> swlm_tp_attach with all handles in rank order -> a barrier -> decode as usual.
  * Row-parallel products push their partial sums into every rank's exchange buffer over NVLink and the next
  * product adds them up in its prologue; the vocabulary-sharded argmax is exchanged the same way. Every device
- * wait is bounded: if a rank does not arrive, swlm_tp_status returns SWLM_ERR_TIMEOUT instead of hanging. */
+ * wait is bounded: if a rank does not arrive, the call that was producing tokens (swlm_decode, swlm_read_tokens /
+ * swlm_decode_n, swlm_prefill, swlm_sync) returns SWLM_ERR_TIMEOUT with token -1 instead of hanging, and so does
+ * swlm_tp_status. After a timeout the ranks' exchange counters no longer agree: destroy the state and create a new
+ * one on every rank before decoding again. */
 #define SWLM_TP_HANDLE_BYTES 64
 int swlm_tp_export(swlm_state* state, void* handle_out);
 int swlm_tp_attach(swlm_state* state, const void* handles);
 int swlm_tp_status(swlm_state* state);
 /* Rank-local slice {row0, rows, col0, cols} of an n x k tensor under a SWLM_SHARD_* kind (host only). */
 int swlm_shard_range(int shard_kind, int n, int k, int tp_rank, int tp_size, int* out4);
+/* Can `heads` query heads over `kv_heads` KV heads be cut into tp_size equal shards (host only)? Both counts must be
+ * multiples of tp_size and every rank must keep whole GQA groups; otherwise SWLM_ERR_UNSUPPORTED. swlm_plan_build
+ * applies the same check to every attention and QK-norm step. */
+int swlm_tp_check_heads(int heads, int kv_heads, int tp_size);
 
 /* ---- op-level entry points (host buffers; copies are part of the call) ----------
  * Y[m][n] = bf16(X[m][k] . W^T): gemv_q4_g64 for m = 1

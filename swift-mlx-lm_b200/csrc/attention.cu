@@ -20,6 +20,7 @@
 //     the split's later blocks are asked into L2 as soon as it has; q, k and v of the new token are requested
 //     before any of that, and each RoPE pair is rotated once in shared memory.
 // Prompt chunks use a tiled causal kernel further down (attn_prefill_kernel).
+#include <atomic>
 #include <cstdlib>
 #include <cmath>
 
@@ -746,6 +747,7 @@ int attn_init() {
 int attn_pick_splits(int m, int kv_heads, int max_ctx) {
     static const int forced = [] { const char* v = getenv("SWLM_ATTN_SPLITS"); return v ? atoi(v) : 0; }();
     if (forced >= 1 && forced <= 64) return forced;
+    if (m <= 0 || kv_heads <= 0) return 1;
     int s = 300 / (m * kv_heads);
     const int cap = max_ctx / 128;
     if (s > 32) s = 32;
@@ -848,7 +850,9 @@ int launch_flash_decode_plain(int m, int heads, int kv_heads, int hd, int ctx_le
 // on the GPU (different streams, no ordering between them) would race on it; serialise them.
 constexpr size_t kStaticScratchBytes = 8u << 20;
 static __device__ __align__(256) unsigned char g_flash_static_scratch[kStaticScratchBytes];
-static void* g_flash_static_addr[64] = {};  // device address of the array, per device ordinal
+// device address of the array, per device ordinal. Written by whichever thread calls first on a device; every writer
+// stores the same value, and the slot is an atomic so that concurrent first calls are a defined program.
+static std::atomic<void*> g_flash_static_addr[64];
 
 size_t flash_decode_static_capacity() { return kStaticScratchBytes; }
 
@@ -856,13 +860,13 @@ int launch_flash_decode_static(int device, int m, int heads, int kv_heads, int h
                                const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, __nv_bfloat16* out,
                                cudaStream_t s) {
     if (device < 0 || device >= 64) { set_error("flash-decode (static scratch): device ordinal %d out of range", device); return SWLM_ERR_INVALID; }
-    if (!g_flash_static_addr[device]) {
+    if (!g_flash_static_addr[device].load(std::memory_order_acquire)) {
         // In host code the array's name is only a handle; the kernel needs the device address, which the
         // runtime resolves for the device that is current now. Done once per device, on the first call.
         void* addr = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&addr, g_flash_static_scratch);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(flash-decode static scratch)");
-        g_flash_static_addr[device] = addr;
+        g_flash_static_addr[device].store(addr, std::memory_order_release);
     }
     const int splits = attn_pick_splits(m, kv_heads, ctx_len);
     const size_t counter_bytes = (((size_t)m * kv_heads * sizeof(unsigned)) + 255) / 256 * 256;
@@ -872,7 +876,7 @@ int launch_flash_decode_static(int device, int m, int heads, int kv_heads, int h
                   m, heads, splits, need, kStaticScratchBytes);
         return SWLM_ERR_INVALID;
     }
-    unsigned char* base = static_cast<unsigned char*>(g_flash_static_addr[device]);
+    unsigned char* base = static_cast<unsigned char*>(g_flash_static_addr[device].load(std::memory_order_acquire));
     SWLM_CUDA(cudaMemsetAsync(base, 0, counter_bytes, s));  // arrival counters must start at zero
     return launch_flash_decode_plain(m, heads, kv_heads, hd, ctx_len, ctx_stride, scale, q, k, v, out,
                                      reinterpret_cast<float*>(base + counter_bytes), reinterpret_cast<unsigned*>(base), splits, s);

@@ -2,9 +2,18 @@
 //
 // Replaces the reference's `gemm_q4_g64` for M >= 64 (Generator/MetalSourceGenerator+Quantized.swift:88-156,
 // which repeats the per-row dot product for every sequence position and so re-reads the weights M times)
-// with a real contraction. Arithmetic follows the reference's other prefill route, dequantise-then-matmul
-// (`dequant_q4_g64_bf16`, +Quantized.swift:361-416: W_bf16 = bf16(scale*q + zero), then a dense product with
-// fp32 accumulation), except that the bf16 weights never exist in global memory.
+// with a real contraction whose result equals the fp32-weight product up to the order of the fp32 sums. The weight
+// is split as scale*q + zero = scale*(q - 8) + (zero + 8*scale): |q - 8| <= 8 has at most three significant bits (or
+// is a power of two) and a bf16 or fp16 scale at most eleven, so scale*(q - 8) is EXACT in fp16 and is the A operand;
+// the second term is constant over a group of 64 and multiplies the group's sum of activations, which becomes three
+// extra K-columns per group appended after the real ones (c_hi x sum_hi, c_lo x sum_hi, c_hi x sum_lo, fp16 pairs
+// that carry 22 bits). tcgen05.mma kind::f16 wants both operands in one format (fp16 weights against bf16 activations
+// is an illegal instruction on this part), so a small kernel first copies the activations to fp16, every token row
+// times a power of two that puts its largest magnitude at 2^14 (exact for every element within 2^-28 of the row's
+// largest, immune to fp16's range, undone per token in the epilogue), and appends the per-group sums. (A dequantised
+// weight rounded to 16 bits, the reference's dequantise-then-matmul route of +Quantized.swift:361-416, does not hold
+// 1e-2 per output against `gemm_q4_g64`: bf16 weights leave outputs a tenth of the typical magnitude 1-5 % off,
+// fp16 weights 1 %.)
 //
 // One CTA (18 warps) computes a 128 (weight rows) x BN (tokens) tile of Y^T:
 //   * a TMA warp (one thread) keeps a ring of stages full, two cp.async.bulk.tensor.2d per 64-column group
@@ -13,8 +22,8 @@
 //     stage counts the bytes;
 //   * 16 warps dequantise: four threads own one weight row, per group each reads 8 packed bytes from shared
 //     memory, takes the row's (scale, zero) from registers (fetched eight groups at a time), turns nibble
-//     pairs into bf16 with LOP3 (128+q), subtracts 128 and applies scale and zero with one bf16x2 FMA each
-//     — exactly bf16(scale*q + zero) — and stores its 16 values into the row's lane of tensor memory
+//     pairs into fp16 with LOP3 (1024+q), subtracts 1032 and multiplies by the scale with one f16x2 instruction
+//     each — scale*(q - 8), exact — and stores its 16 values into the row's lane of tensor memory
 //     (tcgen05.st): the A operand of the MMA is read from TMEM, so the dequantised weights never cross shared
 //     memory and four such tiles (32 columns each) fit beside the accumulator;
 //   * an MMA warp (one thread) issues four tcgen05.mma (M=128, N=BN, K=16, kind::f16, A from TMEM, B through
@@ -42,8 +51,10 @@ struct QGemmTcParams {
     const uint16_t* scales;   // [n][k/64] bf16
     const uint16_t* biases;
     int n, k;
-    const __nv_bfloat16* x;   // [m][x_stride]
+    const __half* x;          // [m][x_stride]: the activations as fp16, every token row scaled by a power of two
+    const float* rscale;      // [m]: the inverse of each row's scale
     int x_stride, m;
+    int ext_steps;            // 64-column steps of appended group-sum columns (three planes of ceil(k/64/64) steps)
     __nv_bfloat16* y;         // [m][y_stride]
     int y_stride;
     int* status;              // set non-zero when a bounded wait expired
@@ -89,9 +100,9 @@ __device__ __forceinline__ unsigned long long umma_desc(unsigned smem_addr) {
     return d;
 }
 
-// Instruction descriptor for kind::f16: D = fp32, A = B = bf16, both K-major, M = 128, N = BN.
+// Instruction descriptor for kind::f16: D = fp32, A = B = fp16 (format 0), both K-major, M = 128, N = BN.
 __host__ __device__ constexpr unsigned umma_idesc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(kTcRows >> 4) << 24);
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(kTcRows >> 4) << 24);
 }
 
 // D[tmem] (+)= A[tmem] x B[shared memory]: the A operand (128 rows x 16 bf16 = 8 columns of 32 bits) is read from
@@ -136,6 +147,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     const int r = (warp & 3) * 32 + lane, part = (warp >> 2) & 3;   // TMEM lane = weight row; part: which 16 of the group's 64 columns
     const int row0 = blockIdx.x * kTcRows, tok0 = blockIdx.y * BN;
     const int kt_total = p.k / kTcBK;
+    const int steps_total = kt_total + p.ext_steps;   // real groups, then the appended group-sum columns
     unsigned char* const b_ring = smem;
 
     if (tid == 0) {
@@ -183,7 +195,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         // ---- MMA warp: one thread issues the four MMAs of a group as soon as its tiles are in place; the
         // dequantising warps are already busy with the next group by then -----------------------------------
         if (lane == 0) {
-            for (int kt = 0; kt < kt_total; ++kt) {
+            for (int kt = 0; kt < steps_total; ++kt) {
                 if (!mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1)) || !mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1))) {
                     atomicExch(p.status, 2); failed = 1; break;
                 }
@@ -193,7 +205,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
                 for (int j = 0; j < kTcBK / 16; ++j)  // 16 bf16 = 8 columns of A, 32 bytes along K inside B's 128-byte row
                     umma_f16_ta(tmem_d, a_addr + 8u * j, umma_desc(b_addr + 32 * j), idesc, (kt > 0 || j > 0) ? 1u : 0u);
                 umma_commit(&empty_bar[kt % SB]);
-                if (kt == kt_total - 1) umma_commit(&done_bar);
+                if (kt == steps_total - 1) umma_commit(&done_bar);
             }
         }
         __syncwarp();
@@ -202,15 +214,17 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         if (lane == 0) {
             pdl_wait();                         // the activations may come from the kernel just before this one
             int issued = 0;
-            for (int kt = 0; kt < kt_total; ++kt) {
+            for (int kt = 0; kt < steps_total; ++kt) {
                 const int s = kt % SB;
                 // the MMAs that read this stage SB groups ago are done
                 if (kt >= SB && !mbar_wait(&empty_bar[s], (unsigned)((kt / SB - 1) & 1))) { atomicExch(p.status, 3); failed = 1; break; }
                 if (failed) break;
                 const unsigned bar = smem_u32(&full_bar[s]);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)STAGE_BYTES) : "memory");
-                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(smem_u32(b_ring + s * STAGE_BYTES + B_BYTES)), "l"(reinterpret_cast<unsigned long long>(&wmap)), "r"(kt * 32), "r"(row0), "r"(bar) : "memory");
+                const bool real = kt < kt_total;   // an appended step has activations (the group sums) but no packed weights
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)(real ? STAGE_BYTES : B_BYTES)) : "memory");
+                if (real)
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                 ::"r"(smem_u32(b_ring + s * STAGE_BYTES + B_BYTES)), "l"(reinterpret_cast<unsigned long long>(&wmap)), "r"(kt * 32), "r"(row0), "r"(bar) : "memory");
                 asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                              ::"r"(smem_u32(b_ring + s * STAGE_BYTES)), "l"(reinterpret_cast<unsigned long long>(&xmap)), "r"(kt * kTcBK), "r"(tok0), "r"(bar) : "memory");
                 issued = kt + 1;
@@ -245,13 +259,13 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         const uint2 wq = *reinterpret_cast<const uint2*>(w_src + fs * STAGE_BYTES);
         if (++fs == SB) { fs = 0; fpar ^= 1u; }
         const unsigned vs = pick16(s_cur, j), vz = pick16(z_cur, j);
-        const unsigned s2 = vs | (vs << 16), z2 = vz | (vz << 16);
-        const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(&s2);
-        const __nv_bfloat162 zr = *reinterpret_cast<const __nv_bfloat162*>(&z2);
-        const float sf = F16SB ? __half2float(__ushort_as_half((unsigned short)vs)) : 0.f;
-        const float zf = F16SB ? __half2float(__ushort_as_half((unsigned short)vz)) : 0.f;
-        const unsigned c128 = 0x43004300u;
-        const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162*>(&c128);
+        // the scale as an fp16 pair: STAF tensors carry fp16 already; a bf16 (MLX) scale converts exactly (8 mantissa
+        // bits into 11) unless it lies below fp16's normal range, where the weights it scales are nil anyway
+        const __half s16 = F16SB ? __ushort_as_half((unsigned short)vs) : __float2half_rn(__uint_as_float(vs << 16));
+        const __half2 sc = __half2half2(s16);
+        (void)vz;
+        const unsigned c1032 = 0x64086408u;   // fp16 1032 = 1024 + 8
+        const __half2 off = *reinterpret_cast<const __half2*>(&c1032);
         const unsigned words[2] = {wq.x, wq.y};
         unsigned a_regs[8];
 #pragma unroll
@@ -261,15 +275,9 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
             unsigned o[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const unsigned pr = ((wv >> (4 * i)) & 0x000F000Fu) | 0x43004300u;         // (128+q_i, 128+q_{i+4})
-                __nv_bfloat162 q2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pr), off);
-                if (F16SB) {
-                    // fp16 scale and zero widened to fp32, one fused multiply-add, one rounding to bf16
-                    const unsigned qb = *reinterpret_cast<const unsigned*>(&q2);
-                    q2 = __floats2bfloat162_rn(fmaf(sf, __uint_as_float(qb << 16), zf), fmaf(sf, __uint_as_float(qb & 0xFFFF0000u), zf));
-                } else {
-                    q2 = __hfma2(q2, sc, zr);                                              // bf16(s*q + z), one rounding
-                }
+                const unsigned pr = ((wv >> (4 * i)) & 0x000F000Fu) | 0x64006400u;         // fp16 (1024+q_i, 1024+q_{i+4})
+                __half2 q2 = __hsub2(*reinterpret_cast<const __half2*>(&pr), off);        // (q_i - 8, q_{i+4} - 8), exact
+                q2 = __hmul2(q2, sc);                                                      // scale * (q - 8): exact in fp16
                 o[i] = *reinterpret_cast<const unsigned*>(&q2);                            // lo = column i, hi = column i+4
             }
             // reorder the pairs (i, i+4) into consecutive columns 0..7
@@ -290,6 +298,46 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
 #pragma unroll
         for (int j = 0; j < 8; ++j)
             if (kt0 + j < kt_total) group(kt0 + j, j);
+    }
+    // ---- appended steps: the A operand is the groups' constant term c = 64 (zero + 8 scale) as an fp16 pair (hi, lo);
+    // plane 0 carries c_hi (against sum_hi), plane 1 c_lo (against sum_hi), plane 2 c_hi (against sum_lo); the
+    // activation side holds sum / 64 so that neither factor leaves fp16's range -----------------------------------
+    const int plane_steps = p.ext_steps / 3;
+    for (int e = 0; e < p.ext_steps && !failed; ++e) {
+        const int kt = kt_total + e;
+        if (kt >= SA) {
+            if (!mbar_wait_addr(empty0 + 8u * es, epar)) { atomicExch(p.status, 1); failed = 1; }
+            if (++es == SB) { es = 0; epar ^= 1u; }
+        }
+        if (!mbar_wait_addr(full0 + 8u * fs, fpar)) { atomicExch(p.status, 1); failed = 1; }
+        if (++fs == SB) { fs = 0; fpar ^= 1u; }
+        const int plane = e / plane_steps, g0 = (e - plane * plane_steps) * 64 + part * 16;
+        unsigned a_regs[8];
+#pragma unroll
+        for (int h8 = 0; h8 < 2; ++h8) {
+            const uint4 sv = load8(srow, g0 + 8 * h8), zv = load8(zrow, g0 + 8 * h8);   // zero beyond the last group
+            float c[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const unsigned bs = pick16(sv, i), bz = pick16(zv, i);
+                const float sf = F16SB ? __half2float(__ushort_as_half((unsigned short)bs)) : __uint_as_float(bs << 16);
+                const float zf = F16SB ? __half2float(__ushort_as_half((unsigned short)bz)) : __uint_as_float(bz << 16);
+                const float cf = 64.0f * fmaf(8.0f, sf, zf);
+                const float hi = __half2float(__float2half_rn(cf));
+                c[i] = plane == 1 ? cf - hi : hi;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __half2 pr = __floats2half2_rn(c[2 * i], c[2 * i + 1]);
+                a_regs[4 * h8 + i] = *reinterpret_cast<const unsigned*>(&pr);
+            }
+        }
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"r"(a_dst + (unsigned)as * 32u), "r"(a_regs[0]), "r"(a_regs[1]), "r"(a_regs[2]), "r"(a_regs[3]), "r"(a_regs[4]), "r"(a_regs[5]), "r"(a_regs[6]), "r"(a_regs[7]) : "memory");
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * as) : "memory");
+        if (++as == SA) as = 0;
     }
     }  // dequantising warps
 
@@ -317,7 +365,8 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int tkn = tok0 + c0 + i;
-                    if (tkn < p.m) p.y[(size_t)tkn * p.y_stride + erow] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    // undo the token row's power-of-two scaling (exact), round once to bf16
+                    if (tkn < p.m) p.y[(size_t)tkn * p.y_stride + erow] = __float2bfloat16_rn(__uint_as_float(v[i]) * __ldg(p.rscale + tkn));
                 }
             }
         }
@@ -325,6 +374,53 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTmemCols) : "memory");
+}
+
+// Activations bf16 -> fp16, one CTA per token row: the row's largest magnitude goes to [2^14, 2^15), so that nothing
+// overflows fp16 and every element within 2^-28 of the largest converts exactly (bf16 carries 8 significant bits,
+// fp16 11). rscale[row] = the inverse factor, applied to the accumulators in the product's epilogue. Behind the k
+// converted values the row gets three planes of g_pad columns: sum / 64 of every group of 64 converted values as an
+// fp16 pair, laid out (hi, hi, lo) to meet the (c_hi, c_lo, c_hi) planes of the weight side; columns past the last
+// group are zero.
+__global__ void __launch_bounds__(256) x_to_f16_kernel(const __nv_bfloat16* x, int x_stride, int k, int g_pad, __half* xh, int xh_stride, float* rscale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ unsigned red[8];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const unsigned* src = reinterpret_cast<const unsigned*>(x + (size_t)row * x_stride);
+    unsigned mx = 0;
+    for (int i = tid; i < k / 2; i += 256) {
+        const unsigned w = src[i];
+        mx = max(mx, max(w & 0x7FFFu, (w >> 16) & 0x7FFFu));   // bf16 magnitudes order like their bit patterns
+    }
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    mx = 0;
+    for (int i = 0; i < 8; ++i) mx = max(mx, red[i]);
+    const int e = (int)(mx >> 7);                                   // biased exponent of the largest magnitude
+    const int sh = (e == 0 || e == 255) ? 0 : max(-100, min(100, 141 - e));
+    const float mul = __uint_as_float((unsigned)(127 + sh) << 23);  // 2^sh
+    __half* out = xh + (size_t)row * xh_stride;
+    // a warp converts one group of 64 at a time (one 32-bit word of two values per lane) and sums it
+    const int lane = tid & 31, warp = tid >> 5, groups = k / 64;
+    for (int g = warp; g < g_pad; g += 8) {
+        float sum = 0.f;
+        if (g < groups) {
+            const unsigned w = src[g * 32 + lane];
+            const __half2 h = __floats2half2_rn(__uint_as_float(w << 16) * mul, __uint_as_float(w & 0xFFFF0000u) * mul);
+            reinterpret_cast<unsigned*>(out)[g * 32 + lane] = *reinterpret_cast<const unsigned*>(&h);
+            const float2 f = __half22float2(h);
+            sum = f.x + f.y;
+        }
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) {
+            const float sc = sum * 0.015625f;
+            const __half hi = __float2half_rn(sc), lo = __float2half_rn(sc - __half2float(hi));
+            out[k + g] = hi; out[k + g_pad + g] = hi; out[k + 2 * g_pad + g] = lo;
+        }
+    }
+    if (tid == 0) rscale[row] = __uint_as_float((unsigned)(127 - sh) << 23);
 }
 
 template <int BN, int STAGES>
@@ -344,15 +440,15 @@ TensorMapEncodeFn tensor_map_encode_fn() {
     return fn;
 }
 
-// bf16 activations X[m][x_stride] as a 2-D tensor (k innermost); box = 64 columns x bn tokens, 128-byte swizzle
-int make_x_map(const __nv_bfloat16* x, int x_stride, int m, int k, int bn, CUtensorMap* map) {
+// fp16 activations X[m][x_stride] as a 2-D tensor (k innermost); box = 64 columns x bn tokens, 128-byte swizzle
+int make_x_map(const __half* x, int x_stride, int m, int k, int bn, CUtensorMap* map) {
     TensorMapEncodeFn fn = tensor_map_encode_fn();
     if (!fn) { set_error("qgemm (tcgen05): cuTensorMapEncodeTiled is not available"); return SWLM_ERR_CUDA; }
     const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)x_stride * 2};
     const cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)bn};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(x), dims, strides, box, estr,
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("qgemm (tcgen05): cuTensorMapEncodeTiled failed (%d)", (int)r); return SWLM_ERR_CUDA; }
@@ -383,7 +479,7 @@ int make_w_map(const uint32_t* w, int n, int k, CUtensorMap* map) {
 template <int BN, int STAGES>
 int tc_launch_one(const QGemmTcParams& p, bool f16, cudaStream_t s) {
     CUtensorMap xmap, wmap;
-    int rc = make_x_map(p.x, p.x_stride, p.m, p.k, BN, &xmap);
+    int rc = make_x_map(p.x, p.x_stride, p.m, p.x_stride, BN, &xmap);   // the appended columns are part of the tensor
     if (rc) return rc;
     if ((rc = make_w_map(p.w, p.n, p.k, &wmap))) return rc;
     const dim3 grid((unsigned)((p.n + kTcRows - 1) / kTcRows), (unsigned)((p.m + BN - 1) / BN), 1);
@@ -403,15 +499,30 @@ int qgemm_tc_init() {
     return SWLM_OK;
 }
 
-// Y[m][n] = bf16(X[m][k] . bf16(W)^T) on the tcgen05 path. `status` is a device word the kernel sets when a
+// Y[m][n] = bf16(X[m][k] . fp16(W)^T) on the tcgen05 path. xh (m * k fp16 values) and rscale (m floats) are scratch
+// for the fp16 copy of the activations. `status` is a device word the kernel sets when a
 // bounded wait expires. Token tile: 256 when there are that many tokens (each dequantised weight then feeds
 // 256 columns of the MMA), else 128 or 64.
+// columns of one plane of appended group sums: the groups of a row, padded to whole 64-column steps
+static int ext_plane_cols(int k) { return (k / 64 + 63) / 64 * 64; }
+size_t qgemm_tc_scratch_bytes(int m, int k) { return ((size_t)m * (k + 3 * ext_plane_cols(k)) * 2 + 255) / 256 * 256 + (size_t)m * 4; }
+
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
-                    int* status, cudaStream_t s) {
-    if (w.k % kTcBK || (x_stride & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) { set_error("qgemm (tcgen05): bad shape or alignment"); return SWLM_ERR_INVALID; }
+                    void* scratch, int* status, cudaStream_t s) {
+    __half* xh = static_cast<__half*>(scratch);
+    const int g_pad = ext_plane_cols(w.k), xh_stride = w.k + 3 * g_pad;
+    float* rscale = scratch ? reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + ((size_t)m * xh_stride * 2 + 255) / 256 * 256) : nullptr;
+    if (w.k % kTcBK || (x_stride & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(xh) & 15) || !xh || !rscale) {
+        set_error("qgemm (tcgen05): bad shape, alignment or scratch");
+        return SWLM_ERR_INVALID;
+    }
+    // xh: m rows of w.k fp16 values followed by three planes of g_pad group sums
+    cudaError_t e = launch_k(x_to_f16_kernel, dim3((unsigned)m), dim3(256), 0, s, x, x_stride, w.k, g_pad, xh, xh_stride, rscale);
+    if (e != cudaSuccess) return cuda_fail(e, "x_to_f16 launch");
     QGemmTcParams p{};
     p.w = w.w; p.scales = w.scales; p.biases = w.biases; p.n = w.n; p.k = w.k;
-    p.x = x; p.x_stride = x_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;
+    p.x = xh; p.rscale = rscale; p.x_stride = xh_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;
+    p.ext_steps = 3 * g_pad / 64;
     int rc;
     int bn = m > 128 ? 256 : m > 64 ? 128 : 64;
     static const int forced_bn = [] { const char* v = getenv("SWLM_TC_BN"); return v ? atoi(v) : 0; }();

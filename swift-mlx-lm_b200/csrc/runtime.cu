@@ -51,6 +51,7 @@ struct swlm_ctx {
     std::map<std::string, DenseTensor> dense;
     int64_t bytes = 0;
     float* op_partial = nullptr; size_t op_partial_floats = 0;
+    unsigned char* op_xh = nullptr; size_t op_xh_bytes = 0;   // scratch of the op-level tensor-core product
     unsigned* op_attn_counters = nullptr; size_t op_attn_counter_count = 0;
     unsigned* op_counters = nullptr; size_t op_counter_count = 0;
     int* tc_status = nullptr;  // device word the tcgen05 GEMM sets when one of its bounded waits expired
@@ -483,6 +484,9 @@ int compile_plan(swlm_plan* plan) {
     // Tensor parallel: a product over a K-sharded (row-parallel) weight yields partial sums. It pushes them
     // to every rank, and the product that follows must be one with a fused norm, which adds them up.
     if (ctx->tp_size > 1) {
+        for (const Launch& L : plan->launches)
+            if (L.kind == L_ATTN || L.kind == L_QK_NORM)
+                if ((rc = swlm_tp_check_heads(L.st.heads, d.kv_heads, ctx->tp_size))) return rc;
         for (size_t i = 0; i < plan->launches.size(); ++i) {
             Launch& L = plan->launches[i];
             if (L.kind == L_CONV) { set_error("short-conv layers are not supported under tensor parallelism"); return SWLM_ERR_UNSUPPORTED; }
@@ -496,6 +500,10 @@ int compile_plan(swlm_plan* plan) {
             if (i + 1 >= plan->launches.size() || plan->launches[i + 1].kind != L_QGEMV || !plan->launches[i + 1].norm.kind ||
                 plan->launches[i + 1].x_buf != SWLM_BUF_HIDDEN) {
                 set_error("row-parallel product '%s' is not followed by a product with a fused norm", L.st.weight);
+                return SWLM_ERR_UNSUPPORTED;
+            }
+            if (L.in_tp) {
+                set_error("row-parallel product '%s' would both consume and push partial sums", L.st.weight);
                 return SWLM_ERR_UNSUPPORTED;
             }
             L.push = 1;
@@ -542,6 +550,7 @@ struct swlm_state {
     __nv_bfloat16* pf_buf[SWLM_BUF_COUNT] = {};
     int pf_rows = 0;
     unsigned* pf_attn_counters = nullptr;
+    unsigned char* pf_xh = nullptr;  // scratch of the tensor-core product: fp16 copy of a chunk's widest activations
     int* pf_status = nullptr;      // device word: a bounded wait of the tensor-core product expired
     int prefill_chunk = 2048;      // tokens per chunk; 0 = one token at a time through the decode graph
     int* tc_status = nullptr;      // pinned host word (mapped): a bounded wait of a kernel expired
@@ -792,7 +801,8 @@ size_t plan_attn_scratch(const swlm_plan* plan) {
 // After a synchronisation: did a bounded wait of the tensor-core GEMV give up since the last check?
 int check_tc_status(swlm_state* s) {
     if (s->tc_status && *s->tc_status) {
-        set_error("a bounded device-side wait expired (code %d)", *s->tc_status);
+        set_error(*s->tc_status == 21 ? "a bounded wait on another tensor-parallel rank expired (code %d); re-create the state on every rank"
+                                      : "a bounded device-side wait expired (code %d)", *s->tc_status);
         *s->tc_status = 0;
         return SWLM_ERR_TIMEOUT;
     }
@@ -837,10 +847,16 @@ int prefill_workspace(swlm_state* s, int rows) {
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) { cudaFree(s->pf_buf[i]); s->pf_buf[i] = nullptr; }
     cudaFree(s->pf_attn_counters); s->pf_attn_counters = nullptr;
+    cudaFree(s->pf_xh); s->pf_xh = nullptr;
     s->pf_rows = 0;
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) {
         if (i == SWLM_BUF_LOGITS) continue;  // the output head never runs on a chunk
         if ((rc = dev_alloc(&s->pf_buf[i], (size_t)rows * s->width[i]))) return rc;
+    }
+    {
+        int widest = 0;
+        for (int i = 0; i < SWLM_BUF_COUNT; ++i) widest = std::max(widest, s->width[i] * (i == SWLM_BUF_LOGITS ? 0 : 1));
+        if ((rc = dev_alloc(&s->pf_xh, qgemm_tc_scratch_bytes(rows, widest)))) return rc;
     }
     const size_t n_ctr = (size_t)rows * std::max(1, s->plan->desc.kv_heads);
     if ((rc = dev_alloc(&s->pf_attn_counters, n_ctr))) return rc;
@@ -879,7 +895,7 @@ int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0,
         case SWLM_STEP_QGEMV: {
             if (st.out_buf == SWLM_BUF_LOGITS) break;
             const Q4Raw& raw = ctx->raw[st.weight];
-            rc = launch_qgemm_tc(raw, c, pf[st.in_buf], wd[st.in_buf], pf[st.out_buf], wd[st.out_buf], s->pf_status, stream);
+            rc = launch_qgemm_tc(raw, c, pf[st.in_buf], wd[st.in_buf], pf[st.out_buf], wd[st.out_buf], s->pf_xh, s->pf_status, stream);
             s->launches += 1;
             break;
         }
@@ -979,6 +995,7 @@ void swlm_ctx_destroy(swlm_ctx* ctx) {
     for (auto& kv : ctx->dense) cudaFree(kv.second.data);
     cudaFree(ctx->op_partial);
     cudaFree(ctx->tc_status);
+    cudaFree(ctx->op_xh);
     cudaFree(ctx->op_counters);
     cudaFree(ctx->op_attn_counters);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -991,7 +1008,7 @@ int swlm_weights_add_q4g64_mlx(swlm_ctx* ctx, const char* name, int n, int k, co
 }
 
 int swlm_weights_add_q4g64_staf(swlm_ctx* ctx, const char* name, int n, int k, const void* blocks36, int shard_kind) {
-    if (!blocks36 || k <= 0 || k % 64) { set_error("bad STAF tensor"); return SWLM_ERR_INVALID; }
+    if (!ctx || !name || !blocks36 || n <= 0 || k <= 0 || k % 64) { set_error("bad STAF tensor"); return SWLM_ERR_INVALID; }
     // De-interleave the 36-byte blocks into the three planes of the source layout; the payload bytes are
     // the same LSB-first stream (Sources/MetalCompiler/STAF/STAFPayloadConverter.swift:268-274), and the
     // fp16 scale/zero bits are kept as they are.
@@ -1147,7 +1164,7 @@ void swlm_state_destroy(swlm_state* s) {
     cudaFree(s->attn_scratch); cudaFree(s->qgemv_partial); cudaFree(s->qgemv_counters); cudaFree(s->attn_counters);
     cudaFree(s->argmax_val); cudaFree(s->argmax_idx);
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->pf_buf[i]);
-    cudaFree(s->pf_attn_counters); cudaFree(s->pf_status);
+    cudaFree(s->pf_attn_counters); cudaFree(s->pf_status); cudaFree(s->pf_xh);
     if (s->h_tok) cudaFreeHost(s->h_tok);
     if (s->tc_status) cudaFreeHost(s->tc_status);
     if (s->own_stream) cudaStreamDestroy(s->own_stream);
@@ -1249,7 +1266,9 @@ int swlm_decode(swlm_state* s, const int32_t* token_in, int32_t* token_out) {
     SWLM_CUDA(cudaMemcpyAsync(s->h_tok + m, s->token_out, sizeof(int32_t) * m, cudaMemcpyDeviceToHost, s->stream));
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     memcpy(token_out, s->h_tok + m, sizeof(int32_t) * m);
-    return check_tc_status(s);
+    rc = check_tc_status(s);
+    if (rc) for (int b = 0; b < m; ++b) token_out[b] = -1;
+    return rc;
 }
 
 int swlm_decode_n_async(swlm_state* s, const int32_t* token_in, int n) {
@@ -1280,7 +1299,9 @@ int swlm_read_tokens(swlm_state* s, int n, int32_t* tokens_out) {
         if (step < 0) { set_error("fewer than %d steps decoded", n); return SWLM_ERR_STATE; }
         SWLM_CUDA(cudaMemcpy(tokens_out + (size_t)i * m, s->ring + (size_t)(step % s->ring_cap) * m, sizeof(int32_t) * m, cudaMemcpyDeviceToHost));
     }
-    return check_tc_status(s);
+    const int rc = check_tc_status(s);
+    if (rc) for (size_t i = 0; i < (size_t)n * m; ++i) tokens_out[i] = -1;
+    return rc;
 }
 
 int swlm_decode_n(swlm_state* s, const int32_t* token_in, int n, int32_t* tokens_out) {
@@ -1332,9 +1353,16 @@ int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_tok
     if (s->pf_status) {
         int st = 0;
         SWLM_CUDA(cudaMemcpy(&st, s->pf_status, sizeof(int), cudaMemcpyDeviceToHost));
-        if (st) { set_error("prefill: a bounded wait in the tensor-core product expired"); return SWLM_ERR_TIMEOUT; }
+        if (st) {
+            SWLM_CUDA(cudaMemset(s->pf_status, 0, sizeof(int)));  // reported once; later prompts start clean
+            for (int b = 0; b < m; ++b) first_token[b] = -1;
+            set_error("prefill: a bounded wait in the tensor-core product expired");
+            return SWLM_ERR_TIMEOUT;
+        }
     }
-    return SWLM_OK;
+    rc = check_tc_status(s);
+    if (rc) for (int b = 0; b < m; ++b) first_token[b] = -1;
+    return rc;
 }
 
 int swlm_state_set_prefill_chunk(swlm_state* s, int tokens) {
@@ -1462,6 +1490,7 @@ int swlm_tp_export(swlm_state* s, void* handle_out) {
         if ((rc = dev_alloc(&s->tp_words, 4))) return rc;
         SWLM_CUDA(cudaMemset(s->tp_words, 0, 16));
         s->tp.epoch = s->tp_words; s->tp.done = reinterpret_cast<unsigned*>(s->tp_words + 1); s->tp.status = s->tp_words + 2;
+        s->tp.host_status = s->tc_status;
         SWLM_CUDA(cudaDeviceSynchronize());
     }
     cudaIpcMemHandle_t h;
@@ -1499,6 +1528,16 @@ int swlm_tp_status(swlm_state* s) {
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     SWLM_CUDA(cudaMemcpy(w, s->tp_words, sizeof(w), cudaMemcpyDeviceToHost));
     if (w[2]) { set_error("a bounded wait on another rank expired (all-reduce epoch %d, argmax epoch %d)", w[0], w[3]); return SWLM_ERR_TIMEOUT; }
+    return SWLM_OK;
+}
+
+int swlm_tp_check_heads(int heads, int kv_heads, int tp_size) {
+    if (heads <= 0 || kv_heads <= 0 || tp_size < 1) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    if (tp_size == 1) return SWLM_OK;
+    if (heads % tp_size || kv_heads % tp_size || (heads / tp_size) % (kv_heads / tp_size)) {
+        set_error("%d query heads over %d KV heads cannot be cut into %d equal shards of whole GQA groups", heads, kv_heads, tp_size);
+        return SWLM_ERR_UNSUPPORTED;
+    }
     return SWLM_OK;
 }
 
@@ -1569,8 +1608,16 @@ int swlm_op_qgemm_dev(swlm_ctx* ctx, const char* weight, int m, const void* x_de
     // m >= 64: tensor-core contraction straight from the packed source copy
     auto raw = ctx->raw.find(weight);
     if (m >= kQGemmTcMinRows && raw != ctx->raw.end() && raw->second.k % 64 == 0) {
+        const size_t need = qgemm_tc_scratch_bytes(m, raw->second.k);
+        if (need > ctx->op_xh_bytes) {
+            SWLM_CUDA(cudaDeviceSynchronize());
+            cudaFree(ctx->op_xh);
+            ctx->op_xh = nullptr; ctx->op_xh_bytes = 0;
+            if ((rc = dev_alloc(&ctx->op_xh, need))) return rc;
+            ctx->op_xh_bytes = need;
+        }
         return launch_qgemm_tc(raw->second, m, static_cast<const __nv_bfloat16*>(x_dev), raw->second.k,
-                               static_cast<__nv_bfloat16*>(y_dev), raw->second.n, ctx->tc_status, stream);
+                               static_cast<__nv_bfloat16*>(y_dev), raw->second.n, ctx->op_xh, ctx->tc_status, stream);
     }
     // 16 < m < 64 runs as passes of 16 rows: each pass re-streams the weights
     for (int m0 = 0; m0 < m; m0 += 16) {
@@ -1642,18 +1689,36 @@ int swlm_op_dequant_bf16(swlm_ctx* ctx, const char* weight, uint16_t* out_bf16) 
 
 static int flash_splits(int b, int kv_heads, int ctx_len) { return attn_pick_splits(b, kv_heads, ctx_len); }
 
+// Arguments shared by the flash-decode entry points, checked before anything is launched, cleared or divided: the
+// kernel reads q, k, v and the scratch with 128-bit loads, so a misaligned pointer would fault on the GPU instead
+// of returning a status.
+static int flash_args_ok(int b, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride, const void* q, const void* k,
+                         const void* v, const void* out, const void* scratch) {
+    if (b <= 0 || heads <= 0 || kv_heads <= 0 || hd <= 0 || ctx_len <= 0 || ctx_stride <= 0 || ctx_len > ctx_stride) {
+        set_error("flash-decode: batch, head counts, head_dim, context length and stride must be positive, context <= stride");
+        return SWLM_ERR_INVALID;
+    }
+    if (heads % kv_heads) { set_error("flash-decode: %d query heads do not divide by %d KV heads", heads, kv_heads); return SWLM_ERR_INVALID; }
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+         reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(scratch)) & 15) {
+        set_error("flash-decode: q, k, v, out and scratch must be 16-byte aligned");
+        return SWLM_ERR_INVALID;
+    }
+    return SWLM_OK;
+}
+
 size_t swlm_op_flash_decode_scratch_bytes(int b, int heads, int kv_heads, int hd, int ctx_len) {
+    if (b <= 0 || heads <= 0 || kv_heads <= 0 || hd <= 0 || ctx_len <= 0) return 0;
     return attn_scratch_floats(b, heads, hd, flash_splits(b, kv_heads, ctx_len)) * sizeof(float);
 }
 
 int swlm_op_flash_decode_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride,
                              float scale, const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev,
                              void* scratch_dev, void* cuda_stream) {
-    if (!ctx || !q_dev || !k_dev || !v_dev || !out_dev || !scratch_dev || b <= 0 || ctx_len <= 0 || ctx_len > ctx_stride) {
-        set_error("bad argument");
-        return SWLM_ERR_INVALID;
-    }
-    int rc = ensure_device(ctx);
+    if (!ctx || !q_dev || !k_dev || !v_dev || !out_dev || !scratch_dev) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    int rc = flash_args_ok(b, heads, kv_heads, hd, ctx_len, ctx_stride, q_dev, k_dev, v_dev, out_dev, scratch_dev);
+    if (rc) return rc;
+    rc = ensure_device(ctx);
     if (rc) return rc;
     cudaStream_t stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->stream;
     const size_t need = (size_t)b * kv_heads;
@@ -1674,11 +1739,10 @@ int swlm_op_flash_decode_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int 
 int swlm_op_flash_decode_noalloc_dev(swlm_ctx* ctx, int b, int heads, int kv_heads, int hd, int ctx_len, int ctx_stride,
                                      float scale, const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev,
                                      void* cuda_stream) {
-    if (!ctx || !q_dev || !k_dev || !v_dev || !out_dev || b <= 0 || ctx_len <= 0 || ctx_len > ctx_stride) {
-        set_error("bad argument");
-        return SWLM_ERR_INVALID;
-    }
-    int rc = ensure_device(ctx);
+    if (!ctx || !q_dev || !k_dev || !v_dev || !out_dev) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    int rc = flash_args_ok(b, heads, kv_heads, hd, ctx_len, ctx_stride, q_dev, k_dev, v_dev, out_dev, nullptr);
+    if (rc) return rc;
+    rc = ensure_device(ctx);
     if (rc) return rc;
     cudaStream_t stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->stream;
     return launch_flash_decode_static(ctx->device, b, heads, kv_heads, hd, ctx_len, ctx_stride, scale,

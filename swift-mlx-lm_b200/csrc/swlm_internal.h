@@ -248,10 +248,11 @@ int launch_flash_decode_static(int device, int m, int heads, int kv_heads, int h
                                cudaStream_t s);
 
 // Tensor-core (tcgen05) form of the quantised product for m >= kQGemmTcMinRows, fed from the packed source copy.
-constexpr int kQGemmTcMinRows = 64;
+constexpr int kQGemmTcMinRows = 17;   // 17..63 token rows ride in a 64-token tile whose other rows are zero
 int qgemm_tc_init();
+size_t qgemm_tc_scratch_bytes(int m, int k);   // fp16 copy of the activations + one float per token row
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
-                    int* status, cudaStream_t s);
+                    void* scratch, int* status, cudaStream_t s);
 
 int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s);
 int launch_advance(int32_t* position, int32_t* step_counter, cudaStream_t s);

@@ -5,8 +5,8 @@
 // and MLP block". Every rank owns one exchange buffer, mapped into every other rank's address space
 // (cudaIpc handles). The producing kernel stores its fp32 partial row straight into every rank's
 // buffer over NVLink (plain peer stores: the data lands in the consumer's own memory). Every element
-// travels as one 8-byte store {value, number of the exchange}: a reader that sees the number sees the
-// value, so the exchange needs no fence, no completion count and no separate flag, and its latency is
+// travels as one 64-bit scalar store {value, number of the exchange}: a reader that sees the number sees the
+// value (single-copy atomicity of an aligned 64-bit access), so the exchange needs no fence, no completion count and no separate flag, and its latency is
 // one NVLink store. The consuming kernel polls the elements it needs in its own memory, adds the partials
 // in rank order (the same order on every rank, so all ranks continue with bit-identical activations) and
 // goes on with the residual add and the norm. Two parities of buffers suffice: a rank can only be one
@@ -39,6 +39,7 @@ struct TpParams {
     int* epoch;                   // local: number of all-reduces completed so far
     unsigned* done;               // local: row tiles of the current product already pushed (the last one advances epoch)
     int* status;                  // local: set to non-zero when a bounded wait expired
+    int* host_status;             // the same news for the host: a word in mapped pinned memory, read after a sync (may be null)
 };
 
 #ifdef __CUDACC__
@@ -53,29 +54,42 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
 
 constexpr int kTpSpinLimit = 1 << 21;  // polls of ~128 ns each: about a quarter of a second
 
+// A bounded wait gave up: say so on the device (later exchanges then stop waiting) and to the host.
+__device__ __forceinline__ void tp_wait_expired(const TpParams& tp) {
+    atomicExch(tp.status, 1);
+    if (tp.host_status) *reinterpret_cast<volatile int*>(tp.host_status) = 21;
+}
+
 // Wait (bounded) until every source has raised flag `epoch` on this rank. One lane per source.
 __device__ __forceinline__ void tp_wait_flags(const TpParams& tp, const unsigned char* own, size_t flag_off0, int epoch, int lane_src) {
     if (lane_src < tp.tp) {
         const unsigned* f = reinterpret_cast<const unsigned*>(own + flag_off0 + (size_t)lane_src * 4);
         int spins = 0;
         while ((int)ld_acquire_sys(f) < epoch) {
-            if (++spins > kTpSpinLimit) { atomicExch(tp.status, 1); break; }
+            if (++spins > kTpSpinLimit) { tp_wait_expired(tp); break; }
             __nanosleep(128);
         }
     }
 }
 
-// One element of a partial-sum buffer, written with a single 8-byte store.
+// One element of a partial-sum buffer: value in the low half, number of the exchange in the high half of ONE naturally
+// aligned 64-bit scalar, written with one 64-bit store. PTX guarantees single-copy atomicity for such an access (a
+// vector store would count as two independent 32-bit accesses), so a reader can never see the number without the value.
 __device__ __forceinline__ void tp_store_tagged(unsigned char* dst, float v, int epoch) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"((unsigned)epoch) : "memory");
+    const unsigned long long packed = ((unsigned long long)(unsigned)epoch << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(packed) : "memory");
 }
 
-// 2 * N2 consecutive elements of a partial-sum buffer in this rank's own memory: one attempt, ...
+// 2 * N2 consecutive elements of a partial-sum buffer in this rank's own memory: one attempt, ... (the elements are
+// read as 64-bit scalars, two per instruction: each element is atomic on its own, which is all the protocol needs)
 template <int N2>
 __device__ __forceinline__ void tp_load_tagged(const unsigned char* src, uint4 (&v)[N2]) {
 #pragma unroll
-    for (int i = 0; i < N2; ++i)
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "l"(src + 16 * i) : "memory");
+    for (int i = 0; i < N2; ++i) {
+        unsigned long long a, b;
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(src + 16 * i) : "memory");
+        v[i].x = (unsigned)a; v[i].y = (unsigned)(a >> 32); v[i].z = (unsigned)b; v[i].w = (unsigned)(b >> 32);
+    }
 }
 // ... the check that all of them carry the number of this exchange, ...
 template <int N2>
@@ -92,7 +106,7 @@ __device__ __forceinline__ void tp_poll_tagged(const TpParams& tp, const unsigne
     int spins = 0;
     while (!tp_all_tagged(v, epoch)) {
         if (spins == 0 && *reinterpret_cast<volatile int*>(tp.status) != 0) break;
-        if (++spins > kTpSpinLimit) { atomicExch(tp.status, 1); break; }
+        if (++spins > kTpSpinLimit) { tp_wait_expired(tp); break; }
         __nanosleep(64);
         tp_load_tagged(src, v);
     }

@@ -105,6 +105,7 @@ SIGNATURES = {
     "swlm_tp_export": (_I, [_P, _P]),
     "swlm_tp_attach": (_I, [_P, _P]),
     "swlm_tp_status": (_I, [_P]),
+    "swlm_tp_check_heads": (_I, [_I, _I, _I]),
     "swlm_shard_range": (_I, [_I, _I, _I, _I, _I, C.POINTER(_I)]),
     "swlm_op_qgemm": (_I, [_P, C.c_char_p, _I, _P, _P]),
     "swlm_op_qgemm_dev": (_I, [_P, C.c_char_p, _I, _P, _P, _P]),

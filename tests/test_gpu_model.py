@@ -27,9 +27,9 @@ def small_lfm2(pkg, batch=1, max_seq=128):
                            max_seq=max_seq, max_batch=batch)
 
 
-def build_pair(pkg, oracle, cfg, seed=3):
+def build_pair(pkg, oracle, cfg, seed=3, centered=False):
     builder = pkg.DispatchPlanBuilder(cfg)
-    weights = pkg.synth_model_weights(builder, seed=seed)
+    weights = pkg.synth_model_weights(builder, seed=seed, centered=centered)
     store = pkg.WeightStore(0)
     gm = pkg.load_model(store, builder, weights)
     om = oracle.model(cfg.buffers_desc())
@@ -131,6 +131,50 @@ def test_chunked_prompt_ingestion_matches_oracle_and_token_by_token(pkg, oracle,
             assert np.linalg.norm(got - ref) <= l2_tol * np.linalg.norm(ref), what
     for got, ref in zip(conv_chunked, conv_oracle):
         assert np.linalg.norm(got - ref) <= 3e-2 * np.linalg.norm(ref)
+    gm.close(); store.close()
+
+
+@pytest.mark.parametrize("family", ["llama", "lfm2"])
+def test_chunked_and_token_by_token_ingestion_fill_the_same_cache(pkg, oracle, family):
+    """The reference's sequence-equivalence property (Tests/MetalCompilerTests/Core/AttentionSequenceEquivalenceTests
+    .swift:21-43, Conv1dSequenceEquivalenceTests.swift:21-30: a prompt ingested as a sequence leaves the caches a
+    token-by-token ingestion leaves), for this library's two ingestion paths. They cannot be equal bit for bit here:
+    the two kinds of product add their fp32 terms in different orders, which flips the bf16 rounding of an element
+    here and there (one bf16 ulp is 0.4-0.8 % of the element, and the flips compound through the layers), and a
+    chunk reads its newest K/V row back from the cache (rounded) where a decode step uses it unrounded. So the
+    property is asserted per cache row, for EVERY row: relative L2 distance at most 4e-2 (median at most 2e-2)
+    between any two of chunked ingestion, token-by-token ingestion and the oracle, on zero-mean weights (with the
+    benchmark distribution's common mean every V row is a small difference of large sums and amplifies any rounding
+    a hundredfold; that case is the test above). The conv recurrence is walked in order inside one kernel and its
+    state must agree likewise."""
+    cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=1, max_seq=256)
+    store, gm, om = build_pair(pkg, oracle, cfg, centered=True)
+    prompt = np.random.default_rng(5).integers(0, cfg.vocab, size=(1, 150), dtype=np.int32)
+    keys = [(w, layer, h) for w in (0, 1) for layer in range(cfg.kv_layer_count) for h in range(cfg.kv_heads)]
+    caches = {}
+    for mode, chunk in (("chunked", 64), ("single", 0)):
+        gm.reset_state()
+        gm.set_prefill_chunk(chunk)
+        before = gm.launches
+        first = gm.prefill(prompt)
+        if chunk:
+            assert gm.launches - before < 60 * gm.launches_per_step   # really the chunked path
+        caches[mode] = ({k: pkg.bf16_to_f32(gm.read_kv(k[0], k[1], 0, k[2], 150)) for k in keys},
+                        [pkg.bf16_to_f32(gm.read_conv(layer, 0)) for layer in range(cfg.conv_layer_count)], first)
+    o_first = om.prefill(prompt)
+    kv_oracle = {k: pkg.bf16_to_f32(om.read_kv(k[0], k[1], 0, k[2], 150)) for k in keys}
+    worst = 0.0
+    for k in keys:
+        a, b, ref = caches["chunked"][0][k], caches["single"][0][k], kv_oracle[k]
+        for name, got, want in (("chunked vs token by token", a, b), ("chunked vs oracle", a, ref), ("token by token vs oracle", b, ref)):
+            row_err = np.linalg.norm(got - want, axis=1) / np.maximum(np.linalg.norm(want, axis=1), 1e-6)
+            worst = max(worst, float(row_err.max()))
+            assert row_err.max() <= 4e-2, f"{name}, cache {k}: row {int(row_err.argmax())} rel L2 {row_err.max():.4f}"
+            assert np.median(row_err) <= 2e-2, f"{name}, cache {k}: median {np.median(row_err):.4f}"
+    for a, b in zip(caches["chunked"][1], caches["single"][1]):
+        assert np.linalg.norm(a - b) <= 3e-2 * np.linalg.norm(b)
+    assert caches["chunked"][2].tolist() == caches["single"][2].tolist() == o_first.tolist()
+    print(f"worst cache-row deviation between any two ingestion paths: {worst:.5f}")
     gm.close(); store.close()
 
 
@@ -246,11 +290,12 @@ def test_errors_surface_as_status(pkg, oracle):
 
 
 def test_full_size_llama3_8b_shape_against_oracle(pkg, oracle):
-    """The benchmark's model shape (32 layers, hidden 4096, FFN 14336, vocab 128256): a short prompt and a few
-    greedy steps against the oracle on all host cores, plus logits parity at the full vocabulary width."""
-    cfg = pkg.llama3_8b_config(max_seq=64)
+    """The benchmark's model shape (32 layers, hidden 4096, FFN 14336, vocab 128256): a short prompt and 64 greedy
+    steps against the oracle on all host cores (the oracle's token is fed to both sides), with logits parity at the
+    full vocabulary width at every step."""
+    cfg = pkg.llama3_8b_config(max_seq=80)
     store, gm, om = build_pair(pkg, oracle, cfg)
     assert store.resident_bytes > 4_221_370_368
-    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=3, steps=3)
-    assert len(mism) <= 1, mism
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=3, steps=64)
+    assert len(mism) <= 2, mism
     gm.close(); store.close()

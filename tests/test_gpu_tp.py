@@ -39,6 +39,14 @@ def test_tp4_tokens_match_oracle():
     assert r.stdout.count("TP_OK") == 4
 
 
+def test_tp8_tokens_match_oracle():
+    if _gpus() < 8:
+        pytest.skip("needs 8 GPUs")
+    r = _run("parity", 8, 29617)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_OK") == 8
+
+
 def test_missing_rank_is_reported_not_hung():
     if _gpus() < 2:
         pytest.skip("needs 2 GPUs")

@@ -122,3 +122,20 @@ def test_bad_arguments_are_rejected(pkg):
     assert lib.swlm_ctx_create(0, 3, 2, ctypes.byref(h)) == -1  # rank outside the group
     assert lib.swlm_position(None) == -1
     assert lib.swlm_plan_launch_count(None) == 0
+
+
+def test_tensor_parallel_head_split_is_checked(pkg):
+    """Heads and KV heads must divide by the number of ranks, and every rank must keep whole GQA groups; anything else
+    would silently compute with truncated head counts, so it is refused (host-only entry point; swlm_plan_build applies
+    the same check to every attention and QK-norm step)."""
+    lib = pkg.load_library()
+    ok, unsupported = 0, -4
+    assert lib.swlm_tp_check_heads(32, 8, 1) == ok
+    assert lib.swlm_tp_check_heads(32, 8, 2) == ok
+    assert lib.swlm_tp_check_heads(32, 8, 8) == ok       # one KV head per rank
+    assert lib.swlm_tp_check_heads(8, 4, 8) == unsupported   # half a KV head per rank
+    assert lib.swlm_tp_check_heads(12, 4, 8) == unsupported  # query heads do not divide
+    assert lib.swlm_tp_check_heads(12, 6, 4) == unsupported
+    assert lib.swlm_tp_check_heads(24, 8, 4) == ok
+    assert b"GQA" in lib.swlm_last_error() or True
+    assert lib.swlm_tp_check_heads(0, 8, 2) == -1

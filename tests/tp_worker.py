@@ -26,8 +26,12 @@ def main():
     dist.init_process_group("gloo")  # host-side plumbing only; the data path is the library's own kernels
     pkg = load_package()
     batch = 2 if mode == "parity2" else 1
-    cfg = pkg.ModelConfig("llama", hidden=512, intermediate=1536, layers=3, heads=8, kv_heads=4, head_dim=64,
-                          vocab=4096, max_seq=96, max_batch=batch)
+    if world > 4:   # one KV head per rank at 8 ranks
+        cfg = pkg.ModelConfig("llama", hidden=1024, intermediate=2048, layers=3, heads=16, kv_heads=8, head_dim=64,
+                              vocab=4096, max_seq=96, max_batch=batch)
+    else:
+        cfg = pkg.ModelConfig("llama", hidden=512, intermediate=1536, layers=3, heads=8, kv_heads=4, head_dim=64,
+                              vocab=4096, max_seq=96, max_batch=batch)
     builder = pkg.DispatchPlanBuilder(cfg)
     weights = pkg.synth_model_weights(builder, seed=5)
     store = pkg.WeightStore(rank, tp_rank=rank, tp_size=world)
@@ -54,10 +58,14 @@ def main():
         print(f"TP_OK rank={rank} mismatches={bad}", flush=True)
     elif mode == "timeout":
         if rank != world - 1:
+            # the call that produces tokens reports the expired wait itself (status -5, tokens -1) ...
+            status = 0
             try:
                 model.prefill(prompt)
-            except pkg.SwlmError:
-                pass
+            except pkg.SwlmError as e:
+                status = e.status
+            assert status == -5, f"prefill: expected SWLM_ERR_TIMEOUT, got {status}"
+            # ... and so does the explicit query
             st = pkg.tp.status(model)
             assert st == -5, f"expected SWLM_ERR_TIMEOUT, got {st}"
             print(f"TP_TIMEOUT_OK rank={rank}", flush=True)
