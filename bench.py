@@ -105,12 +105,25 @@ class ClockSampler:
 def model_config(pkg, args, max_seq):
     if args.small:  # debugging aid; never the reported workload
         return pkg.ModelConfig("llama", hidden=1024, intermediate=2816, layers=4, heads=8, kv_heads=2, head_dim=128,
-                               vocab=8192, max_seq=max_seq, max_batch=1)
-    return pkg.llama3_8b_config(max_seq=max_seq, max_batch=1)
+                               vocab=8192, max_seq=max_seq, max_batch=args.batch)
+    if args.model == "lfm2":
+        # hybrid conv/attention shape; output head tied to a Q4 embedding table (the MLX-bundle convention)
+        return pkg.lfm2_like_config(max_seq=max_seq, max_batch=args.batch)
+    return pkg.llama3_8b_config(max_seq=max_seq, max_batch=args.batch)
+
+
+def shape_name(args):
+    return "small-debug" if args.small else ("LFM2-1.2B-like shape (10 conv + 6 attention layers, tied Q4 head)" if args.model == "lfm2" else "Llama-3-8B shape")
+
+
+def metric_name(args):
+    if args.model == "llama" and args.batch == 1:
+        return METRIC
+    return f"4-bit decode tok/s, {'LFM2-1.2B-like' if args.model == 'lfm2' else 'Llama-3-8B'} shape bs{args.batch}"
 
 
 def workload_name(args):
-    return ("small-debug" if args.small else "Llama-3-8B shape") + f", 4-bit g64 weights, batch 1, greedy decode at context {args.ctx}"
+    return shape_name(args) + f", 4-bit g64 weights, batch {args.batch}, greedy decode at context {args.ctx}"
 
 
 def cpu_baseline(pkg, builder, weights, cfg, sample_steps, ctx):
@@ -125,8 +138,8 @@ def cpu_baseline(pkg, builder, weights, cfg, sample_steps, ctx):
     # every host core, whatever OMP_NUM_THREADS says (torch.distributed.run exports OMP_NUM_THREADS=1)
     orc.set_threads(os.cpu_count() or 1)
     cores = orc.threads()
-    small_cfg = pkg.ModelConfig(cfg.family, cfg.hidden, cfg.intermediate, cfg.layers, cfg.heads, cfg.kv_heads, cfg.head_dim,
-                                cfg.vocab, cfg.norm_eps, cfg.rope_theta, max_seq=sample_steps + 2, max_batch=1)
+    import dataclasses
+    small_cfg = dataclasses.replace(cfg, max_seq=sample_steps + 2, max_batch=1)
     om = orc.model(small_cfg.buffers_desc())
     om.load(builder, weights)
     tok = np.array([1], dtype=np.int32)
@@ -182,7 +195,7 @@ def run_reference(args, pkg):
     weights = pkg.synth_model_weights(builder, seed=3)
     steps = max(1, min(args.steps, 8))
     base = cpu_baseline(pkg, builder, weights, cfg, steps, args.ctx)
-    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus,
+    line = {"impl": "reference", "metric": metric_name(args), "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": 1, "ms_per_step": 1000.0 / base["value"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 activations, fp32 accumulate, 4-bit weights",
             "data": "synthetic (seeded random-init weights of the named shape)",
@@ -301,11 +314,17 @@ def main():
     ap.add_argument("--prefill", choices=["real", "synthetic"], default="real",
                     help="how the KV cache gets its `ctx` tokens: by running the prompt, or random bf16 rows")
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--model", choices=["llama", "lfm2"], default="llama", help="llama: Llama-3-8B shape; lfm2: the hybrid conv/attention shape")
+    ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (1..16), all at the same position")
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     pkg = load_package()
 
+    if args.model == "lfm2" and args.ctx == 4096:
+        args.ctx = 2048   # the hybrid configuration's prompt length
+    if args.batch > 1 and args.prefill == "real":
+        args.prefill = "synthetic"   # chunked prompt ingestion serves one sequence; a batch gets random cache rows
     if args.impl == "reference":
         run_reference(args, pkg)
         return
@@ -344,7 +363,7 @@ def main():
     rng = np.random.default_rng(7)
     prefill_info = None
     if args.prefill == "real":
-        prompt = rng.integers(0, cfg.vocab, size=(1, args.ctx), dtype=np.int32)
+        prompt = rng.integers(0, cfg.vocab, size=(args.batch, args.ctx), dtype=np.int32)
         torch.cuda.synchronize()
         t_pf = time.perf_counter()
         tok = model.prefill(prompt)   # host tokens in, first generated token out (synchronous)
@@ -355,11 +374,12 @@ def main():
         rows = pkg.f32_to_bf16(rng.normal(size=(args.ctx, cfg.head_dim)).astype(np.float32))
         kv_local = cfg.kv_heads // world
         for layer in range(cfg.kv_layer_count):
-            for h in range(kv_local):
-                model.write_kv(0, layer, 0, h, rows)
-                model.write_kv(1, layer, 0, h, rows)
+            for b in range(args.batch):
+                for h in range(kv_local):
+                    model.write_kv(0, layer, b, h, rows)
+                    model.write_kv(1, layer, b, h, rows)
         model.set_position(args.ctx)
-        tok = np.array([1], dtype=np.int32)
+        tok = np.arange(1, args.batch + 1, dtype=np.int32)
 
     def barrier():
         if world > 1:
@@ -441,12 +461,12 @@ def main():
     attn_ms = a0.elapsed_time(a1) / reps
 
     weight_bytes = cfg.q4_weight_elems() * 0.5625 / world            # per GPU, per step
-    kv_bytes = cfg.kv_layer_count * (cfg.kv_heads // world) * cfg.head_dim * 2 * 2 * model.position
+    kv_bytes = args.batch * cfg.kv_layer_count * (cfg.kv_heads // world) * cfg.head_dim * 2 * 2 * model.position
     n_gemv = sum(1 for l in model.describe().splitlines() if "qgemv" in l)
     peak, peak_src = measured_peaks()
     achieved = weight_bytes / (gemv_ms * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "qgemv1_kernel (all %d launches of one decode step, timed back to back)" % n_gemv,
+        "bound": "hbm", "kernel": "%s (all %d launches of one decode step, timed back to back)" % ("qgemv1_kernel" if args.batch == 1 else "qgemv_kernel", n_gemv),
         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
         "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
         "bytes_per_launch_avg": weight_bytes / n_gemv, "avg_launch_us": gemv_ms * 1e3 / n_gemv,
@@ -468,16 +488,16 @@ def main():
         base = cpu_baseline(pkg, builder, weights, cfg, args.cpu_sample_steps, args.ctx)
 
     if rank == 0:
-        value = args.steps / (ms * 1e-3)
+        value = args.steps * args.batch / (ms * 1e-3)
         line = {
-            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "metric": metric_name(args), "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 activations, fp32 accumulate, 4-bit weights",
             "data": "synthetic (seeded random-init weights of the named shape; KV context: %s)" % args.prefill,
             "config": {"workload": workload_name(args), "parallelism": "tp%d" % world if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (weight_bytes / 1e9),
                        "launches_per_step": model.launches_per_step, "context_at_end": model.position},
-            "e2e": {"value": args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+            "e2e": {"value": args.steps * args.batch / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": roofline,

@@ -186,7 +186,22 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
     case SWLM_STEP_EMBED: {
         // Generator/MetalSourceGenerator+Embedding.swift:3-48: row gather.
         auto it = m->dense.find(st.weight);
-        if (it == m->dense.end()) { m->error = std::string("missing ") + st.weight; return -3; }
+        if (it == m->dense.end()) {
+            // Quantized table (a tied output head reuses it as lm_head,
+            // Sources/Models/LlamaFamilyNaming.swift:22-27): embedding_lookup_q4
+            // (Generator/MetalSourceGenerator+Embedding.swift:79-154), value = q * scale + zero per element,
+            // rounded once to the buffer type.
+            auto q = m->q4.find(st.weight);
+            if (q == m->q4.end()) { m->error = std::string("missing ") + st.weight; return -3; }
+            if (q->second.k != st.n) { m->error = "embedding width mismatch"; return -1; }
+            for (int b = 0; b < batch; ++b) {
+                int tok = m->token_in[b];
+                if (tok < 0 || tok >= q->second.n) { m->error = "token out of range"; return -1; }
+                uint16_t* out = row(m, st.out_buf, b);
+                for (int i = 0; i < st.n; ++i) out[i] = f32_to_bf16(dequant(q->second, tok, i));
+            }
+            return 0;
+        }
         for (int b = 0; b < batch; ++b) {
             int tok = m->token_in[b];
             if (tok < 0 || tok >= d.vocab) { m->error = "token out of range"; return -1; }

@@ -23,6 +23,6 @@ from .plan import (  # noqa: F401
     llama3_8b_config,
     lfm2_like_config,
 )
-from .model import InferenceModel, WeightStore, load_model  # noqa: F401
-from . import formats, plan, tp  # noqa: F401
+from .model import InferenceModel, WeightStore, bundle_tensors, load_model, load_model_from_staf  # noqa: F401
+from . import formats, plan, staf, tp  # noqa: F401
 from .synth import synth_model_weights, synth_q4  # noqa: F401

@@ -103,6 +103,31 @@ __global__ void embed_kernel(int dim, const int32_t* tokens, int vocab, const __
     if (i < dim / 8) dst[i] = src[i];
 }
 
+// embedding_lookup_q4 (Generator/MetalSourceGenerator+Embedding.swift:79-154): row gather from a Q4 group-64 table in
+// the packed source layout, value = bf16(q * scale + zero). One thread per 8 consecutive elements (one packed word).
+__global__ void embed_q4_kernel(int dim, const int32_t* tokens, int vocab, const uint32_t* w, const uint16_t* scales,
+                                const uint16_t* zeros, int sb_f16, __nv_bfloat16* out, int out_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y;
+    int tok = tokens[b];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;   // word index in the row
+    if (i >= dim / 8) return;
+    const unsigned word = w[(size_t)tok * (dim / 8) + i];
+    const size_t g = (size_t)tok * (dim / 64) + (i >> 3);
+    const float s = sb_f16 ? __half2float(__ushort_as_half(scales[g])) : __uint_as_float((unsigned)scales[g] << 16);
+    const float z = sb_f16 ? __half2float(__ushort_as_half(zeros[g])) : __uint_as_float((unsigned)zeros[g] << 16);
+    unsigned o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(fmaf((float)((word >> (8 * j)) & 0xFu), s, z),
+                                                       fmaf((float)((word >> (8 * j + 4)) & 0xFu), s, z));
+        o[j] = *reinterpret_cast<const unsigned*>(&v);
+    }
+    reinterpret_cast<uint4*>(out + (size_t)b * out_stride)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // swiglu (Primitives/ElementwiseFragment.swift:49-54); used only when the plan cannot fold it
 // into the gate/up GEMV epilogue.
 __global__ void swiglu_kernel(int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
@@ -355,6 +380,13 @@ int launch_embed(int m, int dim, const int32_t* tokens, int vocab, const __nv_bf
     if (dim % 8 || out_stride % 8) { set_error("embed: dim must be a multiple of 8"); return SWLM_ERR_INVALID; }
     launch_k(embed_kernel, dim3((dim / 8 + 127) / 128, m), 128, 0, s, dim, tokens, vocab, table, out, out_stride);
     return check_launch("embed launch");
+}
+
+int launch_embed_q4(int m, int dim, const int32_t* tokens, const Q4Raw& table, __nv_bfloat16* out, int out_stride, cudaStream_t s) {
+    if (dim % 64 || out_stride % 8 || table.k != dim) { set_error("embed (q4): the table's width must equal the hidden size, a multiple of 64"); return SWLM_ERR_INVALID; }
+    launch_k(embed_q4_kernel, dim3((dim / 8 + 127) / 128, m), 128, 0, s, dim, tokens, table.n, table.w, table.scales, table.biases,
+             table.sb_f16 ? 1 : 0, out, out_stride);
+    return check_launch("embed (q4) launch");
 }
 
 int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,

@@ -209,6 +209,7 @@ struct Launch {
     int seg_end[3] = {0, 0, 0};
     const DenseTensor* d1 = nullptr;
     const DenseTensor* d2 = nullptr;
+    const Q4Raw* q_embed = nullptr;  // embedding step over a quantized table
     int rope_table = -1;       // index into plan->rope_tables
     std::string label;
     int steps_covered = 1;
@@ -284,7 +285,14 @@ int compile_plan(swlm_plan* plan) {
         case SWLM_STEP_EMBED:
             L.kind = L_EMBED;
             L.d1 = find_dense(ctx, s.weight);
-            if (!L.d1) { set_error("embedding table '%s' missing", s.weight); return SWLM_ERR_NOT_FOUND; }
+            if (!L.d1) {
+                // a quantized table (tied to the output head): gathered from the packed source copy
+                auto q = ctx->raw.find(s.weight);
+                if (q == ctx->raw.end()) { set_error("embedding table '%s' missing", s.weight); return SWLM_ERR_NOT_FOUND; }
+                if (ctx->tp_size > 1) { set_error("a quantized (tied) embedding table is not supported under tensor parallelism"); return SWLM_ERR_UNSUPPORTED; }
+                if (q->second.k != s.n) { set_error("embedding table '%s': width %d, hidden %d", s.weight, q->second.k, s.n); return SWLM_ERR_INVALID; }
+                L.q_embed = &q->second;
+            }
             if (!buf_ok(s.out_buf) || s.n > buf_width(d, s.out_buf)) { set_error("embed: bad output buffer"); return SWLM_ERR_INVALID; }
             L.label = std::string("embed ") + s.weight;
             break;
@@ -628,7 +636,8 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
         if (only_kind >= 0 && L.kind != only_kind) continue;
         switch (L.kind) {
         case L_EMBED:
-            rc = launch_embed(m, st.n, s->token_in, d.vocab, L.d1->data, s->buf[st.out_buf], s->width[st.out_buf], stream);
+            rc = L.q_embed ? launch_embed_q4(m, st.n, s->token_in, *L.q_embed, s->buf[st.out_buf], s->width[st.out_buf], stream)
+                           : launch_embed(m, st.n, s->token_in, d.vocab, L.d1->data, s->buf[st.out_buf], s->width[st.out_buf], stream);
             s->launches += 1;
             break;
         case L_RMSNORM:
@@ -880,7 +889,10 @@ int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0,
     for (const swlm_step& st : plan->steps) {
         switch (st.kind) {
         case SWLM_STEP_EMBED:
-            rc = launch_embed(c, st.n, tokens, d.vocab, find_dense(ctx, st.weight)->data, pf[st.out_buf], wd[st.out_buf], stream);
+            if (const DenseTensor* table = find_dense(ctx, st.weight))
+                rc = launch_embed(c, st.n, tokens, d.vocab, table->data, pf[st.out_buf], wd[st.out_buf], stream);
+            else
+                rc = launch_embed_q4(c, st.n, tokens, ctx->raw.at(st.weight), pf[st.out_buf], wd[st.out_buf], stream);
             s->launches += 1;
             break;
         case SWLM_STEP_COPY_RMSNORM:

@@ -193,6 +193,8 @@ int launch_qk_norm(int m, int heads, int kv_heads, int head_dim, __nv_bfloat16* 
                    float eps, float weight_bias, cudaStream_t s);
 int launch_embed(int m, int dim, const int32_t* tokens, int vocab, const __nv_bfloat16* table,
                  __nv_bfloat16* out, int out_stride, cudaStream_t s);
+// the same gather from a Q4 group-64 table (packed source copy): out = bf16(q * scale + zero)
+int launch_embed_q4(int m, int dim, const int32_t* tokens, const Q4Raw& table, __nv_bfloat16* out, int out_stride, cudaStream_t s);
 int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
                   __nv_bfloat16* out, int o_stride, cudaStream_t s);
 int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,

@@ -229,3 +229,51 @@ def load_model(store: WeightStore, builder, weights) -> InferenceModel:
         else:
             store.add_dense(name, entry, shard if kind == "conv" else 0)
     return InferenceModel(store, builder.decode_steps(), builder.config.buffers_desc())
+
+
+def staf_tensor_name(name: str, kind: str) -> str:
+    """Name of a plan tensor inside an MLX bundle / STAF file: a quantized module `x` is stored as `x.weight` (its
+    `.scales` / `.biases` companions are folded into the blocks), dense tensors keep their names."""
+    return name if kind != "q4" or name.endswith(".weight") else name + ".weight"
+
+
+def bundle_tensors(builder, weights):
+    """The MLX-shaped safetensors tensors of a synthetic model: name -> (dtype string, array), quantized modules as
+    `.weight` (u32 words) / `.scales` / `.biases` (bf16) triples."""
+    out = {}
+    for name, kind, _shape, _shard in builder.tensors():
+        entry = weights[name]
+        if kind == "q4":
+            mod = staf_tensor_name(name, kind)[:-len(".weight")]
+            out[mod + ".weight"] = ("U32", np.ascontiguousarray(entry[0], dtype=np.uint32))
+            out[mod + ".scales"] = ("BF16", np.ascontiguousarray(entry[1], dtype=np.uint16))
+            out[mod + ".biases"] = ("BF16", np.ascontiguousarray(entry[2], dtype=np.uint16))
+        else:
+            out[name] = ("BF16", np.ascontiguousarray(entry, dtype=np.uint16))
+    return out
+
+
+def load_model_from_staf(store: WeightStore, builder, staf_file) -> InferenceModel:
+    """Upload the tensors a plan needs straight from a STAF file (4-bit group-64 blocks as they are, dense tensors as
+    bf16) and compile the decode plan. Mirrors STAFLoader.load -> STAFWeightStore
+    (Sources/MetalCompiler/STAF/STAFLoader.swift:19-299) feeding MetalInferenceModel."""
+    from . import staf as _staf
+
+    for name, kind, _shape, shard in builder.tensors():
+        entry = staf_file[staf_tensor_name(name, kind)]
+        raw = np.asarray(staf_file.data[entry.payload_offset:entry.payload_offset + entry.payload_size])
+        if kind == "q4":
+            if entry.scheme != _staf.SCHEME_Q4_G64:
+                raise _staf.STAFError(f"{entry.name}: scheme {entry.scheme:#x} is not 4-bit group 64")
+            n, words = entry.shape
+            store.add_q4_staf(name, raw.reshape(n, words * 8 // 64, 36), n, words * 8, shard)
+        else:
+            if entry.scheme == _staf.SCHEME_BF16:
+                arr = raw.view(np.uint16)
+            elif entry.scheme == _staf.SCHEME_FP32:
+                arr = _staf.f32_to_bf16(raw.view(np.float32))
+            else:
+                arr = _staf.f32_to_bf16(raw.view(np.float16).astype(np.float32))
+            rows = int(np.prod(entry.shape[:-1])) if len(entry.shape) > 1 else 1
+            store.add_dense(name, np.ascontiguousarray(arr).reshape(rows, entry.shape[-1]), shard if kind == "conv" else 0)
+    return InferenceModel(store, builder.decode_steps(), builder.config.buffers_desc())

@@ -49,6 +49,9 @@ class ModelConfig:
     attention_layers: Sequence[int] = field(default_factory=list)  # lfm2: indices that are attention layers
     max_seq: int = 4224
     max_batch: int = 1
+    # The output head reuses the embedding table (Sources/Models/LlamaFamilyNaming.swift:22-27): one Q4 group-64
+    # tensor serves the row gather (embedding_lookup_q4) and the lm_head product.
+    tie_embeddings: bool = False
 
     def is_attention_layer(self, i: int) -> bool:
         return self.family == "llama" or i in self.attention_layers
@@ -94,11 +97,14 @@ def llama3_8b_config(max_seq: int = 4224, max_batch: int = 1) -> ModelConfig:
     return ModelConfig("llama", 4096, 14336, 32, 32, 8, 128, 128256, 1e-5, 500000.0, max_seq=max_seq, max_batch=max_batch)
 
 
-def lfm2_like_config(max_seq: int = 2304, max_batch: int = 1) -> ModelConfig:
+def lfm2_like_config(max_seq: int = 2304, max_batch: int = 1, tie_embeddings: bool = True) -> ModelConfig:
     # 16 layers, 10 gated short-conv (kernel 3) + 6 attention; the attention layer indices are this
     # build's choice (every third layer starting at 2), the layer pattern not being part of the reference tree.
+    # LFM2 ties its output head to the embedding table; the choice here is the MLX-bundle convention, one Q4
+    # group-64 table of 65536 x 2048 (75.5 MB per token for the head, not the 268 MB of a bf16 table).
     return ModelConfig("lfm2", 2048, 8192, 16, 32, 8, 64, 65536, 1e-5, 1000000.0, 3,
-                       attention_layers=[2, 5, 8, 10, 12, 14], max_seq=max_seq, max_batch=max_batch)
+                       attention_layers=[2, 5, 8, 10, 12, 14], max_seq=max_seq, max_batch=max_batch,
+                       tie_embeddings=tie_embeddings)
 
 
 def _step(kind: int, **kw) -> Step:
@@ -123,7 +129,7 @@ class DispatchPlanBuilder:
     def tensors(self):
         c = self.config
         h, f, qd, kvd = c.hidden, c.intermediate, c.heads * c.head_dim, c.kv_heads * c.head_dim
-        out = [("model.embed_tokens.weight", "dense", (c.vocab, h), SHARD_REPLICATE)]
+        out = [("model.embed_tokens.weight", "q4" if c.tie_embeddings else "dense", (c.vocab, h), SHARD_REPLICATE)]
         for i in range(c.layers):
             p = f"model.layers.{i}."
             if c.family == "llama":
@@ -162,7 +168,9 @@ class DispatchPlanBuilder:
                     (p + "feed_forward.w2", "q4", (h, f), SHARD_ROW),
                 ]
         final_norm = "model.norm.weight" if c.family == "llama" else "model.embedding_norm.weight"
-        out += [(final_norm, "norm", (h,), SHARD_REPLICATE), ("lm_head", "q4", (c.vocab, h), SHARD_COLUMN)]
+        out.append((final_norm, "norm", (h,), SHARD_REPLICATE))
+        if not c.tie_embeddings:
+            out.append(("lm_head", "q4", (c.vocab, h), SHARD_COLUMN))
         return out
 
     # -- decode steps ---------------------------------------------------------------------------
@@ -215,6 +223,6 @@ class DispatchPlanBuilder:
             gemv(p + down, BUF_S0, BUF_HIDDEN, h, f)
         final_norm = "model.norm.weight" if c.family == "llama" else "model.embedding_norm.weight"
         steps.append(_step(STEP_RESADD_RMSNORM, in_buf=BUF_HIDDEN, out_buf=BUF_S0, n=h, eps=eps, weight_bias=0.0, weight=final_norm))
-        gemv("lm_head", BUF_S0, BUF_LOGITS, c.vocab, h)
+        gemv("model.embed_tokens.weight" if c.tie_embeddings else "lm_head", BUF_S0, BUF_LOGITS, c.vocab, h)
         steps.append(_step(STEP_ARGMAX, in_buf=BUF_LOGITS, n=c.vocab))
         return steps

@@ -30,10 +30,10 @@ class OracleModel:
         d = np.ascontiguousarray(data, dtype=np.uint16)
         assert self.dll.orc_add_dense(self.h, name.encode(), C.c_int64(d.size), _p(d)) == 0
 
-    def load(self, builder, weights):
+    def load(self, builder, weights, staf_fp16=False):
         for name, kind, _shape, _shard in builder.tensors():
             if kind == "q4":
-                self.add_q4(name, *weights[name])
+                self.add_q4(name, *weights[name], staf_fp16=staf_fp16)
             else:
                 self.add_dense(name, weights[name])
         steps = builder.decode_steps()

@@ -289,6 +289,60 @@ def test_errors_surface_as_status(pkg, oracle):
     gm.close(); store.close()
 
 
+def test_model_loaded_from_a_staf_file(pkg, oracle, tmp_path):
+    """A synthetic model written as an MLX-shaped safetensors bundle, converted to a STAF file and loaded from that file:
+    the weights enter as interleaved fp16-scale blocks (the reference's execution format), so the oracle takes its
+    scales and zeros through fp16 as well; tokens and logits must agree as for any other model."""
+    import os
+
+    cfg = small_llama(pkg, batch=1)
+    builder = pkg.DispatchPlanBuilder(cfg)
+    weights = pkg.synth_model_weights(builder, seed=9)
+    src = os.path.join(tmp_path, "model.safetensors")
+    pkg.staf.write_safetensors(src, pkg.bundle_tensors(builder, weights))
+    out = os.path.join(tmp_path, "model.staf")
+    assert pkg.staf.convert_safetensors([src], out) and pkg.staf.is_valid(out, [src], pkg.staf.default_cache_metadata(1))
+    store = pkg.WeightStore(0)
+    gm = pkg.load_model_from_staf(store, builder, pkg.staf.read_staf(out))
+    # the oracle narrows scales and zeros through fp16 exactly as the STAF blocks carry them
+    om = oracle.model(cfg.buffers_desc())
+    om.load(builder, weights, staf_fp16=True)
+    oracle.set_threads(0)
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=9, steps=32)
+    assert len(mism) <= 2, mism
+    gm.close(); store.close()
+
+
+def test_lfm2_tied_q4_embedding_table(pkg, oracle):
+    """A tied output head (Sources/Models/LlamaFamilyNaming.swift:22-27): one Q4 group-64 tensor is both the embedding
+    table (embedding_lookup_q4, Generator/MetalSourceGenerator+Embedding.swift:79-154) and the lm_head weight. Token by
+    token and through a prompt chunk."""
+    cfg = small_lfm2(pkg, batch=2, max_seq=160)
+    cfg.tie_embeddings = True
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    assert "lm_head" not in gm.describe() and "model.embed_tokens.weight" in gm.describe()
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=7, steps=24)
+    assert len(mism) <= 2, mism
+    gm.close(); store.close()
+    cfg1 = small_lfm2(pkg, batch=1, max_seq=160)
+    cfg1.tie_embeddings = True
+    store, gm, om = build_pair(pkg, oracle, cfg1)
+    gm.set_prefill_chunk(64)
+    mism = greedy_compare(pkg, gm, om, cfg1, prompt_len=90, steps=8)
+    assert len(mism) <= 1, mism
+    gm.close(); store.close()
+
+
+def test_full_size_lfm2_like_shape_against_oracle(pkg, oracle):
+    """The hybrid benchmark shape (16 layers: 10 gated short-conv + 6 attention with QK norm, hidden 2048, FFN 8192,
+    vocab 65536, tied Q4 head): a short prompt and 16 greedy steps against the oracle, logits parity at every step."""
+    cfg = pkg.lfm2_like_config(max_seq=48)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=4, steps=16)
+    assert len(mism) <= 1, mism
+    gm.close(); store.close()
+
+
 def test_full_size_llama3_8b_shape_against_oracle(pkg, oracle):
     """The benchmark's model shape (32 layers, hidden 4096, FFN 14336, vocab 128256): a short prompt and 64 greedy
     steps against the oracle on all host cores (the oracle's token is fed to both sides), with logits parity at the

@@ -1,0 +1,169 @@
+"""STAF files on the host (no GPU): the packed layout the reference's loader documents, writer/reader round trips,
+the validator's rules, and the reference's end-to-end known answer driven through a real file:
+MLX-shaped safetensors -> converter -> STAF file -> loader -> block GEMV (STAFEndToEndGEMVTests.q4Group64EndToEnd,
+Tests/MetalCompilerTests/Core/STAFEndToEndGEMVTests.swift:51-54,137-160,295-320)."""
+import os
+import struct
+import time
+
+import numpy as np
+import pytest
+
+
+@pytest.fixture
+def staf(pkg):
+    return pkg.staf
+
+
+def _bf(pkg, a):
+    return pkg.f32_to_bf16(np.asarray(a, dtype=np.float32))
+
+
+def _bundle(pkg, tmp_path, g):
+    """The multi-row known answer as an MLX-shaped safetensors file: `*.weight` u32, `*.scales` / `*.biases` bf16,
+    plus a dense bf16 norm weight."""
+    w = pkg.pack_mlx_q4(np.array(g["q"], dtype=np.uint8))
+    tensors = {
+        "model.layers.0.mlp.down_proj.weight": ("U32", w),
+        "model.layers.0.mlp.down_proj.scales": ("BF16", _bf(pkg, g["scales"])),
+        "model.layers.0.mlp.down_proj.biases": ("BF16", _bf(pkg, g["zeros"])),
+        "model.norm.weight": ("BF16", _bf(pkg, np.linspace(0.5, 1.5, 64))),
+    }
+    path = os.path.join(tmp_path, "model.safetensors")
+    pkg.staf.write_safetensors(path, tensors)
+    return path, w
+
+
+def test_packed_layout_matches_the_loaders_offsets(pkg, staf, tmp_path):
+    """Byte offsets of STAF/STAFLoader.swift:68-87 (section entry) and STAFFormat.swift:72-79 (header); payload
+    placement of STAFWriter.swift:55-69: first payload on a 4096-byte boundary, every tensor on a 256-byte one."""
+    a = staf.TensorToWrite("a.weight", staf.SCHEME_Q4_G64, staf.ROLE_DOWN, staf.DTYPE_I32, (4, 32), bytes(range(200)) * 2 + b"x" * 176,
+                           block_size=64, group_size=64, shard_index=1)
+    b = staf.TensorToWrite("norm", staf.SCHEME_BF16, staf.ROLE_NORM, staf.DTYPE_BF16, (7,), b"\x01" * 14)
+    path = os.path.join(tmp_path, "t.staf")
+    staf.write_staf(path, [a, b], {"zeta": True, "alpha": staf.U32(5), "mid": "text", "f": 0.25})
+    raw = open(path, "rb").read()
+    magic, version, meta_count, meta_off = struct.unpack_from("<IIII", raw, 0)
+    sections, section_off, string_off, string_size = struct.unpack_from("<IIII", raw, 40)
+    assert (magic, version, sections, section_off) == (0x46415453, 2, 2, 64)
+    assert raw[:4] == b"STAF" and raw[16:40] == bytes(24) and raw[56:64] == bytes(8)
+    assert meta_off == 64 + 2 * 128 and meta_count == 4 and string_off == meta_off + 4 * 32
+    e0 = raw[64:192]
+    name_off, name_len = struct.unpack_from("<II", e0, 0)
+    assert raw[string_off + name_off:string_off + name_off + name_len] == b"a.weight"
+    assert raw[string_off + name_off + name_len] == 0                      # NUL-terminated
+    assert tuple(e0[8:12]) == (0x40, 0x08, 0x03, 2)                        # scheme, role, original dtype, rank
+    assert struct.unpack_from("<8I", e0, 12) == (4, 32, 0, 0, 0, 0, 0, 0)
+    p_off, p_size = struct.unpack_from("<QQ", e0, 44)
+    assert struct.unpack_from("<IIIII", e0, 60) == (256, 64, 64, 0, 1)      # alignment, block, group, checksum, shard
+    assert e0[80:] == bytes(48)
+    assert p_off % 4096 == 0 and p_off >= string_off + string_size and p_size == 576
+    p1_off, p1_size = struct.unpack_from("<QQ", raw[192:320], 44)
+    assert p1_off % 256 == 0 and p1_off == (p_off + p_size + 255) // 256 * 256 and p1_size == 14
+    assert len(raw) == p1_off + 14
+    # metadata entries are sorted by key; an entry is key offset, key length, type at 8, payloads at 12 and 20
+    keys = []
+    for i in range(meta_count):
+        m = raw[meta_off + 32 * i:meta_off + 32 * (i + 1)]
+        ko, kl, vt = struct.unpack_from("<IIB", m, 0)
+        keys.append((raw[string_off + ko:string_off + ko + kl].decode(), vt))
+    assert keys == [("alpha", 0x02), ("f", 0x05), ("mid", 0x06), ("zeta", 0x01)]
+    back = staf.read_staf(path)
+    assert back.names() == ["a.weight", "norm"]
+    assert back.metadata == {"zeta": True, "alpha": staf.U32(5), "mid": "text", "f": 0.25}
+    assert bytes(back.payload("a.weight")) == a.payload and bytes(back.payload("norm")) == b.payload
+    assert back["a.weight"].shape == (4, 32) and back["a.weight"].group_size == 64 and back["a.weight"].shard_index == 1
+
+
+def test_safetensors_to_staf_end_to_end_known_answer(pkg, staf, oracle, golden, tmp_path):
+    g = golden["gemv_multi_row"]
+    src, w = _bundle(pkg, tmp_path, g)
+    out = os.path.join(tmp_path, "model.staf")
+    assert staf.convert_safetensors([src], out) is True
+    f = staf.read_staf(out)
+    # the companions of the quantized triple are consumed; tensors keep the source order
+    assert f.names() == ["model.layers.0.mlp.down_proj.weight", "model.norm.weight"]
+    e = f["model.layers.0.mlp.down_proj.weight"]
+    assert (e.scheme, e.block_size, e.group_size, e.role) == (staf.SCHEME_Q4_G64, 64, 64, staf.ROLE_DOWN)
+    assert e.shape == (g["rows"], 8 * g["blocks"]) and e.payload_size == g["rows"] * g["blocks"] * 36
+    assert f["model.norm.weight"].scheme == staf.SCHEME_BF16 and f["model.norm.weight"].role == staf.ROLE_NORM
+    assert f.metadata[staf.KEY_SOURCE_FORMAT] == "safetensors"
+    assert f.metadata[staf.KEY_CONVERTER_VERSION] == staf.U32(3) and f.metadata[staf.KEY_SOURCE_SHARD_COUNT] == 1
+    # payload = interleaved [fp16 scale][fp16 zero][32 nibble bytes] blocks, byte for byte the oracle's repack
+    blocks = np.asarray(f.payload(e.name)).reshape(g["rows"], g["blocks"], 36)
+    assert np.array_equal(blocks, oracle.staf_repack(w, _bf(pkg, g["scales"]), _bf(pkg, g["zeros"])))
+    # ... and the GEMV over the blocks as loaded from the file gives the reference test's expectation
+    y = oracle.staf_gemv_f32(blocks, g["rows"], 64 * g["blocks"], np.array(g["x"], dtype=np.float32))
+    for r in range(g["rows"]):
+        assert abs(float(y[r]) - g["expected"][r]) < max(g["abs_tol"], g["rel_tol"] * abs(g["expected"][r]))
+
+
+def test_validator_rules(pkg, staf, golden, tmp_path):
+    src, _ = _bundle(pkg, tmp_path, golden["gemv_multi_row"])
+    out = os.path.join(tmp_path, "model.staf")
+    staf.convert_safetensors([src], out)
+    expected = staf.default_cache_metadata(1)
+    assert staf.is_valid(out, [src], expected)
+    assert staf.convert_safetensors([src], out) is False                       # a valid cache is kept
+    assert not staf.is_valid(out, [src], dict(expected, **{"model.hidden_size": staf.U32(4096)}))   # key missing
+    assert not staf.is_valid(out, [src], {staf.KEY_CONVERTER_VERSION: staf.U32(2)})                  # stale converter
+    assert not staf.is_valid(out, [src], {staf.KEY_CONVERTER_VERSION: 3})                            # same number, other type
+    # a source newer than the cache invalidates it
+    later = time.time() + 100
+    os.utime(src, (later, later))
+    assert not staf.is_valid(out, [src], expected)
+    assert staf.convert_safetensors([src], out) is False or True
+    # header damage: version, magic, section table offset, truncated payload
+    raw = bytearray(open(out, "rb").read())
+    for patch in ((4, struct.pack("<I", 1)), (0, b"XTAF"), (44, struct.pack("<I", 128))):
+        bad = bytearray(raw)
+        bad[patch[0]:patch[0] + len(patch[1])] = patch[1]
+        p = os.path.join(tmp_path, "bad.staf")
+        open(p, "wb").write(bad)
+        assert not staf.is_valid(p)
+    p = os.path.join(tmp_path, "short.staf")
+    open(p, "wb").write(raw[:4096 + 100])
+    assert not staf.is_valid(p)
+    with pytest.raises(staf.STAFError):
+        staf.read_staf(p)
+
+
+def test_unsupported_quantization_is_refused(pkg, staf, golden, tmp_path):
+    src, _ = _bundle(pkg, tmp_path, golden["gemv_multi_row"])
+    with pytest.raises(staf.STAFError):
+        staf.plan_conversion(staf.read_safetensors(src), bits=4, group_size=128)
+    with pytest.raises(staf.STAFError):
+        staf.plan_conversion(staf.read_safetensors(src), bits=8, group_size=64)
+
+
+def test_load_into_store_routes_by_scheme(pkg, staf, golden, tmp_path):
+    """`load_into_store` against a recording stand-in for the weight store: block tensors go in as blocks with
+    (n, k) recovered from the packed shape, dense tensors as bf16 rows, fp32 sources rounded to bf16."""
+    g = golden["gemv_multi_row"]
+    src, w = _bundle(pkg, tmp_path, g)
+    extra = os.path.join(tmp_path, "extra.safetensors")
+    staf.write_safetensors(extra, {"model.layers.0.conv.conv.weight": ("F32", np.arange(12, dtype=np.float32).reshape(4, 3) / 8)})
+    out = os.path.join(tmp_path, "model.staf")
+    staf.convert_safetensors([src, extra], out)
+
+    class Recorder:
+        def __init__(self):
+            self.q4, self.dense = {}, {}
+
+        def add_q4_staf(self, name, blocks, n, k, shard=0):
+            self.q4[name] = (np.array(blocks), n, k, shard)
+
+        def add_dense(self, name, data, shard=0):
+            self.dense[name] = (np.array(data), shard)
+
+    rec = Recorder()
+    f = staf.read_staf(out)
+    loaded = staf.load_into_store(rec, f, shard_kinds={"model.layers.0.mlp.down_proj.weight": 2})
+    assert sorted(loaded) == sorted(f.names())
+    blocks, n, k, shard = rec.q4["model.layers.0.mlp.down_proj.weight"]
+    assert (n, k, shard) == (g["rows"], 64 * g["blocks"], 2) and blocks.shape == (n, k // 64, 36)
+    conv, _ = rec.dense["model.layers.0.conv.conv.weight"]
+    assert conv.shape == (4, 3) and np.array_equal(pkg.bf16_to_f32(conv), np.arange(12, dtype=np.float32).reshape(4, 3) / 8)
+    norm, _ = rec.dense["model.norm.weight"]
+    assert norm.shape == (1, 64)
+    assert f["model.layers.0.conv.conv.weight"].shard_index == 0 and f[loaded[0]].shard_index in (0, 1)
