@@ -73,7 +73,11 @@ enum {
     SWLM_STEP_CONV_STATE_UPDATE = 9,
     /* argmax — Generator/MetalSourceGenerator+Sampling.swift:62-107; lowest index
        wins among equal maxima. token_out[b] = argmax(in_buf[b][0..n)). */
-    SWLM_STEP_ARGMAX = 10
+    SWLM_STEP_ARGMAX = 10,
+    /* geglu — the gated activation with GELU (tanh approximation) instead of SiLU
+       (Generator/MetalSourceGenerator+NormAndElementwise.swift:176-208, GatedActivation.geluTanh):
+       out = bf16(0.5 g (1 + tanh(0.7978845608 (g + 0.044715 g^3))) * up), g = in_buf, up = in2_buf. */
+    SWLM_STEP_GEGLU = 11
 };
 
 typedef struct swlm_step {

@@ -338,6 +338,20 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
         }
         return 0;
     }
+    case SWLM_STEP_GEGLU: {
+        // Generator/MetalSourceGenerator+NormAndElementwise.swift:176-208 (GatedActivation.geluTanh).
+        for (int b = 0; b < batch; ++b) {
+            const uint16_t* g = row(m, st.in_buf, b);
+            const uint16_t* u = row(m, st.in2_buf, b);
+            uint16_t* o = row(m, st.out_buf, b);
+            for (int i = 0; i < st.n; ++i) {
+                float gv = bf16_to_f32(g[i]);
+                float act = 0.5f * gv * (1.0f + std::tanh(0.7978845608f * (gv + 0.044715f * gv * gv * gv)));
+                o[i] = f32_to_bf16(act * bf16_to_f32(u[i]));
+            }
+        }
+        return 0;
+    }
     case SWLM_STEP_CONV_STATE_UPDATE: {
         // Generator/MetalSourceGenerator+ConvAndState.swift:49-67.
         auto it = m->dense.find(st.weight);

@@ -131,18 +131,18 @@ __global__ void embed_q4_kernel(int dim, const int32_t* tokens, int vocab, const
 // swiglu (Primitives/ElementwiseFragment.swift:49-54); used only when the plan cannot fold it
 // into the gate/up GEMV epilogue.
 __global__ void swiglu_kernel(int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
-                              __nv_bfloat16* out, int o_stride) {
+                              __nv_bfloat16* out, int o_stride, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float g = __bfloat162float(gate[(size_t)b * g_stride + i]);
     const float u = __bfloat162float(up[(size_t)b * u_stride + i]);
-    out[(size_t)b * o_stride + i] = __float2bfloat16_rn(g * (1.0f / (1.0f + expf(-g))) * u);
+    out[(size_t)b * o_stride + i] = __float2bfloat16_rn(gated_activation(g, u, act));
 }
 
 // the same, eight elements per thread with 128-bit accesses (rows of many tokens in prompt ingestion)
-__global__ void swiglu8_kernel(int n8, const uint4* gate, int g_stride8, const uint4* up, int u_stride8, uint4* out, int o_stride8) {
+__global__ void swiglu8_kernel(int n8, const uint4* gate, int g_stride8, const uint4* up, int u_stride8, uint4* out, int o_stride8, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -154,7 +154,7 @@ __global__ void swiglu8_kernel(int n8, const uint4* gate, int g_stride8, const u
     for (int j = 0; j < 4; ++j) {
         const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
         const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
-        const __nv_bfloat162 o = __floats2bfloat162_rn(g0 * (1.0f / (1.0f + expf(-g0))) * u0, g1 * (1.0f / (1.0f + expf(-g1))) * u1);
+        const __nv_bfloat162 o = __floats2bfloat162_rn(gated_activation(g0, u0, act), gated_activation(g1, u1, act));
         ow[j] = *reinterpret_cast<const unsigned*>(&o);
     }
     out[(size_t)b * o_stride8 + i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
@@ -390,14 +390,14 @@ int launch_embed_q4(int m, int dim, const int32_t* tokens, const Q4Raw& table, _
 }
 
 int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
-                  __nv_bfloat16* out, int o_stride, cudaStream_t s) {
+                  __nv_bfloat16* out, int o_stride, int act, cudaStream_t s) {
     const bool vec = !((n | g_stride | u_stride | o_stride) & 7) &&
                      !((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) & 15);
     if (vec)
         launch_k(swiglu8_kernel, dim3((n / 8 + 255) / 256, m), 256, 0, s, n / 8, reinterpret_cast<const uint4*>(gate), g_stride / 8,
-                 reinterpret_cast<const uint4*>(up), u_stride / 8, reinterpret_cast<uint4*>(out), o_stride / 8);
+                 reinterpret_cast<const uint4*>(up), u_stride / 8, reinterpret_cast<uint4*>(out), o_stride / 8, act);
     else
-        launch_k(swiglu_kernel, dim3((n + 255) / 256, m), 256, 0, s, n, gate, g_stride, up, u_stride, out, o_stride);
+        launch_k(swiglu_kernel, dim3((n + 255) / 256, m), 256, 0, s, n, gate, g_stride, up, u_stride, out, o_stride, act);
     return check_launch("swiglu launch");
 }
 

@@ -60,6 +60,16 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
 }
+__device__ __forceinline__ uint4 lds128b(unsigned sa) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sa));
+    return v;
+}
+__device__ __forceinline__ float2 lds64fb(unsigned sa) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(sa));
+    return v;
+}
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 // one instruction asks for `bytes` (a multiple of 16, 16-byte aligned) to be brought from HBM into L2
 __device__ __forceinline__ void prefetch_l2_bulk(const void* p, unsigned bytes) {
@@ -228,11 +238,13 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
     __nv_bfloat16* xsm = reinterpret_cast<__nv_bfloat16*>(smem + kRingBytes);
     float* xsum = reinterpret_cast<float*>(smem + kRingBytes + (size_t)rows_x * xs_stride * 2);
 
-    // units of this group: u = rt * si + s, s-th slice of the group's k-range; this CTA owns a contiguous
-    // share, its warps take them round-robin
+    // units of this group: u = rt * si + s, s-th slice of the group's k-range
     const int units = p.row_tiles * p.si;
-    const int u_lo = (int)(((long long)blockIdx.x * units) / gridDim.x);
-    const int u_hi = (int)(((long long)(blockIdx.x + 1) * units) / gridDim.x);
+    // dealt cyclically: CTA b takes units 8 b .. 8 b + 7, then those 8 gridDim.x further on, ... so that at any moment
+    // the whole grid reads one contiguous window of the matrix (HBM streams a sweep much faster than hundreds of
+    // separate streams: the same change took the single-sequence kernel's 28672 x 4096 product from 16.8 to 14.3 us)
+    const int u_lo = (int)blockIdx.x * kWarps, u_hi = units;
+    const int u_step = (int)gridDim.x * kWarps;
     auto open_unit = [&](UnitCursor& c) {
         if (c.u < c.u_end) {
             c.rt = c.u / p.si;
@@ -244,7 +256,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
     UnitCursor ic{u_lo + warp, u_hi, 0, 0, 0};  // issue side, runs kStages-1 stages ahead
     open_unit(ic);
     auto issue = [&](int slot) {
-        while (ic.u < ic.u_end && ic.st >= ic.st_end) { ic.u += kWarps; open_unit(ic); }
+        while (ic.u < ic.u_end && ic.st >= ic.st_end) { ic.u += u_step; open_unit(ic); }
         if (ic.u < ic.u_end) {
             unsigned char* dst = my_ring + slot * kStageBytes;
             const uint4* src = p.tiles + ((size_t)ic.rt * p.kt4_total + ic.st) * 128;
@@ -258,9 +270,8 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
 
     // Weights do not depend on the activations or on the preceding kernel: the ring starts filling at once.
     pdl_launch_dependents();
-    int issued = 0, consumed = 0;
 #pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) { issue(issued % kStages); ++issued; }
+    for (int i = 0; i < kStages - 1; ++i) issue(i);
     pdl_wait();
     // ---- x: asynchronous copy in its natural order (the tile layout was chosen so that lane t's B
     // fragments of a group are the 16 consecutive elements 16t..16t+15)-------------------------------
@@ -348,8 +359,25 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
     __syncthreads();
 
     const int s_total = p.sk * p.si;  // partial results per row tile
+    // per-lane shared-memory bases (32-bit): the ring, this lane's 16 activations of a k-tile for each of its batch rows
+    // (second half 16 bytes on), the per-group sums. A row beyond the batch points at a block of zeros with stride 0.
+    __shared__ __align__(16) unsigned zero32[8];
+    if (tid < 8) zero32[tid] = 0u;
+    __syncthreads();
+    const unsigned ring_sa = (unsigned)__cvta_generic_to_shared(my_ring);
+    const unsigned xsum_sa = (unsigned)__cvta_generic_to_shared(xsum);
+    unsigned x_lane_sa[NT], x_lane_step[NT], x_lane_second[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const bool has = 8 * nt + g < p.m;
+        x_lane_sa[nt] = has ? (unsigned)__cvta_generic_to_shared(xsm + (size_t)(8 * nt + g) * xs_stride + t * 16)
+                            : (unsigned)__cvta_generic_to_shared(zero32);
+        x_lane_step[nt] = has ? 128u : 0u;      // bytes per k-tile (64 fp16)
+        x_lane_second[nt] = has ? 16u : 0u;
+    }
+    int islot = (kStages - 1) % kStages, cslot = 0;
     UnitCursor cc{u_lo + warp, u_hi, 0, 0, 0};
-    for (; cc.u < cc.u_end; cc.u += kWarps) {
+    for (; cc.u < cc.u_end; cc.u += u_step) {
         open_unit(cc);
         const int rt = cc.rt;
         float tot[NT][4];
@@ -357,36 +385,30 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
         for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.f;
 
         for (int stg = cc.st; stg < cc.st_end; ++stg) {
-            issue(issued % kStages); ++issued;
+            issue(islot); islot = islot + 1 == kStages ? 0 : islot + 1;
             cp_async_wait<kStages - 1>();
             __syncwarp();
-            const unsigned char* st = my_ring + (consumed % kStages) * kStageBytes;
-            ++consumed;
-            const uint4* wsm = reinterpret_cast<const uint4*>(st) + lane;
-            const uint4 sA = reinterpret_cast<const uint4*>(st + 2048)[g];
-            const uint4 sB = reinterpret_cast<const uint4*>(st + 2048)[g + 8];
+            // every address of the stage is a 32-bit shared-memory address built from per-lane bases set up once
+            const unsigned st = ring_sa + cslot * kStageBytes;
+            cslot = cslot + 1 == kStages ? 0 : cslot + 1;
+            const uint4 sA = lds128b(st + 2048 + g * 16), sB = lds128b(st + 2048 + (g + 8) * 16);
             const unsigned sAw[4] = {sA.x, sA.y, sA.z, sA.w};
             const unsigned sBw[4] = {sB.x, sB.y, sB.z, sB.w};
             const int ktl0 = (stg - g0) * 4;
-            const __nv_bfloat16* xrow = xsm + ktl0 * 64 + t * 16;
-            const float* xsrow = xsum + ktl0 * COLS + 2 * t;
+            const unsigned xs_sa = xsum_sa + ktl0 * (COLS * 4);
 #pragma unroll
             for (int ti = 0; ti < 4; ++ti) {
-                const uint4 wv = wsm[ti * 32];
+                const uint4 wv = lds128b(st + lane * 16 + ti * 512);
                 const unsigned wr[4] = {wv.x, wv.y, wv.z, wv.w};
                 uint4 X0[NT], X1[NT];
                 float acc[NT][4];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-                    if (8 * nt + g < p.m) {
-                        const uint4* xp = reinterpret_cast<const uint4*>(xrow + (size_t)(8 * nt + g) * xs_stride + ti * 64);
-                        X0[nt] = xp[0];
-                        X1[nt] = xp[1];
-                    } else {
-                        X0[nt] = make_uint4(0, 0, 0, 0);
-                        X1[nt] = make_uint4(0, 0, 0, 0);
-                    }
+                    // rows beyond the batch read a block of zeros (stride 0), so the loop has no branch
+                    const unsigned xa = x_lane_sa[nt] + (ktl0 + ti) * x_lane_step[nt];
+                    X0[nt] = lds128b(xa);
+                    X1[nt] = lds128b(xa + x_lane_second[nt]);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -411,7 +433,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
                 const float zp_hi = fmaf(-1024.f, s_hi, z_hi);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    const float2 xs2 = *reinterpret_cast<const float2*>(xsrow + ti * COLS + 8 * nt);
+                    const float2 xs2 = lds64fb(xs_sa + (ti * COLS + 8 * nt + 2 * t) * 4);
                     tot[nt][0] = fmaf(s_lo, acc[nt][0], fmaf(zp_lo, xs2.x, tot[nt][0]));
                     tot[nt][1] = fmaf(s_lo, acc[nt][1], fmaf(zp_lo, xs2.y, tot[nt][1]));
                     tot[nt][2] = fmaf(s_hi, acc[nt][2], fmaf(zp_hi, xs2.x, tot[nt][2]));
@@ -490,8 +512,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) qgemv_kernel(const 
                     if (r < p.seg_end[0]) {
                         const float gate = __bfloat162float(__float2bfloat16_rn(tot[nt][e]));
                         const float up = __bfloat162float(__float2bfloat16_rn(tot[nt][2 + e]));
-                        const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
-                        p.y[0][(size_t)col * p.y_stride[0] + r] = __float2bfloat16_rn(act);
+                        p.y[0][(size_t)col * p.y_stride[0] + r] = __float2bfloat16_rn(gated_activation(gate, up, p.gated_act));
                     }
                 }
             }
@@ -864,7 +885,7 @@ __device__ __forceinline__ void qgemv1_body(const QGemvParams& p, unsigned char*
             if (r < p.seg_end[0]) {
                 const float gate = __bfloat162float(__float2bfloat16_rn(tot_lo));
                 const float up = __bfloat162float(__float2bfloat16_rn(tot_hi));
-                p.y[0][r] = __float2bfloat16_rn(gate * (1.0f / (1.0f + expf(-gate))) * up);
+                p.y[0][r] = __float2bfloat16_rn(gated_activation(gate, up, p.gated_act));
             }
         }
     }
@@ -896,7 +917,8 @@ size_t x_smem_bytes(int rows_x, int cols, int kt4, int sk) {
 
 // Persistent grid: at most occ CTAs per SM, all resident at once; work is cut into (row tile, k-slice)
 // units small enough that every SM streams the same number of bytes to within a few percent.
-QGemvConfig pick_config(const Q4Tiled& w, int m) {
+// one_k_group: the launch carries a fused norm, whose block-wide sum needs the whole activation row in one CTA group
+QGemvConfig pick_config(const Q4Tiled& w, int m, bool one_k_group = false) {
     QGemvConfig c{};
     if (m == 1) {
         // integer dot-product kernel: the whole activation vector in block floating point (2 bytes + 1/8 byte
@@ -940,6 +962,17 @@ QGemvConfig pick_config(const Q4Tiled& w, int m) {
     // a second (or further) CTA group along K only when x does not fit otherwise
     c.occ = 1; c.sk = kt4;
     bool found = false;
+    // Prefer the highest occupancy (more warps streaming per SM hide more latency) and split K across up to eight CTA
+    // groups to make the activations fit, rather than the fewest K-splits: 36.4 -> 27.7 us for 14336 x 4096 at 16
+    // sequences, 43.4 -> 32.3 us for 4096 x 14336. SWLM_BATCH_OCC_FIRST=0 restores the old preference.
+    static const bool occ_first = [] { const char* v = getenv("SWLM_BATCH_OCC_FIRST"); return !(v && v[0] == '0'); }();
+    if (occ_first) {
+        for (int occ = max_occ; occ >= 1 && !found; --occ)
+            for (int sk = 1; sk <= kt4 && sk <= (one_k_group ? 1 : 8) && !found; sk *= 2) {
+                const size_t per_cta = sm_budget / occ - 1024;
+                if ((size_t)kRingBytes + x_smem_bytes(rows_x, cols, kt4, sk) <= per_cta) { c.occ = occ; c.sk = sk; found = true; }
+            }
+    }
     for (int sk = 1; sk <= kt4 && !found; sk *= 2)
         for (int occ = max_occ; occ >= 1 && !found; --occ) {
             const size_t per_cta = sm_budget / occ - 1024;
@@ -1113,9 +1146,13 @@ int qgemv_init() {
 }
 
 size_t qgemv_scratch_floats(const Q4Tiled& w, int m) {
-    QGemvConfig c = pick_config(w, m);
-    if (c.sk * c.si <= 1 || c.cta_mode) return 0;
-    return (size_t)w.row_tiles * c.sk * c.si * 16 * (c.nt ? 8 * c.nt : 1);
+    size_t need = 0;
+    for (int one = 0; one < 2; ++one) {   // with and without a fused norm (different K splits)
+        QGemvConfig c = pick_config(w, m, one != 0);
+        if (c.sk * c.si <= 1 || c.cta_mode) continue;
+        need = std::max(need, (size_t)w.row_tiles * c.sk * c.si * 16 * (c.nt ? 8 * c.nt : 1));
+    }
+    return need;
 }
 int qgemv_counter_count(const Q4Tiled& w) { return w.row_tiles; }
 
@@ -1138,7 +1175,7 @@ static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c) {
         set_error("qgemv: x must be 16-byte aligned with a stride that is a multiple of 8 elements");
         return SWLM_ERR_INVALID;
     }
-    c = pick_config(w, a.m);
+    c = pick_config(w, a.m, a.norm.mode != 0);
     if (g_max_dyn_smem == 0 || c.smem > (size_t)g_max_dyn_smem) { set_error("qgemv: shared memory %zu exceeds the limit %d", c.smem, g_max_dyn_smem); return SWLM_ERR_INVALID; }
     if (c.sk * c.si > 1 && !c.cta_mode && (!a.partial || !a.counters)) { set_error("qgemv: split launch without scratch"); return SWLM_ERR_INVALID; }
     p = QGemvParams{};
@@ -1149,6 +1186,7 @@ static int build_params(const QGemvLaunch& a, QGemvParams& p, QGemvConfig& c) {
         p.seg_end[i] = a.seg_end[i] > 0 ? a.seg_end[i] : (i ? p.seg_end[i - 1] : 0);
     }
     p.m = a.m;
+    p.gated_act = a.gated_act;
     p.si = c.si; p.sk = c.sk; p.cta_mode = c.cta_mode;
     {
         // Ring stages requested before the wait for the preceding kernel, and stages asked into L2 up front. Both

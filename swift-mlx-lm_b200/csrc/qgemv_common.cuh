@@ -27,6 +27,7 @@ struct QGemvParams {
     float* partial;
     unsigned* counters;
     // optional fused residual-add / copy / RMSNorm in front of the product (norm_mode = step kind, 0 = none)
+    int gated_act;   // activation of the gated epilogue (GATED_ACT_*)
     int norm_mode;
     const __nv_bfloat16* res_in;
     __nv_bfloat16* res_out;

@@ -204,6 +204,7 @@ struct Launch {
     std::vector<std::string> w_names;
     int w_mode = 0;
     int epilogue = QGEMV_EPI_STORE;
+    int gated_act = GATED_ACT_SILU;
     int n_seg = 1;
     int seg_buf[3] = {-1, -1, -1};
     int seg_end[3] = {0, 0, 0};
@@ -309,17 +310,18 @@ int compile_plan(swlm_plan* plan) {
             L.kind = L_QGEMV;
             if (!buf_ok(s.in_buf) || !buf_ok(s.out_buf)) { set_error("qgemv: bad buffers"); return SWLM_ERR_INVALID; }
             // gate, up, swiglu -> one launch over row-interleaved weights with a SwiGLU epilogue
-            if (i + 2 < st.size() && st[i + 1].kind == SWLM_STEP_QGEMV && st[i + 2].kind == SWLM_STEP_SWIGLU &&
+            if (i + 2 < st.size() && st[i + 1].kind == SWLM_STEP_QGEMV && (st[i + 2].kind == SWLM_STEP_SWIGLU || st[i + 2].kind == SWLM_STEP_GEGLU) &&
                 st[i + 1].in_buf == s.in_buf && st[i + 1].k == s.k && st[i + 1].n == s.n &&
                 st[i + 2].in_buf == s.out_buf && st[i + 2].in2_buf == st[i + 1].out_buf && (s.n % 8) == 0) {
                 rc = get_tiled(ctx, {s.weight, st[i + 1].weight}, 1, &L.w);
                 if (rc) return rc;
                 L.w_names = {s.weight, st[i + 1].weight}; L.w_mode = 1;
                 L.epilogue = QGEMV_EPI_SWIGLU;
+                L.gated_act = st[i + 2].kind == SWLM_STEP_GEGLU ? GATED_ACT_GELU_TANH : GATED_ACT_SILU;
                 L.seg_buf[0] = st[i + 2].out_buf;
                 L.seg_end[0] = ctx->raw[s.weight].n;
                 L.steps_covered = 3;
-                L.label = std::string("qgemv+swiglu ") + s.weight + " ^ " + st[i + 1].weight;
+                L.label = std::string(L.gated_act ? "qgemv+geglu " : "qgemv+swiglu ") + s.weight + " ^ " + st[i + 1].weight;
                 break;
             }
             // consecutive projections of one input -> one launch over concatenated rows
@@ -367,8 +369,10 @@ int compile_plan(swlm_plan* plan) {
             L.label = "attn_decode";
             break;
         case SWLM_STEP_SWIGLU:
+        case SWLM_STEP_GEGLU:
             L.kind = L_SWIGLU;
-            L.label = "swiglu";
+            L.gated_act = s.kind == SWLM_STEP_GEGLU ? GATED_ACT_GELU_TANH : GATED_ACT_SILU;
+            L.label = L.gated_act ? "geglu" : "swiglu";
             break;
         case SWLM_STEP_CONV_STATE_UPDATE:
             L.kind = L_CONV;
@@ -609,7 +613,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
         const swlm_step& st = L.st;
         QGemvLaunch a;
         const int xb = L.norm.kind ? L.x_buf : st.in_buf;
-        a.w = L.w; a.x = s->buf[xb]; a.x_stride = s->width[xb]; a.m = m; a.epilogue = L.epilogue;
+        a.w = L.w; a.x = s->buf[xb]; a.x_stride = s->width[xb]; a.m = m; a.epilogue = L.epilogue; a.gated_act = L.gated_act;
         if (L.norm.kind) {
             a.norm.mode = L.norm.kind;
             a.norm.res_in = res_buf(s, L.res_in); a.norm.res_out = res_buf(s, L.res_out);
@@ -681,7 +685,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
         }
         case L_SWIGLU:
             rc = launch_swiglu(m, st.n, s->buf[st.in_buf], s->width[st.in_buf], s->buf[st.in2_buf], s->width[st.in2_buf],
-                               s->buf[st.out_buf], s->width[st.out_buf], stream);
+                               s->buf[st.out_buf], s->width[st.out_buf], L.gated_act, stream);
             s->launches += 1;
             break;
         case L_CONV:
@@ -939,7 +943,9 @@ int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0,
             break;
         }
         case SWLM_STEP_SWIGLU:
-            rc = launch_swiglu(c, st.n, pf[st.in_buf], wd[st.in_buf], pf[st.in2_buf], wd[st.in2_buf], pf[st.out_buf], wd[st.out_buf], stream);
+        case SWLM_STEP_GEGLU:
+            rc = launch_swiglu(c, st.n, pf[st.in_buf], wd[st.in_buf], pf[st.in2_buf], wd[st.in2_buf], pf[st.out_buf], wd[st.out_buf],
+                               st.kind == SWLM_STEP_GEGLU ? GATED_ACT_GELU_TANH : GATED_ACT_SILU, stream);
             s->launches += 1;
             break;
         case SWLM_STEP_CONV_STATE_UPDATE:

@@ -100,7 +100,17 @@ struct RepackSrc {
 int launch_repack(const RepackSrc* src, int n_src, int mode, int k, const Q4Tiled& dst, cudaStream_t s);
 int launch_untile_bf16(const Q4Tiled& t, __nv_bfloat16* out, cudaStream_t s);
 
-enum { QGEMV_EPI_STORE = 0, QGEMV_EPI_SWIGLU = 1 };
+enum { QGEMV_EPI_STORE = 0, QGEMV_EPI_SWIGLU = 1 };   // SWIGLU: the gated-activation epilogue (SiLU or GELU, see gated_act)
+enum { GATED_ACT_SILU = 0, GATED_ACT_GELU_TANH = 1 };
+#ifdef __CUDACC__
+// activation(gate) * up of the gated MLP (Generator/MetalSourceGenerator+NormAndElementwise.swift:176-208):
+// SiLU for SwiGLU, the tanh approximation of GELU for GEGLU.
+__device__ __forceinline__ float gated_activation(float g, float up, int act) {
+    const float a = act == GATED_ACT_GELU_TANH ? 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)))
+                                               : g * (1.0f / (1.0f + expf(-g)));
+    return a * up;
+}
+#endif
 
 // Weights of a later launch that this launch asks the memory system to bring from HBM into L2 while it runs
 // (its own data comes from L2 or is small, so HBM would otherwise idle). Two arrays, sizes multiples of 256.
@@ -172,6 +182,7 @@ struct QGemvLaunch {
     int seg_end[3] = {0, 0, 0};
     int m = 1;
     int epilogue = QGEMV_EPI_STORE;
+    int gated_act = GATED_ACT_SILU;   // activation of the gated epilogue
     float* partial = nullptr;     // split-K scratch, see qgemv_scratch_floats()
     unsigned* counters = nullptr; // one per CTA row group, zero between launches
     PrefetchTarget prefetch;      // batch-1 kernel only
@@ -196,7 +207,7 @@ int launch_embed(int m, int dim, const int32_t* tokens, int vocab, const __nv_bf
 // the same gather from a Q4 group-64 table (packed source copy): out = bf16(q * scale + zero)
 int launch_embed_q4(int m, int dim, const int32_t* tokens, const Q4Raw& table, __nv_bfloat16* out, int out_stride, cudaStream_t s);
 int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const __nv_bfloat16* up, int u_stride,
-                  __nv_bfloat16* out, int o_stride, cudaStream_t s);
+                  __nv_bfloat16* out, int o_stride, int act, cudaStream_t s);
 int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,
                      const __nv_bfloat16* in, int in_stride, const __nv_bfloat16* weight,
                      __nv_bfloat16* out, int out_stride, cudaStream_t s);

@@ -29,6 +29,7 @@ STEP_ATTN_DECODE = 7
 STEP_SWIGLU = 8
 STEP_CONV_STATE_UPDATE = 9
 STEP_ARGMAX = 10
+STEP_GEGLU = 11
 
 SHARD_REPLICATE, SHARD_COLUMN, SHARD_ROW, SHARD_COLUMN3 = 0, 1, 2, 3
 
@@ -52,6 +53,11 @@ class ModelConfig:
     # The output head reuses the embedding table (Sources/Models/LlamaFamilyNaming.swift:22-27): one Q4 group-64
     # tensor serves the row gather (embedding_lookup_q4) and the lm_head product.
     tie_embeddings: bool = False
+    # Gemma-style variants of the same recipe (Generator/MetalSourceGenerator+NormAndElementwise.swift:176-208):
+    # the gated MLP's activation ("silu" = SwiGLU, "gelu_tanh" = GEGLU) and the constant added to every RMSNorm
+    # weight (weightBias, 1.0 for checkpoints that store weight - 1).
+    activation: str = "silu"
+    norm_weight_bias: float = 0.0
 
     def is_attention_layer(self, i: int) -> bool:
         return self.family == "llama" or i in self.attention_layers
@@ -186,7 +192,7 @@ class DispatchPlanBuilder:
             nonlocal first
             kind = STEP_COPY_RMSNORM if first else STEP_RESADD_COPY_RMSNORM
             first = False
-            steps.append(_step(kind, in_buf=BUF_HIDDEN, out_buf=BUF_S0, n=h, eps=eps, weight_bias=0.0, weight=name))
+            steps.append(_step(kind, in_buf=BUF_HIDDEN, out_buf=BUF_S0, n=h, eps=eps, weight_bias=c.norm_weight_bias, weight=name))
 
         def gemv(name: str, src: int, dst: int, n: int, k: int):
             steps.append(_step(STEP_QGEMV, in_buf=src, out_buf=dst, n=n, k=k, weight=name))
@@ -219,10 +225,10 @@ class DispatchPlanBuilder:
                               else ("feed_forward.w1", "feed_forward.w3", "feed_forward.w2"))
             gemv(p + gate, BUF_S0, BUF_S1, f, h)
             gemv(p + up, BUF_S0, BUF_S2, f, h)
-            steps.append(_step(STEP_SWIGLU, in_buf=BUF_S1, in2_buf=BUF_S2, out_buf=BUF_S0, n=f))
+            steps.append(_step(STEP_GEGLU if c.activation == "gelu_tanh" else STEP_SWIGLU, in_buf=BUF_S1, in2_buf=BUF_S2, out_buf=BUF_S0, n=f))
             gemv(p + down, BUF_S0, BUF_HIDDEN, h, f)
         final_norm = "model.norm.weight" if c.family == "llama" else "model.embedding_norm.weight"
-        steps.append(_step(STEP_RESADD_RMSNORM, in_buf=BUF_HIDDEN, out_buf=BUF_S0, n=h, eps=eps, weight_bias=0.0, weight=final_norm))
+        steps.append(_step(STEP_RESADD_RMSNORM, in_buf=BUF_HIDDEN, out_buf=BUF_S0, n=h, eps=eps, weight_bias=c.norm_weight_bias, weight=final_norm))
         gemv("model.embed_tokens.weight" if c.tie_embeddings else "lm_head", BUF_S0, BUF_LOGITS, c.vocab, h)
         steps.append(_step(STEP_ARGMAX, in_buf=BUF_LOGITS, n=c.vocab))
         return steps

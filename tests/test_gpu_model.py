@@ -289,6 +289,26 @@ def test_errors_surface_as_status(pkg, oracle):
     gm.close(); store.close()
 
 
+@pytest.mark.parametrize("batch", [1, 3])
+def test_gemma_style_variants_geglu_and_norm_weight_bias(pkg, oracle, batch):
+    """The same recipe with the GELU-gated MLP (GEGLU) and weightBias = 1 on every RMSNorm
+    (Generator/MetalSourceGenerator+NormAndElementwise.swift:160-208): fused epilogue and fused norm prologue at
+    batch 1, the batched kernels at batch 3, and the unfused steps inside a prompt chunk."""
+    cfg = small_llama(pkg, batch=batch, max_seq=160)
+    cfg.activation = "gelu_tanh"
+    cfg.norm_weight_bias = 1.0
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    assert "geglu" in gm.describe() and "swiglu" not in gm.describe()
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=8, steps=32)
+    assert len(mism) <= 2, mism
+    if batch == 1:
+        gm.reset_state(); om.reset()
+        gm.set_prefill_chunk(64)
+        mism = greedy_compare(pkg, gm, om, cfg, prompt_len=90, steps=8)
+        assert len(mism) <= 1, mism
+    gm.close(); store.close()
+
+
 def test_model_loaded_from_a_staf_file(pkg, oracle, tmp_path):
     """A synthetic model written as an MLX-shaped safetensors bundle, converted to a STAF file and loaded from that file:
     the weights enter as interleaved fp16-scale blocks (the reference's execution format), so the oracle takes its
