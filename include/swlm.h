@@ -140,7 +140,23 @@ int swlm_write_buffer(swlm_state* state, int buf, const uint16_t* src, int count
 int swlm_read_kv(swlm_state* state, int which, int layer, int b, int head, int count, uint16_t* dst);
 int swlm_write_kv(swlm_state* state, int which, int layer, int b, int head, int count, const uint16_t* src);
 int swlm_read_conv(swlm_state* state, int layer, int b, uint16_t* dst);
+/* Sets the position of every sequence. */
 int swlm_set_position(swlm_state* state, int position);
+
+/* ---- several sequences per step, each at its own position ------------------------
+ * The reference decodes one sequence (its decode plan has one position, MetalInferenceModel.swift:9); a state with
+ * max_batch > 1 holds max_batch independent sequences (own KV rows, conv state and position) that advance together,
+ * one token each per decode step: 2..16 of them share one pass over the weights in the GEMV kernels, 17..64 take
+ * the tensor-core product with one row per sequence (single GPU). Every slot decodes on every step; a slot
+ * nobody uses is parked by swlm_state_reset_seq before it reaches max_seq. */
+int swlm_set_positions(swlm_state* state, const int32_t* positions);      /* [max_batch] */
+int swlm_get_positions(const swlm_state* state, int32_t* positions);      /* [max_batch] */
+/* Appends n prompt tokens to sequence `seq` alone, starting at that sequence's position (chunks on the tensor
+ * cores, the output head on the last token's row) and returns its next token, which is also left in the device-side
+ * input slot of that sequence; the other sequences are not touched. Single-GPU plans whose steps can run row-wise. */
+int swlm_prefill_seq(swlm_state* state, int seq, const int32_t* tokens, int n, int32_t* first_token);
+/* Position 0 and a cleared short-conv state for one sequence. */
+int swlm_state_reset_seq(swlm_state* state, int seq);
 /* Execute one plan step on the current buffers (kernel-level parity tests). */
 int swlm_run_step(swlm_state* state, const swlm_step* step, const int32_t* token_in, int32_t* token_out);
 /* Kernel launches issued by this state since creation. */

@@ -45,7 +45,7 @@ struct AttnParams {
     __nv_bfloat16* vcache;
     size_t cache_seq_stride;   // elements between sequences
     size_t cache_head_stride;  // elements between KV heads
-    const int32_t* position;   // decode: device scalar; plain: nullptr
+    const int32_t* position;   // decode: device array, one entry per sequence; plain: nullptr
     int ctx_len;               // plain: number of cached tokens
     int pos_base;              // prompt ingestion: position of the chunk's first token
     int chunk_tokens;          // prompt ingestion: tokens in the chunk
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
     if (has_v) vv = *reinterpret_cast<const uint4*>(p.v + (size_t)b * p.v_stride + (size_t)kvh * HD + (size_t)(tid - 96) * 8);
 
     // cached tokens to attend (in a decode step the new token is not among them)
-    const int n_ctx = DECODE ? p.position[0] : PREFILL ? p.pos_base + b + 1 : p.ctx_len;
+    const int n_ctx = DECODE ? p.position[b] : PREFILL ? p.pos_base + b + 1 : p.ctx_len;
     const int rope_pos = PREFILL ? p.pos_base + b : n_ctx;
 
     const __nv_bfloat16* kbase = p.kcache + (PREFILL ? 0 : (size_t)b * p.cache_seq_stride) + (size_t)kvh * p.cache_head_stride;

@@ -265,8 +265,8 @@ __global__ void argmax_final_kernel(int m, const float* pval, const int32_t* pid
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    __shared__ float best_v[16];
-    __shared__ int best_i[16];
+    __shared__ float best_v[kMaxSequences];
+    __shared__ int best_i[kMaxSequences];
     for (int b = warp; b < m; b += (blockDim.x >> 5)) {
         float best = -INFINITY;
         int bi = 0x7fffffff;
@@ -315,9 +315,9 @@ __global__ void argmax_final_kernel(int m, const float* pval, const int32_t* pid
         if (ring) ring[(size_t)(step_counter[0] % ring_cap) * m + b] = bi;
     }
     __syncthreads();
-    if (advance && threadIdx.x == 0) {
-        position[0] += 1;
-        step_counter[0] += 1;
+    if (advance) {   // every sequence has its own position
+        if (threadIdx.x < m) position[threadIdx.x] += 1;
+        if (threadIdx.x == 0) step_counter[0] += 1;
     }
 }
 
@@ -327,11 +327,11 @@ __global__ void fill_u32_kernel(uint32_t* p, size_t n, uint32_t v) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;
 }
-__global__ void advance_kernel(int32_t* position, int32_t* step_counter) {
+__global__ void advance_kernel(int m, int32_t* position, int32_t* step_counter) {
     pdl_launch_dependents();
     pdl_wait();
-    position[0] += 1;
-    if (step_counter) step_counter[0] += 1;
+    if (threadIdx.x < m) position[threadIdx.x] += 1;
+    if (step_counter && threadIdx.x == 0) step_counter[0] += 1;
 }
 
 int check_launch(const char* what) {
@@ -432,8 +432,8 @@ int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s) {
     launch_k(fill_u32_kernel, (unsigned)((n + 255) / 256), 256, 0, s, p, n, v);
     return check_launch("fill launch");
 }
-int launch_advance(int32_t* position, int32_t* step_counter, cudaStream_t s) {
-    launch_k(advance_kernel, 1, 1, 0, s, position, step_counter);
+int launch_advance(int m, int32_t* position, int32_t* step_counter, cudaStream_t s) {
+    launch_k(advance_kernel, 1, kMaxSequences, 0, s, m, position, step_counter);
     return check_launch("advance launch");
 }
 

@@ -508,7 +508,7 @@ static int ext_plane_cols(int k) { return (k / 64 + 63) / 64 * 64; }
 size_t qgemm_tc_scratch_bytes(int m, int k) { return ((size_t)m * (k + 3 * ext_plane_cols(k)) * 2 + 255) / 256 * 256 + (size_t)m * 4; }
 
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
-                    void* scratch, int* status, cudaStream_t s) {
+                    void* scratch, int* status, cudaStream_t s, bool reuse_x) {
     __half* xh = static_cast<__half*>(scratch);
     const int g_pad = ext_plane_cols(w.k), xh_stride = w.k + 3 * g_pad;
     float* rscale = scratch ? reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + ((size_t)m * xh_stride * 2 + 255) / 256 * 256) : nullptr;
@@ -517,8 +517,11 @@ int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride,
         return SWLM_ERR_INVALID;
     }
     // xh: m rows of w.k fp16 values followed by three planes of g_pad group sums
-    cudaError_t e = launch_k(x_to_f16_kernel, dim3((unsigned)m), dim3(256), 0, s, x, x_stride, w.k, g_pad, xh, xh_stride, rscale);
-    if (e != cudaSuccess) return cuda_fail(e, "x_to_f16 launch");
+    // (reuse_x: the scratch still holds the copy of these very rows, made for the product before this one)
+    if (!reuse_x) {
+        cudaError_t e = launch_k(x_to_f16_kernel, dim3((unsigned)m), dim3(256), 0, s, x, x_stride, w.k, g_pad, xh, xh_stride, rscale);
+        if (e != cudaSuccess) return cuda_fail(e, "x_to_f16 launch");
+    }
     QGemmTcParams p{};
     p.w = w.w; p.scales = w.scales; p.biases = w.biases; p.n = w.n; p.k = w.k;
     p.x = xh; p.rscale = rscale; p.x_stride = xh_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;

@@ -391,7 +391,7 @@ int compile_plan(swlm_plan* plan) {
         }
         i += L.steps_covered;
         if (L.kind == L_QGEMV) {
-            plan->qgemv_partial = std::max(plan->qgemv_partial, qgemv_scratch_floats(*L.w, m));
+            plan->qgemv_partial = std::max(plan->qgemv_partial, qgemv_scratch_floats(*L.w, std::min(m, kQGemvMaxRows)));
             plan->qgemv_counters = std::max(plan->qgemv_counters, (size_t)qgemv_counter_count(*L.w));
         }
         plan->launches.push_back(L);
@@ -554,14 +554,16 @@ struct swlm_state {
     bool tp_attached = false;
     int32_t* tp_words = nullptr;  // [0] all-reduce epoch, [1] rows-done counter, [2] status, [3] argmax epoch
     int32_t* h_tok = nullptr;  // pinned host staging, 2 * max_batch
-    int pos_host = 0;
+    std::vector<int> pos_host;   // host mirror of the per-sequence positions
     long long steps_host = 0;
     cudaGraphExec_t graph_full = nullptr, graph_body = nullptr;
+    int graph_full_launches = 0, graph_body_launches = 0;
     int64_t launches = 0;
     // prompt ingestion in chunks: activation rows for `pf_rows` tokens per logical buffer, attention scratch
     __nv_bfloat16* pf_buf[SWLM_BUF_COUNT] = {};
     int pf_rows = 0;
     unsigned* pf_attn_counters = nullptr;
+    unsigned char* wide_xh = nullptr;  // the same for a decode step of more than kQGemvMaxRows sequences
     unsigned char* pf_xh = nullptr;  // scratch of the tensor-core product: fp16 copy of a chunk's widest activations
     int* pf_status = nullptr;      // device word: a bounded wait of the tensor-core product expired
     int prefill_chunk = 2048;      // tokens per chunk; 0 = one token at a time through the decode graph
@@ -571,7 +573,7 @@ struct swlm_state {
 struct swlm_snap {
     std::vector<void*> dev;
     std::vector<size_t> bytes;
-    int pos_host = 0;
+    std::vector<int> pos_host;
 };
 
 namespace {
@@ -597,6 +599,9 @@ size_t head_begin_of(const swlm_plan* plan, bool body_only) {
     return head_begin;
 }
 
+int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos0, int seq, int head_row, bool body_only,
+                 cudaStream_t stream);
+
 // Enqueue the launches of one decode step. body_only skips the output head (lm_head + argmax) and
 // advances the position with a one-thread kernel instead.
 int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_kind = -1) {
@@ -607,6 +612,10 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
     const size_t n_launch = plan->launches.size();
     // the output head is the trailing [norm, lm_head, argmax] group
     (void)n_launch;
+    if (m > kQGemvMaxRows) {
+        if (only_kind >= 0) { set_error("per-kind timing is for plans of up to %d sequences", kQGemvMaxRows); return SWLM_ERR_UNSUPPORTED; }
+        return enqueue_rows(s, true, s->token_in, m, 0, 0, -1, body_only, stream);
+    }
     const size_t head_begin = head_begin_of(plan, body_only);
     bool advanced = false;
     auto gemv_launch_of = [&](const Launch& L) {
@@ -710,7 +719,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
         if (rc) return rc;
     }
     if (!advanced && only_kind < 0) {
-        rc = launch_advance(s->position, nullptr, stream);
+        rc = launch_advance(m, s->position, nullptr, stream);
         s->launches += 1;
     }
     return rc;
@@ -722,6 +731,7 @@ int capture_graph(swlm_state* s, bool body_only, cudaGraphExec_t* out) {
     SWLM_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_step(s, body_only, s->stream);
     cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
+    (body_only ? s->graph_body_launches : s->graph_full_launches) = (int)(s->launches - before);
     s->launches = before;  // capture does not execute
     if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
     if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
@@ -751,8 +761,8 @@ int run_graph(swlm_state* s, bool body_only) {
         if (rc) return rc;
     }
     SWLM_CUDA(cudaGraphLaunch(*g, s->stream));
-    s->launches += launches_per_step(s->plan, body_only);
-    s->pos_host += 1;
+    s->launches += body_only ? s->graph_body_launches : s->graph_full_launches;
+    for (int& p : s->pos_host) p += 1;
     s->steps_host += body_only ? 0 : 1;
     return SWLM_OK;
 }
@@ -771,7 +781,7 @@ std::vector<Region> state_regions(swlm_state* s) {
     r.push_back({s->vcache, (size_t)d.kv_layers * s->kv_layer_elems * 2});
     r.push_back({s->conv, (size_t)d.conv_layers * s->conv_layer_elems * 2});
     r.push_back({s->res2, (size_t)d.max_batch * s->width[SWLM_BUF_RESIDUAL] * 2});
-    r.push_back({s->position, 4});
+    r.push_back({s->position, (size_t)d.max_batch * 4});
     r.push_back({s->token_in, (size_t)d.max_batch * 4});
     r.push_back({s->token_out, (size_t)d.max_batch * 4});
     return r;
@@ -823,8 +833,9 @@ int check_tc_status(swlm_state* s) {
 }
 
 int check_position_room(swlm_state* s, int steps) {
-    if (s->pos_host + steps > s->plan->desc.max_seq) {
-        set_error("position %d + %d steps exceeds max_seq %d", s->pos_host, steps, s->plan->desc.max_seq);
+    const int furthest = *std::max_element(s->pos_host.begin(), s->pos_host.end());
+    if (furthest + steps > s->plan->desc.max_seq) {
+        set_error("position %d + %d steps exceeds max_seq %d", furthest, steps, s->plan->desc.max_seq);
         return SWLM_ERR_STATE;
     }
     return SWLM_OK;
@@ -840,8 +851,9 @@ int check_position_room(swlm_state* s, int steps) {
 // takes the decode graph, so the state a decode step sees afterwards is the one it would have produced itself.
 constexpr int kPrefillMinChunk = 32;
 
-bool prefill_batchable(const swlm_plan* plan) {
-    if (plan->desc.max_batch != 1 || plan->ctx->tp_size != 1 || plan->desc.head_dim > 128) return false;
+// can the plan's steps run row-wise (enqueue_rows)?
+bool rows_capable(const swlm_plan* plan) {
+    if (plan->ctx->tp_size != 1 || plan->desc.head_dim > 128) return false;
     for (const swlm_step& st : plan->steps) {
         if (st.kind == SWLM_STEP_QGEMV && st.in_buf == st.out_buf) return false;
         if (st.kind == SWLM_STEP_QGEMV && (st.k & 63)) return false;
@@ -850,12 +862,36 @@ bool prefill_batchable(const swlm_plan* plan) {
     return true;
 }
 
+bool prefill_batchable(const swlm_plan* plan) { return plan->desc.max_batch == 1 && rows_capable(plan); }
+
+int widest_activation(const swlm_state* s) {
+    int widest = 0;
+    for (int i = 0; i < SWLM_BUF_COUNT; ++i) widest = std::max(widest, s->width[i] * (i == SWLM_BUF_LOGITS ? 0 : 1));
+    return widest;
+}
+
+int ensure_pf_status(swlm_state* s) {
+    if (s->pf_status) return SWLM_OK;
+    int rc;
+    if ((rc = dev_alloc(&s->pf_status, 1))) return rc;
+    SWLM_CUDA(cudaMemset(s->pf_status, 0, sizeof(int)));
+    return SWLM_OK;
+}
+
+// after a synchronize: did a bounded wait of the tensor-core product expire? Reported once.
+int check_pf_status(swlm_state* s) {
+    if (!s->pf_status) return SWLM_OK;
+    int st = 0;
+    SWLM_CUDA(cudaMemcpy(&st, s->pf_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (!st) return SWLM_OK;
+    SWLM_CUDA(cudaMemset(s->pf_status, 0, sizeof(int)));
+    set_error("a bounded wait in the tensor-core product expired");
+    return SWLM_ERR_TIMEOUT;
+}
+
 int prefill_workspace(swlm_state* s, int rows) {
     int rc;
-    if (!s->pf_status) {
-        if ((rc = dev_alloc(&s->pf_status, 1))) return rc;
-        SWLM_CUDA(cudaMemset(s->pf_status, 0, sizeof(int)));
-    }
+    if ((rc = ensure_pf_status(s))) return rc;
     if (rows <= s->pf_rows) return SWLM_OK;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) { cudaFree(s->pf_buf[i]); s->pf_buf[i] = nullptr; }
@@ -866,11 +902,7 @@ int prefill_workspace(swlm_state* s, int rows) {
         if (i == SWLM_BUF_LOGITS) continue;  // the output head never runs on a chunk
         if ((rc = dev_alloc(&s->pf_buf[i], (size_t)rows * s->width[i]))) return rc;
     }
-    {
-        int widest = 0;
-        for (int i = 0; i < SWLM_BUF_COUNT; ++i) widest = std::max(widest, s->width[i] * (i == SWLM_BUF_LOGITS ? 0 : 1));
-        if ((rc = dev_alloc(&s->pf_xh, qgemm_tc_scratch_bytes(rows, widest)))) return rc;
-    }
+    if ((rc = dev_alloc(&s->pf_xh, qgemm_tc_scratch_bytes(rows, widest_activation(s))))) return rc;
     const size_t n_ctr = (size_t)rows * std::max(1, s->plan->desc.kv_heads);
     if ((rc = dev_alloc(&s->pf_attn_counters, n_ctr))) return rc;
     SWLM_CUDA(cudaMemset(s->pf_attn_counters, 0, n_ctr * sizeof(unsigned)));
@@ -882,15 +914,33 @@ int prefill_workspace(swlm_state* s, int rows) {
     return SWLM_OK;
 }
 
-// `c` consecutive prompt tokens of sequence 0 (ids on the device at `tokens`), the first at position pos0.
-int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0, cudaStream_t stream) {
+// The plan's steps, unfused, over `c` activation rows with the products on the tensor cores. Two uses:
+//   * chunk (wide == false): the rows are consecutive prompt tokens of sequence `seq` (ids on the device at
+//     `tokens`), the first at position pos0; causal attention over that sequence's cache, the short-conv recurrence
+//     walked in order. The output head is skipped unless `head_row` >= 0: then the final norm, the output product
+//     and argmax run on that one row and the token lands in token_out[seq] / token_in[seq].
+//   * wide (wide == true): the rows are the state's sequences (17..kMaxSequences of them) in one decode step, each
+//     at its own position: decode attention and the short-conv step per sequence, output head and argmax for all.
+int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos0, int seq, int head_row, bool body_only,
+                 cudaStream_t stream) {
     swlm_plan* plan = s->plan;
     swlm_ctx* ctx = plan->ctx;
     const swlm_buffers_desc& d = plan->desc;
-    __nv_bfloat16** pf = s->pf_buf;
+    __nv_bfloat16** pf = wide ? s->buf : s->pf_buf;
     const int* wd = s->width;
     int rc = SWLM_OK;
+    const __nv_bfloat16* converted = nullptr;  // rows whose fp16 copy the product scratch still holds
+    int converted_k = 0;
+    auto product = [&](const Q4Raw& raw, int rows, const __nv_bfloat16* x, int xs, __nv_bfloat16* y, int ys) {
+        const bool reuse = converted == x && converted_k == raw.k;
+        const int r = launch_qgemm_tc(raw, rows, x, xs, y, ys, wide ? s->wide_xh : s->pf_xh, s->pf_status, stream, reuse);
+        converted = x; converted_k = raw.k;
+        s->launches += reuse ? 1 : 2;
+        return r;
+    };
+    bool advanced = false;
     for (const swlm_step& st : plan->steps) {
+        const bool is_product = st.kind == SWLM_STEP_QGEMV;
         switch (st.kind) {
         case SWLM_STEP_EMBED:
             if (const DenseTensor* table = find_dense(ctx, st.weight))
@@ -905,14 +955,27 @@ int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0,
                                 find_dense(ctx, st.weight)->data, st.eps, st.weight_bias, pf[st.out_buf], wd[st.out_buf], stream);
             s->launches += 1;
             break;
-        case SWLM_STEP_RESADD_RMSNORM:  // final norm: part of the output head, which only the last token runs
-        case SWLM_STEP_ARGMAX:
-            break;
-        case SWLM_STEP_QGEMV: {
-            if (st.out_buf == SWLM_BUF_LOGITS) break;
-            const Q4Raw& raw = ctx->raw[st.weight];
-            rc = launch_qgemm_tc(raw, c, pf[st.in_buf], wd[st.in_buf], pf[st.out_buf], wd[st.out_buf], s->pf_xh, s->pf_status, stream);
+        case SWLM_STEP_RESADD_RMSNORM: {  // final norm: part of the output head
+            if (wide ? body_only : head_row < 0) break;
+            const int r0 = wide ? 0 : head_row, rows = wide ? c : 1;
+            rc = launch_rmsnorm(st.kind, rows, st.n, pf[st.in_buf] + (size_t)r0 * wd[st.in_buf], wd[st.in_buf],
+                                pf[SWLM_BUF_RESIDUAL] + (size_t)r0 * wd[SWLM_BUF_RESIDUAL], wd[SWLM_BUF_RESIDUAL],
+                                find_dense(ctx, st.weight)->data, st.eps, st.weight_bias,
+                                pf[st.out_buf] + (size_t)r0 * wd[st.out_buf], wd[st.out_buf], stream);
             s->launches += 1;
+            break;
+        }
+        case SWLM_STEP_QGEMV: {
+            const Q4Raw& raw = ctx->raw[st.weight];
+            if (st.out_buf == SWLM_BUF_LOGITS) {
+                if (wide ? body_only : head_row < 0) break;
+                // the logits buffer belongs to the state (one row per sequence), also for a chunk's last token
+                if (wide) rc = product(raw, c, pf[st.in_buf], wd[st.in_buf], s->buf[SWLM_BUF_LOGITS], wd[SWLM_BUF_LOGITS]);
+                else rc = product(raw, 1, pf[st.in_buf] + (size_t)head_row * wd[st.in_buf], wd[st.in_buf],
+                                  s->buf[SWLM_BUF_LOGITS] + (size_t)seq * wd[SWLM_BUF_LOGITS], wd[SWLM_BUF_LOGITS]);
+                break;
+            }
+            rc = product(raw, c, pf[st.in_buf], wd[st.in_buf], pf[st.out_buf], wd[st.out_buf]);
             break;
         }
         case SWLM_STEP_QK_NORM:
@@ -933,13 +996,16 @@ int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0,
             a.q = pf[st.in_buf]; a.q_stride = wd[st.in_buf];
             a.k = pf[st.in2_buf]; a.k_stride = wd[st.in2_buf];
             a.v = pf[st.in3_buf]; a.v_stride = wd[st.in3_buf];
-            a.kcache = s->kcache + (size_t)st.layer * s->kv_layer_elems;
-            a.vcache = s->vcache + (size_t)st.layer * s->kv_layer_elems;
-            a.max_seq = d.max_seq; a.position = s->position; a.pos_base = pos0;
+            const size_t seq_elems = s->kv_layer_elems / d.max_batch;
+            a.kcache = s->kcache + (size_t)st.layer * s->kv_layer_elems + (wide ? 0 : (size_t)seq * seq_elems);
+            a.vcache = s->vcache + (size_t)st.layer * s->kv_layer_elems + (wide ? 0 : (size_t)seq * seq_elems);
+            a.max_seq = d.max_seq; a.position = s->position; a.pos_base = wide ? -1 : pos0;
             a.out = pf[st.out_buf]; a.out_stride = wd[st.out_buf];
-            a.scratch = s->attn_scratch; a.counters = s->pf_attn_counters; a.splits = 1;
+            a.scratch = s->attn_scratch;
+            a.counters = wide ? s->attn_counters : s->pf_attn_counters;
+            a.splits = wide ? plan->attn_splits : 1;
             rc = launch_attn_decode(a, stream);
-            s->launches += 2;
+            s->launches += wide ? 1 : 2;
             break;
         }
         case SWLM_STEP_SWIGLU:
@@ -949,19 +1015,47 @@ int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0,
             s->launches += 1;
             break;
         case SWLM_STEP_CONV_STATE_UPDATE:
-            rc = launch_conv_prefill(c, st.n, st.conv_kernel, s->conv + (size_t)st.layer * s->conv_layer_elems, pf[st.in_buf], wd[st.in_buf],
-                                     find_dense(ctx, st.weight)->data, pf[st.out_buf], wd[st.out_buf], stream);
+            if (wide)
+                rc = launch_conv_step(c, st.n, st.conv_kernel, s->conv + (size_t)st.layer * s->conv_layer_elems,
+                                      (size_t)d.conv_kernel * d.conv_dim, pf[st.in_buf], wd[st.in_buf], find_dense(ctx, st.weight)->data,
+                                      pf[st.out_buf], wd[st.out_buf], stream);
+            else
+                rc = launch_conv_prefill(c, st.n, st.conv_kernel,
+                                         s->conv + (size_t)st.layer * s->conv_layer_elems + (size_t)seq * d.conv_kernel * d.conv_dim,
+                                         pf[st.in_buf], wd[st.in_buf], find_dense(ctx, st.weight)->data, pf[st.out_buf], wd[st.out_buf], stream);
             s->launches += 1;
             break;
+        case SWLM_STEP_ARGMAX:
+            if (wide ? body_only : head_row < 0) break;
+            if (wide) {
+                rc = launch_argmax(c, st.n, s->buf[st.in_buf], wd[st.in_buf], s->token_out, s->token_in, s->ring, s->step_counter,
+                                   s->ring_cap, s->position, 1, s->argmax_val, s->argmax_idx, s->tp, nullptr, 0, stream);
+                advanced = true;
+            } else {
+                rc = launch_argmax(1, st.n, s->buf[st.in_buf] + (size_t)seq * wd[st.in_buf], wd[st.in_buf], s->token_out + seq,
+                                   s->token_in + seq, nullptr, s->step_counter, s->ring_cap, s->position, 0, s->argmax_val,
+                                   s->argmax_idx, s->tp, nullptr, 0, stream);
+            }
+            s->launches += 2;
+            break;
         default:
-            set_error("prompt ingestion: step kind %d", st.kind);
+            set_error("row-wise plan: step kind %d", st.kind);
             return SWLM_ERR_UNSUPPORTED;
         }
         if (rc) return rc;
+        if (!is_product) converted = nullptr;
     }
-    rc = launch_fill_u32(reinterpret_cast<uint32_t*>(s->position), 1, (uint32_t)(pos0 + c), stream);
-    s->launches += 1;
+    if (wide) {
+        if (!advanced) { rc = launch_advance(c, s->position, nullptr, stream); s->launches += 1; }
+    } else {
+        rc = launch_fill_u32(reinterpret_cast<uint32_t*>(s->position + seq), 1, (uint32_t)(pos0 + c), stream);
+        s->launches += 1;
+    }
     return rc;
+}
+
+int enqueue_prefill_chunk(swlm_state* s, const int32_t* tokens, int c, int pos0, int seq, cudaStream_t stream, int head_row = -1) {
+    return enqueue_rows(s, false, tokens, c, pos0, seq, head_row, false, stream);
 }
 
 }  // namespace
@@ -1070,7 +1164,8 @@ int64_t swlm_weights_bytes(const swlm_ctx* ctx) { return ctx ? ctx->bytes : 0; }
 int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const swlm_buffers_desc* desc, swlm_plan** out) {
     if (!ctx || !steps || n_steps <= 0 || !desc || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
     *out = nullptr;
-    if (desc->max_batch < 1 || desc->max_batch > 16) { set_error("max_batch %d outside 1..16", desc->max_batch); return SWLM_ERR_INVALID; }
+    if (desc->max_batch < 1 || desc->max_batch > kMaxSequences) { set_error("max_batch %d outside 1..%d", desc->max_batch, kMaxSequences); return SWLM_ERR_INVALID; }
+    if (desc->max_batch > kQGemvMaxRows && ctx->tp_size > 1) { set_error("more than %d sequences per step are not supported under tensor parallelism", kQGemvMaxRows); return SWLM_ERR_UNSUPPORTED; }
     if (desc->hidden % 8 || desc->slot_dim % 8 || desc->vocab % 8) { set_error("hidden, slot_dim and vocab must be multiples of 8"); return SWLM_ERR_INVALID; }
     int rc = ensure_device(ctx);
     if (rc) return rc;
@@ -1139,7 +1234,8 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     s->conv_layer_elems = (size_t)d.max_batch * d.conv_kernel * d.conv_dim;
     if ((rc = dev_alloc(&s->conv, (size_t)d.conv_layers * s->conv_layer_elems))) return fail(rc);
     if ((rc = dev_alloc(&s->res2, (size_t)d.max_batch * s->width[SWLM_BUF_RESIDUAL]))) return fail(rc);
-    if ((rc = dev_alloc(&s->position, 1))) return fail(rc);
+    if ((rc = dev_alloc(&s->position, d.max_batch))) return fail(rc);
+    s->pos_host.assign(d.max_batch, 0);
     if ((rc = dev_alloc(&s->step_counter, 1))) return fail(rc);
     if ((rc = dev_alloc(&s->token_in, d.max_batch))) return fail(rc);
     if ((rc = dev_alloc(&s->token_out, d.max_batch))) return fail(rc);
@@ -1149,6 +1245,10 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     {
         cudaError_t ce = cudaMemset(s->attn_counters, 0, (size_t)d.max_batch * std::max(1, d.kv_heads) * sizeof(unsigned));
         if (ce != cudaSuccess) return fail(cuda_fail(ce, "cudaMemset"));
+    }
+    if (d.max_batch > kQGemvMaxRows) {
+        if ((rc = ensure_pf_status(s))) return fail(rc);
+        if ((rc = dev_alloc(&s->wide_xh, qgemm_tc_scratch_bytes(d.max_batch, widest_activation(s))))) return fail(rc);
     }
     if ((rc = dev_alloc(&s->argmax_val, argmax_scratch_elems(d.max_batch)))) return fail(rc);
     if ((rc = dev_alloc(&s->argmax_idx, argmax_scratch_elems(d.max_batch)))) return fail(rc);
@@ -1182,7 +1282,7 @@ void swlm_state_destroy(swlm_state* s) {
     cudaFree(s->attn_scratch); cudaFree(s->qgemv_partial); cudaFree(s->qgemv_counters); cudaFree(s->attn_counters);
     cudaFree(s->argmax_val); cudaFree(s->argmax_idx);
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->pf_buf[i]);
-    cudaFree(s->pf_attn_counters); cudaFree(s->pf_status); cudaFree(s->pf_xh);
+    cudaFree(s->pf_attn_counters); cudaFree(s->pf_status); cudaFree(s->pf_xh); cudaFree(s->wide_xh);
     if (s->h_tok) cudaFreeHost(s->h_tok);
     if (s->tc_status) cudaFreeHost(s->tc_status);
     if (s->own_stream) cudaStreamDestroy(s->own_stream);
@@ -1207,7 +1307,7 @@ int swlm_state_reset(swlm_state* s) {
         if (r.bytes) SWLM_CUDA(cudaMemsetAsync(r.p, 0, r.bytes, s->stream));
     SWLM_CUDA(cudaMemsetAsync(s->step_counter, 0, 4, s->stream));
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
-    s->pos_host = 0;
+    std::fill(s->pos_host.begin(), s->pos_host.end(), 0);
     s->steps_host = 0;
     return SWLM_OK;
 }
@@ -1254,13 +1354,28 @@ void swlm_snap_destroy(swlm_snap* snap) {
     delete snap;
 }
 
-int swlm_position(const swlm_state* s) { return s ? s->pos_host : -1; }
+int swlm_position(const swlm_state* s) { return s ? s->pos_host[0] : -1; }
 
 int swlm_set_position(swlm_state* s, int position) {
     if (!s || position < 0 || position > s->plan->desc.max_seq) { set_error("bad position"); return SWLM_ERR_INVALID; }
-    SWLM_CUDA(cudaMemcpyAsync(s->position, &position, 4, cudaMemcpyHostToDevice, s->stream));
+    std::vector<int32_t> all(s->plan->desc.max_batch, position);
+    return swlm_set_positions(s, all.data());
+}
+
+int swlm_set_positions(swlm_state* s, const int32_t* positions) {
+    if (!s || !positions) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    const int m = s->plan->desc.max_batch;
+    for (int b = 0; b < m; ++b)
+        if (positions[b] < 0 || positions[b] > s->plan->desc.max_seq) { set_error("bad position %d of sequence %d", positions[b], b); return SWLM_ERR_INVALID; }
+    SWLM_CUDA(cudaMemcpyAsync(s->position, positions, sizeof(int32_t) * m, cudaMemcpyHostToDevice, s->stream));
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
-    s->pos_host = position;
+    s->pos_host.assign(positions, positions + m);
+    return SWLM_OK;
+}
+
+int swlm_get_positions(const swlm_state* s, int32_t* positions) {
+    if (!s || !positions) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    std::copy(s->pos_host.begin(), s->pos_host.end(), positions);
     return SWLM_OK;
 }
 
@@ -1285,6 +1400,7 @@ int swlm_decode(swlm_state* s, const int32_t* token_in, int32_t* token_out) {
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     memcpy(token_out, s->h_tok + m, sizeof(int32_t) * m);
     rc = check_tc_status(s);
+    if (!rc) rc = check_pf_status(s);
     if (rc) for (int b = 0; b < m; ++b) token_out[b] = -1;
     return rc;
 }
@@ -1317,7 +1433,8 @@ int swlm_read_tokens(swlm_state* s, int n, int32_t* tokens_out) {
         if (step < 0) { set_error("fewer than %d steps decoded", n); return SWLM_ERR_STATE; }
         SWLM_CUDA(cudaMemcpy(tokens_out + (size_t)i * m, s->ring + (size_t)(step % s->ring_cap) * m, sizeof(int32_t) * m, cudaMemcpyDeviceToHost));
     }
-    const int rc = check_tc_status(s);
+    int rc = check_tc_status(s);
+    if (!rc) rc = check_pf_status(s);
     if (rc) for (size_t i = 0; i < (size_t)n * m; ++i) tokens_out[i] = -1;
     return rc;
 }
@@ -1355,8 +1472,8 @@ int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_tok
         while (n - 1 - t >= kPrefillMinChunk) {
             const int c = std::min(s->prefill_chunk, n - 1 - t);
             if ((rc = prefill_workspace(s, std::min(s->prefill_chunk, n - 1)))) return rc;
-            if ((rc = enqueue_prefill_chunk(s, s->prompt + t, c, s->pos_host, s->stream))) return rc;
-            s->pos_host += c;
+            if ((rc = enqueue_prefill_chunk(s, s->prompt + t, c, s->pos_host[0], 0, s->stream))) return rc;
+            s->pos_host[0] += c;
             t += c;
         }
     }
@@ -1368,19 +1485,65 @@ int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_tok
     SWLM_CUDA(cudaMemcpyAsync(s->h_tok + m, s->token_out, sizeof(int32_t) * m, cudaMemcpyDeviceToHost, s->stream));
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     memcpy(first_token, s->h_tok + m, sizeof(int32_t) * m);
-    if (s->pf_status) {
-        int st = 0;
-        SWLM_CUDA(cudaMemcpy(&st, s->pf_status, sizeof(int), cudaMemcpyDeviceToHost));
-        if (st) {
-            SWLM_CUDA(cudaMemset(s->pf_status, 0, sizeof(int)));  // reported once; later prompts start clean
-            for (int b = 0; b < m; ++b) first_token[b] = -1;
-            set_error("prefill: a bounded wait in the tensor-core product expired");
-            return SWLM_ERR_TIMEOUT;
-        }
+    if ((rc = check_pf_status(s))) {
+        for (int b = 0; b < m; ++b) first_token[b] = -1;
+        return rc;
     }
     rc = check_tc_status(s);
     if (rc) for (int b = 0; b < m; ++b) first_token[b] = -1;
     return rc;
+}
+
+int swlm_prefill_seq(swlm_state* s, int seq, const int32_t* tokens, int n, int32_t* first_token) {
+    if (!s || !tokens || !first_token || n <= 0) { set_error("bad argument"); return SWLM_ERR_INVALID; }
+    *first_token = -1;
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (seq < 0 || seq >= d.max_batch) { set_error("sequence %d outside 0..%d", seq, d.max_batch - 1); return SWLM_ERR_INVALID; }
+    if (!rows_capable(s->plan)) { set_error("this plan cannot ingest a prompt into one sequence (tensor parallel, head_dim > 128 or an in-place product)"); return SWLM_ERR_UNSUPPORTED; }
+    int rc = ensure_device(s->plan->ctx);
+    if (rc) return rc;
+    if (s->pos_host[seq] + n > d.max_seq) {
+        set_error("sequence %d: position %d + %d tokens exceeds max_seq %d", seq, s->pos_host[seq], n, d.max_seq);
+        return SWLM_ERR_STATE;
+    }
+    if (s->prompt_cap < (size_t)n) {
+        cudaFree(s->prompt);
+        s->prompt = nullptr; s->prompt_cap = 0;
+        if ((rc = dev_alloc(&s->prompt, (size_t)n))) return rc;
+        s->prompt_cap = (size_t)n;
+    }
+    SWLM_CUDA(cudaMemcpyAsync(s->prompt, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, s->stream));
+    const int chunk = s->prefill_chunk >= kPrefillMinChunk ? s->prefill_chunk : 2048;
+    if ((rc = prefill_workspace(s, std::min(chunk, n)))) return rc;
+    for (int t = 0; t < n;) {
+        const int c = std::min(chunk, n - t);
+        // the chunk that holds the prompt's last token also runs the output head on that row
+        if ((rc = enqueue_prefill_chunk(s, s->prompt + t, c, s->pos_host[seq], seq, s->stream, t + c == n ? c - 1 : -1))) return rc;
+        s->pos_host[seq] += c;
+        t += c;
+    }
+    SWLM_CUDA(cudaMemcpyAsync(s->h_tok, s->token_out + seq, sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    if ((rc = check_pf_status(s))) return rc;
+    if ((rc = check_tc_status(s))) return rc;
+    *first_token = s->h_tok[0];
+    return SWLM_OK;
+}
+
+int swlm_state_reset_seq(swlm_state* s, int seq) {
+    if (!s) { set_error("null state"); return SWLM_ERR_INVALID; }
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (seq < 0 || seq >= d.max_batch) { set_error("sequence %d outside 0..%d", seq, d.max_batch - 1); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(s->plan->ctx);
+    if (rc) return rc;
+    // the cache needs no clearing (rows at and beyond the position are never read); the conv state does
+    const size_t per_seq = (size_t)d.conv_kernel * d.conv_dim;
+    for (int l = 0; l < d.conv_layers && per_seq; ++l)
+        SWLM_CUDA(cudaMemsetAsync(s->conv + (size_t)l * s->conv_layer_elems + (size_t)seq * per_seq, 0, per_seq * 2, s->stream));
+    SWLM_CUDA(cudaMemsetAsync(s->position + seq, 0, 4, s->stream));
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    s->pos_host[seq] = 0;
+    return SWLM_OK;
 }
 
 int swlm_state_set_prefill_chunk(swlm_state* s, int tokens) {
@@ -1473,7 +1636,7 @@ int swlm_run_step(swlm_state* s, const swlm_step* step, const int32_t* token_in,
     if (rc) { for (RopeTable& t : tmp.rope_tables) cudaFree(t.inv_freq); return rc; }
     if (token_in) SWLM_CUDA(cudaMemcpyAsync(s->token_in, token_in, sizeof(int32_t) * m, cudaMemcpyHostToDevice, s->stream));
     swlm_plan* saved = s->plan;
-    int saved_pos = s->pos_host;
+    const std::vector<int> saved_pos = s->pos_host;
     // an argmax step advances the device position; keep single-step runs position-neutral
     s->plan = &tmp;
     rc = enqueue_step(s, false, s->stream);
@@ -1482,7 +1645,7 @@ int swlm_run_step(swlm_state* s, const swlm_step* step, const int32_t* token_in,
     for (RopeTable& t : tmp.rope_tables) cudaFree(t.inv_freq);
     if (rc) return rc;
     if (e != cudaSuccess) return cuda_fail(e, "run_step sync");
-    SWLM_CUDA(cudaMemcpy(s->position, &saved_pos, 4, cudaMemcpyHostToDevice));
+    SWLM_CUDA(cudaMemcpy(s->position, saved_pos.data(), sizeof(int32_t) * m, cudaMemcpyHostToDevice));
     const int32_t saved_steps = (int32_t)s->steps_host;
     SWLM_CUDA(cudaMemcpy(s->step_counter, &saved_steps, 4, cudaMemcpyHostToDevice));
     if (token_out) SWLM_CUDA(cudaMemcpy(token_out, s->token_out, sizeof(int32_t) * m, cudaMemcpyDeviceToHost));

@@ -224,6 +224,11 @@ int launch_argmax(int m, int n, const __nv_bfloat16* logits, int stride, int32_t
                   int32_t* am_epoch, int shard_offset, cudaStream_t s);
 size_t argmax_scratch_elems(int m);
 
+// Sequences decoded together: 1..16 ride in the GEMV kernels (one weight pass for all of them), 17..kMaxSequences
+// take the tensor-core product, one row per sequence.
+constexpr int kMaxSequences = 64;
+constexpr int kQGemvMaxRows = 16;
+
 struct AttnLaunch {
     int m = 1;            // sequences
     int heads = 0, kv_heads = 0, head_dim = 0;
@@ -236,7 +241,7 @@ struct AttnLaunch {
     __nv_bfloat16* kcache = nullptr;  // [m][kv_heads][max_seq][hd]
     __nv_bfloat16* vcache = nullptr;
     int max_seq = 0;
-    const int32_t* position = nullptr;  // device scalar: index of the new token
+    const int32_t* position = nullptr;  // device array [m]: index of each sequence's new token
     __nv_bfloat16* out = nullptr; int out_stride = 0;
     float* scratch = nullptr;   // attn_scratch_floats()
     unsigned* counters = nullptr;  // m * kv_heads arrival counters, zero between launches
@@ -265,9 +270,9 @@ constexpr int kQGemmTcMinRows = 17;   // 17..63 token rows ride in a 64-token ti
 int qgemm_tc_init();
 size_t qgemm_tc_scratch_bytes(int m, int k);   // fp16 copy of the activations + one float per token row
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
-                    void* scratch, int* status, cudaStream_t s);
+                    void* scratch, int* status, cudaStream_t s, bool reuse_x = false);
 
 int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s);
-int launch_advance(int32_t* position, int32_t* step_counter, cudaStream_t s);
+int launch_advance(int m, int32_t* position, int32_t* step_counter, cudaStream_t s);
 
 }  // namespace swlm

@@ -99,6 +99,10 @@ SIGNATURES = {
     "swlm_write_kv": (_I, [_P, _I, _I, _I, _I, _I, _P]),
     "swlm_read_conv": (_I, [_P, _I, _I, _P]),
     "swlm_set_position": (_I, [_P, _I]),
+    "swlm_set_positions": (_I, [_P, _P]),
+    "swlm_get_positions": (_I, [_P, _P]),
+    "swlm_prefill_seq": (_I, [_P, _I, _P, _I, _P]),
+    "swlm_state_reset_seq": (_I, [_P, _I]),
     "swlm_run_step": (_I, [_P, C.POINTER(Step), _P, _P]),
     "swlm_launches": (C.c_int64, [_P]),
     "swlm_profile_kind": (_I, [_P, _I, _I]),

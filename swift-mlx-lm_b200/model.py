@@ -193,6 +193,27 @@ class InferenceModel:
     def set_position(self, position: int) -> None:
         self.lib.check(self.lib.swlm_set_position(self.state, position))
 
+    # -- several sequences, each at its own position ---------------------------------------------------
+    def set_positions(self, positions) -> None:
+        p = np.ascontiguousarray(np.asarray(positions, dtype=np.int32).reshape(self.batch))
+        self.lib.check(self.lib.swlm_set_positions(self.state, _ptr(p)))
+
+    @property
+    def positions(self) -> np.ndarray:
+        out = np.empty(self.batch, dtype=np.int32)
+        self.lib.check(self.lib.swlm_get_positions(self.state, _ptr(out)))
+        return out
+
+    def prefill_sequence(self, seq: int, tokens) -> int:
+        """Append a prompt to one sequence only; returns that sequence's next token."""
+        t = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(-1))
+        out = np.empty(1, dtype=np.int32)
+        self.lib.check(self.lib.swlm_prefill_seq(self.state, seq, _ptr(t), t.size, _ptr(out)))
+        return int(out[0])
+
+    def reset_sequence(self, seq: int) -> None:
+        self.lib.check(self.lib.swlm_state_reset_seq(self.state, seq))
+
     def run_step(self, step: Step, token_in=None) -> np.ndarray:
         tin = None
         if token_in is not None:

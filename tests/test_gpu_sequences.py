@@ -1,0 +1,138 @@
+"""Several sequences per decode step: more than 16 of them (tensor-core products, one row per sequence) and
+sequences at different positions (a prompt appended to one sequence while the others keep theirs).
+
+The oracle interprets the same plan. For equal-length prompts it runs the whole batch; for ragged ones it runs
+every sequence alone, one after the other, because sequences never interact: the same logits must come out of
+the batched CUDA step whatever the neighbours' positions are."""
+import numpy as np
+import pytest
+
+from swlm_helpers import rel_err
+from test_gpu_model import build_pair, greedy_compare, small_lfm2, small_llama
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("family,batch", [("llama", 17), ("llama", 40), ("lfm2", 24), ("lfm2", 64)])
+def test_wide_batches_greedy_against_oracle(pkg, oracle, family, batch):
+    cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=batch, max_seq=64)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    oracle.set_threads(8)
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=6, steps=20)
+    assert len(mism) <= max(2, batch // 8), mism
+    for layer in range(cfg.conv_layer_count):
+        for b in (0, batch - 1):
+            g, o = pkg.bf16_to_f32(gm.read_conv(layer, b)), pkg.bf16_to_f32(om.read_conv(layer, b))
+            assert rel_err(g, o).max() <= 3e-2
+    gm.close(); store.close()
+
+
+def test_more_than_64_sequences_is_refused(pkg, oracle):
+    cfg = small_llama(pkg, batch=65, max_seq=32)
+    builder = pkg.DispatchPlanBuilder(cfg)
+    weights = pkg.synth_model_weights(builder, seed=3)
+    store = pkg.WeightStore(0)
+    with pytest.raises(pkg.SwlmError):
+        pkg.load_model(store, builder, weights)
+    store.close()
+
+
+def _oracle_traces(pkg, oracle, cfg1, builder_weights, prompts, steps):
+    """Every sequence alone through a batch-1 oracle: per sequence the tokens fed and the logits after each step."""
+    builder, weights = builder_weights
+    om = oracle.model(cfg1.buffers_desc())
+    om.load(builder, weights)
+    traces = []
+    for prompt in prompts:
+        om.reset()
+        tok = om.prefill(np.asarray(prompt, dtype=np.int32).reshape(1, -1))
+        toks, logits = [int(tok[0])], [pkg.bf16_to_f32(om.read_buffer(pkg.plan.BUF_LOGITS, cfg1.vocab))[0]]
+        for _ in range(steps):
+            tok = om.decode(tok)
+            toks.append(int(tok[0]))
+            logits.append(pkg.bf16_to_f32(om.read_buffer(pkg.plan.BUF_LOGITS, cfg1.vocab))[0])
+        traces.append((toks, logits))
+    return traces
+
+
+def _check_tokens(logits_o, got, want, where):
+    if got == want:
+        return
+    top2 = np.sort(logits_o)[-2:]
+    ulp = 2.0 ** (np.floor(np.log2(max(abs(top2[1]), 1e-30))) - 7)
+    assert top2[1] - top2[0] <= ulp, f"{where}: token {got} != {want}, margin {top2[1] - top2[0]} (bf16 ulp {ulp})"
+
+
+@pytest.mark.parametrize("family,batch", [("llama", 4), ("lfm2", 3), ("lfm2", 20)])
+def test_sequences_at_their_own_positions(pkg, oracle, family, batch):
+    """Prompts of different lengths go into the sequences one at a time (swlm_prefill_seq), then all sequences
+    decode together, each at its own position. Every sequence must behave as if it were alone."""
+    mk = small_llama if family == "llama" else small_lfm2
+    cfg, cfg1 = mk(pkg, batch=batch, max_seq=160), mk(pkg, batch=1, max_seq=160)
+    builder = pkg.DispatchPlanBuilder(cfg)
+    weights = pkg.synth_model_weights(builder, seed=5)
+    store = pkg.WeightStore(0)
+    gm = pkg.load_model(store, builder, weights)
+    oracle.set_threads(8)
+    rng = np.random.default_rng(23)
+    lengths = [int(x) for x in rng.integers(1, 90, size=batch)]
+    lengths[0], lengths[-1] = 1, 97                      # a one-token prompt and one of two chunks
+    prompts = [rng.integers(0, cfg.vocab, size=n, dtype=np.int32) for n in lengths]
+    steps = 12
+    traces = _oracle_traces(pkg, oracle, cfg1, (pkg.DispatchPlanBuilder(cfg1), weights), prompts, steps)
+    gm.set_prefill_chunk(64)
+    # fill in an order that is not the slot order, so that nothing depends on it
+    for b in reversed(range(batch)):
+        first = gm.prefill_sequence(b, prompts[b])
+        _check_tokens(traces[b][1][0], first, traces[b][0][0], f"prompt of sequence {b}")
+    assert list(gm.positions) == lengths
+    feed = np.array([traces[b][0][0] for b in range(batch)], dtype=np.int32)
+    for step in range(1, steps + 1):
+        got = gm.decode(feed)
+        logits_g = pkg.bf16_to_f32(gm.logits())
+        for b in range(batch):
+            err = rel_err(logits_g[b], traces[b][1][step]).max()
+            assert err <= 4e-2, f"step {step} sequence {b} (position {lengths[b] + step}): logits rel-err {err}"
+            _check_tokens(traces[b][1][step], int(got[b]), traces[b][0][step], f"step {step} sequence {b}")
+        feed = np.array([traces[b][0][step] for b in range(batch)], dtype=np.int32)   # the oracle's tokens
+    assert list(gm.positions) == [n + steps for n in lengths]
+
+    # one sequence leaves and another prompt takes its slot; the neighbours go on undisturbed
+    victim = batch // 2
+    gm.reset_sequence(victim)
+    new_prompt = rng.integers(0, cfg.vocab, size=37, dtype=np.int32)
+    t2 = _oracle_traces(pkg, oracle, cfg1, (pkg.DispatchPlanBuilder(cfg1), weights), [new_prompt], 3)[0]
+    first = gm.prefill_sequence(victim, new_prompt)
+    _check_tokens(t2[1][0], first, t2[0][0], "second prompt")
+    other = 0 if victim != 0 else 1
+    o_more = _oracle_traces(pkg, oracle, cfg1, (pkg.DispatchPlanBuilder(cfg1), weights), [prompts[other]], steps + 3)[0]
+    feed[victim] = t2[0][0]
+    for step in range(1, 4):
+        got = gm.decode(feed)
+        logits_g = pkg.bf16_to_f32(gm.logits())
+        assert rel_err(logits_g[victim], t2[1][step]).max() <= 4e-2
+        assert rel_err(logits_g[other], o_more[1][steps + step]).max() <= 4e-2
+        _check_tokens(t2[1][step], int(got[victim]), t2[0][step], f"refilled slot, step {step}")
+        for b in range(batch):
+            feed[b] = got[b]
+        feed[victim] = t2[0][step]
+        feed[other] = o_more[0][steps + step]
+    gm.close(); store.close()
+
+
+def test_positions_can_be_set_and_bad_arguments_are_refused(pkg, oracle):
+    cfg = small_llama(pkg, batch=3, max_seq=64)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    gm.set_positions([5, 0, 17])
+    assert list(gm.positions) == [5, 0, 17] and gm.position == 5
+    gm.set_position(2)
+    assert list(gm.positions) == [2, 2, 2]
+    with pytest.raises(pkg.SwlmError):
+        gm.set_positions([1, 65, 1])
+    with pytest.raises(pkg.SwlmError):
+        gm.prefill_sequence(3, [1, 2, 3])
+    with pytest.raises(pkg.SwlmError):
+        gm.prefill_sequence(0, np.zeros(63, dtype=np.int32))      # 2 + 63 > max_seq
+    with pytest.raises(pkg.SwlmError):
+        gm.reset_sequence(-1)
+    gm.close(); store.close()
