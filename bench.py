@@ -27,7 +27,7 @@ from __graft_entry__ import load_package  # noqa: E402
 
 METRIC = "4-bit decode tok/s, Llama-3-8B shape bs1"
 NOMINAL_HBM_GBS = 8000.0
-NCU_TRAFFIC_RATIO = 123.797 / 122.683
+NCU_TRAFFIC_RATIO = 123.679 / 122.683
 
 
 def measured_peaks():
@@ -479,7 +479,7 @@ def main():
         "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
         "bytes_per_launch_avg": weight_bytes / n_gemv, "avg_launch_us": gemv_ms * 1e3 / n_gemv,
         # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from an ncu capture of one layer's four
-        # product shapes (123.80 MB of HBM traffic for 122.68 MB of weights), applied to this run's average launch:
+        # product shapes (123.68 MB of HBM traffic for 122.68 MB of weights), applied to this run's average launch:
         # an estimate carried over from that capture, not a counter read in this run
         "traffic": weight_bytes / n_gemv * NCU_TRAFFIC_RATIO,
         "traffic_source": "estimate: ncu capture of the four product shapes of one layer, ratio %.4f to algorithmic bytes" % NCU_TRAFFIC_RATIO,

@@ -20,7 +20,7 @@ public enum CUDAPlanEntry {
                 weightBias: Float, q: Slot, k: Slot)
     /// FlashAttentionFragment (decode): inline RoPE, KV append, attention over [0, position].
     case attention(layer: Int, heads: Int, kvHeads: Int, headDimension: Int, ropeDimension: Int, ropeBase: Float,
-                   scale: Float, q: Slot, k: Slot, v: Slot, output: Slot)
+                   scale: Float, windowLeft: Int?, q: Slot, k: Slot, v: Slot, output: Slot)
     /// ElementwiseFragment(.swiglu) or the gated activation with .geluTanh.
     case gatedActivation(gelu: Bool, dimension: Int, gate: Slot, up: Slot, output: Slot)
     /// Conv1dFragment: conv_state_update over the packed B|C|x projection.
@@ -94,12 +94,13 @@ public struct CUDADispatchPlanBuilder {
             try setName(qWeight, into: &s)
             try setName(kWeight, into: &s, second: true)
             return s
-        case let .attention(layer, heads, kvHeads, headDimension, ropeDimension, ropeBase, scale, q, k, v, output):
+        case let .attention(layer, heads, kvHeads, headDimension, ropeDimension, ropeBase, scale, windowLeft, q, k, v, output):
             var s = blank(Int32(SWLM_STEP_ATTN_DECODE))
             s.layer = Int32(layer)
             s.in_buf = q.rawValue; s.in2_buf = k.rawValue; s.in3_buf = v.rawValue; s.out_buf = output.rawValue
             s.heads = Int32(heads); s.kv_heads = Int32(kvHeads); s.head_dim = Int32(headDimension)
             s.rope_dim = Int32(ropeDimension); s.rope_base = ropeBase; s.scale = scale
+            s.window_left = Int32(windowLeft ?? 0)   // FlashAttentionFragment.windowLeft (nil = full attention)
             return s
         case let .gatedActivation(gelu, dimension, gate, up, output):
             var s = blank(Int32(gelu ? SWLM_STEP_GEGLU : SWLM_STEP_SWIGLU))

@@ -39,7 +39,8 @@ extern "C" {
 #define SWLM_SHARD_REPLICATE 0
 #define SWLM_SHARD_COLUMN 1 /* split output rows N; result stays sharded */
 #define SWLM_SHARD_ROW 2    /* split input columns K on 64-element group boundaries; result needs an all-reduce */
-#define SWLM_SHARD_COLUMN3 3 /* N = three equal thirds (B|C|x of LFM2 in_proj), each split on its own */
+#define SWLM_SHARD_COLUMN3 3 /* N = three equal thirds (B|C|x of LFM2 in_proj), each split on its own: a rank holds
+                               rows [row0, row0 + rows) of every third, one third after the other */
 
 typedef struct swlm_ctx swlm_ctx;
 typedef struct swlm_plan swlm_plan;
@@ -70,6 +71,15 @@ int swlm_weights_add_q4g64_mlx(swlm_ctx* ctx, const char* name, int n, int k, co
  * (Sources/MetalCompiler/STAF/QuantizationFormat.swift:463-528). */
 int swlm_weights_add_q4g64_staf(swlm_ctx* ctx, const char* name, int n, int k, const void* blocks36,
                                 int shard_kind);
+/* The same two formats with one scale / bias pair per 128 weights (AffineQ4Group128Format,
+ * Sources/MetalCompiler/STAF/QuantizationFormat.swift:539-604): MLX scales/biases are [n][k/128], STAF blocks are
+ * 68 bytes (fp16 scale | fp16 zero | 64 payload bytes). On the device the tensor takes the group-64 streaming layout
+ * with every pair written for both halves of its group, so all kernels serve it unchanged and results are those of
+ * w = scale * q + zero with the group-128 parameters; 0.5625 bytes per weight are streamed instead of 0.53125. */
+int swlm_weights_add_q4g128_mlx(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* weight,
+                                const uint16_t* scales_bf16, const uint16_t* biases_bf16, int shard_kind);
+int swlm_weights_add_q4g128_staf(swlm_ctx* ctx, const char* name, int n, int k, const void* blocks68,
+                                 int shard_kind);
 /* Dense bf16 tensor (norm weights, embedding table, conv weights). `count` elements;
  * rows/cols describe a 2-D view when shard_kind != replicate (cols = count / rows). */
 int swlm_weights_add_dense_bf16(swlm_ctx* ctx, const char* name, int64_t rows, int64_t cols,

@@ -100,6 +100,9 @@ typedef struct swlm_step {
     float   rope_base;
     char    weight[SWLM_NAME_MAX];
     char    weight2[SWLM_NAME_MAX];
+    /* attention: sliding window. 0 = attend everything; W > 0 = the current token and the W - 1 before it
+       (windowLeft, Generator/MetalSourceGenerator+Attention.swift:851-853; decode and prompt chunks alike). */
+    int32_t window_left;
 } swlm_step;
 
 /* Sizes of the runtime buffer set; mirrors the inputs of

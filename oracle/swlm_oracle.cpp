@@ -81,17 +81,18 @@ constexpr int kBlockBytes = 36;
 
 struct Q4Tensor {
     int n = 0, k = 0;
+    int group = kGroup;        // 64, or 128 (AffineQ4Group128Format, STAF/QuantizationFormat.swift:539-604)
     std::vector<uint32_t> w;   // [n][k/8]
-    std::vector<float> scale;  // [n][k/64], widened exactly from bf16 (or through fp16)
+    std::vector<float> scale;  // [n][k/group], widened exactly from bf16 (or through fp16)
     std::vector<float> zero;
 };
 
 // w = scale * float(q) + zero — Sources/SwiftLM/CPUWeightStore.swift:147-170.
 inline float dequant(const Q4Tensor& t, int row, int col) {
     const uint32_t* words = t.w.data() + (size_t)row * (t.k / 8);
-    int g = col / kGroup;
-    float s = t.scale[(size_t)row * (t.k / kGroup) + g];
-    float z = t.zero[(size_t)row * (t.k / kGroup) + g];
+    int g = col / t.group;
+    float s = t.scale[(size_t)row * (t.k / t.group) + g];
+    float z = t.zero[(size_t)row * (t.k / t.group) + g];
     return s * (float)mlx_nibble(words, col) + z;
 }
 
@@ -100,7 +101,7 @@ inline float dequant(const Q4Tensor& t, int row, int col) {
 // y64 (optional) receives the same dot product accumulated in fp64, unrounded.
 void qgemm(const Q4Tensor& t, int m, const uint16_t* x, int x_stride, uint16_t* y, int y_stride,
            double* y64) {
-    const int groups = t.k / kGroup;
+    const int groups = t.k / t.group;
 #pragma omp parallel for schedule(static) num_threads(g_threads)
     for (int row = 0; row < t.n; ++row) {
         const uint32_t* words = t.w.data() + (size_t)row * (t.k / 8);
@@ -111,8 +112,8 @@ void qgemm(const Q4Tensor& t, int m, const uint16_t* x, int x_stride, uint16_t* 
             for (int g = 0; g < groups; ++g) {
                 float s = t.scale[(size_t)row * groups + g];
                 float z = t.zero[(size_t)row * groups + g];
-                for (int e = 0; e < kGroup; ++e) {
-                    int col = g * kGroup + e;
+                for (int e = 0; e < t.group; ++e) {
+                    int col = g * t.group + e;
                     float w = s * (float)mlx_nibble(words, col) + z;
                     float xv = bf16_to_f32(xb[col]);
                     sum += w * xv;
@@ -285,7 +286,9 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
             const uint16_t* kbase = m->kcache.data() + kv_index(m, st.layer, b, kvh, 0);
             const uint16_t* vbase = m->vcache.data() + kv_index(m, st.layer, b, kvh, 0);
             float max_score = -HUGE_VALF, sum_exp = 0.0f;
-            for (int t = 0; t <= pos; ++t) {
+            // sliding window (:851-853): the current token and the window_left - 1 before it
+            const int t_first = st.window_left > 0 && pos + 1 > st.window_left ? pos - st.window_left + 1 : 0;
+            for (int t = t_first; t <= pos; ++t) {
                 float score = 0.0f;
                 if (t == pos) {
                     // the current token's key and value are used unrounded (:866-868, :905-907)
@@ -435,13 +438,20 @@ const char* orc_error(const orc_model* m) { return m->error.c_str(); }
 
 // staf_fp16 != 0 narrows scale and bias through fp16, as the reference's STAF
 // converter does (Sources/MetalCompiler/STAF/STAFPayloadConverter.swift:326-368).
+int orc_add_q4_group(orc_model* m, const char* name, int n, int k, int group, const uint32_t* w,
+                     const uint16_t* scales_bf16, const uint16_t* biases_bf16, int staf_fp16);
 int orc_add_q4(orc_model* m, const char* name, int n, int k, const uint32_t* w,
                const uint16_t* scales_bf16, const uint16_t* biases_bf16, int staf_fp16) {
-    if (k % kGroup) { m->error = "k must be a multiple of 64"; return -1; }
+    return orc_add_q4_group(m, name, n, k, kGroup, w, scales_bf16, biases_bf16, staf_fp16);
+}
+// group = 64 or 128 weights per scale / bias pair
+int orc_add_q4_group(orc_model* m, const char* name, int n, int k, int group, const uint32_t* w,
+                     const uint16_t* scales_bf16, const uint16_t* biases_bf16, int staf_fp16) {
+    if ((group != 64 && group != 128) || k % group) { m->error = "group must be 64 or 128 and divide k"; return -1; }
     Q4Tensor t;
-    t.n = n; t.k = k;
+    t.n = n; t.k = k; t.group = group;
     t.w.assign(w, w + (size_t)n * (k / 8));
-    size_t g = (size_t)n * (k / kGroup);
+    size_t g = (size_t)n * (k / group);
     t.scale.resize(g); t.zero.resize(g);
     for (size_t i = 0; i < g; ++i) {
         float s = bf16_to_f32(scales_bf16[i]), z = bf16_to_f32(biases_bf16[i]);
@@ -568,6 +578,39 @@ void orc_staf_repack_mlx(int n, int k, const uint32_t* w, const uint16_t* scales
         }
 }
 
+// The same repack and block dequant for a group of `group` weights (64: 36-byte blocks, 128: 68-byte blocks,
+// AffineQ4Group128Format, Sources/MetalCompiler/STAF/QuantizationFormat.swift:539-604).
+void orc_staf_repack_mlx_group(int n, int k, int group, const uint32_t* w, const uint16_t* scales_bf16,
+                               const uint16_t* biases_bf16, uint8_t* blocks) {
+    const int groups = k / group, block_bytes = 4 + group / 2;
+    const uint8_t* wb = (const uint8_t*)w;
+    for (int r = 0; r < n; ++r)
+        for (int g = 0; g < groups; ++g) {
+            uint8_t* blk = blocks + ((size_t)r * groups + g) * block_bytes;
+            uint16_t s = f32_to_f16(bf16_to_f32(scales_bf16[(size_t)r * groups + g]));
+            uint16_t z = f32_to_f16(bf16_to_f32(biases_bf16[(size_t)r * groups + g]));
+            std::memcpy(blk, &s, 2);
+            std::memcpy(blk + 2, &z, 2);
+            std::memcpy(blk + 4, wb + (size_t)r * (k / 2) + (size_t)g * (group / 2), group / 2);
+        }
+}
+void orc_q4_dequant_staf_group(int n, int k, int group, const uint8_t* blocks, float* out) {
+    const int groups = k / group, block_bytes = 4 + group / 2;
+    for (int r = 0; r < n; ++r)
+        for (int g = 0; g < groups; ++g) {
+            const uint8_t* blk = blocks + ((size_t)r * groups + g) * block_bytes;
+            uint16_t sb, zb;
+            std::memcpy(&sb, blk, 2);
+            std::memcpy(&zb, blk + 2, 2);
+            float s = f16_to_f32(sb), z = f16_to_f32(zb);
+            for (int e = 0; e < group; ++e) {
+                uint8_t byte = blk[4 + e / 2];
+                uint8_t q = (e % 2 == 0) ? (byte & 0x0F) : (byte >> 4);   // Q4AffineMSL.perWeightExpression, :1084-1089
+                out[(size_t)r * k + g * group + e] = s * (float)q + z;
+            }
+        }
+}
+
 // decodeQuantized — Sources/SwiftLM/CPUWeightStore.swift:109-174 (the reference's own CPU dequant).
 void orc_q4_dequant_staf(int n, int k, const uint8_t* blocks, float* out) {
     const int groups = k / kGroup;
@@ -597,13 +640,19 @@ void orc_q4_dequant_bf16(int n, int k, const uint32_t* w, const uint16_t* scales
 // Y[m][n] = X[m][k] . W^T, bf16 in/out; y64 optional fp64 accumulation.
 // staf_fp16: narrow scale/bias through fp16 first. x_is_f16: x holds fp16 (the
 // reference's kernel tests feed fp16 activations), otherwise bf16.
+int orc_qgemm_group(int m, int n, int k, int group, const uint16_t* x, const uint32_t* w, const uint16_t* scales_bf16,
+                    const uint16_t* biases_bf16, uint16_t* y, double* y64, int staf_fp16);
 int orc_qgemm(int m, int n, int k, const uint16_t* x, const uint32_t* w, const uint16_t* scales_bf16,
               const uint16_t* biases_bf16, uint16_t* y, double* y64, int staf_fp16) {
-    if (k % kGroup) return -1;
+    return orc_qgemm_group(m, n, k, kGroup, x, w, scales_bf16, biases_bf16, y, y64, staf_fp16);
+}
+int orc_qgemm_group(int m, int n, int k, int group, const uint16_t* x, const uint32_t* w, const uint16_t* scales_bf16,
+                    const uint16_t* biases_bf16, uint16_t* y, double* y64, int staf_fp16) {
+    if ((group != 64 && group != 128) || k % group) return -1;
     Q4Tensor t;
-    t.n = n; t.k = k;
+    t.n = n; t.k = k; t.group = group;
     t.w.assign(w, w + (size_t)n * (k / 8));
-    size_t g = (size_t)n * (k / kGroup);
+    size_t g = (size_t)n * (k / group);
     t.scale.resize(g); t.zero.resize(g);
     for (size_t i = 0; i < g; ++i) {
         float s = bf16_to_f32(scales_bf16[i]), z = bf16_to_f32(biases_bf16[i]);

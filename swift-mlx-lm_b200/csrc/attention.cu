@@ -49,6 +49,8 @@ struct AttnParams {
     int ctx_len;               // plain: number of cached tokens
     int pos_base;              // prompt ingestion: position of the chunk's first token
     int chunk_tokens;          // prompt ingestion: tokens in the chunk
+    int window;                // sliding window (0 = none): a token attends itself and the window - 1 rows before it
+    int q_first;               // 1: the first K/V rows are requested only after q, k, v have arrived
     __nv_bfloat16* out; int out_stride;
     float* part_o;   // [m][heads][splits][HD]
     float* part_ml;  // [m][heads][splits][2]
@@ -171,8 +173,17 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         }
     };
     int tok0 = t_begin + warp * 16;
-    if (DECODE) { load_k(tok0, p.max_seq - 1); load_v(tok0, p.max_seq - 1); }
+    if (p.q_first) { /* requested below, once q, k and v are in shared memory */ }
+    else if (DECODE) { load_k(tok0, p.max_seq - 1); load_v(tok0, p.max_seq - 1); }
     else if (tok0 < t_end) { load_k(tok0, t_end - 1); load_v(tok0, t_end - 1); }
+    // sliding window (Generator/MetalSourceGenerator+Attention.swift:851-853): cached rows below t_lo are left out.
+    // A split whose first blocks lie wholly below the window starts at its first block that reaches into it.
+    const int t_lo = p.window > 0 ? max(0, n_ctx + (DECODE ? 1 : 0) - p.window) : 0;
+    if (t_lo / kBlock > split) {
+        const int skip = (t_lo / kBlock - split + p.splits - 1) / p.splits;
+        tok0 = (split + skip * p.splits) * kBlock + warp * 16;
+        if (!p.q_first && tok0 < t_end) { load_k(tok0, t_end - 1); load_v(tok0, t_end - 1); }
+    }
     // the split's later blocks are asked into L2 (two ahead; the loop keeps that distance): the register loads
     // of the loop then find them there
     constexpr int kAhead = 2;
@@ -205,6 +216,9 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
         }
     }
     __syncthreads();
+    // 8 MB of K/V requests from all CTAs at once delay the 4 KB of q, k, v that the whole prologue waits for (the
+    // memory system serves requests in arrival order): in this mode the rows are requested behind them
+    if (p.q_first && tok0 < t_end) { load_k(tok0, t_end - 1); load_v(tok0, t_end - 1); }
     const int n_ctas = gridDim.x * gridDim.y * gridDim.z;
     const bool stamp0 = p.trace && cta_linear == 0 && threadIdx.x == 0;  // finer stamps of the first CTA only
     if (stamp0) p.trace[n_ctas * 4 + 1] = attn_timer_ns();
@@ -295,19 +309,20 @@ __global__ void __launch_bounds__(kSplitThreads) attn_split_kernel(const AttnPar
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int tok = tok0 + 8 * nt + 2 * t + e;
-                sv[nt][e] = tok < t_end ? (sacc[nt][e] + sacc[nt][2 + e]) * p.scale_log2 : -INFINITY;
+                sv[nt][e] = tok < t_end && tok >= t_lo ? (sacc[nt][e] + sacc[nt][2 + e]) * p.scale_log2 : -INFINITY;
                 rmax = fmaxf(rmax, sv[nt][e]);
             }
         rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
         rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
         const float m_new = fmaxf(m_run, rmax);
-        const float corr = exp2f(m_run - m_new);
+        const float m_ref = m_new == -INFINITY ? 0.f : m_new;  // 16 rows wholly below a sliding window: all weights 0
+        const float corr = exp2f(m_run - m_ref);
         float pv[2][2];
         float psum = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) { pv[nt][e] = exp2f(sv[nt][e] - m_new); psum += pv[nt][e]; }
+            for (int e = 0; e < 2; ++e) { pv[nt][e] = exp2f(sv[nt][e] - m_ref); psum += pv[nt][e]; }
         l_run = l_run * corr + psum;
         m_run = m_new;
         if (__any_sync(0xffffffffu, corr != 1.0f)) {
@@ -586,6 +601,8 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const AttnPara
     const __nv_bfloat16* vbase = p.vcache + (size_t)kvh * p.cache_head_stride;
     const int last_row = p.pos_base + p.chunk_tokens - 1;              // last cache row that holds data
     const int n_tiles = (p.pos_base + tok0 + n_tok - 1) / kPfTile + 1; // tiles the CTA's last token attends
+    // sliding window: the CTA's first token reaches back furthest
+    const int tile_lo = p.window > 0 ? max(0, p.pos_base + tok0 - p.window + 1) / kPfTile : 0;
     auto load_tile = [&](int tile, int stage) {
         unsigned char* kd = kv_sm + (size_t)stage * 2 * TILE_BYTES;
         unsigned char* vd = kd + TILE_BYTES;
@@ -600,7 +617,7 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const AttnPara
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    load_tile(0, 0);
+    load_tile(tile_lo, tile_lo & 1);
 
     // ---- prologue: q rows (row = token * G + head) to shared memory as floats, rotation table, rotation ----
     for (int idx = tid; idx < kPfRows * (HD / 8); idx += kPfThreads) {
@@ -654,7 +671,8 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const AttnPara
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
 
-    for (int tile = 0; tile < n_tiles; ++tile) {
+    const int row_lo = p.window > 0 ? pos_row - p.window + 1 : 0;   // first key this lane's row attends
+    for (int tile = tile_lo; tile < n_tiles; ++tile) {
         if (tile + 1 < n_tiles) load_tile(tile + 1, (tile + 1) & 1);
         else asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -682,19 +700,20 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const AttnPara
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int key = tile * kPfTile + 8 * j + 2 * t + e;
-                    const float v = key <= pos_row ? (sacc[j][e] + sacc[j][2 + e]) * p.scale_log2 : -INFINITY;
+                    const float v = key <= pos_row && key >= row_lo ? (sacc[j][e] + sacc[j][2 + e]) * p.scale_log2 : -INFINITY;
                     sacc[j][e] = v;
                     rmax = fmaxf(rmax, v);
                 }
             rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
             rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
-            const float m_new = fmaxf(m_run, rmax);   // finite: key 0 is never masked
-            const float corr = exp2f(m_run - m_new);
+            const float m_new = fmaxf(m_run, rmax);
+            const float m_ref = m_new == -INFINITY ? 0.f : m_new;   // a tile wholly outside this row's window: all weights 0
+            const float corr = exp2f(m_run - m_ref);
             float psum = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int e = 0; e < 2; ++e) { sacc[j][e] = exp2f(sacc[j][e] - m_new); psum += sacc[j][e]; }
+                for (int e = 0; e < 2; ++e) { sacc[j][e] = exp2f(sacc[j][e] - m_ref); psum += sacc[j][e]; }
             l_run = l_run * corr + psum;
             m_run = m_new;
             if (__any_sync(0xffffffffu, corr != 1.0f)) {
@@ -785,7 +804,9 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     p.kcache = a.kcache; p.vcache = a.vcache;
     p.cache_head_stride = (size_t)a.max_seq * a.head_dim;
     p.cache_seq_stride = p.cache_head_stride * a.kv_heads;
-    p.position = a.position; p.ctx_len = 0;
+    p.position = a.position; p.ctx_len = 0; p.window = a.window > 0 ? a.window : 0;
+    static const int q_first = [] { const char* v = getenv("SWLM_ATTN_QFIRST"); return v ? atoi(v) : 0; }();
+    p.q_first = q_first;
     p.out = a.out; p.out_stride = a.out_stride;
     p.part_o = a.scratch;
     p.part_ml = a.scratch + (size_t)a.m * a.heads * a.splits * a.head_dim;

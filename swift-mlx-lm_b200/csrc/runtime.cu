@@ -88,7 +88,9 @@ int alloc_tiled(swlm_ctx* ctx, int n, int k, bool sb_f16, Q4Tiled* t) {
 }
 
 // Rank-local slice of a [rows][cols] matrix given in `unit`-sized column units.
-struct Slice { int row0, rows, col0, cols; };
+// `parts` > 1: the rows are `parts` equal sections of `part_stride` source rows and the slice takes rows
+// [row0, row0 + rows) of every section, laid one after the other.
+struct Slice { int row0, rows, col0, cols; int parts = 1; int part_stride = 0; };
 int shard_slice(const swlm_ctx* ctx, int shard_kind, int n, int k, Slice* s) {
     *s = Slice{0, n, 0, k};
     if (ctx->tp_size == 1 || shard_kind == SWLM_SHARD_REPLICATE) return SWLM_OK;
@@ -100,6 +102,12 @@ int shard_slice(const swlm_ctx* ctx, int shard_kind, int n, int k, Slice* s) {
     if (shard_kind == SWLM_SHARD_ROW) {
         if (k % (64 * ctx->tp_size)) { set_error("row shard: k=%d not divisible by 64*tp", k); return SWLM_ERR_INVALID; }
         s->cols = k / ctx->tp_size; s->col0 = ctx->tp_rank * s->cols;
+        return SWLM_OK;
+    }
+    if (shard_kind == SWLM_SHARD_COLUMN3) {
+        if (n % (3 * ctx->tp_size)) { set_error("three-section column shard: n=%d not divisible by 3*tp=%d", n, 3 * ctx->tp_size); return SWLM_ERR_INVALID; }
+        s->parts = 3; s->part_stride = n / 3;
+        s->rows = n / 3 / ctx->tp_size; s->row0 = ctx->tp_rank * s->rows;
         return SWLM_OK;
     }
     set_error("unsupported shard kind %d", shard_kind);
@@ -176,14 +184,17 @@ int add_q4_raw(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* w,
         }
     }
     Q4Raw r;
-    r.n = sl.rows; r.k = sl.cols; r.sb_f16 = f16; r.shard_kind = shard_kind;
+    r.n = sl.rows * sl.parts; r.k = sl.cols; r.sb_f16 = f16; r.shard_kind = shard_kind;
     const int wpr = k / 8, gpr = k / 64, lw = sl.cols / 8, lg = sl.cols / 64;
     if ((rc = dev_alloc(&r.w, (size_t)r.n * lw, ctx))) return rc;
     if ((rc = dev_alloc(&r.scales, (size_t)r.n * lg, ctx))) return rc;
     if ((rc = dev_alloc(&r.biases, (size_t)r.n * lg, ctx))) return rc;
-    SWLM_CUDA(cudaMemcpy2D(r.w, (size_t)lw * 4, w + (size_t)sl.row0 * wpr + sl.col0 / 8, (size_t)wpr * 4, (size_t)lw * 4, r.n, cudaMemcpyHostToDevice));
-    SWLM_CUDA(cudaMemcpy2D(r.scales, (size_t)lg * 2, s + (size_t)sl.row0 * gpr + sl.col0 / 64, (size_t)gpr * 2, (size_t)lg * 2, r.n, cudaMemcpyHostToDevice));
-    SWLM_CUDA(cudaMemcpy2D(r.biases, (size_t)lg * 2, b + (size_t)sl.row0 * gpr + sl.col0 / 64, (size_t)gpr * 2, (size_t)lg * 2, r.n, cudaMemcpyHostToDevice));
+    for (int part = 0; part < sl.parts; ++part) {
+        const size_t src_row = (size_t)part * sl.part_stride + sl.row0, dst_row = (size_t)part * sl.rows;
+        SWLM_CUDA(cudaMemcpy2D(r.w + dst_row * lw, (size_t)lw * 4, w + src_row * wpr + sl.col0 / 8, (size_t)wpr * 4, (size_t)lw * 4, sl.rows, cudaMemcpyHostToDevice));
+        SWLM_CUDA(cudaMemcpy2D(r.scales + dst_row * lg, (size_t)lg * 2, s + src_row * gpr + sl.col0 / 64, (size_t)gpr * 2, (size_t)lg * 2, sl.rows, cudaMemcpyHostToDevice));
+        SWLM_CUDA(cudaMemcpy2D(r.biases + dst_row * lg, (size_t)lg * 2, b + src_row * gpr + sl.col0 / 64, (size_t)gpr * 2, (size_t)lg * 2, sl.rows, cudaMemcpyHostToDevice));
+    }
     ctx->raw[name] = r;
     return SWLM_OK;
 }
@@ -365,6 +376,7 @@ int compile_plan(swlm_plan* plan) {
             L.kind = L_ATTN;
             if (s.layer < 0 || s.layer >= d.kv_layers) { set_error("attention: layer %d outside the KV cache", s.layer); return SWLM_ERR_INVALID; }
             if (s.head_dim != d.head_dim) { set_error("attention: head_dim differs from the KV cache"); return SWLM_ERR_INVALID; }
+            if (s.window_left < 0) { set_error("attention: negative sliding window"); return SWLM_ERR_INVALID; }
             if (s.rope_dim > 0) { rc = rope_table_for(plan, s.rope_dim, s.rope_base, &L.rope_table); if (rc) return rc; }
             L.label = "attn_decode";
             break;
@@ -501,7 +513,16 @@ int compile_plan(swlm_plan* plan) {
                 if ((rc = swlm_tp_check_heads(L.st.heads, d.kv_heads, ctx->tp_size))) return rc;
         for (size_t i = 0; i < plan->launches.size(); ++i) {
             Launch& L = plan->launches[i];
-            if (L.kind == L_CONV) { set_error("short-conv layers are not supported under tensor parallelism"); return SWLM_ERR_UNSUPPORTED; }
+            if (L.kind == L_CONV) {
+                // channels are split across ranks: the B|C|x projection arrives as this rank's three thirds
+                // (SWLM_SHARD_COLUMN3), the conv weight rows are this rank's channels, the out projection is row-parallel
+                if (L.st.n % ctx->tp_size || L.d1->rows != L.st.n / ctx->tp_size) {
+                    set_error("conv '%s': %d channels over %d ranks need a weight of %d rows (add it with SWLM_SHARD_COLUMN)", L.st.weight,
+                              L.st.n, ctx->tp_size, L.st.n / ctx->tp_size);
+                    return SWLM_ERR_INVALID;
+                }
+                continue;
+            }
             if (L.kind != L_QGEMV) continue;
             auto it = ctx->raw.find(L.st.weight);
             if (it == ctx->raw.end() || it->second.shard_kind != SWLM_SHARD_ROW) continue;
@@ -678,7 +699,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             AttnLaunch a;
             a.m = m; a.heads = st.heads / plan->ctx->tp_size; a.kv_heads = kv_heads_local(plan); a.head_dim = st.head_dim;
             a.rope_dim = st.rope_dim; a.inv_freq = L.rope_table >= 0 ? plan->rope_tables[L.rope_table].inv_freq : nullptr;
-            a.scale = st.scale;
+            a.scale = st.scale; a.window = st.window_left;
             a.q = s->buf[st.in_buf]; a.q_stride = s->width[st.in_buf];
             a.k = s->buf[st.in2_buf]; a.k_stride = s->width[st.in2_buf];
             a.v = s->buf[st.in3_buf]; a.v_stride = s->width[st.in3_buf];
@@ -698,7 +719,8 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             s->launches += 1;
             break;
         case L_CONV:
-            rc = launch_conv_step(m, st.n, st.conv_kernel, s->conv + (size_t)st.layer * s->conv_layer_elems,
+            // under tensor parallelism a rank owns n / tp channels (its slab is used from the front)
+            rc = launch_conv_step(m, st.n / plan->ctx->tp_size, st.conv_kernel, s->conv + (size_t)st.layer * s->conv_layer_elems,
                                   (size_t)d.conv_kernel * d.conv_dim, s->buf[st.in_buf], s->width[st.in_buf], L.d1->data,
                                   s->buf[st.out_buf], s->width[st.out_buf], stream);
             s->launches += 1;
@@ -992,7 +1014,7 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
                 if ((rc = rope_table_for(plan, st.rope_dim, st.rope_base, &ti))) return rc;
                 a.inv_freq = plan->rope_tables[ti].inv_freq;
             }
-            a.scale = st.scale;
+            a.scale = st.scale; a.window = st.window_left;
             a.q = pf[st.in_buf]; a.q_stride = wd[st.in_buf];
             a.k = pf[st.in2_buf]; a.k_stride = wd[st.in2_buf];
             a.v = pf[st.in3_buf]; a.v_stride = wd[st.in3_buf];
@@ -1137,6 +1159,31 @@ int swlm_weights_add_q4g64_staf(swlm_ctx* ctx, const char* name, int n, int k, c
     return add_q4_raw(ctx, name, n, k, w.data(), s.data(), z.data(), true, shard_kind);
 }
 
+int swlm_weights_add_q4g128_mlx(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* weight,
+                                const uint16_t* scales_bf16, const uint16_t* biases_bf16, int shard_kind) {
+    if (!ctx || !name || !weight || !scales_bf16 || !biases_bf16 || n <= 0 || k <= 0 || k % 128) { set_error("q4g128 tensor: k must be a positive multiple of 128"); return SWLM_ERR_INVALID; }
+    // every (scale, bias) pair serves both 64-weight halves of its group
+    const size_t g128 = (size_t)n * (k / 128);
+    std::vector<uint16_t> s(2 * g128), z(2 * g128);
+    for (size_t g = 0; g < g128; ++g) { s[2 * g] = s[2 * g + 1] = scales_bf16[g]; z[2 * g] = z[2 * g + 1] = biases_bf16[g]; }
+    return add_q4_raw(ctx, name, n, k, weight, s.data(), z.data(), false, shard_kind);
+}
+
+int swlm_weights_add_q4g128_staf(swlm_ctx* ctx, const char* name, int n, int k, const void* blocks68, int shard_kind) {
+    if (!ctx || !name || !blocks68 || n <= 0 || k <= 0 || k % 128) { set_error("bad STAF tensor"); return SWLM_ERR_INVALID; }
+    const size_t g128 = (size_t)n * (k / 128);
+    std::vector<uint32_t> w((size_t)n * (k / 8));
+    std::vector<uint16_t> s(2 * g128), z(2 * g128);
+    const uint8_t* src = static_cast<const uint8_t*>(blocks68);
+    for (size_t g = 0; g < g128; ++g) {
+        const uint8_t* blk = src + g * 68;
+        memcpy(&s[2 * g], blk, 2); s[2 * g + 1] = s[2 * g];
+        memcpy(&z[2 * g], blk + 2, 2); z[2 * g + 1] = z[2 * g];
+        memcpy(reinterpret_cast<uint8_t*>(w.data()) + g * 64, blk + 4, 64);
+    }
+    return add_q4_raw(ctx, name, n, k, w.data(), s.data(), z.data(), true, shard_kind);
+}
+
 int swlm_weights_add_dense_bf16(swlm_ctx* ctx, const char* name, int64_t rows, int64_t cols, const uint16_t* data,
                                 int shard_kind) {
     if (!ctx || !name || !data || rows <= 0 || cols <= 0) { set_error("bad dense tensor"); return SWLM_ERR_INVALID; }
@@ -1145,6 +1192,7 @@ int swlm_weights_add_dense_bf16(swlm_ctx* ctx, const char* name, int64_t rows, i
     Slice sl;
     rc = shard_slice(ctx, shard_kind == SWLM_SHARD_ROW ? SWLM_SHARD_REPLICATE : shard_kind, (int)rows, (int)cols, &sl);
     if (rc) return rc;
+    if (sl.parts != 1) { set_error("dense tensors are replicated or split by rows"); return SWLM_ERR_UNSUPPORTED; }
     auto old = ctx->dense.find(name);
     if (old != ctx->dense.end()) {
         SWLM_CUDA(cudaDeviceSynchronize());

@@ -249,6 +249,7 @@ struct AttnLaunch {
     // >= 0: prompt ingestion. The m rows are consecutive tokens of sequence 0 starting at this position; their
     // k/v rows are appended first, then token b attends cache rows 0..pos_base+b. `position` is not read.
     int pos_base = -1;
+    int window = 0;       // sliding window: the current token and the window - 1 before it; 0 = everything
     PrefetchTarget prefetch;
 };
 int attn_pick_splits(int m, int kv_heads, int max_ctx);

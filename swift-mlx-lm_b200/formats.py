@@ -52,21 +52,22 @@ def unpack_mlx_q4(w: np.ndarray, k: int) -> np.ndarray:
     return ((w[:, :, None] >> shifts) & np.uint32(0xF)).reshape(w.shape[0], k).astype(np.uint8)
 
 
-def repack_mlx_to_staf(w: np.ndarray, scales_bf16: np.ndarray, biases_bf16: np.ndarray) -> np.ndarray:
-    """MLX triple -> STAF 36-byte blocks, [n, k/64, 36] uint8.
+def repack_mlx_to_staf(w: np.ndarray, scales_bf16: np.ndarray, biases_bf16: np.ndarray, group: int = 64) -> np.ndarray:
+    """MLX triple -> STAF blocks, [n, k/group, 4 + group/2] uint8: 36 bytes for groups of 64 weights, 68 bytes for
+    groups of 128 (AffineQ4Group128Format, STAF/QuantizationFormat.swift:539-604).
 
-    Per (row, group): fp16(scale), fp16(bias), then the group's 32 payload bytes verbatim — the MLX
+    Per (row, group): fp16(scale), fp16(bias), then the group's payload bytes verbatim — the MLX
     LSB-first bit stream already is the block's `qs` order (STAFPayloadConverter.swift:268-274); scale and
     bias are narrowed bf16 -> fp16 (:326-368).
     """
     n, words = w.shape
-    groups = words // 8
-    out = np.zeros((n, groups, 36), dtype=np.uint8)
+    groups = words * 8 // group
+    out = np.zeros((n, groups, 4 + group // 2), dtype=np.uint8)
     s16 = bf16_to_f32(scales_bf16).astype(np.float16).view(np.uint16).reshape(n, groups)
     z16 = bf16_to_f32(biases_bf16).astype(np.float16).view(np.uint16).reshape(n, groups)
     out[:, :, 0:2] = s16[:, :, None].view(np.uint8).reshape(n, groups, 2)
     out[:, :, 2:4] = z16[:, :, None].view(np.uint8).reshape(n, groups, 2)
-    out[:, :, 4:] = np.ascontiguousarray(w, dtype=np.uint32).view(np.uint8).reshape(n, groups, 32)
+    out[:, :, 4:] = np.ascontiguousarray(w, dtype=np.uint32).view(np.uint8).reshape(n, groups, group // 2)
     return out
 
 

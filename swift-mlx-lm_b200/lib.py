@@ -39,6 +39,7 @@ class Step(C.Structure):
         ("rope_base", C.c_float),
         ("weight", C.c_char * NAME_MAX),
         ("weight2", C.c_char * NAME_MAX),
+        ("window_left", C.c_int32),
     ]
 
 
@@ -71,6 +72,8 @@ SIGNATURES = {
     "swlm_ctx_destroy": (None, [_P]),
     "swlm_weights_add_q4g64_mlx": (_I, [_P, C.c_char_p, _I, _I, _P, _P, _P, _I]),
     "swlm_weights_add_q4g64_staf": (_I, [_P, C.c_char_p, _I, _I, _P, _I]),
+    "swlm_weights_add_q4g128_mlx": (_I, [_P, C.c_char_p, _I, _I, _P, _P, _P, _I]),
+    "swlm_weights_add_q4g128_staf": (_I, [_P, C.c_char_p, _I, _I, _P, _I]),
     "swlm_weights_add_dense_bf16": (_I, [_P, C.c_char_p, C.c_int64, C.c_int64, _P, _I]),
     "swlm_weights_bytes": (C.c_int64, [_P]),
     "swlm_plan_build": (_I, [_P, C.POINTER(Step), _I, C.POINTER(BuffersDesc), C.POINTER(_P)]),

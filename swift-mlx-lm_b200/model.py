@@ -43,11 +43,19 @@ class WeightStore:
         s = np.ascontiguousarray(scales_bf16, dtype=np.uint16)
         b = np.ascontiguousarray(biases_bf16, dtype=np.uint16)
         n, words = w.shape
-        self.lib.check(self.lib.swlm_weights_add_q4g64_mlx(self.handle, name.encode(), n, words * 8, _ptr(w), _ptr(s), _ptr(b), shard))
+        # the group size (64 or 128 weights per scale / bias pair) follows from the shape of the scales
+        group = words * 8 // s.shape[-1] if s.size else 64
+        if group not in (64, 128) or s.shape != (n, words * 8 // group) or b.shape != s.shape:
+            raise ValueError(f"{name}: scales {s.shape} / biases {b.shape} do not describe groups of 64 or 128 over k={words * 8}")
+        add = self.lib.swlm_weights_add_q4g64_mlx if group == 64 else self.lib.swlm_weights_add_q4g128_mlx
+        self.lib.check(add(self.handle, name.encode(), n, words * 8, _ptr(w), _ptr(s), _ptr(b), shard))
 
-    def add_q4_staf(self, name: str, blocks: np.ndarray, n: int, k: int, shard: int = 0) -> None:
+    def add_q4_staf(self, name: str, blocks: np.ndarray, n: int, k: int, shard: int = 0, group: int = 64) -> None:
         blk = np.ascontiguousarray(blocks, dtype=np.uint8)
-        self.lib.check(self.lib.swlm_weights_add_q4g64_staf(self.handle, name.encode(), n, k, _ptr(blk), shard))
+        if blk.size != n * (k // group) * (4 + group // 2):
+            raise ValueError(f"{name}: {blk.size} bytes are not {n} x {k // group} blocks of {4 + group // 2} bytes")
+        add = self.lib.swlm_weights_add_q4g64_staf if group == 64 else self.lib.swlm_weights_add_q4g128_staf
+        self.lib.check(add(self.handle, name.encode(), n, k, _ptr(blk), shard))
 
     def add_dense(self, name: str, data_bf16: np.ndarray, shard: int = 0) -> None:
         d = np.ascontiguousarray(data_bf16, dtype=np.uint16)

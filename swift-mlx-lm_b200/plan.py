@@ -58,6 +58,11 @@ class ModelConfig:
     # weight (weightBias, 1.0 for checkpoints that store weight - 1).
     activation: str = "silu"
     norm_weight_bias: float = 0.0
+    # Sliding-window attention (windowLeft, Generator/MetalSourceGenerator+Attention.swift:851-853): a token attends
+    # itself and the sliding_window - 1 positions before it; 0 = full attention. `sliding_window_layers` names the
+    # layers that use it (None: every attention layer), the others attend everything.
+    sliding_window: int = 0
+    sliding_window_layers: Sequence[int] = None
 
     def is_attention_layer(self, i: int) -> bool:
         return self.family == "llama" or i in self.attention_layers
@@ -211,7 +216,9 @@ class DispatchPlanBuilder:
                                        weight=p + "self_attn.q_layernorm.weight", weight2=p + "self_attn.k_layernorm.weight"))
                 steps.append(_step(STEP_ATTN_DECODE, layer=kv_layer, in_buf=BUF_S1, in2_buf=BUF_S2, in3_buf=BUF_S3,
                                    out_buf=BUF_S0, heads=c.heads, kv_heads=c.kv_heads, head_dim=c.head_dim,
-                                   rope_dim=c.head_dim, rope_base=c.rope_theta, scale=1.0 / math.sqrt(c.head_dim)))
+                                   rope_dim=c.head_dim, rope_base=c.rope_theta, scale=1.0 / math.sqrt(c.head_dim),
+                                   window_left=c.sliding_window if c.sliding_window > 0 and (
+                                       c.sliding_window_layers is None or i in c.sliding_window_layers) else 0))
                 kv_layer += 1
                 gemv(p + ("self_attn.o_proj" if c.family == "llama" else "self_attn.out_proj"), BUF_S0, BUF_HIDDEN, h, qd)
             else:

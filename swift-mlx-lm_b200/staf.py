@@ -360,9 +360,11 @@ def plan_conversion(tensors: Dict[str, Tuple[str, Tuple[int, ...], np.ndarray]],
                     shard_index: int = 0) -> List[TensorToWrite]:
     """STAFConversionPlanner + STAFPayloadConverter for one shard: a `*.weight` with `.scales` and `.biases` companions
     is an MLX quantized triple (the companions are consumed, STAFConversionPlanner.swift:63-78) and becomes interleaved
-    36-byte blocks; every other tensor is stored row-major in its own dtype. Entries keep the source order."""
-    if (bits, group_size) != (4, 64):
-        raise STAFError(f"MLX quantization bits={bits} group_size={group_size} is outside the hot path (4-bit, group 64)")
+    blocks (36 bytes for group 64, scheme 0x40; 68 bytes for group 128, scheme 0x41); every other tensor is stored
+    row-major in its own dtype. Entries keep the source order. `bits` / `group_size` are the bundle's quantization hint
+    (config.json `quantization`), checked against the tensor shapes as STAFConversionPlanner.verifyTensorShape does."""
+    if bits != 4 or group_size not in (64, 128):
+        raise STAFError(f"MLX quantization bits={bits} group_size={group_size} is outside the hot path (4-bit, group 64 or 128)")
     consumed = set()
     for name in tensors:
         if name.endswith(".weight"):
@@ -384,9 +386,10 @@ def plan_conversion(tensors: Dict[str, Tuple[str, Tuple[int, ...], np.ndarray]],
             def as_bf16(t):
                 return t[2] if t[0] == "BF16" else f32_to_bf16(np.asarray(t[2], dtype=np.float32))
 
-            blocks = repack_mlx_to_staf(np.asarray(arr), as_bf16(scales), as_bf16(biases))
-            out.append(TensorToWrite(name, SCHEME_Q4_G64, semantic_role(name), DTYPE_I32, tuple(shape), blocks.tobytes(),
-                                     block_size=64, group_size=64, shard_index=shard_index))
+            blocks = repack_mlx_to_staf(np.asarray(arr), as_bf16(scales), as_bf16(biases), group=group_size)
+            out.append(TensorToWrite(name, SCHEME_Q4_G64 if group_size == 64 else SCHEME_Q4_G128, semantic_role(name), DTYPE_I32,
+                                     tuple(shape), blocks.tobytes(), block_size=group_size, group_size=group_size,
+                                     shard_index=shard_index))
             continue
         scheme = {"F16": SCHEME_FP16, "BF16": SCHEME_BF16, "F32": SCHEME_FP32}.get(dtype, SCHEME_PASSTHROUGH)
         out.append(TensorToWrite(name, scheme, semantic_role(name), _ST_DTYPES[dtype][1], tuple(shape),
@@ -395,7 +398,7 @@ def plan_conversion(tensors: Dict[str, Tuple[str, Tuple[int, ...], np.ndarray]],
 
 
 def convert_safetensors(safetensors_paths: Sequence[str], staf_path: str, extra_metadata: Optional[Dict[str, MetadataValue]] = None,
-                        force: bool = False) -> bool:
+                        force: bool = False, group_size: int = 64) -> bool:
     """Write `staf_path` from the shards unless a valid cache is already there (STAFConverter's
     convert-if-invalid). Returns True when the file was (re)written."""
     expected = default_cache_metadata(len(safetensors_paths))
@@ -404,7 +407,7 @@ def convert_safetensors(safetensors_paths: Sequence[str], staf_path: str, extra_
         return False
     entries: List[TensorToWrite] = []
     for shard, p in enumerate(sorted(safetensors_paths)):
-        entries += plan_conversion(read_safetensors(p), shard_index=shard)
+        entries += plan_conversion(read_safetensors(p), group_size=group_size, shard_index=shard)
     write_staf(staf_path, entries, expected)
     return True
 
@@ -412,8 +415,8 @@ def convert_safetensors(safetensors_paths: Sequence[str], staf_path: str, extra_
 # ---- into the weight store -------------------------------------------------------------------------------------
 
 def load_into_store(store, staf: STAFFile, shard_kinds: Optional[Dict[str, int]] = None, names: Optional[Iterable[str]] = None) -> List[str]:
-    """Hand every tensor of the file that the hot path can hold to the weight store: 4-bit group-64 block tensors as
-    they are (`swlm_weights_add_q4g64_staf`), dense tensors as bf16 (fp16 and fp32 sources are rounded to bf16, the
+    """Hand every tensor of the file that the hot path can hold to the weight store: 4-bit group-64 / group-128 block
+    tensors as they are (`swlm_weights_add_q4g64_staf`, `swlm_weights_add_q4g128_staf`), dense tensors as bf16 (fp16 and fp32 sources are rounded to bf16, the
     activation dtype of the path). `shard_kinds` maps names to SWLM_SHARD_* for tensor-parallel contexts. Returns the
     names loaded; tensors of other schemes are skipped."""
     shard_kinds = shard_kinds or {}
@@ -423,12 +426,17 @@ def load_into_store(store, staf: STAFFile, shard_kinds: Optional[Dict[str, int]]
         if wanted is not None and e.name not in wanted:
             continue
         raw = np.asarray(staf.data[e.payload_offset:e.payload_offset + e.payload_size])
-        if e.scheme == SCHEME_Q4_G64:
+        if e.scheme in (SCHEME_Q4_G64, SCHEME_Q4_G128):
             n, words = e.shape
             k = words * 8
-            if e.payload_size != n * (k // 64) * 36:
-                raise STAFError(f"{e.name}: payload size does not match {n} x {k} in 36-byte blocks")
-            store.add_q4_staf(e.name, raw.reshape(n, k // 64, 36), n, k, shard_kinds.get(e.name, 0))
+            group = 64 if e.scheme == SCHEME_Q4_G64 else 128
+            bb = 4 + group // 2
+            if k % group or e.payload_size != n * (k // group) * bb:
+                raise STAFError(f"{e.name}: payload size does not match {n} x {k} in {bb}-byte blocks")
+            if group == 64:
+                store.add_q4_staf(e.name, raw.reshape(n, k // 64, 36), n, k, shard_kinds.get(e.name, 0))
+            else:
+                store.add_q4_staf(e.name, raw.reshape(n, k // 128, 68), n, k, shard_kinds.get(e.name, 0), group=128)
         elif e.scheme in (SCHEME_BF16, SCHEME_FP16, SCHEME_FP32, SCHEME_PASSTHROUGH):
             if e.scheme == SCHEME_BF16:
                 arr = raw.view(np.uint16)

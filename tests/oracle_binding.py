@@ -22,8 +22,10 @@ class OracleModel:
             self.h = None
 
     def add_q4(self, name, w, s, b, staf_fp16=False):
+        """The group size (64 or 128) follows from the shape of the scales."""
         w = np.ascontiguousarray(w, dtype=np.uint32); s = np.ascontiguousarray(s, dtype=np.uint16); b = np.ascontiguousarray(b, dtype=np.uint16)
-        rc = self.dll.orc_add_q4(self.h, name.encode(), w.shape[0], w.shape[1] * 8, _p(w), _p(s), _p(b), int(staf_fp16))
+        group = w.shape[1] * 8 // s.shape[1]
+        rc = self.dll.orc_add_q4_group(self.h, name.encode(), w.shape[0], w.shape[1] * 8, group, _p(w), _p(s), _p(b), int(staf_fp16))
         assert rc == 0, self.error()
 
     def add_dense(self, name, data):
@@ -111,6 +113,9 @@ class Oracle:
         d.orc_error.restype = C.c_char_p
         d.orc_error.argtypes = [C.c_void_p]
         d.orc_add_q4.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+        d.orc_add_q4_group.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+        d.orc_staf_repack_mlx_group.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        d.orc_q4_dequant_staf_group.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         d.orc_add_dense.argtypes = [C.c_void_p, C.c_char_p, C.c_int64, C.c_void_p]
         d.orc_set_plan.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         d.orc_reset.argtypes = [C.c_void_p]
@@ -129,6 +134,7 @@ class Oracle:
         d.orc_q4_dequant_staf.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         d.orc_q4_dequant_bf16.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         d.orc_qgemm.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+        d.orc_qgemm_group.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
         d.orc_staf_gemv_f32.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         d.orc_rope_bf16.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
         d.orc_rope_inv_freq.argtypes = [C.c_int, C.c_float, C.c_void_p]
@@ -164,6 +170,19 @@ class Oracle:
         self.dll.orc_staf_repack_mlx(n, k, _p(w), _p(s), _p(b), _p(out))
         return out
 
+    def staf_repack_group(self, w, s, b, group):
+        w = np.ascontiguousarray(w, dtype=np.uint32); s = np.ascontiguousarray(s, dtype=np.uint16); b = np.ascontiguousarray(b, dtype=np.uint16)
+        n, k = w.shape[0], w.shape[1] * 8
+        out = np.empty((n, k // group, 4 + group // 2), dtype=np.uint8)
+        self.dll.orc_staf_repack_mlx_group(n, k, group, _p(w), _p(s), _p(b), _p(out))
+        return out
+
+    def dequant_staf_group(self, blocks, n, k, group):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        out = np.empty((n, k), dtype=np.float32)
+        self.dll.orc_q4_dequant_staf_group(n, k, group, _p(blocks), _p(out))
+        return out
+
     def dequant_staf(self, blocks, n, k):
         blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
         out = np.empty((n, k), dtype=np.float32)
@@ -183,7 +202,7 @@ class Oracle:
         n = w.shape[0]
         y = np.empty((m, n), dtype=np.uint16)
         y64 = np.empty((m, n), dtype=np.float64) if want_f64 else None
-        rc = self.dll.orc_qgemm(m, n, k, _p(x), _p(w), _p(s), _p(b), _p(y), _p(y64) if want_f64 else None, int(staf_fp16))
+        rc = self.dll.orc_qgemm_group(m, n, k, k // s.shape[1], _p(x), _p(w), _p(s), _p(b), _p(y), _p(y64) if want_f64 else None, int(staf_fp16))
         assert rc == 0
         return (y, y64) if want_f64 else y
 

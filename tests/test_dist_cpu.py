@@ -46,6 +46,20 @@ def _worker(rank, world, port, q):
     dist.all_gather_object(pieces, mine.tolist())
     assert np.array_equal(np.concatenate([np.array(p, dtype=np.uint16) for p in pieces], axis=1), orc.qgemm(x, w, s, b))
 
+    # three-section column shard (B|C|x of the short-conv input projection): each rank takes the same channel range of
+    # every third, so the gated conv stays rank-local; the ranks' thirds concatenate to the full thirds
+    r0, rows, c0, cols = pkg.tp.shard_range(lib, P.SHARD_COLUMN3, n, k, rank, world)
+    third = n // 3
+    assert (c0, cols) == (0, k) and rows == third // world and r0 == rank * rows
+    full = orc.qgemm(x, w, s, b)[0]
+    sel = np.concatenate([np.arange(p * third + r0, p * third + r0 + rows) for p in range(3)])
+    mine = orc.qgemm(x, w[sel], s[sel], b[sel])[0]
+    pieces = [None] * world
+    dist.all_gather_object(pieces, mine.tolist())
+    for p in range(3):
+        got = np.concatenate([np.array(piece, dtype=np.uint16)[p * rows:(p + 1) * rows] for piece in pieces])
+        assert np.array_equal(got, full[p * third:(p + 1) * third])
+
     # vocabulary-sharded argmax: (max, global index) pairs, lowest index wins among equal maxima
     logits = pkg.bf16_to_f32(pkg.f32_to_bf16(np.random.default_rng(4).normal(size=4096).astype(np.float32)))
     logits[[100, 3000]] = 9.0

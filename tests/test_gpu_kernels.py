@@ -71,6 +71,33 @@ def test_qgemm_matches_oracle(pkg, store, oracle, n, k, m):
         assert rel_err(got[row], ref64[row]).max() <= RTOL
 
 
+@pytest.mark.parametrize("n,k,m", [(4096, 4096, 1), (100, 384, 3), (1024, 14336, 1), (512, 4096, 16), (768, 2048, 40), (1024, 4096, 128)])
+def test_qgemm_group128_matches_oracle(pkg, store, oracle, n, k, m):
+    """One scale / bias pair per 128 weights (AffineQ4Group128Format): through the MLX entry point and through 68-byte
+    STAF blocks, in the single-sequence kernel, the 2..16-sequence kernel and the tensor-core product. The oracle
+    dequantises with the group-128 parameters natively."""
+    w, s, b = pkg.synth_q4(n, k, seed=n * 13 + k, group=128)
+    assert s.shape == (n, k // 128)
+    rng = np.random.default_rng(m * 5 + 2)
+    x = _bf(pkg, rng.normal(size=(m, k)))
+    store.add_q4_mlx(f"g128.{n}x{k}", w, s, b)
+    store.add_q4_staf(f"g128s.{n}x{k}", pkg.formats.repack_mlx_to_staf(w, s, b, group=128), n, k, group=128)
+    oracle.set_threads(0)
+    for name, fp16 in ((f"g128.{n}x{k}", False), (f"g128s.{n}x{k}", True)):
+        got = pkg.bf16_to_f32(store.qgemm(name, x, n))
+        ref_bf16, ref64 = oracle.qgemm(x, w, s, b, staf_fp16=fp16, want_f64=True)
+        ref = pkg.bf16_to_f32(ref_bf16)
+        for row in range(m):
+            assert rel_err(got[row], ref[row]).max() <= RTOL
+            assert rel_err(got[row], ref64[row]).max() <= RTOL
+    # the dequantised matrix, bit for bit
+    if n * k <= 4096 * 4096:
+        ref = pkg.f32_to_bf16(oracle.dequant_staf_group(oracle.staf_repack_group(w, s, b, 128), n, k, 128))
+        assert np.array_equal(store.dequant_bf16(f"g128s.{n}x{k}", n, k), ref)
+    with pytest.raises(ValueError):
+        store.add_q4_mlx("g128.bad", w, s[:, :-1], b[:, :-1])
+
+
 @pytest.mark.parametrize("m", [17, 40, 63])
 def test_qgemm_17_to_63_rows_ride_in_one_tensor_core_tile(pkg, store, oracle, m):
     """Between 17 and 63 token rows the product runs once over the weights, in a 64-token tensor-core tile whose
@@ -361,6 +388,47 @@ def test_attention_decode_matches_oracle(pkg, store, oracle, hd, heads, kvh, bat
             gk, ok = gm.read_kv(0, 0, b, h, ctx + 1)[ctx], om.read_kv(0, 0, b, h, ctx + 1)[ctx]
             assert rel_err(pkg.bf16_to_f32(gk), pkg.bf16_to_f32(ok)).max() <= RTOL
             assert np.array_equal(gm.read_kv(1, 0, b, h, ctx + 1)[ctx], om.read_kv(1, 0, b, h, ctx + 1)[ctx])
+    gm.close()
+
+
+@pytest.mark.parametrize("window,ctx", [(1, 300), (16, 5), (16, 15), (16, 16), (16, 17), (64, 200), (100, 1000), (1000, 4095),
+                                        (4096, 700), (63, 2111), (129, 4000)])
+@pytest.mark.parametrize("hd,heads,kvh,batch", [(128, 32, 8, 1), (64, 16, 4, 2)])
+def test_attention_decode_sliding_window_matches_oracle(pkg, store, oracle, hd, heads, kvh, batch, window, ctx):
+    """windowLeft: the new token attends itself and the window - 1 cached rows before it, wherever the window's
+    left edge falls relative to the 64-row blocks the splits walk (inside the first block, on a block boundary,
+    whole splits below it), and a window wider than the context changes nothing."""
+    P = pkg.plan
+    max_seq = 4096
+    gm, om = _mini(pkg, store, oracle, batch=batch, hidden=256, slot=heads * hd, max_seq=max_seq, kv_heads=kvh, head_dim=hd)
+    rng = np.random.default_rng(ctx * 7 + window)
+    for b in range(batch):
+        for h in range(kvh):
+            kr, vr = _bf(pkg, rng.normal(size=(ctx, hd))), _bf(pkg, rng.normal(size=(ctx, hd)))
+            for mdl in (gm, om):
+                mdl.write_kv(0, 0, b, h, kr)
+                mdl.write_kv(1, 0, b, h, vr)
+    q = _bf(pkg, rng.normal(size=(batch, heads * hd)))
+    k = _bf(pkg, np.pad(rng.normal(size=(batch, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+    v = _bf(pkg, np.pad(rng.normal(size=(batch, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+    outs = {}
+    for w in (window, 0):
+        step = P._step(P.STEP_ATTN_DECODE, layer=0, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, in3_buf=P.BUF_S3, out_buf=P.BUF_S0,
+                       heads=heads, kv_heads=kvh, head_dim=hd, rope_dim=hd, rope_base=500000.0, scale=1.0 / np.sqrt(hd),
+                       window_left=w)
+        for mdl in (gm, om):
+            mdl.set_position(ctx)
+            mdl.write_buffer(P.BUF_S1, q)
+            mdl.write_buffer(P.BUF_S2, k)
+            mdl.write_buffer(P.BUF_S3, v)
+            mdl.run_step(step)
+        outs[w] = (pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, heads * hd)), pkg.bf16_to_f32(om.read_buffer(P.BUF_S0, heads * hd)))
+    got, ref = outs[window]
+    assert rel_err(got, ref).max() <= RTOL
+    if window > ctx:
+        assert np.array_equal(outs[window][0], outs[0][0])       # the window covers everything
+    else:
+        assert not np.array_equal(outs[window][1], outs[0][1])   # ... or it really leaves rows out
     gm.close()
 
 

@@ -136,3 +136,48 @@ def test_positions_can_be_set_and_bad_arguments_are_refused(pkg, oracle):
     with pytest.raises(pkg.SwlmError):
         gm.reset_sequence(-1)
     gm.close(); store.close()
+
+
+@pytest.mark.parametrize("family,batch,window", [("llama", 1, 16), ("llama", 3, 40), ("lfm2", 1, 24), ("llama", 20, 16)])
+def test_sliding_window_model_against_oracle(pkg, oracle, family, batch, window):
+    """Sliding-window attention through the whole plan: decode steps past the window, for one, a few and more than
+    16 sequences; in the LFM2-like recipe only the first attention layer is windowed."""
+    import dataclasses
+    cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=batch, max_seq=128)
+    cfg = dataclasses.replace(cfg, sliding_window=window, sliding_window_layers=None if family == "llama" else [1])
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    oracle.set_threads(8)
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=10, steps=48 if batch > 16 else 64)
+    assert len(mism) <= 2, mism
+    gm.close(); store.close()
+
+
+@pytest.mark.parametrize("family", ["llama", "lfm2"])
+def test_sliding_window_chunked_prompt(pkg, oracle, family):
+    """A 150-token prompt in chunks of 64 with a 40-token window: the tiled causal kernel masks per row and skips
+    the key tiles wholly left of the window; the oracle ingests token by token."""
+    import dataclasses
+    cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=1, max_seq=256)
+    cfg = dataclasses.replace(cfg, sliding_window=40)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    gm.set_prefill_chunk(64)
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=150, steps=16)
+    assert len(mism) <= 2, mism
+    gm.close(); store.close()
+
+
+@pytest.mark.parametrize("family,batch", [("llama", 1), ("lfm2", 2)])
+def test_group128_weights_model_against_oracle(pkg, oracle, family, batch):
+    """The whole plan over weights quantized in groups of 128 (prompt chunks on the tensor cores, then decode)."""
+    cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=batch, max_seq=160)
+    builder = pkg.DispatchPlanBuilder(cfg)
+    weights = pkg.synth_model_weights(builder, seed=9, group=128)
+    store = pkg.WeightStore(0)
+    gm = pkg.load_model(store, builder, weights)
+    om = oracle.model(cfg.buffers_desc())
+    om.load(builder, weights)
+    oracle.set_threads(8)
+    gm.set_prefill_chunk(64)
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=70 if batch == 1 else 9, steps=32)
+    assert len(mism) <= 2, mism
+    gm.close(); store.close()

@@ -31,6 +31,22 @@ def test_tp2_tokens_match_oracle(mode):
     assert r.stdout.count("TP_OK") == 2, r.stdout[-2000:]
 
 
+def test_tp2_lfm2_conv_layers_split_by_channel():
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _run("parity_lfm2", 2, 29619)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_OK") == 2, r.stdout[-2000:]
+
+
+def test_tp4_lfm2_conv_layers_split_by_channel():
+    if _gpus() < 4:
+        pytest.skip("needs 4 GPUs")
+    r = _run("parity_lfm2", 4, 29621)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_OK") == 4, r.stdout[-2000:]
+
+
 def test_tp4_tokens_match_oracle():
     if _gpus() < 4:
         pytest.skip("needs 4 GPUs")

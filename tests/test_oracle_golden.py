@@ -97,6 +97,38 @@ def test_attention_decode_trace(pkg, oracle, golden, case):
         assert np.array_equal(vc, v.reshape(T, KV, D)[:, h])
 
 
+@pytest.mark.parametrize("window", [1, 3, 8, 100])
+def test_attention_sliding_window_against_fp64_softmax(pkg, oracle, window):
+    """windowLeft (Generator/MetalSourceGenerator+Attention.swift:851-853): position p attends rows
+    max(0, p - W + 1) .. p. The reference's tests hold no known answer for it, so the oracle is checked against an
+    fp64 softmax over exactly those rows."""
+    H, KV, D, T = 4, 2, 64, 12
+    rng = np.random.default_rng(window)
+    q = pkg.bf16_to_f32(pkg.f32_to_bf16(rng.normal(size=(T, H * D)).astype(np.float32)))
+    k = pkg.bf16_to_f32(pkg.f32_to_bf16(rng.normal(size=(T, KV * D)).astype(np.float32)))
+    v = pkg.bf16_to_f32(pkg.f32_to_bf16(rng.normal(size=(T, KV * D)).astype(np.float32)))
+    desc = pkg.BuffersDesc(hidden=H * D, slot_dim=H * D, vocab=8, max_seq=16, max_batch=1, kv_layers=1,
+                           kv_heads=KV, head_dim=D, conv_layers=0, conv_dim=0, conv_kernel=0)
+    m = oracle.model(desc)
+    step = pkg.plan._step(pkg.plan.STEP_ATTN_DECODE, layer=0, in_buf=3, in2_buf=4, in3_buf=5, out_buf=2, heads=H,
+                          kv_heads=KV, head_dim=D, rope_dim=0, rope_base=0.0, scale=1.0 / np.sqrt(D), window_left=window)
+    for t in range(T):
+        m.set_position(t)
+        m.write_buffer(3, pkg.f32_to_bf16(q[t]))
+        m.write_buffer(4, pkg.f32_to_bf16(np.pad(k[t], (0, (H - KV) * D))))
+        m.write_buffer(5, pkg.f32_to_bf16(np.pad(v[t], (0, (H - KV) * D))))
+        m.run_step(step)
+        out = pkg.bf16_to_f32(m.read_buffer(2, H * D))[0].reshape(H, D)
+        lo = max(0, t - window + 1)
+        for h in range(H):
+            kh = h * KV // H
+            keys = k[lo:t + 1].reshape(-1, KV, D)[:, kh].astype(np.float64)
+            vals = v[lo:t + 1].reshape(-1, KV, D)[:, kh].astype(np.float64)
+            sc = keys @ q[t].reshape(H, D)[h].astype(np.float64) / np.sqrt(D)
+            w = np.exp(sc - sc.max()); w /= w.sum()
+            assert np.max(np.abs(out[h] - w @ vals)) < 2e-2
+
+
 def test_conv_decode_trace_matches_sequence_formula_bit_for_bit(pkg, oracle, golden):
     g = golden["conv_pattern"]
     D, K, T = g["dim"], g["kernel"], g["seq_len"]

@@ -136,6 +136,41 @@ def test_unsupported_quantization_is_refused(pkg, staf, golden, tmp_path):
         staf.plan_conversion(staf.read_safetensors(src), bits=8, group_size=64)
 
 
+def test_group128_bundle_becomes_68_byte_blocks(pkg, staf, oracle, tmp_path):
+    """AffineQ4Group128Format (STAF/QuantizationFormat.swift:539-604): scheme 0x41, 128 weights per 68-byte block, the
+    same per-weight expression. The file's blocks equal the oracle's repack byte for byte and dequantise to
+    scale * q + zero with the fp16-narrowed group-128 parameters."""
+    n, k = 6, 384
+    w, s, b = pkg.synth_q4(n, k, seed=77, group=128)
+    src = os.path.join(tmp_path, "g128.safetensors")
+    staf.write_safetensors(src, {"model.layers.0.mlp.up_proj.weight": ("U32", w),
+                                 "model.layers.0.mlp.up_proj.scales": ("BF16", s),
+                                 "model.layers.0.mlp.up_proj.biases": ("BF16", b)})
+    out = os.path.join(tmp_path, "g128.staf")
+    with pytest.raises(staf.STAFError):
+        staf.convert_safetensors([src], out)                       # the default hint (group 64) contradicts the shapes
+    assert staf.convert_safetensors([src], out, group_size=128) is True
+    f = staf.read_staf(out)
+    e = f["model.layers.0.mlp.up_proj.weight"]
+    assert (e.scheme, e.block_size, e.group_size, e.payload_size) == (staf.SCHEME_Q4_G128, 128, 128, n * (k // 128) * 68)
+    blocks = np.asarray(f.payload(e.name)).reshape(n, k // 128, 68)
+    assert np.array_equal(blocks, oracle.staf_repack_group(w, s, b, 128))
+    assert np.array_equal(blocks, pkg.formats.repack_mlx_to_staf(w, s, b, group=128))
+    deq = oracle.dequant_staf_group(blocks, n, k, 128)
+    q = np.array([[(int(w[r, c // 8]) >> (4 * (c % 8))) & 15 for c in range(k)] for r in range(n)], dtype=np.float32)
+    s16 = pkg.bf16_to_f32(s).astype(np.float16).astype(np.float32)
+    z16 = pkg.bf16_to_f32(b).astype(np.float16).astype(np.float32)
+    assert np.array_equal(deq, np.repeat(s16, 128, axis=1) * q + np.repeat(z16, 128, axis=1))
+
+    class Recorder:
+        def add_q4_staf(self, name, blk, n_, k_, shard=0, group=64):
+            self.got = (name, np.array(blk).shape, n_, k_, shard, group)
+
+    rec = Recorder()
+    staf.load_into_store(rec, f)
+    assert rec.got == (e.name, (n, k // 128, 68), n, k, 0, 128)
+
+
 def test_load_into_store_routes_by_scheme(pkg, staf, golden, tmp_path):
     """`load_into_store` against a recording stand-in for the weight store: block tensors go in as blocks with
     (n, k) recovered from the packed shape, dense tensors as bf16 rows, fp32 sources rounded to bf16."""

@@ -2,6 +2,8 @@
 
 mode "parity":  small Llama-shape model sharded over WORLD_SIZE GPUs; prompt + greedy steps, every rank checks its
                 tokens against the CPU oracle of the unsharded model.
+mode "parity_lfm2": the same for a small LFM2-like model: short-conv layers with their channels split across ranks
+                (three-section column shard of the B|C|x projection) next to attention layers with QK-norm.
 mode "timeout": the last rank stays alive but never decodes; the others' bounded waits must expire and
                 surface as SWLM_ERR_TIMEOUT. No rank exits, traps or faults while kernels are in flight.
 """
@@ -26,7 +28,11 @@ def main():
     dist.init_process_group("gloo")  # host-side plumbing only; the data path is the library's own kernels
     pkg = load_package()
     batch = 2 if mode == "parity2" else 1
-    if world > 4:   # one KV head per rank at 8 ranks
+    if mode == "parity_lfm2":
+        cfg = pkg.ModelConfig("lfm2", hidden=512, intermediate=1024, layers=5, heads=8, kv_heads=4, head_dim=64,
+                              vocab=4096, norm_eps=1e-5, rope_theta=1000000.0, conv_kernel=3, attention_layers=[1, 3],
+                              max_seq=96, max_batch=batch)
+    elif world > 4:   # one KV head per rank at 8 ranks
         cfg = pkg.ModelConfig("llama", hidden=1024, intermediate=2048, layers=3, heads=16, kv_heads=8, head_dim=64,
                               vocab=4096, max_seq=96, max_batch=batch)
     else:
