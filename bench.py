@@ -102,13 +102,14 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def model_config(pkg, args, max_seq):
+def model_config(pkg, args, max_seq, world=1):
     if args.small:  # debugging aid; never the reported workload
         return pkg.ModelConfig("llama", hidden=1024, intermediate=2816, layers=4, heads=8, kv_heads=2, head_dim=128,
                                vocab=8192, max_seq=max_seq, max_batch=args.batch)
     if args.model == "lfm2":
         # hybrid conv/attention shape; output head tied to a Q4 embedding table (the MLX-bundle convention)
-        return pkg.lfm2_like_config(max_seq=max_seq, max_batch=args.batch)
+        # (under tensor parallelism the head is a tensor of its own: a vocabulary-sharded table cannot serve the gather)
+        return pkg.lfm2_like_config(max_seq=max_seq, max_batch=args.batch, tie_embeddings=world == 1)
     return pkg.llama3_8b_config(max_seq=max_seq, max_batch=args.batch)
 
 
@@ -347,7 +348,7 @@ def main():
     tp_parity = tp_parity_check(pkg, dist, rank, world, local_rank) if world > 1 else None
     warm = max(3, args.warmup)
     max_seq = args.ctx + 2 * (warm + args.steps) + 64 + 8 * 64   # + room for the clock sampler's extra warm-up bursts
-    cfg = model_config(pkg, args, max_seq)
+    cfg = model_config(pkg, args, max_seq, world)
     builder = pkg.DispatchPlanBuilder(cfg)
     weights = pkg.synth_model_weights(builder, seed=3)
     store = pkg.WeightStore(local_rank, tp_rank=rank, tp_size=world)

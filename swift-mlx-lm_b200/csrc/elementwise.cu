@@ -334,6 +334,59 @@ __global__ void advance_kernel(int m, int32_t* position, int32_t* step_counter) 
     if (step_counter && threadIdx.x == 0) step_counter[0] += 1;
 }
 
+// ---- tensor parallel: all-reduce of a prompt chunk's partial rows ------------------------------------------------
+// Push: rows x hidden bf16 of this rank into slot [parity][this rank] of every rank's exchange buffer (plain peer
+// stores, 16 bytes each); the last CTA to finish raises the flag on every rank.
+__global__ void tp_rows_push_kernel(TpParams tp, const __nv_bfloat16* x, int x_stride, int rows, int hidden, int epoch,
+                                    unsigned* done_counter) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int par = epoch & 1, vec_per_row = hidden / 8;
+    const size_t n_vec = (size_t)rows * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / vec_per_row), c = (int)(i - (size_t)r * vec_per_row);
+        const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)r * x_stride + (size_t)c * 8);
+        for (int dst = 0; dst < tp.tp; ++dst)
+            *reinterpret_cast<uint4*>(tp.peer[dst] + tp.lay.recv_rows(par, tp.rank) + ((size_t)r * hidden + (size_t)c * 8) * 2) = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int last;
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(done_counter, 1u);
+        last = prev == gridDim.x - 1;
+        if (last) *done_counter = 0u;   // ready for the next exchange
+    }
+    __syncthreads();
+    if (last && threadIdx.x < tp.tp)
+        st_release_sys(reinterpret_cast<unsigned*>(tp.peer[threadIdx.x] + tp.lay.flags_rows(par, tp.rank)), (unsigned)epoch);
+}
+
+// Reduce: wait (bounded) for every rank's flag, then x = bf16(sum over ranks, in rank order, in fp32).
+__global__ void tp_rows_reduce_kernel(TpParams tp, __nv_bfloat16* x, int x_stride, int rows, int hidden, int epoch) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int par = epoch & 1, vec_per_row = hidden / 8;
+    const unsigned char* own = tp.peer[tp.rank];
+    if (*reinterpret_cast<volatile int*>(tp.status) == 0) tp_wait_flags(tp, own, tp.lay.flags_rows(par, 0), epoch, threadIdx.x);
+    __syncthreads();
+    const size_t n_vec = (size_t)rows * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / vec_per_row), c = (int)(i - (size_t)r * vec_per_row);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int src = 0; src < tp.tp; ++src) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(own + tp.lay.recv_rows(par, src) + ((size_t)r * hidden + (size_t)c * 8) * 2));
+            const unsigned u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { acc[2 * j] += __uint_as_float(u[j] << 16); acc[2 * j + 1] += __uint_as_float(u[j] & 0xffff0000u); }
+        }
+        uint4 o;
+        o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(x + (size_t)r * x_stride + (size_t)c * 8) = o;
+    }
+}
+
 int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, what);
@@ -425,6 +478,20 @@ int launch_argmax(int m, int n, const __nv_bfloat16* logits, int stride, int32_t
     launch_k(argmax_final_kernel, 1, 256, 0, s, m, scratch_val, scratch_idx, token_out, token_in_next, ring, step_counter,
                                           ring_cap, position, advance, tp, am_epoch, shard_offset);
     return check_launch("argmax launch");
+}
+
+int launch_tp_rows_allreduce(const TpParams& tp, __nv_bfloat16* x, int x_stride, int rows, int hidden, int epoch,
+                             unsigned* done_counter, cudaStream_t s) {
+    if (tp.tp < 2 || rows < 1 || rows > tp.lay.rows || hidden != tp.lay.hidden || (hidden & 7) || (x_stride & 7) ||
+        (reinterpret_cast<uintptr_t>(x) & 15)) {
+        set_error("tensor-parallel row exchange: %d rows x %d (capacity %d x %d)", rows, hidden, tp.lay.rows, tp.lay.hidden);
+        return SWLM_ERR_INVALID;
+    }
+    const size_t n_vec = (size_t)rows * (hidden / 8);
+    const unsigned grid = (unsigned)std::min<size_t>(148, (n_vec + 1023) / 1024);
+    launch_k(tp_rows_push_kernel, grid, 256, 0, s, tp, (const __nv_bfloat16*)x, x_stride, rows, hidden, epoch, done_counter);
+    launch_k(tp_rows_reduce_kernel, grid, 256, 0, s, tp, x, x_stride, rows, hidden, epoch);
+    return check_launch("tp rows all-reduce launch");
 }
 
 int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s) {

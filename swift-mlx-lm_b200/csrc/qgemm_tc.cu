@@ -58,6 +58,11 @@ struct QGemmTcParams {
     __nv_bfloat16* y;         // [m][y_stride]
     int y_stride;
     int* status;              // set non-zero when a bounded wait expired
+    // launches of at most 64 token rows over few weight rows: K is cut into gridDim.z ranges of `split_steps` groups
+    // (a multiple of 8) so that more SMs take part; every range writes its fp32 sums to part[z][m][n] and a second
+    // launch adds the ranges in order. The last range also takes the appended group-sum steps.
+    float* part;
+    int split_steps;
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -147,7 +152,11 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     const int r = (warp & 3) * 32 + lane, part = (warp >> 2) & 3;   // TMEM lane = weight row; part: which 16 of the group's 64 columns
     const int row0 = blockIdx.x * kTcRows, tok0 = blockIdx.y * BN;
     const int kt_total = p.k / kTcBK;
-    const int steps_total = kt_total + p.ext_steps;   // real groups, then the appended group-sum columns
+    // this CTA's range of groups [kt_lo, kt_lo + real_steps) and, for the last range, the appended group-sum columns
+    const int kt_lo = gridDim.z > 1 ? (int)blockIdx.z * p.split_steps : 0;
+    const int real_steps = gridDim.z > 1 ? min(p.split_steps, kt_total - kt_lo) : kt_total;
+    const int ext_steps = blockIdx.z == gridDim.z - 1 ? p.ext_steps : 0;
+    const int steps_total = real_steps + ext_steps;
     unsigned char* const b_ring = smem;
 
     if (tid == 0) {
@@ -220,13 +229,14 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
                 if (kt >= SB && !mbar_wait(&empty_bar[s], (unsigned)((kt / SB - 1) & 1))) { atomicExch(p.status, 3); failed = 1; break; }
                 if (failed) break;
                 const unsigned bar = smem_u32(&full_bar[s]);
-                const bool real = kt < kt_total;   // an appended step has activations (the group sums) but no packed weights
+                const bool real = kt < real_steps;   // an appended step has activations (the group sums) but no packed weights
+                const int kg = real ? kt_lo + kt : kt_total + (kt - real_steps);   // 64-column step within the activation rows
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)(real ? STAGE_BYTES : B_BYTES)) : "memory");
                 if (real)
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                                 ::"r"(smem_u32(b_ring + s * STAGE_BYTES + B_BYTES)), "l"(reinterpret_cast<unsigned long long>(&wmap)), "r"(kt * 32), "r"(row0), "r"(bar) : "memory");
+                                 ::"r"(smem_u32(b_ring + s * STAGE_BYTES + B_BYTES)), "l"(reinterpret_cast<unsigned long long>(&wmap)), "r"(kg * 32), "r"(row0), "r"(bar) : "memory");
                 asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(smem_u32(b_ring + s * STAGE_BYTES)), "l"(reinterpret_cast<unsigned long long>(&xmap)), "r"(kt * kTcBK), "r"(tok0), "r"(bar) : "memory");
+                             ::"r"(smem_u32(b_ring + s * STAGE_BYTES)), "l"(reinterpret_cast<unsigned long long>(&xmap)), "r"(kg * kTcBK), "r"(tok0), "r"(bar) : "memory");
                 issued = kt + 1;
             }
             if (failed) {
@@ -236,7 +246,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         }
         __syncwarp();
     } else {
-    uint4 s_cur = load8(srow, 0), z_cur = load8(zrow, 0), s_nxt = load8(srow, 8), z_nxt = load8(zrow, 8);
+    uint4 s_cur = load8(srow, kt_lo), z_cur = load8(zrow, kt_lo), s_nxt = load8(srow, kt_lo + 8), z_nxt = load8(zrow, kt_lo + 8);
 
     // ring bookkeeping without divisions: stage and parity of this group's activations/packed weights, and of
     // the group SA back whose MMAs free this group's weight tile
@@ -293,18 +303,19 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * as) : "memory");
         if (++as == SA) as = 0;
     };
-    for (int kt0 = 0; kt0 < kt_total && !failed; kt0 += 8) {
-        if (kt0 > 0) { s_cur = s_nxt; z_cur = z_nxt; s_nxt = load8(srow, kt0 + 8); z_nxt = load8(zrow, kt0 + 8); }
+    // (group indices are local to this CTA's range: they only drive the rings; the scales come from kt_lo on)
+    for (int kt0 = 0; kt0 < real_steps && !failed; kt0 += 8) {
+        if (kt0 > 0) { s_cur = s_nxt; z_cur = z_nxt; s_nxt = load8(srow, kt_lo + kt0 + 8); z_nxt = load8(zrow, kt_lo + kt0 + 8); }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            if (kt0 + j < kt_total) group(kt0 + j, j);
+            if (kt0 + j < real_steps) group(kt0 + j, j);
     }
     // ---- appended steps: the A operand is the groups' constant term c = 64 (zero + 8 scale) as an fp16 pair (hi, lo);
     // plane 0 carries c_hi (against sum_hi), plane 1 c_lo (against sum_hi), plane 2 c_hi (against sum_lo); the
     // activation side holds sum / 64 so that neither factor leaves fp16's range -----------------------------------
     const int plane_steps = p.ext_steps / 3;
-    for (int e = 0; e < p.ext_steps && !failed; ++e) {
-        const int kt = kt_total + e;
+    for (int e = 0; e < ext_steps && !failed; ++e) {
+        const int kt = real_steps + e;
         if (kt >= SA) {
             if (!mbar_wait_addr(empty0 + 8u * es, epar)) { atomicExch(p.status, 1); failed = 1; }
             if (++es == SB) { es = 0; epar ^= 1u; }
@@ -365,8 +376,13 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int tkn = tok0 + c0 + i;
-                    // undo the token row's power-of-two scaling (exact), round once to bf16
-                    if (tkn < p.m) p.y[(size_t)tkn * p.y_stride + erow] = __float2bfloat16_rn(__uint_as_float(v[i]) * __ldg(p.rscale + tkn));
+                    // undo the token row's power-of-two scaling (exact), round once to bf16 (or leave this K range's
+                    // sum for the launch that adds the ranges up)
+                    if (tkn < p.m) {
+                        const float val = __uint_as_float(v[i]) * __ldg(p.rscale + tkn);
+                        if (gridDim.z > 1) p.part[((size_t)blockIdx.z * p.m + tkn) * p.n + erow] = val;
+                        else p.y[(size_t)tkn * p.y_stride + erow] = __float2bfloat16_rn(val);
+                    }
                 }
             }
         }
@@ -374,6 +390,19 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTmemCols) : "memory");
+}
+
+// Y[t][n] = bf16(sum over the K ranges, in order) for a launch whose K was cut in `splits` ranges.
+__global__ void __launch_bounds__(256) tc_sum_splits_kernel(const float* part, int splits, int m, int n, __nv_bfloat16* y, int y_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t total = (size_t)m * n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < splits; ++z) acc += __ldcg(part + (size_t)z * total + i);
+        const int t = (int)(i / n), r = (int)(i - (size_t)t * n);
+        y[(size_t)t * y_stride + r] = __float2bfloat16_rn(acc);
+    }
 }
 
 // Activations bf16 -> fp16, one CTA per token row: the row's largest magnitude goes to [2^14, 2^15), so that nothing
@@ -482,11 +511,38 @@ int tc_launch_one(const QGemmTcParams& p, bool f16, cudaStream_t s) {
     int rc = make_x_map(p.x, p.x_stride, p.m, p.x_stride, BN, &xmap);   // the appended columns are part of the tensor
     if (rc) return rc;
     if ((rc = make_w_map(p.w, p.n, p.k, &wmap))) return rc;
-    const dim3 grid((unsigned)((p.n + kTcRows - 1) / kTcRows), (unsigned)((p.m + BN - 1) / BN), 1);
+    const int splits = p.split_steps > 0 ? (p.k / kTcBK + p.split_steps - 1) / p.split_steps : 1;
+    const dim3 grid((unsigned)((p.n + kTcRows - 1) / kTcRows), (unsigned)((p.m + BN - 1) / BN), (unsigned)splits);
     const cudaError_t e = f16 ? launch_k(qgemm_tc_kernel<BN, STAGES, true>, grid, dim3(kTcAllThreads), tc_smem_bytes<BN, STAGES>(), s, p, xmap, wmap)
                               : launch_k(qgemm_tc_kernel<BN, STAGES, false>, grid, dim3(kTcAllThreads), tc_smem_bytes<BN, STAGES>(), s, p, xmap, wmap);
     if (e != cudaSuccess) return cuda_fail(e, "qgemm_tc launch");
+    if (splits > 1) {
+        const size_t total = (size_t)p.m * p.n;
+        const cudaError_t e2 = launch_k(tc_sum_splits_kernel, dim3((unsigned)std::min<size_t>(296, (total + 1023) / 1024)), dim3(256), 0, s,
+                                        (const float*)p.part, splits, p.m, p.n, p.y, p.y_stride);
+        if (e2 != cudaSuccess) return cuda_fail(e2, "qgemm_tc split sum launch");
+    }
     return SWLM_OK;
+}
+
+// K ranges for a launch of at most 64 token rows: as many as keep all CTAs resident at once (two per SM for the
+// 64-token tile: 576 threads x 42 registers, 74 KB of shared memory, 128 columns of tensor memory each), each a whole
+// number of 8-group blocks (the scale/zero vectors are read 8 groups at a time) and all of equal length. 0 = no split.
+constexpr int kTcSplitMaxRows = 64;
+constexpr int kTcSplitMaxCtas = 296;
+constexpr size_t kTcSplitBytes = (size_t)kTcSplitMaxRows * kTcSplitMaxCtas * kTcRows * 4;   // fp32 partial sums of all CTAs
+int tc_pick_split_steps(int m, int n, int k) {
+    static const bool off = [] { const char* v = getenv("SWLM_TC_KSPLIT"); return v && v[0] == '0'; }();
+    if (off || m > kTcSplitMaxRows) return 0;
+    static const int cap = [] { const char* v = getenv("SWLM_TC_KSPLIT_CTAS"); const int c = v ? atoi(v) : 0; return c >= 1 && c <= kTcSplitMaxCtas ? c : kTcSplitMaxCtas; }();
+    const int n_tiles = (n + kTcRows - 1) / kTcRows, kt_total = k / kTcBK;
+    int best = 0;
+    for (int per = kt_total - 8; per >= 8; per -= 8) {
+        if (kt_total % per) continue;
+        if (n_tiles * (kt_total / per) > cap) break;
+        best = per;
+    }
+    return best;
 }
 
 }  // namespace
@@ -505,13 +561,15 @@ int qgemm_tc_init() {
 // 256 columns of the MMA), else 128 or 64.
 // columns of one plane of appended group sums: the groups of a row, padded to whole 64-column steps
 static int ext_plane_cols(int k) { return (k / 64 + 63) / 64 * 64; }
-size_t qgemm_tc_scratch_bytes(int m, int k) { return ((size_t)m * (k + 3 * ext_plane_cols(k)) * 2 + 255) / 256 * 256 + (size_t)m * 4; }
+// [partial sums of a K-split launch][fp16 activations + group sums][one float per token row]
+size_t qgemm_tc_scratch_bytes(int m, int k) { return kTcSplitBytes + ((size_t)m * (k + 3 * ext_plane_cols(k)) * 2 + 255) / 256 * 256 + (size_t)m * 4; }
 
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
                     void* scratch, int* status, cudaStream_t s, bool reuse_x) {
-    __half* xh = static_cast<__half*>(scratch);
+    float* part = static_cast<float*>(scratch);
+    __half* xh = scratch ? reinterpret_cast<__half*>(static_cast<unsigned char*>(scratch) + kTcSplitBytes) : nullptr;
     const int g_pad = ext_plane_cols(w.k), xh_stride = w.k + 3 * g_pad;
-    float* rscale = scratch ? reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + ((size_t)m * xh_stride * 2 + 255) / 256 * 256) : nullptr;
+    float* rscale = scratch ? reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + kTcSplitBytes + ((size_t)m * xh_stride * 2 + 255) / 256 * 256) : nullptr;
     if (w.k % kTcBK || (x_stride & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(xh) & 15) || !xh || !rscale) {
         set_error("qgemm (tcgen05): bad shape, alignment or scratch");
         return SWLM_ERR_INVALID;
@@ -526,6 +584,8 @@ int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride,
     p.w = w.w; p.scales = w.scales; p.biases = w.biases; p.n = w.n; p.k = w.k;
     p.x = xh; p.rscale = rscale; p.x_stride = xh_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;
     p.ext_steps = 3 * g_pad / 64;
+    p.part = part;
+    p.split_steps = tc_pick_split_steps(m, w.n, w.k);
     int rc;
     int bn = m > 128 ? 256 : m > 64 ? 128 : 64;
     static const int forced_bn = [] { const char* v = getenv("SWLM_TC_BN"); return v ? atoi(v) : 0; }();

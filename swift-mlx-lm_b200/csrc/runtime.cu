@@ -573,7 +573,8 @@ struct swlm_state {
     // tensor-parallel exchange (tp_size > 1): this rank's buffer, the peers' mappings, local counters
     TpParams tp{};
     bool tp_attached = false;
-    int32_t* tp_words = nullptr;  // [0] all-reduce epoch, [1] rows-done counter, [2] status, [3] argmax epoch
+    int32_t* tp_words = nullptr;  // [0] all-reduce epoch, [1] rows-done counter, [2] status, [3] argmax epoch, [4] CTAs done pushing a prompt chunk
+    int tp_rows_epoch = 0;        // prompt-chunk exchanges issued so far (the same count on every rank)
     int32_t* h_tok = nullptr;  // pinned host staging, 2 * max_batch
     std::vector<int> pos_host;   // host mirror of the per-sequence positions
     long long steps_host = 0;
@@ -874,8 +875,12 @@ int check_position_room(swlm_state* s, int steps) {
 constexpr int kPrefillMinChunk = 32;
 
 // can the plan's steps run row-wise (enqueue_rows)?
-bool rows_capable(const swlm_plan* plan) {
-    if (plan->ctx->tp_size != 1 || plan->desc.head_dim > 128) return false;
+// Prompt chunks of one sequence under tensor parallelism: up to this many token rows per exchange.
+constexpr int kTpChunkRows = 256;
+
+bool rows_capable(const swlm_plan* plan, bool allow_tp = false) {
+    if ((plan->ctx->tp_size != 1 && !allow_tp) || plan->desc.head_dim > 128) return false;
+    if (plan->ctx->tp_size > 1 && (plan->desc.hidden & 7)) return false;
     for (const swlm_step& st : plan->steps) {
         if (st.kind == SWLM_STEP_QGEMV && st.in_buf == st.out_buf) return false;
         if (st.kind == SWLM_STEP_QGEMV && (st.k & 63)) return false;
@@ -884,7 +889,7 @@ bool rows_capable(const swlm_plan* plan) {
     return true;
 }
 
-bool prefill_batchable(const swlm_plan* plan) { return plan->desc.max_batch == 1 && rows_capable(plan); }
+bool prefill_batchable(const swlm_plan* plan) { return plan->desc.max_batch == 1 && rows_capable(plan, true); }
 
 int widest_activation(const swlm_state* s) {
     int widest = 0;
@@ -961,6 +966,7 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
         return r;
     };
     bool advanced = false;
+    const int tp = ctx->tp_size;   // > 1 only for prompt chunks: heads, conv channels and the products' rows are this rank's share
     for (const swlm_step& st : plan->steps) {
         const bool is_product = st.kind == SWLM_STEP_QGEMV;
         switch (st.kind) {
@@ -998,16 +1004,23 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
                 break;
             }
             rc = product(raw, c, pf[st.in_buf], wd[st.in_buf], pf[st.out_buf], wd[st.out_buf]);
+            if (!rc && tp > 1 && raw.shard_kind == SWLM_SHARD_ROW) {
+                // row-parallel weight: the rows are partial sums; add them up across the ranks, in place
+                rc = launch_tp_rows_allreduce(s->tp, pf[st.out_buf], wd[st.out_buf], c, raw.n, ++s->tp_rows_epoch,
+                                              reinterpret_cast<unsigned*>(s->tp_words + 4), stream);
+                s->launches += 2;
+                converted = nullptr;
+            }
             break;
         }
         case SWLM_STEP_QK_NORM:
-            rc = launch_qk_norm(c, st.heads, kv_heads_local(plan), st.head_dim, pf[st.in_buf], wd[st.in_buf], pf[st.in2_buf], wd[st.in2_buf],
+            rc = launch_qk_norm(c, st.heads / tp, kv_heads_local(plan), st.head_dim, pf[st.in_buf], wd[st.in_buf], pf[st.in2_buf], wd[st.in2_buf],
                                 find_dense(ctx, st.weight)->data, find_dense(ctx, st.weight2)->data, st.eps, st.weight_bias, stream);
             s->launches += 1;
             break;
         case SWLM_STEP_ATTN_DECODE: {
             AttnLaunch a;
-            a.m = c; a.heads = st.heads; a.kv_heads = kv_heads_local(plan); a.head_dim = st.head_dim;
+            a.m = c; a.heads = st.heads / tp; a.kv_heads = kv_heads_local(plan); a.head_dim = st.head_dim;
             a.rope_dim = st.rope_dim;
             if (st.rope_dim > 0) {
                 int ti = -1;
@@ -1032,7 +1045,7 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
         }
         case SWLM_STEP_SWIGLU:
         case SWLM_STEP_GEGLU:
-            rc = launch_swiglu(c, st.n, pf[st.in_buf], wd[st.in_buf], pf[st.in2_buf], wd[st.in2_buf], pf[st.out_buf], wd[st.out_buf],
+            rc = launch_swiglu(c, st.n / tp, pf[st.in_buf], wd[st.in_buf], pf[st.in2_buf], wd[st.in2_buf], pf[st.out_buf], wd[st.out_buf],
                                st.kind == SWLM_STEP_GEGLU ? GATED_ACT_GELU_TANH : GATED_ACT_SILU, stream);
             s->launches += 1;
             break;
@@ -1042,7 +1055,7 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
                                       (size_t)d.conv_kernel * d.conv_dim, pf[st.in_buf], wd[st.in_buf], find_dense(ctx, st.weight)->data,
                                       pf[st.out_buf], wd[st.out_buf], stream);
             else
-                rc = launch_conv_prefill(c, st.n, st.conv_kernel,
+                rc = launch_conv_prefill(c, st.n / tp, st.conv_kernel,
                                          s->conv + (size_t)st.layer * s->conv_layer_elems + (size_t)seq * d.conv_kernel * d.conv_dim,
                                          pf[st.in_buf], wd[st.in_buf], find_dense(ctx, st.weight)->data, pf[st.out_buf], wd[st.out_buf], stream);
             s->launches += 1;
@@ -1516,10 +1529,13 @@ int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_tok
     // prefill replays the decode plan's lm_head + argmax for the final position
     // (Execution/MetalPrefillExecutor.swift:1320-1359).
     int t = 0;
-    if (s->prefill_chunk >= kPrefillMinChunk && prefill_batchable(s->plan)) {
+    // under tensor parallelism a chunk is bounded by what one exchange of partial rows carries
+    const bool tp_run = s->plan->ctx->tp_size > 1;
+    const int chunk_cap = tp_run ? std::min(s->prefill_chunk, s->tp.lay.rows) : s->prefill_chunk;
+    if (chunk_cap >= kPrefillMinChunk && prefill_batchable(s->plan) && (!tp_run || s->tp_attached)) {
         while (n - 1 - t >= kPrefillMinChunk) {
-            const int c = std::min(s->prefill_chunk, n - 1 - t);
-            if ((rc = prefill_workspace(s, std::min(s->prefill_chunk, n - 1)))) return rc;
+            const int c = std::min(chunk_cap, n - 1 - t);
+            if ((rc = prefill_workspace(s, std::min(chunk_cap, n - 1)))) return rc;
             if ((rc = enqueue_prefill_chunk(s, s->prompt + t, c, s->pos_host[0], 0, s->stream))) return rc;
             s->pos_host[0] += c;
             t += c;
@@ -1711,13 +1727,13 @@ int swlm_tp_export(swlm_state* s, void* handle_out) {
     if (rc) return rc;
     if (!s->tp.peer[ctx->tp_rank]) {
         s->tp.tp = ctx->tp_size; s->tp.rank = ctx->tp_rank;
-        s->tp.lay = TpLayout{ctx->tp_size, s->plan->desc.max_batch, s->plan->desc.hidden};
+        s->tp.lay = TpLayout{ctx->tp_size, s->plan->desc.max_batch, s->plan->desc.hidden, prefill_batchable(s->plan) ? kTpChunkRows : 0};
         unsigned char* buf = nullptr;
         if ((rc = dev_alloc(&buf, s->tp.lay.total()))) return rc;
         SWLM_CUDA(cudaMemset(buf, 0, s->tp.lay.total()));
         s->tp.peer[ctx->tp_rank] = buf;
-        if ((rc = dev_alloc(&s->tp_words, 4))) return rc;
-        SWLM_CUDA(cudaMemset(s->tp_words, 0, 16));
+        if ((rc = dev_alloc(&s->tp_words, 8))) return rc;
+        SWLM_CUDA(cudaMemset(s->tp_words, 0, 32));
         s->tp.epoch = s->tp_words; s->tp.done = reinterpret_cast<unsigned*>(s->tp_words + 1); s->tp.status = s->tp_words + 2;
         s->tp.host_status = s->tc_status;
         SWLM_CUDA(cudaDeviceSynchronize());

@@ -273,6 +273,11 @@ size_t qgemm_tc_scratch_bytes(int m, int k);   // fp16 copy of the activations +
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
                     void* scratch, int* status, cudaStream_t s, bool reuse_x = false);
 
+// Tensor-parallel sum of `rows` bf16 partial rows (prompt chunks): every rank copies its partials into every rank's
+// exchange buffer and raises a flag carrying `epoch` (the host counts exchanges); then each rank waits (bounded) for
+// all flags and adds the partials in rank order into `x` (in place). Two launches.
+int launch_tp_rows_allreduce(const TpParams& tp, __nv_bfloat16* x, int x_stride, int rows, int hidden, int epoch,
+                             unsigned* done_counter, cudaStream_t s);
 int launch_fill_u32(uint32_t* p, size_t n, uint32_t v, cudaStream_t s);
 int launch_advance(int m, int32_t* position, int32_t* step_counter, cudaStream_t s);
 

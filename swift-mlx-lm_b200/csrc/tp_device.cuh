@@ -24,11 +24,16 @@ constexpr int kTpMax = 8;
 
 struct TpLayout {
     int tp, batch, hidden;
+    int rows = 0;  // prompt chunks: token rows one exchange can carry (0: none)
     __host__ __device__ size_t flags_am(int par, int src) const { return 64 + ((size_t)par * kTpMax + src) * 4; }
+    __host__ __device__ size_t flags_rows(int par, int src) const { return 128 + ((size_t)par * kTpMax + src) * 4; }
     // partial sums: 8 bytes per element {fp32 bits, exchange number}
     __host__ __device__ size_t recv_ar(int par, int src, int b) const { return 256 + ((((size_t)par * tp + src) * batch + b) * hidden) * 8; }
     __host__ __device__ size_t recv_am(int par, int src, int b) const { return 256 + (size_t)2 * tp * batch * hidden * 8 + (((size_t)par * tp + src) * batch + b) * 8; }
-    __host__ __device__ size_t total() const { return 256 + (size_t)2 * tp * batch * hidden * 8 + (size_t)2 * tp * batch * 8; }
+    __host__ __device__ size_t decode_total() const { return (256 + (size_t)2 * tp * batch * hidden * 8 + (size_t)2 * tp * batch * 8 + 255) / 256 * 256; }
+    // prompt chunks: bf16 partial rows [rows][hidden] per source, two parities, completion signalled by flags_rows
+    __host__ __device__ size_t recv_rows(int par, int src) const { return decode_total() + ((size_t)par * tp + src) * rows * hidden * 2; }
+    __host__ __device__ size_t total() const { return decode_total() + (size_t)2 * tp * rows * hidden * 2; }
 };
 
 // What a kernel needs to take part in an exchange. tp == 1: unused.

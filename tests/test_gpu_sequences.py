@@ -13,8 +13,10 @@ from test_gpu_model import build_pair, greedy_compare, small_lfm2, small_llama
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("family,batch", [("llama", 17), ("llama", 40), ("lfm2", 24), ("lfm2", 64)])
+@pytest.mark.parametrize("family,batch", [("llama", 16), ("llama", 17), ("llama", 40), ("lfm2", 24), ("lfm2", 32), ("lfm2", 64)])
 def test_wide_batches_greedy_against_oracle(pkg, oracle, family, batch):
+    """16 sequences are the last size of the GEMV kernels, 17 the first of the tensor-core product with one row per
+    sequence, 64 the largest state."""
     cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=batch, max_seq=64)
     store, gm, om = build_pair(pkg, oracle, cfg)
     oracle.set_threads(8)

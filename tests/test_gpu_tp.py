@@ -39,6 +39,15 @@ def test_tp2_lfm2_conv_layers_split_by_channel():
     assert r.stdout.count("TP_OK") == 2, r.stdout[-2000:]
 
 
+@pytest.mark.parametrize("mode", ["prompt", "prompt_lfm2"])
+def test_tp2_chunked_prompt_sums_partial_rows_across_ranks(mode):
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _run(mode, 2, 29623)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_OK") == 2, r.stdout[-2000:]
+
+
 def test_tp4_lfm2_conv_layers_split_by_channel():
     if _gpus() < 4:
         pytest.skip("needs 4 GPUs")
