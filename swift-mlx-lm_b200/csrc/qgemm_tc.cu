@@ -564,6 +564,10 @@ static int ext_plane_cols(int k) { return (k / 64 + 63) / 64 * 64; }
 // [partial sums of a K-split launch][fp16 activations + group sums][one float per token row]
 size_t qgemm_tc_scratch_bytes(int m, int k) { return kTcSplitBytes + ((size_t)m * (k + 3 * ext_plane_cols(k)) * 2 + 255) / 256 * 256 + (size_t)m * 4; }
 
+int qgemm_tc_launch_count(const Q4Raw& w, int m, bool reuse_x) {
+    return (reuse_x ? 0 : 1) + 1 + (tc_pick_split_steps(m, w.n, w.k) > 0 ? 1 : 0);
+}
+
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
                     void* scratch, int* status, cudaStream_t s, bool reuse_x) {
     float* part = static_cast<float*>(scratch);

@@ -767,6 +767,27 @@ int capture_graph(swlm_state* s, bool body_only, cudaGraphExec_t* out) {
 int launches_per_step(const swlm_plan* plan, bool body_only) {
     int n = 0;
     bool has_argmax = false;
+    if (plan->desc.max_batch > kQGemvMaxRows) {
+        // more than 16 sequences: the unfused steps, as enqueue_rows issues them
+        int converted_buf = -1, converted_k = 0;
+        for (const swlm_step& st : plan->steps) {
+            const bool head = st.kind == SWLM_STEP_RESADD_RMSNORM || st.kind == SWLM_STEP_ARGMAX ||
+                              (st.kind == SWLM_STEP_QGEMV && st.out_buf == SWLM_BUF_LOGITS);
+            if (head && body_only) continue;
+            if (st.kind == SWLM_STEP_QGEMV) {
+                auto it = plan->ctx->raw.find(st.weight);
+                if (it == plan->ctx->raw.end()) continue;
+                const bool reuse = converted_buf == st.in_buf && converted_k == it->second.k;
+                n += qgemm_tc_launch_count(it->second, plan->desc.max_batch, reuse);
+                converted_buf = st.in_buf; converted_k = it->second.k;
+                continue;
+            }
+            converted_buf = -1;
+            n += st.kind == SWLM_STEP_ARGMAX ? 2 : 1;
+            has_argmax |= st.kind == SWLM_STEP_ARGMAX;
+        }
+        return n + (has_argmax ? 0 : 1);
+    }
     const size_t end = head_begin_of(plan, body_only);
     for (size_t li = 0; li < end; ++li) {
         const Launch& L = plan->launches[li];
@@ -962,7 +983,7 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
         const bool reuse = converted == x && converted_k == raw.k;
         const int r = launch_qgemm_tc(raw, rows, x, xs, y, ys, wide ? s->wide_xh : s->pf_xh, s->pf_status, stream, reuse);
         converted = x; converted_k = raw.k;
-        s->launches += reuse ? 1 : 2;
+        s->launches += qgemm_tc_launch_count(raw, rows, reuse);
         return r;
     };
     bool advanced = false;

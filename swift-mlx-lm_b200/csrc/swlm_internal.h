@@ -270,6 +270,9 @@ int launch_flash_decode_static(int device, int m, int heads, int kv_heads, int h
 constexpr int kQGemmTcMinRows = 17;   // 17..63 token rows ride in a 64-token tile whose other rows are zero
 int qgemm_tc_init();
 size_t qgemm_tc_scratch_bytes(int m, int k);   // fp16 copy of the activations + one float per token row
+// kernels one call of launch_qgemm_tc issues: the fp16 copy of the rows (unless reused), the product, and the sum over
+// K ranges when a short launch is split
+int qgemm_tc_launch_count(const Q4Raw& w, int m, bool reuse_x);
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
                     void* scratch, int* status, cudaStream_t s, bool reuse_x = false);
 
