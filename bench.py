@@ -370,7 +370,7 @@ def main():
         tok = model.prefill(prompt)   # host tokens in, first generated token out (synchronous)
         t_pf = time.perf_counter() - t_pf
         prefill_info = {"prompt_tokens": int(args.ctx), "seconds": t_pf, "tok_s": args.ctx / t_pf,
-                        "how": "chunked prompt ingestion on 1 GPU" if world == 1 else "token by token (tensor-parallel states)"}
+                        "how": "chunked prompt ingestion on 1 GPU" if world == 1 else "chunked prompt ingestion, partial rows summed across %d GPUs per chunk" % world}
     else:
         rows = pkg.f32_to_bf16(rng.normal(size=(args.ctx, cfg.head_dim)).astype(np.float32))
         kv_local = cfg.kv_heads // world

@@ -55,8 +55,7 @@ struct QGemmTcParams {
     const float* rscale;      // [m]: the inverse of each row's scale
     int x_stride, m;
     int ext_steps;            // 64-column steps of appended group-sum columns (three planes of ceil(k/64/64) steps)
-    __nv_bfloat16* y;         // [m][y_stride]
-    int y_stride;
+    TcSegments out;           // weight rows [end[q-1], end[q]) go to out.y[q][token][row - end[q-1]]
     int* status;              // set non-zero when a bounded wait expired
     // launches of at most 64 token rows over few weight rows: K is cut into gridDim.z ranges of `split_steps` groups
     // (a multiple of 8) so that more SMs take part; every range writes its fp32 sums to part[z][m][n] and a second
@@ -121,6 +120,13 @@ __device__ __forceinline__ void umma_f16_ta(unsigned d_tmem, unsigned a_tmem, un
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// One result, rounded once to bf16, to the output its weight row belongs to.
+__device__ __forceinline__ void tc_store(const TcSegments& o, int token, int row, float val) {
+    const int q = row < o.end[0] ? 0 : row < o.end[1] ? 1 : 2;
+    const int first = q == 0 ? 0 : o.end[q - 1];
+    o.y[q][(size_t)token * o.stride[q] + (row - first)] = __float2bfloat16_rn(val);
 }
 
 // F16SB: scale and zero are fp16 (tensors uploaded as STAF blocks) instead of bf16 (MLX tensors).
@@ -381,7 +387,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
                     if (tkn < p.m) {
                         const float val = __uint_as_float(v[i]) * __ldg(p.rscale + tkn);
                         if (gridDim.z > 1) p.part[((size_t)blockIdx.z * p.m + tkn) * p.n + erow] = val;
-                        else p.y[(size_t)tkn * p.y_stride + erow] = __float2bfloat16_rn(val);
+                        else tc_store(p.out, tkn, erow, val);
                     }
                 }
             }
@@ -393,7 +399,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
 }
 
 // Y[t][n] = bf16(sum over the K ranges, in order) for a launch whose K was cut in `splits` ranges.
-__global__ void __launch_bounds__(256) tc_sum_splits_kernel(const float* part, int splits, int m, int n, __nv_bfloat16* y, int y_stride) {
+__global__ void __launch_bounds__(256) tc_sum_splits_kernel(const float* part, int splits, int m, int n, const TcSegments out) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t total = (size_t)m * n;
@@ -401,7 +407,7 @@ __global__ void __launch_bounds__(256) tc_sum_splits_kernel(const float* part, i
         float acc = 0.f;
         for (int z = 0; z < splits; ++z) acc += __ldcg(part + (size_t)z * total + i);
         const int t = (int)(i / n), r = (int)(i - (size_t)t * n);
-        y[(size_t)t * y_stride + r] = __float2bfloat16_rn(acc);
+        tc_store(out, t, r, acc);
     }
 }
 
@@ -519,7 +525,7 @@ int tc_launch_one(const QGemmTcParams& p, bool f16, cudaStream_t s) {
     if (splits > 1) {
         const size_t total = (size_t)p.m * p.n;
         const cudaError_t e2 = launch_k(tc_sum_splits_kernel, dim3((unsigned)std::min<size_t>(296, (total + 1023) / 1024)), dim3(256), 0, s,
-                                        (const float*)p.part, splits, p.m, p.n, p.y, p.y_stride);
+                                        (const float*)p.part, splits, p.m, p.n, p.out);
         if (e2 != cudaSuccess) return cuda_fail(e2, "qgemm_tc split sum launch");
     }
     return SWLM_OK;
@@ -569,7 +575,7 @@ int qgemm_tc_launch_count(const Q4Raw& w, int m, bool reuse_x) {
 }
 
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
-                    void* scratch, int* status, cudaStream_t s, bool reuse_x) {
+                    void* scratch, int* status, cudaStream_t s, bool reuse_x, const TcSegments* segments) {
     float* part = static_cast<float*>(scratch);
     __half* xh = scratch ? reinterpret_cast<__half*>(static_cast<unsigned char*>(scratch) + kTcSplitBytes) : nullptr;
     const int g_pad = ext_plane_cols(w.k), xh_stride = w.k + 3 * g_pad;
@@ -586,7 +592,14 @@ int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride,
     }
     QGemmTcParams p{};
     p.w = w.w; p.scales = w.scales; p.biases = w.biases; p.n = w.n; p.k = w.k;
-    p.x = xh; p.rscale = rscale; p.x_stride = xh_stride; p.m = m; p.y = y; p.y_stride = y_stride; p.status = status;
+    p.x = xh; p.rscale = rscale; p.x_stride = xh_stride; p.m = m; p.status = status;
+    if (segments) {
+        p.out = *segments;
+        if (p.out.count < 1 || p.out.count > 3 || p.out.end[p.out.count - 1] != w.n) { set_error("qgemm (tcgen05): output segments do not cover the %d weight rows", w.n); return SWLM_ERR_INVALID; }
+        for (int q = p.out.count; q < 3; ++q) p.out.end[q] = p.out.end[p.out.count - 1];   // never selected
+    } else {
+        p.out.count = 1; p.out.y[0] = y; p.out.stride[0] = y_stride; p.out.end[0] = p.out.end[1] = p.out.end[2] = w.n;
+    }
     p.ext_steps = 3 * g_pad / 64;
     p.part = part;
     p.split_steps = tc_pick_split_steps(m, w.n, w.k);

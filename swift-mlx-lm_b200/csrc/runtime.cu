@@ -48,6 +48,7 @@ struct swlm_ctx {
     cudaStream_t stream = nullptr;
     std::map<std::string, Q4Raw> raw;
     std::map<std::string, Q4Tiled> tiled;  // plain and fused tensors, keyed by name ("a|b|c" for fused)
+    std::map<std::string, Q4Raw> raw_cat;  // source-layout tensors with the rows of several raw tensors one after the other ("a|b|c")
     std::map<std::string, DenseTensor> dense;
     int64_t bytes = 0;
     float* op_partial = nullptr; size_t op_partial_floats = 0;
@@ -182,6 +183,19 @@ int add_q4_raw(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* w,
             if (uses) { cudaFree(it->second.tiles); cudaFree(it->second.sb); it = ctx->tiled.erase(it); }
             else ++it;
         }
+        for (auto it = ctx->raw_cat.begin(); it != ctx->raw_cat.end();) {
+            bool uses = false;
+            size_t start = 0;
+            const std::string& key = it->first;
+            while (start <= key.size()) {
+                size_t end = key.find('|', start);
+                if (end == std::string::npos) end = key.size();
+                uses |= key.compare(start, end - start, needle) == 0;
+                start = end + 1;
+            }
+            if (uses) { cudaFree(it->second.w); cudaFree(it->second.scales); cudaFree(it->second.biases); it = ctx->raw_cat.erase(it); }
+            else ++it;
+        }
     }
     Q4Raw r;
     r.n = sl.rows * sl.parts; r.k = sl.cols; r.sb_f16 = f16; r.shard_kind = shard_kind;
@@ -248,6 +262,12 @@ struct swlm_plan {
     int attn_splits = 1;
     size_t attn_scratch = 0, qgemv_partial = 0, qgemv_counters = 0;
     int final_res = 0;  // physical residual buffer that holds the residual stream after a step
+    // Row-wise execution (prompt chunks, more than 16 sequences): consecutive products of one input run as one product
+    // over their concatenated rows. Per step: how many steps the product starting there covers (0: covered by an
+    // earlier one) and the tensor it multiplies.
+    struct RowsGroup { int count = 1; const Q4Raw* raw = nullptr; };
+    std::vector<RowsGroup> rows_groups;
+    bool rows_groups_ready = false;
     int users = 0;
     bool destroy_requested = false;
 };
@@ -775,11 +795,19 @@ int launches_per_step(const swlm_plan* plan, bool body_only) {
                               (st.kind == SWLM_STEP_QGEMV && st.out_buf == SWLM_BUF_LOGITS);
             if (head && body_only) continue;
             if (st.kind == SWLM_STEP_QGEMV) {
-                auto it = plan->ctx->raw.find(st.weight);
-                if (it == plan->ctx->raw.end()) continue;
-                const bool reuse = converted_buf == st.in_buf && converted_k == it->second.k;
-                n += qgemm_tc_launch_count(it->second, plan->desc.max_batch, reuse);
-                converted_buf = st.in_buf; converted_k = it->second.k;
+                const size_t si = (size_t)(&st - plan->steps.data());
+                const Q4Raw* raw = nullptr;
+                if (plan->rows_groups_ready) {
+                    if (plan->rows_groups[si].count == 0) continue;
+                    raw = plan->rows_groups[si].raw;
+                } else {
+                    auto it = plan->ctx->raw.find(st.weight);
+                    if (it != plan->ctx->raw.end()) raw = &it->second;
+                }
+                if (!raw) continue;
+                const bool reuse = converted_buf == st.in_buf && converted_k == raw->k;
+                n += qgemm_tc_launch_count(*raw, plan->desc.max_batch, reuse);
+                converted_buf = st.in_buf; converted_k = raw->k;
                 continue;
             }
             converted_buf = -1;
@@ -896,6 +924,76 @@ int check_position_room(swlm_state* s, int steps) {
 constexpr int kPrefillMinChunk = 32;
 
 // can the plan's steps run row-wise (enqueue_rows)?
+// The rows of several source-layout tensors one after the other (q | k | v, gate | up), built once per set of names.
+int get_raw_cat(swlm_ctx* ctx, const std::vector<std::string>& names, const Q4Raw** out) {
+    std::string key = names[0];
+    for (size_t i = 1; i < names.size(); ++i) key += "|" + names[i];
+    auto hit = ctx->raw_cat.find(key);
+    if (hit != ctx->raw_cat.end()) { *out = &hit->second; return SWLM_OK; }
+    Q4Raw cat;
+    const Q4Raw& first = ctx->raw.at(names[0]);
+    cat.k = first.k; cat.sb_f16 = first.sb_f16; cat.shard_kind = first.shard_kind;
+    for (const std::string& nm : names) cat.n += ctx->raw.at(nm).n;
+    const size_t wpr = (size_t)cat.k / 8, gpr = (size_t)cat.k / 64;
+    int rc;
+    if ((rc = dev_alloc(&cat.w, (size_t)cat.n * wpr, ctx))) return rc;
+    if ((rc = dev_alloc(&cat.scales, (size_t)cat.n * gpr, ctx))) return rc;
+    if ((rc = dev_alloc(&cat.biases, (size_t)cat.n * gpr, ctx))) return rc;
+    size_t row = 0;
+    for (const std::string& nm : names) {
+        const Q4Raw& r = ctx->raw.at(nm);
+        SWLM_CUDA(cudaMemcpy(cat.w + row * wpr, r.w, (size_t)r.n * wpr * 4, cudaMemcpyDeviceToDevice));
+        SWLM_CUDA(cudaMemcpy(cat.scales + row * gpr, r.scales, (size_t)r.n * gpr * 2, cudaMemcpyDeviceToDevice));
+        SWLM_CUDA(cudaMemcpy(cat.biases + row * gpr, r.biases, (size_t)r.n * gpr * 2, cudaMemcpyDeviceToDevice));
+        row += r.n;
+    }
+    ctx->raw_cat[key] = cat;
+    *out = &ctx->raw_cat[key];
+    return SWLM_OK;
+}
+
+// Decide which products of the unfused step list run together (allocates: never call while a stream is capturing).
+// SWLM_ROWS_FUSE=0 keeps one product per step.
+int ensure_rows_groups(swlm_plan* plan) {
+    if (plan->rows_groups_ready) return SWLM_OK;
+    static const bool fuse = [] { const char* v = getenv("SWLM_ROWS_FUSE"); return !(v && v[0] == '0'); }();
+    swlm_ctx* ctx = plan->ctx;
+    const std::vector<swlm_step>& st = plan->steps;
+    plan->rows_groups.assign(st.size(), swlm_plan::RowsGroup{});
+    for (size_t i = 0; i < st.size(); ++i) {
+        if (plan->rows_groups[i].count == 0 || st[i].kind != SWLM_STEP_QGEMV) continue;
+        auto it = ctx->raw.find(st[i].weight);
+        if (it == ctx->raw.end()) { set_error("tensor '%s' not in the weight store", st[i].weight); return SWLM_ERR_NOT_FOUND; }
+        const Q4Raw& r0 = it->second;
+        plan->rows_groups[i].raw = &r0;
+        const bool partial = ctx->tp_size > 1 && r0.shard_kind == SWLM_SHARD_ROW;   // its rows go through an exchange
+        if (!fuse || st[i].out_buf == SWLM_BUF_LOGITS || partial) continue;
+        std::vector<std::string> names{st[i].weight};
+        size_t j = i + 1;
+        while (j < st.size() && names.size() < 3 && st[j].kind == SWLM_STEP_QGEMV && st[j].in_buf == st[i].in_buf &&
+               st[j].out_buf != st[i].in_buf && st[j].out_buf != SWLM_BUF_LOGITS) {
+            auto jt = ctx->raw.find(st[j].weight);
+            if (jt == ctx->raw.end()) break;
+            const Q4Raw& rj = jt->second;
+            if (rj.k != r0.k || rj.sb_f16 != r0.sb_f16 || (ctx->tp_size > 1 && rj.shard_kind == SWLM_SHARD_ROW)) break;
+            bool clash = false;
+            for (size_t q = i; q < j; ++q) clash |= st[q].out_buf == st[j].out_buf;
+            if (clash) break;
+            names.push_back(st[j].weight);
+            ++j;
+        }
+        if (names.size() < 2) continue;
+        const Q4Raw* cat = nullptr;
+        int rc = get_raw_cat(ctx, names, &cat);
+        if (rc) return rc;
+        plan->rows_groups[i].count = (int)names.size();
+        plan->rows_groups[i].raw = cat;
+        for (size_t q = i + 1; q < j; ++q) plan->rows_groups[q].count = 0;
+    }
+    plan->rows_groups_ready = true;
+    return SWLM_OK;
+}
+
 // Prompt chunks of one sequence under tensor parallelism: up to this many token rows per exchange.
 constexpr int kTpChunkRows = 256;
 
@@ -940,6 +1038,7 @@ int check_pf_status(swlm_state* s) {
 int prefill_workspace(swlm_state* s, int rows) {
     int rc;
     if ((rc = ensure_pf_status(s))) return rc;
+    if ((rc = ensure_rows_groups(s->plan))) return rc;
     if (rows <= s->pf_rows) return SWLM_OK;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) { cudaFree(s->pf_buf[i]); s->pf_buf[i] = nullptr; }
@@ -979,16 +1078,20 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
     int rc = SWLM_OK;
     const __nv_bfloat16* converted = nullptr;  // rows whose fp16 copy the product scratch still holds
     int converted_k = 0;
-    auto product = [&](const Q4Raw& raw, int rows, const __nv_bfloat16* x, int xs, __nv_bfloat16* y, int ys) {
+    auto product = [&](const Q4Raw& raw, int rows, const __nv_bfloat16* x, int xs, __nv_bfloat16* y, int ys, const TcSegments* seg = nullptr) {
         const bool reuse = converted == x && converted_k == raw.k;
-        const int r = launch_qgemm_tc(raw, rows, x, xs, y, ys, wide ? s->wide_xh : s->pf_xh, s->pf_status, stream, reuse);
+        const int r = launch_qgemm_tc(raw, rows, x, xs, y, ys, wide ? s->wide_xh : s->pf_xh, s->pf_status, stream, reuse, seg);
         converted = x; converted_k = raw.k;
         s->launches += qgemm_tc_launch_count(raw, rows, reuse);
         return r;
     };
     bool advanced = false;
     const int tp = ctx->tp_size;   // > 1 only for prompt chunks: heads, conv channels and the products' rows are this rank's share
-    for (const swlm_step& st : plan->steps) {
+    if (!plan->rows_groups_ready) { set_error("row-wise execution was not prepared for this plan"); return SWLM_ERR_STATE; }
+    for (size_t si = 0; si < plan->steps.size(); ++si) {
+        const swlm_step& st = plan->steps[si];
+        const swlm_plan::RowsGroup& grp = plan->rows_groups[si];
+        if (grp.count == 0) continue;   // ran with an earlier product
         const bool is_product = st.kind == SWLM_STEP_QGEMV;
         switch (st.kind) {
         case SWLM_STEP_EMBED:
@@ -1015,7 +1118,20 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
             break;
         }
         case SWLM_STEP_QGEMV: {
-            const Q4Raw& raw = ctx->raw[st.weight];
+            const Q4Raw& raw = *grp.raw;
+            if (grp.count > 1) {
+                // q | k | v or gate | up: one product over the concatenated rows, each part to its own buffer
+                TcSegments seg;
+                seg.count = grp.count;
+                int end = 0;
+                for (int q = 0; q < grp.count; ++q) {
+                    const swlm_step& sq = plan->steps[si + q];
+                    end += ctx->raw.at(sq.weight).n;
+                    seg.end[q] = end; seg.y[q] = pf[sq.out_buf]; seg.stride[q] = wd[sq.out_buf];
+                }
+                rc = product(raw, c, pf[st.in_buf], wd[st.in_buf], nullptr, 0, &seg);
+                break;
+            }
             if (st.out_buf == SWLM_BUF_LOGITS) {
                 if (wide ? body_only : head_row < 0) break;
                 // the logits buffer belongs to the state (one row per sequence), also for a chunk's last token
@@ -1160,6 +1276,7 @@ void swlm_ctx_destroy(swlm_ctx* ctx) {
     cudaSetDevice(ctx->device);
     for (auto& kv : ctx->raw) { cudaFree(kv.second.w); cudaFree(kv.second.scales); cudaFree(kv.second.biases); }
     for (auto& kv : ctx->tiled) { cudaFree(kv.second.tiles); cudaFree(kv.second.sb); }
+    for (auto& kv : ctx->raw_cat) { cudaFree(kv.second.w); cudaFree(kv.second.scales); cudaFree(kv.second.biases); }
     for (auto& kv : ctx->dense) cudaFree(kv.second.data);
     cudaFree(ctx->op_partial);
     cudaFree(ctx->tc_status);
@@ -1257,6 +1374,8 @@ int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const sw
     plan->desc = *desc;
     plan->steps.assign(steps, steps + n_steps);
     rc = compile_plan(plan);
+    // more than 16 sequences run row-wise inside a CUDA graph: build the concatenated tensors now, not while capturing
+    if (!rc && desc->max_batch > kQGemvMaxRows) rc = ensure_rows_groups(plan);
     if (rc) { swlm_plan_destroy(plan); return rc; }
     plan->attn_scratch = plan_attn_scratch(plan);
     *out = plan;
@@ -1715,6 +1834,7 @@ int swlm_run_step(swlm_state* s, const swlm_step* step, const int32_t* token_in,
     tmp.desc = s->plan->desc;
     tmp.steps.assign(step, step + 1);
     rc = compile_plan(&tmp);
+    if (!rc && m > kQGemvMaxRows) rc = ensure_rows_groups(&tmp);
     if (rc) return rc;
     // a step the state's own plan does not contain may need more scratch than the state holds
     rc = grow_scratch(s, plan_attn_scratch(&tmp), tmp.qgemv_partial, tmp.qgemv_counters);

@@ -273,8 +273,16 @@ size_t qgemm_tc_scratch_bytes(int m, int k);   // fp16 copy of the activations +
 // kernels one call of launch_qgemm_tc issues: the fp16 copy of the rows (unless reused), the product, and the sum over
 // K ranges when a short launch is split
 int qgemm_tc_launch_count(const Q4Raw& w, int m, bool reuse_x);
+// Where the rows of a product over concatenated weights go: rows [end[q-1], end[q]) to y[q] (up to three outputs,
+// e.g. q | k | v); null = all rows to `y`.
+struct TcSegments {
+    int count = 1;
+    int end[3] = {0, 0, 0};
+    __nv_bfloat16* y[3] = {nullptr, nullptr, nullptr};
+    int stride[3] = {0, 0, 0};
+};
 int launch_qgemm_tc(const Q4Raw& w, int m, const __nv_bfloat16* x, int x_stride, __nv_bfloat16* y, int y_stride,
-                    void* scratch, int* status, cudaStream_t s, bool reuse_x = false);
+                    void* scratch, int* status, cudaStream_t s, bool reuse_x = false, const TcSegments* segments = nullptr);
 
 // Tensor-parallel sum of `rows` bf16 partial rows (prompt chunks): every rank copies its partials into every rank's
 // exchange buffer and raises a flag carrying `epoch` (the host counts exchanges); then each rank waits (bounded) for
