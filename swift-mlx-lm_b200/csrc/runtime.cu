@@ -995,7 +995,7 @@ int ensure_rows_groups(swlm_plan* plan) {
 }
 
 // Prompt chunks of one sequence under tensor parallelism: up to this many token rows per exchange.
-constexpr int kTpChunkRows = 256;
+constexpr int kTpChunkRows = 1024;
 
 bool rows_capable(const swlm_plan* plan, bool allow_tp = false) {
     if ((plan->ctx->tp_size != 1 && !allow_tp) || plan->desc.head_dim > 128) return false;
@@ -1374,8 +1374,9 @@ int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const sw
     plan->desc = *desc;
     plan->steps.assign(steps, steps + n_steps);
     rc = compile_plan(plan);
-    // more than 16 sequences run row-wise inside a CUDA graph: build the concatenated tensors now, not while capturing
-    if (!rc && desc->max_batch > kQGemvMaxRows) rc = ensure_rows_groups(plan);
+    // Row-wise execution (prompt chunks; more than 16 sequences, inside a CUDA graph): build the concatenated tensors
+    // now, not inside the first prompt's latency and not while a stream is capturing.
+    if (!rc && (desc->max_batch > kQGemvMaxRows || rows_capable(plan, true))) rc = ensure_rows_groups(plan);
     if (rc) { swlm_plan_destroy(plan); return rc; }
     plan->attn_scratch = plan_attn_scratch(plan);
     *out = plan;
