@@ -10,6 +10,7 @@ and loading fails loudly when the CUDA library has not been built.
 from .lib import Library, SwlmError, load_library  # noqa: F401
 from .formats import (  # noqa: F401
     AffineQ4Group64Format,
+    AffineQ4Group128Format,
     KVCacheSpecification,
     bf16_to_f32,
     f32_to_bf16,

@@ -212,7 +212,9 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
         if (lane == 0) {
             for (int kt = 0; kt < steps_total; ++kt) {
                 if (!mbar_wait(&ready_bar[kt % SA], (unsigned)((kt / SA) & 1)) || !mbar_wait(&full_bar[kt % SB], (unsigned)((kt / SB) & 1))) {
-                    atomicExch(p.status, 2); failed = 1; break;
+                    // giving up: let done_bar complete behind the MMAs already issued, so that tensor memory is not
+                    // freed under them
+                    atomicExch(p.status, 2); failed = 1; umma_commit(&done_bar); break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned a_addr = tmem_d + kACol0 + (unsigned)(kt % SA) * 32u, b_addr = smem_u32(b_ring + (kt % SB) * STAGE_BYTES);
@@ -363,6 +365,7 @@ __global__ void __launch_bounds__(kTcAllThreads) qgemm_tc_kernel(const QGemmTcPa
     // the token columns
     bool ok = !failed && warp < kTcThreads / 32;
     if (ok && !mbar_wait(&done_bar, 0u)) { atomicExch(p.status, 1); ok = false; }
+    if (failed && tid == 0) mbar_wait(&done_bar, 0u);   // (bounded) the MMAs issued before the failure have drained
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
         const int erow = row0 + (warp & 3) * 32 + lane;

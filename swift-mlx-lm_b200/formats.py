@@ -19,11 +19,27 @@ class AffineQ4Group64Format:
     weights_per_block = 64
     bytes_per_block = 36  # fp16 scale | fp16 zero | 32 payload bytes
     is_quantized = True
-    scheme_identifier = "q4Group64ScaleZero"
+    scheme_identifier = "q4Group64ScaleF16"   # QuantizationSchemeIdentifier, STAF/STAFFormat.swift (0x40)
 
     @staticmethod
     def bytes_per_weight() -> float:
         return 36.0 / 64.0
+
+
+class AffineQ4Group128Format:
+    """The same arithmetic with one scale / zero pair per 128 weights; STAF block = 68 bytes
+    (STAF/QuantizationFormat.swift:539-604)."""
+
+    bits = 4
+    group_size = 128
+    weights_per_block = 128
+    bytes_per_block = 68  # fp16 scale | fp16 zero | 64 payload bytes
+    is_quantized = True
+    scheme_identifier = "q4Group128ScaleF16"  # 0x41
+
+    @staticmethod
+    def bytes_per_weight() -> float:
+        return 68.0 / 128.0
 
 
 def f32_to_bf16(x: np.ndarray) -> np.ndarray:
