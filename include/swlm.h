@@ -111,8 +111,9 @@ int swlm_state_set_stream(swlm_state* state, void* cuda_stream);
 /* Prompt ingestion (swlm_prefill) runs the prompt in chunks of up to `tokens` tokens with one activation row per
  * token and the products on the tensor cores, as the reference's sequence prefill does
  * (Execution/MetalPrefillExecutor.swift); the last prompt token always takes the decode path. 0 = one token at a
- * time through the decode graph. Default 2048. Chunking applies to single-sequence, single-GPU states; others
- * ingest token by token. */
+ * time through the decode graph. Default 2048. Chunking applies to single-sequence states (under tensor parallelism
+ * in chunks of at most 1024 tokens, whose partial rows are summed across the ranks) and, on one GPU, to the sequences
+ * of a batch one after the other; other cases ingest token by token through the decode graph. */
 int swlm_state_set_prefill_chunk(swlm_state* state, int tokens);
 /* resetState() — MetalInferenceModel.swift:1911. */
 int swlm_state_reset(swlm_state* state);

@@ -1655,6 +1655,15 @@ int swlm_prefill(swlm_state* s, const int32_t* tokens, int n, int32_t* first_tok
     int rc = ensure_device(s->plan->ctx);
     if (!rc) rc = check_position_room(s, n);
     if (rc) return rc;
+    // several sequences with prompts long enough for chunks: one sequence after the other through the row-wise path
+    if (m > 1 && n >= kPrefillMinChunk && s->prefill_chunk >= kPrefillMinChunk && rows_capable(s->plan)) {
+        for (int b = 0; b < m; ++b)
+            if ((rc = swlm_prefill_seq(s, b, tokens + (size_t)b * n, n, first_token + b))) {
+                for (int q = 0; q < m; ++q) first_token[q] = -1;
+                return rc;
+            }
+        return SWLM_OK;
+    }
     // token-major copy of the prompt so that step t reads m consecutive ids
     std::vector<int32_t> tm((size_t)n * m);
     for (int b = 0; b < m; ++b)

@@ -183,3 +183,20 @@ def test_group128_weights_model_against_oracle(pkg, oracle, family, batch):
     mism = greedy_compare(pkg, gm, om, cfg, prompt_len=70 if batch == 1 else 9, steps=32)
     assert len(mism) <= 2, mism
     gm.close(); store.close()
+
+
+@pytest.mark.parametrize("family,batch", [("llama", 3), ("lfm2", 20)])
+def test_batch_prompt_goes_through_the_chunked_path(pkg, oracle, family, batch):
+    """swlm_prefill with several sequences and a prompt long enough for chunks: every sequence is ingested through the
+    row-wise path in turn (far fewer launches than one decode step per token), then all decode together."""
+    cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=batch, max_seq=160)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    oracle.set_threads(8)
+    gm.set_prefill_chunk(64)
+    before = gm.launches
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=100, steps=8)
+    assert len(mism) <= max(2, batch // 8), mism
+    # token by token this would be 108 decode steps; the chunks need far fewer launches
+    assert gm.launches - before < 60 * gm.launches_per_step
+    assert list(gm.positions) == [108] * batch
+    gm.close(); store.close()
