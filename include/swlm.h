@@ -84,6 +84,9 @@ int swlm_weights_add_q4g128_staf(swlm_ctx* ctx, const char* name, int n, int k, 
  * rows/cols describe a 2-D view when shard_kind != replicate (cols = count / rows). */
 int swlm_weights_add_dense_bf16(swlm_ctx* ctx, const char* name, int64_t rows, int64_t cols,
                                 const uint16_t* data, int shard_kind);
+/* Dense fp32 tensor, replicated: the recurrent layers' norm weight and A_log, which the reference keeps in fp32
+ * whatever the bundle's dtype (STAF/STAFConversionPlanner.swift:117-127). */
+int swlm_weights_add_dense_f32(swlm_ctx* ctx, const char* name, int64_t count, const float* data);
 /* Total bytes of weights resident on the device for this context. */
 int64_t swlm_weights_bytes(const swlm_ctx* ctx);
 
@@ -151,6 +154,8 @@ int swlm_write_buffer(swlm_state* state, int buf, const uint16_t* src, int count
 int swlm_read_kv(swlm_state* state, int which, int layer, int b, int head, int count, uint16_t* dst);
 int swlm_write_kv(swlm_state* state, int which, int layer, int b, int head, int count, const uint16_t* src);
 int swlm_read_conv(swlm_state* state, int layer, int b, uint16_t* dst);
+/* fp32 recurrent state [ssm_heads][ssm_key_dim][ssm_value_dim] of one recurrent layer / sequence. */
+int swlm_read_ssm_state(swlm_state* state, int layer, int b, float* dst);
 /* Sets the position of every sequence. */
 int swlm_set_position(swlm_state* state, int position);
 

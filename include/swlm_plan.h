@@ -77,7 +77,18 @@ enum {
     /* geglu — the gated activation with GELU (tanh approximation) instead of SiLU
        (Generator/MetalSourceGenerator+NormAndElementwise.swift:176-208, GatedActivation.geluTanh):
        out = bf16(0.5 g (1 + tanh(0.7978845608 (g + 0.044715 g^3))) * up), g = in_buf, up = in2_buf. */
-    SWLM_STEP_GEGLU = 11
+    SWLM_STEP_GEGLU = 11,
+    /* ssm_recurrence (gated delta rule of the DeltaNet / Qwen3.5 linear-attention layers) —
+       Generator/MetalSourceGenerator+ConvAndState.swift:282-500, Primitives/SSMRecurrenceFragment.swift.
+       in_buf = projected q|k|v (2*groups*key_dim + heads*value_dim values), in2_buf = z (heads*value_dim),
+       in3_buf = beta (heads), in4_buf = alpha (heads), out_buf = heads*value_dim values.
+       Per channel: causal conv over conv_kernel taps (state [conv_kernel][conv_dim], weight dtype) + SiLU; per head:
+       decay = exp(-exp(A_log) * softplus(alpha + dt_bias)), beta = sigmoid(beta), q and k L2-normalised (q also scaled
+       by key_dim^-1/2), S = decay * S + k (x) beta (v - S^T k), out = S^T q (state S [key_dim][value_dim] fp32); then
+       RMS norm over value_dim with `weight2` and the gate z * sigmoid(z).
+       weight = conv taps [conv_dim][conv_kernel] bf16, weight2 = norm weight [value_dim] fp32, weight3 = dt_bias
+       [heads] bf16, weight4 = A_log [heads] fp32 (the two fp32 tensors: swlm_weights_add_dense_f32). */
+    SWLM_STEP_SSM_RECURRENCE = 12
 };
 
 typedef struct swlm_step {
@@ -103,6 +114,13 @@ typedef struct swlm_step {
     /* attention: sliding window. 0 = attend everything; W > 0 = the current token and the W - 1 before it
        (windowLeft, Generator/MetalSourceGenerator+Attention.swift:851-853; decode and prompt chunks alike). */
     int32_t window_left;
+    /* SWLM_STEP_SSM_RECURRENCE only */
+    int32_t in4_buf;
+    int32_t groups;      /* key groups; heads / groups value heads share one q and k */
+    int32_t key_dim;
+    int32_t value_dim;
+    char    weight3[SWLM_NAME_MAX];
+    char    weight4[SWLM_NAME_MAX];
 } swlm_step;
 
 /* Sizes of the runtime buffer set; mirrors the inputs of
@@ -120,6 +138,15 @@ typedef struct swlm_buffers_desc {
     int32_t conv_layers;  /* number of short-conv layers (state slabs) */
     int32_t conv_dim;
     int32_t conv_kernel;
+    /* recurrent layers (SWLM_STEP_SSM_RECURRENCE): per layer and sequence a conv state [ssm_conv_kernel][conv_dim]
+       (conv_dim = 2*ssm_groups*ssm_key_dim + ssm_heads*ssm_value_dim) and an fp32 state [ssm_heads][ssm_key_dim][ssm_value_dim].
+       All zero when the plan has no such layer. */
+    int32_t ssm_layers;
+    int32_t ssm_heads;
+    int32_t ssm_groups;
+    int32_t ssm_key_dim;
+    int32_t ssm_value_dim;
+    int32_t ssm_conv_kernel;
 } swlm_buffers_desc;
 
 #ifdef __cplusplus

@@ -167,6 +167,9 @@ struct orc_model {
     int width[SWLM_BUF_COUNT]{};
     std::vector<uint16_t> kcache, vcache;  // [layer][b][kv_head][max_seq][head_dim]
     std::vector<uint16_t> conv;            // [layer][b][conv_kernel][conv_dim]
+    std::map<std::string, std::vector<float>> densef;   // fp32 tensors (recurrent layers' norm weight, A_log)
+    std::vector<uint16_t> ssm_conv;        // [layer][b][ssm_conv_kernel][ssm conv dim]
+    std::vector<float> ssm_state;          // [layer][b][heads][key_dim][value_dim]
     std::vector<int32_t> token_in, token_out;
     int position = 0;
     std::string error;
@@ -378,6 +381,81 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
         }
         return 0;
     }
+    case SWLM_STEP_SSM_RECURRENCE: {
+        // Generator/MetalSourceGenerator+ConvAndState.swift:347-497 (ssm_recurrence, bf16 buffers and weights),
+        // helpers :224-227. Scalar restatement in the kernel's own order of operations.
+        auto cw = m->dense.find(st.weight);
+        auto nw = m->densef.find(st.weight2);
+        auto db = m->dense.find(st.weight3);
+        auto al = m->densef.find(st.weight4);
+        if (cw == m->dense.end() || nw == m->densef.end() || db == m->dense.end() || al == m->densef.end()) {
+            m->error = std::string("missing tensors of ") + st.weight; return -3;
+        }
+        const int H = st.heads, G = st.groups > 0 ? st.groups : 1, dk = st.key_dim, dv = st.value_dim, K = st.conv_kernel;
+        const int hpg = H / G > 0 ? H / G : 1, kgd = G * dk, conv_dim = 2 * kgd + H * dv;
+        auto sigmoid = [](float x) { return 1.0f / (1.0f + std::exp(-x)); };
+        auto softplus = [](float x) { return std::fmax(x, 0.0f) + std::log(1.0f + std::exp(-std::fabs(x))); };
+        for (int b = 0; b < batch; ++b) {
+            const uint16_t* qkv = row(m, st.in_buf, b);
+            const uint16_t* zz = row(m, st.in2_buf, b);
+            const uint16_t* pbeta = row(m, st.in3_buf, b);
+            const uint16_t* palpha = row(m, st.in4_buf, b);
+            uint16_t* out = row(m, st.out_buf, b);
+            uint16_t* cstate = m->ssm_conv.data() + ((size_t)st.layer * d.max_batch + b) * (size_t)K * conv_dim;
+            float* rstate = m->ssm_state.data() + ((size_t)st.layer * d.max_batch + b) * (size_t)H * dk * dv;
+            // phase 1: conv shift + SiLU for every channel (:392-414)
+            std::vector<float> act(conv_dim);
+            for (int ch = 0; ch < conv_dim; ++ch) {
+                float sum = 0.0f;
+                for (int k = 0; k + 1 < K; ++k) {
+                    float val = bf16_to_f32(cstate[(size_t)(k + 1) * conv_dim + ch]);
+                    cstate[(size_t)k * conv_dim + ch] = f32_to_bf16(val);
+                    sum += val * bf16_to_f32(cw->second[(size_t)ch * K + k]);
+                }
+                float nv = bf16_to_f32(qkv[ch]);
+                cstate[(size_t)(K - 1) * conv_dim + ch] = f32_to_bf16(nv);
+                sum += nv * bf16_to_f32(cw->second[(size_t)ch * K + (K - 1)]);
+                act[ch] = sum * sigmoid(sum);
+            }
+            // phases 2 and 3 per head (:418-497)
+            for (int h = 0; h < H; ++h) {
+                const int g = h / hpg;
+                const float* Q = act.data() + (size_t)g * dk;
+                const float* Kk = act.data() + kgd + (size_t)g * dk;
+                const float* V = act.data() + 2 * kgd + (size_t)h * dv;
+                float decay = std::exp(-std::exp(al->second[h]) * softplus(bf16_to_f32(palpha[h]) + bf16_to_f32(db->second[h])));
+                float beta = sigmoid(bf16_to_f32(pbeta[h]));
+                float* S = rstate + (size_t)h * dk * dv;
+                float qn = 0.0f, kn = 0.0f, kq = 0.0f;
+                for (int j = 0; j < dk; ++j) { qn += Q[j] * Q[j]; kn += Kk[j] * Kk[j]; kq += Q[j] * Kk[j]; }
+                float q_inv = (1.0f / std::sqrt(qn + 1e-6f)) * (1.0f / std::sqrt((float)dk));
+                float k_inv = 1.0f / std::sqrt(kn + 1e-6f);
+                std::vector<float> stored(dv);
+                float norm_sq = 0.0f;
+                for (int dd = 0; dd < dv; ++dd) {
+                    float kvmem = 0.0f, sq = 0.0f;
+                    for (int j = 0; j < dk; ++j) {
+                        float s = S[(size_t)j * dv + dd] * decay;
+                        kvmem += s * Kk[j];
+                        sq += s * Q[j];
+                    }
+                    float delta = beta * (V[dd] - kvmem * k_inv);
+                    float kid = k_inv * delta;
+                    float dot = (sq + kid * kq) * q_inv;
+                    for (int j = 0; j < dk; ++j) S[(size_t)j * dv + dd] = S[(size_t)j * dv + dd] * decay + Kk[j] * kid;
+                    stored[dd] = round_bf16(dot);
+                    norm_sq += dot * dot;
+                }
+                float rms = 1.0f / std::sqrt(norm_sq / (float)dv + 1e-6f);
+                for (int dd = 0; dd < dv; ++dd) {
+                    float normed = stored[dd] * rms * nw->second[dd];
+                    float z = bf16_to_f32(zz[(size_t)h * dv + dd]);
+                    out[(size_t)h * dv + dd] = f32_to_bf16(normed * z * sigmoid(z));
+                }
+            }
+        }
+        return 0;
+    }
     case SWLM_STEP_ARGMAX: {
         // Generator/MetalSourceGenerator+Sampling.swift:79-103: strict '>' comparisons;
         // restated as "lowest index wins among equal maxima" for the whole vector.
@@ -429,6 +507,9 @@ orc_model* orc_create(const swlm_buffers_desc* desc) {
     m->kcache.assign(kv, 0);
     m->vcache.assign(kv, 0);
     m->conv.assign((size_t)d.conv_layers * d.max_batch * d.conv_kernel * d.conv_dim, 0);
+    const size_t ssm_conv_dim = (size_t)2 * d.ssm_groups * d.ssm_key_dim + (size_t)d.ssm_heads * d.ssm_value_dim;
+    m->ssm_conv.assign((size_t)d.ssm_layers * d.max_batch * d.ssm_conv_kernel * ssm_conv_dim, 0);
+    m->ssm_state.assign((size_t)d.ssm_layers * d.max_batch * d.ssm_heads * d.ssm_key_dim * d.ssm_value_dim, 0.0f);
     m->token_in.assign(d.max_batch, 0);
     m->token_out.assign(d.max_batch, 0);
     return m;
@@ -474,6 +555,8 @@ void orc_reset(orc_model* m) {
     std::fill(m->kcache.begin(), m->kcache.end(), 0);
     std::fill(m->vcache.begin(), m->vcache.end(), 0);
     std::fill(m->conv.begin(), m->conv.end(), 0);
+    std::fill(m->ssm_conv.begin(), m->ssm_conv.end(), 0);
+    std::fill(m->ssm_state.begin(), m->ssm_state.end(), 0.0f);
     for (auto& b : m->buf) std::fill(b.begin(), b.end(), 0);
 }
 int orc_position(const orc_model* m) { return m->position; }
@@ -537,6 +620,16 @@ int orc_read_kv(orc_model* m, int which, int layer, int b, int head, int count, 
 int orc_write_kv(orc_model* m, int which, int layer, int b, int head, int count, const uint16_t* src) {
     std::vector<uint16_t>& c = which ? m->vcache : m->kcache;
     std::memcpy(c.data() + kv_index(m, layer, b, head, 0), src, (size_t)count * m->desc.head_dim * 2);
+    return 0;
+}
+int orc_add_dense_f32(orc_model* m, const char* name, int64_t count, const float* data) {
+    m->densef[name].assign(data, data + count);
+    return 0;
+}
+int orc_read_ssm_state(orc_model* m, int layer, int b, float* dst) {
+    const swlm_buffers_desc& d = m->desc;
+    size_t n = (size_t)d.ssm_heads * d.ssm_key_dim * d.ssm_value_dim;
+    std::memcpy(dst, m->ssm_state.data() + ((size_t)layer * d.max_batch + b) * n, n * 4);
     return 0;
 }
 int orc_read_conv(orc_model* m, int layer, int b, uint16_t* dst) {

@@ -387,6 +387,88 @@ __global__ void tp_rows_reduce_kernel(TpParams tp, __nv_bfloat16* x, int x_strid
     }
 }
 
+// ssm_recurrence (Generator/MetalSourceGenerator+ConvAndState.swift:347-497): one block per (key group, sequence). The
+// block's channels (q and k of the group, v of its heads) go through the conv shift + SiLU into shared memory; then
+// one thread per (head, value dimension) walks the key dimension of the fp32 state twice (decay + read, then the full
+// write), so consecutive threads touch consecutive state elements; then the RMS norm over the value dimension and the
+// z gate. The arithmetic keeps the reference's order; the un-normalised output is rounded to the buffer type before
+// the norm, as there.
+__device__ __forceinline__ float ssm_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float ssm_softplus(float x) { return fmaxf(x, 0.0f) + logf(1.0f + expf(-fabsf(x))); }
+
+__global__ void ssm_recurrence_kernel(const SsmLaunch a) {
+    pdl_launch_dependents();
+    extern __shared__ float ssm_smem[];
+    const int tid = threadIdx.x, T = blockDim.x;
+    const int dk = a.key_dim, dv = a.value_dim, K = a.kernel;
+    const int groups = gridDim.x, hpg = a.heads / groups;
+    const int kgd = groups * dk, conv_dim = 2 * kgd + a.heads * dv;
+    const int g = blockIdx.x, b = blockIdx.y, head0 = g * hpg;
+    const int local_dim = 2 * dk + hpg * dv;
+    float* act = ssm_smem;                   // [local_dim]: q, k, then v of the group's heads
+    float* dots = act + local_dim;           // [hpg * dv]: un-normalised outputs as stored
+    float* partial = dots + hpg * dv;        // [T]
+    pdl_wait();
+    const __nv_bfloat16* qkv = a.qkv + (size_t)b * a.qkv_stride;
+    __nv_bfloat16* cstate = a.conv_state + (size_t)b * a.conv_seq_stride;
+    for (int lc = tid; lc < local_dim; lc += T) {
+        const int ch = lc < dk ? g * dk + lc : lc < 2 * dk ? kgd + g * dk + (lc - dk) : 2 * kgd + head0 * dv + (lc - 2 * dk);
+        float sum = 0.f;
+        for (int k = 0; k + 1 < K; ++k) {
+            const __nv_bfloat16 v = cstate[(size_t)(k + 1) * conv_dim + ch];
+            cstate[(size_t)k * conv_dim + ch] = v;
+            sum += __bfloat162float(v) * __bfloat162float(a.conv_weight[(size_t)ch * K + k]);
+        }
+        const __nv_bfloat16 nv = qkv[ch];
+        cstate[(size_t)(K - 1) * conv_dim + ch] = nv;
+        sum += __bfloat162float(nv) * __bfloat162float(a.conv_weight[(size_t)ch * K + (K - 1)]);
+        act[lc] = sum * ssm_sigmoid(sum);
+    }
+    __syncthreads();
+    const int tph = min(T / hpg, dv), active = hpg * tph;   // threads per head
+    const int lh = tid / tph, head = head0 + lh, lt = tid - lh * tph;
+    const int chunk = dv / tph, d0 = lt * chunk, d1 = lt + 1 == tph ? dv : d0 + chunk;
+    partial[tid] = 0.f;
+    if (tid < active) {
+        const float decay = expf(-expf(a.a_log[head]) * ssm_softplus(__bfloat162float(a.alpha[(size_t)b * a.alpha_stride + head]) + __bfloat162float(a.dt_bias[head])));
+        const float beta = ssm_sigmoid(__bfloat162float(a.beta[(size_t)b * a.beta_stride + head]));
+        float* S = a.state + (size_t)b * a.state_seq_stride + (size_t)head * dk * dv;
+        const float* Q = act;
+        const float* Kk = act + dk;
+        const float* V = act + 2 * dk + lh * dv;
+        float qn = 0.f, kn = 0.f, kq = 0.f;
+        for (int j = 0; j < dk; ++j) { qn += Q[j] * Q[j]; kn += Kk[j] * Kk[j]; kq += Q[j] * Kk[j]; }
+        const float q_inv = rsqrtf(qn + 1e-6f) * rsqrtf((float)dk), k_inv = rsqrtf(kn + 1e-6f);
+        float norm_sq = 0.f;
+        for (int d = d0; d < d1; ++d) {
+            float kvmem = 0.f, sq = 0.f;
+            for (int j = 0; j < dk; ++j) {
+                const float sv = S[(size_t)j * dv + d] * decay;
+                kvmem += sv * Kk[j];
+                sq += sv * Q[j];
+            }
+            const float delta = beta * (V[d] - kvmem * k_inv);
+            const float kid = k_inv * delta;
+            const float dot = (sq + kid * kq) * q_inv;
+            for (int j = 0; j < dk; ++j) S[(size_t)j * dv + d] = S[(size_t)j * dv + d] * decay + Kk[j] * kid;
+            dots[lh * dv + d] = __bfloat162float(__float2bfloat16_rn(dot));
+            norm_sq += dot * dot;
+        }
+        partial[tid] = norm_sq;
+    }
+    __syncthreads();
+    if (tid < active) {
+        float total = 0.f;
+        for (int t = 0; t < tph; ++t) total += partial[lh * tph + t];
+        const float rms = rsqrtf(total / (float)dv + 1e-6f);
+        for (int d = d0; d < d1; ++d) {
+            const float normed = dots[lh * dv + d] * rms * a.norm_weight[d];
+            const float z = __bfloat162float(a.z[(size_t)b * a.z_stride + (size_t)head * dv + d]);
+            a.out[(size_t)b * a.out_stride + (size_t)head * dv + d] = __float2bfloat16_rn(normed * z * ssm_sigmoid(z));
+        }
+    }
+}
+
 int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, what);
@@ -452,6 +534,20 @@ int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const _
     else
         launch_k(swiglu_kernel, dim3((n + 255) / 256, m), 256, 0, s, n, gate, g_stride, up, u_stride, out, o_stride, act);
     return check_launch("swiglu launch");
+}
+
+int launch_ssm_recurrence(const SsmLaunch& a, cudaStream_t s) {
+    const int groups = a.groups > 0 ? a.groups : 1;
+    if (a.heads <= 0 || a.heads % groups || a.key_dim <= 0 || a.value_dim <= 0 || a.kernel < 1 || a.m < 1) { set_error("ssm recurrence: bad head layout"); return SWLM_ERR_INVALID; }
+    const int hpg = a.heads / groups, local_dim = 2 * a.key_dim + hpg * a.value_dim;
+    // a block owns one key group: enough threads for its channels and for one thread per (head, value dimension)
+    int threads = std::max(local_dim, hpg * std::min(a.value_dim, 256));
+    threads = std::min(1024, (threads + 31) / 32 * 32);
+    if (threads / hpg < 1) { set_error("ssm recurrence: %d heads per key group exceed a block", hpg); return SWLM_ERR_UNSUPPORTED; }
+    const size_t smem = ((size_t)local_dim + (size_t)hpg * a.value_dim + (size_t)threads) * sizeof(float);
+    if (smem > 48 * 1024) { set_error("ssm recurrence: a key group of %d channels does not fit shared memory", local_dim); return SWLM_ERR_UNSUPPORTED; }
+    launch_k(ssm_recurrence_kernel, dim3((unsigned)groups, (unsigned)a.m), dim3((unsigned)threads), smem, s, a);
+    return check_launch("ssm recurrence launch");
 }
 
 int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t state_seq_stride,

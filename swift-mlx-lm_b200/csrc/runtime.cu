@@ -50,6 +50,7 @@ struct swlm_ctx {
     std::map<std::string, Q4Tiled> tiled;  // plain and fused tensors, keyed by name ("a|b|c" for fused)
     std::map<std::string, Q4Raw> raw_cat;  // source-layout tensors with the rows of several raw tensors one after the other ("a|b|c")
     std::map<std::string, DenseTensor> dense;
+    std::map<std::string, DenseF32> densef;   // fp32 tensors (recurrent layers' norm weight and A_log)
     int64_t bytes = 0;
     float* op_partial = nullptr; size_t op_partial_floats = 0;
     unsigned char* op_xh = nullptr; size_t op_xh_bytes = 0;   // scratch of the op-level tensor-core product
@@ -220,7 +221,7 @@ int add_q4_raw(swlm_ctx* ctx, const char* name, int n, int k, const uint32_t* w,
 // =====================================================================================================
 namespace {
 
-enum LaunchKind { L_EMBED, L_RMSNORM, L_QGEMV, L_QK_NORM, L_ATTN, L_SWIGLU, L_CONV, L_ARGMAX };
+enum LaunchKind { L_EMBED, L_RMSNORM, L_QGEMV, L_QK_NORM, L_ATTN, L_SWIGLU, L_CONV, L_ARGMAX, L_SSM };
 
 struct Launch {
     int kind = 0;
@@ -236,6 +237,8 @@ struct Launch {
     const DenseTensor* d1 = nullptr;
     const DenseTensor* d2 = nullptr;
     const Q4Raw* q_embed = nullptr;  // embedding step over a quantized table
+    const DenseF32* f1 = nullptr;    // recurrent step: norm weight, A_log (d1 = conv taps, d2 = dt_bias)
+    const DenseF32* f2 = nullptr;
     int rope_table = -1;       // index into plan->rope_tables
     std::string label;
     int steps_covered = 1;
@@ -413,6 +416,37 @@ int compile_plan(swlm_plan* plan) {
             if (s.layer < 0 || s.layer >= d.conv_layers) { set_error("conv: layer %d outside the conv state", s.layer); return SWLM_ERR_INVALID; }
             L.label = std::string("conv_state_update ") + s.weight;
             break;
+        case SWLM_STEP_SSM_RECURRENCE: {
+            L.kind = L_SSM;
+            if (ctx->tp_size > 1) { set_error("recurrent layers are not supported under tensor parallelism"); return SWLM_ERR_UNSUPPORTED; }
+            if (m > kQGemvMaxRows) { set_error("recurrent layers are limited to %d sequences per step", kQGemvMaxRows); return SWLM_ERR_UNSUPPORTED; }
+            const int groups = s.groups > 0 ? s.groups : 1;
+            if (s.layer < 0 || s.layer >= d.ssm_layers || s.heads != d.ssm_heads || groups != std::max(1, d.ssm_groups) ||
+                s.key_dim != d.ssm_key_dim || s.value_dim != d.ssm_value_dim || s.conv_kernel != d.ssm_conv_kernel ||
+                s.heads <= 0 || s.heads % groups || s.key_dim <= 0 || s.value_dim <= 0 || s.conv_kernel < 1) {
+                set_error("ssm recurrence: the step's head layout differs from the state's (layer %d)", s.layer);
+                return SWLM_ERR_INVALID;
+            }
+            const int conv_dim = 2 * groups * s.key_dim + s.heads * s.value_dim;
+            if (!buf_ok(s.in_buf) || !buf_ok(s.in2_buf) || !buf_ok(s.in3_buf) || !buf_ok(s.in4_buf) || !buf_ok(s.out_buf) ||
+                conv_dim > buf_width(d, s.in_buf) || s.heads * s.value_dim > buf_width(d, s.in2_buf) || s.heads > buf_width(d, s.in3_buf) ||
+                s.heads > buf_width(d, s.in4_buf) || s.heads * s.value_dim > buf_width(d, s.out_buf)) {
+                set_error("ssm recurrence: bad buffers");
+                return SWLM_ERR_INVALID;
+            }
+            L.d1 = find_dense(ctx, s.weight);
+            L.d2 = find_dense(ctx, s.weight3);
+            auto f1 = ctx->densef.find(s.weight2), f2 = ctx->densef.find(s.weight4);
+            if (!L.d1 || !L.d2 || f1 == ctx->densef.end() || f2 == ctx->densef.end()) {
+                set_error("ssm recurrence: conv taps / dt_bias (bf16) or norm weight / A_log (fp32) of '%s' missing", s.weight);
+                return SWLM_ERR_NOT_FOUND;
+            }
+            L.f1 = &f1->second; L.f2 = &f2->second;
+            if (L.d1->rows * L.d1->cols < (int64_t)conv_dim * s.conv_kernel || L.d2->rows * L.d2->cols < s.heads ||
+                L.f1->count < s.value_dim || L.f2->count < s.heads) { set_error("ssm recurrence: tensor sizes of '%s'", s.weight); return SWLM_ERR_INVALID; }
+            L.label = std::string("ssm_recurrence ") + s.weight;
+            break;
+        }
         case SWLM_STEP_ARGMAX:
             L.kind = L_ARGMAX;
             L.label = "argmax";
@@ -437,6 +471,7 @@ int compile_plan(swlm_plan* plan) {
         for (Launch& L : plan->launches) {
             auto redirect = [&](int& b) { if (from >= 0 && b == from) b = to; };
             redirect(L.st.in_buf); redirect(L.st.in2_buf); redirect(L.st.in3_buf);
+            if (L.kind == L_SSM) redirect(L.st.in4_buf);
             bool writes = L.st.out_buf == from;
             for (int q = 0; q < L.n_seg; ++q) writes |= L.seg_buf[q] == from;
             if (L.kind == L_QGEMV && L.epilogue == QGEMV_EPI_SWIGLU && L.seg_buf[0] == L.st.in_buf) {
@@ -461,7 +496,8 @@ int compile_plan(swlm_plan* plan) {
         for (int q = 0; q < B.n_seg; ++q) ok &= B.seg_buf[q] != A.st.in_buf && B.seg_buf[q] != SWLM_BUF_RESIDUAL;
         for (size_t j = i + 2; j < plan->launches.size() && ok; ++j) {
             const Launch& C = plan->launches[j];
-            if (C.st.in_buf == A.st.out_buf || C.st.in2_buf == A.st.out_buf || C.st.in3_buf == A.st.out_buf) ok = false;
+            if (C.st.in_buf == A.st.out_buf || C.st.in2_buf == A.st.out_buf || C.st.in3_buf == A.st.out_buf ||
+                (C.kind == L_SSM && C.st.in4_buf == A.st.out_buf)) ok = false;
             bool writes = C.st.out_buf == A.st.out_buf;
             for (int q = 0; q < C.n_seg; ++q) writes |= C.seg_buf[q] == A.st.out_buf;
             if (writes) break;
@@ -581,6 +617,8 @@ struct swlm_state {
     int width[SWLM_BUF_COUNT] = {};
     __nv_bfloat16* kcache = nullptr; __nv_bfloat16* vcache = nullptr; size_t kv_layer_elems = 0;
     __nv_bfloat16* conv = nullptr; size_t conv_layer_elems = 0;
+    __nv_bfloat16* ssm_conv = nullptr; size_t ssm_conv_layer_elems = 0;   // [layer][seq][kernel][conv_dim]
+    float* ssm_state = nullptr; size_t ssm_state_layer_elems = 0;         // [layer][seq][heads][key_dim][value_dim]
     int32_t* position = nullptr; int32_t* step_counter = nullptr;
     int32_t* token_in = nullptr; int32_t* token_out = nullptr; int32_t* ring = nullptr;
     int32_t* prompt = nullptr; size_t prompt_cap = 0;
@@ -746,6 +784,23 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
                                   s->buf[st.out_buf], s->width[st.out_buf], stream);
             s->launches += 1;
             break;
+        case L_SSM: {
+            SsmLaunch a;
+            a.m = m; a.heads = st.heads; a.groups = std::max(1, st.groups); a.key_dim = st.key_dim; a.value_dim = st.value_dim; a.kernel = st.conv_kernel;
+            a.qkv = s->buf[st.in_buf]; a.qkv_stride = s->width[st.in_buf];
+            a.z = s->buf[st.in2_buf]; a.z_stride = s->width[st.in2_buf];
+            a.beta = s->buf[st.in3_buf]; a.beta_stride = s->width[st.in3_buf];
+            a.alpha = s->buf[st.in4_buf]; a.alpha_stride = s->width[st.in4_buf];
+            a.conv_weight = L.d1->data; a.dt_bias = L.d2->data; a.norm_weight = L.f1->data; a.a_log = L.f2->data;
+            a.conv_seq_stride = s->ssm_conv_layer_elems / d.max_batch;
+            a.conv_state = s->ssm_conv + (size_t)st.layer * s->ssm_conv_layer_elems;
+            a.state_seq_stride = s->ssm_state_layer_elems / d.max_batch;
+            a.state = s->ssm_state + (size_t)st.layer * s->ssm_state_layer_elems;
+            a.out = s->buf[st.out_buf]; a.out_stride = s->width[st.out_buf];
+            rc = launch_ssm_recurrence(a, stream);
+            s->launches += 1;
+            break;
+        }
         case L_ARGMAX:
             if (plan->ctx->tp_size > 1 && !s->tp_attached) { set_error("tensor-parallel plan: call swlm_tp_export / swlm_tp_attach on the state first"); return SWLM_ERR_STATE; }
             {
@@ -853,6 +908,8 @@ std::vector<Region> state_regions(swlm_state* s) {
     r.push_back({s->vcache, (size_t)d.kv_layers * s->kv_layer_elems * 2});
     r.push_back({s->conv, (size_t)d.conv_layers * s->conv_layer_elems * 2});
     r.push_back({s->res2, (size_t)d.max_batch * s->width[SWLM_BUF_RESIDUAL] * 2});
+    r.push_back({s->ssm_conv, (size_t)d.ssm_layers * s->ssm_conv_layer_elems * 2});
+    r.push_back({s->ssm_state, (size_t)d.ssm_layers * s->ssm_state_layer_elems * 4});
     r.push_back({s->position, (size_t)d.max_batch * 4});
     r.push_back({s->token_in, (size_t)d.max_batch * 4});
     r.push_back({s->token_out, (size_t)d.max_batch * 4});
@@ -1004,6 +1061,7 @@ bool rows_capable(const swlm_plan* plan, bool allow_tp = false) {
         if (st.kind == SWLM_STEP_QGEMV && st.in_buf == st.out_buf) return false;
         if (st.kind == SWLM_STEP_QGEMV && (st.k & 63)) return false;
         if (st.kind == SWLM_STEP_CONV_STATE_UPDATE && st.conv_kernel > 8) return false;
+        if (st.kind == SWLM_STEP_SSM_RECURRENCE) return false;   // recurrent layers ingest prompts token by token
     }
     return true;
 }
@@ -1278,6 +1336,7 @@ void swlm_ctx_destroy(swlm_ctx* ctx) {
     for (auto& kv : ctx->tiled) { cudaFree(kv.second.tiles); cudaFree(kv.second.sb); }
     for (auto& kv : ctx->raw_cat) { cudaFree(kv.second.w); cudaFree(kv.second.scales); cudaFree(kv.second.biases); }
     for (auto& kv : ctx->dense) cudaFree(kv.second.data);
+    for (auto& kv : ctx->densef) cudaFree(kv.second.data);
     cudaFree(ctx->op_partial);
     cudaFree(ctx->tc_status);
     cudaFree(ctx->op_xh);
@@ -1355,6 +1414,24 @@ int swlm_weights_add_dense_bf16(swlm_ctx* ctx, const char* name, int64_t rows, i
     if ((rc = dev_alloc(&t.data, (size_t)t.rows * cols, ctx))) return rc;
     SWLM_CUDA(cudaMemcpy(t.data, data + (size_t)sl.row0 * cols, (size_t)t.rows * cols * 2, cudaMemcpyHostToDevice));
     ctx->dense[name] = t;
+    return SWLM_OK;
+}
+
+int swlm_weights_add_dense_f32(swlm_ctx* ctx, const char* name, int64_t count, const float* data) {
+    if (!ctx || !name || !data || count <= 0) { set_error("bad fp32 tensor"); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(ctx);
+    if (rc) return rc;
+    auto old = ctx->densef.find(name);
+    if (old != ctx->densef.end()) {
+        SWLM_CUDA(cudaDeviceSynchronize());
+        cudaFree(old->second.data);
+        ctx->densef.erase(old);
+    }
+    DenseF32 t;
+    t.count = count;
+    if ((rc = dev_alloc(&t.data, (size_t)count, ctx))) return rc;
+    SWLM_CUDA(cudaMemcpy(t.data, data, (size_t)count * 4, cudaMemcpyHostToDevice));
+    ctx->densef[name] = t;
     return SWLM_OK;
 }
 
@@ -1436,6 +1513,13 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     s->conv_layer_elems = (size_t)d.max_batch * d.conv_kernel * d.conv_dim;
     if ((rc = dev_alloc(&s->conv, (size_t)d.conv_layers * s->conv_layer_elems))) return fail(rc);
     if ((rc = dev_alloc(&s->res2, (size_t)d.max_batch * s->width[SWLM_BUF_RESIDUAL]))) return fail(rc);
+    if (d.ssm_layers > 0) {
+        const size_t ssm_conv_dim = (size_t)2 * std::max(1, d.ssm_groups) * d.ssm_key_dim + (size_t)d.ssm_heads * d.ssm_value_dim;
+        s->ssm_conv_layer_elems = (size_t)d.max_batch * d.ssm_conv_kernel * ssm_conv_dim;
+        s->ssm_state_layer_elems = (size_t)d.max_batch * d.ssm_heads * d.ssm_key_dim * d.ssm_value_dim;
+        if ((rc = dev_alloc(&s->ssm_conv, (size_t)d.ssm_layers * s->ssm_conv_layer_elems))) return fail(rc);
+        if ((rc = dev_alloc(&s->ssm_state, (size_t)d.ssm_layers * s->ssm_state_layer_elems))) return fail(rc);
+    }
     if ((rc = dev_alloc(&s->position, d.max_batch))) return fail(rc);
     s->pos_host.assign(d.max_batch, 0);
     if ((rc = dev_alloc(&s->step_counter, 1))) return fail(rc);
@@ -1473,6 +1557,7 @@ void swlm_state_destroy(swlm_state* s) {
     drop_graphs(s);
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->buf[i]);
     cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->conv); cudaFree(s->res2);
+    cudaFree(s->ssm_conv); cudaFree(s->ssm_state);
     if (s->tp.tp > 1) {
         for (int r = 0; r < s->tp.tp; ++r)
             if (r != s->tp.rank && s->tp_attached && s->tp.peer[r]) cudaIpcCloseMemHandle(s->tp.peer[r]);
@@ -1754,6 +1839,11 @@ int swlm_state_reset_seq(swlm_state* s, int seq) {
     const size_t per_seq = (size_t)d.conv_kernel * d.conv_dim;
     for (int l = 0; l < d.conv_layers && per_seq; ++l)
         SWLM_CUDA(cudaMemsetAsync(s->conv + (size_t)l * s->conv_layer_elems + (size_t)seq * per_seq, 0, per_seq * 2, s->stream));
+    for (int l = 0; l < d.ssm_layers; ++l) {
+        const size_t cs = s->ssm_conv_layer_elems / d.max_batch, rs = s->ssm_state_layer_elems / d.max_batch;
+        SWLM_CUDA(cudaMemsetAsync(s->ssm_conv + (size_t)l * s->ssm_conv_layer_elems + (size_t)seq * cs, 0, cs * 2, s->stream));
+        SWLM_CUDA(cudaMemsetAsync(s->ssm_state + (size_t)l * s->ssm_state_layer_elems + (size_t)seq * rs, 0, rs * 4, s->stream));
+    }
     SWLM_CUDA(cudaMemsetAsync(s->position + seq, 0, 4, s->stream));
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     s->pos_host[seq] = 0;
@@ -1830,6 +1920,16 @@ int swlm_read_conv(swlm_state* s, int layer, int b, uint16_t* dst) {
     const size_t n = (size_t)d.conv_kernel * d.conv_dim;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     SWLM_CUDA(cudaMemcpy(dst, s->conv + (size_t)layer * s->conv_layer_elems + (size_t)b * n, n * 2, cudaMemcpyDeviceToHost));
+    return SWLM_OK;
+}
+
+int swlm_read_ssm_state(swlm_state* s, int layer, int b, float* dst) {
+    if (!s || !dst) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (layer < 0 || layer >= d.ssm_layers || b < 0 || b >= d.max_batch) { set_error("bad recurrent state address"); return SWLM_ERR_INVALID; }
+    const size_t n = s->ssm_state_layer_elems / d.max_batch;
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    SWLM_CUDA(cudaMemcpy(dst, s->ssm_state + (size_t)layer * s->ssm_state_layer_elems + (size_t)b * n, n * 4, cudaMemcpyDeviceToHost));
     return SWLM_OK;
 }
 

@@ -87,6 +87,11 @@ struct DenseTensor {
     __nv_bfloat16* data = nullptr;
 };
 
+struct DenseF32 {
+    int64_t count = 0;
+    float* data = nullptr;
+};
+
 // ---- kernels: launch wrappers (each returns a status; no synchronisation) -------
 
 struct RepackSrc {
@@ -213,6 +218,24 @@ int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t st
                      __nv_bfloat16* out, int out_stride, cudaStream_t s);
 // conv_state_update over `tokens` consecutive tokens of one sequence (state of that sequence), bit-identical to
 // `tokens` single steps.
+// One step of the gated delta rule for m sequences (see SWLM_STEP_SSM_RECURRENCE): conv shift + SiLU over the q|k|v
+// channels, per-head state update and read-out, RMS norm and z gate. conv_state [m][kernel][conv_dim] bf16 (row pitch
+// conv_seq_stride elements per sequence), state [m][heads][key_dim][value_dim] fp32.
+struct SsmLaunch {
+    int m = 1, heads = 0, groups = 1, key_dim = 0, value_dim = 0, kernel = 0;
+    const __nv_bfloat16* qkv = nullptr; int qkv_stride = 0;
+    const __nv_bfloat16* z = nullptr; int z_stride = 0;
+    const __nv_bfloat16* beta = nullptr; int beta_stride = 0;
+    const __nv_bfloat16* alpha = nullptr; int alpha_stride = 0;
+    const __nv_bfloat16* conv_weight = nullptr;   // [conv_dim][kernel]
+    const float* norm_weight = nullptr;           // [value_dim]
+    const __nv_bfloat16* dt_bias = nullptr;       // [heads]
+    const float* a_log = nullptr;                 // [heads]
+    __nv_bfloat16* conv_state = nullptr; size_t conv_seq_stride = 0;
+    float* state = nullptr; size_t state_seq_stride = 0;
+    __nv_bfloat16* out = nullptr; int out_stride = 0;
+};
+int launch_ssm_recurrence(const SsmLaunch& a, cudaStream_t s);
 int launch_conv_prefill(int tokens, int dim, int kernel, __nv_bfloat16* state, const __nv_bfloat16* in, int in_stride,
                         const __nv_bfloat16* weight, __nv_bfloat16* out, int out_stride, cudaStream_t s);
 // argmax over [m][n] bf16, lowest index wins. Writes token_out[m], token_in_next[m] (may be null) and

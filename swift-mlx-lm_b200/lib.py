@@ -40,6 +40,12 @@ class Step(C.Structure):
         ("weight", C.c_char * NAME_MAX),
         ("weight2", C.c_char * NAME_MAX),
         ("window_left", C.c_int32),
+        ("in4_buf", C.c_int32),
+        ("groups", C.c_int32),
+        ("key_dim", C.c_int32),
+        ("value_dim", C.c_int32),
+        ("weight3", C.c_char * NAME_MAX),
+        ("weight4", C.c_char * NAME_MAX),
     ]
 
 
@@ -58,6 +64,12 @@ class BuffersDesc(C.Structure):
         ("conv_layers", C.c_int32),
         ("conv_dim", C.c_int32),
         ("conv_kernel", C.c_int32),
+        ("ssm_layers", C.c_int32),
+        ("ssm_heads", C.c_int32),
+        ("ssm_groups", C.c_int32),
+        ("ssm_key_dim", C.c_int32),
+        ("ssm_value_dim", C.c_int32),
+        ("ssm_conv_kernel", C.c_int32),
     ]
 
 
@@ -75,6 +87,7 @@ SIGNATURES = {
     "swlm_weights_add_q4g128_mlx": (_I, [_P, C.c_char_p, _I, _I, _P, _P, _P, _I]),
     "swlm_weights_add_q4g128_staf": (_I, [_P, C.c_char_p, _I, _I, _P, _I]),
     "swlm_weights_add_dense_bf16": (_I, [_P, C.c_char_p, C.c_int64, C.c_int64, _P, _I]),
+    "swlm_weights_add_dense_f32": (_I, [_P, C.c_char_p, C.c_int64, _P]),
     "swlm_weights_bytes": (C.c_int64, [_P]),
     "swlm_plan_build": (_I, [_P, C.POINTER(Step), _I, C.POINTER(BuffersDesc), C.POINTER(_P)]),
     "swlm_plan_destroy": (None, [_P]),
@@ -101,6 +114,7 @@ SIGNATURES = {
     "swlm_read_kv": (_I, [_P, _I, _I, _I, _I, _I, _P]),
     "swlm_write_kv": (_I, [_P, _I, _I, _I, _I, _I, _P]),
     "swlm_read_conv": (_I, [_P, _I, _I, _P]),
+    "swlm_read_ssm_state": (_I, [_P, _I, _I, _P]),
     "swlm_set_position": (_I, [_P, _I]),
     "swlm_set_positions": (_I, [_P, _P]),
     "swlm_get_positions": (_I, [_P, _P]),

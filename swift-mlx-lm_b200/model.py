@@ -57,6 +57,11 @@ class WeightStore:
         add = self.lib.swlm_weights_add_q4g64_staf if group == 64 else self.lib.swlm_weights_add_q4g128_staf
         self.lib.check(add(self.handle, name.encode(), n, k, _ptr(blk), shard))
 
+    def add_dense_f32(self, name: str, data: np.ndarray) -> None:
+        """fp32 tensor, replicated (norm weight and A_log of the recurrent layers)."""
+        d = np.ascontiguousarray(data, dtype=np.float32)
+        self.lib.check(self.lib.swlm_weights_add_dense_f32(self.handle, name.encode(), d.size, _ptr(d)))
+
     def add_dense(self, name: str, data_bf16: np.ndarray, shard: int = 0) -> None:
         d = np.ascontiguousarray(data_bf16, dtype=np.uint16)
         rows = d.shape[0] if d.ndim == 2 else 1
@@ -196,6 +201,12 @@ class InferenceModel:
     def read_conv(self, layer: int, b: int) -> np.ndarray:
         out = np.empty((int(self.desc.conv_kernel), int(self.desc.conv_dim)), dtype=np.uint16)
         self.lib.check(self.lib.swlm_read_conv(self.state, layer, b, _ptr(out)))
+        return out
+
+    def read_ssm_state(self, layer: int, b: int) -> np.ndarray:
+        d = self.desc
+        out = np.empty((int(d.ssm_heads), int(d.ssm_key_dim), int(d.ssm_value_dim)), dtype=np.float32)
+        self.lib.check(self.lib.swlm_read_ssm_state(self.state, layer, b, _ptr(out)))
         return out
 
     def set_position(self, position: int) -> None:

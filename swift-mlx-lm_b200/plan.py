@@ -30,6 +30,7 @@ STEP_SWIGLU = 8
 STEP_CONV_STATE_UPDATE = 9
 STEP_ARGMAX = 10
 STEP_GEGLU = 11
+STEP_SSM_RECURRENCE = 12
 
 SHARD_REPLICATE, SHARD_COLUMN, SHARD_ROW, SHARD_COLUMN3 = 0, 1, 2, 3
 
@@ -122,9 +123,9 @@ def _step(kind: int, **kw) -> Step:
     s = Step()
     s.kind = kind
     s.layer = -1
-    s.in_buf = s.in2_buf = s.in3_buf = s.out_buf = -1
+    s.in_buf = s.in2_buf = s.in3_buf = s.in4_buf = s.out_buf = -1
     for key, value in kw.items():
-        if key in ("weight", "weight2"):
+        if key in ("weight", "weight2", "weight3", "weight4"):
             value = value.encode()
         setattr(s, key, value)
     return s

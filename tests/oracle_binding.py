@@ -32,6 +32,16 @@ class OracleModel:
         d = np.ascontiguousarray(data, dtype=np.uint16)
         assert self.dll.orc_add_dense(self.h, name.encode(), C.c_int64(d.size), _p(d)) == 0
 
+    def add_dense_f32(self, name, data):
+        d = np.ascontiguousarray(data, dtype=np.float32)
+        assert self.dll.orc_add_dense_f32(self.h, name.encode(), C.c_int64(d.size), _p(d)) == 0
+
+    def read_ssm_state(self, layer, b):
+        d = self.desc
+        out = np.empty((int(d.ssm_heads), int(d.ssm_key_dim), int(d.ssm_value_dim)), dtype=np.float32)
+        self.dll.orc_read_ssm_state(self.h, layer, b, _p(out))
+        return out
+
     def load(self, builder, weights, staf_fp16=False):
         for name, kind, _shape, _shard in builder.tensors():
             if kind == "q4":
@@ -117,6 +127,8 @@ class Oracle:
         d.orc_staf_repack_mlx_group.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         d.orc_q4_dequant_staf_group.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         d.orc_add_dense.argtypes = [C.c_void_p, C.c_char_p, C.c_int64, C.c_void_p]
+        d.orc_add_dense_f32.argtypes = [C.c_void_p, C.c_char_p, C.c_int64, C.c_void_p]
+        d.orc_read_ssm_state.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         d.orc_set_plan.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         d.orc_reset.argtypes = [C.c_void_p]
         d.orc_position.argtypes = [C.c_void_p]

@@ -456,3 +456,51 @@ def test_flash_decode_op_long_context(pkg, store, B, ctx):
     ref = torch.einsum("bgrt,bgtd->bgrd", torch.softmax(s, dim=-1), v.float()).reshape(B, H, D)
     err = rel_err(out.float().cpu().numpy().reshape(B * H, D), ref.cpu().numpy().reshape(B * H, D))
     assert err.max() <= RTOL
+
+
+# ---- recurrent (gated delta rule) step ---------------------------------------------------------------------
+
+@pytest.mark.parametrize("heads,groups,dk,dv,K,batch", [(4, 2, 16, 16, 4, 1), (32, 16, 128, 128, 4, 1), (8, 8, 64, 128, 3, 2),
+                                                        (6, 2, 32, 64, 4, 3)])
+def test_ssm_recurrence_matches_oracle_over_steps(pkg, store, oracle, heads, groups, dk, dv, K, batch):
+    """ssm_recurrence (the DeltaNet / Qwen3.5 linear-attention step): 5 steps with the conv state and the fp32 recurrent
+    state carried, outputs against the oracle per step, states at the end; (32, 16, 128, 128) is the full-size layer."""
+    from test_oracle_golden import ssm_case, ssm_step_and_desc
+    c = ssm_case(pkg, heads=heads, groups=groups, dk=dk, dv=dv, K=K, batch=batch, seed=heads + dk)
+    desc, step, width = ssm_step_and_desc(pkg, c, max_batch=batch)
+    tag = f"ssm{heads}x{dk}x{dv}b{batch}"
+    for name in ("weight", "weight2", "weight3", "weight4"):
+        setattr(step, name, getattr(step, name).replace(b"l0.", tag.encode() + b"."))
+    P = pkg.plan
+    store.add_dense(tag + ".conv1d.weight", _bf(pkg, c["conv_w"]))
+    store.add_dense_f32(tag + ".norm.weight", c["norm_w"])
+    store.add_dense(tag + ".dt_bias", _bf(pkg, c["dt_bias"]))
+    store.add_dense_f32(tag + ".A_log", c["a_log"])
+    store.add_dense("ssm.embed", np.zeros((8, 256), dtype=np.uint16))
+    steps = [P._step(P.STEP_EMBED, out_buf=P.BUF_HIDDEN, n=256, weight="ssm.embed"), step]
+    gm = pkg.InferenceModel(store, steps, desc)
+    om = oracle.model(desc)
+    om.add_dense(tag + ".conv1d.weight", _bf(pkg, c["conv_w"]))
+    om.add_dense_f32(tag + ".norm.weight", c["norm_w"])
+    om.add_dense(tag + ".dt_bias", _bf(pkg, c["dt_bias"]))
+    om.add_dense_f32(tag + ".A_log", c["a_log"])
+    rng = c["rng"]
+    pad = lambda a: np.pad(a, ((0, 0), (0, width - a.shape[1])))
+    for t in range(5):
+        ins = {P.BUF_S1: rng.normal(size=(batch, c["conv_dim"])), P.BUF_S2: rng.normal(size=(batch, heads * dv)),
+               P.BUF_S3: rng.normal(size=(batch, heads)), P.BUF_S4: rng.normal(size=(batch, heads))}
+        for buf, v in ins.items():
+            for mdl in (gm, om):
+                mdl.write_buffer(buf, _bf(pkg, pad(v)))
+        gm.run_step(step)
+        om.run_step(step)
+        got = pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, heads * dv))
+        ref = pkg.bf16_to_f32(om.read_buffer(P.BUF_S0, heads * dv))
+        assert rel_err(got, ref).max() <= RTOL, t
+    for b in range(batch):
+        gs, os_ = gm.read_ssm_state(0, b), om.read_ssm_state(0, b)
+        assert np.max(np.abs(gs - os_)) <= 1e-4 * max(1.0, np.max(np.abs(os_)))
+    # a sequence that is reset starts from an empty state again
+    gm.reset_sequence(0)
+    assert not gm.read_ssm_state(0, 0).any()
+    gm.close()

@@ -129,6 +129,86 @@ def test_attention_sliding_window_against_fp64_softmax(pkg, oracle, window):
             assert np.max(np.abs(out[h] - w @ vals)) < 2e-2
 
 
+def ssm_case(pkg, heads=4, groups=2, dk=16, dv=16, K=4, batch=1, seed=1):
+    """Random inputs and weights of one recurrent layer (bf16-exact where the reference reads bf16)."""
+    rng = np.random.default_rng(seed)
+    conv_dim = 2 * groups * dk + heads * dv
+    bf = lambda a: pkg.bf16_to_f32(pkg.f32_to_bf16(np.asarray(a, dtype=np.float32)))
+    return dict(heads=heads, groups=groups, dk=dk, dv=dv, K=K, conv_dim=conv_dim, batch=batch,
+                conv_w=bf(rng.normal(0.0, 0.5, size=(conv_dim, K))), norm_w=(1.0 + rng.normal(0.0, 0.1, size=dv)).astype(np.float32),
+                dt_bias=bf(rng.normal(0.0, 0.5, size=heads)), a_log=rng.normal(0.0, 0.5, size=heads).astype(np.float32),
+                rng=rng, bf=bf)
+
+
+def ssm_reference_f64(c, state, cstate, qkv, z, beta, alpha):
+    """fp64 restatement of the gated delta rule step (Generator/MetalSourceGenerator+ConvAndState.swift:392-497) for
+    one sequence; updates `state` [H][dk][dv] and `cstate` [K][conv_dim] in place, returns the output [H*dv]."""
+    H, G, dk, dv, K = c["heads"], c["groups"], c["dk"], c["dv"], c["K"]
+    kgd, hpg = G * dk, H // G
+    cstate[:-1] = cstate[1:]
+    cstate[-1] = qkv
+    s = (cstate * c["conv_w"].T.astype(np.float64)).sum(axis=0)
+    act = s / (1.0 + np.exp(-s))
+    out = np.zeros(H * dv)
+    for h in range(H):
+        g = h // hpg
+        Q, Kk, V = act[g * dk:(g + 1) * dk], act[kgd + g * dk:kgd + (g + 1) * dk], act[2 * kgd + h * dv:2 * kgd + (h + 1) * dv]
+        x = float(alpha[h]) + float(c["dt_bias"][h])
+        decay = np.exp(-np.exp(float(c["a_log"][h])) * (max(x, 0.0) + np.log1p(np.exp(-abs(x)))))
+        b = 1.0 / (1.0 + np.exp(-float(beta[h])))
+        qn = Q / np.sqrt((Q * Q).sum() + 1e-6) / np.sqrt(dk)
+        kn = Kk / np.sqrt((Kk * Kk).sum() + 1e-6)
+        S = state[h] * decay
+        delta = b * (V - kn @ S)
+        S = S + np.outer(kn, delta)
+        state[h] = S
+        o = qn @ S
+        o = o / np.sqrt((o * o).mean() + 1e-6) * c["norm_w"]
+        zz = z[h * dv:(h + 1) * dv]
+        out[h * dv:(h + 1) * dv] = o * zz / (1.0 + np.exp(-zz))
+    return out
+
+
+def ssm_step_and_desc(pkg, c, max_batch=1):
+    P = pkg.plan
+    width = max(c["conv_dim"], c["heads"] * c["dv"], 256)
+    desc = pkg.BuffersDesc(hidden=256, slot_dim=width, vocab=8, max_seq=8, max_batch=max_batch, kv_layers=0, kv_heads=0, head_dim=0,
+                           conv_layers=0, conv_dim=0, conv_kernel=0, ssm_layers=1, ssm_heads=c["heads"], ssm_groups=c["groups"],
+                           ssm_key_dim=c["dk"], ssm_value_dim=c["dv"], ssm_conv_kernel=c["K"])
+    step = P._step(P.STEP_SSM_RECURRENCE, layer=0, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, in3_buf=P.BUF_S3, in4_buf=P.BUF_S4,
+                   out_buf=P.BUF_S0, heads=c["heads"], groups=c["groups"], key_dim=c["dk"], value_dim=c["dv"], conv_kernel=c["K"],
+                   weight="l0.conv1d.weight", weight2="l0.norm.weight", weight3="l0.dt_bias", weight4="l0.A_log")
+    return desc, step, width
+
+
+def test_ssm_recurrence_against_fp64_gated_delta_rule(pkg, oracle):
+    """The reference's tests compare its two SSM kernels with each other and hold no known answer, so the oracle's
+    restatement is checked against the textbook form of the recurrence in fp64: S <- decay S + k (x) beta (v - S^T k),
+    out = norm(S^T q) * silu(z), over 6 steps with the state carried."""
+    c = ssm_case(pkg)
+    desc, step, width = ssm_step_and_desc(pkg, c)
+    m = oracle.model(desc)
+    m.add_dense("l0.conv1d.weight", pkg.f32_to_bf16(c["conv_w"]))
+    m.add_dense_f32("l0.norm.weight", c["norm_w"])
+    m.add_dense("l0.dt_bias", pkg.f32_to_bf16(c["dt_bias"]))
+    m.add_dense_f32("l0.A_log", c["a_log"])
+    P = pkg.plan
+    state = np.zeros((c["heads"], c["dk"], c["dv"]))
+    cstate = np.zeros((c["K"], c["conv_dim"]))
+    pad = lambda a: np.pad(a, (0, width - a.size))[None, :]
+    for t in range(6):
+        qkv, z = c["bf"](c["rng"].normal(size=c["conv_dim"])), c["bf"](c["rng"].normal(size=c["heads"] * c["dv"]))
+        beta, alpha = c["bf"](c["rng"].normal(size=c["heads"])), c["bf"](c["rng"].normal(size=c["heads"]))
+        for buf, v in ((P.BUF_S1, qkv), (P.BUF_S2, z), (P.BUF_S3, beta), (P.BUF_S4, alpha)):
+            m.write_buffer(buf, pkg.f32_to_bf16(pad(v)))
+        m.run_step(step)
+        got = pkg.bf16_to_f32(m.read_buffer(P.BUF_S0, c["heads"] * c["dv"]))[0]
+        ref = ssm_reference_f64(c, state, cstate, qkv.astype(np.float64), z.astype(np.float64), beta, alpha)
+        # the kernel rounds the un-normalised output to bf16 before the norm and the result once more
+        assert np.max(np.abs(got - ref)) <= 2e-2 * max(1.0, np.max(np.abs(ref))), t
+        assert np.max(np.abs(m.read_ssm_state(0, 0) - state)) <= 1e-4 * max(1.0, np.max(np.abs(state)))
+
+
 def test_conv_decode_trace_matches_sequence_formula_bit_for_bit(pkg, oracle, golden):
     g = golden["conv_pattern"]
     D, K, T = g["dim"], g["kernel"], g["seq_len"]
