@@ -25,6 +25,10 @@ public enum CUDAPlanEntry {
     case gatedActivation(gelu: Bool, dimension: Int, gate: Slot, up: Slot, output: Slot)
     /// Conv1dFragment: conv_state_update over the packed B|C|x projection.
     case shortConv(layer: Int, weight: String, dimension: Int, kernelSize: Int, input: Slot, output: Slot)
+    /// SSMRecurrenceFragment (decode): gated delta rule over the projected q|k|v, z, beta and alpha buffers.
+    case recurrence(layer: Int, heads: Int, groups: Int, keyDimension: Int, valueDimension: Int, convKernelSize: Int,
+                    convWeight: String, normWeight: String, dtBias: String, aLog: String,
+                    qkv: Slot, z: Slot, beta: Slot, alpha: Slot, output: Slot)
     /// ArgmaxFragment over the logits.
     case argmax(vocabulary: Int)
 
@@ -47,7 +51,7 @@ public struct CUDADispatchPlanBuilder {
         var s = swlm_step()
         s.kind = kind
         s.layer = -1
-        s.in_buf = -1; s.in2_buf = -1; s.in3_buf = -1; s.out_buf = -1
+        s.in_buf = -1; s.in2_buf = -1; s.in3_buf = -1; s.in4_buf = -1; s.out_buf = -1
         return s
     }
 
@@ -55,6 +59,15 @@ public struct CUDADispatchPlanBuilder {
         let bytes = Array(name.utf8)
         guard bytes.count < Int(SWLM_NAME_MAX) else { throw CUDACompilerError.unsupportedTensor(name) }
         withUnsafeMutableBytes(of: second ? &field.weight2 : &field.weight) { raw in
+            raw.initializeMemory(as: UInt8.self, repeating: 0)
+            raw.copyBytes(from: bytes)
+        }
+    }
+
+    func setName<T>(_ name: String, into field: inout T) throws {
+        let bytes = Array(name.utf8)
+        guard bytes.count < Int(SWLM_NAME_MAX) else { throw CUDACompilerError.unsupportedTensor(name) }
+        withUnsafeMutableBytes(of: &field) { raw in
             raw.initializeMemory(as: UInt8.self, repeating: 0)
             raw.copyBytes(from: bytes)
         }
@@ -113,6 +126,19 @@ public struct CUDADispatchPlanBuilder {
             s.in_buf = input.rawValue; s.out_buf = output.rawValue
             s.n = Int32(dimension); s.conv_kernel = Int32(kernelSize)
             try setName(weight, into: &s)
+            return s
+        case let .recurrence(layer, heads, groups, keyDimension, valueDimension, convKernelSize, convWeight, normWeight, dtBias, aLog,
+                             qkv, z, beta, alpha, output):
+            var s = blank(Int32(SWLM_STEP_SSM_RECURRENCE))
+            s.layer = Int32(layer)
+            s.in_buf = qkv.rawValue; s.in2_buf = z.rawValue; s.in3_buf = beta.rawValue; s.in4_buf = alpha.rawValue
+            s.out_buf = output.rawValue
+            s.heads = Int32(heads); s.groups = Int32(groups); s.key_dim = Int32(keyDimension); s.value_dim = Int32(valueDimension)
+            s.conv_kernel = Int32(convKernelSize)
+            try setName(convWeight, into: &s)
+            try setName(normWeight, into: &s, second: true)
+            try setName(dtBias, into: &s.weight3)
+            try setName(aLog, into: &s.weight4)
             return s
         case let .argmax(vocabulary):
             var s = blank(Int32(SWLM_STEP_ARGMAX))

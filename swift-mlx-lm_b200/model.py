@@ -266,6 +266,8 @@ def load_model(store: WeightStore, builder, weights) -> InferenceModel:
         entry = weights[name]
         if kind == "q4":
             store.add_q4_mlx(name, entry[0], entry[1], entry[2], shard)
+        elif kind == "f32":
+            store.add_dense_f32(name, entry)
         else:
             store.add_dense(name, entry, shard if kind == "conv" else 0)
     return InferenceModel(store, builder.decode_steps(), builder.config.buffers_desc())
@@ -288,6 +290,8 @@ def bundle_tensors(builder, weights):
             out[mod + ".weight"] = ("U32", np.ascontiguousarray(entry[0], dtype=np.uint32))
             out[mod + ".scales"] = ("BF16", np.ascontiguousarray(entry[1], dtype=np.uint16))
             out[mod + ".biases"] = ("BF16", np.ascontiguousarray(entry[2], dtype=np.uint16))
+        elif kind == "f32":
+            out[name] = ("F32", np.ascontiguousarray(entry, dtype=np.float32))
         else:
             out[name] = ("BF16", np.ascontiguousarray(entry, dtype=np.uint16))
     return out
@@ -307,6 +311,10 @@ def load_model_from_staf(store: WeightStore, builder, staf_file) -> InferenceMod
                 raise _staf.STAFError(f"{entry.name}: scheme {entry.scheme:#x} is not 4-bit group 64")
             n, words = entry.shape
             store.add_q4_staf(name, raw.reshape(n, words * 8 // 64, 36), n, words * 8, shard)
+        elif kind == "f32":
+            if entry.scheme != _staf.SCHEME_FP32:
+                raise _staf.STAFError(f"{entry.name}: expected an fp32 section")
+            store.add_dense_f32(name, raw.view(np.float32))
         else:
             if entry.scheme == _staf.SCHEME_BF16:
                 arr = raw.view(np.uint16)

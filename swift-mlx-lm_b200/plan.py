@@ -37,7 +37,7 @@ SHARD_REPLICATE, SHARD_COLUMN, SHARD_ROW, SHARD_COLUMN3 = 0, 1, 2, 3
 
 @dataclass
 class ModelConfig:
-    family: str  # "llama" | "lfm2"
+    family: str  # "llama" | "lfm2" | "deltanet" (recurrent layers of the Qwen3.5 kind between Llama-style attention layers)
     hidden: int
     intermediate: int
     layers: int
@@ -64,6 +64,15 @@ class ModelConfig:
     # layers that use it (None: every attention layer), the others attend everything.
     sliding_window: int = 0
     sliding_window_layers: Sequence[int] = None
+    # "deltanet": the layers not listed in attention_layers are gated-delta-rule recurrent layers
+    # (Sources/LMArchitecture/Declaration/Components/DeltaNet.swift, Primitives/SSMRecurrenceFragment.swift) with
+    # `ssm_heads` value heads of `ssm_value_dim`, `ssm_groups` key groups of `ssm_key_dim`, a causal conv of
+    # `ssm_conv_kernel` taps over the q|k|v channels; tensor names follow Models/Qwen35/Qwen35FamilyNaming.swift:73-87.
+    ssm_heads: int = 0
+    ssm_groups: int = 0
+    ssm_key_dim: int = 0
+    ssm_value_dim: int = 0
+    ssm_conv_kernel: int = 4
 
     def is_attention_layer(self, i: int) -> bool:
         return self.family == "llama" or i in self.attention_layers
@@ -74,13 +83,22 @@ class ModelConfig:
 
     @property
     def conv_layer_count(self) -> int:
-        return self.layers - self.kv_layer_count
+        return self.layers - self.kv_layer_count if self.family == "lfm2" else 0
+
+    @property
+    def ssm_layer_count(self) -> int:
+        return self.layers - self.kv_layer_count if self.family == "deltanet" else 0
+
+    @property
+    def ssm_conv_dim(self) -> int:
+        return 2 * self.ssm_groups * self.ssm_key_dim + self.ssm_heads * self.ssm_value_dim
 
     @property
     def slot_dim(self) -> int:
         # slotDimension = max(hidden, max(intermediate, 4*hidden), widest projection)
         # (Sources/MetalCompiler/Buffer/MetalBufferAllocator.swift:13-18)
-        widest = max(self.heads * self.head_dim, 3 * self.hidden if self.family == "lfm2" else 0)
+        widest = max(self.heads * self.head_dim, 3 * self.hidden if self.family == "lfm2" else 0,
+                     self.ssm_conv_dim if self.family == "deltanet" else 0)
         return max(self.hidden, self.intermediate, 4 * self.hidden, widest)
 
     def buffers_desc(self) -> BuffersDesc:
@@ -90,6 +108,10 @@ class ModelConfig:
             head_dim=self.head_dim, conv_layers=self.conv_layer_count,
             conv_dim=self.hidden if self.conv_layer_count else 0,
             conv_kernel=self.conv_kernel if self.conv_layer_count else 0,
+            ssm_layers=self.ssm_layer_count, ssm_heads=self.ssm_heads if self.ssm_layer_count else 0,
+            ssm_groups=self.ssm_groups if self.ssm_layer_count else 0, ssm_key_dim=self.ssm_key_dim if self.ssm_layer_count else 0,
+            ssm_value_dim=self.ssm_value_dim if self.ssm_layer_count else 0,
+            ssm_conv_kernel=self.ssm_conv_kernel if self.ssm_layer_count else 0,
         )
 
     # Algorithmic weight bytes one decode step streams: 0.5625 bytes per quantized weight.
@@ -100,6 +122,8 @@ class ModelConfig:
             total += 3 * h * f
             if self.is_attention_layer(i):
                 total += 2 * h * self.heads * self.head_dim + 2 * h * self.kv_heads * self.head_dim
+            elif self.family == "deltanet":
+                total += h * (self.ssm_conv_dim + 2 * self.ssm_heads * self.ssm_value_dim + 2 * self.ssm_heads)
             else:
                 total += 3 * h * h + h * h
         return total + h * self.vocab
@@ -144,13 +168,29 @@ class DispatchPlanBuilder:
         out = [("model.embed_tokens.weight", "q4" if c.tie_embeddings else "dense", (c.vocab, h), SHARD_REPLICATE)]
         for i in range(c.layers):
             p = f"model.layers.{i}."
-            if c.family == "llama":
+            if c.family in ("llama", "deltanet"):
+                out.append((p + "input_layernorm.weight", "norm", (h,), SHARD_REPLICATE))
+                if c.is_attention_layer(i):
+                    out += [
+                        (p + "self_attn.q_proj", "q4", (qd, h), SHARD_COLUMN),
+                        (p + "self_attn.k_proj", "q4", (kvd, h), SHARD_COLUMN),
+                        (p + "self_attn.v_proj", "q4", (kvd, h), SHARD_COLUMN),
+                        (p + "self_attn.o_proj", "q4", (h, qd), SHARD_ROW),
+                    ]
+                else:
+                    vd = c.ssm_heads * c.ssm_value_dim
+                    out += [
+                        (p + "linear_attn.in_proj_qkv", "q4", (c.ssm_conv_dim, h), SHARD_REPLICATE),
+                        (p + "linear_attn.in_proj_z", "q4", (vd, h), SHARD_REPLICATE),
+                        (p + "linear_attn.in_proj_b", "q4", (c.ssm_heads, h), SHARD_REPLICATE),
+                        (p + "linear_attn.in_proj_a", "q4", (c.ssm_heads, h), SHARD_REPLICATE),
+                        (p + "linear_attn.conv1d.weight", "conv", (c.ssm_conv_dim, c.ssm_conv_kernel), SHARD_REPLICATE),
+                        (p + "linear_attn.norm.weight", "f32", (c.ssm_value_dim,), SHARD_REPLICATE),
+                        (p + "linear_attn.dt_bias", "dense", (c.ssm_heads,), SHARD_REPLICATE),
+                        (p + "linear_attn.A_log", "f32", (c.ssm_heads,), SHARD_REPLICATE),
+                        (p + "linear_attn.out_proj", "q4", (h, vd), SHARD_REPLICATE),
+                    ]
                 out += [
-                    (p + "input_layernorm.weight", "norm", (h,), SHARD_REPLICATE),
-                    (p + "self_attn.q_proj", "q4", (qd, h), SHARD_COLUMN),
-                    (p + "self_attn.k_proj", "q4", (kvd, h), SHARD_COLUMN),
-                    (p + "self_attn.v_proj", "q4", (kvd, h), SHARD_COLUMN),
-                    (p + "self_attn.o_proj", "q4", (h, qd), SHARD_ROW),
                     (p + "post_attention_layernorm.weight", "norm", (h,), SHARD_REPLICATE),
                     (p + "mlp.gate_proj", "q4", (f, h), SHARD_COLUMN),
                     (p + "mlp.up_proj", "q4", (f, h), SHARD_COLUMN),
@@ -179,7 +219,7 @@ class DispatchPlanBuilder:
                     (p + "feed_forward.w3", "q4", (f, h), SHARD_COLUMN),
                     (p + "feed_forward.w2", "q4", (h, f), SHARD_ROW),
                 ]
-        final_norm = "model.norm.weight" if c.family == "llama" else "model.embedding_norm.weight"
+        final_norm = "model.norm.weight" if c.family != "lfm2" else "model.embedding_norm.weight"
         out.append((final_norm, "norm", (h,), SHARD_REPLICATE))
         if not c.tie_embeddings:
             out.append(("lm_head", "q4", (c.vocab, h), SHARD_COLUMN))
@@ -191,7 +231,7 @@ class DispatchPlanBuilder:
         h, f, qd, kvd = c.hidden, c.intermediate, c.heads * c.head_dim, c.kv_heads * c.head_dim
         eps = c.norm_eps
         steps = [_step(STEP_EMBED, out_buf=BUF_HIDDEN, n=h, weight="model.embed_tokens.weight")]
-        kv_layer = conv_layer = 0
+        kv_layer = conv_layer = ssm_layer = 0
         first = True
 
         def norm(name: str):
@@ -206,7 +246,7 @@ class DispatchPlanBuilder:
         for i in range(c.layers):
             p = f"model.layers.{i}."
             attn = c.is_attention_layer(i)
-            norm(p + ("input_layernorm.weight" if c.family == "llama" else "operator_norm.weight"))
+            norm(p + ("input_layernorm.weight" if c.family != "lfm2" else "operator_norm.weight"))
             if attn:
                 gemv(p + "self_attn.q_proj", BUF_S0, BUF_S1, qd, h)
                 gemv(p + "self_attn.k_proj", BUF_S0, BUF_S2, kvd, h)
@@ -221,21 +261,33 @@ class DispatchPlanBuilder:
                                    window_left=c.sliding_window if c.sliding_window > 0 and (
                                        c.sliding_window_layers is None or i in c.sliding_window_layers) else 0))
                 kv_layer += 1
-                gemv(p + ("self_attn.o_proj" if c.family == "llama" else "self_attn.out_proj"), BUF_S0, BUF_HIDDEN, h, qd)
+                gemv(p + ("self_attn.o_proj" if c.family != "lfm2" else "self_attn.out_proj"), BUF_S0, BUF_HIDDEN, h, qd)
+            elif c.family == "deltanet":
+                lp, vd = p + "linear_attn.", c.ssm_heads * c.ssm_value_dim
+                gemv(lp + "in_proj_qkv", BUF_S0, BUF_S1, c.ssm_conv_dim, h)
+                gemv(lp + "in_proj_z", BUF_S0, BUF_S2, vd, h)
+                gemv(lp + "in_proj_b", BUF_S0, BUF_S3, c.ssm_heads, h)
+                gemv(lp + "in_proj_a", BUF_S0, BUF_S4, c.ssm_heads, h)
+                steps.append(_step(STEP_SSM_RECURRENCE, layer=ssm_layer, in_buf=BUF_S1, in2_buf=BUF_S2, in3_buf=BUF_S3, in4_buf=BUF_S4,
+                                   out_buf=BUF_S0, heads=c.ssm_heads, groups=c.ssm_groups, key_dim=c.ssm_key_dim,
+                                   value_dim=c.ssm_value_dim, conv_kernel=c.ssm_conv_kernel, weight=lp + "conv1d.weight",
+                                   weight2=lp + "norm.weight", weight3=lp + "dt_bias", weight4=lp + "A_log"))
+                ssm_layer += 1
+                gemv(lp + "out_proj", BUF_S0, BUF_HIDDEN, h, vd)
             else:
                 gemv(p + "conv.in_proj", BUF_S0, BUF_S1, 3 * h, h)
                 steps.append(_step(STEP_CONV_STATE_UPDATE, layer=conv_layer, in_buf=BUF_S1, out_buf=BUF_S0, n=h,
                                    conv_kernel=c.conv_kernel, weight=p + "conv.conv.weight"))
                 conv_layer += 1
                 gemv(p + "conv.out_proj", BUF_S0, BUF_HIDDEN, h, h)
-            norm(p + ("post_attention_layernorm.weight" if c.family == "llama" else "ffn_norm.weight"))
-            gate, up, down = (("mlp.gate_proj", "mlp.up_proj", "mlp.down_proj") if c.family == "llama"
+            norm(p + ("post_attention_layernorm.weight" if c.family != "lfm2" else "ffn_norm.weight"))
+            gate, up, down = (("mlp.gate_proj", "mlp.up_proj", "mlp.down_proj") if c.family != "lfm2"
                               else ("feed_forward.w1", "feed_forward.w3", "feed_forward.w2"))
             gemv(p + gate, BUF_S0, BUF_S1, f, h)
             gemv(p + up, BUF_S0, BUF_S2, f, h)
             steps.append(_step(STEP_GEGLU if c.activation == "gelu_tanh" else STEP_SWIGLU, in_buf=BUF_S1, in2_buf=BUF_S2, out_buf=BUF_S0, n=f))
             gemv(p + down, BUF_S0, BUF_HIDDEN, h, f)
-        final_norm = "model.norm.weight" if c.family == "llama" else "model.embedding_norm.weight"
+        final_norm = "model.norm.weight" if c.family != "lfm2" else "model.embedding_norm.weight"
         steps.append(_step(STEP_RESADD_RMSNORM, in_buf=BUF_HIDDEN, out_buf=BUF_S0, n=h, eps=eps, weight_bias=c.norm_weight_bias, weight=final_norm))
         gemv("model.embed_tokens.weight" if c.tie_embeddings else "lm_head", BUF_S0, BUF_LOGITS, c.vocab, h)
         steps.append(_step(STEP_ARGMAX, in_buf=BUF_LOGITS, n=c.vocab))

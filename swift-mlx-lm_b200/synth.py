@@ -42,6 +42,12 @@ def synth_model_weights(builder, seed: int = 3, centered: bool = False, group: i
             out[name] = synth_q4(shape[0], shape[1], _seed(seed, name), centered=centered, group=group)
         elif kind == "norm":
             out[name] = f32_to_bf16((1.0 + rng.normal(0.0, 0.02, size=shape)).astype(np.float32))
+        elif kind == "f32":   # recurrent layers: norm weight ~ 1, A_log ~ U(-1, 1); kept in fp32
+            out[name] = (rng.uniform(-1.0, 1.0, size=shape) if name.endswith("A_log") else 1.0 + rng.normal(0.0, 0.02, size=shape)).astype(np.float32)
+        elif name.endswith("dt_bias"):
+            out[name] = f32_to_bf16(rng.normal(0.0, 0.5, size=shape).astype(np.float32))
+        elif name.endswith("conv1d.weight"):
+            out[name] = f32_to_bf16(rng.normal(0.0, 0.3, size=shape).astype(np.float32))
         else:  # embedding table, conv weights
             out[name] = f32_to_bf16(rng.normal(0.0, 0.02, size=shape).astype(np.float32))
     return out

@@ -46,6 +46,8 @@ class OracleModel:
         for name, kind, _shape, _shard in builder.tensors():
             if kind == "q4":
                 self.add_q4(name, *weights[name], staf_fp16=staf_fp16)
+            elif kind == "f32":
+                self.add_dense_f32(name, weights[name])
             else:
                 self.add_dense(name, weights[name])
         steps = builder.decode_steps()

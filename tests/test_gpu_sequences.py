@@ -200,3 +200,34 @@ def test_batch_prompt_goes_through_the_chunked_path(pkg, oracle, family, batch):
     assert gm.launches - before < 60 * gm.launches_per_step
     assert list(gm.positions) == [108] * batch
     gm.close(); store.close()
+
+
+def small_deltanet(pkg, batch=1, max_seq=128):
+    return pkg.ModelConfig("deltanet", hidden=512, intermediate=1024, layers=5, heads=8, kv_heads=2, head_dim=64, vocab=4096,
+                           norm_eps=1e-5, rope_theta=1000000.0, attention_layers=[3], max_seq=max_seq, max_batch=batch,
+                           ssm_heads=8, ssm_groups=4, ssm_key_dim=32, ssm_value_dim=64, ssm_conv_kernel=4)
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_recurrent_layers_model_against_oracle(pkg, oracle, batch):
+    """Four gated-delta-rule layers and one attention layer: greedy tokens and logits against the oracle over 48 steps,
+    the fp32 recurrent state of every layer at the end. The prompt goes token by token (recurrent layers have no
+    chunked path)."""
+    cfg = small_deltanet(pkg, batch=batch)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    oracle.set_threads(8)
+    assert "ssm_recurrence" in gm.describe()
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=40, steps=48)
+    assert len(mism) <= 2, mism
+    for layer in range(cfg.ssm_layer_count):
+        for b in range(batch):
+            g, o = gm.read_ssm_state(layer, b), om.read_ssm_state(layer, b)
+            assert np.max(np.abs(g - o)) <= 2e-2 * max(1e-3, np.max(np.abs(o))), (layer, b)
+    # snapshot / restore carries the recurrent state
+    snap = gm.prompt_snapshot()
+    tok = np.arange(1, batch + 1, dtype=np.int32)
+    a = gm.decode_n(tok, 4)
+    gm.restore(snap)
+    assert np.array_equal(gm.decode_n(tok, 4), a)
+    gm.free_snapshot(snap)
+    gm.close(); store.close()
