@@ -409,8 +409,15 @@ __global__ void ssm_recurrence_kernel(const SsmLaunch a) {
     float* dots = act + local_dim;           // [hpg * dv]: un-normalised outputs as stored
     float* partial = dots + hpg * dv;        // [T]
     pdl_wait();
-    const __nv_bfloat16* qkv = a.qkv + (size_t)b * a.qkv_stride;
     __nv_bfloat16* cstate = a.conv_state + (size_t)b * a.conv_seq_stride;
+    const int tph = min(T / hpg, dv), active = hpg * tph;   // threads per head
+    const int lh = tid / tph, head = head0 + lh, lt = tid - lh * tph;
+    const int chunk = dv / tph, d0 = lt * chunk, d1 = lt + 1 == tph ? dv : d0 + chunk;
+    // every channel, state column and output element belongs to the same thread at every token, so walking a chunk's
+    // tokens in order needs no synchronisation beyond the barriers of one step
+    for (int tok = 0; tok < a.tokens; ++tok) {
+    const int row = b + tok;   // decode: sequence b; prompt chunk: token `tok` of the one sequence
+    const __nv_bfloat16* qkv = a.qkv + (size_t)row * a.qkv_stride;
     for (int lc = tid; lc < local_dim; lc += T) {
         const int ch = lc < dk ? g * dk + lc : lc < 2 * dk ? kgd + g * dk + (lc - dk) : 2 * kgd + head0 * dv + (lc - 2 * dk);
         float sum = 0.f;
@@ -425,13 +432,10 @@ __global__ void ssm_recurrence_kernel(const SsmLaunch a) {
         act[lc] = sum * ssm_sigmoid(sum);
     }
     __syncthreads();
-    const int tph = min(T / hpg, dv), active = hpg * tph;   // threads per head
-    const int lh = tid / tph, head = head0 + lh, lt = tid - lh * tph;
-    const int chunk = dv / tph, d0 = lt * chunk, d1 = lt + 1 == tph ? dv : d0 + chunk;
     partial[tid] = 0.f;
     if (tid < active) {
-        const float decay = expf(-expf(a.a_log[head]) * ssm_softplus(__bfloat162float(a.alpha[(size_t)b * a.alpha_stride + head]) + __bfloat162float(a.dt_bias[head])));
-        const float beta = ssm_sigmoid(__bfloat162float(a.beta[(size_t)b * a.beta_stride + head]));
+        const float decay = expf(-expf(a.a_log[head]) * ssm_softplus(__bfloat162float(a.alpha[(size_t)row * a.alpha_stride + head]) + __bfloat162float(a.dt_bias[head])));
+        const float beta = ssm_sigmoid(__bfloat162float(a.beta[(size_t)row * a.beta_stride + head]));
         float* S = a.state + (size_t)b * a.state_seq_stride + (size_t)head * dk * dv;
         const float* Q = act;
         const float* Kk = act + dk;
@@ -463,9 +467,11 @@ __global__ void ssm_recurrence_kernel(const SsmLaunch a) {
         const float rms = rsqrtf(total / (float)dv + 1e-6f);
         for (int d = d0; d < d1; ++d) {
             const float normed = dots[lh * dv + d] * rms * a.norm_weight[d];
-            const float z = __bfloat162float(a.z[(size_t)b * a.z_stride + (size_t)head * dv + d]);
-            a.out[(size_t)b * a.out_stride + (size_t)head * dv + d] = __float2bfloat16_rn(normed * z * ssm_sigmoid(z));
+            const float z = __bfloat162float(a.z[(size_t)row * a.z_stride + (size_t)head * dv + d]);
+            a.out[(size_t)row * a.out_stride + (size_t)head * dv + d] = __float2bfloat16_rn(normed * z * ssm_sigmoid(z));
         }
+    }
+    __syncthreads();   // shared memory is reused by the next token
     }
 }
 
@@ -538,7 +544,8 @@ int launch_swiglu(int m, int n, const __nv_bfloat16* gate, int g_stride, const _
 
 int launch_ssm_recurrence(const SsmLaunch& a, cudaStream_t s) {
     const int groups = a.groups > 0 ? a.groups : 1;
-    if (a.heads <= 0 || a.heads % groups || a.key_dim <= 0 || a.value_dim <= 0 || a.kernel < 1 || a.m < 1) { set_error("ssm recurrence: bad head layout"); return SWLM_ERR_INVALID; }
+    if (a.heads <= 0 || a.heads % groups || a.key_dim <= 0 || a.value_dim <= 0 || a.kernel < 1 || a.m < 1 || a.tokens < 1 ||
+        (a.tokens > 1 && a.m != 1)) { set_error("ssm recurrence: bad head layout"); return SWLM_ERR_INVALID; }
     const int hpg = a.heads / groups, local_dim = 2 * a.key_dim + hpg * a.value_dim;
     // a block owns one key group: enough threads for its channels and for one thread per (head, value dimension)
     int threads = std::max(local_dim, hpg * std::min(a.value_dim, 256));

@@ -419,7 +419,6 @@ int compile_plan(swlm_plan* plan) {
         case SWLM_STEP_SSM_RECURRENCE: {
             L.kind = L_SSM;
             if (ctx->tp_size > 1) { set_error("recurrent layers are not supported under tensor parallelism"); return SWLM_ERR_UNSUPPORTED; }
-            if (m > kQGemvMaxRows) { set_error("recurrent layers are limited to %d sequences per step", kQGemvMaxRows); return SWLM_ERR_UNSUPPORTED; }
             const int groups = s.groups > 0 ? s.groups : 1;
             if (s.layer < 0 || s.layer >= d.ssm_layers || s.heads != d.ssm_heads || groups != std::max(1, d.ssm_groups) ||
                 s.key_dim != d.ssm_key_dim || s.value_dim != d.ssm_value_dim || s.conv_kernel != d.ssm_conv_kernel ||
@@ -1061,7 +1060,7 @@ bool rows_capable(const swlm_plan* plan, bool allow_tp = false) {
         if (st.kind == SWLM_STEP_QGEMV && st.in_buf == st.out_buf) return false;
         if (st.kind == SWLM_STEP_QGEMV && (st.k & 63)) return false;
         if (st.kind == SWLM_STEP_CONV_STATE_UPDATE && st.conv_kernel > 8) return false;
-        if (st.kind == SWLM_STEP_SSM_RECURRENCE) return false;   // recurrent layers ingest prompts token by token
+        if (st.kind == SWLM_STEP_SSM_RECURRENCE && plan->ctx->tp_size > 1) return false;
     }
     return true;
 }
@@ -1255,6 +1254,26 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
                                          pf[st.in_buf], wd[st.in_buf], find_dense(ctx, st.weight)->data, pf[st.out_buf], wd[st.out_buf], stream);
             s->launches += 1;
             break;
+        case SWLM_STEP_SSM_RECURRENCE: {
+            SsmLaunch a;
+            a.m = wide ? c : 1; a.tokens = wide ? 1 : c;
+            a.heads = st.heads; a.groups = std::max(1, st.groups); a.key_dim = st.key_dim; a.value_dim = st.value_dim; a.kernel = st.conv_kernel;
+            a.qkv = pf[st.in_buf]; a.qkv_stride = wd[st.in_buf];
+            a.z = pf[st.in2_buf]; a.z_stride = wd[st.in2_buf];
+            a.beta = pf[st.in3_buf]; a.beta_stride = wd[st.in3_buf];
+            a.alpha = pf[st.in4_buf]; a.alpha_stride = wd[st.in4_buf];
+            a.conv_weight = find_dense(ctx, st.weight)->data; a.dt_bias = find_dense(ctx, st.weight3)->data;
+            a.norm_weight = ctx->densef.at(st.weight2).data; a.a_log = ctx->densef.at(st.weight4).data;
+            a.conv_seq_stride = s->ssm_conv_layer_elems / d.max_batch;
+            a.state_seq_stride = s->ssm_state_layer_elems / d.max_batch;
+            // a chunk belongs to one sequence: its slabs; a decode step of many sequences: all slabs
+            a.conv_state = s->ssm_conv + (size_t)st.layer * s->ssm_conv_layer_elems + (wide ? 0 : (size_t)seq * a.conv_seq_stride);
+            a.state = s->ssm_state + (size_t)st.layer * s->ssm_state_layer_elems + (wide ? 0 : (size_t)seq * a.state_seq_stride);
+            a.out = pf[st.out_buf]; a.out_stride = wd[st.out_buf];
+            rc = launch_ssm_recurrence(a, stream);
+            s->launches += 1;
+            break;
+        }
         case SWLM_STEP_ARGMAX:
             if (wide ? body_only : head_row < 0) break;
             if (wide) {

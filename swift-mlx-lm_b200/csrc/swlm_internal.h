@@ -223,6 +223,10 @@ int launch_conv_step(int m, int dim, int kernel, __nv_bfloat16* state, size_t st
 // conv_seq_stride elements per sequence), state [m][heads][key_dim][value_dim] fp32.
 struct SsmLaunch {
     int m = 1, heads = 0, groups = 1, key_dim = 0, value_dim = 0, kernel = 0;
+    // > 1 (with m == 1): the rows are consecutive prompt tokens of one sequence, walked in order inside the kernel
+    // (ssm_recurrence_seq, Generator/MetalSourceGenerator+ConvAndState.swift:502-): the same code as the single step,
+    // so a chunk leaves the state repeated decode steps would
+    int tokens = 1;
     const __nv_bfloat16* qkv = nullptr; int qkv_stride = 0;
     const __nv_bfloat16* z = nullptr; int z_stride = 0;
     const __nv_bfloat16* beta = nullptr; int beta_stride = 0;

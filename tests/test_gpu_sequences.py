@@ -231,3 +231,30 @@ def test_recurrent_layers_model_against_oracle(pkg, oracle, batch):
     assert np.array_equal(gm.decode_n(tok, 4), a)
     gm.free_snapshot(snap)
     gm.close(); store.close()
+
+
+def test_recurrent_layers_chunked_prompt_and_many_sequences(pkg, oracle):
+    """The recurrence walks a prompt chunk's tokens in order inside one launch (the reference's sequence variant), with
+    the products of the chunk on the tensor cores; and 20 sequences decode through the row-wise executor with one
+    recurrent state each. Both against the oracle, which ingests token by token."""
+    cfg = small_deltanet(pkg, batch=1, max_seq=192)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    oracle.set_threads(8)
+    gm.set_prefill_chunk(64)
+    before = gm.launches
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=150, steps=16)
+    assert len(mism) <= 2, mism
+    assert gm.launches - before < 60 * gm.launches_per_step   # chunks, not 150 decode steps
+    for layer in range(cfg.ssm_layer_count):
+        g, o = gm.read_ssm_state(layer, 0), om.read_ssm_state(layer, 0)
+        assert np.max(np.abs(g - o)) <= 3e-2 * max(1e-3, np.max(np.abs(o))), layer
+    gm.close(); store.close()
+
+    cfg = small_deltanet(pkg, batch=20, max_seq=64)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=6, steps=16)
+    assert len(mism) <= 2, mism
+    for b in (0, 19):
+        g, o = gm.read_ssm_state(0, b), om.read_ssm_state(0, b)
+        assert np.max(np.abs(g - o)) <= 3e-2 * max(1e-3, np.max(np.abs(o)))
+    gm.close(); store.close()
