@@ -147,7 +147,14 @@ typedef struct swlm_buffers_desc {
     int32_t ssm_key_dim;
     int32_t ssm_value_dim;
     int32_t ssm_conv_kernel;
+    /* KV cache element scheme (KVCacheSpecification, Buffer/MetalGraphAllocator.swift): 0 or SWLM_KV_BF16 = dense bf16;
+       SWLM_KV_Q8G32 = 8-bit groups of 32 along the head dimension, 36-byte blocks fp16 scale | fp16 zero | 32 bytes,
+       value = scale * q + zero (read_kv_element / write_kv_quantized_q8, Generator/MetalSourceGenerator+Attention.swift:
+       1923-1956, 2057-2101). K and V use the same scheme. */
+    int32_t kv_scheme;
 } swlm_buffers_desc;
+
+enum { SWLM_KV_BF16 = 0x01, SWLM_KV_Q8G32 = 0x10 };
 
 #ifdef __cplusplus
 }

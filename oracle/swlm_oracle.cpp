@@ -166,6 +166,7 @@ struct orc_model {
     std::vector<uint16_t> buf[SWLM_BUF_COUNT];
     int width[SWLM_BUF_COUNT]{};
     std::vector<uint16_t> kcache, vcache;  // [layer][b][kv_head][max_seq][head_dim]
+    std::vector<uint8_t> kq8, vq8;         // the same rows as 36-byte Q8 group-32 blocks when desc.kv_scheme == SWLM_KV_Q8G32
     std::vector<uint16_t> conv;            // [layer][b][conv_kernel][conv_dim]
     std::map<std::string, std::vector<float>> densef;   // fp32 tensors (recurrent layers' norm weight, A_log)
     std::vector<uint16_t> ssm_conv;        // [layer][b][ssm_conv_kernel][ssm conv dim]
@@ -182,6 +183,39 @@ uint16_t* row(orc_model* m, int buf, int b) { return m->buf[buf].data() + (size_
 size_t kv_index(const orc_model* m, int layer, int b, int head, int t) {
     const swlm_buffers_desc& d = m->desc;
     return ((((size_t)layer * d.max_batch + b) * d.kv_heads + head) * d.max_seq + t) * d.head_dim;
+}
+
+// ---- 8-bit group-32 KV rows ---------------------------------------------------
+// write_kv_quantized_q8 (Generator/MetalSourceGenerator+Attention.swift:2057-2101): per group of 32 values
+// scale = max((max - min) / 255, 1e-10), q = clamp(round((v - min) / scale), 0, 255) with the fp32 scale and min;
+// the block stores half(scale), half(min), then the 32 bytes.
+void kv_q8_write_row(uint8_t* row, const float* v, int hd) {
+    for (int g = 0; g * 32 < hd; ++g) {
+        float lo = HUGE_VALF, hi = -HUGE_VALF;
+        for (int i = 0; i < 32; ++i) { lo = std::fmin(lo, v[g * 32 + i]); hi = std::fmax(hi, v[g * 32 + i]); }
+        float scale = (hi - lo) / 255.0f;
+        if (scale < 1e-10f) scale = 1e-10f;
+        uint8_t* blk = row + (size_t)g * 36;
+        uint16_t hs = f32_to_f16(scale), hz = f32_to_f16(lo);
+        std::memcpy(blk, &hs, 2);
+        std::memcpy(blk + 2, &hz, 2);
+        for (int i = 0; i < 32; ++i) {
+            int q = (int)std::round((v[g * 32 + i] - lo) / scale);
+            blk[4 + i] = (uint8_t)(q < 0 ? 0 : q > 255 ? 255 : q);
+        }
+    }
+}
+// read_kv_element (:1923-1956): scale * float(q) + zero with the stored fp16 scale and zero.
+inline float kv_q8_read(const uint8_t* row, int e) {
+    const uint8_t* blk = row + (size_t)(e / 32) * 36;
+    uint16_t hs, hz;
+    std::memcpy(&hs, blk, 2);
+    std::memcpy(&hz, blk + 2, 2);
+    return f16_to_f32(hs) * (float)blk[4 + e % 32] + f16_to_f32(hz);
+}
+size_t kv_q8_index(const orc_model* m, int layer, int b, int head, int t) {
+    const swlm_buffers_desc& d = m->desc;
+    return ((((size_t)layer * d.max_batch + b) * d.kv_heads + head) * d.max_seq + t) * (size_t)(d.head_dim / 32 * 36);
 }
 
 int run_step(orc_model* m, const swlm_step& st, int batch) {
@@ -286,8 +320,12 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 rope_inplace(q.data(), st.rope_dim, st.rope_base, pos);
                 rope_inplace(kc.data(), st.rope_dim, st.rope_base, pos);
             }
-            const uint16_t* kbase = m->kcache.data() + kv_index(m, st.layer, b, kvh, 0);
-            const uint16_t* vbase = m->vcache.data() + kv_index(m, st.layer, b, kvh, 0);
+            const bool q8 = d.kv_scheme == SWLM_KV_Q8G32;
+            const size_t q8_row = (size_t)(hd / 32) * 36;
+            const uint16_t* kbase = q8 ? nullptr : m->kcache.data() + kv_index(m, st.layer, b, kvh, 0);
+            const uint16_t* vbase = q8 ? nullptr : m->vcache.data() + kv_index(m, st.layer, b, kvh, 0);
+            const uint8_t* kq = q8 ? m->kq8.data() + kv_q8_index(m, st.layer, b, kvh, 0) : nullptr;
+            const uint8_t* vq = q8 ? m->vq8.data() + kv_q8_index(m, st.layer, b, kvh, 0) : nullptr;
             float max_score = -HUGE_VALF, sum_exp = 0.0f;
             // sliding window (:851-853): the current token and the window_left - 1 before it
             const int t_first = st.window_left > 0 && pos + 1 > st.window_left ? pos - st.window_left + 1 : 0;
@@ -296,6 +334,8 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 if (t == pos) {
                     // the current token's key and value are used unrounded (:866-868, :905-907)
                     for (int i = 0; i < hd; ++i) score += q[i] * kc[i];
+                } else if (q8) {
+                    for (int i = 0; i < hd; ++i) score += q[i] * kv_q8_read(kq + (size_t)t * q8_row, i);
                 } else {
                     const uint16_t* kr = kbase + (size_t)t * hd;
                     for (int i = 0; i < hd; ++i) score += q[i] * bf16_to_f32(kr[i]);
@@ -308,6 +348,8 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 float wgt = std::exp(score - max_score);
                 if (t == pos) {
                     for (int i = 0; i < hd; ++i) out[i] = out[i] * corr + wgt * vc[i];
+                } else if (q8) {
+                    for (int i = 0; i < hd; ++i) out[i] = out[i] * corr + wgt * kv_q8_read(vq + (size_t)t * q8_row, i);
                 } else {
                     const uint16_t* vr = vbase + (size_t)t * hd;
                     for (int i = 0; i < hd; ++i) out[i] = out[i] * corr + wgt * bf16_to_f32(vr[i]);
@@ -325,6 +367,13 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 const uint16_t* vin = row(m, st.in3_buf, b) + (size_t)kvh * hd;
                 for (int i = 0; i < hd; ++i) kc[i] = bf16_to_f32(kin[i]);
                 if (st.rope_dim > 0) rope_inplace(kc.data(), st.rope_dim, st.rope_base, pos);
+                if (d.kv_scheme == SWLM_KV_Q8G32) {   // quantized from the unrounded rotated k and from v as given
+                    std::vector<float> vf(hd);
+                    for (int i = 0; i < hd; ++i) vf[i] = bf16_to_f32(vin[i]);
+                    kv_q8_write_row(m->kq8.data() + kv_q8_index(m, st.layer, b, kvh, pos), kc.data(), hd);
+                    kv_q8_write_row(m->vq8.data() + kv_q8_index(m, st.layer, b, kvh, pos), vf.data(), hd);
+                    continue;
+                }
                 uint16_t* kw = m->kcache.data() + kv_index(m, st.layer, b, kvh, pos);
                 uint16_t* vw = m->vcache.data() + kv_index(m, st.layer, b, kvh, pos);
                 for (int i = 0; i < hd; ++i) { kw[i] = f32_to_bf16(kc[i]); vw[i] = vin[i]; }
@@ -504,6 +553,12 @@ orc_model* orc_create(const swlm_buffers_desc* desc) {
         m->buf[i].assign((size_t)d.max_batch * w, 0);
     }
     size_t kv = (size_t)d.kv_layers * d.max_batch * d.kv_heads * d.max_seq * d.head_dim;
+    if (d.kv_scheme == SWLM_KV_Q8G32) {
+        const size_t bytes = (size_t)d.kv_layers * d.max_batch * d.kv_heads * d.max_seq * (size_t)(d.head_dim / 32 * 36);
+        m->kq8.assign(bytes, 0);
+        m->vq8.assign(bytes, 0);
+        kv = 0;
+    }
     m->kcache.assign(kv, 0);
     m->vcache.assign(kv, 0);
     m->conv.assign((size_t)d.conv_layers * d.max_batch * d.conv_kernel * d.conv_dim, 0);
@@ -554,6 +609,8 @@ void orc_reset(orc_model* m) {
     m->position = 0;
     std::fill(m->kcache.begin(), m->kcache.end(), 0);
     std::fill(m->vcache.begin(), m->vcache.end(), 0);
+    std::fill(m->kq8.begin(), m->kq8.end(), 0);
+    std::fill(m->vq8.begin(), m->vq8.end(), 0);
     std::fill(m->conv.begin(), m->conv.end(), 0);
     std::fill(m->ssm_conv.begin(), m->ssm_conv.end(), 0);
     std::fill(m->ssm_state.begin(), m->ssm_state.end(), 0.0f);
@@ -613,11 +670,28 @@ int orc_run_step(orc_model* m, const swlm_step* st, const int32_t* token_in, int
 }
 // K or V cache rows of one (layer, sequence, head): [count][head_dim] bf16 from token 0.
 int orc_read_kv(orc_model* m, int which, int layer, int b, int head, int count, uint16_t* dst) {
+    if (m->desc.kv_scheme == SWLM_KV_Q8G32) {   // the dequantised rows, rounded to bf16
+        const int hd = m->desc.head_dim;
+        const uint8_t* rows = (which ? m->vq8 : m->kq8).data() + kv_q8_index(m, layer, b, head, 0);
+        for (int t = 0; t < count; ++t)
+            for (int e = 0; e < hd; ++e) dst[(size_t)t * hd + e] = f32_to_bf16(kv_q8_read(rows + (size_t)t * (hd / 32 * 36), e));
+        return 0;
+    }
     const std::vector<uint16_t>& c = which ? m->vcache : m->kcache;
     std::memcpy(dst, c.data() + kv_index(m, layer, b, head, 0), (size_t)count * m->desc.head_dim * 2);
     return 0;
 }
 int orc_write_kv(orc_model* m, int which, int layer, int b, int head, int count, const uint16_t* src) {
+    if (m->desc.kv_scheme == SWLM_KV_Q8G32) {   // the rows are quantised as an appended row would be
+        const int hd = m->desc.head_dim;
+        uint8_t* rows = (which ? m->vq8 : m->kq8).data() + kv_q8_index(m, layer, b, head, 0);
+        std::vector<float> f(hd);
+        for (int t = 0; t < count; ++t) {
+            for (int e = 0; e < hd; ++e) f[e] = bf16_to_f32(src[(size_t)t * hd + e]);
+            kv_q8_write_row(rows + (size_t)t * (hd / 32 * 36), f.data(), hd);
+        }
+        return 0;
+    }
     std::vector<uint16_t>& c = which ? m->vcache : m->kcache;
     std::memcpy(c.data() + kv_index(m, layer, b, head, 0), src, (size_t)count * m->desc.head_dim * 2);
     return 0;

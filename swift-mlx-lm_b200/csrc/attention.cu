@@ -538,6 +538,184 @@ int check_launch(const char* what) {
     return SWLM_OK;
 }
 
+
+// ---- decode attention over an 8-bit group-32 cache --------------------------------------------------------------
+// Rows are (head_dim / 32) blocks of 36 bytes: fp16 scale | fp16 zero | 32 bytes, value = scale * q + zero
+// (read_kv_element, Generator/MetalSourceGenerator+Attention.swift:1923-1956). Half the bytes of the bf16 cache cross
+// HBM. One CTA per (split, KV head, sequence) as in the bf16 kernel; a warp takes one token at a time, every lane
+// dequantises its head_dim / 32 consecutive elements of the K row and of the V row and the dot products of the GQA
+// group's q rows are reduced across the warp; online softmax in fp32. The new token enters with its unrounded rotated k
+// and its v (:866-868, :905-907); split 0 quantises both into the cache (write_kv_quantized_q8, :2057-2101: scale =
+// (max - min) / 255 per group, q = round((x - min) / scale), fp16 scale and min stored). The last CTA of a
+// (sequence, KV head) to arrive merges the splits.
+constexpr int kQ8Warps = 4, kQ8Threads = kQ8Warps * 32;
+
+__device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char* row, int hd, int warp, int lane) {
+    for (int g = warp; g * 32 < hd; g += kQ8Warps) {
+        const float x = src[g * 32 + lane];
+        float lo = x, hi = x;
+        for (int o = 16; o > 0; o >>= 1) { lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o)); hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o)); }
+        float scale = (hi - lo) / 255.0f;
+        if (scale < 1e-10f) scale = 1e-10f;
+        unsigned char* blk = row + (size_t)g * 36;
+        if (lane == 0) {
+            const __half2 hdr = __floats2half2_rn(scale, lo);
+            *reinterpret_cast<__half2*>(blk) = hdr;
+        }
+        const int q = (int)roundf((x - lo) / scale);
+        blk[4 + lane] = (unsigned char)min(max(q, 0), 255);
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnParams p) {
+    constexpr int EPL = HD / 32;           // elements per lane
+    constexpr int ROW_BYTES = HD / 32 * 36;
+    pdl_launch_dependents();
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = p.heads / p.kv_heads;
+    __shared__ float qs[kMaxGroup][HD];
+    __shared__ float kcur[HD], vcur[HD];
+    __shared__ float osm[kQ8Warps][kMaxGroup][HD];
+    __shared__ float msm[kQ8Warps][kMaxGroup], lsm[kQ8Warps][kMaxGroup];
+    __shared__ int is_last;
+    pdl_wait();
+    const int n_ctx = p.position[b];
+    for (int idx = tid; idx < G * HD; idx += kQ8Threads)
+        qs[idx / HD][idx % HD] = __bfloat162float(p.q[(size_t)b * p.q_stride + (size_t)kvh * G * HD + idx]);
+    for (int d = tid; d < HD; d += kQ8Threads) {
+        kcur[d] = __bfloat162float(p.k[(size_t)b * p.k_stride + (size_t)kvh * HD + d]);
+        vcur[d] = __bfloat162float(p.v[(size_t)b * p.v_stride + (size_t)kvh * HD + d]);
+    }
+    __syncthreads();
+    if (p.rope_dim > 0) {
+        // rotate-half RoPE (Generator/MetalSourceGenerator+Attention.swift:596-617): pairs (i, i + rope_dim/2)
+        const int pairs = p.rope_dim >> 1;
+        for (int idx = tid; idx < (G + 1) * pairs; idx += kQ8Threads) {
+            const int r = idx / pairs, i = idx - r * pairs;
+            float sn, cs;
+            sincosf((float)n_ctx * p.inv_freq[i], &sn, &cs);
+            float* row = r < G ? qs[r] : kcur;
+            const float lo = row[i], hi = row[i + pairs];
+            row[i] = lo * cs - hi * sn;
+            row[i + pairs] = lo * sn + hi * cs;
+        }
+        __syncthreads();
+    }
+    const size_t head_bytes = (size_t)p.max_seq * ROW_BYTES;
+    unsigned char* kbase = reinterpret_cast<unsigned char*>(p.kcache) + ((size_t)b * p.kv_heads + kvh) * head_bytes;
+    unsigned char* vbase = reinterpret_cast<unsigned char*>(p.vcache) + ((size_t)b * p.kv_heads + kvh) * head_bytes;
+    if (split == 0 && n_ctx < p.max_seq) {
+        q8_quantise_row(kcur, kbase + (size_t)n_ctx * ROW_BYTES, HD, warp, lane);
+        q8_quantise_row(vcur, vbase + (size_t)n_ctx * ROW_BYTES, HD, warp, lane);
+    }
+    // this lane's elements e0 .. e0 + EPL - 1 lie in one block
+    const int e0 = lane * EPL, blk_off = (e0 / 32) * 36, pay_off = blk_off + 4 + (e0 & 31);
+    float qr[kMaxGroup][EPL];
+#pragma unroll
+    for (int r = 0; r < kMaxGroup; ++r)
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) qr[r][j] = r < G ? qs[r][e0 + j] : 0.f;
+    float m_run[kMaxGroup], l_run[kMaxGroup], acc[kMaxGroup][EPL];
+#pragma unroll
+    for (int r = 0; r < kMaxGroup; ++r) {
+        m_run[r] = -INFINITY; l_run[r] = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) acc[r][j] = 0.f;
+    }
+    auto absorb = [&](const float (&kf)[EPL], const float (&vf)[EPL]) {
+#pragma unroll
+        for (int r = 0; r < kMaxGroup; ++r) {
+            if (r >= G) break;
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) s = fmaf(qr[r][j], kf[j], s);
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            s *= p.scale_log2;
+            const float m_new = fmaxf(m_run[r], s);
+            const float corr = exp2f(m_run[r] - m_new), w = exp2f(s - m_new);
+            l_run[r] = l_run[r] * corr + w;
+            m_run[r] = m_new;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) acc[r][j] = fmaf(w, vf[j], acc[r][j] * corr);
+        }
+    };
+    // the split's share of the cached rows [t_lo, n_ctx): contiguous; a warp takes every fourth row of it
+    const int t_lo = p.window > 0 ? max(0, n_ctx + 1 - p.window) : 0;
+    const int per = (n_ctx - t_lo + p.splits - 1) / p.splits;
+    const int t0 = t_lo + split * per, t1 = min(n_ctx, t0 + per);
+    for (int t = t0 + warp; t < t1; t += kQ8Warps) {
+        const unsigned char* kr = kbase + (size_t)t * ROW_BYTES;
+        const unsigned char* vr = vbase + (size_t)t * ROW_BYTES;
+        const __half2 kh = *reinterpret_cast<const __half2*>(kr + blk_off), vh = *reinterpret_cast<const __half2*>(vr + blk_off);
+        const float ks = __low2float(kh), kz = __high2float(kh), vs = __low2float(vh), vz = __high2float(vh);
+        float kf[EPL], vf[EPL];
+        if (EPL == 4) {
+            const unsigned kw = *reinterpret_cast<const unsigned*>(kr + pay_off), vw = *reinterpret_cast<const unsigned*>(vr + pay_off);
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) { kf[j] = fmaf(ks, (float)((kw >> (8 * j)) & 0xffu), kz); vf[j] = fmaf(vs, (float)((vw >> (8 * j)) & 0xffu), vz); }
+        } else {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) { kf[j] = fmaf(ks, (float)kr[pay_off + j], kz); vf[j] = fmaf(vs, (float)vr[pay_off + j], vz); }
+        }
+        absorb(kf, vf);
+    }
+    if (split == 0 && warp == 0) {   // the new token: unrounded rotated k, v as given
+        float kf[EPL], vf[EPL];
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) { kf[j] = kcur[e0 + j]; vf[j] = vcur[e0 + j]; }
+        absorb(kf, vf);
+    }
+    // ---- merge the warps, publish the split's partial ----------------------------------------------------
+#pragma unroll
+    for (int r = 0; r < kMaxGroup; ++r) {
+        if (r >= G) break;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) osm[warp][r][e0 + j] = acc[r][j];
+        if (lane == 0) { msm[warp][r] = m_run[r]; lsm[warp][r] = l_run[r]; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += kQ8Threads) {
+        const int r = idx / HD, d = idx - r * HD;
+        float mx = -INFINITY;
+        for (int w = 0; w < kQ8Warps; ++w) mx = fmaxf(mx, msm[w][r]);
+        float o = 0.f, l = 0.f;
+        for (int w = 0; w < kQ8Warps; ++w) {
+            const float wgt = msm[w][r] == -INFINITY ? 0.f : exp2f(msm[w][r] - mx);
+            o = fmaf(wgt, osm[w][r][d], o);
+            l = fmaf(wgt, lsm[w][r], l);
+        }
+        const size_t slot = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits + split;
+        __stcg(p.part_o + slot * HD + d, o);
+        if (d == 0) { __stcg(p.part_ml + slot * 2, mx); __stcg(p.part_ml + slot * 2 + 1, l); }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        unsigned* ctr = p.counters + (size_t)b * p.kv_heads + kvh;
+        unsigned prev;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(ctr) : "memory");
+        is_last = prev == (unsigned)p.splits - 1u;
+        if (is_last) *ctr = 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    for (int idx = tid; idx < G * HD; idx += kQ8Threads) {
+        const int r = idx / HD, d = idx - r * HD;
+        const size_t slot0 = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits;
+        float mx = -INFINITY;
+        for (int sidx = 0; sidx < p.splits; ++sidx) mx = fmaxf(mx, __ldcg(p.part_ml + (slot0 + sidx) * 2));
+        float num = 0.f, den = 0.f;
+        for (int sidx = 0; sidx < p.splits; ++sidx) {
+            const float ms = __ldcg(p.part_ml + (slot0 + sidx) * 2);
+            const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - mx);
+            num = fmaf(wgt, __ldcg(p.part_o + (slot0 + sidx) * HD + d), num);
+            den = fmaf(wgt, __ldcg(p.part_ml + (slot0 + sidx) * 2 + 1), den);
+        }
+        p.out[(size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
+}
+
 template <int MODE>
 int launch_both(const AttnParams& p, int m, int hd, cudaStream_t s) {
     const dim3 grid(p.splits, p.kv_heads, m);
@@ -814,6 +992,14 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     p.prefetch = a.prefetch;
     if (a.pos_base < 0 && a.m * a.kv_heads * a.splits + a.m * a.kv_heads <= 512)
         p.trace = qgemv_trace_slot(a.m * a.kv_heads * a.splits, -a.kv_heads * a.m, a.splits, 9, 0);
+    if (a.kv_scheme == SWLM_KV_Q8G32) {
+        if (a.pos_base >= 0) { set_error("attention: prompt chunks over an 8-bit cache are not supported"); return SWLM_ERR_UNSUPPORTED; }
+        const dim3 grid(p.splits, p.kv_heads, a.m);
+        if (a.head_dim == 128) launch_k(attn_q8_split_kernel<128>, grid, dim3(kQ8Threads), 0, s, p);
+        else if (a.head_dim == 64) launch_k(attn_q8_split_kernel<64>, grid, dim3(kQ8Threads), 0, s, p);
+        else { set_error("attention: head_dim %d not supported over an 8-bit cache (64 or 128)", a.head_dim); return SWLM_ERR_UNSUPPORTED; }
+        return check_launch("attention (8-bit cache) launch");
+    }
     if (a.pos_base >= 0) {
         // prompt ingestion: rows of q/k/v are consecutive tokens of sequence 0
         if (a.head_dim > 128) { set_error("attention: head_dim %d not supported", a.head_dim); return SWLM_ERR_UNSUPPORTED; }

@@ -666,6 +666,10 @@ PrefetchTarget prefetch_of(const Launch& L) {
 
 __nv_bfloat16* res_buf(swlm_state* s, int phys) { return phys ? s->res2 : s->buf[SWLM_BUF_RESIDUAL]; }
 
+size_t kv_row_bytes(const swlm_buffers_desc& d) {
+    return d.kv_scheme == SWLM_KV_Q8G32 ? (size_t)d.head_dim / 32 * 36 : (size_t)d.head_dim * 2;
+}
+
 int kv_heads_local(const swlm_plan* p) { return std::max(1, p->desc.kv_heads / std::max(1, p->ctx->tp_size)); }
 
 size_t head_begin_of(const swlm_plan* plan, bool body_only) {
@@ -716,8 +720,8 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             a.prefetch.p[0] = s->kcache + (size_t)at.layer * s->kv_layer_elems;
             a.prefetch.p[1] = s->vcache + (size_t)at.layer * s->kv_layer_elems;
             a.prefetch.heads = kv_heads_local(plan);
-            a.prefetch.row_bytes = at.head_dim * 2;
-            a.prefetch.head_stride = (unsigned long long)d.max_seq * at.head_dim * 2;
+            a.prefetch.row_bytes = (unsigned)kv_row_bytes(d);
+            a.prefetch.head_stride = (unsigned long long)d.max_seq * kv_row_bytes(d);
             a.prefetch.position = s->position;
         }
         return a;
@@ -757,7 +761,7 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             AttnLaunch a;
             a.m = m; a.heads = st.heads / plan->ctx->tp_size; a.kv_heads = kv_heads_local(plan); a.head_dim = st.head_dim;
             a.rope_dim = st.rope_dim; a.inv_freq = L.rope_table >= 0 ? plan->rope_tables[L.rope_table].inv_freq : nullptr;
-            a.scale = st.scale; a.window = st.window_left;
+            a.scale = st.scale; a.window = st.window_left; a.kv_scheme = d.kv_scheme;
             a.q = s->buf[st.in_buf]; a.q_stride = s->width[st.in_buf];
             a.k = s->buf[st.in2_buf]; a.k_stride = s->width[st.in2_buf];
             a.v = s->buf[st.in3_buf]; a.v_stride = s->width[st.in3_buf];
@@ -1055,6 +1059,7 @@ constexpr int kTpChunkRows = 1024;
 
 bool rows_capable(const swlm_plan* plan, bool allow_tp = false) {
     if ((plan->ctx->tp_size != 1 && !allow_tp) || plan->desc.head_dim > 128) return false;
+    if (plan->desc.kv_scheme == SWLM_KV_Q8G32) return false;   // prompts over an 8-bit cache go token by token
     if (plan->ctx->tp_size > 1 && (plan->desc.hidden & 7)) return false;
     for (const swlm_step& st : plan->steps) {
         if (st.kind == SWLM_STEP_QGEMV && st.in_buf == st.out_buf) return false;
@@ -1221,7 +1226,7 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
                 if ((rc = rope_table_for(plan, st.rope_dim, st.rope_base, &ti))) return rc;
                 a.inv_freq = plan->rope_tables[ti].inv_freq;
             }
-            a.scale = st.scale; a.window = st.window_left;
+            a.scale = st.scale; a.window = st.window_left; a.kv_scheme = d.kv_scheme;
             a.q = pf[st.in_buf]; a.q_stride = wd[st.in_buf];
             a.k = pf[st.in2_buf]; a.k_stride = wd[st.in2_buf];
             a.v = pf[st.in3_buf]; a.v_stride = wd[st.in3_buf];
@@ -1459,6 +1464,14 @@ int64_t swlm_weights_bytes(const swlm_ctx* ctx) { return ctx ? ctx->bytes : 0; }
 int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const swlm_buffers_desc* desc, swlm_plan** out) {
     if (!ctx || !steps || n_steps <= 0 || !desc || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
     *out = nullptr;
+    if (desc->kv_scheme != 0 && desc->kv_scheme != SWLM_KV_BF16 && desc->kv_scheme != SWLM_KV_Q8G32) {
+        set_error("KV cache scheme %#x not supported (bf16 or 8-bit group 32)", desc->kv_scheme);
+        return SWLM_ERR_UNSUPPORTED;
+    }
+    if (desc->kv_scheme == SWLM_KV_Q8G32 && desc->kv_layers > 0 && desc->head_dim != 64 && desc->head_dim != 128) {
+        set_error("an 8-bit KV cache needs head_dim 64 or 128");
+        return SWLM_ERR_UNSUPPORTED;
+    }
     if (desc->max_batch < 1 || desc->max_batch > kMaxSequences) { set_error("max_batch %d outside 1..%d", desc->max_batch, kMaxSequences); return SWLM_ERR_INVALID; }
     if (desc->max_batch > kQGemvMaxRows && ctx->tp_size > 1) { set_error("more than %d sequences per step are not supported under tensor parallelism", kQGemvMaxRows); return SWLM_ERR_UNSUPPORTED; }
     if (desc->hidden % 8 || desc->slot_dim % 8 || desc->vocab % 8) { set_error("hidden, slot_dim and vocab must be multiples of 8"); return SWLM_ERR_INVALID; }
@@ -1526,7 +1539,8 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
         s->width[i] = buf_width(d, i);
         if ((rc = dev_alloc(&s->buf[i], (size_t)d.max_batch * s->width[i]))) return fail(rc);
     }
-    s->kv_layer_elems = (size_t)d.max_batch * kv_heads_local(plan) * d.max_seq * d.head_dim;
+    // (counted in 2-byte units whatever the scheme: an 8-bit row of head_dim values is head_dim / 32 blocks of 36 bytes)
+    s->kv_layer_elems = (size_t)d.max_batch * kv_heads_local(plan) * d.max_seq * kv_row_bytes(d) / 2;
     if ((rc = dev_alloc(&s->kcache, (size_t)d.kv_layers * s->kv_layer_elems))) return fail(rc);
     if ((rc = dev_alloc(&s->vcache, (size_t)d.kv_layers * s->kv_layer_elems))) return fail(rc);
     s->conv_layer_elems = (size_t)d.max_batch * d.conv_kernel * d.conv_dim;
@@ -1908,9 +1922,34 @@ static int kv_ptr(swlm_state* s, int which, int layer, int b, int head, int coun
     if (layer < 0 || layer >= d.kv_layers || b < 0 || b >= d.max_batch || head < 0 || head >= kv_heads_local(s->plan) ||
         count < 0 || count > d.max_seq) { set_error("bad KV address"); return SWLM_ERR_INVALID; }
     __nv_bfloat16* base = which ? s->vcache : s->kcache;
-    *p = base + (size_t)layer * s->kv_layer_elems + ((size_t)b * kv_heads_local(s->plan) + head) * d.max_seq * d.head_dim;
+    *p = base + (size_t)layer * s->kv_layer_elems + ((size_t)b * kv_heads_local(s->plan) + head) * d.max_seq * kv_row_bytes(d) / 2;
     return SWLM_OK;
 }
+
+// 8-bit group-32 rows on the host, for the probes: the arithmetic of write_kv_quantized_q8 / read_kv_element
+// (Generator/MetalSourceGenerator+Attention.swift:2057-2101, 1923-1956).
+static void kv_q8_quantise_host(const float* v, int hd, unsigned char* row) {
+    for (int g = 0; g * 32 < hd; ++g) {
+        float lo = v[g * 32], hi = v[g * 32];
+        for (int i = 1; i < 32; ++i) { lo = std::min(lo, v[g * 32 + i]); hi = std::max(hi, v[g * 32 + i]); }
+        float scale = (hi - lo) / 255.0f;
+        if (scale < 1e-10f) scale = 1e-10f;
+        unsigned char* blk = row + (size_t)g * 36;
+        const __half hs = __float2half_rn(scale), hz = __float2half_rn(lo);
+        memcpy(blk, &hs, 2);
+        memcpy(blk + 2, &hz, 2);
+        for (int i = 0; i < 32; ++i) blk[4 + i] = (unsigned char)std::min(255, std::max(0, (int)roundf((v[g * 32 + i] - lo) / scale)));
+    }
+}
+static float kv_q8_read_host(const unsigned char* row, int e) {
+    const unsigned char* blk = row + (size_t)(e / 32) * 36;
+    __half hs, hz;
+    memcpy(&hs, blk, 2);
+    memcpy(&hz, blk + 2, 2);
+    return __half2float(hs) * (float)blk[4 + e % 32] + __half2float(hz);
+}
+static float bf16_bits_to_float(uint16_t h) { const uint32_t u = (uint32_t)h << 16; float f; memcpy(&f, &u, 4); return f; }
+static uint16_t float_to_bf16_bits(float f) { uint32_t u; memcpy(&u, &f, 4); u += 0x7FFFu + ((u >> 16) & 1u); return (uint16_t)(u >> 16); }
 
 int swlm_read_kv(swlm_state* s, int which, int layer, int b, int head, int count, uint16_t* dst) {
     if (!s || !dst) { set_error("null argument"); return SWLM_ERR_INVALID; }
@@ -1918,6 +1957,15 @@ int swlm_read_kv(swlm_state* s, int which, int layer, int b, int head, int count
     int rc = kv_ptr(s, which, layer, b, head, count, &p);
     if (rc) return rc;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (d.kv_scheme == SWLM_KV_Q8G32) {   // the dequantised rows, rounded to bf16
+        std::vector<unsigned char> rows((size_t)count * kv_row_bytes(d));
+        SWLM_CUDA(cudaMemcpy(rows.data(), p, rows.size(), cudaMemcpyDeviceToHost));
+        for (int t = 0; t < count; ++t)
+            for (int e = 0; e < d.head_dim; ++e)
+                dst[(size_t)t * d.head_dim + e] = float_to_bf16_bits(kv_q8_read_host(rows.data() + (size_t)t * kv_row_bytes(d), e));
+        return SWLM_OK;
+    }
     SWLM_CUDA(cudaMemcpy(dst, p, (size_t)count * s->plan->desc.head_dim * 2, cudaMemcpyDeviceToHost));
     return SWLM_OK;
 }
@@ -1928,6 +1976,17 @@ int swlm_write_kv(swlm_state* s, int which, int layer, int b, int head, int coun
     int rc = kv_ptr(s, which, layer, b, head, count, &p);
     if (rc) return rc;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (d.kv_scheme == SWLM_KV_Q8G32) {   // quantised as an appended row would be
+        std::vector<unsigned char> rows((size_t)count * kv_row_bytes(d));
+        std::vector<float> f(d.head_dim);
+        for (int t = 0; t < count; ++t) {
+            for (int e = 0; e < d.head_dim; ++e) f[e] = bf16_bits_to_float(src[(size_t)t * d.head_dim + e]);
+            kv_q8_quantise_host(f.data(), d.head_dim, rows.data() + (size_t)t * kv_row_bytes(d));
+        }
+        SWLM_CUDA(cudaMemcpy(p, rows.data(), rows.size(), cudaMemcpyHostToDevice));
+        return SWLM_OK;
+    }
     SWLM_CUDA(cudaMemcpy(p, src, (size_t)count * s->plan->desc.head_dim * 2, cudaMemcpyHostToDevice));
     return SWLM_OK;
 }

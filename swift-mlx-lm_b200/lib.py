@@ -70,6 +70,7 @@ class BuffersDesc(C.Structure):
         ("ssm_key_dim", C.c_int32),
         ("ssm_value_dim", C.c_int32),
         ("ssm_conv_kernel", C.c_int32),
+        ("kv_scheme", C.c_int32),
     ]
 
 

@@ -68,6 +68,8 @@ class ModelConfig:
     # (Sources/LMArchitecture/Declaration/Components/DeltaNet.swift, Primitives/SSMRecurrenceFragment.swift) with
     # `ssm_heads` value heads of `ssm_value_dim`, `ssm_groups` key groups of `ssm_key_dim`, a causal conv of
     # `ssm_conv_kernel` taps over the q|k|v channels; tensor names follow Models/Qwen35/Qwen35FamilyNaming.swift:73-87.
+    # KV cache elements: 0 = bf16; 0x10 = 8-bit groups of 32 (36-byte blocks, KVCacheSpecification's Q8 group-32 scheme)
+    kv_scheme: int = 0
     ssm_heads: int = 0
     ssm_groups: int = 0
     ssm_key_dim: int = 0
@@ -112,6 +114,7 @@ class ModelConfig:
             ssm_groups=self.ssm_groups if self.ssm_layer_count else 0, ssm_key_dim=self.ssm_key_dim if self.ssm_layer_count else 0,
             ssm_value_dim=self.ssm_value_dim if self.ssm_layer_count else 0,
             ssm_conv_kernel=self.ssm_conv_kernel if self.ssm_layer_count else 0,
+            kv_scheme=self.kv_scheme,
         )
 
     # Algorithmic weight bytes one decode step streams: 0.5625 bytes per quantized weight.

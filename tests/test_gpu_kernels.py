@@ -504,3 +504,54 @@ def test_ssm_recurrence_matches_oracle_over_steps(pkg, store, oracle, heads, gro
     gm.reset_sequence(0)
     assert not gm.read_ssm_state(0, 0).any()
     gm.close()
+
+
+# ---- 8-bit KV cache ----------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("hd,heads,kvh", [(128, 32, 8), (64, 16, 4), (128, 8, 8)])
+@pytest.mark.parametrize("batch,ctx,window", [(1, 0, 0), (1, 1, 0), (1, 63, 0), (1, 65, 0), (1, 1000, 0), (1, 4095, 0), (3, 300, 0), (1, 900, 100)])
+def test_attention_decode_over_q8_group32_cache(pkg, store, oracle, hd, heads, kvh, batch, ctx, window):
+    """KV rows as 36-byte blocks of 32 8-bit values: the cache is filled through the probe (quantised on the host by
+    both sides with the reference's rule, so both start from the same bytes), one decode step appends the new token's
+    row and attends; output and the appended (dequantised) rows against the oracle."""
+    P = pkg.plan
+    max_seq = 4096
+    desc = pkg.BuffersDesc(hidden=256, slot_dim=heads * hd, vocab=512, max_seq=max_seq, max_batch=batch, kv_layers=1, kv_heads=kvh,
+                           head_dim=hd, conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=0x10)
+    table = _bf(pkg, np.zeros((512, 256)))
+    store.add_dense("q8.embed", table)
+    gm = pkg.InferenceModel(store, [P._step(P.STEP_EMBED, out_buf=0, n=256, weight="q8.embed")], desc)
+    om = oracle.model(desc)
+    rng = np.random.default_rng(ctx * 3 + hd + batch)
+    if ctx:
+        for b in range(batch):
+            for h in range(kvh):
+                kr, vr = _bf(pkg, rng.normal(size=(ctx, hd))), _bf(pkg, rng.normal(size=(ctx, hd)))
+                for mdl in (gm, om):
+                    mdl.write_kv(0, 0, b, h, kr)
+                    mdl.write_kv(1, 0, b, h, vr)
+        assert np.array_equal(gm.read_kv(0, 0, 0, 0, ctx), om.read_kv(0, 0, 0, 0, ctx))   # same bytes, same dequantisation
+    q = _bf(pkg, rng.normal(size=(batch, heads * hd)))
+    k = _bf(pkg, np.pad(rng.normal(size=(batch, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+    v = _bf(pkg, np.pad(rng.normal(size=(batch, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+    step = P._step(P.STEP_ATTN_DECODE, layer=0, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, in3_buf=P.BUF_S3, out_buf=P.BUF_S0,
+                   heads=heads, kv_heads=kvh, head_dim=hd, rope_dim=hd, rope_base=500000.0, scale=1.0 / np.sqrt(hd), window_left=window)
+    for mdl in (gm, om):
+        mdl.set_position(ctx)
+        mdl.write_buffer(P.BUF_S1, q)
+        mdl.write_buffer(P.BUF_S2, k)
+        mdl.write_buffer(P.BUF_S3, v)
+        mdl.run_step(step)
+    got = pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, heads * hd))
+    ref = pkg.bf16_to_f32(om.read_buffer(P.BUF_S0, heads * hd))
+    assert rel_err(got, ref).max() <= RTOL
+    for b in range(batch):
+        for h in range(kvh):
+            for which in (0, 1):
+                g = pkg.bf16_to_f32(gm.read_kv(which, 0, b, h, ctx + 1)[ctx])
+                o = pkg.bf16_to_f32(om.read_kv(which, 0, b, h, ctx + 1)[ctx])
+                # the same row quantised on the device and by the oracle: at most one 8-bit step apart (RoPE in fp32 may
+                # differ in the last bit, which can move a value across a rounding boundary)
+                step_size = (o.reshape(-1, 32).max(-1) - o.reshape(-1, 32).min(-1)) / 255.0
+                assert np.all(np.abs(g - o).reshape(-1, 32).max(-1) <= 1.5 * step_size + 2.0 ** -7 * np.abs(o).max())
+    gm.close()

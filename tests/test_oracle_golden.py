@@ -129,6 +129,41 @@ def test_attention_sliding_window_against_fp64_softmax(pkg, oracle, window):
             assert np.max(np.abs(out[h] - w @ vals)) < 2e-2
 
 
+def test_attention_over_q8_group32_cache_against_fp64(pkg, oracle):
+    """8-bit KV rows (36-byte blocks of 32 values, Generator/MetalSourceGenerator+Attention.swift:1923-1956, 2057-2101):
+    the rows the oracle appends dequantise to within half a quantisation step of what was written, and attention over
+    them equals an fp64 softmax over the DEQUANTISED rows plus the current token's unrounded k and v."""
+    H, KV, D, T = 4, 2, 64, 10
+    rng = np.random.default_rng(5)
+    bf = lambda a: pkg.bf16_to_f32(pkg.f32_to_bf16(np.asarray(a, dtype=np.float32)))
+    q, k, v = bf(rng.normal(size=(T, H * D))), bf(rng.normal(size=(T, KV * D))), bf(rng.normal(size=(T, KV * D)))
+    desc = pkg.BuffersDesc(hidden=H * D, slot_dim=H * D, vocab=8, max_seq=16, max_batch=1, kv_layers=1, kv_heads=KV, head_dim=D,
+                           conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=0x10)
+    m = oracle.model(desc)
+    step = pkg.plan._step(pkg.plan.STEP_ATTN_DECODE, layer=0, in_buf=3, in2_buf=4, in3_buf=5, out_buf=2, heads=H, kv_heads=KV,
+                          head_dim=D, rope_dim=0, rope_base=0.0, scale=1.0 / np.sqrt(D))
+    for t in range(T):
+        m.set_position(t)
+        m.write_buffer(3, pkg.f32_to_bf16(q[t]))
+        m.write_buffer(4, pkg.f32_to_bf16(np.pad(k[t], (0, (H - KV) * D))))
+        m.write_buffer(5, pkg.f32_to_bf16(np.pad(v[t], (0, (H - KV) * D))))
+        m.run_step(step)
+        out = pkg.bf16_to_f32(m.read_buffer(2, H * D))[0].reshape(H, D)
+        for h in range(H):
+            kh = h * KV // H
+            keys = np.concatenate([pkg.bf16_to_f32(m.read_kv(0, 0, 0, kh, t)).reshape(t, D), k[t].reshape(KV, D)[kh][None]]).astype(np.float64)
+            vals = np.concatenate([pkg.bf16_to_f32(m.read_kv(1, 0, 0, kh, t)).reshape(t, D), v[t].reshape(KV, D)[kh][None]]).astype(np.float64)
+            sc = keys @ q[t].reshape(H, D)[h].astype(np.float64) / np.sqrt(D)
+            w = np.exp(sc - sc.max()); w /= w.sum()
+            assert np.max(np.abs(out[h] - w @ vals)) < 2e-2
+    # appended rows: within half a step (range / 255 per group of 32) of the inputs, plus the bf16 rounding of the probe
+    for h in range(KV):
+        got = pkg.bf16_to_f32(m.read_kv(0, 0, 0, h, T)).reshape(T, D)
+        want = k.reshape(T, KV, D)[:, h]
+        step_size = (want.reshape(T, D // 32, 32).max(-1) - want.reshape(T, D // 32, 32).min(-1)) / 255.0
+        assert np.all(np.abs(got - want).reshape(T, D // 32, 32).max(-1) <= 0.51 * step_size + 2.0 ** -7 * np.abs(want).max())
+
+
 def ssm_case(pkg, heads=4, groups=2, dk=16, dv=16, K=4, batch=1, seed=1):
     """Random inputs and weights of one recurrent layer (bf16-exact where the reference reads bf16)."""
     rng = np.random.default_rng(seed)
