@@ -12,6 +12,7 @@ With --impl reference the CPU oracle (a scalar restatement of the reference's ar
 Metal kernels cannot run here) decodes a bounded sample of the same workload on the host cores.
 """
 import argparse
+import dataclasses
 import json
 import os
 import subprocess
@@ -118,13 +119,15 @@ def shape_name(args):
 
 
 def metric_name(args):
-    if args.model == "llama" and args.batch == 1:
+    if args.model == "llama" and args.batch == 1 and getattr(args, "kv", "bf16") == "bf16":
         return METRIC
-    return f"4-bit decode tok/s, {'LFM2-1.2B-like' if args.model == 'lfm2' else 'Llama-3-8B'} shape bs{args.batch}"
+    return f"4-bit decode tok/s, {'LFM2-1.2B-like' if args.model == 'lfm2' else 'Llama-3-8B'} shape bs{args.batch}" + (
+        ", 8-bit KV" if getattr(args, "kv", "bf16") == "q8" else "")
 
 
 def workload_name(args):
-    return shape_name(args) + f", 4-bit g64 weights, batch {args.batch}, greedy decode at context {args.ctx}"
+    kv = ", 8-bit group-32 KV cache" if getattr(args, "kv", "bf16") == "q8" else ""
+    return shape_name(args) + f", 4-bit g64 weights, batch {args.batch}, greedy decode at context {args.ctx}" + kv
 
 
 def cpu_baseline(pkg, builder, weights, cfg, sample_steps, ctx):
@@ -317,6 +320,7 @@ def main():
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--model", choices=["llama", "lfm2"], default="llama", help="llama: Llama-3-8B shape; lfm2: the hybrid conv/attention shape")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (1..64), all at the same position")
+    ap.add_argument("--kv", choices=["bf16", "q8"], default="bf16", help="KV cache elements: bf16, or 8-bit groups of 32 (36-byte blocks)")
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -349,6 +353,10 @@ def main():
     warm = max(3, args.warmup)
     max_seq = args.ctx + 2 * (warm + args.steps) + 64 + 8 * 64   # + room for the clock sampler's extra warm-up bursts
     cfg = model_config(pkg, args, max_seq, world)
+    if args.kv == "q8":
+        cfg = dataclasses.replace(cfg, kv_scheme=0x10)
+        if args.prefill == "real":
+            args.prefill = "synthetic"   # prompts over an 8-bit cache go token by token; the timed region is the decode
     builder = pkg.DispatchPlanBuilder(cfg)
     weights = pkg.synth_model_weights(builder, seed=3)
     store = pkg.WeightStore(local_rank, tp_rank=rank, tp_size=world)
@@ -466,7 +474,8 @@ def main():
         attn_ms = a0.elapsed_time(a1) / reps
 
     weight_bytes = cfg.q4_weight_elems() * 0.5625 / world            # per GPU, per step
-    kv_bytes = args.batch * cfg.kv_layer_count * (cfg.kv_heads // world) * cfg.head_dim * 2 * 2 * model.position
+    kv_row_bytes = cfg.head_dim // 32 * 36 if args.kv == "q8" else cfg.head_dim * 2
+    kv_bytes = args.batch * cfg.kv_layer_count * (cfg.kv_heads // world) * kv_row_bytes * 2 * model.position
     n_gemv = sum(1 for l in model.describe().splitlines() if "qgemv" in l)
     kernel_name = "qgemv1_kernel" if args.batch == 1 else "qgemv_kernel"
     kernel_scope = "all %d launches of one decode step, timed back to back" % n_gemv
@@ -484,7 +493,7 @@ def main():
         # an estimate carried over from that capture, not a counter read in this run
         "traffic": weight_bytes / n_gemv * NCU_TRAFFIC_RATIO,
         "traffic_source": "estimate: ncu capture of the four product shapes of one layer, ratio %.4f to algorithmic bytes" % NCU_TRAFFIC_RATIO,
-        "attention": {"kernel": "attn_split_kernel", "bytes_per_step": kv_bytes,
+        "attention": {"kernel": "attn_q8_split_kernel" if args.kv == "q8" else "attn_split_kernel", "bytes_per_step": kv_bytes,
                       "achieved": kv_bytes / (attn_ms * 1e-3) / 1e9, "unit": "GB/s"},
         "whole_step": {"weight_bytes": weight_bytes, "weight_GBs": weight_bytes / (ms / args.steps * 1e-3) / 1e9,
                        "weight_plus_kv_GBs": (weight_bytes + kv_bytes) / (ms / args.steps * 1e-3) / 1e9,

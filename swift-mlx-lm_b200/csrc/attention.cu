@@ -548,7 +548,7 @@ int check_launch(const char* what) {
 // and its v (:866-868, :905-907); split 0 quantises both into the cache (write_kv_quantized_q8, :2057-2101: scale =
 // (max - min) / 255 per group, q = round((x - min) / scale), fp16 scale and min stored). The last CTA of a
 // (sequence, KV head) to arrive merges the splits.
-constexpr int kQ8Warps = 4, kQ8Threads = kQ8Warps * 32;
+constexpr int kQ8Warps = 8, kQ8Threads = kQ8Warps * 32;
 
 __device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char* row, int hd, int warp, int lane) {
     for (int g = warp; g * 32 < hd; g += kQ8Warps) {
@@ -567,17 +567,18 @@ __device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char*
     }
 }
 
-template <int HD>
+// G (query heads per KV head) is a template argument: the per-head dot products, warp reductions and softmax updates of
+// a row are then one basic block whose four or eight independent chains the compiler interleaves.
+template <int HD, int G>
 __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnParams p) {
     constexpr int EPL = HD / 32;           // elements per lane
     constexpr int ROW_BYTES = HD / 32 * 36;
     pdl_launch_dependents();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int G = p.heads / p.kv_heads;
-    __shared__ float qs[kMaxGroup][HD];
+    __shared__ float qs[G][HD];
     __shared__ float kcur[HD], vcur[HD];
-    __shared__ float osm[kQ8Warps][kMaxGroup][HD];
+    __shared__ float osm[kQ8Warps][kMaxGroup][HD];   // (sized for the merge scratch below whatever G is)
     __shared__ float msm[kQ8Warps][kMaxGroup], lsm[kQ8Warps][kMaxGroup];
     __shared__ int is_last;
     pdl_wait();
@@ -612,27 +613,23 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
     }
     // this lane's elements e0 .. e0 + EPL - 1 lie in one block
     const int e0 = lane * EPL, blk_off = (e0 / 32) * 36, pay_off = blk_off + 4 + (e0 & 31);
-    float qr[kMaxGroup][EPL];
+    float qr[G][EPL];
 #pragma unroll
-    for (int r = 0; r < kMaxGroup; ++r)
+    for (int r = 0; r < G; ++r)
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) qr[r][j] = r < G ? qs[r][e0 + j] : 0.f;
-    float m_run[kMaxGroup], l_run[kMaxGroup], acc[kMaxGroup][EPL];
+        for (int j = 0; j < EPL; ++j) qr[r][j] = qs[r][e0 + j];
+    float m_run[G], l_run[G], acc[G][EPL];
 #pragma unroll
-    for (int r = 0; r < kMaxGroup; ++r) {
+    for (int r = 0; r < G; ++r) {
         m_run[r] = -INFINITY; l_run[r] = 0.f;
 #pragma unroll
         for (int j = 0; j < EPL; ++j) acc[r][j] = 0.f;
     }
-    auto absorb = [&](const float (&kf)[EPL], const float (&vf)[EPL]) {
+    // one row's scores (already reduced over the warp, unscaled) and values enter the running softmax of every head
+    auto update = [&](const float (&sc)[G], const float (&vf)[EPL]) {
 #pragma unroll
-        for (int r = 0; r < kMaxGroup; ++r) {
-            if (r >= G) break;
-            float s = 0.f;
-#pragma unroll
-            for (int j = 0; j < EPL; ++j) s = fmaf(qr[r][j], kf[j], s);
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            s *= p.scale_log2;
+        for (int r = 0; r < G; ++r) {
+            const float s = sc[r] * p.scale_log2;
             const float m_new = fmaxf(m_run[r], s);
             const float corr = exp2f(m_run[r] - m_new), w = exp2f(s - m_new);
             l_run[r] = l_run[r] * corr + w;
@@ -645,32 +642,96 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
     const int t_lo = p.window > 0 ? max(0, n_ctx + 1 - p.window) : 0;
     const int per = (n_ctx - t_lo + p.splits - 1) / p.splits;
     const int t0 = t_lo + split * per, t1 = min(n_ctx, t0 + per);
-    for (int t = t0 + warp; t < t1; t += kQ8Warps) {
-        const unsigned char* kr = kbase + (size_t)t * ROW_BYTES;
-        const unsigned char* vr = vbase + (size_t)t * ROW_BYTES;
-        const __half2 kh = *reinterpret_cast<const __half2*>(kr + blk_off), vh = *reinterpret_cast<const __half2*>(vr + blk_off);
-        const float ks = __low2float(kh), kz = __high2float(kh), vs = __low2float(vh), vz = __high2float(vh);
-        float kf[EPL], vf[EPL];
-        if (EPL == 4) {
-            const unsigned kw = *reinterpret_cast<const unsigned*>(kr + pay_off), vw = *reinterpret_cast<const unsigned*>(vr + pay_off);
+    // eight rows per warp are requested before the first is used: one trip to memory per eight rows instead of one per row
+    constexpr int UN = 8;
+    for (int tb = t0 + warp; tb < t1; tb += kQ8Warps * UN) {
+        unsigned kw[UN], vw[UN], khd[UN], vhd[UN];
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) { kf[j] = fmaf(ks, (float)((kw >> (8 * j)) & 0xffu), kz); vf[j] = fmaf(vs, (float)((vw >> (8 * j)) & 0xffu), vz); }
-        } else {
-#pragma unroll
-            for (int j = 0; j < EPL; ++j) { kf[j] = fmaf(ks, (float)kr[pay_off + j], kz); vf[j] = fmaf(vs, (float)vr[pay_off + j], vz); }
+        for (int u = 0; u < UN; ++u) {
+            const int t = min(tb + u * kQ8Warps, t1 - 1);   // rows past the end repeat the last one and are not absorbed
+            const unsigned char* kr = kbase + (size_t)t * ROW_BYTES;
+            const unsigned char* vr = vbase + (size_t)t * ROW_BYTES;
+            khd[u] = __ldg(reinterpret_cast<const unsigned*>(kr + blk_off));
+            vhd[u] = __ldg(reinterpret_cast<const unsigned*>(vr + blk_off));
+            if (EPL == 4) {
+                kw[u] = __ldg(reinterpret_cast<const unsigned*>(kr + pay_off));
+                vw[u] = __ldg(reinterpret_cast<const unsigned*>(vr + pay_off));
+            } else {
+                kw[u] = __ldg(reinterpret_cast<const unsigned short*>(kr + pay_off));
+                vw[u] = __ldg(reinterpret_cast<const unsigned short*>(vr + pay_off));
+            }
         }
-        absorb(kf, vf);
+        // the scores of the eight rows for all heads: 8 x G independent dot products and warp reductions, interleaved
+        float sc[UN][G];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const __half2 kh = *reinterpret_cast<const __half2*>(&khd[u]);
+            const float ks = __low2float(kh), kz = __high2float(kh);
+            float kf[EPL];
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) kf[j] = fmaf(ks, (float)((kw[u] >> (8 * j)) & 0xffu), kz);
+#pragma unroll
+            for (int r = 0; r < G; ++r) {
+                sc[u][r] = 0.f;
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) sc[u][r] = fmaf(qr[r][j], kf[j], sc[u][r]);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < UN; ++u)
+#pragma unroll
+                for (int r = 0; r < G; ++r) sc[u][r] += __shfl_xor_sync(0xffffffffu, sc[u][r], o);
+        // the eight rows enter the running softmax together: one new maximum and one rescale per head for the lot
+        // (rows past the end carry the score -inf, i.e. weight 0)
+        float vfu[UN][EPL];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const __half2 vh = *reinterpret_cast<const __half2*>(&vhd[u]);
+            const float vs = __low2float(vh), vz = __high2float(vh);
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) vfu[u][j] = fmaf(vs, (float)((vw[u] >> (8 * j)) & 0xffu), vz);
+        }
+#pragma unroll
+        for (int r = 0; r < G; ++r) {
+            float m_new = m_run[r];
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                sc[u][r] = tb + u * kQ8Warps < t1 ? sc[u][r] * p.scale_log2 : -INFINITY;
+                m_new = fmaxf(m_new, sc[u][r]);
+            }
+            const float corr = exp2f(m_run[r] - m_new);   // m_new is finite: the batch's first row is inside the range
+            float wsum = 0.f;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) acc[r][j] *= corr;
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const float w = exp2f(sc[u][r] - m_new);
+                wsum += w;
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) acc[r][j] = fmaf(w, vfu[u][j], acc[r][j]);
+            }
+            l_run[r] = l_run[r] * corr + wsum;
+            m_run[r] = m_new;
+        }
     }
     if (split == 0 && warp == 0) {   // the new token: unrounded rotated k, v as given
-        float kf[EPL], vf[EPL];
+        float vf[EPL], sc[G];
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) { kf[j] = kcur[e0 + j]; vf[j] = vcur[e0 + j]; }
-        absorb(kf, vf);
+        for (int j = 0; j < EPL; ++j) vf[j] = vcur[e0 + j];
+#pragma unroll
+        for (int r = 0; r < G; ++r) {
+            sc[r] = 0.f;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) sc[r] = fmaf(qr[r][j], kcur[e0 + j], sc[r]);
+            for (int o = 16; o > 0; o >>= 1) sc[r] += __shfl_xor_sync(0xffffffffu, sc[r], o);
+        }
+        update(sc, vf);
     }
     // ---- merge the warps, publish the split's partial ----------------------------------------------------
 #pragma unroll
-    for (int r = 0; r < kMaxGroup; ++r) {
-        if (r >= G) break;
+    for (int r = 0; r < G; ++r) {
 #pragma unroll
         for (int j = 0; j < EPL; ++j) osm[warp][r][e0 + j] = acc[r][j];
         if (lane == 0) { msm[warp][r] = m_run[r]; lsm[warp][r] = l_run[r]; }
@@ -700,19 +761,49 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
     }
     __syncthreads();
     if (!is_last) return;
-    for (int idx = tid; idx < G * HD; idx += kQ8Threads) {
-        const int r = idx / HD, d = idx - r * HD;
-        const size_t slot0 = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits;
+    // the merge: all (max, sum) pairs travel together, then every thread adds up one float4 of one head's output over
+    // the splits with the loads of eight splits in flight at a time (rolled loops of dependent L2 round trips made this
+    // the longest part of the kernel)
+    float* wsm = &osm[0][0][0];              // [G][splits] weights (splits <= 64)
+    float* lsm2 = &osm[1][0][0];             // [G][splits] sums
+    __shared__ float inv_den[kMaxGroup];
+    for (int idx = tid; idx < G * p.splits; idx += kQ8Threads) {
+        const int r = idx / p.splits, sidx = idx - r * p.splits;
+        const size_t slot = ((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits + sidx;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + slot * 2));
+        wsm[idx] = ml.x; lsm2[idx] = ml.y;
+    }
+    __syncthreads();
+    for (int r = warp; r < G; r += kQ8Warps) {
         float mx = -INFINITY;
-        for (int sidx = 0; sidx < p.splits; ++sidx) mx = fmaxf(mx, __ldcg(p.part_ml + (slot0 + sidx) * 2));
-        float num = 0.f, den = 0.f;
-        for (int sidx = 0; sidx < p.splits; ++sidx) {
-            const float ms = __ldcg(p.part_ml + (slot0 + sidx) * 2);
-            const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - mx);
-            num = fmaf(wgt, __ldcg(p.part_o + (slot0 + sidx) * HD + d), num);
-            den = fmaf(wgt, __ldcg(p.part_ml + (slot0 + sidx) * 2 + 1), den);
+        for (int sidx = lane; sidx < p.splits; sidx += 32) mx = fmaxf(mx, wsm[r * p.splits + sidx]);
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float den = 0.f;
+        for (int sidx = lane; sidx < p.splits; sidx += 32) {
+            const float ms = wsm[r * p.splits + sidx];
+            const float w = ms == -INFINITY ? 0.f : exp2f(ms - mx);
+            wsm[r * p.splits + sidx] = w;
+            den = fmaf(w, lsm2[r * p.splits + sidx], den);
         }
-        p.out[(size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        if (lane == 0) inv_den[r] = den > 0.f ? 1.0f / den : 0.f;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD / 4; idx += kQ8Threads) {
+        const int r = idx / (HD / 4), d4 = idx - r * (HD / 4);
+        const float* po = p.part_o + (((size_t)b * p.heads + (size_t)kvh * G + r) * p.splits) * HD + d4 * 4;
+        const float* wr = wsm + r * p.splits;
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int sidx = 0; sidx < p.splits; ++sidx) {
+            const float4 v4 = __ldcg(reinterpret_cast<const float4*>(po + (size_t)sidx * HD));
+            const float w = wr[sidx];
+            num.x = fmaf(w, v4.x, num.x); num.y = fmaf(w, v4.y, num.y); num.z = fmaf(w, v4.z, num.z); num.w = fmaf(w, v4.w, num.w);
+        }
+        const float inv = inv_den[r];
+        __nv_bfloat16* o = p.out + (size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d4 * 4;
+        o[0] = __float2bfloat16_rn(num.x * inv); o[1] = __float2bfloat16_rn(num.y * inv);
+        o[2] = __float2bfloat16_rn(num.z * inv); o[3] = __float2bfloat16_rn(num.w * inv);
     }
 }
 
@@ -995,9 +1086,13 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     if (a.kv_scheme == SWLM_KV_Q8G32) {
         if (a.pos_base >= 0) { set_error("attention: prompt chunks over an 8-bit cache are not supported"); return SWLM_ERR_UNSUPPORTED; }
         const dim3 grid(p.splits, p.kv_heads, a.m);
-        if (a.head_dim == 128) launch_k(attn_q8_split_kernel<128>, grid, dim3(kQ8Threads), 0, s, p);
-        else if (a.head_dim == 64) launch_k(attn_q8_split_kernel<64>, grid, dim3(kQ8Threads), 0, s, p);
-        else { set_error("attention: head_dim %d not supported over an 8-bit cache (64 or 128)", a.head_dim); return SWLM_ERR_UNSUPPORTED; }
+        const int G = a.heads / a.kv_heads;
+        if (a.head_dim != 64 && a.head_dim != 128) { set_error("attention: head_dim %d not supported over an 8-bit cache (64 or 128)", a.head_dim); return SWLM_ERR_UNSUPPORTED; }
+        if (G != 1 && G != 2 && G != 4 && G != 8) { set_error("attention over an 8-bit cache: %d query heads per KV head (1, 2, 4 or 8)", G); return SWLM_ERR_UNSUPPORTED; }
+#define SWLM_Q8_CASE(HDV, GV) if (a.head_dim == HDV && G == GV) launch_k(attn_q8_split_kernel<HDV, GV>, grid, dim3(kQ8Threads), 0, s, p)
+        SWLM_Q8_CASE(128, 1); SWLM_Q8_CASE(128, 2); SWLM_Q8_CASE(128, 4); SWLM_Q8_CASE(128, 8);
+        SWLM_Q8_CASE(64, 1); SWLM_Q8_CASE(64, 2); SWLM_Q8_CASE(64, 4); SWLM_Q8_CASE(64, 8);
+#undef SWLM_Q8_CASE
         return check_launch("attention (8-bit cache) launch");
     }
     if (a.pos_base >= 0) {
