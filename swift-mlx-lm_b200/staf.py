@@ -25,7 +25,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
 import numpy as np
 
-from .formats import f32_to_bf16, repack_mlx_to_staf
+from .formats import bf16_to_f32, f32_to_bf16, repack_mlx_to_staf
 
 MAGIC = 0x46415453                # "STAF", little-endian (STAFFormat.swift:13)
 FORMAT_VERSION = 2                # STAFFormat.swift:27
@@ -391,6 +391,13 @@ def plan_conversion(tensors: Dict[str, Tuple[str, Tuple[int, ...], np.ndarray]],
                                      tuple(shape), blocks.tobytes(), block_size=group_size, group_size=group_size,
                                      shard_index=shard_index))
             continue
+        if name.endswith(".linear_attn.norm.weight") and dtype in ("BF16", "F16"):
+            # the recurrent layers' norm weight is read as fp32 by the kernel: promoted whatever the bundle stores
+            # (STAFConversionPlanner.swift:117-127, isSSMNormWeight :138-140)
+            f = bf16_to_f32(np.asarray(arr)) if dtype == "BF16" else np.asarray(arr).view(np.float16).astype(np.float32)
+            out.append(TensorToWrite(name, SCHEME_FP32, semantic_role(name), _ST_DTYPES["F32"][1], tuple(shape),
+                                     np.ascontiguousarray(f, dtype=np.float32).tobytes(), shard_index=shard_index))
+            continue
         scheme = {"F16": SCHEME_FP16, "BF16": SCHEME_BF16, "F32": SCHEME_FP32}.get(dtype, SCHEME_PASSTHROUGH)
         out.append(TensorToWrite(name, scheme, semantic_role(name), _ST_DTYPES[dtype][1], tuple(shape),
                                  np.ascontiguousarray(arr).tobytes(), shard_index=shard_index))
@@ -437,6 +444,8 @@ def load_into_store(store, staf: STAFFile, shard_kinds: Optional[Dict[str, int]]
                 store.add_q4_staf(e.name, raw.reshape(n, k // 64, 36), n, k, shard_kinds.get(e.name, 0))
             else:
                 store.add_q4_staf(e.name, raw.reshape(n, k // 128, 68), n, k, shard_kinds.get(e.name, 0), group=128)
+        elif e.scheme == SCHEME_FP32 and (e.name.endswith(".linear_attn.norm.weight") or e.name.endswith(".A_log")) and hasattr(store, "add_dense_f32"):
+            store.add_dense_f32(e.name, raw.view(np.float32))    # what the recurrent step reads as fp32 stays fp32
         elif e.scheme in (SCHEME_BF16, SCHEME_FP16, SCHEME_FP32, SCHEME_PASSTHROUGH):
             if e.scheme == SCHEME_BF16:
                 arr = raw.view(np.uint16)

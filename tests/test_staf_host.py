@@ -202,3 +202,44 @@ def test_load_into_store_routes_by_scheme(pkg, staf, golden, tmp_path):
     norm, _ = rec.dense["model.norm.weight"]
     assert norm.shape == (1, 64)
     assert f["model.layers.0.conv.conv.weight"].shard_index == 0 and f[loaded[0]].shard_index in (0, 1)
+
+
+def test_recurrent_layer_tensors_keep_fp32(pkg, staf, tmp_path):
+    """A bundle of the hybrid recurrent recipe: `linear_attn.norm.weight` is promoted to an fp32 section even when the
+    bundle stores it as bf16 (STAFConversionPlanner.swift:117-140), `A_log` stays fp32, and both reach the weight store
+    through the fp32 entry point; the quantized projections of the layer become 36-byte blocks like any other."""
+    cfg = pkg.ModelConfig("deltanet", hidden=128, intermediate=256, layers=2, heads=4, kv_heads=2, head_dim=32, vocab=256,
+                          attention_layers=[1], max_seq=16, ssm_heads=4, ssm_groups=2, ssm_key_dim=32, ssm_value_dim=32, ssm_conv_kernel=4)
+    builder = pkg.DispatchPlanBuilder(cfg)
+    weights = pkg.synth_model_weights(builder, seed=2)
+    tensors = pkg.bundle_tensors(builder, weights)
+    norm = "model.layers.0.linear_attn.norm.weight"
+    tensors[norm] = ("BF16", pkg.f32_to_bf16(weights[norm]))          # as an MLX bundle would carry it
+    src = os.path.join(tmp_path, "model.safetensors")
+    staf.write_safetensors(src, tensors)
+    out = os.path.join(tmp_path, "model.staf")
+    assert staf.convert_safetensors([src], out)
+    f = staf.read_staf(out)
+    assert f[norm].scheme == staf.SCHEME_FP32 and f[norm].payload_size == 4 * cfg.ssm_value_dim
+    assert np.array_equal(np.asarray(f.payload(norm)).view(np.float32), pkg.bf16_to_f32(pkg.f32_to_bf16(weights[norm])))
+    assert f["model.layers.0.linear_attn.A_log"].scheme == staf.SCHEME_FP32
+    assert f["model.layers.0.linear_attn.in_proj_qkv.weight"].scheme == staf.SCHEME_Q4_G64
+
+    class Recorder:
+        def __init__(self):
+            self.f32, self.q4, self.dense = {}, [], []
+
+        def add_dense_f32(self, name, data):
+            self.f32[name] = np.array(data)
+
+        def add_q4_staf(self, name, *a, **k):
+            self.q4.append(name)
+
+        def add_dense(self, name, *a, **k):
+            self.dense.append(name)
+
+    rec = Recorder()
+    staf.load_into_store(rec, f)
+    assert sorted(rec.f32) == ["model.layers.0.linear_attn.A_log", norm]
+    assert np.array_equal(rec.f32["model.layers.0.linear_attn.A_log"], weights["model.layers.0.linear_attn.A_log"])
+    assert "model.layers.0.linear_attn.dt_bias" in rec.dense and "model.layers.0.linear_attn.conv1d.weight" in rec.dense
