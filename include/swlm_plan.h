@@ -148,13 +148,28 @@ typedef struct swlm_buffers_desc {
     int32_t ssm_value_dim;
     int32_t ssm_conv_kernel;
     /* KV cache element scheme (KVCacheSpecification, Buffer/MetalGraphAllocator.swift): 0 or SWLM_KV_BF16 = dense bf16;
-       SWLM_KV_Q8G32 = 8-bit groups of 32 along the head dimension, 36-byte blocks fp16 scale | fp16 zero | 32 bytes,
-       value = scale * q + zero (read_kv_element / write_kv_quantized_q8, Generator/MetalSourceGenerator+Attention.swift:
-       1923-1956, 2057-2101). K and V use the same scheme. */
+       the quantized schemes keep groups of 32 / 64 / 128 values along the head dimension as blocks fp16 scale | fp16 zero
+       | payload (8-bit: one byte per value; 4-bit: two values per byte, the even one in the low nibble), value = scale *
+       q + zero (kv_quant_bits / _group_size / _bytes_per_block, read_kv_element, write_kv_quantized_q8 / _q4:
+       Generator/MetalSourceGenerator+Attention.swift:1894-1956, 2057-2155). K and V use the same scheme; a group may not
+       be wider than head_dim. */
     int32_t kv_scheme;
 } swlm_buffers_desc;
 
-enum { SWLM_KV_BF16 = 0x01, SWLM_KV_Q8G32 = 0x10 };
+enum {
+    SWLM_KV_BF16 = 0x01,
+    SWLM_KV_Q8G32 = 0x10, SWLM_KV_Q8G64 = 0x11, SWLM_KV_Q8G128 = 0x12,   /* 36 / 68 / 132 bytes per block */
+    SWLM_KV_Q4G64 = 0x40, SWLM_KV_Q4G128 = 0x41                          /* 36 / 68 bytes per block */
+};
+/* bits per value (0: dense), values per group, bytes per block and bytes per row of head_dim values */
+static inline int swlm_kv_bits(int scheme) { return scheme >= 0x10 && scheme <= 0x12 ? 8 : (scheme == 0x40 || scheme == 0x41) ? 4 : 0; }
+static inline int swlm_kv_group(int scheme) {
+    return scheme == 0x10 ? 32 : (scheme == 0x11 || scheme == 0x40) ? 64 : (scheme == 0x12 || scheme == 0x41) ? 128 : 0;
+}
+static inline int swlm_kv_block_bytes(int scheme) { return swlm_kv_bits(scheme) ? 4 + swlm_kv_group(scheme) * swlm_kv_bits(scheme) / 8 : 0; }
+static inline int swlm_kv_row_bytes(int scheme, int head_dim) {
+    return swlm_kv_bits(scheme) ? head_dim / swlm_kv_group(scheme) * swlm_kv_block_bytes(scheme) : head_dim * 2;
+}
 
 #ifdef __cplusplus
 }

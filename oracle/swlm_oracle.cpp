@@ -166,7 +166,7 @@ struct orc_model {
     std::vector<uint16_t> buf[SWLM_BUF_COUNT];
     int width[SWLM_BUF_COUNT]{};
     std::vector<uint16_t> kcache, vcache;  // [layer][b][kv_head][max_seq][head_dim]
-    std::vector<uint8_t> kq8, vq8;         // the same rows as 36-byte Q8 group-32 blocks when desc.kv_scheme == SWLM_KV_Q8G32
+    std::vector<uint8_t> kq8, vq8;         // the same rows as quantized blocks when desc.kv_scheme is one of the 8- / 4-bit schemes
     std::vector<uint16_t> conv;            // [layer][b][conv_kernel][conv_dim]
     std::map<std::string, std::vector<float>> densef;   // fp32 tensors (recurrent layers' norm weight, A_log)
     std::vector<uint16_t> ssm_conv;        // [layer][b][ssm_conv_kernel][ssm conv dim]
@@ -185,37 +185,42 @@ size_t kv_index(const orc_model* m, int layer, int b, int head, int t) {
     return ((((size_t)layer * d.max_batch + b) * d.kv_heads + head) * d.max_seq + t) * d.head_dim;
 }
 
-// ---- 8-bit group-32 KV rows ---------------------------------------------------
-// write_kv_quantized_q8 (Generator/MetalSourceGenerator+Attention.swift:2057-2101): per group of 32 values
-// scale = max((max - min) / 255, 1e-10), q = clamp(round((v - min) / scale), 0, 255) with the fp32 scale and min;
-// the block stores half(scale), half(min), then the 32 bytes.
-void kv_q8_write_row(uint8_t* row, const float* v, int hd) {
-    for (int g = 0; g * 32 < hd; ++g) {
+// ---- quantized KV rows ------------------------------------------------------------
+// write_kv_quantized_q8 / _q4 (Generator/MetalSourceGenerator+Attention.swift:2057-2101, 2108-2150): per group of
+// `group` values scale = max((max - min) / levels, 1e-10) with levels = 255 or 15, q = clamp(round((v - min) / scale), 0,
+// levels) with the fp32 scale and min; the block stores half(scale), half(min), then the payload (4-bit: value 2i in
+// the low nibble of byte i, value 2i + 1 in the high one).
+void kv_q_write_row(uint8_t* row, const float* v, int hd, int scheme) {
+    const int bits = swlm_kv_bits(scheme), group = swlm_kv_group(scheme), bb = swlm_kv_block_bytes(scheme);
+    const int levels = bits == 8 ? 255 : 15;
+    for (int g = 0; g * group < hd; ++g) {
         float lo = HUGE_VALF, hi = -HUGE_VALF;
-        for (int i = 0; i < 32; ++i) { lo = std::fmin(lo, v[g * 32 + i]); hi = std::fmax(hi, v[g * 32 + i]); }
-        float scale = (hi - lo) / 255.0f;
+        for (int i = 0; i < group; ++i) { lo = std::fmin(lo, v[g * group + i]); hi = std::fmax(hi, v[g * group + i]); }
+        float scale = (hi - lo) / (float)levels;
         if (scale < 1e-10f) scale = 1e-10f;
-        uint8_t* blk = row + (size_t)g * 36;
+        uint8_t* blk = row + (size_t)g * bb;
         uint16_t hs = f32_to_f16(scale), hz = f32_to_f16(lo);
         std::memcpy(blk, &hs, 2);
         std::memcpy(blk + 2, &hz, 2);
-        for (int i = 0; i < 32; ++i) {
-            int q = (int)std::round((v[g * 32 + i] - lo) / scale);
-            blk[4 + i] = (uint8_t)(q < 0 ? 0 : q > 255 ? 255 : q);
-        }
+        auto quant = [&](float x) { int q = (int)std::round((x - lo) / scale); return (uint8_t)(q < 0 ? 0 : q > levels ? levels : q); };
+        if (bits == 8) for (int i = 0; i < group; ++i) blk[4 + i] = quant(v[g * group + i]);
+        else for (int i = 0; i < group / 2; ++i) blk[4 + i] = (uint8_t)(quant(v[g * group + 2 * i]) | (quant(v[g * group + 2 * i + 1]) << 4));
     }
 }
 // read_kv_element (:1923-1956): scale * float(q) + zero with the stored fp16 scale and zero.
-inline float kv_q8_read(const uint8_t* row, int e) {
-    const uint8_t* blk = row + (size_t)(e / 32) * 36;
+inline float kv_q_read(const uint8_t* row, int e, int scheme) {
+    const int bits = swlm_kv_bits(scheme), group = swlm_kv_group(scheme);
+    const uint8_t* blk = row + (size_t)(e / group) * swlm_kv_block_bytes(scheme);
     uint16_t hs, hz;
     std::memcpy(&hs, blk, 2);
     std::memcpy(&hz, blk + 2, 2);
-    return f16_to_f32(hs) * (float)blk[4 + e % 32] + f16_to_f32(hz);
+    const int i = e % group;
+    const int q = bits == 8 ? blk[4 + i] : (i % 2 == 0 ? blk[4 + i / 2] & 0x0F : blk[4 + i / 2] >> 4);
+    return f16_to_f32(hs) * (float)q + f16_to_f32(hz);
 }
-size_t kv_q8_index(const orc_model* m, int layer, int b, int head, int t) {
+size_t kv_q_index(const orc_model* m, int layer, int b, int head, int t) {
     const swlm_buffers_desc& d = m->desc;
-    return ((((size_t)layer * d.max_batch + b) * d.kv_heads + head) * d.max_seq + t) * (size_t)(d.head_dim / 32 * 36);
+    return ((((size_t)layer * d.max_batch + b) * d.kv_heads + head) * d.max_seq + t) * (size_t)swlm_kv_row_bytes(d.kv_scheme, d.head_dim);
 }
 
 int run_step(orc_model* m, const swlm_step& st, int batch) {
@@ -320,12 +325,12 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 rope_inplace(q.data(), st.rope_dim, st.rope_base, pos);
                 rope_inplace(kc.data(), st.rope_dim, st.rope_base, pos);
             }
-            const bool q8 = d.kv_scheme == SWLM_KV_Q8G32;
-            const size_t q8_row = (size_t)(hd / 32) * 36;
+            const bool q8 = swlm_kv_bits(d.kv_scheme) != 0;
+            const size_t q8_row = (size_t)swlm_kv_row_bytes(d.kv_scheme, hd);
             const uint16_t* kbase = q8 ? nullptr : m->kcache.data() + kv_index(m, st.layer, b, kvh, 0);
             const uint16_t* vbase = q8 ? nullptr : m->vcache.data() + kv_index(m, st.layer, b, kvh, 0);
-            const uint8_t* kq = q8 ? m->kq8.data() + kv_q8_index(m, st.layer, b, kvh, 0) : nullptr;
-            const uint8_t* vq = q8 ? m->vq8.data() + kv_q8_index(m, st.layer, b, kvh, 0) : nullptr;
+            const uint8_t* kq = q8 ? m->kq8.data() + kv_q_index(m, st.layer, b, kvh, 0) : nullptr;
+            const uint8_t* vq = q8 ? m->vq8.data() + kv_q_index(m, st.layer, b, kvh, 0) : nullptr;
             float max_score = -HUGE_VALF, sum_exp = 0.0f;
             // sliding window (:851-853): the current token and the window_left - 1 before it
             const int t_first = st.window_left > 0 && pos + 1 > st.window_left ? pos - st.window_left + 1 : 0;
@@ -335,7 +340,7 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                     // the current token's key and value are used unrounded (:866-868, :905-907)
                     for (int i = 0; i < hd; ++i) score += q[i] * kc[i];
                 } else if (q8) {
-                    for (int i = 0; i < hd; ++i) score += q[i] * kv_q8_read(kq + (size_t)t * q8_row, i);
+                    for (int i = 0; i < hd; ++i) score += q[i] * kv_q_read(kq + (size_t)t * q8_row, i, d.kv_scheme);
                 } else {
                     const uint16_t* kr = kbase + (size_t)t * hd;
                     for (int i = 0; i < hd; ++i) score += q[i] * bf16_to_f32(kr[i]);
@@ -349,7 +354,7 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 if (t == pos) {
                     for (int i = 0; i < hd; ++i) out[i] = out[i] * corr + wgt * vc[i];
                 } else if (q8) {
-                    for (int i = 0; i < hd; ++i) out[i] = out[i] * corr + wgt * kv_q8_read(vq + (size_t)t * q8_row, i);
+                    for (int i = 0; i < hd; ++i) out[i] = out[i] * corr + wgt * kv_q_read(vq + (size_t)t * q8_row, i, d.kv_scheme);
                 } else {
                     const uint16_t* vr = vbase + (size_t)t * hd;
                     for (int i = 0; i < hd; ++i) out[i] = out[i] * corr + wgt * bf16_to_f32(vr[i]);
@@ -367,11 +372,11 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 const uint16_t* vin = row(m, st.in3_buf, b) + (size_t)kvh * hd;
                 for (int i = 0; i < hd; ++i) kc[i] = bf16_to_f32(kin[i]);
                 if (st.rope_dim > 0) rope_inplace(kc.data(), st.rope_dim, st.rope_base, pos);
-                if (d.kv_scheme == SWLM_KV_Q8G32) {   // quantized from the unrounded rotated k and from v as given
+                if (swlm_kv_bits(d.kv_scheme)) {   // quantized from the unrounded rotated k and from v as given
                     std::vector<float> vf(hd);
                     for (int i = 0; i < hd; ++i) vf[i] = bf16_to_f32(vin[i]);
-                    kv_q8_write_row(m->kq8.data() + kv_q8_index(m, st.layer, b, kvh, pos), kc.data(), hd);
-                    kv_q8_write_row(m->vq8.data() + kv_q8_index(m, st.layer, b, kvh, pos), vf.data(), hd);
+                    kv_q_write_row(m->kq8.data() + kv_q_index(m, st.layer, b, kvh, pos), kc.data(), hd, d.kv_scheme);
+                    kv_q_write_row(m->vq8.data() + kv_q_index(m, st.layer, b, kvh, pos), vf.data(), hd, d.kv_scheme);
                     continue;
                 }
                 uint16_t* kw = m->kcache.data() + kv_index(m, st.layer, b, kvh, pos);
@@ -553,8 +558,8 @@ orc_model* orc_create(const swlm_buffers_desc* desc) {
         m->buf[i].assign((size_t)d.max_batch * w, 0);
     }
     size_t kv = (size_t)d.kv_layers * d.max_batch * d.kv_heads * d.max_seq * d.head_dim;
-    if (d.kv_scheme == SWLM_KV_Q8G32) {
-        const size_t bytes = (size_t)d.kv_layers * d.max_batch * d.kv_heads * d.max_seq * (size_t)(d.head_dim / 32 * 36);
+    if (swlm_kv_bits(d.kv_scheme)) {
+        const size_t bytes = (size_t)d.kv_layers * d.max_batch * d.kv_heads * d.max_seq * (size_t)swlm_kv_row_bytes(d.kv_scheme, d.head_dim);
         m->kq8.assign(bytes, 0);
         m->vq8.assign(bytes, 0);
         kv = 0;
@@ -670,11 +675,11 @@ int orc_run_step(orc_model* m, const swlm_step* st, const int32_t* token_in, int
 }
 // K or V cache rows of one (layer, sequence, head): [count][head_dim] bf16 from token 0.
 int orc_read_kv(orc_model* m, int which, int layer, int b, int head, int count, uint16_t* dst) {
-    if (m->desc.kv_scheme == SWLM_KV_Q8G32) {   // the dequantised rows, rounded to bf16
-        const int hd = m->desc.head_dim;
-        const uint8_t* rows = (which ? m->vq8 : m->kq8).data() + kv_q8_index(m, layer, b, head, 0);
+    if (swlm_kv_bits(m->desc.kv_scheme)) {   // the dequantised rows, rounded to bf16
+        const int hd = m->desc.head_dim, sch = m->desc.kv_scheme;
+        const uint8_t* rows = (which ? m->vq8 : m->kq8).data() + kv_q_index(m, layer, b, head, 0);
         for (int t = 0; t < count; ++t)
-            for (int e = 0; e < hd; ++e) dst[(size_t)t * hd + e] = f32_to_bf16(kv_q8_read(rows + (size_t)t * (hd / 32 * 36), e));
+            for (int e = 0; e < hd; ++e) dst[(size_t)t * hd + e] = f32_to_bf16(kv_q_read(rows + (size_t)t * swlm_kv_row_bytes(sch, hd), e, sch));
         return 0;
     }
     const std::vector<uint16_t>& c = which ? m->vcache : m->kcache;
@@ -682,13 +687,13 @@ int orc_read_kv(orc_model* m, int which, int layer, int b, int head, int count, 
     return 0;
 }
 int orc_write_kv(orc_model* m, int which, int layer, int b, int head, int count, const uint16_t* src) {
-    if (m->desc.kv_scheme == SWLM_KV_Q8G32) {   // the rows are quantised as an appended row would be
-        const int hd = m->desc.head_dim;
-        uint8_t* rows = (which ? m->vq8 : m->kq8).data() + kv_q8_index(m, layer, b, head, 0);
+    if (swlm_kv_bits(m->desc.kv_scheme)) {   // the rows are quantised as an appended row would be
+        const int hd = m->desc.head_dim, sch = m->desc.kv_scheme;
+        uint8_t* rows = (which ? m->vq8 : m->kq8).data() + kv_q_index(m, layer, b, head, 0);
         std::vector<float> f(hd);
         for (int t = 0; t < count; ++t) {
             for (int e = 0; e < hd; ++e) f[e] = bf16_to_f32(src[(size_t)t * hd + e]);
-            kv_q8_write_row(rows + (size_t)t * (hd / 32 * 36), f.data(), hd);
+            kv_q_write_row(rows + (size_t)t * swlm_kv_row_bytes(sch, hd), f.data(), hd, sch);
         }
         return 0;
     }

@@ -50,6 +50,7 @@ struct AttnParams {
     int pos_base;              // prompt ingestion: position of the chunk's first token
     int chunk_tokens;          // prompt ingestion: tokens in the chunk
     int window;                // sliding window (0 = none): a token attends itself and the window - 1 rows before it
+    int kv_bits, kv_group;     // quantized cache: bits per value (8 or 4) and values per block (32, 64 or 128)
     int q_first;               // 1: the first K/V rows are requested only after q, k, v have arrived
     __nv_bfloat16* out; int out_stride;
     float* part_o;   // [m][heads][splits][HD]
@@ -539,8 +540,8 @@ int check_launch(const char* what) {
 }
 
 
-// ---- decode attention over an 8-bit group-32 cache --------------------------------------------------------------
-// Rows are (head_dim / 32) blocks of 36 bytes: fp16 scale | fp16 zero | 32 bytes, value = scale * q + zero
+// ---- decode attention over a quantized cache (8-bit groups of 32 / 64 / 128, 4-bit groups of 64 / 128) ----------------
+// Rows are head_dim / group blocks of fp16 scale | fp16 zero | payload (36 bytes for 8-bit groups of 32), value = scale * q + zero
 // (read_kv_element, Generator/MetalSourceGenerator+Attention.swift:1923-1956). Half the bytes of the bf16 cache cross
 // HBM. One CTA per (split, KV head, sequence) as in the bf16 kernel; a warp takes one token at a time, every lane
 // dequantises its head_dim / 32 consecutive elements of the K row and of the V row and the dot products of the GQA
@@ -550,29 +551,40 @@ int check_launch(const char* what) {
 // (sequence, KV head) to arrive merges the splits.
 constexpr int kQ8Warps = 8, kQ8Threads = kQ8Warps * 32;
 
-__device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char* row, int hd, int warp, int lane) {
-    for (int g = warp; g * 32 < hd; g += kQ8Warps) {
-        const float x = src[g * 32 + lane];
-        float lo = x, hi = x;
+// One row of head_dim floats into blocks of `group` values with `bits` bits each: a warp per group, a lane takes
+// group / 32 consecutive values (write_kv_quantized_q8 / _q4, Generator/MetalSourceGenerator+Attention.swift:2057-2150).
+__device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char* row, int hd, int bits, int group, int warp, int lane) {
+    const int epg = group / 32, bb = 4 + group * bits / 8;
+    const float levels = bits == 8 ? 255.0f : 15.0f;
+    for (int g = warp; g * group < hd; g += kQ8Warps) {
+        float x[4];
+        float lo = HUGE_VALF, hi = -HUGE_VALF;
+        for (int j = 0; j < epg; ++j) { x[j] = src[g * group + lane * epg + j]; lo = fminf(lo, x[j]); hi = fmaxf(hi, x[j]); }
         for (int o = 16; o > 0; o >>= 1) { lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o)); hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o)); }
-        float scale = (hi - lo) / 255.0f;
+        float scale = (hi - lo) / levels;
         if (scale < 1e-10f) scale = 1e-10f;
-        unsigned char* blk = row + (size_t)g * 36;
+        unsigned char* blk = row + (size_t)g * bb;
         if (lane == 0) {
             const __half2 hdr = __floats2half2_rn(scale, lo);
             *reinterpret_cast<__half2*>(blk) = hdr;
         }
-        const int q = (int)roundf((x - lo) / scale);
-        blk[4 + lane] = (unsigned char)min(max(q, 0), 255);
+        int q[4];
+        for (int j = 0; j < epg; ++j) q[j] = min(max((int)roundf((x[j] - lo) / scale), 0), (int)levels);
+        if (bits == 8) {
+            for (int j = 0; j < epg; ++j) blk[4 + lane * epg + j] = (unsigned char)q[j];
+        } else {   // two values per byte, the even one in the low nibble (epg is 2 or 4)
+            for (int j = 0; j < epg; j += 2) blk[4 + (lane * epg + j) / 2] = (unsigned char)(q[j] | (q[j + 1] << 4));
+        }
     }
 }
 
 // G (query heads per KV head) is a template argument: the per-head dot products, warp reductions and softmax updates of
 // a row are then one basic block whose four or eight independent chains the compiler interleaves.
-template <int HD, int G>
+template <int HD, int G, int BITS>
 __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnParams p) {
     constexpr int EPL = HD / 32;           // elements per lane
-    constexpr int ROW_BYTES = HD / 32 * 36;
+    const int GROUP = p.kv_group, BB = 4 + GROUP * BITS / 8;   // values and bytes per block (BITS per value)
+    const int ROW_BYTES = HD / GROUP * BB;
     pdl_launch_dependents();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -608,11 +620,19 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
     unsigned char* kbase = reinterpret_cast<unsigned char*>(p.kcache) + ((size_t)b * p.kv_heads + kvh) * head_bytes;
     unsigned char* vbase = reinterpret_cast<unsigned char*>(p.vcache) + ((size_t)b * p.kv_heads + kvh) * head_bytes;
     if (split == 0 && n_ctx < p.max_seq) {
-        q8_quantise_row(kcur, kbase + (size_t)n_ctx * ROW_BYTES, HD, warp, lane);
-        q8_quantise_row(vcur, vbase + (size_t)n_ctx * ROW_BYTES, HD, warp, lane);
+        q8_quantise_row(kcur, kbase + (size_t)n_ctx * ROW_BYTES, HD, BITS, GROUP, warp, lane);
+        q8_quantise_row(vcur, vbase + (size_t)n_ctx * ROW_BYTES, HD, BITS, GROUP, warp, lane);
     }
-    // this lane's elements e0 .. e0 + EPL - 1 lie in one block
-    const int e0 = lane * EPL, blk_off = (e0 / 32) * 36, pay_off = blk_off + 4 + (e0 & 31);
+    // this lane's elements e0 .. e0 + EPL - 1 lie in one block; its payload is EPL * BITS / 8 bytes (4, 2 or 1),
+    // naturally aligned
+    const int e0 = lane * EPL, blk_off = (e0 / GROUP) * BB, pay_off = blk_off + 4 + (e0 % GROUP) * BITS / 8;
+    constexpr int pay_bytes = EPL * BITS / 8;
+    constexpr unsigned qmask = BITS == 8 ? 0xffu : 0xfu;
+    auto load_payload = [&](const unsigned char* ptr) -> unsigned {
+        if (pay_bytes == 4) return __ldg(reinterpret_cast<const unsigned*>(ptr));
+        if (pay_bytes == 2) return __ldg(reinterpret_cast<const unsigned short*>(ptr));
+        return __ldg(ptr);
+    };
     float qr[G][EPL];
 #pragma unroll
     for (int r = 0; r < G; ++r)
@@ -653,13 +673,8 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
             const unsigned char* vr = vbase + (size_t)t * ROW_BYTES;
             khd[u] = __ldg(reinterpret_cast<const unsigned*>(kr + blk_off));
             vhd[u] = __ldg(reinterpret_cast<const unsigned*>(vr + blk_off));
-            if (EPL == 4) {
-                kw[u] = __ldg(reinterpret_cast<const unsigned*>(kr + pay_off));
-                vw[u] = __ldg(reinterpret_cast<const unsigned*>(vr + pay_off));
-            } else {
-                kw[u] = __ldg(reinterpret_cast<const unsigned short*>(kr + pay_off));
-                vw[u] = __ldg(reinterpret_cast<const unsigned short*>(vr + pay_off));
-            }
+            kw[u] = load_payload(kr + pay_off);
+            vw[u] = load_payload(vr + pay_off);
         }
         // the scores of the eight rows for all heads: 8 x G independent dot products and warp reductions, interleaved
         float sc[UN][G];
@@ -669,7 +684,7 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
             const float ks = __low2float(kh), kz = __high2float(kh);
             float kf[EPL];
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) kf[j] = fmaf(ks, (float)((kw[u] >> (8 * j)) & 0xffu), kz);
+            for (int j = 0; j < EPL; ++j) kf[j] = fmaf(ks, (float)((kw[u] >> (BITS * j)) & qmask), kz);
 #pragma unroll
             for (int r = 0; r < G; ++r) {
                 sc[u][r] = 0.f;
@@ -691,7 +706,7 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
             const __half2 vh = *reinterpret_cast<const __half2*>(&vhd[u]);
             const float vs = __low2float(vh), vz = __high2float(vh);
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) vfu[u][j] = fmaf(vs, (float)((vw[u] >> (8 * j)) & 0xffu), vz);
+            for (int j = 0; j < EPL; ++j) vfu[u][j] = fmaf(vs, (float)((vw[u] >> (BITS * j)) & qmask), vz);
         }
 #pragma unroll
         for (int r = 0; r < G; ++r) {
@@ -1083,13 +1098,17 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
     p.prefetch = a.prefetch;
     if (a.pos_base < 0 && a.m * a.kv_heads * a.splits + a.m * a.kv_heads <= 512)
         p.trace = qgemv_trace_slot(a.m * a.kv_heads * a.splits, -a.kv_heads * a.m, a.splits, 9, 0);
-    if (a.kv_scheme == SWLM_KV_Q8G32) {
-        if (a.pos_base >= 0) { set_error("attention: prompt chunks over an 8-bit cache are not supported"); return SWLM_ERR_UNSUPPORTED; }
+    if (swlm_kv_bits(a.kv_scheme)) {
+        if (a.pos_base >= 0) { set_error("attention: prompt chunks over a quantized cache are not supported"); return SWLM_ERR_UNSUPPORTED; }
+        p.kv_bits = swlm_kv_bits(a.kv_scheme); p.kv_group = swlm_kv_group(a.kv_scheme);
+        if (p.kv_group > a.head_dim) { set_error("attention: cache groups of %d values exceed head_dim %d", p.kv_group, a.head_dim); return SWLM_ERR_UNSUPPORTED; }
         const dim3 grid(p.splits, p.kv_heads, a.m);
         const int G = a.heads / a.kv_heads;
         if (a.head_dim != 64 && a.head_dim != 128) { set_error("attention: head_dim %d not supported over an 8-bit cache (64 or 128)", a.head_dim); return SWLM_ERR_UNSUPPORTED; }
         if (G != 1 && G != 2 && G != 4 && G != 8) { set_error("attention over an 8-bit cache: %d query heads per KV head (1, 2, 4 or 8)", G); return SWLM_ERR_UNSUPPORTED; }
-#define SWLM_Q8_CASE(HDV, GV) if (a.head_dim == HDV && G == GV) launch_k(attn_q8_split_kernel<HDV, GV>, grid, dim3(kQ8Threads), 0, s, p)
+#define SWLM_Q8_CASE(HDV, GV) if (a.head_dim == HDV && G == GV) { \
+            if (p.kv_bits == 8) launch_k(attn_q8_split_kernel<HDV, GV, 8>, grid, dim3(kQ8Threads), 0, s, p); \
+            else launch_k(attn_q8_split_kernel<HDV, GV, 4>, grid, dim3(kQ8Threads), 0, s, p); }
         SWLM_Q8_CASE(128, 1); SWLM_Q8_CASE(128, 2); SWLM_Q8_CASE(128, 4); SWLM_Q8_CASE(128, 8);
         SWLM_Q8_CASE(64, 1); SWLM_Q8_CASE(64, 2); SWLM_Q8_CASE(64, 4); SWLM_Q8_CASE(64, 8);
 #undef SWLM_Q8_CASE

@@ -667,7 +667,7 @@ PrefetchTarget prefetch_of(const Launch& L) {
 __nv_bfloat16* res_buf(swlm_state* s, int phys) { return phys ? s->res2 : s->buf[SWLM_BUF_RESIDUAL]; }
 
 size_t kv_row_bytes(const swlm_buffers_desc& d) {
-    return d.kv_scheme == SWLM_KV_Q8G32 ? (size_t)d.head_dim / 32 * 36 : (size_t)d.head_dim * 2;
+    return (size_t)swlm_kv_row_bytes(d.kv_scheme, d.head_dim);
 }
 
 int kv_heads_local(const swlm_plan* p) { return std::max(1, p->desc.kv_heads / std::max(1, p->ctx->tp_size)); }
@@ -1059,7 +1059,7 @@ constexpr int kTpChunkRows = 1024;
 
 bool rows_capable(const swlm_plan* plan, bool allow_tp = false) {
     if ((plan->ctx->tp_size != 1 && !allow_tp) || plan->desc.head_dim > 128) return false;
-    if (plan->desc.kv_scheme == SWLM_KV_Q8G32) return false;   // prompts over an 8-bit cache go token by token
+    if (swlm_kv_bits(plan->desc.kv_scheme)) return false;   // prompts over a quantized cache go token by token
     if (plan->ctx->tp_size > 1 && (plan->desc.hidden & 7)) return false;
     for (const swlm_step& st : plan->steps) {
         if (st.kind == SWLM_STEP_QGEMV && st.in_buf == st.out_buf) return false;
@@ -1464,12 +1464,13 @@ int64_t swlm_weights_bytes(const swlm_ctx* ctx) { return ctx ? ctx->bytes : 0; }
 int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const swlm_buffers_desc* desc, swlm_plan** out) {
     if (!ctx || !steps || n_steps <= 0 || !desc || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
     *out = nullptr;
-    if (desc->kv_scheme != 0 && desc->kv_scheme != SWLM_KV_BF16 && desc->kv_scheme != SWLM_KV_Q8G32) {
-        set_error("KV cache scheme %#x not supported (bf16 or 8-bit group 32)", desc->kv_scheme);
+    if (desc->kv_scheme != 0 && desc->kv_scheme != SWLM_KV_BF16 && !swlm_kv_bits(desc->kv_scheme)) {
+        set_error("KV cache scheme %#x not supported (bf16, 8-bit groups of 32 / 64 / 128, 4-bit groups of 64 / 128)", desc->kv_scheme);
         return SWLM_ERR_UNSUPPORTED;
     }
-    if (desc->kv_scheme == SWLM_KV_Q8G32 && desc->kv_layers > 0 && desc->head_dim != 64 && desc->head_dim != 128) {
-        set_error("an 8-bit KV cache needs head_dim 64 or 128");
+    if (swlm_kv_bits(desc->kv_scheme) && desc->kv_layers > 0 &&
+        ((desc->head_dim != 64 && desc->head_dim != 128) || swlm_kv_group(desc->kv_scheme) > desc->head_dim)) {
+        set_error("a quantized KV cache needs head_dim 64 or 128 and groups no wider than head_dim");
         return SWLM_ERR_UNSUPPORTED;
     }
     if (desc->max_batch < 1 || desc->max_batch > kMaxSequences) { set_error("max_batch %d outside 1..%d", desc->max_batch, kMaxSequences); return SWLM_ERR_INVALID; }
@@ -1928,25 +1929,31 @@ static int kv_ptr(swlm_state* s, int which, int layer, int b, int head, int coun
 
 // 8-bit group-32 rows on the host, for the probes: the arithmetic of write_kv_quantized_q8 / read_kv_element
 // (Generator/MetalSourceGenerator+Attention.swift:2057-2101, 1923-1956).
-static void kv_q8_quantise_host(const float* v, int hd, unsigned char* row) {
-    for (int g = 0; g * 32 < hd; ++g) {
-        float lo = v[g * 32], hi = v[g * 32];
-        for (int i = 1; i < 32; ++i) { lo = std::min(lo, v[g * 32 + i]); hi = std::max(hi, v[g * 32 + i]); }
-        float scale = (hi - lo) / 255.0f;
+static void kv_q8_quantise_host(const float* v, int hd, int scheme, unsigned char* row) {
+    const int bits = swlm_kv_bits(scheme), group = swlm_kv_group(scheme), bb = swlm_kv_block_bytes(scheme), levels = bits == 8 ? 255 : 15;
+    for (int g = 0; g * group < hd; ++g) {
+        float lo = v[g * group], hi = v[g * group];
+        for (int i = 1; i < group; ++i) { lo = std::min(lo, v[g * group + i]); hi = std::max(hi, v[g * group + i]); }
+        float scale = (hi - lo) / (float)levels;
         if (scale < 1e-10f) scale = 1e-10f;
-        unsigned char* blk = row + (size_t)g * 36;
+        unsigned char* blk = row + (size_t)g * bb;
         const __half hs = __float2half_rn(scale), hz = __float2half_rn(lo);
         memcpy(blk, &hs, 2);
         memcpy(blk + 2, &hz, 2);
-        for (int i = 0; i < 32; ++i) blk[4 + i] = (unsigned char)std::min(255, std::max(0, (int)roundf((v[g * 32 + i] - lo) / scale)));
+        auto quant = [&](float x) { return (unsigned char)std::min(levels, std::max(0, (int)roundf((x - lo) / scale))); };
+        if (bits == 8) for (int i = 0; i < group; ++i) blk[4 + i] = quant(v[g * group + i]);
+        else for (int i = 0; i < group / 2; ++i) blk[4 + i] = (unsigned char)(quant(v[g * group + 2 * i]) | (quant(v[g * group + 2 * i + 1]) << 4));
     }
 }
-static float kv_q8_read_host(const unsigned char* row, int e) {
-    const unsigned char* blk = row + (size_t)(e / 32) * 36;
+static float kv_q8_read_host(const unsigned char* row, int e, int scheme) {
+    const int bits = swlm_kv_bits(scheme), group = swlm_kv_group(scheme);
+    const unsigned char* blk = row + (size_t)(e / group) * swlm_kv_block_bytes(scheme);
     __half hs, hz;
     memcpy(&hs, blk, 2);
     memcpy(&hz, blk + 2, 2);
-    return __half2float(hs) * (float)blk[4 + e % 32] + __half2float(hz);
+    const int i = e % group;
+    const int q = bits == 8 ? blk[4 + i] : (i % 2 == 0 ? blk[4 + i / 2] & 0x0F : blk[4 + i / 2] >> 4);
+    return __half2float(hs) * (float)q + __half2float(hz);
 }
 static float bf16_bits_to_float(uint16_t h) { const uint32_t u = (uint32_t)h << 16; float f; memcpy(&f, &u, 4); return f; }
 static uint16_t float_to_bf16_bits(float f) { uint32_t u; memcpy(&u, &f, 4); u += 0x7FFFu + ((u >> 16) & 1u); return (uint16_t)(u >> 16); }
@@ -1958,12 +1965,12 @@ int swlm_read_kv(swlm_state* s, int which, int layer, int b, int head, int count
     if (rc) return rc;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     const swlm_buffers_desc& d = s->plan->desc;
-    if (d.kv_scheme == SWLM_KV_Q8G32) {   // the dequantised rows, rounded to bf16
+    if (swlm_kv_bits(d.kv_scheme)) {   // the dequantised rows, rounded to bf16
         std::vector<unsigned char> rows((size_t)count * kv_row_bytes(d));
         SWLM_CUDA(cudaMemcpy(rows.data(), p, rows.size(), cudaMemcpyDeviceToHost));
         for (int t = 0; t < count; ++t)
             for (int e = 0; e < d.head_dim; ++e)
-                dst[(size_t)t * d.head_dim + e] = float_to_bf16_bits(kv_q8_read_host(rows.data() + (size_t)t * kv_row_bytes(d), e));
+                dst[(size_t)t * d.head_dim + e] = float_to_bf16_bits(kv_q8_read_host(rows.data() + (size_t)t * kv_row_bytes(d), e, d.kv_scheme));
         return SWLM_OK;
     }
     SWLM_CUDA(cudaMemcpy(dst, p, (size_t)count * s->plan->desc.head_dim * 2, cudaMemcpyDeviceToHost));
@@ -1977,12 +1984,12 @@ int swlm_write_kv(swlm_state* s, int which, int layer, int b, int head, int coun
     if (rc) return rc;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     const swlm_buffers_desc& d = s->plan->desc;
-    if (d.kv_scheme == SWLM_KV_Q8G32) {   // quantised as an appended row would be
+    if (swlm_kv_bits(d.kv_scheme)) {   // quantised as an appended row would be
         std::vector<unsigned char> rows((size_t)count * kv_row_bytes(d));
         std::vector<float> f(d.head_dim);
         for (int t = 0; t < count; ++t) {
             for (int e = 0; e < d.head_dim; ++e) f[e] = bf16_bits_to_float(src[(size_t)t * d.head_dim + e]);
-            kv_q8_quantise_host(f.data(), d.head_dim, rows.data() + (size_t)t * kv_row_bytes(d));
+            kv_q8_quantise_host(f.data(), d.head_dim, d.kv_scheme, rows.data() + (size_t)t * kv_row_bytes(d));
         }
         SWLM_CUDA(cudaMemcpy(p, rows.data(), rows.size(), cudaMemcpyHostToDevice));
         return SWLM_OK;

@@ -277,7 +277,7 @@ struct AttnLaunch {
     // k/v rows are appended first, then token b attends cache rows 0..pos_base+b. `position` is not read.
     int pos_base = -1;
     int window = 0;       // sliding window: the current token and the window - 1 before it; 0 = everything
-    int kv_scheme = 0;    // SWLM_KV_Q8G32: the cache rows are 36-byte blocks of 32 8-bit values (decode steps only)
+    int kv_scheme = 0;    // one of the quantized SWLM_KV_* schemes: the cache rows are blocks of 8- or 4-bit values (decode steps only)
     PrefetchTarget prefetch;
 };
 int attn_pick_splits(int m, int kv_heads, int max_ctx);

@@ -68,7 +68,8 @@ class ModelConfig:
     # (Sources/LMArchitecture/Declaration/Components/DeltaNet.swift, Primitives/SSMRecurrenceFragment.swift) with
     # `ssm_heads` value heads of `ssm_value_dim`, `ssm_groups` key groups of `ssm_key_dim`, a causal conv of
     # `ssm_conv_kernel` taps over the q|k|v channels; tensor names follow Models/Qwen35/Qwen35FamilyNaming.swift:73-87.
-    # KV cache elements: 0 = bf16; 0x10 = 8-bit groups of 32 (36-byte blocks, KVCacheSpecification's Q8 group-32 scheme)
+    # KV cache elements: 0 = bf16; 0x10 / 0x11 / 0x12 = 8-bit groups of 32 / 64 / 128; 0x40 / 0x41 = 4-bit groups of 64 / 128
+    # (KVCacheSpecification's affine block schemes)
     kv_scheme: int = 0
     ssm_heads: int = 0
     ssm_groups: int = 0

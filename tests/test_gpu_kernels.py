@@ -508,16 +508,25 @@ def test_ssm_recurrence_matches_oracle_over_steps(pkg, store, oracle, heads, gro
 
 # ---- 8-bit KV cache ----------------------------------------------------------------------------------------
 
+KV_SCHEMES = {0x10: (8, 32), 0x11: (8, 64), 0x12: (8, 128), 0x40: (4, 64), 0x41: (4, 128)}
+
+
+@pytest.mark.parametrize("scheme", sorted(KV_SCHEMES))
 @pytest.mark.parametrize("hd,heads,kvh", [(128, 32, 8), (64, 16, 4), (128, 8, 8)])
-@pytest.mark.parametrize("batch,ctx,window", [(1, 0, 0), (1, 1, 0), (1, 63, 0), (1, 65, 0), (1, 1000, 0), (1, 4095, 0), (3, 300, 0), (1, 900, 100)])
-def test_attention_decode_over_q8_group32_cache(pkg, store, oracle, hd, heads, kvh, batch, ctx, window):
-    """KV rows as 36-byte blocks of 32 8-bit values: the cache is filled through the probe (quantised on the host by
-    both sides with the reference's rule, so both start from the same bytes), one decode step appends the new token's
-    row and attends; output and the appended (dequantised) rows against the oracle."""
+@pytest.mark.parametrize("batch,ctx,window", [(1, 0, 0), (1, 1, 0), (1, 65, 0), (1, 1000, 0), (1, 4095, 0), (3, 300, 0), (1, 900, 100)])
+def test_attention_decode_over_q8_group32_cache(pkg, store, oracle, hd, heads, kvh, batch, ctx, window, scheme):
+    """KV rows as blocks of 8- or 4-bit values (36 bytes per 32 8-bit values, and the other four schemes): the cache is
+    filled through the probe (quantised on the host by both sides with the reference's rule, so both start from the
+    same bytes), one decode step appends the new token's row and attends; output and the appended (dequantised) rows
+    against the oracle."""
+    bits, group = KV_SCHEMES[scheme]
+    if group > hd:
+        pytest.skip("a group wider than the head dimension is refused")
+    levels = 255.0 if bits == 8 else 15.0
     P = pkg.plan
     max_seq = 4096
     desc = pkg.BuffersDesc(hidden=256, slot_dim=heads * hd, vocab=512, max_seq=max_seq, max_batch=batch, kv_layers=1, kv_heads=kvh,
-                           head_dim=hd, conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=0x10)
+                           head_dim=hd, conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=scheme)
     table = _bf(pkg, np.zeros((512, 256)))
     store.add_dense("q8.embed", table)
     gm = pkg.InferenceModel(store, [P._step(P.STEP_EMBED, out_buf=0, n=256, weight="q8.embed")], desc)
@@ -550,8 +559,8 @@ def test_attention_decode_over_q8_group32_cache(pkg, store, oracle, hd, heads, k
             for which in (0, 1):
                 g = pkg.bf16_to_f32(gm.read_kv(which, 0, b, h, ctx + 1)[ctx])
                 o = pkg.bf16_to_f32(om.read_kv(which, 0, b, h, ctx + 1)[ctx])
-                # the same row quantised on the device and by the oracle: at most one 8-bit step apart (RoPE in fp32 may
+                # the same row quantised on the device and by the oracle: at most one step apart (RoPE in fp32 may
                 # differ in the last bit, which can move a value across a rounding boundary)
-                step_size = (o.reshape(-1, 32).max(-1) - o.reshape(-1, 32).min(-1)) / 255.0
-                assert np.all(np.abs(g - o).reshape(-1, 32).max(-1) <= 1.5 * step_size + 2.0 ** -7 * np.abs(o).max())
+                step_size = (o.reshape(-1, group).max(-1) - o.reshape(-1, group).min(-1)) / levels
+                assert np.all(np.abs(g - o).reshape(-1, group).max(-1) <= 1.5 * step_size + 2.0 ** -7 * np.abs(o).max())
     gm.close()

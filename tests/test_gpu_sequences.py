@@ -260,13 +260,15 @@ def test_recurrent_layers_chunked_prompt_and_many_sequences(pkg, oracle):
     gm.close(); store.close()
 
 
-@pytest.mark.parametrize("family,batch", [("llama", 1), ("llama", 3), ("lfm2", 1), ("llama", 20)])
-def test_q8_kv_cache_model_against_oracle(pkg, oracle, family, batch):
-    """The whole plan over an 8-bit group-32 KV cache (prompt token by token, then decode; 20 sequences through the
-    row-wise executor): tokens and logits against the oracle, which quantises and reads the cache by the same rule."""
+@pytest.mark.parametrize("family,batch,scheme", [("llama", 1, 0x10), ("llama", 3, 0x10), ("lfm2", 1, 0x10), ("llama", 20, 0x10),
+                                                 ("llama", 1, 0x11), ("llama", 2, 0x40)])
+def test_q8_kv_cache_model_against_oracle(pkg, oracle, family, batch, scheme):
+    """The whole plan over a quantized KV cache (8-bit groups of 32 or 64, 4-bit groups of 64; prompt token by token,
+    then decode; 20 sequences through the row-wise executor): tokens and logits against the oracle, which quantises
+    and reads the cache by the same rule."""
     import dataclasses
     cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=batch, max_seq=128)
-    cfg = dataclasses.replace(cfg, kv_scheme=0x10)
+    cfg = dataclasses.replace(cfg, kv_scheme=scheme)
     # (the small LFM2-like model runs with one sequence here: with 2 or 3 sequences, i.e. through the fp16 GEMV kernel,
     # its random weights have an input, the 40-token prompt of seed 11, at which a gated conv output nearly cancels and
     # the next norm blows rounding noise up to a different answer than the oracle's; with a bf16 cache just the same)

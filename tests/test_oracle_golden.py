@@ -129,7 +129,8 @@ def test_attention_sliding_window_against_fp64_softmax(pkg, oracle, window):
             assert np.max(np.abs(out[h] - w @ vals)) < 2e-2
 
 
-def test_attention_over_q8_group32_cache_against_fp64(pkg, oracle):
+@pytest.mark.parametrize("scheme,bits,group", [(0x10, 8, 32), (0x11, 8, 64), (0x40, 4, 64)])
+def test_attention_over_q8_group32_cache_against_fp64(pkg, oracle, scheme, bits, group):
     """8-bit KV rows (36-byte blocks of 32 values, Generator/MetalSourceGenerator+Attention.swift:1923-1956, 2057-2101):
     the rows the oracle appends dequantise to within half a quantisation step of what was written, and attention over
     them equals an fp64 softmax over the DEQUANTISED rows plus the current token's unrounded k and v."""
@@ -138,7 +139,7 @@ def test_attention_over_q8_group32_cache_against_fp64(pkg, oracle):
     bf = lambda a: pkg.bf16_to_f32(pkg.f32_to_bf16(np.asarray(a, dtype=np.float32)))
     q, k, v = bf(rng.normal(size=(T, H * D))), bf(rng.normal(size=(T, KV * D))), bf(rng.normal(size=(T, KV * D)))
     desc = pkg.BuffersDesc(hidden=H * D, slot_dim=H * D, vocab=8, max_seq=16, max_batch=1, kv_layers=1, kv_heads=KV, head_dim=D,
-                           conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=0x10)
+                           conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=scheme)
     m = oracle.model(desc)
     step = pkg.plan._step(pkg.plan.STEP_ATTN_DECODE, layer=0, in_buf=3, in2_buf=4, in3_buf=5, out_buf=2, heads=H, kv_heads=KV,
                           head_dim=D, rope_dim=0, rope_base=0.0, scale=1.0 / np.sqrt(D))
@@ -160,8 +161,8 @@ def test_attention_over_q8_group32_cache_against_fp64(pkg, oracle):
     for h in range(KV):
         got = pkg.bf16_to_f32(m.read_kv(0, 0, 0, h, T)).reshape(T, D)
         want = k.reshape(T, KV, D)[:, h]
-        step_size = (want.reshape(T, D // 32, 32).max(-1) - want.reshape(T, D // 32, 32).min(-1)) / 255.0
-        assert np.all(np.abs(got - want).reshape(T, D // 32, 32).max(-1) <= 0.51 * step_size + 2.0 ** -7 * np.abs(want).max())
+        step_size = (want.reshape(T, D // group, group).max(-1) - want.reshape(T, D // group, group).min(-1)) / (255.0 if bits == 8 else 15.0)
+        assert np.all(np.abs(got - want).reshape(T, D // group, group).max(-1) <= 0.51 * step_size + 2.0 ** -7 * np.abs(want).max())
 
 
 def ssm_case(pkg, heads=4, groups=2, dk=16, dv=16, K=4, batch=1, seed=1):
