@@ -17,8 +17,8 @@
 //
 // One CTA (18 warps) computes a 128 (weight rows) x BN (tokens) tile of Y^T:
 //   * a TMA warp (one thread) keeps a ring of stages full, two cp.async.bulk.tensor.2d per 64-column group
-//     (no multicast): the packed weights of the group (128 rows x 32 bytes) and the activation tile (BN tokens
-//     x 64 columns of bf16, 128-byte swizzle, rows past the last token filled with zeros); an mbarrier per
+//     (every CTA fetches its own copy): the packed weights of the group (128 rows x 32 bytes) and the activation tile (BN tokens
+//     x 64 columns of fp16, 128-byte swizzle, rows past the last token filled with zeros); an mbarrier per
 //     stage counts the bytes;
 //   * 16 warps dequantise: four threads own one weight row, per group each reads 8 packed bytes from shared
 //     memory, takes the row's (scale, zero) from registers (fetched eight groups at a time), turns nibble
