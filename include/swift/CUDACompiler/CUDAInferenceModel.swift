@@ -60,6 +60,29 @@ public final class CUDAInferenceModel {
 
     public func resetState() { _ = swlm_state_reset(state) }
 
+    // ---- several sequences per step (swlm_buffers_desc.max_batch > 1; no counterpart in the reference) ----------
+    /// Append a prompt to one sequence while the others keep their state; returns that sequence's next token (-1 on failure).
+    public func prefill(sequence: Int, tokens: [Int32]) -> Int32 {
+        var first: Int32 = -1
+        _ = tokens.withUnsafeBufferPointer { swlm_prefill_seq(state, Int32(sequence), $0.baseAddress, Int32($0.count), &first) }
+        return first
+    }
+
+    /// One decode step for all sequences, each at its own position.
+    public func decode(tokenIDs: [Int32]) -> [Int32] {
+        var out = [Int32](repeating: -1, count: tokenIDs.count)
+        _ = tokenIDs.withUnsafeBufferPointer { swlm_decode(state, $0.baseAddress, &out) }
+        return out
+    }
+
+    public func resetSequence(_ sequence: Int) throws { try swlmCheck(swlm_state_reset_seq(state, Int32(sequence))) }
+
+    public func positions(count: Int) throws -> [Int32] {
+        var out = [Int32](repeating: 0, count: count)
+        try swlmCheck(swlm_get_positions(state, &out))
+        return out
+    }
+
     /// MetalInferenceModel.promptSnapshot / restore: KV cache, conv state, position and last tokens.
     public func promptSnapshot() throws -> CUDAPromptSnapshot {
         var h: OpaquePointer?

@@ -56,6 +56,12 @@ public final class CUDAWeightStore {
             case 0x40:  // q4Group64ScaleF16: shape is the packed safetensors shape [rows, cols / 8]
                 guard e.shape.count == 2 else { throw CUDACompilerError.unsupportedTensor(e.name) }
                 try addSTAFBlocks(name: e.name, rows: e.shape[0], cols: e.shape[1] * 8, blocks: payload, shard: shardKind(e.name))
+            case 0x41:  // q4Group128ScaleF16: 68-byte blocks of 128 weights
+                guard e.shape.count == 2 else { throw CUDACompilerError.unsupportedTensor(e.name) }
+                try swlmCheck(swlm_weights_add_q4g128_staf(ctx, e.name, Int32(e.shape[0]), Int32(e.shape[1] * 8), payload, shardKind(e.name)))
+            case 0x02 where e.name.hasSuffix(".linear_attn.norm.weight") || e.name.hasSuffix(".A_log"):
+                // fp32RowMajor tensors the recurrent step reads as fp32 (STAFConversionPlanner.swift:117-140)
+                try swlmCheck(swlm_weights_add_dense_f32(ctx, e.name, Int64(e.payloadSize / 4), payload.assumingMemoryBound(to: Float.self)))
             case 0x01:  // bf16RowMajor
                 let cols = e.shape.last ?? 1
                 let rows = e.shape.dropLast().reduce(1, *)
