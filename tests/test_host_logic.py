@@ -77,6 +77,46 @@ def test_lfm2_plan_shape(pkg):
     assert cfg.q4_weight_elems() == 16 * 50_331_648 + 10 * 16_777_216 + 6 * 10_485_760 + 134_217_728
 
 
+def test_deltanet_plan_shape_windows_and_cache_scheme(pkg):
+    """The hybrid recurrent recipe: per recurrent layer four projections of one input, the recurrence step with its
+    four buffers and four tensors, the out projection; every name the steps use is in the tensor inventory with the
+    right kind; sliding windows and the cache scheme travel through the plan and the buffer description."""
+    import dataclasses
+    P = pkg.plan
+    cfg = pkg.ModelConfig("deltanet", hidden=256, intermediate=512, layers=6, heads=4, kv_heads=2, head_dim=64, vocab=1024,
+                          attention_layers=[2, 5], max_seq=64, ssm_heads=8, ssm_groups=4, ssm_key_dim=32, ssm_value_dim=64,
+                          ssm_conv_kernel=4, sliding_window=16, sliding_window_layers=[5], kv_scheme=0x11)
+    b = pkg.DispatchPlanBuilder(cfg)
+    steps = b.decode_steps()
+    kinds = [s.kind for s in steps]
+    assert cfg.ssm_layer_count == 4 and cfg.kv_layer_count == 2 and cfg.conv_layer_count == 0
+    assert cfg.ssm_conv_dim == 2 * 4 * 32 + 8 * 64 and cfg.slot_dim >= cfg.ssm_conv_dim
+    assert kinds.count(P.STEP_SSM_RECURRENCE) == 4 and kinds.count(P.STEP_ATTN_DECODE) == 2
+    assert kinds.count(P.STEP_QGEMV) == 4 * 5 + 2 * 4 + 6 * 3 + 1
+    rec = [s for s in steps if s.kind == P.STEP_SSM_RECURRENCE]
+    assert [s.layer for s in rec] == [0, 1, 2, 3]
+    r0 = rec[0]
+    assert (r0.in_buf, r0.in2_buf, r0.in3_buf, r0.in4_buf, r0.out_buf) == (P.BUF_S1, P.BUF_S2, P.BUF_S3, P.BUF_S4, P.BUF_S0)
+    assert (r0.heads, r0.groups, r0.key_dim, r0.value_dim, r0.conv_kernel) == (8, 4, 32, 64, 4)
+    assert r0.weight.decode().endswith("linear_attn.conv1d.weight") and r0.weight4.decode().endswith("linear_attn.A_log")
+    kinds_by_name = {t[0]: t[1] for t in b.tensors()}
+    assert kinds_by_name[r0.weight2.decode()] == "f32" and kinds_by_name[r0.weight4.decode()] == "f32"
+    assert kinds_by_name[r0.weight.decode()] == "conv" and kinds_by_name[r0.weight3.decode()] == "dense"
+    for s in steps:
+        for w in (s.weight, s.weight2, s.weight3, s.weight4):
+            if w:
+                assert w.decode() in kinds_by_name
+    att = [s for s in steps if s.kind == P.STEP_ATTN_DECODE]
+    assert [s.window_left for s in att] == [0, 16]                 # only model layer 5 is windowed
+    d = cfg.buffers_desc()
+    assert (d.ssm_layers, d.ssm_heads, d.ssm_groups, d.ssm_key_dim, d.ssm_value_dim, d.ssm_conv_kernel, d.kv_scheme) == (4, 8, 4, 32, 64, 4, 0x11)
+    plain = dataclasses.replace(cfg, family="llama", attention_layers=[]).buffers_desc()
+    assert plain.ssm_layers == 0 and plain.ssm_heads == 0
+    w = pkg.synth_model_weights(b, seed=1)
+    assert w[r0.weight2.decode()].dtype == np.float32 and w[r0.weight3.decode()].dtype == np.uint16
+    assert abs(float(w[r0.weight4.decode()].min())) <= 1.0
+
+
 def test_synth_distributions(pkg):
     w, s, b = pkg.synth_q4(64, 4096, seed=0)
     q = pkg.formats.unpack_mlx_q4(w, 4096)
