@@ -153,6 +153,17 @@ int swlm_write_buffer(swlm_state* state, int buf, const uint16_t* src, int count
 /* K (which=0) or V (which=1) rows [count][head_dim] bf16 of one KV slab / sequence / head. */
 int swlm_read_kv(swlm_state* state, int which, int layer, int b, int head, int count, uint16_t* dst);
 int swlm_write_kv(swlm_state* state, int which, int layer, int b, int head, int count, const uint16_t* src);
+/* Rotated KV schemes (SWLM_KV_ROTOR_*). The probes above speak the model's basis: swlm_write_kv turns the rows before
+ * it quantises them (K rows also get their projected residuals when kv_qjl_dim > 0), swlm_read_kv turns the
+ * dequantised rows back. The rotors are [kv_layers][kv_heads][swlm_kv_rotor_groups(head_dim)][4] fp16 values
+ * (s, b12, b13, b23), filled at state creation by the reference's deterministic rule (MetalKVCache.
+ * initializeRandomUnitRotors, Buffer/MetalGraphAllocator.swift:349-390; the reference keeps them in a CPU-writable
+ * buffer); swlm_state_set_rotors replaces all of them and must be called before the first row is cached.
+ * swlm_read_qjl copies the projected K residuals [count][kv_qjl_dim] fp16 of one KV slab / sequence / head
+ * (qjlResidualK, :268-272). */
+int swlm_state_get_rotors(swlm_state* state, uint16_t* dst, size_t count);
+int swlm_state_set_rotors(swlm_state* state, const uint16_t* src, size_t count);
+int swlm_read_qjl(swlm_state* state, int layer, int b, int head, int count, uint16_t* dst);
 int swlm_read_conv(swlm_state* state, int layer, int b, uint16_t* dst);
 /* fp32 recurrent state [ssm_heads][ssm_key_dim][ssm_value_dim] of one recurrent layer / sequence. */
 int swlm_read_ssm_state(swlm_state* state, int layer, int b, float* dst);

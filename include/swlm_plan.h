@@ -154,16 +154,35 @@ typedef struct swlm_buffers_desc {
        Generator/MetalSourceGenerator+Attention.swift:1894-1956, 2057-2155). K and V use the same scheme; a group may not
        be wider than head_dim. */
     int32_t kv_scheme;
+    /* The two rotated schemes (is_rotor_scheme / rotor_base_scheme, :1791-1800) store rows in the block layout of their
+       base scheme after every group of three consecutive values of a K or V row was turned by a unit rotor of Cl(3,0)
+       (rotor_sandwich, :1807-1813; one rotor per attention layer, KV head and group, ceil(head_dim / 3) groups, the
+       last one padded with zeros); q is turned the same way and the attention output turned back
+       (rotor_sandwich_inverse, :1815-1821). kv_qjl_dim > 0 (at most 64; rotated schemes only) adds the correction of
+       the K quantisation error: per cached row kv_qjl_dim fp16 values Phi . (k_rotated - dequantised row) with the fixed
+       +-1/sqrt(kv_qjl_dim) matrix Phi [head_dim][kv_qjl_dim], and every score over a cached row gains
+       (Phi . q_rotated) . (that row's values) (qjl_compute_residual, qjl_project_query, qjl_score_correction,
+       :1983-2048). */
+    int32_t kv_qjl_dim;
 } swlm_buffers_desc;
 
 enum {
     SWLM_KV_BF16 = 0x01,
     SWLM_KV_Q8G32 = 0x10, SWLM_KV_Q8G64 = 0x11, SWLM_KV_Q8G128 = 0x12,   /* 36 / 68 / 132 bytes per block */
-    SWLM_KV_Q4G64 = 0x40, SWLM_KV_Q4G128 = 0x41                          /* 36 / 68 bytes per block */
+    SWLM_KV_Q4G64 = 0x40, SWLM_KV_Q4G128 = 0x41,                         /* 36 / 68 bytes per block */
+    SWLM_KV_ROTOR_Q8G32 = 0x70, SWLM_KV_ROTOR_Q4G64 = 0x71               /* rotated rows in the layout of 0x10 / 0x40 */
 };
+static inline int swlm_kv_is_rotor(int scheme) { return scheme == 0x70 || scheme == 0x71; }
+static inline int swlm_kv_base_scheme(int scheme) { return scheme == 0x70 ? 0x10 : scheme == 0x71 ? 0x40 : scheme; }
+/* rotors per KV head: groups of three values along the head dimension (KVCacheSpecification.numRotorGroups) */
+static inline int swlm_kv_rotor_groups(int head_dim) { return (head_dim + 2) / 3; }
 /* bits per value (0: dense), values per group, bytes per block and bytes per row of head_dim values */
-static inline int swlm_kv_bits(int scheme) { return scheme >= 0x10 && scheme <= 0x12 ? 8 : (scheme == 0x40 || scheme == 0x41) ? 4 : 0; }
+static inline int swlm_kv_bits(int scheme) {
+    scheme = swlm_kv_base_scheme(scheme);
+    return scheme >= 0x10 && scheme <= 0x12 ? 8 : (scheme == 0x40 || scheme == 0x41) ? 4 : 0;
+}
 static inline int swlm_kv_group(int scheme) {
+    scheme = swlm_kv_base_scheme(scheme);
     return scheme == 0x10 ? 32 : (scheme == 0x11 || scheme == 0x40) ? 64 : (scheme == 0x12 || scheme == 0x41) ? 128 : 0;
 }
 static inline int swlm_kv_block_bytes(int scheme) { return swlm_kv_bits(scheme) ? 4 + swlm_kv_group(scheme) * swlm_kv_bits(scheme) / 8 : 0; }

@@ -167,6 +167,9 @@ struct orc_model {
     int width[SWLM_BUF_COUNT]{};
     std::vector<uint16_t> kcache, vcache;  // [layer][b][kv_head][max_seq][head_dim]
     std::vector<uint8_t> kq8, vq8;         // the same rows as quantized blocks when desc.kv_scheme is one of the 8- / 4-bit schemes
+    // rotated schemes: fp16 rotors [layer][kv_head][group][4], projection matrix [head_dim][qjl], projected K residuals
+    // [layer][b][kv_head][max_seq][qjl]
+    std::vector<uint16_t> rotors, qjl_matrix, qjl_res;
     std::vector<uint16_t> conv;            // [layer][b][conv_kernel][conv_dim]
     std::map<std::string, std::vector<float>> densef;   // fp32 tensors (recurrent layers' norm weight, A_log)
     std::vector<uint16_t> ssm_conv;        // [layer][b][ssm_conv_kernel][ssm conv dim]
@@ -221,6 +224,73 @@ inline float kv_q_read(const uint8_t* row, int e, int scheme) {
 size_t kv_q_index(const orc_model* m, int layer, int b, int head, int t) {
     const swlm_buffers_desc& d = m->desc;
     return ((((size_t)layer * d.max_batch + b) * d.kv_heads + head) * d.max_seq + t) * (size_t)swlm_kv_row_bytes(d.kv_scheme, d.head_dim);
+}
+
+// ---- rotated schemes ----------------------------------------------------------------
+// rotor_sandwich / rotor_sandwich_inverse (Generator/MetalSourceGenerator+Attention.swift:1807-1821) over the groups
+// of three values of a row (rotor_apply_forward / _inverse, :1827-1884): R = (s, b12, b13, b23) acts like the unit
+// quaternion (s, b23, -b13, b12); values past the end of the row enter as zeros and are not stored.
+void rotor_turn_row(float* row, int hd, const uint16_t* R, bool inverse) {
+    for (int g = 0; 3 * g < hd; ++g) {
+        const int base = 3 * g;
+        const float x = row[base], y = base + 1 < hd ? row[base + 1] : 0.0f, z = base + 2 < hd ? row[base + 2] : 0.0f;
+        const float s = f16_to_f32(R[4 * g]);
+        float px = f16_to_f32(R[4 * g + 3]), py = -f16_to_f32(R[4 * g + 2]), pz = f16_to_f32(R[4 * g + 1]);
+        if (inverse) { px = -px; py = -py; pz = -pz; }
+        const float tx = 2.0f * (py * z - pz * y), ty = 2.0f * (pz * x - px * z), tz = 2.0f * (px * y - py * x);
+        row[base] = x + s * tx + (py * tz - pz * ty);
+        if (base + 1 < hd) row[base + 1] = y + s * ty + (pz * tx - px * tz);
+        if (base + 2 < hd) row[base + 2] = z + s * tz + (px * ty - py * tx);
+    }
+}
+const uint16_t* head_rotors(const orc_model* m, int layer, int head) {
+    const swlm_buffers_desc& d = m->desc;
+    return m->rotors.data() + ((size_t)layer * d.kv_heads + head) * swlm_kv_rotor_groups(d.head_dim) * 4;
+}
+uint16_t* qjl_row(orc_model* m, int layer, int b, int head, int t) {
+    const swlm_buffers_desc& d = m->desc;
+    return m->qjl_res.data() + ((((size_t)layer * d.max_batch + b) * d.kv_heads + head) * d.max_seq + t) * d.kv_qjl_dim;
+}
+// qjl_compute_residual (:1983-2013): Phi . (row - the values its quantized blocks give back), as fp16
+void qjl_store_residual(orc_model* m, int layer, int b, int head, int t, const float* turned, const uint8_t* blocks) {
+    const swlm_buffers_desc& d = m->desc;
+    const int hd = d.head_dim, qjl = d.kv_qjl_dim;
+    std::vector<float> res(hd);
+    for (int e = 0; e < hd; ++e) res[e] = turned[e] - kv_q_read(blocks, e, d.kv_scheme);
+    uint16_t* out = qjl_row(m, layer, b, head, t);
+    for (int j = 0; j < qjl; ++j) {
+        float a = 0.0f;
+        for (int e = 0; e < hd; ++e) a += res[e] * f16_to_f32(m->qjl_matrix[(size_t)e * qjl + j]);
+        out[j] = f32_to_f16(a);
+    }
+}
+// initializeRandomUnitRotors / initializeRademacherMatrix (Buffer/MetalGraphAllocator.swift:349-411)
+void rotor_defaults(orc_model* m) {
+    const swlm_buffers_desc& d = m->desc;
+    const size_t total = (size_t)d.kv_layers * d.kv_heads * swlm_kv_rotor_groups(d.head_dim);
+    m->rotors.assign(total * 4, 0);
+    const float unit = 1.0f / (float)(1 << 30);
+    for (size_t i = 0; i < total; ++i) {
+        uint64_t h = (uint64_t)i;
+        float c[4];
+        for (int j = 0; j < 4; ++j) {
+            h = h * 6364136223846793005ull + 1442695040888963407ull;
+            c[j] = (float)((int64_t)(h >> 33) - ((int64_t)1 << 30)) * unit;
+        }
+        const float norm = std::sqrt(c[0] * c[0] + c[1] * c[1] + c[2] * c[2] + c[3] * c[3]);
+        if (norm < 1e-8f) { c[0] = 1.0f; c[1] = c[2] = c[3] = 0.0f; }
+        else { const float inv = 1.0f / norm; for (int j = 0; j < 4; ++j) c[j] *= inv; }
+        for (int j = 0; j < 4; ++j) m->rotors[i * 4 + j] = f32_to_f16(c[j]);
+    }
+    const int qjl = d.kv_qjl_dim;
+    if (qjl <= 0) return;
+    const float scale = 1.0f / std::sqrt((float)qjl);
+    m->qjl_matrix.assign((size_t)d.head_dim * qjl, 0);
+    for (size_t i = 0; i < m->qjl_matrix.size(); ++i) {
+        const uint64_t h = (uint64_t)i * 6364136223846793005ull + 1442695040888963407ull;
+        m->qjl_matrix[i] = f32_to_f16(((h >> 33) & 1) == 0 ? scale : -scale);
+    }
+    m->qjl_res.assign((size_t)d.kv_layers * d.max_batch * d.kv_heads * d.max_seq * qjl, 0);
 }
 
 int run_step(orc_model* m, const swlm_step& st, int batch) {
@@ -325,6 +395,21 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 rope_inplace(q.data(), st.rope_dim, st.rope_base, pos);
                 rope_inplace(kc.data(), st.rope_dim, st.rope_base, pos);
             }
+            // rotated schemes (:708-760, :813-840): q, the new k and the new v are turned; Phi . q for the correction
+            const bool rotor = swlm_kv_is_rotor(d.kv_scheme);
+            const int qjl = rotor ? d.kv_qjl_dim : 0;
+            std::vector<float> qproj(qjl > 0 ? qjl : 1, 0.0f);
+            if (rotor) {
+                const uint16_t* R = head_rotors(m, st.layer, kvh);
+                rotor_turn_row(q.data(), hd, R, false);
+                rotor_turn_row(kc.data(), hd, R, false);
+                rotor_turn_row(vc.data(), hd, R, false);
+                for (int j = 0; j < qjl; ++j) {
+                    float a = 0.0f;
+                    for (int i = 0; i < hd; ++i) a += q[i] * f16_to_f32(m->qjl_matrix[(size_t)i * qjl + j]);
+                    qproj[j] = a;
+                }
+            }
             const bool q8 = swlm_kv_bits(d.kv_scheme) != 0;
             const size_t q8_row = (size_t)swlm_kv_row_bytes(d.kv_scheme, hd);
             const uint16_t* kbase = q8 ? nullptr : m->kcache.data() + kv_index(m, st.layer, b, kvh, 0);
@@ -341,6 +426,10 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                     for (int i = 0; i < hd; ++i) score += q[i] * kc[i];
                 } else if (q8) {
                     for (int i = 0; i < hd; ++i) score += q[i] * kv_q_read(kq + (size_t)t * q8_row, i, d.kv_scheme);
+                    if (qjl > 0) {   // qjl_score_correction (:2036-2048), cached rows only (:873-876)
+                        const uint16_t* rr = qjl_row(m, st.layer, b, kvh, t);
+                        for (int j = 0; j < qjl; ++j) score += qproj[j] * f16_to_f32(rr[j]);
+                    }
                 } else {
                     const uint16_t* kr = kbase + (size_t)t * hd;
                     for (int i = 0; i < hd; ++i) score += q[i] * bf16_to_f32(kr[i]);
@@ -362,7 +451,9 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
             }
             float inv = sum_exp > 0.0f ? 1.0f / sum_exp : 0.0f;
             uint16_t* o = row(m, st.out_buf, b) + (size_t)h * hd;
-            for (int i = 0; i < hd; ++i) o[i] = f32_to_bf16(out[i] * inv);
+            for (int i = 0; i < hd; ++i) out[i] *= inv;
+            if (rotor) rotor_turn_row(out.data(), hd, head_rotors(m, st.layer, kvh), true);   // (:914-923)
+            for (int i = 0; i < hd; ++i) o[i] = f32_to_bf16(out[i]);
         }
         // KV append, once per KV head, rounded to bf16 (:761-805, write_kv_element_dense :1961-1963).
         for (int b = 0; b < batch; ++b)
@@ -375,8 +466,14 @@ int run_step(orc_model* m, const swlm_step& st, int batch) {
                 if (swlm_kv_bits(d.kv_scheme)) {   // quantized from the unrounded rotated k and from v as given
                     std::vector<float> vf(hd);
                     for (int i = 0; i < hd; ++i) vf[i] = bf16_to_f32(vin[i]);
-                    kv_q_write_row(m->kq8.data() + kv_q_index(m, st.layer, b, kvh, pos), kc.data(), hd, d.kv_scheme);
+                    if (swlm_kv_is_rotor(d.kv_scheme)) {
+                        rotor_turn_row(kc.data(), hd, head_rotors(m, st.layer, kvh), false);
+                        rotor_turn_row(vf.data(), hd, head_rotors(m, st.layer, kvh), false);
+                    }
+                    uint8_t* kblocks = m->kq8.data() + kv_q_index(m, st.layer, b, kvh, pos);
+                    kv_q_write_row(kblocks, kc.data(), hd, d.kv_scheme);
                     kv_q_write_row(m->vq8.data() + kv_q_index(m, st.layer, b, kvh, pos), vf.data(), hd, d.kv_scheme);
+                    if (swlm_kv_is_rotor(d.kv_scheme) && d.kv_qjl_dim > 0) qjl_store_residual(m, st.layer, b, kvh, pos, kc.data(), kblocks);
                     continue;
                 }
                 uint16_t* kw = m->kcache.data() + kv_index(m, st.layer, b, kvh, pos);
@@ -563,6 +660,7 @@ orc_model* orc_create(const swlm_buffers_desc* desc) {
         m->kq8.assign(bytes, 0);
         m->vq8.assign(bytes, 0);
         kv = 0;
+        if (swlm_kv_is_rotor(d.kv_scheme)) rotor_defaults(m);
     }
     m->kcache.assign(kv, 0);
     m->vcache.assign(kv, 0);
@@ -678,8 +776,12 @@ int orc_read_kv(orc_model* m, int which, int layer, int b, int head, int count, 
     if (swlm_kv_bits(m->desc.kv_scheme)) {   // the dequantised rows, rounded to bf16
         const int hd = m->desc.head_dim, sch = m->desc.kv_scheme;
         const uint8_t* rows = (which ? m->vq8 : m->kq8).data() + kv_q_index(m, layer, b, head, 0);
-        for (int t = 0; t < count; ++t)
-            for (int e = 0; e < hd; ++e) dst[(size_t)t * hd + e] = f32_to_bf16(kv_q_read(rows + (size_t)t * swlm_kv_row_bytes(sch, hd), e, sch));
+        std::vector<float> f(hd);
+        for (int t = 0; t < count; ++t) {   // (rows of a rotated scheme are turned back)
+            for (int e = 0; e < hd; ++e) f[e] = kv_q_read(rows + (size_t)t * swlm_kv_row_bytes(sch, hd), e, sch);
+            if (swlm_kv_is_rotor(sch)) rotor_turn_row(f.data(), hd, head_rotors(m, layer, head), true);
+            for (int e = 0; e < hd; ++e) dst[(size_t)t * hd + e] = f32_to_bf16(f[e]);
+        }
         return 0;
     }
     const std::vector<uint16_t>& c = which ? m->vcache : m->kcache;
@@ -693,12 +795,25 @@ int orc_write_kv(orc_model* m, int which, int layer, int b, int head, int count,
         std::vector<float> f(hd);
         for (int t = 0; t < count; ++t) {
             for (int e = 0; e < hd; ++e) f[e] = bf16_to_f32(src[(size_t)t * hd + e]);
-            kv_q_write_row(rows + (size_t)t * swlm_kv_row_bytes(sch, hd), f.data(), hd, sch);
+            if (swlm_kv_is_rotor(sch)) rotor_turn_row(f.data(), hd, head_rotors(m, layer, head), false);
+            uint8_t* blocks = rows + (size_t)t * swlm_kv_row_bytes(sch, hd);
+            kv_q_write_row(blocks, f.data(), hd, sch);
+            if (swlm_kv_is_rotor(sch) && which == 0 && m->desc.kv_qjl_dim > 0) qjl_store_residual(m, layer, b, head, t, f.data(), blocks);
         }
         return 0;
     }
     std::vector<uint16_t>& c = which ? m->vcache : m->kcache;
     std::memcpy(c.data() + kv_index(m, layer, b, head, 0), src, (size_t)count * m->desc.head_dim * 2);
+    return 0;
+}
+// rotated schemes: all rotors [kv_layers][kv_heads][groups][4] fp16, and the projected K residuals [count][kv_qjl_dim]
+int64_t orc_rotor_count(orc_model* m) { return (int64_t)m->rotors.size(); }
+int orc_get_rotors(orc_model* m, uint16_t* dst) { std::memcpy(dst, m->rotors.data(), m->rotors.size() * 2); return 0; }
+int orc_set_rotors(orc_model* m, const uint16_t* src) { std::memcpy(m->rotors.data(), src, m->rotors.size() * 2); return 0; }
+int orc_get_qjl_matrix(orc_model* m, uint16_t* dst) { std::memcpy(dst, m->qjl_matrix.data(), m->qjl_matrix.size() * 2); return 0; }
+int orc_read_qjl(orc_model* m, int layer, int b, int head, int count, uint16_t* dst) {
+    if (m->qjl_res.empty()) return -1;
+    std::memcpy(dst, qjl_row(m, layer, b, head, 0), (size_t)count * m->desc.kv_qjl_dim * 2);
     return 0;
 }
 int orc_add_dense_f32(orc_model* m, const char* name, int64_t count, const float* data) {

@@ -58,6 +58,12 @@ struct AttnParams {
     unsigned* counters;  // [m][kv_heads], zero between launches
     PrefetchTarget prefetch;  // weights of a later product, requested into L2 while this kernel runs
     unsigned long long* trace;  // SWLM_TRACE=1: [cta][4] = entry, predecessor complete, loop done, partials published
+    // rotated cache schemes: this layer's rotors [kv_heads][ceil(HD / 3)][4] fp16, the projection matrix
+    // [HD][qjl_dim] fp16 and this layer's projected K residuals [m][kv_heads][max_seq][qjl_dim] fp16 (qjl_dim 0: none)
+    const __half* rotors;
+    const __half* qjl_matrix;
+    __half* qjl_res;
+    int qjl_dim;
 };
 
 __device__ __forceinline__ unsigned long long attn_timer_ns() {
@@ -553,7 +559,10 @@ constexpr int kQ8Warps = 8, kQ8Threads = kQ8Warps * 32;
 
 // One row of head_dim floats into blocks of `group` values with `bits` bits each: a warp per group, a lane takes
 // group / 32 consecutive values (write_kv_quantized_q8 / _q4, Generator/MetalSourceGenerator+Attention.swift:2057-2150).
-__device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char* row, int hd, int bits, int group, int warp, int lane) {
+// RESID: resid[i] = src[i] - the value the stored block gives back for it (fp16 scale and zero), the residual that
+// qjl_compute_residual (:1983-2013) projects.
+template <bool RESID = false>
+__device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char* row, int hd, int bits, int group, int warp, int lane, float* resid = nullptr) {
     const int epg = group / 32, bb = 4 + group * bits / 8;
     const float levels = bits == 8 ? 255.0f : 15.0f;
     for (int g = warp; g * group < hd; g += kQ8Warps) {
@@ -570,6 +579,10 @@ __device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char*
         }
         int q[4];
         for (int j = 0; j < epg; ++j) q[j] = min(max((int)roundf((x[j] - lo) / scale), 0), (int)levels);
+        if (RESID) {
+            const float sh = __half2float(__float2half_rn(scale)), zh = __half2float(__float2half_rn(lo));
+            for (int j = 0; j < epg; ++j) resid[g * group + lane * epg + j] = x[j] - fmaf(sh, (float)q[j], zh);
+        }
         if (bits == 8) {
             for (int j = 0; j < epg; ++j) blk[4 + lane * epg + j] = (unsigned char)q[j];
         } else {   // two values per byte, the even one in the low nibble (epg is 2 or 4)
@@ -578,11 +591,43 @@ __device__ __forceinline__ void q8_quantise_row(const float* src, unsigned char*
     }
 }
 
+// Sandwich product of Cl(3,0) (rotor_sandwich / rotor_sandwich_inverse, Generator/MetalSourceGenerator+Attention.swift:
+// 1807-1821): the rotor R = (s, b12, b13, b23) turns (x, y, z) like the unit quaternion (s, b23, -b13, b12), in the
+// cross-product form v + s t + p x t with t = 2 p x v; INV uses the conjugate.
+template <bool INV>
+__device__ __forceinline__ void rotor_turn(const __half* R, float& x, float& y, float& z) {
+    const float s = __half2float(R[0]);
+    float px = __half2float(R[3]), py = -__half2float(R[2]), pz = __half2float(R[1]);
+    if (INV) { px = -px; py = -py; pz = -pz; }
+    const float tx = 2.0f * (py * z - pz * y), ty = 2.0f * (pz * x - px * z), tz = 2.0f * (px * y - py * x);
+    const float rx = x + s * tx + (py * tz - pz * ty);
+    const float ry = y + s * ty + (pz * tx - px * tz);
+    const float rz = z + s * tz + (px * ty - py * tx);
+    x = rx; y = ry; z = rz;
+}
+// group g = values 3g .. 3g + 2 of a row of hd floats, in place; values past the row's end enter as zeros and are not
+// stored (rotor_apply_forward / _inverse, :1827-1884)
+template <bool INV>
+__device__ __forceinline__ void rotor_turn_group(float* row, int hd, const __half* rotors, int g) {
+    const int base = 3 * g;
+    float x = row[base], y = base + 1 < hd ? row[base + 1] : 0.0f, z = base + 2 < hd ? row[base + 2] : 0.0f;
+    rotor_turn<INV>(rotors + 4 * g, x, y, z);
+    row[base] = x;
+    if (base + 1 < hd) row[base + 1] = y;
+    if (base + 2 < hd) row[base + 2] = z;
+}
+
 // G (query heads per KV head) is a template argument: the per-head dot products, warp reductions and softmax updates of
 // a row are then one basic block whose four or eight independent chains the compiler interleaves.
-template <int HD, int G, int BITS>
+//
+// ROTOR (the rotated schemes, :694-930): q, the new k (both after RoPE) and the new v are turned by the KV head's rotors
+// before anything else, so the cache holds turned rows and q . k is unchanged; the merged output is turned back. With
+// qjl_dim > 0 split 0 also stores Phi . (k - its dequantised row) for the new row, and the score of a cached row gains
+// (Phi . q) . (that row's stored values): lane l carries columns l and l + 32 of both into the warp reduction.
+template <int HD, int G, int BITS, bool ROTOR>
 __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnParams p) {
     constexpr int EPL = HD / 32;           // elements per lane
+    constexpr int NG = (HD + 2) / 3;       // rotors per KV head
     const int GROUP = p.kv_group, BB = 4 + GROUP * BITS / 8;   // values and bytes per block (BITS per value)
     const int ROW_BYTES = HD / GROUP * BB;
     pdl_launch_dependents();
@@ -593,6 +638,10 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
     __shared__ float osm[kQ8Warps][kMaxGroup][HD];   // (sized for the merge scratch below whatever G is)
     __shared__ float msm[kQ8Warps][kMaxGroup], lsm[kQ8Warps][kMaxGroup];
     __shared__ int is_last;
+    __shared__ float kres[ROTOR ? HD : 1];          // the new k row minus its dequantised blocks
+    __shared__ float qp[ROTOR ? G : 1][64];         // Phi . q of every head of the group
+    const __half* const head_rotors = ROTOR ? p.rotors + (size_t)kvh * NG * 4 : nullptr;
+    const int qjl = ROTOR ? p.qjl_dim : 0;
     pdl_wait();
     const int n_ctx = p.position[b];
     for (int idx = tid; idx < G * HD; idx += kQ8Threads)
@@ -616,12 +665,47 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
         }
         __syncthreads();
     }
+    if (ROTOR) {
+        for (int idx = tid; idx < (G + 2) * NG; idx += kQ8Threads) {
+            const int r = idx / NG, g = idx - r * NG;
+            rotor_turn_group<false>(r < G ? qs[r] : r == G ? kcur : vcur, HD, head_rotors, g);
+        }
+        __syncthreads();
+    }
     const size_t head_bytes = (size_t)p.max_seq * ROW_BYTES;
     unsigned char* kbase = reinterpret_cast<unsigned char*>(p.kcache) + ((size_t)b * p.kv_heads + kvh) * head_bytes;
     unsigned char* vbase = reinterpret_cast<unsigned char*>(p.vcache) + ((size_t)b * p.kv_heads + kvh) * head_bytes;
+    const __half* const res_base = ROTOR && qjl > 0 ? p.qjl_res + ((size_t)b * p.kv_heads + kvh) * p.max_seq * qjl : nullptr;
     if (split == 0 && n_ctx < p.max_seq) {
-        q8_quantise_row(kcur, kbase + (size_t)n_ctx * ROW_BYTES, HD, BITS, GROUP, warp, lane);
+        q8_quantise_row<ROTOR>(kcur, kbase + (size_t)n_ctx * ROW_BYTES, HD, BITS, GROUP, warp, lane, kres);
         q8_quantise_row(vcur, vbase + (size_t)n_ctx * ROW_BYTES, HD, BITS, GROUP, warp, lane);
+        if (ROTOR && qjl > 0) {   // (the branch is uniform over the CTA)
+            __syncthreads();
+            __half* res = p.qjl_res + (((size_t)b * p.kv_heads + kvh) * p.max_seq + n_ctx) * qjl;
+            for (int j = warp; j < qjl; j += kQ8Warps) {
+                float a = 0.f;
+                for (int d = lane; d < HD; d += 32) a = fmaf(kres[d], __half2float(__ldg(p.qjl_matrix + (size_t)d * qjl + j)), a);
+                for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                if (lane == 0) res[j] = __float2half_rn(a);
+            }
+        }
+    }
+    float qpr[G][2];   // this lane's two columns of Phi . q (zero past qjl_dim)
+#pragma unroll
+    for (int r = 0; r < G; ++r) qpr[r][0] = qpr[r][1] = 0.f;
+    if (ROTOR && qjl > 0) {
+        for (int idx = tid; idx < G * qjl; idx += kQ8Threads) {
+            const int r = idx / qjl, j = idx - r * qjl;
+            float a = 0.f;
+            for (int d = 0; d < HD; ++d) a = fmaf(qs[r][d], __half2float(__ldg(p.qjl_matrix + (size_t)d * qjl + j)), a);
+            qp[r][j] = a;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < G; ++r) {
+            if (lane < qjl) qpr[r][0] = qp[r][lane];
+            if (lane + 32 < qjl) qpr[r][1] = qp[r][lane + 32];
+        }
     }
     // this lane's elements e0 .. e0 + EPL - 1 lie in one block; its payload is EPL * BITS / 8 bytes (4, 2 or 1),
     // naturally aligned
@@ -666,6 +750,7 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
     constexpr int UN = 8;
     for (int tb = t0 + warp; tb < t1; tb += kQ8Warps * UN) {
         unsigned kw[UN], vw[UN], khd[UN], vhd[UN];
+        unsigned short rz0[ROTOR ? UN : 1], rz1[ROTOR ? UN : 1];   // the row's projected residual, columns lane and lane + 32
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
             const int t = min(tb + u * kQ8Warps, t1 - 1);   // rows past the end repeat the last one and are not absorbed
@@ -675,6 +760,14 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
             vhd[u] = __ldg(reinterpret_cast<const unsigned*>(vr + blk_off));
             kw[u] = load_payload(kr + pay_off);
             vw[u] = load_payload(vr + pay_off);
+            if (ROTOR) {
+                rz0[u] = rz1[u] = 0;
+                if (qjl > 0) {
+                    const unsigned short* rr = reinterpret_cast<const unsigned short*>(res_base) + (size_t)t * qjl;
+                    if (lane < qjl) rz0[u] = __ldg(rr + lane);
+                    if (lane + 32 < qjl) rz1[u] = __ldg(rr + lane + 32);
+                }
+            }
         }
         // the scores of the eight rows for all heads: 8 x G independent dot products and warp reductions, interleaved
         float sc[UN][G];
@@ -690,6 +783,11 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
                 sc[u][r] = 0.f;
 #pragma unroll
                 for (int j = 0; j < EPL; ++j) sc[u][r] = fmaf(qr[r][j], kf[j], sc[u][r]);
+            }
+            if (ROTOR) {
+                const float r0 = __half2float(__ushort_as_half(rz0[u])), r1 = __half2float(__ushort_as_half(rz1[u]));
+#pragma unroll
+                for (int r = 0; r < G; ++r) sc[u][r] = fmaf(qpr[r][1], r1, fmaf(qpr[r][0], r0, sc[u][r]));
             }
         }
 #pragma unroll
@@ -816,9 +914,21 @@ __global__ void __launch_bounds__(kQ8Threads) attn_q8_split_kernel(const AttnPar
             num.x = fmaf(w, v4.x, num.x); num.y = fmaf(w, v4.y, num.y); num.z = fmaf(w, v4.z, num.z); num.w = fmaf(w, v4.w, num.w);
         }
         const float inv = inv_den[r];
+        if (ROTOR) {   // normalised, still in the turned basis
+            qs[r][d4 * 4 + 0] = num.x * inv; qs[r][d4 * 4 + 1] = num.y * inv;
+            qs[r][d4 * 4 + 2] = num.z * inv; qs[r][d4 * 4 + 3] = num.w * inv;
+            continue;
+        }
         __nv_bfloat16* o = p.out + (size_t)b * p.out_stride + (size_t)(kvh * G + r) * HD + d4 * 4;
         o[0] = __float2bfloat16_rn(num.x * inv); o[1] = __float2bfloat16_rn(num.y * inv);
         o[2] = __float2bfloat16_rn(num.z * inv); o[3] = __float2bfloat16_rn(num.w * inv);
+    }
+    if (ROTOR) {
+        __syncthreads();
+        for (int idx = tid; idx < G * NG; idx += kQ8Threads) rotor_turn_group<true>(qs[idx / NG], HD, head_rotors, idx % NG);
+        __syncthreads();
+        for (int idx = tid; idx < G * HD; idx += kQ8Threads)
+            p.out[(size_t)b * p.out_stride + (size_t)kvh * G * HD + idx] = __float2bfloat16_rn(qs[idx / HD][idx % HD]);
     }
 }
 
@@ -1106,9 +1216,20 @@ int launch_attn_decode(const AttnLaunch& a, cudaStream_t s) {
         const int G = a.heads / a.kv_heads;
         if (a.head_dim != 64 && a.head_dim != 128) { set_error("attention: head_dim %d not supported over an 8-bit cache (64 or 128)", a.head_dim); return SWLM_ERR_UNSUPPORTED; }
         if (G != 1 && G != 2 && G != 4 && G != 8) { set_error("attention over an 8-bit cache: %d query heads per KV head (1, 2, 4 or 8)", G); return SWLM_ERR_UNSUPPORTED; }
+        const bool rotor = swlm_kv_is_rotor(a.kv_scheme);
+        if (rotor) {
+            if (!a.rotors || a.qjl_dim < 0 || a.qjl_dim > 64 || (a.qjl_dim > 0 && (!a.qjl_matrix || !a.qjl_res))) {
+                set_error("attention over a rotated cache: rotors, projection matrix or residual rows missing (qjl_dim %d)", a.qjl_dim);
+                return SWLM_ERR_INVALID;
+            }
+            p.rotors = a.rotors; p.qjl_matrix = a.qjl_matrix; p.qjl_res = a.qjl_res; p.qjl_dim = a.qjl_dim;
+        }
 #define SWLM_Q8_CASE(HDV, GV) if (a.head_dim == HDV && G == GV) { \
-            if (p.kv_bits == 8) launch_k(attn_q8_split_kernel<HDV, GV, 8>, grid, dim3(kQ8Threads), 0, s, p); \
-            else launch_k(attn_q8_split_kernel<HDV, GV, 4>, grid, dim3(kQ8Threads), 0, s, p); }
+            if (rotor) { \
+                if (p.kv_bits == 8) launch_k(attn_q8_split_kernel<HDV, GV, 8, true>, grid, dim3(kQ8Threads), 0, s, p); \
+                else launch_k(attn_q8_split_kernel<HDV, GV, 4, true>, grid, dim3(kQ8Threads), 0, s, p); \
+            } else if (p.kv_bits == 8) launch_k(attn_q8_split_kernel<HDV, GV, 8, false>, grid, dim3(kQ8Threads), 0, s, p); \
+            else launch_k(attn_q8_split_kernel<HDV, GV, 4, false>, grid, dim3(kQ8Threads), 0, s, p); }
         SWLM_Q8_CASE(128, 1); SWLM_Q8_CASE(128, 2); SWLM_Q8_CASE(128, 4); SWLM_Q8_CASE(128, 8);
         SWLM_Q8_CASE(64, 1); SWLM_Q8_CASE(64, 2); SWLM_Q8_CASE(64, 4); SWLM_Q8_CASE(64, 8);
 #undef SWLM_Q8_CASE

@@ -615,6 +615,12 @@ struct swlm_state {
     __nv_bfloat16* buf[SWLM_BUF_COUNT] = {};
     int width[SWLM_BUF_COUNT] = {};
     __nv_bfloat16* kcache = nullptr; __nv_bfloat16* vcache = nullptr; size_t kv_layer_elems = 0;
+    // rotated KV schemes: rotors [kv_layers][kv_heads][groups][4], projection matrix [head_dim][qjl_dim], projected K
+    // residuals [kv_layers][seq][kv_heads][max_seq][qjl_dim], all fp16
+    __half* rotors = nullptr; size_t rotor_layer_elems = 0;
+    __half* qjl_matrix = nullptr;
+    __half* qjl_res = nullptr; size_t qjl_layer_elems = 0;
+    std::vector<uint16_t> rotors_host, qjl_matrix_host;   // host copies for the cache probes
     __nv_bfloat16* conv = nullptr; size_t conv_layer_elems = 0;
     __nv_bfloat16* ssm_conv = nullptr; size_t ssm_conv_layer_elems = 0;   // [layer][seq][kernel][conv_dim]
     float* ssm_state = nullptr; size_t ssm_state_layer_elems = 0;         // [layer][seq][heads][key_dim][value_dim]
@@ -656,6 +662,57 @@ struct swlm_snap {
 };
 
 namespace {
+
+// ---- rotated KV schemes on the host: parameters by the reference's rule, and the arithmetic of the cache probes ----
+uint16_t host_f16_bits(float f) { const __half h = __float2half_rn(f); uint16_t u; memcpy(&u, &h, 2); return u; }
+float host_f16_value(uint16_t u) { __half h; memcpy(&h, &u, 2); return __half2float(h); }
+
+// initializeRandomUnitRotors (Buffer/MetalGraphAllocator.swift:349-390): rotor i of [layer][kv_head][group] takes four
+// successive values of the 64-bit LCG x -> x * 6364136223846793005 + 1442695040888963407 started from that map of i,
+// each mapped to [-1, 1) by its top 31 bits, normalised to a unit quaternion in fp32 and stored as fp16 (s, b12, b13, b23).
+void kv_rotor_init_host(int layers, int kv_heads, int groups, std::vector<uint16_t>* out) {
+    const size_t total = (size_t)layers * kv_heads * groups;
+    out->assign(total * 4, 0);
+    const float unit = 1.0f / (float)(1 << 30);
+    for (size_t i = 0; i < total; ++i) {
+        uint64_t h = (uint64_t)i;
+        float c[4];
+        for (int j = 0; j < 4; ++j) {
+            h = h * 6364136223846793005ull + 1442695040888963407ull;
+            c[j] = (float)((int64_t)(h >> 33) - ((int64_t)1 << 30)) * unit;
+        }
+        const float norm = sqrtf(c[0] * c[0] + c[1] * c[1] + c[2] * c[2] + c[3] * c[3]);
+        if (norm < 1e-8f) { c[0] = 1.0f; c[1] = c[2] = c[3] = 0.0f; }
+        else { const float inv = 1.0f / norm; for (int j = 0; j < 4; ++j) c[j] *= inv; }
+        for (int j = 0; j < 4; ++j) (*out)[i * 4 + j] = host_f16_bits(c[j]);
+    }
+}
+// initializeRademacherMatrix (:393-411): entry i of [head_dim][qjl_dim] is +1/sqrt(qjl_dim) when bit 33 of the first
+// LCG value of i is clear, else -1/sqrt(qjl_dim).
+void kv_qjl_matrix_init_host(int head_dim, int qjl_dim, std::vector<uint16_t>* out) {
+    const float scale = 1.0f / sqrtf((float)qjl_dim);
+    const uint16_t pos = host_f16_bits(scale), neg = host_f16_bits(-scale);
+    out->assign((size_t)head_dim * qjl_dim, 0);
+    for (size_t i = 0; i < out->size(); ++i) {
+        const uint64_t h = (uint64_t)i * 6364136223846793005ull + 1442695040888963407ull;
+        (*out)[i] = ((h >> 33) & 1) == 0 ? pos : neg;
+    }
+}
+// rotor_sandwich / rotor_sandwich_inverse over every group of three values of a row (rotor_apply_forward / _inverse,
+// Generator/MetalSourceGenerator+Attention.swift:1807-1884); R = [groups][4] fp16
+void kv_rotor_turn_row_host(float* row, int hd, const uint16_t* R, bool inverse) {
+    for (int g = 0; 3 * g < hd; ++g) {
+        const int base = 3 * g;
+        const float x = row[base], y = base + 1 < hd ? row[base + 1] : 0.0f, z = base + 2 < hd ? row[base + 2] : 0.0f;
+        const float s = host_f16_value(R[4 * g]);
+        float px = host_f16_value(R[4 * g + 3]), py = -host_f16_value(R[4 * g + 2]), pz = host_f16_value(R[4 * g + 1]);
+        if (inverse) { px = -px; py = -py; pz = -pz; }
+        const float tx = 2.0f * (py * z - pz * y), ty = 2.0f * (pz * x - px * z), tz = 2.0f * (px * y - py * x);
+        row[base] = x + s * tx + (py * tz - pz * ty);
+        if (base + 1 < hd) row[base + 1] = y + s * ty + (pz * tx - px * tz);
+        if (base + 2 < hd) row[base + 2] = z + s * tz + (px * ty - py * tx);
+    }
+}
 
 PrefetchTarget prefetch_of(const Launch& L) {
     PrefetchTarget t;
@@ -762,6 +819,11 @@ int enqueue_step(swlm_state* s, bool body_only, cudaStream_t stream, int only_ki
             a.m = m; a.heads = st.heads / plan->ctx->tp_size; a.kv_heads = kv_heads_local(plan); a.head_dim = st.head_dim;
             a.rope_dim = st.rope_dim; a.inv_freq = L.rope_table >= 0 ? plan->rope_tables[L.rope_table].inv_freq : nullptr;
             a.scale = st.scale; a.window = st.window_left; a.kv_scheme = d.kv_scheme;
+            if (swlm_kv_is_rotor(d.kv_scheme)) {
+                a.rotors = s->rotors + (size_t)st.layer * s->rotor_layer_elems;
+                a.qjl_dim = d.kv_qjl_dim; a.qjl_matrix = s->qjl_matrix;
+                a.qjl_res = s->qjl_res ? s->qjl_res + (size_t)st.layer * s->qjl_layer_elems : nullptr;
+            }
             a.q = s->buf[st.in_buf]; a.q_stride = s->width[st.in_buf];
             a.k = s->buf[st.in2_buf]; a.k_stride = s->width[st.in2_buf];
             a.v = s->buf[st.in3_buf]; a.v_stride = s->width[st.in3_buf];
@@ -909,6 +971,7 @@ std::vector<Region> state_regions(swlm_state* s) {
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) r.push_back({s->buf[i], (size_t)d.max_batch * s->width[i] * 2});
     r.push_back({s->kcache, (size_t)d.kv_layers * s->kv_layer_elems * 2});
     r.push_back({s->vcache, (size_t)d.kv_layers * s->kv_layer_elems * 2});
+    r.push_back({s->qjl_res, (size_t)d.kv_layers * s->qjl_layer_elems * 2});
     r.push_back({s->conv, (size_t)d.conv_layers * s->conv_layer_elems * 2});
     r.push_back({s->res2, (size_t)d.max_batch * s->width[SWLM_BUF_RESIDUAL] * 2});
     r.push_back({s->ssm_conv, (size_t)d.ssm_layers * s->ssm_conv_layer_elems * 2});
@@ -1227,6 +1290,11 @@ int enqueue_rows(swlm_state* s, bool wide, const int32_t* tokens, int c, int pos
                 a.inv_freq = plan->rope_tables[ti].inv_freq;
             }
             a.scale = st.scale; a.window = st.window_left; a.kv_scheme = d.kv_scheme;
+            if (swlm_kv_is_rotor(d.kv_scheme)) {   // (only decode steps of many sequences get here with a quantized cache)
+                a.rotors = s->rotors + (size_t)st.layer * s->rotor_layer_elems;
+                a.qjl_dim = d.kv_qjl_dim; a.qjl_matrix = s->qjl_matrix;
+                a.qjl_res = s->qjl_res ? s->qjl_res + (size_t)st.layer * s->qjl_layer_elems : nullptr;
+            }
             a.q = pf[st.in_buf]; a.q_stride = wd[st.in_buf];
             a.k = pf[st.in2_buf]; a.k_stride = wd[st.in2_buf];
             a.v = pf[st.in3_buf]; a.v_stride = wd[st.in3_buf];
@@ -1465,7 +1533,15 @@ int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const sw
     if (!ctx || !steps || n_steps <= 0 || !desc || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
     *out = nullptr;
     if (desc->kv_scheme != 0 && desc->kv_scheme != SWLM_KV_BF16 && !swlm_kv_bits(desc->kv_scheme)) {
-        set_error("KV cache scheme %#x not supported (bf16, 8-bit groups of 32 / 64 / 128, 4-bit groups of 64 / 128)", desc->kv_scheme);
+        set_error("KV cache scheme %#x not supported (bf16, 8-bit groups of 32 / 64 / 128, 4-bit groups of 64 / 128, rotated 8-bit groups of 32 / 4-bit groups of 64)", desc->kv_scheme);
+        return SWLM_ERR_UNSUPPORTED;
+    }
+    if (desc->kv_qjl_dim < 0 || desc->kv_qjl_dim > 64 || (desc->kv_qjl_dim > 0 && !swlm_kv_is_rotor(desc->kv_scheme))) {
+        set_error("kv_qjl_dim %d: 0..64, and only with a rotated KV scheme", desc->kv_qjl_dim);
+        return SWLM_ERR_INVALID;
+    }
+    if (swlm_kv_is_rotor(desc->kv_scheme) && ctx->tp_size > 1) {
+        set_error("rotated KV schemes are not supported under tensor parallelism");
         return SWLM_ERR_UNSUPPORTED;
     }
     if (swlm_kv_bits(desc->kv_scheme) && desc->kv_layers > 0 &&
@@ -1544,6 +1620,26 @@ int swlm_state_create(swlm_plan* plan, swlm_state** out) {
     s->kv_layer_elems = (size_t)d.max_batch * kv_heads_local(plan) * d.max_seq * kv_row_bytes(d) / 2;
     if ((rc = dev_alloc(&s->kcache, (size_t)d.kv_layers * s->kv_layer_elems))) return fail(rc);
     if ((rc = dev_alloc(&s->vcache, (size_t)d.kv_layers * s->kv_layer_elems))) return fail(rc);
+    if (swlm_kv_is_rotor(d.kv_scheme) && d.kv_layers > 0) {
+        // rotors and projection matrix by the reference's deterministic rule (initializeRandomUnitRotors /
+        // initializeRademacherMatrix, Buffer/MetalGraphAllocator.swift:349-411)
+        const int groups = swlm_kv_rotor_groups(d.head_dim);
+        s->rotor_layer_elems = (size_t)d.kv_heads * groups * 4;
+        kv_rotor_init_host(d.kv_layers, d.kv_heads, groups, &s->rotors_host);
+        if ((rc = dev_alloc(&s->rotors, s->rotors_host.size()))) return fail(rc);
+        cudaError_t ce = cudaMemcpy(s->rotors, s->rotors_host.data(), s->rotors_host.size() * 2, cudaMemcpyHostToDevice);
+        if (ce != cudaSuccess) return fail(cuda_fail(ce, "cudaMemcpy(rotors)"));
+        if (d.kv_qjl_dim > 0) {
+            kv_qjl_matrix_init_host(d.head_dim, d.kv_qjl_dim, &s->qjl_matrix_host);
+            if ((rc = dev_alloc(&s->qjl_matrix, s->qjl_matrix_host.size()))) return fail(rc);
+            ce = cudaMemcpy(s->qjl_matrix, s->qjl_matrix_host.data(), s->qjl_matrix_host.size() * 2, cudaMemcpyHostToDevice);
+            if (ce != cudaSuccess) return fail(cuda_fail(ce, "cudaMemcpy(projection matrix)"));
+            s->qjl_layer_elems = (size_t)d.max_batch * d.kv_heads * d.max_seq * d.kv_qjl_dim;
+            if ((rc = dev_alloc(&s->qjl_res, (size_t)d.kv_layers * s->qjl_layer_elems))) return fail(rc);
+            ce = cudaMemset(s->qjl_res, 0, (size_t)d.kv_layers * s->qjl_layer_elems * 2);
+            if (ce != cudaSuccess) return fail(cuda_fail(ce, "cudaMemset(residual rows)"));
+        }
+    }
     s->conv_layer_elems = (size_t)d.max_batch * d.conv_kernel * d.conv_dim;
     if ((rc = dev_alloc(&s->conv, (size_t)d.conv_layers * s->conv_layer_elems))) return fail(rc);
     if ((rc = dev_alloc(&s->res2, (size_t)d.max_batch * s->width[SWLM_BUF_RESIDUAL]))) return fail(rc);
@@ -1591,6 +1687,7 @@ void swlm_state_destroy(swlm_state* s) {
     drop_graphs(s);
     for (int i = 0; i < SWLM_BUF_COUNT; ++i) cudaFree(s->buf[i]);
     cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->conv); cudaFree(s->res2);
+    cudaFree(s->rotors); cudaFree(s->qjl_matrix); cudaFree(s->qjl_res);
     cudaFree(s->ssm_conv); cudaFree(s->ssm_state);
     if (s->tp.tp > 1) {
         for (int r = 0; r < s->tp.tp; ++r)
@@ -1965,12 +2062,16 @@ int swlm_read_kv(swlm_state* s, int which, int layer, int b, int head, int count
     if (rc) return rc;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     const swlm_buffers_desc& d = s->plan->desc;
-    if (swlm_kv_bits(d.kv_scheme)) {   // the dequantised rows, rounded to bf16
+    if (swlm_kv_bits(d.kv_scheme)) {   // the dequantised rows (of a rotated scheme: turned back), rounded to bf16
         std::vector<unsigned char> rows((size_t)count * kv_row_bytes(d));
         SWLM_CUDA(cudaMemcpy(rows.data(), p, rows.size(), cudaMemcpyDeviceToHost));
-        for (int t = 0; t < count; ++t)
-            for (int e = 0; e < d.head_dim; ++e)
-                dst[(size_t)t * d.head_dim + e] = float_to_bf16_bits(kv_q8_read_host(rows.data() + (size_t)t * kv_row_bytes(d), e, d.kv_scheme));
+        std::vector<float> f(d.head_dim);
+        const uint16_t* R = swlm_kv_is_rotor(d.kv_scheme) ? s->rotors_host.data() + ((size_t)layer * d.kv_heads + head) * swlm_kv_rotor_groups(d.head_dim) * 4 : nullptr;
+        for (int t = 0; t < count; ++t) {
+            for (int e = 0; e < d.head_dim; ++e) f[e] = kv_q8_read_host(rows.data() + (size_t)t * kv_row_bytes(d), e, d.kv_scheme);
+            if (R) kv_rotor_turn_row_host(f.data(), d.head_dim, R, true);
+            for (int e = 0; e < d.head_dim; ++e) dst[(size_t)t * d.head_dim + e] = float_to_bf16_bits(f[e]);
+        }
         return SWLM_OK;
     }
     SWLM_CUDA(cudaMemcpy(dst, p, (size_t)count * s->plan->desc.head_dim * 2, cudaMemcpyDeviceToHost));
@@ -1984,17 +2085,65 @@ int swlm_write_kv(swlm_state* s, int which, int layer, int b, int head, int coun
     if (rc) return rc;
     SWLM_CUDA(cudaStreamSynchronize(s->stream));
     const swlm_buffers_desc& d = s->plan->desc;
-    if (swlm_kv_bits(d.kv_scheme)) {   // quantised as an appended row would be
+    if (swlm_kv_bits(d.kv_scheme)) {   // quantised (a rotated scheme: turned first, K rows with their projected residual) as an appended row would be
         std::vector<unsigned char> rows((size_t)count * kv_row_bytes(d));
         std::vector<float> f(d.head_dim);
+        const bool rotor = swlm_kv_is_rotor(d.kv_scheme);
+        const uint16_t* R = rotor ? s->rotors_host.data() + ((size_t)layer * d.kv_heads + head) * swlm_kv_rotor_groups(d.head_dim) * 4 : nullptr;
+        const int qjl = rotor && which == 0 ? d.kv_qjl_dim : 0;
+        std::vector<uint16_t> res((size_t)count * qjl);
         for (int t = 0; t < count; ++t) {
             for (int e = 0; e < d.head_dim; ++e) f[e] = bf16_bits_to_float(src[(size_t)t * d.head_dim + e]);
-            kv_q8_quantise_host(f.data(), d.head_dim, d.kv_scheme, rows.data() + (size_t)t * kv_row_bytes(d));
+            if (R) kv_rotor_turn_row_host(f.data(), d.head_dim, R, false);
+            unsigned char* row = rows.data() + (size_t)t * kv_row_bytes(d);
+            kv_q8_quantise_host(f.data(), d.head_dim, d.kv_scheme, row);
+            if (qjl > 0) {   // qjl_compute_residual (:1983-2013)
+                for (int e = 0; e < d.head_dim; ++e) f[e] -= kv_q8_read_host(row, e, d.kv_scheme);
+                for (int j = 0; j < qjl; ++j) {
+                    float a = 0.0f;
+                    for (int e = 0; e < d.head_dim; ++e) a += f[e] * host_f16_value(s->qjl_matrix_host[(size_t)e * qjl + j]);
+                    res[(size_t)t * qjl + j] = host_f16_bits(a);
+                }
+            }
         }
         SWLM_CUDA(cudaMemcpy(p, rows.data(), rows.size(), cudaMemcpyHostToDevice));
+        if (qjl > 0)
+            SWLM_CUDA(cudaMemcpy(s->qjl_res + (size_t)layer * s->qjl_layer_elems + ((size_t)b * d.kv_heads + head) * d.max_seq * qjl,
+                                 res.data(), res.size() * 2, cudaMemcpyHostToDevice));
         return SWLM_OK;
     }
     SWLM_CUDA(cudaMemcpy(p, src, (size_t)count * s->plan->desc.head_dim * 2, cudaMemcpyHostToDevice));
+    return SWLM_OK;
+}
+
+int swlm_state_get_rotors(swlm_state* s, uint16_t* dst, size_t count) {
+    if (!s || !dst) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    if (count != s->rotors_host.size() || count == 0) { set_error("this state holds %zu rotor values", s->rotors_host.size()); return SWLM_ERR_INVALID; }
+    memcpy(dst, s->rotors_host.data(), count * 2);
+    return SWLM_OK;
+}
+
+int swlm_state_set_rotors(swlm_state* s, const uint16_t* src, size_t count) {
+    if (!s || !src) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    if (count != s->rotors_host.size() || count == 0) { set_error("this state holds %zu rotor values", s->rotors_host.size()); return SWLM_ERR_INVALID; }
+    int rc = ensure_device(s->plan->ctx);
+    if (rc) return rc;
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    s->rotors_host.assign(src, src + count);
+    SWLM_CUDA(cudaMemcpy(s->rotors, src, count * 2, cudaMemcpyHostToDevice));
+    return SWLM_OK;
+}
+
+int swlm_read_qjl(swlm_state* s, int layer, int b, int head, int count, uint16_t* dst) {
+    if (!s || !dst) { set_error("null argument"); return SWLM_ERR_INVALID; }
+    const swlm_buffers_desc& d = s->plan->desc;
+    if (!s->qjl_res) { set_error("this state keeps no projected residuals (kv_qjl_dim 0 or no rotated scheme)"); return SWLM_ERR_STATE; }
+    if (layer < 0 || layer >= d.kv_layers || b < 0 || b >= d.max_batch || head < 0 || head >= d.kv_heads || count < 0 || count > d.max_seq) {
+        set_error("bad KV address"); return SWLM_ERR_INVALID;
+    }
+    SWLM_CUDA(cudaStreamSynchronize(s->stream));
+    SWLM_CUDA(cudaMemcpy(dst, s->qjl_res + (size_t)layer * s->qjl_layer_elems + ((size_t)b * d.kv_heads + head) * d.max_seq * d.kv_qjl_dim,
+                         (size_t)count * d.kv_qjl_dim * 2, cudaMemcpyDeviceToHost));
     return SWLM_OK;
 }
 

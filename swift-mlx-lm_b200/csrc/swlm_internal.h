@@ -278,6 +278,12 @@ struct AttnLaunch {
     int pos_base = -1;
     int window = 0;       // sliding window: the current token and the window - 1 before it; 0 = everything
     int kv_scheme = 0;    // one of the quantized SWLM_KV_* schemes: the cache rows are blocks of 8- or 4-bit values (decode steps only)
+    // rotated schemes: this layer's rotors [kv_heads][ceil(head_dim / 3)][4], the projection matrix [head_dim][qjl_dim]
+    // and this layer's projected K residuals [m][kv_heads][max_seq][qjl_dim] (qjl_dim 0: no correction)
+    const __half* rotors = nullptr;
+    const __half* qjl_matrix = nullptr;
+    __half* qjl_res = nullptr;
+    int qjl_dim = 0;
     PrefetchTarget prefetch;
 };
 int attn_pick_splits(int m, int kv_heads, int max_ctx);

@@ -71,6 +71,7 @@ class BuffersDesc(C.Structure):
         ("ssm_value_dim", C.c_int32),
         ("ssm_conv_kernel", C.c_int32),
         ("kv_scheme", C.c_int32),
+        ("kv_qjl_dim", C.c_int32),
     ]
 
 
@@ -114,6 +115,9 @@ SIGNATURES = {
     "swlm_write_buffer": (_I, [_P, _I, _P, _I]),
     "swlm_read_kv": (_I, [_P, _I, _I, _I, _I, _I, _P]),
     "swlm_write_kv": (_I, [_P, _I, _I, _I, _I, _I, _P]),
+    "swlm_state_get_rotors": (_I, [_P, _P, C.c_size_t]),
+    "swlm_state_set_rotors": (_I, [_P, _P, C.c_size_t]),
+    "swlm_read_qjl": (_I, [_P, _I, _I, _I, _I, _P]),
     "swlm_read_conv": (_I, [_P, _I, _I, _P]),
     "swlm_read_ssm_state": (_I, [_P, _I, _I, _P]),
     "swlm_set_position": (_I, [_P, _I]),

@@ -198,6 +198,22 @@ class InferenceModel:
         d = np.ascontiguousarray(rows_bf16, dtype=np.uint16)
         self.lib.check(self.lib.swlm_write_kv(self.state, which, layer, b, head, d.shape[0], _ptr(d)))
 
+    # rotated KV schemes: the fp16 rotors [kv_layers][kv_heads][ceil(head_dim / 3)][4] and the projected K residuals
+    def rotors(self) -> np.ndarray:
+        d = self.desc
+        out = np.empty((int(d.kv_layers), int(d.kv_heads), (int(d.head_dim) + 2) // 3, 4), dtype=np.uint16)
+        self.lib.check(self.lib.swlm_state_get_rotors(self.state, _ptr(out), out.size))
+        return out
+
+    def set_rotors(self, values_f16_bits: np.ndarray) -> None:
+        v = np.ascontiguousarray(values_f16_bits, dtype=np.uint16).reshape(-1)
+        self.lib.check(self.lib.swlm_state_set_rotors(self.state, _ptr(v), v.size))
+
+    def read_qjl(self, layer: int, b: int, head: int, count: int) -> np.ndarray:
+        out = np.empty((count, int(self.desc.kv_qjl_dim)), dtype=np.uint16)
+        self.lib.check(self.lib.swlm_read_qjl(self.state, layer, b, head, count, _ptr(out)))
+        return out
+
     def read_conv(self, layer: int, b: int) -> np.ndarray:
         out = np.empty((int(self.desc.conv_kernel), int(self.desc.conv_dim)), dtype=np.uint16)
         self.lib.check(self.lib.swlm_read_conv(self.state, layer, b, _ptr(out)))

@@ -69,8 +69,11 @@ class ModelConfig:
     # `ssm_heads` value heads of `ssm_value_dim`, `ssm_groups` key groups of `ssm_key_dim`, a causal conv of
     # `ssm_conv_kernel` taps over the q|k|v channels; tensor names follow Models/Qwen35/Qwen35FamilyNaming.swift:73-87.
     # KV cache elements: 0 = bf16; 0x10 / 0x11 / 0x12 = 8-bit groups of 32 / 64 / 128; 0x40 / 0x41 = 4-bit groups of 64 / 128
-    # (KVCacheSpecification's affine block schemes)
+    # (KVCacheSpecification's affine block schemes); 0x70 / 0x71 = the rotated forms of 0x10 / 0x40 (rows turned by
+    # Cl(3,0) rotors before quantisation), with kv_qjl_dim > 0 (at most 64) plus the projected K residuals that correct
+    # the scores (RotorQuant + QJL, Buffer/MetalGraphAllocator.swift:177-216)
     kv_scheme: int = 0
+    kv_qjl_dim: int = 0
     ssm_heads: int = 0
     ssm_groups: int = 0
     ssm_key_dim: int = 0
@@ -115,7 +118,7 @@ class ModelConfig:
             ssm_groups=self.ssm_groups if self.ssm_layer_count else 0, ssm_key_dim=self.ssm_key_dim if self.ssm_layer_count else 0,
             ssm_value_dim=self.ssm_value_dim if self.ssm_layer_count else 0,
             ssm_conv_kernel=self.ssm_conv_kernel if self.ssm_layer_count else 0,
-            kv_scheme=self.kv_scheme,
+            kv_scheme=self.kv_scheme, kv_qjl_dim=self.kv_qjl_dim,
         )
 
     # Algorithmic weight bytes one decode step streams: 0.5625 bytes per quantized weight.

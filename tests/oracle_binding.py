@@ -109,6 +109,26 @@ class OracleModel:
         d = np.ascontiguousarray(rows, dtype=np.uint16)
         self.dll.orc_write_kv(self.h, which, layer, b, head, d.shape[0], _p(d))
 
+    def rotors(self):
+        out = np.empty(int(self.dll.orc_rotor_count(self.h)), dtype=np.uint16)
+        self.dll.orc_get_rotors(self.h, _p(out))
+        return out
+
+    def set_rotors(self, values):
+        d = np.ascontiguousarray(values, dtype=np.uint16).reshape(-1)
+        assert d.size == int(self.dll.orc_rotor_count(self.h))
+        self.dll.orc_set_rotors(self.h, _p(d))
+
+    def qjl_matrix(self):
+        out = np.empty((int(self.desc.head_dim), int(self.desc.kv_qjl_dim)), dtype=np.uint16)
+        self.dll.orc_get_qjl_matrix(self.h, _p(out))
+        return out
+
+    def read_qjl(self, layer, b, head, count):
+        out = np.empty((count, int(self.desc.kv_qjl_dim)), dtype=np.uint16)
+        assert self.dll.orc_read_qjl(self.h, layer, b, head, count, _p(out)) == 0
+        return out
+
     def read_conv(self, layer, b):
         out = np.empty((int(self.desc.conv_kernel), int(self.desc.conv_dim)), dtype=np.uint16)
         self.dll.orc_read_conv(self.h, layer, b, _p(out))
@@ -143,6 +163,12 @@ class Oracle:
         d.orc_read_kv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         d.orc_write_kv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         d.orc_read_conv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        d.orc_rotor_count.argtypes = [C.c_void_p]
+        d.orc_rotor_count.restype = C.c_int64
+        d.orc_get_rotors.argtypes = [C.c_void_p, C.c_void_p]
+        d.orc_set_rotors.argtypes = [C.c_void_p, C.c_void_p]
+        d.orc_get_qjl_matrix.argtypes = [C.c_void_p, C.c_void_p]
+        d.orc_read_qjl.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         d.orc_q4_dequant_mlx.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         d.orc_staf_repack_mlx.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         d.orc_q4_dequant_staf.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p]

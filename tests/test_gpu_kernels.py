@@ -564,3 +564,108 @@ def test_attention_decode_over_q8_group32_cache(pkg, store, oracle, hd, heads, k
                 step_size = (o.reshape(-1, group).max(-1) - o.reshape(-1, group).min(-1)) / levels
                 assert np.all(np.abs(g - o).reshape(-1, group).max(-1) <= 1.5 * step_size + 2.0 ** -7 * np.abs(o).max())
     gm.close()
+
+
+# ---- rotated KV schemes (rotors + projected K residuals) --------------------------------------------------------------
+
+ROTOR_SCHEMES = {0x70: (8, 32), 0x71: (4, 64)}
+
+
+@pytest.mark.parametrize("scheme,qjl", [(0x70, 0), (0x71, 0), (0x70, 64), (0x71, 16), (0x71, 64)])
+@pytest.mark.parametrize("hd,heads,kvh", [(128, 32, 8), (64, 16, 4)])
+@pytest.mark.parametrize("batch,ctx,window", [(1, 0, 0), (1, 65, 0), (1, 1000, 0), (3, 300, 0), (1, 900, 100)])
+def test_attention_decode_over_rotated_cache(pkg, store, oracle, hd, heads, kvh, batch, ctx, window, scheme, qjl):
+    """Rows turned by the KV head's rotors before they are quantised, q turned likewise, the output turned back, and with
+    qjl > 0 the projected K residuals in the scores (Generator/MetalSourceGenerator+Attention.swift:694-930). The cache
+    is filled through the probe (turned, quantised and projected on the host by both sides), then three decode steps
+    append and attend: outputs, appended rows and their residual rows against the oracle; the default rotors are the
+    oracle's (the reference's deterministic rule)."""
+    bits, group = ROTOR_SCHEMES[scheme]
+    levels = 255.0 if bits == 8 else 15.0
+    P = pkg.plan
+    desc = pkg.BuffersDesc(hidden=256, slot_dim=heads * hd, vocab=512, max_seq=2048, max_batch=batch, kv_layers=1, kv_heads=kvh,
+                           head_dim=hd, conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=scheme, kv_qjl_dim=qjl)
+    store.add_dense("rotor.embed", _bf(pkg, np.zeros((512, 256))))
+    gm = pkg.InferenceModel(store, [P._step(P.STEP_EMBED, out_buf=0, n=256, weight="rotor.embed")], desc)
+    om = oracle.model(desc)
+    assert np.array_equal(gm.rotors().reshape(-1), om.rotors())
+    rng = np.random.default_rng(ctx * 3 + hd + batch + qjl)
+    if ctx:
+        for b in range(batch):
+            for h in range(kvh):
+                kr, vr = _bf(pkg, rng.normal(size=(ctx, hd))), _bf(pkg, rng.normal(size=(ctx, hd)))
+                for mdl in (gm, om):
+                    mdl.write_kv(0, 0, b, h, kr)
+                    mdl.write_kv(1, 0, b, h, vr)
+        assert np.array_equal(gm.read_kv(0, 0, 0, 0, ctx), om.read_kv(0, 0, 0, 0, ctx))
+        if qjl:
+            assert np.array_equal(gm.read_qjl(0, batch - 1, kvh - 1, ctx), om.read_qjl(0, batch - 1, kvh - 1, ctx))
+    step = P._step(P.STEP_ATTN_DECODE, layer=0, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, in3_buf=P.BUF_S3, out_buf=P.BUF_S0,
+                   heads=heads, kv_heads=kvh, head_dim=hd, rope_dim=hd, rope_base=500000.0, scale=1.0 / np.sqrt(hd), window_left=window)
+    steps = 3
+    for i in range(steps):
+        q = _bf(pkg, rng.normal(size=(batch, heads * hd)))
+        k = _bf(pkg, np.pad(rng.normal(size=(batch, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+        v = _bf(pkg, np.pad(rng.normal(size=(batch, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+        for mdl in (gm, om):
+            mdl.set_position(ctx + i)
+            mdl.write_buffer(P.BUF_S1, q)
+            mdl.write_buffer(P.BUF_S2, k)
+            mdl.write_buffer(P.BUF_S3, v)
+            mdl.run_step(step)
+        got = pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, heads * hd))
+        ref = pkg.bf16_to_f32(om.read_buffer(P.BUF_S0, heads * hd))
+        assert rel_err(got, ref).max() <= RTOL, (i, rel_err(got, ref).max())
+    n = ctx + steps
+    for b in range(batch):
+        for h in range(kvh):
+            for which in (0, 1):
+                g = pkg.bf16_to_f32(gm.read_kv(which, 0, b, h, n)[ctx:]).reshape(steps, hd)
+                o = pkg.bf16_to_f32(om.read_kv(which, 0, b, h, n)[ctx:]).reshape(steps, hd)
+                # the rows the device appended, turned back by the probe: a value may sit one quantisation step from the
+                # oracle's (RoPE in fp32 differs in the last bit), and the turn spreads a step over the three values of a group
+                span = np.abs(o).max() * 2.0 / levels
+                assert np.abs(g - o).max() <= 3.0 * span + 2.0 ** -6 * np.abs(o).max()
+                assert np.median(np.abs(g - o)) <= 2.0 ** -7 * np.abs(o).max()
+            if qjl:
+                g = gm.read_qjl(0, b, h, n)[ctx:].view(np.float16).astype(np.float64)
+                o = om.read_qjl(0, b, h, n)[ctx:].view(np.float16).astype(np.float64)
+                assert np.all(np.isfinite(g))
+                assert np.median(np.abs(g - o)) <= 4e-3 * max(np.abs(o).max(), 1e-3)
+                assert np.abs(g - o).max() <= 0.5 * max(np.abs(o).max(), 1e-3) + 1e-3
+    gm.close()
+
+
+def test_identity_rotors_give_the_base_scheme(pkg, store, oracle):
+    """'Identity rotor preserves vector' (RotorQuantCorrectnessTests:500-518) end to end: with every rotor (1, 0, 0, 0) and
+    no residuals the rotated 8-bit scheme computes what the plain 8-bit group-32 scheme computes."""
+    P = pkg.plan
+    hd, heads, kvh, ctx = 128, 8, 2, 200
+    rng = np.random.default_rng(4)
+    kr = [[_bf(pkg, rng.normal(size=(ctx, hd))) for _ in range(2)] for _ in range(kvh)]
+    q = _bf(pkg, rng.normal(size=(1, heads * hd)))
+    k = _bf(pkg, np.pad(rng.normal(size=(1, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+    v = _bf(pkg, np.pad(rng.normal(size=(1, kvh * hd)), ((0, 0), (0, (heads - kvh) * hd))))
+    step = P._step(P.STEP_ATTN_DECODE, layer=0, in_buf=P.BUF_S1, in2_buf=P.BUF_S2, in3_buf=P.BUF_S3, out_buf=P.BUF_S0,
+                   heads=heads, kv_heads=kvh, head_dim=hd, rope_dim=hd, rope_base=10000.0, scale=1.0 / np.sqrt(hd))
+    store.add_dense("rotor.embed", _bf(pkg, np.zeros((512, 256))))
+    outs, rows = [], []
+    for scheme in (0x70, 0x10):
+        desc = pkg.BuffersDesc(hidden=256, slot_dim=heads * hd, vocab=512, max_seq=256, max_batch=1, kv_layers=1, kv_heads=kvh,
+                               head_dim=hd, conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=scheme)
+        gm = pkg.InferenceModel(store, [P._step(P.STEP_EMBED, out_buf=0, n=256, weight="rotor.embed")], desc)
+        if scheme == 0x70:
+            ident = np.zeros(gm.rotors().shape, dtype=np.float16)
+            ident[..., 0] = 1.0
+            gm.set_rotors(ident.view(np.uint16))
+        for h in range(kvh):
+            gm.write_kv(0, 0, 0, h, kr[h][0])
+            gm.write_kv(1, 0, 0, h, kr[h][1])
+        gm.set_position(ctx)
+        gm.write_buffer(P.BUF_S1, q); gm.write_buffer(P.BUF_S2, k); gm.write_buffer(P.BUF_S3, v)
+        gm.run_step(step)
+        outs.append(pkg.bf16_to_f32(gm.read_buffer(P.BUF_S0, heads * hd)))
+        rows.append(gm.read_kv(0, 0, 0, 1, ctx + 1))
+        gm.close()
+    assert np.array_equal(rows[0], rows[1])
+    assert rel_err(outs[0], outs[1]).max() <= 2.0 ** -7

@@ -260,15 +260,16 @@ def test_recurrent_layers_chunked_prompt_and_many_sequences(pkg, oracle):
     gm.close(); store.close()
 
 
-@pytest.mark.parametrize("family,batch,scheme", [("llama", 1, 0x10), ("llama", 3, 0x10), ("lfm2", 1, 0x10), ("llama", 20, 0x10),
-                                                 ("llama", 1, 0x11), ("llama", 2, 0x40)])
-def test_q8_kv_cache_model_against_oracle(pkg, oracle, family, batch, scheme):
+@pytest.mark.parametrize("family,batch,scheme,qjl", [("llama", 1, 0x10, 0), ("llama", 3, 0x10, 0), ("lfm2", 1, 0x10, 0), ("llama", 20, 0x10, 0),
+                                                     ("llama", 1, 0x11, 0), ("llama", 2, 0x40, 0),
+                                                     ("llama", 1, 0x70, 0), ("llama", 2, 0x71, 16), ("llama", 20, 0x71, 64)])
+def test_q8_kv_cache_model_against_oracle(pkg, oracle, family, batch, scheme, qjl):
     """The whole plan over a quantized KV cache (8-bit groups of 32 or 64, 4-bit groups of 64; prompt token by token,
     then decode; 20 sequences through the row-wise executor): tokens and logits against the oracle, which quantises
     and reads the cache by the same rule."""
     import dataclasses
     cfg = (small_llama if family == "llama" else small_lfm2)(pkg, batch=batch, max_seq=128)
-    cfg = dataclasses.replace(cfg, kv_scheme=scheme)
+    cfg = dataclasses.replace(cfg, kv_scheme=scheme, kv_qjl_dim=qjl)   # 0x70 / 0x71: the rotated schemes, with K residuals when qjl > 0
     # (the small LFM2-like model runs with one sequence here: with 2 or 3 sequences, i.e. through the fp16 GEMV kernel,
     # its random weights have an input, the 40-token prompt of seed 11, at which a gated conv output nearly cancels and
     # the next norm blows rounding noise up to a different answer than the oracle's; with a bf16 cache just the same)
