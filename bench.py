@@ -122,11 +122,12 @@ def metric_name(args):
     if args.model == "llama" and args.batch == 1 and getattr(args, "kv", "bf16") == "bf16":
         return METRIC
     return f"4-bit decode tok/s, {'LFM2-1.2B-like' if args.model == 'lfm2' else 'Llama-3-8B'} shape bs{args.batch}" + (
-        ", 8-bit KV" if getattr(args, "kv", "bf16") == "q8" else "")
+        {"bf16": "", "q8": ", 8-bit KV"}.get(getattr(args, "kv", "bf16"), ", rotated 4-bit KV"))
 
 
 def workload_name(args):
-    kv = ", 8-bit group-32 KV cache" if getattr(args, "kv", "bf16") == "q8" else ""
+    kv = {"bf16": "", "q8": ", 8-bit group-32 KV cache", "rotor-q4": ", rotated 4-bit group-64 KV cache",
+          "rotor-q4-qjl16": ", rotated 4-bit group-64 KV cache with 16 projected K residuals per row"}[getattr(args, "kv", "bf16")]
     return shape_name(args) + f", 4-bit g64 weights, batch {args.batch}, greedy decode at context {args.ctx}" + kv
 
 
@@ -320,7 +321,9 @@ def main():
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--model", choices=["llama", "lfm2"], default="llama", help="llama: Llama-3-8B shape; lfm2: the hybrid conv/attention shape")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (1..64), all at the same position")
-    ap.add_argument("--kv", choices=["bf16", "q8"], default="bf16", help="KV cache elements: bf16, or 8-bit groups of 32 (36-byte blocks)")
+    ap.add_argument("--kv", choices=["bf16", "q8", "rotor-q4", "rotor-q4-qjl16"], default="bf16",
+                    help="KV cache elements: bf16, 8-bit groups of 32 (36-byte blocks), or the rotated 4-bit groups of 64 "
+                         "(the reference's default policy for plain transformer graphs), optionally with 16 projected K residuals per row")
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -355,6 +358,8 @@ def main():
     cfg = model_config(pkg, args, max_seq, world)
     if args.kv == "q8":
         cfg = dataclasses.replace(cfg, kv_scheme=0x10)
+    elif args.kv.startswith("rotor-q4"):
+        cfg = dataclasses.replace(cfg, kv_scheme=0x71, kv_qjl_dim=16 if args.kv.endswith("qjl16") else 0)
         if args.prefill == "real":
             args.prefill = "synthetic"   # prompts over an 8-bit cache go token by token; the timed region is the decode
     builder = pkg.DispatchPlanBuilder(cfg)
@@ -474,8 +479,9 @@ def main():
         attn_ms = a0.elapsed_time(a1) / reps
 
     weight_bytes = cfg.q4_weight_elems() * 0.5625 / world            # per GPU, per step
-    kv_row_bytes = cfg.head_dim // 32 * 36 if args.kv == "q8" else cfg.head_dim * 2
+    kv_row_bytes = {"bf16": cfg.head_dim * 2, "q8": cfg.head_dim // 32 * 36}.get(args.kv, cfg.head_dim // 64 * 36)
     kv_bytes = args.batch * cfg.kv_layer_count * (cfg.kv_heads // world) * kv_row_bytes * 2 * model.position
+    kv_bytes += args.batch * cfg.kv_layer_count * cfg.kv_heads * cfg.kv_qjl_dim * 2 * model.position   # projected K residuals
     n_gemv = sum(1 for l in model.describe().splitlines() if "qgemv" in l)
     kernel_name = "qgemv1_kernel" if args.batch == 1 else "qgemv_kernel"
     kernel_scope = "all %d launches of one decode step, timed back to back" % n_gemv
@@ -493,7 +499,7 @@ def main():
         # an estimate carried over from that capture, not a counter read in this run
         "traffic": weight_bytes / n_gemv * NCU_TRAFFIC_RATIO,
         "traffic_source": "estimate: ncu capture of the four product shapes of one layer, ratio %.4f to algorithmic bytes" % NCU_TRAFFIC_RATIO,
-        "attention": {"kernel": "attn_q8_split_kernel" if args.kv == "q8" else "attn_split_kernel", "bytes_per_step": kv_bytes,
+        "attention": {"kernel": "attn_split_kernel" if args.kv == "bf16" else "attn_q8_split_kernel", "bytes_per_step": kv_bytes,
                       "achieved": kv_bytes / (attn_ms * 1e-3) / 1e9, "unit": "GB/s"},
         "whole_step": {"weight_bytes": weight_bytes, "weight_GBs": weight_bytes / (ms / args.steps * 1e-3) / 1e9,
                        "weight_plus_kv_GBs": (weight_bytes + kv_bytes) / (ms / args.steps * 1e-3) / 1e9,
