@@ -7,6 +7,16 @@ public struct CUDAPromptSnapshot {
     let handle: OpaquePointer
 }
 
+extension swlm_buffers_desc {
+    /// InferencePolicy.kvCache (Sources/MetalCompiler/InferencePolicy.swift:55-86) into the plan description: the raw value
+    /// of the resolved QuantizationSchemeIdentifier (0x01 bf16, 0x10 / 0x11 / 0x12, 0x40 / 0x41, rotated 0x70 / 0x71; one
+    /// scheme for K and V) and the projection dimension of the rotated schemes' K residuals (0 = none, at most 64).
+    public mutating func setKVCache(schemeRawValue: UInt8, qjlDimension: Int = 0) {
+        kv_scheme = Int32(schemeRawValue)
+        kv_qjl_dim = Int32(qjlDimension)
+    }
+}
+
 public final class CUDAInferenceModel {
     let store: CUDAWeightStore
     let plan: OpaquePointer

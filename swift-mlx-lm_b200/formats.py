@@ -91,23 +91,41 @@ def _align_up(v: int, a: int) -> int:
     return (v + a - 1) // a * a
 
 
+# KV scheme identifier -> (values per block, bytes per block); dense schemes are one value per "block"
+# (QuantizationFormatRegistry as KVCacheSpecification.resolveBlockLayout uses it, MetalGraphAllocator.swift:71-79)
+KV_BLOCK_LAYOUTS = {0x00: (1, 2), 0x01: (1, 2), 0x02: (1, 4), 0x10: (32, 36), 0x11: (64, 68), 0x12: (128, 132),
+                    0x40: (64, 36), 0x41: (128, 68), 0x42: (128, 68)}
+KV_ROTOR_BASE = {0x70: 0x10, 0x71: 0x40}   # the rotated schemes store the block layout of their base scheme
+
+
 @dataclass(frozen=True)
 class KVCacheSpecification:
-    """Sizing contract of the reference's dense bf16 KV cache (scheme 0x01, sequence-major layout).
+    """Sizing contract of the reference's KV cache (sequence-major layout; dense bf16 = scheme 0x01 by default).
 
-    The device layout of this build packs head slots without the 256-byte padding (it only matters for
-    head_dim < 128); the figures below are the reference's, kept for the sizing contract tests.
+    The device layout of this build packs head slots without the reference's padding (256 bytes for dense, 64 bytes
+    for block-quantized slots); the figures below are the reference's, kept for the sizing contract tests.
     """
 
     layer_count: int
     kv_head_count: int
     head_dimension: int
     maximum_sequence_length: int
+    scheme: int = 0x01
 
     token_slot_alignment = 256  # dense formats (MetalGraphAllocator.swift:90-114)
 
+    @property
+    def uses_rotor_quant(self) -> bool:
+        return self.scheme in KV_ROTOR_BASE
+
+    def slot_alignment(self) -> int:
+        weights_per_block, _ = KV_BLOCK_LAYOUTS[KV_ROTOR_BASE.get(self.scheme, self.scheme)]
+        return 64 if weights_per_block > 1 else self.token_slot_alignment
+
     def bytes_per_head_slot(self) -> int:
-        return _align_up(self.head_dimension * 2, self.token_slot_alignment)
+        weights_per_block, bytes_per_block = KV_BLOCK_LAYOUTS[KV_ROTOR_BASE.get(self.scheme, self.scheme)]
+        blocks = (self.head_dimension + weights_per_block - 1) // weights_per_block
+        return _align_up(blocks * bytes_per_block, self.slot_alignment())
 
     def bytes_per_token_slot(self) -> int:
         return self.kv_head_count * self.bytes_per_head_slot()
@@ -118,6 +136,26 @@ class KVCacheSpecification:
     def total_bytes(self) -> int:
         """K plus V over all layers for one sequence."""
         return 2 * self.layer_count * self.bytes_per_layer()
+
+    # rotated schemes (MetalGraphAllocator.swift:177-216): one rotor (s, b12, b13, b23) of fp16 per KV head and group of
+    # three values; with a projection dimension m > 0 a shared [head_dim][m] fp16 matrix and m fp16 values per cached K row
+    def num_rotor_groups(self) -> int:
+        return (self.head_dimension + 2) // 3
+
+    def rotor_parameters_bytes_per_layer(self) -> int:
+        return self.kv_head_count * self.num_rotor_groups() * 4 * 2
+
+    def total_rotor_parameters_size(self) -> int:
+        return self.layer_count * self.rotor_parameters_bytes_per_layer()
+
+    def qjl_matrix_size(self, qjl_dimension: int) -> int:
+        return self.head_dimension * qjl_dimension * 2 if qjl_dimension > 0 else 0
+
+    def qjl_residual_bytes_per_layer(self, qjl_dimension: int) -> int:
+        return self.maximum_sequence_length * self.kv_head_count * qjl_dimension * 2 if qjl_dimension > 0 else 0
+
+    def total_qjl_residual_size(self, qjl_dimension: int) -> int:
+        return self.layer_count * self.qjl_residual_bytes_per_layer(qjl_dimension)
 
     def sequence_major_offset(self, layer: int, head: int, position: int) -> int:
         head_stride = self.maximum_sequence_length * self.bytes_per_head_slot()

@@ -41,6 +41,30 @@ def test_kv_cache_sizing_contract(pkg):
     assert small.sequence_major_offset(1, 2, 3) == 1 * 8 * 16 * 256 + 2 * 16 * 256 + 3 * 256
 
 
+def test_kv_cache_sizing_of_block_and_rotated_schemes(pkg):
+    # Tests/MetalCompilerTests/Core/KVCacheSizingContractTests.swift:32-80, 100-125 (rotated schemes size like their base);
+    # Tests/MetalCompilerTests/Models/RotorQuant/RotorQuantCorrectnessTests.swift:52-67, 163-202
+    def spec(scheme, hd=128, layers=16, seq=4096):
+        return pkg.KVCacheSpecification(layer_count=layers, kv_head_count=8, head_dimension=hd, maximum_sequence_length=seq, scheme=scheme)
+    assert spec(0x00).bytes_per_head_slot() == 256 and spec(0x01, hd=192).bytes_per_head_slot() == 512 and spec(0x02).bytes_per_head_slot() == 512
+    assert spec(0x10).bytes_per_head_slot() == 192     # 4 blocks x 36 = 144 -> 64-byte slots
+    assert spec(0x11).bytes_per_head_slot() == 192     # 2 x 68 = 136
+    assert spec(0x40).bytes_per_head_slot() == 128     # 2 x 36 = 72
+    assert spec(0x42).bytes_per_head_slot() == 128     # 1 x 68
+    assert spec(0x70).bytes_per_head_slot() == spec(0x10).bytes_per_head_slot() and spec(0x71).bytes_per_head_slot() == spec(0x40).bytes_per_head_slot()
+    assert spec(0x70).uses_rotor_quant and spec(0x71).uses_rotor_quant and not spec(0x10).uses_rotor_quant and not spec(0x01).uses_rotor_quant
+    assert [spec(0x70, hd=h).num_rotor_groups() for h in (3, 4, 6, 64, 128, 1)] == [1, 2, 2, 22, 43, 1]
+    r = spec(0x70)
+    assert r.rotor_parameters_bytes_per_layer() == 8 * 43 * 4 * 2 and r.total_rotor_parameters_size() == 8 * 43 * 4 * 2 * 16
+    assert r.qjl_matrix_size(16) == 128 * 16 * 2
+    assert r.qjl_residual_bytes_per_layer(16) == 4096 * 8 * 16 * 2 and r.total_qjl_residual_size(16) == 4096 * 8 * 16 * 2 * 16
+    assert r.qjl_matrix_size(0) == 0 and r.qjl_residual_bytes_per_layer(0) == 0 and r.total_qjl_residual_size(0) == 0
+    # the C header's helpers agree on the unpadded rows this build stores (144 / 72 bytes for head_dim 128)
+    desc = pkg.ModelConfig(family="llama", hidden=256, intermediate=512, layers=2, heads=4, kv_heads=2, head_dim=128, vocab=512,
+                           max_seq=64, kv_scheme=0x71, kv_qjl_dim=16).buffers_desc()
+    assert desc.kv_scheme == 0x71 and desc.kv_qjl_dim == 16
+
+
 def test_llama_plan_shape(pkg):
     cfg = pkg.llama3_8b_config()
     b = pkg.DispatchPlanBuilder(cfg)
