@@ -169,7 +169,9 @@ typedef struct swlm_buffers_desc {
 enum {
     SWLM_KV_BF16 = 0x01,
     SWLM_KV_Q8G32 = 0x10, SWLM_KV_Q8G64 = 0x11, SWLM_KV_Q8G128 = 0x12,   /* 36 / 68 / 132 bytes per block */
-    SWLM_KV_Q4G64 = 0x40, SWLM_KV_Q4G128 = 0x41,                         /* 36 / 68 bytes per block */
+    SWLM_KV_Q4G64 = 0x40, SWLM_KV_Q4G128 = 0x41, SWLM_KV_Q4G128Z = 0x42, /* 36 / 68 / 68 bytes per block (0x42, the
+                                                                            reference's q4Group128ScaleF16Zero, reads and
+                                                                            writes cache rows exactly as 0x41 does) */
     SWLM_KV_ROTOR_Q8G32 = 0x70, SWLM_KV_ROTOR_Q4G64 = 0x71               /* rotated rows in the layout of 0x10 / 0x40 */
 };
 static inline int swlm_kv_is_rotor(int scheme) { return scheme == 0x70 || scheme == 0x71; }
@@ -179,11 +181,11 @@ static inline int swlm_kv_rotor_groups(int head_dim) { return (head_dim + 2) / 3
 /* bits per value (0: dense), values per group, bytes per block and bytes per row of head_dim values */
 static inline int swlm_kv_bits(int scheme) {
     scheme = swlm_kv_base_scheme(scheme);
-    return scheme >= 0x10 && scheme <= 0x12 ? 8 : (scheme == 0x40 || scheme == 0x41) ? 4 : 0;
+    return scheme >= 0x10 && scheme <= 0x12 ? 8 : (scheme >= 0x40 && scheme <= 0x42) ? 4 : 0;
 }
 static inline int swlm_kv_group(int scheme) {
     scheme = swlm_kv_base_scheme(scheme);
-    return scheme == 0x10 ? 32 : (scheme == 0x11 || scheme == 0x40) ? 64 : (scheme == 0x12 || scheme == 0x41) ? 128 : 0;
+    return scheme == 0x10 ? 32 : (scheme == 0x11 || scheme == 0x40) ? 64 : (scheme == 0x12 || scheme == 0x41 || scheme == 0x42) ? 128 : 0;
 }
 static inline int swlm_kv_block_bytes(int scheme) { return swlm_kv_bits(scheme) ? 4 + swlm_kv_group(scheme) * swlm_kv_bits(scheme) / 8 : 0; }
 static inline int swlm_kv_row_bytes(int scheme, int head_dim) {

@@ -1533,7 +1533,7 @@ int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const sw
     if (!ctx || !steps || n_steps <= 0 || !desc || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
     *out = nullptr;
     if (desc->kv_scheme != 0 && desc->kv_scheme != SWLM_KV_BF16 && !swlm_kv_bits(desc->kv_scheme)) {
-        set_error("KV cache scheme %#x not supported (bf16, 8-bit groups of 32 / 64 / 128, 4-bit groups of 64 / 128, rotated 8-bit groups of 32 / 4-bit groups of 64)", desc->kv_scheme);
+        set_error("KV cache scheme %#x not supported (0x01 bf16; 0x10 / 0x11 / 0x12 8-bit groups of 32 / 64 / 128; 0x40 / 0x41 / 0x42 4-bit groups of 64 / 128 / 128; 0x70 / 0x71 rotated 8-bit groups of 32 / 4-bit groups of 64)", desc->kv_scheme);
         return SWLM_ERR_UNSUPPORTED;
     }
     if (desc->kv_qjl_dim < 0 || desc->kv_qjl_dim > 64 || (desc->kv_qjl_dim > 0 && !swlm_kv_is_rotor(desc->kv_scheme))) {

@@ -68,7 +68,7 @@ class ModelConfig:
     # (Sources/LMArchitecture/Declaration/Components/DeltaNet.swift, Primitives/SSMRecurrenceFragment.swift) with
     # `ssm_heads` value heads of `ssm_value_dim`, `ssm_groups` key groups of `ssm_key_dim`, a causal conv of
     # `ssm_conv_kernel` taps over the q|k|v channels; tensor names follow Models/Qwen35/Qwen35FamilyNaming.swift:73-87.
-    # KV cache elements: 0 = bf16; 0x10 / 0x11 / 0x12 = 8-bit groups of 32 / 64 / 128; 0x40 / 0x41 = 4-bit groups of 64 / 128
+    # KV cache elements: 0 = bf16; 0x10 / 0x11 / 0x12 = 8-bit groups of 32 / 64 / 128; 0x40 / 0x41 / 0x42 = 4-bit groups of 64 / 128 / 128
     # (KVCacheSpecification's affine block schemes); 0x70 / 0x71 = the rotated forms of 0x10 / 0x40 (rows turned by
     # Cl(3,0) rotors before quantisation), with kv_qjl_dim > 0 (at most 64) plus the projected K residuals that correct
     # the scores (RotorQuant + QJL, Buffer/MetalGraphAllocator.swift:177-216)

@@ -508,7 +508,7 @@ def test_ssm_recurrence_matches_oracle_over_steps(pkg, store, oracle, heads, gro
 
 # ---- 8-bit KV cache ----------------------------------------------------------------------------------------
 
-KV_SCHEMES = {0x10: (8, 32), 0x11: (8, 64), 0x12: (8, 128), 0x40: (4, 64), 0x41: (4, 128)}
+KV_SCHEMES = {0x10: (8, 32), 0x11: (8, 64), 0x12: (8, 128), 0x40: (4, 64), 0x41: (4, 128), 0x42: (4, 128)}
 
 
 @pytest.mark.parametrize("scheme", sorted(KV_SCHEMES))

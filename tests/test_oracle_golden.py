@@ -129,12 +129,12 @@ def test_attention_sliding_window_against_fp64_softmax(pkg, oracle, window):
             assert np.max(np.abs(out[h] - w @ vals)) < 2e-2
 
 
-@pytest.mark.parametrize("scheme,bits,group", [(0x10, 8, 32), (0x11, 8, 64), (0x40, 4, 64)])
+@pytest.mark.parametrize("scheme,bits,group", [(0x10, 8, 32), (0x11, 8, 64), (0x40, 4, 64), (0x42, 4, 128)])
 def test_attention_over_q8_group32_cache_against_fp64(pkg, oracle, scheme, bits, group):
     """8-bit KV rows (36-byte blocks of 32 values, Generator/MetalSourceGenerator+Attention.swift:1923-1956, 2057-2101):
     the rows the oracle appends dequantise to within half a quantisation step of what was written, and attention over
     them equals an fp64 softmax over the DEQUANTISED rows plus the current token's unrounded k and v."""
-    H, KV, D, T = 4, 2, 64, 10
+    H, KV, D, T = 4, 2, max(64, group), 10
     rng = np.random.default_rng(5)
     bf = lambda a: pkg.bf16_to_f32(pkg.f32_to_bf16(np.asarray(a, dtype=np.float32)))
     q, k, v = bf(rng.normal(size=(T, H * D))), bf(rng.normal(size=(T, KV * D))), bf(rng.normal(size=(T, KV * D)))
