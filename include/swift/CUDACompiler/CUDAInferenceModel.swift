@@ -113,4 +113,18 @@ public final class CUDAInferenceModel {
     }
 
     public func setPrefillChunk(tokens: Int) throws { try swlmCheck(swlm_state_set_prefill_chunk(state, Int32(tokens))) }
+
+    // ---- rotated KV schemes: MetalKVCache.rotorParameters (Buffer/MetalGraphAllocator.swift:258-262) --------------------
+
+    /// fp16 bit patterns [kvLayers][kvHeads][ceil(headDimension / 3)][4] = (s, b12, b13, b23) per rotor.
+    public func rotorParameters(count: Int) throws -> [UInt16] {
+        var out = [UInt16](repeating: 0, count: count)
+        try out.withUnsafeMutableBufferPointer { try swlmCheck(swlm_state_get_rotors(state, $0.baseAddress, $0.count)) }
+        return out
+    }
+
+    /// Replaces every rotor; call before the first token is cached (rows already in the cache were turned by the old ones).
+    public func setRotorParameters(_ values: [UInt16]) throws {
+        try values.withUnsafeBufferPointer { try swlmCheck(swlm_state_set_rotors(state, $0.baseAddress, $0.count)) }
+    }
 }
