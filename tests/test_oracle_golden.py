@@ -453,3 +453,26 @@ def test_attention_over_rotated_cache_against_fp64(pkg, oracle, scheme, bits, gr
         got = m.read_qjl(0, 0, 0, T).view(np.float16).astype(np.float64)
         assert np.max(np.abs(got - res[:, 0])) <= 2e-3 * max(1.0, np.abs(res).max())
         assert np.isfinite(err_fixed).all() and len(err_fixed) == len(err_plain)
+
+
+def test_q4_embedding_lookup_known_answer(pkg, oracle):
+    """QuantizedEmbeddingKernelTests.q4EmbeddingExecution (Tests/MetalCompilerTests/Core/QuantizedEmbeddingKernelTests.swift:
+    48-53, 152-245): a table of two 64-wide rows whose block is fp16 scale 1 | fp16 zero 0 | every nibble = 1 (row 0) or 2
+    (row 1); looking up token 1 gives 64 times 2.0. Checked on the block bytes the test builds, and through the plan's
+    embedding step over the same table in MLX packing."""
+    tokens = [1, 2]
+    blocks = np.zeros((2, 36), dtype=np.uint8)
+    for r, v in enumerate(tokens):
+        blocks[r, 0:2] = np.array([1.0], dtype=np.float16).view(np.uint8)
+        blocks[r, 2:4] = np.array([0.0], dtype=np.float16).view(np.uint8)
+        blocks[r, 4:] = v | (v << 4)
+    deq = oracle.dequant_staf(blocks, 2, 64)
+    assert np.array_equal(deq[1], np.full(64, 2.0, dtype=np.float32)) and np.array_equal(deq[0], np.full(64, 1.0, dtype=np.float32))
+    w = np.array([[int("".join([format(v, "x")] * 8), 16)] * 8 for v in tokens], dtype=np.uint32)   # 8 nibbles per word, 8 words
+    one, zero = pkg.f32_to_bf16(np.ones((2, 1), dtype=np.float32)), pkg.f32_to_bf16(np.zeros((2, 1), dtype=np.float32))
+    desc = pkg.BuffersDesc(hidden=64, slot_dim=64, vocab=8, max_seq=4, max_batch=1, kv_layers=0, kv_heads=0, head_dim=0,
+                           conv_layers=0, conv_dim=0, conv_kernel=0)
+    m = oracle.model(desc)
+    m.add_q4("table", w, one, zero)
+    m.run_step(pkg.plan._step(pkg.plan.STEP_EMBED, out_buf=0, n=64, weight="table"), token_in=[1])
+    assert np.array_equal(pkg.bf16_to_f32(m.read_buffer(0, 64))[0], np.full(64, 2.0, dtype=np.float32))
