@@ -8,6 +8,7 @@ repository's oracle or kernels. Sources (paths relative to the reference project
   gemv_single_block   Tests/MetalCompilerTests/Core/UnifiedGEMVBitLevelTests.swift:114-122, 205-208, 247-255
   gemv_multi_row      Tests/MetalCompilerTests/Core/UnifiedGEMVMultiRowTests.swift:108-176 and
                       Tests/MetalCompilerTests/Core/STAFEndToEndGEMVTests.swift:137-160, 252-255, 295-320
+  gemv_multi_block_*  Tests/MetalCompilerTests/Core/UnifiedGEMVMultiBlockTests.swift:51-60, 108-215 (Q4G64, Q4G128)
   dequant_block       Tests/MetalCompilerTests/Core/UnifiedDequantBitLevelTests.swift:129-137
   staf_roundtrip_*    Tests/MetalCompilerTests/Core/STAFQuantizedRoundtripTests.swift:133-143, 159-171, 187-198, 225-240
   attention_pattern   Tests/MetalCompilerTests/Core/AttentionSequenceEquivalenceTests.swift:21-43, 94-103
@@ -75,6 +76,22 @@ def gemv_multi_row(rows=4, blocks=4):
         q.append(qr); scales.append(sr); zeros.append(zr); expected.append(float(e))
     return {"rows": rows, "blocks": blocks, "q": q, "scales": scales, "zeros": zeros,
             "x": [float(v) for v in x], "expected": expected, "abs_tol": 0.03, "rel_tol": 0.03}
+
+
+def gemv_multi_block(weights_per_block, blocks=4):
+    """One output row over `blocks` consecutive blocks with their own scale and zero; fp32 expectation in block order."""
+    total = weights_per_block * blocks
+    x = [F(np.float16(F(F(k % 11) * F(0.0625)) - F(0.3))) for k in range(total)]
+    q, scales, zeros = [], [], []
+    e = F(0)
+    for b in range(blocks):
+        scale, zero = F(F(0.0625) * F(b + 1)), F(F(-0.25) + F(0.125) * F(b))
+        qb = [(k + b * 7) % 16 for k in range(weights_per_block)]
+        for k in range(weights_per_block):
+            e = F(e + F(F(scale * F(qb[k]) + zero) * x[b * weights_per_block + k]))
+        q += qb; scales.append(float(scale)); zeros.append(float(zero))
+    return {"group": weights_per_block, "blocks": blocks, "q": q, "scales": scales, "zeros": zeros,
+            "x": [float(v) for v in x], "expected": float(e), "abs_tol": 0.03, "rel_tol": 0.03}
 
 
 def dequant_block():
@@ -182,6 +199,8 @@ def main():
     data = {
         "gemv_single_block": gemv_single_block(),
         "gemv_multi_row": gemv_multi_row(),
+        "gemv_multi_block_g64": gemv_multi_block(64),
+        "gemv_multi_block_g128": gemv_multi_block(128),
         "dequant_block": dequant_block(),
         "staf_roundtrip_single": staf_roundtrip_single(),
         "staf_roundtrip_multi": staf_roundtrip_multi(),

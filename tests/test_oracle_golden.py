@@ -50,6 +50,31 @@ def test_gemv_multi_row_and_staf_end_to_end(pkg, oracle, golden):
     assert np.array_equal(oracle.dequant_mlx(w, s, z), oracle.dequant_staf(blocks, g["rows"], k))
 
 
+@pytest.mark.parametrize("case", ["gemv_multi_block_g64", "gemv_multi_block_g128"])
+def test_gemv_multi_block_aggregates_across_blocks(pkg, oracle, golden, case):
+    """UnifiedGEMVMultiBlockTests 'Q4G64 / Q4G128 multi-block GEMV aggregates across blocks': four consecutive blocks of
+    one row, each with its own scale and zero; the dequantised weights are exact, the product of the fp32-weight route
+    stays within the reference's tolerance of its fp32 expectation (and within 1e-4 in fp64 with the exact inputs)."""
+    g = golden[case]
+    group, k = g["group"], g["group"] * g["blocks"]
+    w = _pack(pkg, [g["q"]])
+    s, z = _bf(pkg, [g["scales"]]), _bf(pkg, [g["zeros"]])
+    assert np.array_equal(pkg.bf16_to_f32(s)[0], np.array(g["scales"], dtype=np.float32))   # exact in bf16 and fp16
+    blocks = oracle.staf_repack_group(w, s, z, group)
+    assert blocks.shape == (1, g["blocks"], 4 + group // 2)
+    deq = oracle.dequant_staf_group(blocks, 1, k, group)[0]
+    want = np.repeat(np.array(g["scales"], dtype=np.float32), group) * np.array(g["q"], dtype=np.float32) + np.repeat(np.array(g["zeros"], dtype=np.float32), group)
+    assert np.array_equal(deq, want)
+    x = np.array(g["x"], dtype=np.float32)
+    tol = max(g["abs_tol"], g["rel_tol"] * abs(g["expected"]))
+    assert abs(float(deq.astype(np.float64) @ x.astype(np.float64)) - g["expected"]) < 1e-4
+    if group == 64:
+        assert float(oracle.staf_gemv_f32(blocks, 1, k, x)[0]) == pytest.approx(g["expected"], abs=2e-6)   # same fp32 loop, same order
+    # the product routes take bf16 activations: the test's fp16 inputs rounded once more (well inside the tolerance)
+    y = oracle.qgemm(pkg.f32_to_bf16(x)[None, :], w, s, z)
+    assert abs(float(pkg.bf16_to_f32(y)[0, 0]) - g["expected"]) < tol
+
+
 def test_dequant_block_bits(pkg, oracle, golden):
     g = golden["dequant_block"]
     w = _pack(pkg, [g["q"]])
