@@ -243,3 +243,39 @@ def test_recurrent_layer_tensors_keep_fp32(pkg, staf, tmp_path):
     assert sorted(rec.f32) == ["model.layers.0.linear_attn.A_log", norm]
     assert np.array_equal(rec.f32["model.layers.0.linear_attn.A_log"], weights["model.layers.0.linear_attn.A_log"])
     assert "model.layers.0.linear_attn.dt_bias" in rec.dense and "model.layers.0.linear_attn.conv1d.weight" in rec.dense
+
+
+def test_many_tensors_long_names_edge_values_and_shards(pkg, staf, tmp_path):
+    """File-level properties of the reference's STAFDeepTests (Tests/MetalCompilerTests/Core/STAFDeepTests.swift:222-290
+    '100 tensors load at non-overlapping offsets', :703-745 'payload starts at 256-byte aligned offset', :746-791 'shapes
+    survive', :792-846 'Float16 edge values survive', :847-913 'Multiple safetensors shards merge', :958-996 'Long tensor
+    names survive'), on this package's converter, writer and reader."""
+    rng = np.random.default_rng(3)
+    edge = np.array([0.0, -0.0, 65504.0, -65504.0, 6.1035e-05, 5.96e-08, 1.0, -1.0], dtype=np.float16)
+    long_name = "model.layers.0." + ".".join(f"block{i}" for i in range(40)) + ".weight"
+    shards = []
+    for shard in range(2):
+        tensors = {}
+        for i in range(50):
+            shape = (1 + (i % 5), 3 + (i % 7))
+            tensors[f"s{shard}.t{i:03d}.weight"] = ("F16", rng.normal(size=shape).astype(np.float16))
+        tensors[f"s{shard}.edge.weight"] = ("F16", edge.reshape(2, 4))
+        if shard == 1:
+            tensors[long_name] = ("BF16", pkg.f32_to_bf16(rng.normal(size=(3, 5)).astype(np.float32)))
+        path = os.path.join(tmp_path, f"model-0000{shard + 1}-of-00002.safetensors")
+        staf.write_safetensors(path, tensors)
+        shards.append((path, tensors))
+    out = os.path.join(tmp_path, "model.staf")
+    assert staf.convert_safetensors([p for p, _ in shards], out) is True
+    f = staf.read_staf(out)
+    assert len(f.names()) == 2 * 51 + 1 and f.metadata[staf.KEY_SOURCE_SHARD_COUNT] == 2
+    spans = sorted((f[n].payload_offset, f[n].payload_size) for n in f.names())
+    assert spans[0][0] % 4096 == 0
+    for (o0, s0), (o1, _) in zip(spans, spans[1:]):
+        assert o0 % 256 == 0 and o1 % 256 == 0 and o0 + s0 <= o1           # aligned, in order, no overlap
+    for shard, (_, tensors) in enumerate(shards):
+        for name, (_, arr) in tensors.items():
+            e = f[name]
+            assert e.shape == arr.shape and e.shard_index == shard
+            assert bytes(f.payload(name)) == np.ascontiguousarray(arr).tobytes()   # bit patterns: -0, subnormals, max
+    assert long_name in f.names() and len(long_name) > 300
