@@ -162,6 +162,11 @@ int swlm_write_kv(swlm_state* state, int which, int layer, int b, int head, int 
  * swlm_read_qjl copies the projected K residuals [count][kv_qjl_dim] fp16 of one KV slab / sequence / head
  * (qjlResidualK, :268-272). */
 int swlm_state_get_rotors(swlm_state* state, uint16_t* dst, size_t count);
+/* 1 when swlm_plan_build accepts `scheme` as swlm_buffers_desc.kv_scheme (0 = unset = bf16), else 0: the counterpart of
+ * QuantizationSchemeIdentifier.isSupportedForKVCache (the reference's set also holds dense fp16 0x00 and fp32 0x02
+ * caches, which this library, whose activations are bf16, does not offer; note that 0 means "unset" here, not fp16).
+ * Needs no device. */
+int swlm_kv_scheme_supported(int scheme);
 int swlm_state_set_rotors(swlm_state* state, const uint16_t* src, size_t count);
 int swlm_read_qjl(swlm_state* state, int layer, int b, int head, int count, uint16_t* dst);
 int swlm_read_conv(swlm_state* state, int layer, int b, uint16_t* dst);

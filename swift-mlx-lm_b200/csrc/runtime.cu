@@ -1532,7 +1532,7 @@ int64_t swlm_weights_bytes(const swlm_ctx* ctx) { return ctx ? ctx->bytes : 0; }
 int swlm_plan_build(swlm_ctx* ctx, const swlm_step* steps, int n_steps, const swlm_buffers_desc* desc, swlm_plan** out) {
     if (!ctx || !steps || n_steps <= 0 || !desc || !out) { set_error("null argument"); return SWLM_ERR_INVALID; }
     *out = nullptr;
-    if (desc->kv_scheme != 0 && desc->kv_scheme != SWLM_KV_BF16 && !swlm_kv_bits(desc->kv_scheme)) {
+    if (!swlm_kv_scheme_supported(desc->kv_scheme)) {
         set_error("KV cache scheme %#x not supported (0x01 bf16; 0x10 / 0x11 / 0x12 8-bit groups of 32 / 64 / 128; 0x40 / 0x41 / 0x42 4-bit groups of 64 / 128 / 128; 0x70 / 0x71 rotated 8-bit groups of 32 / 4-bit groups of 64)", desc->kv_scheme);
         return SWLM_ERR_UNSUPPORTED;
     }
@@ -2115,6 +2115,8 @@ int swlm_write_kv(swlm_state* s, int which, int layer, int b, int head, int coun
     SWLM_CUDA(cudaMemcpy(p, src, (size_t)count * s->plan->desc.head_dim * 2, cudaMemcpyHostToDevice));
     return SWLM_OK;
 }
+
+int swlm_kv_scheme_supported(int scheme) { return scheme == 0 || scheme == SWLM_KV_BF16 || swlm_kv_bits(scheme) != 0; }
 
 int swlm_state_get_rotors(swlm_state* s, uint16_t* dst, size_t count) {
     if (!s || !dst) { set_error("null argument"); return SWLM_ERR_INVALID; }

@@ -115,6 +115,7 @@ SIGNATURES = {
     "swlm_write_buffer": (_I, [_P, _I, _P, _I]),
     "swlm_read_kv": (_I, [_P, _I, _I, _I, _I, _I, _P]),
     "swlm_write_kv": (_I, [_P, _I, _I, _I, _I, _I, _P]),
+    "swlm_kv_scheme_supported": (_I, [_I]),
     "swlm_state_get_rotors": (_I, [_P, _P, C.c_size_t]),
     "swlm_state_set_rotors": (_I, [_P, _P, C.c_size_t]),
     "swlm_read_qjl": (_I, [_P, _I, _I, _I, _I, _P]),

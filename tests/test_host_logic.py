@@ -188,6 +188,21 @@ def test_bad_arguments_are_rejected(pkg):
     assert lib.swlm_plan_launch_count(None) == 0
 
 
+def test_kv_cache_schemes_the_library_accepts(pkg):
+    """KVCacheKernelSupportContractTests 'isSupportedForKVCache matches the pinned supported set'
+    (Tests/MetalCompilerTests/Core/KVCacheKernelSupportContractTests.swift:20-50): the reference's attention kernels read
+    and write fp16 / bf16 / fp32, q4 g64 / g128 / g128zero, q8 g32 / g64 / g128 and the two rotated schemes, and nothing
+    else. This library offers that set without the dense fp16 and fp32 caches (its activations are bf16), 0 standing
+    for "unset" = bf16; the sizable-but-unsupported schemes of the reference are refused here as well."""
+    lib = pkg.load_library()
+    reference_supported = {0x00, 0x01, 0x02, 0x40, 0x41, 0x42, 0x10, 0x11, 0x12, 0x71, 0x70}
+    here = {s for s in range(0x100) if lib.swlm_kv_scheme_supported(s)}
+    assert here == (reference_supported - {0x02}) and lib.swlm_kv_scheme_supported(0x00)    # (0 accepted as "unset", not as fp16)
+    for scheme in here - {0x00, 0x01}:
+        spec = pkg.KVCacheSpecification(layer_count=1, kv_head_count=1, head_dimension=128, maximum_sequence_length=1, scheme=scheme)
+        assert spec.bytes_per_head_slot() % 64 == 0 and spec.bytes_per_head_slot() < 256     # every accepted block scheme is sizable
+
+
 def test_tensor_parallel_head_split_is_checked(pkg):
     """Heads and KV heads must divide by the number of ranks, and every rank must keep whole GQA groups; anything else
     would silently compute with truncated head counts, so it is refused (host-only entry point; swlm_plan_build applies
