@@ -356,6 +356,32 @@ def semantic_role(name: str) -> int:
     return ROLE_OTHER
 
 
+@dataclass(frozen=True)
+class TensorNameCanonicalizer:
+    """Source-convention tensor names into the HuggingFace form the naming conventions expect
+    (STAF/TensorNameCanonicalizer.swift:15-77): prefix-substitution rules, the first match wins. MLX vision-language
+    bundles package the text backbone under `language_model.model.*` where HuggingFace has `model.language_model.*`."""
+    rules: Tuple[Tuple[str, str], ...] = ()
+
+    def canonicalize(self, name: str) -> str:
+        for src, dst in self.rules:
+            if name.startswith(src):
+                return dst + name[len(src):]
+        return name
+
+    @staticmethod
+    def detect(names: Iterable[str]) -> "TensorNameCanonicalizer":
+        """The MLX rule when any name carries the MLX prefix (the two conventions exclude each other), else identity."""
+        for name in names:
+            if name.startswith("language_model.model."):
+                return MLX_VLM_TO_HUGGINGFACE
+        return IDENTITY_NAMES
+
+
+IDENTITY_NAMES = TensorNameCanonicalizer()
+MLX_VLM_TO_HUGGINGFACE = TensorNameCanonicalizer((("language_model.model.", "model.language_model."),))
+
+
 def plan_conversion(tensors: Dict[str, Tuple[str, Tuple[int, ...], np.ndarray]], bits: int = 4, group_size: int = 64,
                     shard_index: int = 0) -> List[TensorToWrite]:
     """STAFConversionPlanner + STAFPayloadConverter for one shard: a `*.weight` with `.scales` and `.biases` companions
@@ -413,8 +439,12 @@ def convert_safetensors(safetensors_paths: Sequence[str], staf_path: str, extra_
     if not force and os.path.exists(staf_path) and is_valid(staf_path, safetensors_paths, expected):
         return False
     entries: List[TensorToWrite] = []
-    for shard, p in enumerate(sorted(safetensors_paths)):
-        entries += plan_conversion(read_safetensors(p), group_size=group_size, shard_index=shard)
+    shards = [read_safetensors(p) for p in sorted(safetensors_paths)]
+    # the source convention is detected over all shards, and every name canonicalized before the quantized triples
+    # are matched (STAFConversionPlanner.swift:21-31)
+    names = TensorNameCanonicalizer.detect(n for t in shards for n in t)
+    for shard, tensors in enumerate(shards):
+        entries += plan_conversion({names.canonicalize(n): v for n, v in tensors.items()}, group_size=group_size, shard_index=shard)
     write_staf(staf_path, entries, expected)
     return True
 

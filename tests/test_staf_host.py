@@ -279,3 +279,35 @@ def test_many_tensors_long_names_edge_values_and_shards(pkg, staf, tmp_path):
             assert e.shape == arr.shape and e.shard_index == shard
             assert bytes(f.payload(name)) == np.ascontiguousarray(arr).tobytes()   # bit patterns: -0, subnormals, max
     assert long_name in f.names() and len(long_name) > 300
+
+
+def test_tensor_names_are_canonicalized_at_conversion(pkg, staf, golden, tmp_path):
+    """TensorNameCanonicalizerTests (Tests/MetalCompilerTests/Core/TensorNameCanonicalizerTests.swift:7-86): identity,
+    the MLX vision-language prefix rewritten to the HuggingFace form, other names untouched, detection from any one name,
+    first rule wins; and the converter applies it before it pairs a weight with its scales and biases."""
+    C = staf.TensorNameCanonicalizer
+    for name in ("model.language_model.embed_tokens.weight", "model.visual.patch_embed.weight", "lm_head.weight"):
+        assert staf.IDENTITY_NAMES.canonicalize(name) == name
+    mlx = staf.MLX_VLM_TO_HUGGINGFACE
+    assert mlx.canonicalize("language_model.model.embed_tokens.weight") == "model.language_model.embed_tokens.weight"
+    assert mlx.canonicalize("language_model.model.layers.0.self_attn.q_proj.scales") == "model.language_model.layers.0.self_attn.q_proj.scales"
+    for name in ("visual.blocks.0.attn.qkv.weight", "lm_head.weight", "model.language_model.embed_tokens.weight"):
+        assert mlx.canonicalize(name) == name
+    assert C.detect(["visual.x", "language_model.model.embed_tokens.weight"]) == mlx
+    assert C.detect(["model.language_model.embed_tokens.weight", "model.visual.patch_embed.weight"]) == staf.IDENTITY_NAMES
+    assert C.detect(["model.embed_tokens.weight", "lm_head.weight"]) == staf.IDENTITY_NAMES
+    assert C((("a.", "x."), ("a.b.", "y."))).canonicalize("a.b.c") == "x.b.c"
+    g = golden["gemv_multi_row"]
+    w = pkg.pack_mlx_q4(np.array(g["q"], dtype=np.uint8))
+    src = os.path.join(tmp_path, "model.safetensors")
+    staf.write_safetensors(src, {
+        "language_model.model.layers.0.mlp.down_proj.weight": ("U32", w),
+        "language_model.model.layers.0.mlp.down_proj.scales": ("BF16", _bf(pkg, g["scales"])),
+        "language_model.model.layers.0.mlp.down_proj.biases": ("BF16", _bf(pkg, g["zeros"])),
+        "visual.patch_embed.weight": ("BF16", _bf(pkg, np.ones((2, 4)))),
+    })
+    out = os.path.join(tmp_path, "model.staf")
+    staf.convert_safetensors([src], out)
+    f = staf.read_staf(out)
+    assert f.names() == ["model.language_model.layers.0.mlp.down_proj.weight", "visual.patch_embed.weight"]
+    assert f["model.language_model.layers.0.mlp.down_proj.weight"].scheme == staf.SCHEME_Q4_G64
