@@ -53,6 +53,20 @@ KEY_SOURCE_SHARD_COUNT = "staf.source_shard_count"
 KEY_METADATA_SCHEMA_VERSION = "staf.metadata_schema_version"
 
 
+# model and provenance keys of a bundle's cache (STAFMetadataKey.swift:9-34)
+KEY_MODEL_FAMILY, KEY_MODEL_HIDDEN, KEY_MODEL_LAYERS = "model.architecture_family", "model.hidden_size", "model.layer_count"
+KEY_MODEL_INTERMEDIATE, KEY_MODEL_VOCAB = "model.intermediate_size", "model.vocab_size"
+KEY_MODEL_HEADS, KEY_MODEL_KV_HEADS, KEY_MODEL_HEAD_DIM = "model.attention_heads", "model.kv_heads", "model.head_dim"
+KEY_MODEL_TIED, KEY_MODEL_ROPE_DIM, KEY_MODEL_ROPE_THETA = "model.tied_embeddings", "model.rope_dimension", "model.rope_theta"
+KEY_SRC_CONFIG_HASH, KEY_SRC_MANIFEST_HASH = "source.config_hash", "source.safetensors_manifest_hash"
+KEY_SRC_TOKENIZER_HASH, KEY_SRC_TOKENIZER_CONFIG_HASH = "source.tokenizer_hash", "source.tokenizer_config_hash"
+KEY_SRC_SPECIAL_TOKENS_HASH, KEY_SRC_CHAT_TEMPLATE_HASH = "source.special_tokens_hash", "source.chat_template_hash"
+KEY_SRC_CHAT_TEMPLATE_SOURCE = "source.chat_template_source"
+KEY_SRC_TOKENIZER_PRESENT, KEY_SRC_TOKENIZER_CONFIG_PRESENT = "source.tokenizer_present", "source.tokenizer_config_present"
+KEY_SRC_SPECIAL_TOKENS_PRESENT, KEY_SRC_CHAT_TEMPLATE_PRESENT = "source.special_tokens_present", "source.chat_template_present"
+CHAT_TEMPLATE_JINJA_SOURCE, TOKENIZER_CONFIG_SOURCE = "chat_template.jinja", "tokenizer_config.json"
+
+
 class STAFError(ValueError):
     pass
 
@@ -115,6 +129,60 @@ def default_cache_metadata(source_shard_count: int) -> Dict[str, MetadataValue]:
     """STAFFileMetadata.defaultCacheMetadata (STAF/STAFFileMetadata.swift:50-58)."""
     return {KEY_SOURCE_FORMAT: "safetensors", KEY_CONVERTER_VERSION: U32(CONVERTER_VERSION),
             KEY_SOURCE_SHARD_COUNT: int(source_shard_count), KEY_METADATA_SCHEMA_VERSION: U32(METADATA_SCHEMA_VERSION)}
+
+
+def stable_hash64(*parts: Union[bytes, str, int]) -> int:
+    """STAFStableHash64 (STAFStableHash.swift:3-42): FNV-1a over the bytes of every part in order; a string enters as
+    UTF-8, an integer as 8 little-endian bytes."""
+    state = 0xcbf29ce484222325
+    for part in parts:
+        data = part.encode() if isinstance(part, str) else struct.pack("<Q", part) if isinstance(part, int) else bytes(part)
+        for byte in data:
+            state = ((state ^ byte) * 0x00000100000001B3) & 0xFFFFFFFFFFFFFFFF
+    return state
+
+
+def bundle_metadata(directory: str, model_type: str, config, config_data: bytes, safetensors_paths: Sequence[str]) -> Dict[str, MetadataValue]:
+    """What a bundle's STAF cache must carry to be taken as valid for that bundle (STAFModelBundleMetadataBuilder.swift:
+    7-128): the model's dimensions (`config`: a plan.ModelConfig), which tokenizer files are present, FNV-1a hashes of
+    config.json, of the tokenizer files and of the chat template (chat_template.jinja wins over the `chat_template` string
+    of tokenizer_config.json), and a hash over (file name, size, modification time in ns) of the shards sorted by name;
+    merged over the converter's own keys."""
+    def optional(name):
+        path = os.path.join(directory, name)
+        return open(path, "rb").read() if os.path.exists(path) else None
+
+    tokenizer, tokenizer_config, special = optional("tokenizer.json"), optional("tokenizer_config.json"), optional("special_tokens_map.json")
+    template = optional("chat_template.jinja")
+    template_source = CHAT_TEMPLATE_JINJA_SOURCE if template is not None else None
+    if template is None and tokenizer_config is not None:
+        parsed = json.loads(tokenizer_config.decode())
+        if isinstance(parsed, dict) and isinstance(parsed.get("chat_template"), str):
+            template, template_source = parsed["chat_template"].encode(), TOKENIZER_CONFIG_SOURCE
+    values: Dict[str, MetadataValue] = {
+        KEY_MODEL_FAMILY: model_type, KEY_MODEL_HIDDEN: int(config.hidden), KEY_MODEL_LAYERS: int(config.layers),
+        KEY_MODEL_INTERMEDIATE: int(config.intermediate), KEY_MODEL_VOCAB: int(config.vocab), KEY_MODEL_HEADS: int(config.heads),
+        KEY_MODEL_KV_HEADS: int(config.kv_heads), KEY_MODEL_HEAD_DIM: int(config.head_dim),
+        KEY_MODEL_TIED: bool(config.tie_embeddings), KEY_MODEL_ROPE_DIM: int(config.head_dim),
+        KEY_MODEL_ROPE_THETA: float(config.rope_theta),
+        KEY_SRC_TOKENIZER_PRESENT: tokenizer is not None, KEY_SRC_TOKENIZER_CONFIG_PRESENT: tokenizer_config is not None,
+        KEY_SRC_SPECIAL_TOKENS_PRESENT: special is not None, KEY_SRC_CHAT_TEMPLATE_PRESENT: template is not None,
+        KEY_SRC_CONFIG_HASH: stable_hash64(config_data),
+    }
+    manifest = []
+    for path in sorted(safetensors_paths, key=os.path.basename):
+        st = os.stat(os.path.realpath(path))
+        manifest += [os.path.basename(path), int(st.st_size), max(0, int(st.st_mtime_ns))]
+    values[KEY_SRC_MANIFEST_HASH] = stable_hash64(*manifest)
+    for key, data in ((KEY_SRC_TOKENIZER_HASH, tokenizer), (KEY_SRC_TOKENIZER_CONFIG_HASH, tokenizer_config),
+                      (KEY_SRC_SPECIAL_TOKENS_HASH, special), (KEY_SRC_CHAT_TEMPLATE_HASH, template)):
+        if data is not None:
+            values[key] = stable_hash64(data)
+    if template_source is not None:
+        values[KEY_SRC_CHAT_TEMPLATE_SOURCE] = template_source
+    merged = default_cache_metadata(len(safetensors_paths))
+    merged.update(values)
+    return merged
 
 
 def _align_up(x: int, a: int) -> int:

@@ -311,3 +311,49 @@ def test_tensor_names_are_canonicalized_at_conversion(pkg, staf, golden, tmp_pat
     f = staf.read_staf(out)
     assert f.names() == ["model.language_model.layers.0.mlp.down_proj.weight", "visual.patch_embed.weight"]
     assert f["model.language_model.layers.0.mlp.down_proj.weight"].scheme == staf.SCHEME_Q4_G64
+
+
+def test_bundle_metadata_carries_provenance(pkg, staf, tmp_path):
+    """STAFModelBundleMetadataBuilderTests 'Builder emits provenance and prefers chat_template.jinja'
+    (Tests/MetalCompilerTests/Core/STAFModelBundleMetadataBuilderTests.swift:8-58), on the same files; the hash is FNV-1a
+    64 (STAFStableHash.swift), checked on its published test vectors; and a cache written with this metadata is valid
+    for the bundle until one of the hashed files changes."""
+    assert staf.stable_hash64(b"") == 0xcbf29ce484222325 and staf.stable_hash64(b"a") == 0xaf63dc4c8601ec8c
+    assert staf.stable_hash64("foobar") == 0x85944171f73967e8
+    assert staf.stable_hash64("ab", 1) == staf.stable_hash64(b"ab" + (1).to_bytes(8, "little"))
+    d = str(tmp_path)
+    files = {"config.json": b'{"model_type":"lfm2","hidden_size":2048}', "tokenizer.json": b'{"version":"1.0"}',
+             "tokenizer_config.json": b'{"chat_template":"from tokenizer config"}', "special_tokens_map.json": b'{"eos_token":"<eos>"}',
+             "chat_template.jinja": b"from jinja", "model.safetensors": bytes([0, 1, 2, 3])}
+    for name, data in files.items():
+        open(os.path.join(d, name), "wb").write(data)
+    cfg = pkg.ModelConfig("lfm2", hidden=2048, intermediate=6144, layers=24, heads=16, kv_heads=8, head_dim=128, vocab=32768,
+                          max_seq=64, attention_layers=(2, 5), tie_embeddings=True)
+    shard = os.path.join(d, "model.safetensors")
+    m = staf.bundle_metadata(d, "lfm2", cfg, files["config.json"], [shard])
+    assert m[staf.KEY_SOURCE_FORMAT] == "safetensors" and m[staf.KEY_SOURCE_SHARD_COUNT] == 1
+    assert m[staf.KEY_CONVERTER_VERSION] == staf.U32(staf.CONVERTER_VERSION) and m[staf.KEY_METADATA_SCHEMA_VERSION] == staf.U32(staf.METADATA_SCHEMA_VERSION)
+    assert (m[staf.KEY_MODEL_FAMILY], m[staf.KEY_MODEL_HIDDEN], m[staf.KEY_MODEL_LAYERS]) == ("lfm2", 2048, 24)
+    assert (m[staf.KEY_MODEL_INTERMEDIATE], m[staf.KEY_MODEL_VOCAB], m[staf.KEY_MODEL_HEADS], m[staf.KEY_MODEL_KV_HEADS]) == (6144, 32768, 16, 8)
+    assert m[staf.KEY_MODEL_TIED] is True and m[staf.KEY_MODEL_HEAD_DIM] == 128 and isinstance(m[staf.KEY_MODEL_ROPE_THETA], float)
+    assert all(m[k] is True for k in (staf.KEY_SRC_TOKENIZER_PRESENT, staf.KEY_SRC_TOKENIZER_CONFIG_PRESENT,
+                                      staf.KEY_SRC_SPECIAL_TOKENS_PRESENT, staf.KEY_SRC_CHAT_TEMPLATE_PRESENT))
+    assert m[staf.KEY_SRC_CHAT_TEMPLATE_SOURCE] == "chat_template.jinja"
+    assert m[staf.KEY_SRC_CHAT_TEMPLATE_HASH] == staf.stable_hash64(b"from jinja")
+    assert m[staf.KEY_SRC_CONFIG_HASH] == staf.stable_hash64(files["config.json"])
+    for key in (staf.KEY_SRC_TOKENIZER_HASH, staf.KEY_SRC_TOKENIZER_CONFIG_HASH, staf.KEY_SRC_SPECIAL_TOKENS_HASH, staf.KEY_SRC_MANIFEST_HASH):
+        assert isinstance(m[key], int) and 0 <= m[key] < 1 << 64
+    # without chat_template.jinja the template of tokenizer_config.json is the one that counts
+    os.remove(os.path.join(d, "chat_template.jinja"))
+    m2 = staf.bundle_metadata(d, "lfm2", cfg, files["config.json"], [shard])
+    assert m2[staf.KEY_SRC_CHAT_TEMPLATE_SOURCE] == "tokenizer_config.json"
+    assert m2[staf.KEY_SRC_CHAT_TEMPLATE_HASH] == staf.stable_hash64(b"from tokenizer config")
+    # a cache written with the bundle's metadata: valid for it, stale once config.json changes
+    src = os.path.join(d, "w.safetensors")
+    staf.write_safetensors(src, {"model.norm.weight": ("BF16", _bf(pkg, np.ones(8)))})
+    expect = staf.bundle_metadata(d, "lfm2", cfg, files["config.json"], [src])
+    out = os.path.join(d, "model.staf")
+    assert staf.convert_safetensors([src], out, extra_metadata=expect) is True
+    assert staf.is_valid(out, [src], expect)
+    changed = staf.bundle_metadata(d, "lfm2", cfg, files["config.json"] + b" ", [src])
+    assert not staf.is_valid(out, [src], changed)
