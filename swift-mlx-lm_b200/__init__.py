@@ -25,5 +25,6 @@ from .plan import (  # noqa: F401
     lfm2_like_config,
 )
 from .model import InferenceModel, WeightStore, bundle_tensors, load_model, load_model_from_staf  # noqa: F401
-from . import formats, plan, staf, tp  # noqa: F401
+from . import bundle, formats, plan, staf, tp  # noqa: F401
+from .bundle import load_bundle, prepare_bundle  # noqa: F401
 from .synth import synth_model_weights, synth_q4  # noqa: F401

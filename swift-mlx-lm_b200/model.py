@@ -314,7 +314,7 @@ def bundle_tensors(builder, weights):
 
 
 def load_model_from_staf(store: WeightStore, builder, staf_file) -> InferenceModel:
-    """Upload the tensors a plan needs straight from a STAF file (4-bit group-64 blocks as they are, dense tensors as
+    """Upload the tensors a plan needs straight from a STAF file (4-bit group-64 / group-128 blocks as they are, dense tensors as
     bf16) and compile the decode plan. Mirrors STAFLoader.load -> STAFWeightStore
     (Sources/MetalCompiler/STAF/STAFLoader.swift:19-299) feeding MetalInferenceModel."""
     from . import staf as _staf
@@ -323,10 +323,11 @@ def load_model_from_staf(store: WeightStore, builder, staf_file) -> InferenceMod
         entry = staf_file[staf_tensor_name(name, kind)]
         raw = np.asarray(staf_file.data[entry.payload_offset:entry.payload_offset + entry.payload_size])
         if kind == "q4":
-            if entry.scheme != _staf.SCHEME_Q4_G64:
-                raise _staf.STAFError(f"{entry.name}: scheme {entry.scheme:#x} is not 4-bit group 64")
+            if entry.scheme not in (_staf.SCHEME_Q4_G64, _staf.SCHEME_Q4_G128):
+                raise _staf.STAFError(f"{entry.name}: scheme {entry.scheme:#x} is not 4-bit group 64 or 128")
+            group = 64 if entry.scheme == _staf.SCHEME_Q4_G64 else 128
             n, words = entry.shape
-            store.add_q4_staf(name, raw.reshape(n, words * 8 // 64, 36), n, words * 8, shard)
+            store.add_q4_staf(name, raw.reshape(n, words * 8 // group, 4 + group // 2), n, words * 8, shard, group=group)
         elif kind == "f32":
             if entry.scheme != _staf.SCHEME_FP32:
                 raise _staf.STAFError(f"{entry.name}: expected an fp32 section")

@@ -218,3 +218,87 @@ def test_tensor_parallel_head_split_is_checked(pkg):
     assert lib.swlm_tp_check_heads(24, 8, 4) == ok
     assert b"GQA" in lib.swlm_last_error() or True
     assert lib.swlm_tp_check_heads(0, 8, 2) == -1
+
+
+# ---- model directories (config.json + shards) ------------------------------------------------------------------------
+
+LLAMA_CONFIG = {"model_type": "llama", "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 2, "num_attention_heads": 4,
+                "num_key_value_heads": 2, "vocab_size": 512, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+                "quantization": {"group_size": 64, "bits": 4}}
+
+
+def test_config_json_decoding_follows_the_reference_rules(pkg):
+    """HFConfigDecoder (Sources/SwiftLM/HFConfigDecoder.swift:6-170): quantization hint (also under text_config), defaults
+    of heads / KV heads / head_dim / epsilon / RoPE base, LFM2's feed-forward adjustment and layer pattern, text_config
+    merged over the top level; ModelGraphResolver's model types; refusal of what the recipes cannot express."""
+    B = pkg.bundle
+    assert B.quantization_hint(LLAMA_CONFIG) == (4, 64)
+    assert B.quantization_hint({"text_config": {"quantization": {"bits": 4, "group_size": 128}}}) == (4, 128)
+    assert B.quantization_hint({"quantization": {"bits": 4}}) is None and B.quantization_hint({}) is None
+    c = B.decode_config(LLAMA_CONFIG)
+    assert (c.family, c.hidden, c.intermediate, c.layers, c.heads, c.kv_heads, c.head_dim, c.vocab) == ("llama", 256, 512, 2, 4, 2, 64, 512)
+    assert c.norm_eps == 1e-5 and c.rope_theta == 10000.0 and c.tie_embeddings is False and c.sliding_window == 0
+    d = B.decode_config({"model_type": "mistral", "hidden_size": 128, "num_hidden_layers": 1, "vocab_size": 64, "sliding_window": 32})
+    assert (d.heads, d.kv_heads, d.head_dim, d.intermediate, d.norm_eps, d.rope_theta, d.sliding_window) == (32, 32, 4, 512, 1e-6, 500000.0, 32)
+    lfm2 = {"model_type": "lfm2", "hidden_size": 2048, "num_hidden_layers": 16, "vocab_size": 65536, "num_attention_heads": 32,
+            "num_key_value_heads": 8, "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True, "block_ffn_dim_multiplier": 1.0,
+            "block_multiple_of": 256, "norm_eps": 1e-5, "rope_theta": 1000000.0, "conv_L_cache": 3, "tie_embedding": True,
+            "full_attn_idxs": [2, 5, 8, 10, 12, 14]}
+    l = B.decode_config(lfm2)
+    assert (l.family, l.intermediate, l.head_dim, l.conv_kernel, l.tie_embeddings) == ("lfm2", 8192, 64, 3, True)
+    assert list(l.attention_layers) == [2, 5, 8, 10, 12, 14] and l.kv_layer_count == 6 and l.conv_layer_count == 10
+    types = ["conv", "conv", "full_attention", "conv"]
+    assert list(B.decode_config(dict(lfm2, num_hidden_layers=4, layer_types=types, full_attn_idxs=None)).attention_layers) == [2]
+    merged = B.decode_config({"model_type": "llama", "vocab_size": 8, "text_config": {"hidden_size": 64, "num_hidden_layers": 3, "num_attention_heads": 2}})
+    assert (merged.hidden, merged.layers, merged.vocab, merged.head_dim) == (64, 3, 8, 32)
+    for bad, word in ((dict(LLAMA_CONFIG, num_local_experts=8), "experts"), (dict(LLAMA_CONFIG, attention_bias=True), "biases"),
+                      (dict(LLAMA_CONFIG, model_type="gemma3_text"), "Unsupported"), (dict(LLAMA_CONFIG, model_type="qwen3", qk_norm=True), "QK norm"),
+                      (dict(LLAMA_CONFIG, partial_rotary_factor=0.25), "rotary"), ({"model_type": "llama"}, "Missing hidden_size")):
+        with pytest.raises(B.BundleError, match=word):
+            B.decode_config(bad)
+    with pytest.raises(B.BundleError, match="model_type"):
+        B.decode_config({"hidden_size": 8})
+
+
+def test_default_cache_policy_is_model_aware(pkg):
+    """RotorQuantCorrectnessTests 'ModelBundleLoader resolves default policy to RotorQuant only for plain transformer
+    attention graphs' (:99-161): the untouched default becomes the rotated 4-bit group-64 cache for K and V when the model
+    has attention and no short-conv or recurrent layer; an explicit policy stands."""
+    B = pkg.bundle
+    llama, lfm2 = B.decode_config(LLAMA_CONFIG), pkg.lfm2_like_config()
+    assert B.resolve_kv_policy(llama) == (0x71, 0)
+    assert B.resolve_kv_policy(lfm2) == (0x01, 0)
+    assert B.resolve_kv_policy(llama, requested_scheme=0x10) == (0x10, 0) and B.resolve_kv_policy(llama, 0x70, 16) == (0x70, 16)
+    assert B.resolve_kv_policy(llama, maximum_sequence_length=8192) == (0x01, 0)     # not the default policy any more
+
+
+def test_model_directory_is_prepared_without_a_gpu(pkg, tmp_path):
+    """config.json + one MLX-quantized shard -> decoded recipe, resolved cache policy, model.staf beside the shards with
+    the bundle's validity metadata; a second call reuses the file, a changed config.json rewrites it."""
+    import json
+    import os
+    B, staf = pkg.bundle, pkg.staf
+    d = str(tmp_path)
+    config = dict(LLAMA_CONFIG, tie_word_embeddings=False)
+    open(os.path.join(d, "config.json"), "w").write(json.dumps(config))
+    cfg = B.decode_config(config)
+    builder = pkg.DispatchPlanBuilder(cfg)
+    weights = pkg.synth_model_weights(builder, seed=3)
+    staf.write_safetensors(os.path.join(d, "model.safetensors"), pkg.bundle_tensors(builder, weights))
+    got_cfg, got_builder, f = B.prepare_bundle(d, max_batch=2)
+    assert (got_cfg.kv_scheme, got_cfg.kv_qjl_dim, got_cfg.max_batch, got_cfg.max_seq) == (0x71, 0, 2, 4096 + 128)
+    assert got_cfg.buffers_desc().kv_scheme == 0x71
+    out = os.path.join(d, "model.staf")
+    assert f.metadata[staf.KEY_MODEL_FAMILY] == "llama" and f.metadata[staf.KEY_MODEL_HIDDEN] == 256
+    for name, kind, _shape, _shard in got_builder.tensors():
+        assert pkg.model.staf_tensor_name(name, kind) in f.names()
+    stamp = os.stat(out).st_mtime_ns
+    B.prepare_bundle(d, max_batch=2)
+    assert os.stat(out).st_mtime_ns == stamp                                  # valid cache: kept
+    open(os.path.join(d, "config.json"), "w").write(json.dumps(dict(config, rope_theta=20000.0)))
+    cfg2, _, f2 = B.prepare_bundle(d, kv_scheme=0x10)
+    assert cfg2.rope_theta == 20000.0 and cfg2.kv_scheme == 0x10 and f2.metadata[staf.KEY_MODEL_ROPE_THETA] == 20000.0
+    assert f2.metadata[staf.KEY_SRC_CONFIG_HASH] != f.metadata[staf.KEY_SRC_CONFIG_HASH]
+    with pytest.raises(B.BundleError, match="4-bit"):
+        open(os.path.join(d, "config.json"), "w").write(json.dumps(dict(config, quantization={"bits": 8, "group_size": 64})))
+        B.prepare_bundle(d)
