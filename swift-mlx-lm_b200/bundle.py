@@ -159,6 +159,8 @@ def prepare_bundle(directory: str, max_seq: Optional[int] = None, max_batch: int
     shards = sorted(glob.glob(os.path.join(directory, "*.safetensors")))
     if not shards:
         raise BundleError(f"{directory}: no safetensors shard")
+    # MLX-quantized bundles carry the embedding table as a quantized triple as well
+    cfg.quantized_embedding = any(name.endswith("embed_tokens.scales") for p in shards for name in _staf.safetensors_names(p))
     expected = _staf.bundle_metadata(directory, model_type(config), cfg, config_data, shards)
     out = os.path.join(directory, "model.staf")
     _staf.convert_safetensors(shards, out, extra_metadata=expected, group_size=hint[1])

@@ -54,6 +54,9 @@ class ModelConfig:
     # The output head reuses the embedding table (Sources/Models/LlamaFamilyNaming.swift:22-27): one Q4 group-64
     # tensor serves the row gather (embedding_lookup_q4) and the lm_head product.
     tie_embeddings: bool = False
+    # An untied model whose embedding table is a Q4 tensor of its own (MLX-quantized bundles quantize embed_tokens as
+    # well as lm_head): the row gather reads the packed rows (embedding_lookup_q4), the head stays a separate tensor.
+    quantized_embedding: bool = False
     # Gemma-style variants of the same recipe (Generator/MetalSourceGenerator+NormAndElementwise.swift:176-208):
     # the gated MLP's activation ("silu" = SwiGLU, "gelu_tanh" = GEGLU) and the constant added to every RMSNorm
     # weight (weightBias, 1.0 for checkpoints that store weight - 1).
@@ -172,7 +175,7 @@ class DispatchPlanBuilder:
     def tensors(self):
         c = self.config
         h, f, qd, kvd = c.hidden, c.intermediate, c.heads * c.head_dim, c.kv_heads * c.head_dim
-        out = [("model.embed_tokens.weight", "q4" if c.tie_embeddings else "dense", (c.vocab, h), SHARD_REPLICATE)]
+        out = [("model.embed_tokens.weight", "q4" if c.tie_embeddings or c.quantized_embedding else "dense", (c.vocab, h), SHARD_REPLICATE)]
         for i in range(c.layers):
             p = f"model.layers.{i}."
             if c.family in ("llama", "deltanet"):

@@ -396,6 +396,14 @@ def read_safetensors(path: str) -> Dict[str, Tuple[str, Tuple[int, ...], np.ndar
     return out
 
 
+def safetensors_names(path: str) -> List[str]:
+    """Tensor names of a shard, from its JSON header alone."""
+    with open(path, "rb") as f:
+        (hlen,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(hlen).decode())
+    return [name for name in header if name != "__metadata__"]
+
+
 def write_safetensors(path: str, tensors: Dict[str, Tuple[str, np.ndarray]]) -> None:
     """Minimal writer (tests build MLX-shaped bundles with it): name -> (dtype string, array)."""
     header, blobs, off = {}, [], 0

@@ -49,21 +49,6 @@ def test_qgemv_reference_known_answers(pkg, store, golden):
             assert abs(float(y[r]) - g["expected"][r]) < max(g["abs_tol"], g["rel_tol"] * abs(g["expected"][r]))
 
 
-@pytest.mark.parametrize("case", ["gemv_multi_block_g64", "gemv_multi_block_g128"])
-def test_qgemv_multi_block_known_answers(pkg, store, golden, case):
-    """UnifiedGEMVMultiBlockTests (Q4G64, Q4G128): one row over four blocks with their own scale and zero, against the
-    reference test's fp32 expectation and tolerance; as MLX words and as STAF blocks."""
-    g = golden[case]
-    group, k = g["group"], g["group"] * g["blocks"]
-    w = pkg.pack_mlx_q4(np.array([g["q"]], dtype=np.uint8))
-    s, z = _bf(pkg, [g["scales"]]), _bf(pkg, [g["zeros"]])
-    store.add_q4_mlx(f"kat.{case}", w, s, z)
-    store.add_q4_staf(f"kat.{case}.staf", pkg.formats.repack_mlx_to_staf(w, s, z, group=group), 1, k, group=group)
-    for name in (f"kat.{case}", f"kat.{case}.staf"):
-        y = pkg.bf16_to_f32(store.qgemm(name, _bf(pkg, [g["x"]]), 1))
-        assert abs(float(y[0, 0]) - g["expected"]) < max(g["abs_tol"], g["rel_tol"] * abs(g["expected"]))
-
-
 @pytest.mark.parametrize("n,k,m", [
     (4096, 4096, 1),      # the op-level benchmark shape
     (1, 64, 1), (17, 128, 1), (100, 320, 3), (33, 64 * 5, 2),   # ragged: padding rows and k-tiles

@@ -333,36 +333,6 @@ def test_model_loaded_from_a_staf_file(pkg, oracle, tmp_path):
     gm.close(); store.close()
 
 
-@pytest.mark.parametrize("default_policy", [False, True])
-def test_model_directory_loads_and_decodes(pkg, oracle, tmp_path, default_policy):
-    """ModelBundleLoader's route for the plain transformer recipe: config.json + an MLX-quantized shard in a directory ->
-    decoded recipe, model.staf with the bundle's metadata, upload, plan. With an explicit sequence length the cache is dense
-    bf16; with the loader's untouched default policy it is the rotated 4-bit group-64 cache, as the reference resolves it
-    (Sources/SwiftLM/ModelBundleLoader.swift:352-370). Tokens and logits against the oracle under the same policy."""
-    import json
-    import os
-
-    d = str(tmp_path)
-    config = {"model_type": "llama", "hidden_size": 512, "intermediate_size": 1536, "num_hidden_layers": 4, "num_attention_heads": 8,
-              "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 4096, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
-              "tie_word_embeddings": False, "quantization": {"group_size": 64, "bits": 4}}
-    open(os.path.join(d, "config.json"), "w").write(json.dumps(config))
-    builder = pkg.DispatchPlanBuilder(pkg.bundle.decode_config(config))
-    weights = pkg.synth_model_weights(builder, seed=9)
-    pkg.staf.write_safetensors(os.path.join(d, "model.safetensors"), pkg.bundle_tensors(builder, weights))
-    store = pkg.WeightStore(0)
-    gm = pkg.load_bundle(d, store) if default_policy else pkg.load_bundle(d, store, max_seq=128)
-    cfg, _, _ = pkg.prepare_bundle(d) if default_policy else pkg.prepare_bundle(d, max_seq=128)
-    assert (cfg.kv_scheme, cfg.max_seq) == ((0x71, 4096 + 128) if default_policy else (0x01, 128))
-    assert os.path.exists(os.path.join(d, "model.staf"))
-    om = oracle.model(cfg.buffers_desc())
-    om.load(pkg.DispatchPlanBuilder(cfg), weights, staf_fp16=True)     # STAF blocks carry fp16 scales and zeros
-    oracle.set_threads(0)
-    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=9, steps=24)
-    assert len(mism) <= 2, mism
-    gm.close(); store.close()
-
-
 def test_lfm2_tied_q4_embedding_table(pkg, oracle):
     """A tied output head (Sources/Models/LlamaFamilyNaming.swift:22-27): one Q4 group-64 tensor is both the embedding
     table (embedding_lookup_q4, Generator/MetalSourceGenerator+Embedding.swift:79-154) and the lm_head weight. Token by

@@ -302,3 +302,14 @@ def test_model_directory_is_prepared_without_a_gpu(pkg, tmp_path):
     with pytest.raises(B.BundleError, match="4-bit"):
         open(os.path.join(d, "config.json"), "w").write(json.dumps(dict(config, quantization={"bits": 8, "group_size": 64})))
         B.prepare_bundle(d)
+    # a bundle whose embedding table is quantized too (what MLX's converter writes): the gather reads the Q4 rows, the
+    # head stays its own tensor
+    open(os.path.join(d, "config.json"), "w").write(json.dumps(config))
+    qcfg = B.decode_config(config)
+    qcfg.quantized_embedding = True
+    qb = pkg.DispatchPlanBuilder(qcfg)
+    kinds = {name: kind for name, kind, _s, _k in qb.tensors()}
+    assert kinds["model.embed_tokens.weight"] == "q4" and kinds["lm_head"] == "q4"
+    staf.write_safetensors(os.path.join(d, "model.safetensors"), pkg.bundle_tensors(qb, pkg.synth_model_weights(qb, seed=4)))
+    cfg3, b3, f3 = B.prepare_bundle(d)
+    assert cfg3.quantized_embedding and f3["model.embed_tokens.weight"].scheme == staf.SCHEME_Q4_G64 and "lm_head.weight" in f3.names()
