@@ -118,10 +118,9 @@ def decode_config(config: Dict, max_seq: int = DEFAULT_MAXIMUM_SEQUENCE_LENGTH +
         kernel = _first(config, ("conv_L_cache", "conv_kernel_size"), 3)
         return ModelConfig("lfm2", conv_kernel=int(kernel), attention_layers=attention, **common)
     if mt in TRANSFORMER_MODEL_TYPES:
-        if config.get("qk_norm"):
-            refuse("QK norm in the plain transformer recipe")
-        window = config.get("sliding_window") if config.get("use_sliding_window", True) else None
-        return ModelConfig("llama", sliding_window=int(window) if isinstance(window, int) and window > 0 else 0, **common)
+        window = config.get("sliding_window")
+        return ModelConfig("llama", sliding_window=int(window) if isinstance(window, int) and window > 0 else 0,
+                           qk_norm=bool(config.get("qk_norm", False)), **common)
     raise BundleError(f"Unsupported model_type: {mt}")
 
 

@@ -57,6 +57,10 @@ class ModelConfig:
     # An untied model whose embedding table is a Q4 tensor of its own (MLX-quantized bundles quantize embed_tokens as
     # well as lm_head): the row gather reads the packed rows (embedding_lookup_q4), the head stays a separate tensor.
     quantized_embedding: bool = False
+    # Per-head RMS norm of q and k before RoPE in the plain transformer recipe (Attention(qkNorm: .rmsNorm),
+    # Sources/Models/Transformer.swift:49-64; tensors `self_attn.q_layernorm.weight` / `k_layernorm.weight`,
+    # LlamaFamilyNaming.swift:50-54). The LFM2 recipe always has it.
+    qk_norm: bool = False
     # Gemma-style variants of the same recipe (Generator/MetalSourceGenerator+NormAndElementwise.swift:176-208):
     # the gated MLP's activation ("silu" = SwiGLU, "gelu_tanh" = GEGLU) and the constant added to every RMSNorm
     # weight (weightBias, 1.0 for checkpoints that store weight - 1).
@@ -187,6 +191,9 @@ class DispatchPlanBuilder:
                         (p + "self_attn.v_proj", "q4", (kvd, h), SHARD_COLUMN),
                         (p + "self_attn.o_proj", "q4", (h, qd), SHARD_ROW),
                     ]
+                    if c.qk_norm:
+                        out += [(p + "self_attn.q_layernorm.weight", "norm", (c.head_dim,), SHARD_REPLICATE),
+                                (p + "self_attn.k_layernorm.weight", "norm", (c.head_dim,), SHARD_REPLICATE)]
                 else:
                     vd = c.ssm_heads * c.ssm_value_dim
                     out += [
@@ -261,7 +268,7 @@ class DispatchPlanBuilder:
                 gemv(p + "self_attn.q_proj", BUF_S0, BUF_S1, qd, h)
                 gemv(p + "self_attn.k_proj", BUF_S0, BUF_S2, kvd, h)
                 gemv(p + "self_attn.v_proj", BUF_S0, BUF_S3, kvd, h)
-                if c.family == "lfm2":
+                if c.family == "lfm2" or c.qk_norm:
                     steps.append(_step(STEP_QK_NORM, in_buf=BUF_S1, in2_buf=BUF_S2, heads=c.heads, kv_heads=c.kv_heads,
                                        head_dim=c.head_dim, eps=eps, weight_bias=0.0,
                                        weight=p + "self_attn.q_layernorm.weight", weight2=p + "self_attn.k_layernorm.weight"))

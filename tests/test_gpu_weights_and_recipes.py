@@ -1,5 +1,5 @@
-"""Weights that arrive through files, on a B200: the reference's multi-block known answers through both upload formats,
-and a model directory (config.json + MLX-quantized shard) loaded the way the reference's bundle loader takes it."""
+"""On a B200: the reference's multi-block known answers through both upload formats, a model directory (config.json +
+MLX-quantized shard) loaded the way the reference's bundle loader takes it, and the plain transformer recipe with QK norm."""
 import numpy as np
 import pytest
 
@@ -62,5 +62,20 @@ def test_model_directory_loads_and_decodes(pkg, oracle, tmp_path, default_policy
     om.load(pkg.DispatchPlanBuilder(cfg), weights, staf_fp16=True)     # STAF blocks carry fp16 scales and zeros
     oracle.set_threads(0)
     mism = greedy_compare(pkg, gm, om, cfg, prompt_len=9, steps=24)
+    assert len(mism) <= 2, mism
+    gm.close(); store.close()
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_transformer_recipe_with_qk_norm_against_oracle(pkg, oracle, batch):
+    """The plain transformer recipe with per-head q / k RMS norm before RoPE (Sources/Models/Transformer.swift:49-64):
+    a short prompt and greedy steps against the oracle, one sequence and three."""
+    from test_gpu_model import build_pair
+
+    cfg = pkg.ModelConfig("llama", hidden=512, intermediate=1536, layers=4, heads=8, kv_heads=2, head_dim=64, vocab=4096,
+                          norm_eps=1e-5, rope_theta=500000.0, max_seq=128, max_batch=batch, qk_norm=True)
+    store, gm, om = build_pair(pkg, oracle, cfg)
+    assert "qk" in gm.describe().lower()
+    mism = greedy_compare(pkg, gm, om, cfg, prompt_len=7, steps=24)
     assert len(mism) <= 2, mism
     gm.close(); store.close()

@@ -249,10 +249,11 @@ def test_config_json_decoding_follows_the_reference_rules(pkg):
     assert list(l.attention_layers) == [2, 5, 8, 10, 12, 14] and l.kv_layer_count == 6 and l.conv_layer_count == 10
     types = ["conv", "conv", "full_attention", "conv"]
     assert list(B.decode_config(dict(lfm2, num_hidden_layers=4, layer_types=types, full_attn_idxs=None)).attention_layers) == [2]
+    assert B.decode_config(dict(LLAMA_CONFIG, model_type="qwen3", qk_norm=True)).qk_norm is True and c.qk_norm is False
     merged = B.decode_config({"model_type": "llama", "vocab_size": 8, "text_config": {"hidden_size": 64, "num_hidden_layers": 3, "num_attention_heads": 2}})
     assert (merged.hidden, merged.layers, merged.vocab, merged.head_dim) == (64, 3, 8, 32)
     for bad, word in ((dict(LLAMA_CONFIG, num_local_experts=8), "experts"), (dict(LLAMA_CONFIG, attention_bias=True), "biases"),
-                      (dict(LLAMA_CONFIG, model_type="gemma3_text"), "Unsupported"), (dict(LLAMA_CONFIG, model_type="qwen3", qk_norm=True), "QK norm"),
+                      (dict(LLAMA_CONFIG, model_type="gemma3_text"), "Unsupported"),
                       (dict(LLAMA_CONFIG, partial_rotary_factor=0.25), "rotary"), ({"model_type": "llama"}, "Missing hidden_size")):
         with pytest.raises(B.BundleError, match=word):
             B.decode_config(bad)
@@ -313,3 +314,29 @@ def test_model_directory_is_prepared_without_a_gpu(pkg, tmp_path):
     staf.write_safetensors(os.path.join(d, "model.safetensors"), pkg.bundle_tensors(qb, pkg.synth_model_weights(qb, seed=4)))
     cfg3, b3, f3 = B.prepare_bundle(d)
     assert cfg3.quantized_embedding and f3["model.embed_tokens.weight"].scheme == staf.SCHEME_Q4_G64 and "lm_head.weight" in f3.names()
+
+
+def test_transformer_recipe_with_qk_norm(pkg, oracle):
+    """Attention(qkNorm: .rmsNorm) of the plain transformer recipe (Sources/Models/Transformer.swift:49-64): the plan
+    gains the two per-head norm weights per layer and a QK-norm step between the projections and attention; the oracle
+    runs it, and the norm changes the result."""
+    P = pkg.plan
+    base = dict(hidden=256, intermediate=512, layers=2, heads=4, kv_heads=2, head_dim=64, vocab=512, max_seq=32)
+    plain, normed = pkg.ModelConfig("llama", **base), pkg.ModelConfig("llama", qk_norm=True, **base)
+    b0, b1 = pkg.DispatchPlanBuilder(plain), pkg.DispatchPlanBuilder(normed)
+    names = [n for n, _k, _s, _sh in b1.tensors()]
+    assert "model.layers.1.self_attn.q_layernorm.weight" in names and "model.layers.0.self_attn.k_layernorm.weight" in names
+    assert len(b1.tensors()) == len(b0.tensors()) + 2 * base["layers"]
+    kinds0, kinds1 = [s.kind for s in b0.decode_steps()], [s.kind for s in b1.decode_steps()]
+    assert kinds0.count(P.STEP_QK_NORM) == 0 and kinds1.count(P.STEP_QK_NORM) == base["layers"]
+    i = kinds1.index(P.STEP_QK_NORM)
+    assert kinds1[i - 1] == P.STEP_QGEMV and kinds1[i + 1] == P.STEP_ATTN_DECODE
+    weights = pkg.synth_model_weights(b1, seed=2)
+    out = []
+    for builder in (b0, b1):
+        m = oracle.model(builder.config.buffers_desc())
+        m.load(builder, weights)
+        tok = m.prefill(np.array([[5, 6, 7, 8]], dtype=np.int32))
+        out.append(pkg.bf16_to_f32(m.read_buffer(P.BUF_LOGITS, base["vocab"]))[0].copy())
+        assert 0 <= int(tok[0]) < base["vocab"]
+    assert np.max(np.abs(out[0] - out[1])) > 1e-3
