@@ -9,11 +9,11 @@ failed decode returns token -1 as `MetalDecodeExecutor` does (Execution/MetalDec
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 
-from .lib import BuffersDesc, Library, Step, SwlmError, load_library
+from .lib import BuffersDesc, Library, Step, load_library
 
 
 def _ptr(a: np.ndarray) -> C.c_void_p:
