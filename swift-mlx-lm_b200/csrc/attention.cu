@@ -624,10 +624,11 @@ __device__ __forceinline__ void rotor_turn_group(float* row, int hd, const __hal
 // before anything else, so the cache holds turned rows and q . k is unchanged; the merged output is turned back. With
 // qjl_dim > 0 split 0 also stores Phi . (k - its dequantised row) for the new row, and the score of a cached row gains
 // (Phi . q) . (that row's stored values): lane l carries columns l and l + 32 of both into the warp reduction.
-// (The rotated form is held to 128 registers up to four query heads per KV head so that two CTAs share an SM like the
-// plain form's: the kernel is bound by instruction issue and needs both.)
+// (Up to four query heads per KV head the rotated form is held to 128 registers so that two CTAs share an SM like the
+// plain form's, which fits by itself: the kernel is bound by instruction issue and needs both. The plain form states no
+// minimum - a minimum of one would let the compiler spread it over 150 registers and halve its occupancy.)
 template <int HD, int G, int BITS, bool ROTOR>
-__global__ void __launch_bounds__(kQ8Threads, ROTOR && G <= 4 ? 2 : 1) attn_q8_split_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kQ8Threads, ROTOR && G <= 4 ? 2 : 0) attn_q8_split_kernel(const AttnParams p) {
     constexpr int EPL = HD / 32;           // elements per lane
     constexpr int NG = (HD + 2) / 3;       // rotors per KV head
     const int GROUP = p.kv_group, BB = 4 + GROUP * BITS / 8;   // values and bytes per block (BITS per value)
@@ -696,8 +697,9 @@ __global__ void __launch_bounds__(kQ8Threads, ROTOR && G <= 4 ? 2 : 1) attn_q8_s
 #pragma unroll
     for (int r = 0; r < G; ++r) qpr[r][0] = qpr[r][1] = 0.f;
     if (ROTOR && qjl > 0) {
+        const int cols = ROTOR ? qjl : 1;   // (the plain instantiation never gets here; keeps its dead code free of a constant zero divisor)
         for (int idx = tid; idx < G * qjl; idx += kQ8Threads) {
-            const int r = idx / qjl, j = idx - r * qjl;
+            const int r = idx / cols, j = idx - r * cols;
             float a = 0.f;
             for (int d = 0; d < HD; ++d) a = fmaf(qs[r][d], __half2float(__ldg(p.qjl_matrix + (size_t)d * qjl + j)), a);
             qp[r][j] = a;

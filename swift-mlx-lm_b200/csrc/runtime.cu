@@ -665,7 +665,7 @@ namespace {
 
 // ---- rotated KV schemes on the host: parameters by the reference's rule, and the arithmetic of the cache probes ----
 uint16_t host_f16_bits(float f) { const __half h = __float2half_rn(f); uint16_t u; memcpy(&u, &h, 2); return u; }
-float host_f16_value(uint16_t u) { __half h; memcpy(&h, &u, 2); return __half2float(h); }
+float host_f16_value(uint16_t u) { __half h; memcpy(static_cast<void*>(&h), &u, 2); return __half2float(h); }
 
 // initializeRandomUnitRotors (Buffer/MetalGraphAllocator.swift:349-390): rotor i of [layer][kv_head][group] takes four
 // successive values of the 64-bit LCG x -> x * 6364136223846793005 + 1442695040888963407 started from that map of i,
