@@ -10,6 +10,8 @@ repository's oracle or kernels. Sources (paths relative to the reference project
                       Tests/MetalCompilerTests/Core/STAFEndToEndGEMVTests.swift:137-160, 252-255, 295-320
   gemv_multi_block_*  Tests/MetalCompilerTests/Core/UnifiedGEMVMultiBlockTests.swift:51-60, 108-215 (Q4G64, Q4G128)
   dequant_block       Tests/MetalCompilerTests/Core/UnifiedDequantBitLevelTests.swift:129-137
+  rotor_defaults      Sources/MetalCompiler/Buffer/MetalGraphAllocator.swift:349-411 (the deterministic rotors and sign
+                      matrix of the rotated KV schemes; the reference's tests check their properties, not their values)
   staf_roundtrip_*    Tests/MetalCompilerTests/Core/STAFQuantizedRoundtripTests.swift:133-143, 159-171, 187-198, 225-240
   attention_pattern   Tests/MetalCompilerTests/Core/AttentionSequenceEquivalenceTests.swift:21-43, 94-103
   conv_pattern        Tests/MetalCompilerTests/Core/Conv1dSequenceEquivalenceTests.swift:21-30
@@ -92,6 +94,24 @@ def gemv_multi_block(weights_per_block, blocks=4):
         q += qb; scales.append(float(scale)); zeros.append(float(zero))
     return {"group": weights_per_block, "blocks": blocks, "q": q, "scales": scales, "zeros": zeros,
             "x": [float(v) for v in x], "expected": float(e), "abs_tol": 0.03, "rel_tol": 0.03}
+
+
+def rotor_defaults(rotors=12, head_dim=8, qjl=4):
+    """fp16 bit patterns of the first `rotors` unit rotors (four LCG draws each, mapped to [-1, 1), normalised in fp32) and
+    of a head_dim x qjl sign matrix (+-1/sqrt(qjl) by bit 33 of the first draw of each index)."""
+    a, c, mask = 6364136223846793005, 1442695040888963407, (1 << 64) - 1
+    out = []
+    for i in range(rotors):
+        h, comp = i, []
+        for _ in range(4):
+            h = (h * a + c) & mask
+            comp.append(F(F((h >> 33) - (1 << 30)) * F(1.0 / (1 << 30))))
+        norm = F(np.sqrt(F(F(F(comp[0] * comp[0] + comp[1] * comp[1]) + comp[2] * comp[2]) + comp[3] * comp[3])))
+        comp = [F(1), F(0), F(0), F(0)] if norm < 1e-8 else [F(v * F(F(1.0) / norm)) for v in comp]
+        out.append([f16_bits(v) for v in comp])
+    scale = F(F(1.0) / F(np.sqrt(F(qjl))))
+    signs = [f16_bits(scale) if ((((i * a + c) & mask) >> 33) & 1) == 0 else f16_bits(-scale) for i in range(head_dim * qjl)]
+    return {"rotors_f16_bits": out, "head_dim": head_dim, "qjl": qjl, "matrix_f16_bits": signs}
 
 
 def dequant_block():
@@ -202,6 +222,7 @@ def main():
         "gemv_multi_block_g64": gemv_multi_block(64),
         "gemv_multi_block_g128": gemv_multi_block(128),
         "dequant_block": dequant_block(),
+        "rotor_defaults": rotor_defaults(),
         "staf_roundtrip_single": staf_roundtrip_single(),
         "staf_roundtrip_multi": staf_roundtrip_multi(),
         "attention_pattern": attention_pattern(),

@@ -379,7 +379,7 @@ def quantise_rows_restated(x, bits, group):
     return (scale.astype(np.float16).astype(np.float64) * q + lo.astype(np.float16).astype(np.float64)).reshape(np.shape(x))
 
 
-def test_rotor_and_projection_defaults_follow_the_reference_rule(pkg, oracle):
+def test_rotor_and_projection_defaults_follow_the_reference_rule(pkg, oracle, golden):
     """Deterministic unit rotors and the +-1/sqrt(m) matrix (RotorQuantCorrectnessTests: 'Random rotors are unit
     quaternions, non-identity, and deterministic', 'Rademacher matrix contains only +-1/sqrt(m) values')."""
     KV, D, L, QJL = 2, 64, 3, 16
@@ -399,6 +399,13 @@ def test_rotor_and_projection_defaults_follow_the_reference_rule(pkg, oracle):
     assert np.array_equal(phi, rademacher_restated(D, QJL))
     vals = phi.view(np.float16).astype(np.float64)
     assert np.allclose(np.abs(vals), 1.0 / np.sqrt(QJL), rtol=1e-3) and (vals > 0).any() and (vals < 0).any()
+    # the committed vectors (tests/golden/make_golden.py draws them in Python integers): rotor i and matrix entry i depend
+    # on i alone, so the first ones of any shape are the same
+    g = golden["rotor_defaults"]
+    assert got[:len(g["rotors_f16_bits"])].tolist() == g["rotors_f16_bits"]
+    small = oracle.model(pkg.BuffersDesc(hidden=4 * D, slot_dim=4 * D, vocab=8, max_seq=8, max_batch=1, kv_layers=1, kv_heads=1, head_dim=D,
+                                         conv_layers=0, conv_dim=0, conv_kernel=0, kv_scheme=0x70, kv_qjl_dim=g["qjl"]))
+    assert small.qjl_matrix().reshape(-1)[:len(g["matrix_f16_bits"])].tolist() == g["matrix_f16_bits"]
     # sizing contract (rotorParameterBufferSizing, qjlBufferSizing): bytes per layer
     assert got[: KV * groups].nbytes == KV * groups * 4 * 2 and phi.nbytes == D * QJL * 2
 
